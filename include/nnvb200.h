@@ -1,0 +1,230 @@
+/*
+ * nnvb200.h — C ABI of libnnvb200.so, the sm_100a engine for the approx-star
+ * (estimated-bounds) reachability path of NNV.
+ *
+ * Everything crosses this boundary as plain pointers and sizes.  All floating
+ * point is IEEE double; all tensors use MATLAB's column-major layout, i.e. an
+ * image-shaped set is V[h + H*(w + W*(c + C*j))] for predicate column j
+ * (j = 0 is the centre), exactly what mxGetDoubles returns for the reference's
+ * ImageStar.V.  Indices are 0-based here; the MEX gateway converts.
+ *
+ * Every function returns an nnvb_status (0 = NNVB_OK); nothing throws, nothing
+ * calls back.  Host buffers stay owned by the caller and are only read unless
+ * the parameter is documented as an output.  Device memory lives behind the
+ * opaque handles and is released by the matching *_destroy.
+ *
+ * Citations name the reference interface each entry point stands in for
+ * (paths relative to the reference repository).
+ */
+#ifndef NNVB200_H
+#define NNVB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    NNVB_OK = 0,
+    NNVB_E_ARG = 1,        /* bad argument / inconsistent dimensions (the reference raises error(...)) */
+    NNVB_E_CUDA = 2,       /* a CUDA runtime call failed; see nnvb_last_error */
+    NNVB_E_CAPACITY = 3,   /* the set outgrew the context's arena; retry with a smaller batch or bigger arena */
+    NNVB_E_STATE = 4,      /* call order violated (e.g. results requested before reach) */
+    NNVB_E_UNSUPPORTED = 5 /* layer type / option outside the engine's path */
+} nnvb_status;
+
+typedef struct nnvb_ctx nnvb_ctx;
+typedef struct nnvb_net nnvb_net;
+typedef struct nnvb_batch nnvb_batch;
+
+/* ---- layer descriptions ------------------------------------------------- */
+
+typedef enum {
+    NNVB_LAYER_CONV2D = 1,   /* code/nnv/engine/nn/layers/Conv2DLayer.m */
+    NNVB_LAYER_FC = 2,       /* code/nnv/engine/nn/layers/FullyConnectedLayer.m */
+    NNVB_LAYER_BN = 3,       /* code/nnv/engine/nn/layers/BatchNormalizationLayer.m */
+    NNVB_LAYER_AVGPOOL2D = 4,/* code/nnv/engine/nn/layers/AveragePooling2DLayer.m */
+    NNVB_LAYER_RELU = 5      /* code/nnv/engine/nn/layers/ReluLayer.m */
+} nnvb_layer_type;
+
+/* One layer.  Parameter layouts are the reference's own:
+ *   CONV2D   W[kh,kw,Cin,Cout] column-major, b[Cout], pad = [t b l r], stride, dilation
+ *            (Conv2DLayer.m:84-144)
+ *   FC       W[Out,In] column-major, b[Out]; In is indexed h-fastest
+ *            (FullyConnectedLayer.m:56-66, :312)
+ *   BN       mean/var/scale/offset[C], eps (BatchNormalizationLayer.m:311-327)
+ *   AVGPOOL  pool[2], stride[2], pad[4]; zero padding counts in the divisor
+ *            (AveragePooling2DLayer.m:378-386)
+ *   RELU     no parameters
+ * Unused fields are ignored. */
+typedef struct {
+    int32_t type;
+    int32_t kh, kw, cin, cout;       /* conv: filter dims; fc: cout = Out, cin = In */
+    int32_t pad[4];                  /* t b l r */
+    int32_t stride[2];
+    int32_t dilation[2];
+    int32_t pool[2];
+    const double* W;
+    const double* b;
+    const double* bn_mean;
+    const double* bn_var;
+    const double* bn_scale;
+    const double* bn_offset;
+    double bn_eps;
+} nnvb_layer_desc;
+
+/* ---- options and statistics -------------------------------------------- */
+
+/* Counterpart of the reachOptions struct parsed in NN.reach (NN.m:189-247).
+ * Only the LP-free bound mode exists here: reachMethod 'approx-star' with
+ * estimated ranges == 'relax-star-*' with relaxFactor = 1 (PosLin.m:1588-1646). */
+typedef struct {
+    int32_t keep_constraints;  /* 1: record the rows needed to emit C,d (Star.C / Star.d) */
+    int32_t keep_layer_bounds; /* 1: keep lb/ub and crossing lists of every ReLU layer for download */
+    int32_t reserved[6];
+} nnvb_opts;
+
+/* Per-ReLU-layer counters summed over the batch; maps onto the reference's
+ * per-layer tic/toc record obj.reachTime (NN.m:1542-1545). */
+typedef struct {
+    int64_t n_neurons;   /* N of the layer */
+    int64_t n_cross;     /* crossing neurons, summed over queries */
+    int64_t n_dead;      /* ub <= 0 neurons, summed over queries */
+    int64_t cols_after;  /* total columns in the batch after the layer */
+} nnvb_relu_stats;
+
+/* ---- context ------------------------------------------------------------ */
+
+/* Bind a context to one CUDA device and reserve `arena_bytes` of device memory
+ * for set tensors (two ping-pong generator buffers plus records).  One context
+ * per process per GPU; mirrors the reference's reachOptions.device switch
+ * (NN.m:216-222) and params2gpu (NN.m:1257-1263). */
+int nnvb_init(int device, size_t arena_bytes, nnvb_ctx** out);
+int nnvb_destroy(nnvb_ctx* ctx);
+/* Text of the most recent failure on this thread (never NULL). */
+const char* nnvb_last_error(void);
+const char* nnvb_strerror(int status);
+/* Version of this ABI; bumps when a signature changes. */
+int nnvb_abi_version(void);
+/* The stream every kernel of the context is launched on (a cudaStream_t cast
+ * to void*), so a host harness can record events on it. */
+void* nnvb_stream(nnvb_ctx* ctx);
+/* Number of kernels this library has launched on the context so far. */
+int64_t nnvb_launch_count(nnvb_ctx* ctx);
+
+/* ---- network ------------------------------------------------------------ */
+
+/* Copy the layer parameters to the device once and pre-arrange them for the
+ * kernels.  Stands in for constructing NN({layers...}) (NN.m:99-105) followed by
+ * params2gpu.  (in_h,in_w,in_c) is the input image size; a vector input of
+ * length n is (n,1,1). */
+int nnvb_net_create(nnvb_ctx* ctx, const nnvb_layer_desc* layers, int n_layers,
+                    int64_t in_h, int64_t in_w, int64_t in_c, nnvb_net** out);
+int nnvb_net_destroy(nnvb_net* net);
+/* Output size (H,W,C) of the network. */
+int nnvb_net_out_shape(const nnvb_net* net, int64_t shape[3]);
+
+/* ---- batches of input sets ---------------------------------------------- */
+
+/* A batch is a list of independent input sets (queries) pushed through the same
+ * network together; a single NN.reach call is a batch of one.  Stands in for
+ * the array-of-sets handling of reach_star_multipleInputs
+ * (e.g. Conv2DLayer.m:862-886). */
+int nnvb_batch_create(nnvb_net* net, int n_queries, nnvb_batch** out);
+int nnvb_batch_destroy(nnvb_batch* b);
+
+/* Query q := ImageStar(lb, ub) (ImageStar.m:302-343 -> Star.m:220-237 ->
+ * Box.m:16-58): centre (lb+ub)/2, one generator per entry with ub != lb, each
+ * predicate in [-1,1], C = zeros(1,P), d = 0.  lb/ub have H*W*C entries. */
+int nnvb_batch_set_bounds(nnvb_batch* b, int q, const double* lb, const double* ub);
+
+/* Query q := ImageStar(V, C, d, pred_lb, pred_ub) (ImageStar.m:172-227).
+ * V is [N x (P+1)] column-major, Cmat is [m x P] column-major (may be NULL when
+ * m = 0), pl/pu have P entries.  C and d are kept on the host side of the
+ * record: no layer reads them (they only enter the final feasibility system). */
+int nnvb_batch_set_star(nnvb_batch* b, int q, int64_t P, const double* V,
+                        const double* pl, const double* pu,
+                        int64_t m, const double* Cmat, const double* d);
+
+/* Copy all staged queries to the device (asynchronous on the context stream). */
+int nnvb_batch_upload(nnvb_batch* b);
+
+/* Run every layer on the uploaded batch: NN.reach / reach_noConns
+ * (NN.m:189-278, :1529-1551) with the LP-free ReLU step.  Can be called again
+ * on the same uploaded inputs. */
+int nnvb_batch_reach(nnvb_batch* b, const nnvb_opts* opts);
+
+/* ---- results of a reach -------------------------------------------------- */
+
+/* Number of predicates P and of constraint rows m of query q's output set. */
+int nnvb_batch_out_dims(const nnvb_batch* b, int q, int64_t* P, int64_t* m);
+/* Output generator matrix of query q, [N_out x (P+1)] column-major, columns in
+ * the reference's predicate order (ImageStar.V of the returned set). */
+int nnvb_batch_get_V(nnvb_batch* b, int q, double* V);
+/* pred_lb / pred_ub of the output set (P entries each). */
+int nnvb_batch_get_pred_bounds(nnvb_batch* b, int q, double* pl, double* pu);
+/* Star.estimateRanges (Star.m:1078-1106) of the output set: N_out entries each. */
+int nnvb_batch_get_ranges(nnvb_batch* b, int q, double* lb, double* ub);
+/* Dense constraint system [m x P] column-major and d[m] of the output set, as
+ * PosLin.multipleStepReachStarApprox_at_one stacks it (PosLin.m:711-735).
+ * Requires opts.keep_constraints. */
+int nnvb_batch_get_constraints(nnvb_batch* b, int q, double* Cmat, double* d);
+/* Number of ReLU layers, and the per-layer counters. */
+int nnvb_batch_relu_layers(const nnvb_batch* b, int* n);
+int nnvb_batch_relu_stats(const nnvb_batch* b, int relu_layer, nnvb_relu_stats* st);
+/* Crossing neurons of query q at ReLU layer `relu_layer`: count, then (when the
+ * pointers are non-NULL) their ascending 0-based linear indices and estimated
+ * bounds — map2 / lb / ub of PosLin.m:1598-1607.  Requires opts.keep_layer_bounds. */
+int nnvb_batch_get_crossing(nnvb_batch* b, int q, int relu_layer, int64_t* k,
+                            int64_t* idx, double* lb, double* ub);
+/* Estimated bounds of all N neurons of query q entering ReLU layer `relu_layer`. */
+int nnvb_batch_get_layer_ranges(nnvb_batch* b, int q, int relu_layer, double* lb, double* ub);
+
+/* ---- output specification ------------------------------------------------ */
+
+/* Verdict codes follow verify_specification.m: 1 = every halfspace
+ * intersection is empty (robust / safe), 2 = some intersection is non-empty
+ * (unknown for an over-approximation).  NNVB_UNDECIDED marks a halfspace the
+ * device-side tests could not settle; the caller finishes it with the
+ * feasibility LP of Star.isEmptySet (Star.m:1216-1232). */
+#define NNVB_VERDICT_EMPTY 1
+#define NNVB_VERDICT_NONEMPTY 2
+#define NNVB_UNDECIDED (-1)
+
+/* For query q and halfspaces G x <= g (G is [nh x N_out] column-major): the
+ * minimum of G x - g over the output set's predicate box, one value per
+ * halfspace.  A positive value proves Star.intersectHalfSpace (Star.m:555-589)
+ * empty without an LP.  status[h] receives NNVB_VERDICT_EMPTY or NNVB_UNDECIDED. */
+int nnvb_batch_halfspace_margins(nnvb_batch* b, int q, const double* G, const double* g,
+                                 int nh, double* margin_lo, int* status);
+
+/* Robustness form of the same test for the whole batch: for query q the
+ * halfspaces are NN.robustness_set(target[q], kind) (NN.m:1334-1368), kind 0 =
+ * 'max', 1 = 'min'.  status is [n_queries x (N_out-1)] row-major per query;
+ * margin_lo likewise (may be NULL).  verdict[q] = 1 when all are empty, else
+ * NNVB_UNDECIDED. */
+int nnvb_batch_verify_robust(nnvb_batch* b, const int32_t* target, int kind,
+                             int* verdict, int* status, double* margin_lo);
+
+/* ---- single-layer entry points ------------------------------------------- */
+
+/* One layer applied to one host-resident set, result back on the host:
+ * L.reach(in_set, 'approx-star') for the affine layers
+ * (Conv2DLayer.m:559-601, FullyConnectedLayer.m:295-317,
+ * BatchNormalizationLayer.m:287-329, AveragePooling2DLayer.m:424-438).
+ * V_in is [H*W*C x ncols] column-major (column 0 = centre), V_out must hold
+ * Ho*Wo*Co x ncols doubles; out_shape receives (Ho,Wo,Co). */
+int nnvb_layer_apply(nnvb_ctx* ctx, const nnvb_layer_desc* layer,
+                     int64_t H, int64_t W, int64_t C, int64_t ncols,
+                     const double* V_in, double* V_out, int64_t out_shape[3]);
+
+/* Star.estimateRanges on a host-resident set: V is [N x (P+1)]. */
+int nnvb_estimate_ranges(nnvb_ctx* ctx, int64_t N, int64_t P, const double* V,
+                         const double* pl, const double* pu, double* lb, double* ub);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NNVB200_H */

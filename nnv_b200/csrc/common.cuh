@@ -1,0 +1,169 @@
+// Shared declarations of the sm_100a engine: error plumbing, device helpers
+// and the launch signatures of the kernels (one .cu file per kernel family).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stddef.h>
+
+#include "../../include/nnvb200.h"
+
+namespace nnvb {
+
+void set_error(const char* fmt, ...);
+
+#define NNVB_CUDA(call)                                                          \
+    do {                                                                         \
+        cudaError_t e_ = (call);                                                 \
+        if (e_ != cudaSuccess) {                                                 \
+            nnvb::set_error("%s failed at %s:%d: %s", #call, __FILE__, __LINE__, \
+                            cudaGetErrorString(e_));                             \
+            return NNVB_E_CUDA;                                                  \
+        }                                                                        \
+    } while (0)
+
+#define NNVB_TRY(call)                  \
+    do {                                \
+        int s_ = (call);                \
+        if (s_ != NNVB_OK) return s_;   \
+    } while (0)
+
+#define NNVB_REQUIRE(cond, ...)         \
+    do {                                \
+        if (!(cond)) {                  \
+            nnvb::set_error(__VA_ARGS__); \
+            return NNVB_E_ARG;          \
+        }                               \
+    } while (0)
+
+static inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+static inline int64_t ceil_div(int64_t x, int64_t m) { return (x + m - 1) / m; }
+
+// Leading dimension (doubles) of a generator matrix with N rows: columns start
+// on 128-byte lines for large N, on 16-byte boundaries always.
+static inline int64_t lead_dim(int64_t N) { return N >= 64 ? round_up(N, 16) : round_up(N, 2); }
+
+// ---------------------------------------------------------------------------
+// Kernel launch wrappers.  Every wrapper enqueues on `st`, returns the number of
+// kernels it launched through *launches (added), and reports launch errors.
+
+struct ConvGeom {
+    int H, W, Cin;          // input image
+    int Ho, Wo, Cout;       // output image
+    int kh, kw;
+    int pad_t, pad_l;
+    int sh, sw, dh, dw;
+};
+
+// Pre-arranged convolution weights (see conv_f64.cu for the layout).
+struct ConvWeights {
+    double* w;              // device, arranged [n_tile][ci_chunk][tap][KC][CS]
+    double* bias;           // device [Cout]
+    int bn_tile;            // output channels per CTA tile (32, 64 or 128)
+    int cs;                 // padded channel stride in shared memory (doubles)
+    int n_tiles;            // ceil(Cout / bn_tile)
+    int n_chunks;           // ceil(Cin / KC)
+};
+
+// Optional per-channel affine fused behind a contraction (BatchNormalization
+// in eval mode): centre: ((x - mean) / den) * scale + offset, generators:
+// (x / den) * scale.  All pointers device, length = channels; null = off.
+struct ChanAffine {
+    const double* mean;
+    const double* den;      // sqrt(var + eps)
+    const double* scale;
+    const double* offset;
+};
+
+size_t conv_weights_doubles(const ConvGeom& g, int* bn_tile, int* cs, int* n_tiles, int* n_chunks);
+// Host-side re-layout of W[kh,kw,Cin,Cout] (column-major) into the kernel's layout.
+void conv_arrange_weights(const ConvGeom& g, const double* W, double* dst, int bn_tile, int cs,
+                          int n_tiles, int n_chunks);
+
+int launch_conv_f64(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
+                    const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
+                    int64_t ncols, int64_t n_center, int64_t* launches);
+
+// FC: Vout[Out x ncols] = W * Vin[In x ncols]; bias (and the optional affine) on
+// the first n_center columns.  Wt is the device copy arranged [In_pad][ldw]
+// (ldw = Out rounded up to 8, zero filled).
+int launch_fc_f64(cudaStream_t st, int In, int Out, const double* Wt, int ldw, const double* bias,
+                  const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out, int64_t ncols,
+                  int64_t n_center, int64_t* launches);
+
+// Per-channel affine (BatchNormalization) in place on V[N x ncols]; channel of
+// row i is i / plane (plane = H*W).
+int launch_bn_f64(cudaStream_t st, const ChanAffine& bn, int64_t plane, int64_t N, double* V,
+                  int64_t ld, int64_t ncols, int64_t n_center, int64_t* launches);
+
+struct PoolGeom {
+    int H, W, C, Ho, Wo;
+    int ph, pw, sh, sw, pad_t, pad_l;
+};
+int launch_avgpool_f64(cudaStream_t st, const PoolGeom& g, const double* Vin, int64_t ld_in,
+                       double* Vout, int64_t ld_out, int64_t ncols, int64_t* launches);
+
+// ReLU approx-star step; see relu_star.cu.  All pointers are device pointers.
+struct ReluWork {
+    int nq;
+    int64_t N, ld;
+    double* V;                 // [ld x ncols]; column q (< nq) is the centre of query q
+    const int64_t* qcol_off;   // [nq+1] offsets into qcol_idx
+    const int32_t* qcol_idx;   // predicate-ordered generator columns of each query
+    const double* pl;          // [ncols] predicate bounds by column
+    const double* pu;
+    // chunk list for the bound reduction
+    int n_chunks;
+    const int64_t* chunk_beg;  // [n_chunks] positions in qcol_idx
+    const int64_t* chunk_end;
+    const int32_t* q_chunk_off;// [nq+1] chunks of query q are q_chunk_off[q] .. q_chunk_off[q+1]
+    double* partial;           // [n_chunks][2][N]
+    // outputs
+    double* lb;                // [nq][N]
+    double* ub;                // [nq][N]
+    uint8_t* state;            // [nq][N] 0 keep, 1 dead, 2 crossing
+    int32_t* rank;             // [nq][N] rank of a crossing neuron within its query
+    int32_t* blk_cross;        // [nq][blocks] crossing count per row block, then its exclusive scan
+    int64_t* q_cross;          // [nq] crossing count per query
+    int64_t* q_dead;           // [nq]
+    int64_t* q_new_off;        // [nq+1] exclusive scan of q_cross
+};
+// Per-layer record of the appended columns (K = total crossing neurons of the batch).
+struct ReluRecord {
+    int32_t* idx;              // [K] neuron index of new column c
+    int32_t* q;                // [K] its query
+    double* c;                 // [K] centre value of the row before zeroing
+    double* l;                 // [K] estimated lower bound
+    double* u;                 // [K] estimated upper bound
+    double* G;                 // crossing rows before zeroing, per query a [k_q x P_q] column-major block (null: not kept)
+    int64_t* G_off;            // [nq] start of each block
+};
+int relu_blocks_per_query(int64_t N);
+int launch_estimate_ranges(cudaStream_t st, const ReluWork& w, int64_t* launches);
+int launch_classify_scan(cudaStream_t st, const ReluWork& w, int64_t* launches);
+int launch_rank_cross(cudaStream_t st, const ReluWork& w, const ReluRecord& rec, int64_t* launches);
+// Zero dead and crossing rows in all existing columns; save crossing rows.
+int launch_relu_zero_rows(cudaStream_t st, const ReluWork& w, int64_t ncols, const int32_t* col_q,
+                          const ReluRecord& rec, const int64_t* col_pos, int64_t* launches);
+// Append one one-hot column per crossing neuron with its predicate bounds and
+// rebuild the per-query column lists.
+int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, int64_t K,
+                       const ReluRecord& rec, int32_t* col_q, double* pl, double* pu, int64_t* col_pos,
+                       int64_t* new_qcol_off, int32_t* new_qcol_idx, int64_t* launches);
+
+// Halfspace rows: r[h][col] = sum_o G[h][o] * V[o][col], then the box minimum.
+// Block b handles query q_base + b; G, g and margin are indexed by b.
+int launch_halfspace_margins(cudaStream_t st, int nq, int q_base, int64_t Nout, int64_t ld, const double* V,
+                             const int64_t* qcol_off, const int32_t* qcol_idx, const double* pl,
+                             const double* pu, const double* G /*[nq][nh][Nout]*/,
+                             const double* g /*[nq][nh]*/, int nh, double* margin /*[nq][nh]*/,
+                             int64_t* launches);
+
+// Build the dense input set of a bounds-form query batch.
+int launch_build_from_bounds(cudaStream_t st, int nq, int64_t N, int64_t ld, const double* lbub,
+                             const int64_t* q_gen_off, double* V, int32_t* col_q, double* pl,
+                             double* pu, int32_t* qcol_idx, int64_t* col_pos, int64_t* launches);
+int launch_count_bounds(cudaStream_t st, int nq, int64_t N, const double* lbub, int64_t* q_count,
+                        int64_t* launches);
+
+}  // namespace nnvb

@@ -1,0 +1,367 @@
+// Conv2D layer over every generator slice at once as an implicit GEMM:
+//   out(oh,ow,co,j) = sum_{kh,kw,ci} in(oh*sh - pt + kh*dh, ow*sw - pl + kw*dw, ci, j) * W(kh,kw,ci,co)
+// bias on the centre slices only (Conv2DLayer.reach_star_single_input,
+// Conv2DLayer.m:591-596; arithmetic of compute_featureMap, :1180-1197).
+// An optional per-channel affine (the BatchNormalization layer that follows,
+// BatchNormalizationLayer.m:311-327) is applied in the epilogue in the
+// reference's operation order.
+//
+// Dense FP64 contraction on the DMMA tensor path:
+//   M = output positions of a tile (TH x TW patch of NJ generator columns),
+//   N = output channels (BN_TILE per CTA), K = taps x input channels.
+// Per K chunk of KC = 8 input channels a stage holds
+//   - the input halo of the tile, [KC][NJ][HW][HH] with h fastest (the set's own
+//     layout, so global reads run along h), fetched with 8-byte cp.async and
+//     zero-filled outside the image;
+//   - the weights of the chunk, [tap][KC][CS], one contiguous pre-arranged block.
+// The per-channel halo stride PS and the channel stride CS are = 4 (mod 8)
+// doubles, which makes the A and B fragment reads bank-conflict free for
+// stride-1 convolutions.  Every tap reuses the staged halo, so global traffic
+// is that of the input itself, not of an im2col matrix.
+#include "common.cuh"
+#include "mma_f64.cuh"
+
+#include <algorithm>
+#include <vector>
+
+namespace nnvb {
+
+namespace {
+
+constexpr int KC = 8;   // input channels per K chunk
+
+struct ConvParams {
+    ConvGeom g;
+    int TH, TW, NJ;        // output tile: TH x TW positions of NJ columns
+    int HH, HW;            // halo height / width
+    int plane;             // NJ * HH * HW
+    int PS;                // per-channel halo stride (doubles), = 4 mod 8
+    int CS;                // weight channel stride (doubles)
+    int n_th, n_tw;        // spatial tiles per image
+    int n_chunks;
+    int taps;
+    int halo_stage;        // doubles
+    int w_stage;           // doubles
+    int64_t col_groups;    // ceil(ncols / NJ)
+};
+
+template <int WM_TILES, int WN_TILES, int WARPS_M, int WARPS_N, int STAGES>
+__global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, 1)
+conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double* __restrict__ bias,
+                const ChanAffine bn, const double* __restrict__ Vin, int64_t ld_in,
+                double* __restrict__ Vout, int64_t ld_out, int64_t ncols, int64_t n_center) {
+    constexpr int BM = WARPS_M * WM_TILES * 16;
+    constexpr int BN = WARPS_N * WN_TILES * 8;
+    constexpr int THREADS = WARPS_M * WARPS_N * 32;
+    constexpr int NWARPS = WARPS_M * WARPS_N;
+
+    extern __shared__ __align__(16) double smem[];
+    double* halo = smem;                                  // [STAGES][halo_stage]
+    double* wts = smem + STAGES * p.halo_stage;           // [STAGES][w_stage]
+    int* gtab = reinterpret_cast<int*>(wts + STAGES * p.w_stage);   // [plane]
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int wm = warp % WARPS_M;
+    const int wn = warp / WARPS_M;
+    const int g = lane >> 2;
+    const int t = lane & 3;
+
+    // tile coordinates: spatial tiles fastest, then column groups
+    const int sp_tiles = p.n_th * p.n_tw;
+    const int64_t cg = blockIdx.x / sp_tiles;
+    const int sp = int(blockIdx.x % sp_tiles);
+    const int oh0 = (sp % p.n_th) * p.TH;
+    const int ow0 = (sp / p.n_th) * p.TW;
+    const int64_t j0 = cg * p.NJ;
+    const int n_tile = blockIdx.y;
+    const int n0 = n_tile * BN;
+
+    const int H = p.g.H, W = p.g.W;
+    const int hw_in = H * W;
+
+    // table: halo element r -> offset in the input relative to column j0, channel 0
+    for (int r = tid; r < p.plane; r += THREADS) {
+        const int jl = r / (p.HH * p.HW);
+        const int r2 = r - jl * (p.HH * p.HW);
+        const int wl = r2 / p.HH;
+        const int hl = r2 - wl * p.HH;
+        const int hi = oh0 * p.g.sh - p.g.pad_t + hl;
+        const int wi = ow0 * p.g.sw - p.g.pad_l + wl;
+        int off = -1;
+        if (hi >= 0 && hi < H && wi >= 0 && wi < W && j0 + jl < ncols)
+            off = int(jl * ld_in) + hi + H * wi;
+        gtab[r] = off;
+    }
+    __syncthreads();
+
+    const double* in_base = Vin + j0 * ld_in;
+    const int64_t w_block = int64_t(p.w_stage);
+    const double* w_base = Wg + (int64_t(n_tile) * p.n_chunks) * w_block;
+
+    auto load_stage = [&](int stage, int chunk) {
+        double* hs = halo + stage * p.halo_stage;
+        // each warp fetches the halo planes of channels warp, warp+NWARPS, ...
+        for (int cil = warp; cil < KC; cil += NWARPS) {
+            const int ci = chunk * KC + cil;
+            const bool ci_ok = ci < p.g.Cin;
+            const double* src_c = in_base + int64_t(ci_ok ? ci : 0) * hw_in;
+            double* dst_c = hs + cil * p.PS;
+            for (int r = lane; r < p.plane; r += 32) {
+                const int off = gtab[r];
+                const bool ok = ci_ok && off >= 0;
+                cp_async8(dst_c + r, ok ? (src_c + off) : Vin, ok ? 8 : 0);
+            }
+        }
+        double* ws = wts + stage * p.w_stage;
+        const double* wsrc = w_base + int64_t(chunk) * w_block;
+        for (int c = tid; c < p.w_stage / 2; c += THREADS) cp_async16(ws + 2 * c, wsrc + 2 * c, 16);
+    };
+
+    // shared-memory base of the rows this lane owns in each m16 tile
+    int rowbase[WM_TILES][2];
+#pragma unroll
+    for (int mi = 0; mi < WM_TILES; ++mi) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            int m = wm * WM_TILES * 16 + mi * 16 + g + half * 8;
+            const int per_col = p.TH * p.TW;
+            int jl = m / per_col;
+            int rem = m - jl * per_col;
+            int owl = rem / p.TH;
+            int ohl = rem - owl * p.TH;
+            if (jl >= p.NJ) { jl = 0; owl = 0; ohl = 0; }   // padding rows read a valid address
+            rowbase[mi][half] = jl * (p.HH * p.HW) + (owl * p.g.sw) * p.HH + ohl * p.g.sh;
+        }
+    }
+
+    double acc[WM_TILES][WN_TILES][4];
+#pragma unroll
+    for (int mi = 0; mi < WM_TILES; ++mi)
+#pragma unroll
+        for (int ni = 0; ni < WN_TILES; ++ni)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) acc[mi][ni][r] = 0.0;
+
+    const int NCH = p.n_chunks;
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < NCH) load_stage(s, s);
+        cp_async_commit();
+    }
+
+    for (int ch = 0; ch < NCH; ++ch) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();
+        {
+            const int nc = ch + STAGES - 1;
+            if (nc < NCH) load_stage(nc % STAGES, nc);
+            cp_async_commit();
+        }
+        const double* hs = halo + (ch % STAGES) * p.halo_stage + t * p.PS;
+        const double* ws = wts + (ch % STAGES) * p.w_stage + t * p.CS + wn * WN_TILES * 8 + g;
+        int tap = 0;
+        for (int kwi = 0; kwi < p.g.kw; ++kwi) {
+            for (int khi = 0; khi < p.g.kh; ++khi, ++tap) {
+                // tap index follows W's memory order (kh fastest)
+                const int tapoff = (kwi * p.g.dw) * p.HH + khi * p.g.dh;
+                const double* wt = ws + tap * (KC * p.CS);
+                double af[WM_TILES][4];
+                double bf[WN_TILES][2];
+#pragma unroll
+                for (int mi = 0; mi < WM_TILES; ++mi) {
+                    const double* p0 = hs + rowbase[mi][0] + tapoff;
+                    const double* p1 = hs + rowbase[mi][1] + tapoff;
+                    af[mi][0] = p0[0];
+                    af[mi][1] = p1[0];
+                    af[mi][2] = p0[4 * p.PS];
+                    af[mi][3] = p1[4 * p.PS];
+                }
+#pragma unroll
+                for (int ni = 0; ni < WN_TILES; ++ni) {
+                    bf[ni][0] = wt[ni * 8];
+                    bf[ni][1] = wt[ni * 8 + 4 * p.CS];
+                }
+#pragma unroll
+                for (int mi = 0; mi < WM_TILES; ++mi)
+#pragma unroll
+                    for (int ni = 0; ni < WN_TILES; ++ni) dmma_16x8x8(acc[mi][ni], af[mi], bf[ni]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+    // epilogue
+    const int Ho = p.g.Ho, Wo = p.g.Wo, Cout = p.g.Cout;
+    const int64_t hw_out = int64_t(Ho) * Wo;
+#pragma unroll
+    for (int mi = 0; mi < WM_TILES; ++mi) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int m = wm * WM_TILES * 16 + mi * 16 + g + half * 8;
+            const int per_col = p.TH * p.TW;
+            const int jl = m / per_col;
+            const int rem = m - jl * per_col;
+            const int owl = rem / p.TH;
+            const int ohl = rem - owl * p.TH;
+            const int oh = oh0 + ohl, ow = ow0 + owl;
+            const int64_t j = j0 + jl;
+            if (jl >= p.NJ || oh >= Ho || ow >= Wo || j >= ncols) continue;
+            const bool is_center = j < n_center;
+            double* dst = Vout + j * ld_out + oh + int64_t(Ho) * ow;
+#pragma unroll
+            for (int ni = 0; ni < WN_TILES; ++ni) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int co = n0 + wn * WN_TILES * 8 + ni * 8 + 2 * t + e;
+                    if (co >= Cout) continue;
+                    double v = acc[mi][ni][half * 2 + e];
+                    if (is_center) v += bias[co];
+                    if (bn.den != nullptr) {
+                        if (is_center) v = v - bn.mean[co];
+                        v = (v * 1.0) / bn.den[co];
+                        v = v * bn.scale[co];
+                        if (is_center) v = v + bn.offset[co];
+                    }
+                    dst[hw_out * co] = v;
+                }
+            }
+        }
+    }
+}
+
+int pad_stride(int n) {            // smallest s >= n with s = 4 (mod 8)
+    int s = (n + 7) / 8 * 8 + 4;
+    if (s - 8 >= n) s -= 8;
+    return s;
+}
+
+int pick_bn_tile(int Cout) { return Cout <= 16 ? 16 : (Cout <= 32 ? 32 : 64); }
+
+void pick_tile(const ConvGeom& g, int BM, int* TH, int* TW, int* NJ) {
+    const int per_img = g.Ho * g.Wo;
+    if (per_img * 2 <= BM) {       // several columns per tile
+        *TH = g.Ho;
+        *TW = g.Wo;
+        *NJ = BM / per_img;
+        return;
+    }
+    *NJ = 1;
+    double best = -1.0;
+    for (int th = 1; th <= std::min(g.Ho, BM); ++th) {
+        int tw = std::min(g.Wo, BM / th);
+        if (tw < 1) continue;
+        const int64_t tiles = ceil_div(g.Ho, th) * ceil_div(g.Wo, tw);
+        double eff = double(per_img) / double(tiles * BM);
+        // prefer tall tiles (longer runs along the contiguous axis) on ties
+        eff += 1e-6 * th;
+        if (eff > best) { best = eff; *TH = th; *TW = tw; }
+    }
+}
+
+template <int WM_TILES, int WN_TILES, int WARPS_M, int WARPS_N>
+int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
+               const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out, int64_t ncols,
+               int64_t n_center) {
+    constexpr int BM = WARPS_M * WM_TILES * 16;
+    constexpr int BN = WARPS_N * WN_TILES * 8;
+    constexpr int THREADS = WARPS_M * WARPS_N * 32;
+    ConvParams p;
+    p.g = g;
+    pick_tile(g, BM, &p.TH, &p.TW, &p.NJ);
+    p.HH = (p.TH - 1) * g.sh + (g.kh - 1) * g.dh + 1;
+    p.HW = (p.TW - 1) * g.sw + (g.kw - 1) * g.dw + 1;
+    p.plane = p.NJ * p.HH * p.HW;
+    p.PS = pad_stride(p.plane);
+    p.CS = w.cs;
+    p.n_th = (int)ceil_div(g.Ho, p.TH);
+    p.n_tw = (int)ceil_div(g.Wo, p.TW);
+    p.n_chunks = w.n_chunks;
+    p.taps = g.kh * g.kw;
+    p.halo_stage = KC * p.PS;
+    p.w_stage = p.taps * KC * p.CS;
+    p.col_groups = ceil_div(ncols, p.NJ);
+    if (w.bn_tile != BN) {
+        set_error("conv: weight arrangement (%d) does not match kernel tile (%d)", w.bn_tile, BN);
+        return NNVB_E_ARG;
+    }
+    if (int64_t(p.NJ) * ld_in >= (int64_t(1) << 31)) {
+        set_error("conv: column stride too large for the tile offset table");
+        return NNVB_E_UNSUPPORTED;
+    }
+    const size_t stage_bytes = size_t(p.halo_stage + p.w_stage) * sizeof(double);
+    const size_t tab_bytes = size_t(p.plane) * sizeof(int);
+    const size_t limit = 227 * 1024;
+    const int64_t blocks = p.col_groups * p.n_th * p.n_tw;
+    if (blocks >= (int64_t(1) << 31)) {
+        set_error("conv: grid too large");
+        return NNVB_E_UNSUPPORTED;
+    }
+    dim3 grid((unsigned)blocks, (unsigned)w.n_tiles);
+    if (3 * stage_bytes + tab_bytes <= limit) {
+        auto kern = conv_f64_kernel<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 3>;
+        const size_t smem = 3 * stage_bytes + tab_bytes;
+        NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<grid, THREADS, smem, st>>>(p, w.w, w.bias, bn, Vin, ld_in, Vout, ld_out, ncols, n_center);
+    } else if (2 * stage_bytes + tab_bytes <= limit) {
+        auto kern = conv_f64_kernel<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 2>;
+        const size_t smem = 2 * stage_bytes + tab_bytes;
+        NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<grid, THREADS, smem, st>>>(p, w.w, w.bias, bn, Vin, ld_in, Vout, ld_out, ncols, n_center);
+    } else {
+        set_error("conv: filter %dx%d with stride (%d,%d) needs %zu bytes of shared memory per stage",
+                  g.kh, g.kw, g.sh, g.sw, stage_bytes);
+        return NNVB_E_UNSUPPORTED;
+    }
+    NNVB_CUDA(cudaGetLastError());
+    return NNVB_OK;
+}
+
+}  // namespace
+
+size_t conv_weights_doubles(const ConvGeom& g, int* bn_tile, int* cs, int* n_tiles, int* n_chunks) {
+    *bn_tile = pick_bn_tile(g.Cout);
+    *cs = *bn_tile + 4;
+    *n_tiles = (int)ceil_div(g.Cout, *bn_tile);
+    *n_chunks = (int)ceil_div(g.Cin, KC);
+    return size_t(*n_tiles) * (*n_chunks) * (g.kh * g.kw) * KC * (*cs);
+}
+
+void conv_arrange_weights(const ConvGeom& g, const double* W, double* dst, int bn_tile, int cs,
+                          int n_tiles, int n_chunks) {
+    // dst[n_tile][chunk][tap][cil][cs]; tap = kh + KH*kw (W's own order); zero padded
+    const int taps = g.kh * g.kw;
+    const size_t total = size_t(n_tiles) * n_chunks * taps * KC * cs;
+    std::fill(dst, dst + total, 0.0);
+    for (int nt = 0; nt < n_tiles; ++nt)
+        for (int ch = 0; ch < n_chunks; ++ch)
+            for (int tap = 0; tap < taps; ++tap)
+                for (int cil = 0; cil < KC; ++cil) {
+                    const int ci = ch * KC + cil;
+                    if (ci >= g.Cin) continue;
+                    double* row = dst + ((((size_t(nt) * n_chunks + ch) * taps + tap) * KC + cil) * cs);
+                    for (int n = 0; n < bn_tile; ++n) {
+                        const int co = nt * bn_tile + n;
+                        if (co >= g.Cout) break;
+                        row[n] = W[size_t(tap) + size_t(taps) * (ci + size_t(g.Cin) * co)];
+                    }
+                }
+}
+
+int launch_conv_f64(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
+                    const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
+                    int64_t ncols, int64_t n_center, int64_t* launches) {
+    if (ncols <= 0) return NNVB_OK;
+    int s;
+    if (w.bn_tile == 16)
+        s = launch_cfg<1, 2, 8, 1>(st, g, w, bn, Vin, ld_in, Vout, ld_out, ncols, n_center);
+    else if (w.bn_tile == 32)
+        s = launch_cfg<2, 2, 4, 2>(st, g, w, bn, Vin, ld_in, Vout, ld_out, ncols, n_center);
+    else
+        s = launch_cfg<2, 4, 4, 2>(st, g, w, bn, Vin, ld_in, Vout, ld_out, ncols, n_center);
+    if (s == NNVB_OK && launches) *launches += 1;
+    return s;
+}
+
+}  // namespace nnvb

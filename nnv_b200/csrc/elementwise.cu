@@ -1,0 +1,192 @@
+// Bandwidth-bound layer maps over every generator column: BatchNormalization
+// (per-channel affine), AveragePooling2D, and construction of the dense input
+// set ImageStar(lb, ub).
+#include "common.cuh"
+
+namespace nnvb {
+
+namespace {
+
+// BatchNormalizationLayer.reach_star_single_input, BatchNormalizationLayer.m:311-327:
+// c -= mean; (c,G) = ((c,G).*1)/sqrt(var+eps); (c,G) .*= scale; c += offset.
+// One thread per pair of rows, grid.y walks the columns.
+__global__ void bn_f64_kernel(ChanAffine bn, int64_t plane, int64_t N, double* __restrict__ V,
+                              int64_t ld, int64_t ncols, int64_t n_center) {
+    const int64_t i = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) * 2;
+    if (i >= N) return;
+    const bool two = i + 1 < N;
+    const int64_t c0 = i / plane;
+    const int64_t c1 = two ? (i + 1) / plane : c0;
+    const double den0 = bn.den[c0], den1 = bn.den[c1];
+    const double sc0 = bn.scale[c0], sc1 = bn.scale[c1];
+    const double mu0 = bn.mean[c0], mu1 = bn.mean[c1];
+    const double of0 = bn.offset[c0], of1 = bn.offset[c1];
+    for (int64_t j = blockIdx.y; j < ncols; j += gridDim.y) {
+        double* p = V + j * ld + i;
+        const bool is_center = j < n_center;
+        if (two) {
+            double2 v = *reinterpret_cast<double2*>(p);
+            if (is_center) { v.x -= mu0; v.y -= mu1; }
+            v.x = (v.x * 1.0) / den0;
+            v.y = (v.y * 1.0) / den1;
+            v.x *= sc0;
+            v.y *= sc1;
+            if (is_center) { v.x += of0; v.y += of1; }
+            *reinterpret_cast<double2*>(p) = v;
+        } else {
+            double v = *p;
+            if (is_center) v -= mu0;
+            v = (v * 1.0) / den0;
+            v *= sc0;
+            if (is_center) v += of0;
+            *p = v;
+        }
+    }
+}
+
+// AveragePooling2DLayer.compute_averageMap, AveragePooling2DLayer.m:316-393: window sum in
+// row-major order of the window, divided by ph*pw (zero padding counted).
+// One thread per output element of a column; grid.y walks the columns.
+__global__ void avgpool_f64_kernel(PoolGeom g, const double* __restrict__ Vin, int64_t ld_in,
+                                   double* __restrict__ Vout, int64_t ld_out, int64_t ncols) {
+    const int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t n_out = int64_t(g.Ho) * g.Wo * g.C;
+    if (o >= n_out) return;
+    const int oh = int(o % g.Ho);
+    const int ow = int((o / g.Ho) % g.Wo);
+    const int c = int(o / (int64_t(g.Ho) * g.Wo));
+    const int h0 = oh * g.sh - g.pad_t;
+    const int w0 = ow * g.sw - g.pad_l;
+    const double div = double(g.ph * g.pw);
+    const int64_t cbase = int64_t(c) * g.H * g.W;
+    for (int64_t j = blockIdx.y; j < ncols; j += gridDim.y) {
+        const double* src = Vin + j * ld_in + cbase;
+        double acc = 0.0;
+        for (int a = 0; a < g.ph; ++a) {
+            const int h = h0 + a;
+            for (int b = 0; b < g.pw; ++b) {
+                const int w = w0 + b;
+                double v = 0.0;
+                if (h >= 0 && h < g.H && w >= 0 && w < g.W) v = src[h + int64_t(g.H) * w];
+                acc = acc + v;
+            }
+        }
+        Vout[j * ld_out + o] = acc / div;
+    }
+}
+
+// Number of generators of ImageStar(lb,ub): entries with ub != lb (Box.m:36-43).
+// One block per query.
+__global__ void count_bounds_kernel(int64_t N, const double* __restrict__ lbub, int64_t* q_count) {
+    const int q = blockIdx.x;
+    const double* lb = lbub + int64_t(q) * 2 * N;
+    const double* ub = lb + N;
+    int cnt = 0;
+    for (int64_t i = threadIdx.x; i < N; i += blockDim.x) cnt += (0.5 * (ub[i] - lb[i]) != 0.0 || N == 1) ? 1 : 0;
+    __shared__ int s[32];
+    for (int o = 16; o; o >>= 1) cnt += __shfl_down_sync(0xffffffffu, cnt, o);
+    if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = cnt;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        int v = threadIdx.x < (blockDim.x + 31) / 32 ? s[threadIdx.x] : 0;
+        for (int o = 16; o; o >>= 1) v += __shfl_down_sync(0xffffffffu, v, o);
+        if (threadIdx.x == 0) q_count[q] = v;
+    }
+}
+
+// Fill centre and generator columns of ImageStar(lb,ub).  One block per query:
+// centre = (lb+ub)/2; the r-th entry with nonzero half width gets generator
+// column q_gen_off[q] + r holding that half width at its row (columns are zeroed
+// beforehand).  Order of generators = ascending linear index, as diag() gives it.
+__global__ void build_from_bounds_kernel(int nq, int64_t N, int64_t ld, const double* __restrict__ lbub,
+                                         const int64_t* __restrict__ q_gen_off, double* __restrict__ V,
+                                         int32_t* __restrict__ col_q, double* __restrict__ pl,
+                                         double* __restrict__ pu, int32_t* __restrict__ qcol_idx,
+                                         int64_t* __restrict__ col_pos) {
+    const int q = blockIdx.x;
+    const double* lb = lbub + int64_t(q) * 2 * N;
+    const double* ub = lb + N;
+    const int64_t gen0 = q_gen_off[q];            // first generator column of this query (global index)
+    const int64_t list0 = gen0 - nq;              // its position in qcol_idx (generators start at column nq)
+    __shared__ int warp_cnt[32];
+    __shared__ int64_t running;
+    if (threadIdx.x == 0) running = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    for (int64_t base = 0; base < N; base += blockDim.x) {
+        const int64_t i = base + threadIdx.x;
+        double c = 0.0, hw = 0.0;
+        bool has = false;
+        if (i < N) {
+            c = 0.5 * (lb[i] + ub[i]);
+            hw = 0.5 * (ub[i] - lb[i]);
+            has = hw != 0.0 || N == 1;
+            V[int64_t(q) * ld + i] = c;
+        }
+        const unsigned bal = __ballot_sync(0xffffffffu, has);
+        if (lane == 0) warp_cnt[warp] = __popc(bal);
+        __syncthreads();
+        int before = 0;
+        for (int w = 0; w < warp; ++w) before += warp_cnt[w];
+        int total = 0;
+        for (int w = 0; w < nwarp; ++w) total += warp_cnt[w];
+        const int64_t r = running + before + __popc(bal & ((1u << lane) - 1u));
+        if (has) {
+            const int64_t col = gen0 + r;
+            V[col * ld + i] = hw;
+            col_q[col] = q;
+            pl[col] = -1.0;
+            pu[col] = 1.0;
+            qcol_idx[list0 + r] = int32_t(col);
+            col_pos[col] = r;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) running += total;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) { col_q[q] = q; pl[q] = 0.0; pu[q] = 0.0; }
+}
+
+}  // namespace
+
+int launch_bn_f64(cudaStream_t st, const ChanAffine& bn, int64_t plane, int64_t N, double* V,
+                  int64_t ld, int64_t ncols, int64_t n_center, int64_t* launches) {
+    if (ncols <= 0) return NNVB_OK;
+    const int threads = 128;
+    dim3 grid((unsigned)ceil_div(ceil_div(N, 2), threads), (unsigned)std::min<int64_t>(ncols, 65535));
+    bn_f64_kernel<<<grid, threads, 0, st>>>(bn, plane, N, V, ld, ncols, n_center);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_avgpool_f64(cudaStream_t st, const PoolGeom& g, const double* Vin, int64_t ld_in,
+                       double* Vout, int64_t ld_out, int64_t ncols, int64_t* launches) {
+    if (ncols <= 0) return NNVB_OK;
+    const int threads = 256;
+    const int64_t n_out = int64_t(g.Ho) * g.Wo * g.C;
+    dim3 grid((unsigned)ceil_div(n_out, threads), (unsigned)std::min<int64_t>(ncols, 65535));
+    avgpool_f64_kernel<<<grid, threads, 0, st>>>(g, Vin, ld_in, Vout, ld_out, ncols);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_count_bounds(cudaStream_t st, int nq, int64_t N, const double* lbub, int64_t* q_count,
+                        int64_t* launches) {
+    count_bounds_kernel<<<nq, 256, 0, st>>>(N, lbub, q_count);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_build_from_bounds(cudaStream_t st, int nq, int64_t N, int64_t ld, const double* lbub,
+                             const int64_t* q_gen_off, double* V, int32_t* col_q, double* pl,
+                             double* pu, int32_t* qcol_idx, int64_t* col_pos, int64_t* launches) {
+    build_from_bounds_kernel<<<nq, 256, 0, st>>>(nq, N, ld, lbub, q_gen_off, V, col_q, pl, pu, qcol_idx, col_pos);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+}  // namespace nnvb

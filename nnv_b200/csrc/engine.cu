@@ -1,0 +1,1264 @@
+// Host side of libnnvb200.so: contexts, networks, batches of star sets and the
+// layer loop of NN.reach (NN.m:1529-1551), all behind the C ABI of
+// include/nnvb200.h.  The arithmetic lives in the kernel files; this file
+// owns device memory, the per-query column bookkeeping and the order of
+// launches on the context's stream.
+#include "common.cuh"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+namespace nnvb {
+
+static thread_local char g_err[1024] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+// Device buffer that grows geometrically and is reused across calls, so that a
+// steady-state reach performs no allocation.
+struct DevBuf {
+    void* p = nullptr;
+    size_t cap = 0;
+    int ensure(size_t bytes, cudaStream_t st, bool keep = false) {
+        if (bytes <= cap) return NNVB_OK;
+        size_t want = std::max(bytes, cap + cap / 2);
+        want = (want + 255) / 256 * 256;
+        void* np = nullptr;
+        NNVB_CUDA(cudaStreamSynchronize(st));
+        cudaError_t e = cudaMalloc(&np, want);
+        if (e != cudaSuccess) {
+            set_error("device allocation of %zu bytes failed: %s", want, cudaGetErrorString(e));
+            cudaGetLastError();
+            return NNVB_E_CAPACITY;
+        }
+        if (keep && p && cap) NNVB_CUDA(cudaMemcpy(np, p, cap, cudaMemcpyDeviceToDevice));
+        if (p) NNVB_CUDA(cudaFree(p));
+        p = np;
+        cap = want;
+        return NNVB_OK;
+    }
+    void release() {
+        if (p) cudaFree(p);
+        p = nullptr;
+        cap = 0;
+    }
+    template <typename T>
+    T* as() const { return static_cast<T*>(p); }
+};
+
+struct PinnedBuf {
+    void* p = nullptr;
+    size_t cap = 0;
+    int ensure(size_t bytes, bool keep = false) {
+        if (bytes <= cap) return NNVB_OK;
+        size_t want = std::max(bytes, cap + cap / 2);
+        void* np = nullptr;
+        NNVB_CUDA(cudaMallocHost(&np, want));
+        if (keep && p && cap) memcpy(np, p, cap);
+        if (p) cudaFreeHost(p);
+        p = np;
+        cap = want;
+        return NNVB_OK;
+    }
+    void release() {
+        if (p) cudaFreeHost(p);
+        p = nullptr;
+        cap = 0;
+    }
+    template <typename T>
+    T* as() const { return static_cast<T*>(p); }
+};
+
+}  // namespace nnvb
+
+using namespace nnvb;
+
+struct nnvb_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    char* arena = nullptr;
+    size_t arena_bytes = 0;
+    int64_t launches = 0;
+    PinnedBuf scratch;      // small host->device traffic of the layer loop
+    size_t scratch_off = 0; // bytes of `scratch` handed out since the last stream sync
+    double* vbuf(int i) const { return reinterpret_cast<double*>(arena + (arena_bytes / 2 / 256 * 256) * i); }
+    size_t vbuf_bytes() const { return arena_bytes / 2 / 256 * 256; }
+};
+
+struct Layer {
+    int type = 0;
+    int64_t H = 0, W = 0, C = 0;       // input shape
+    int64_t Ho = 0, Wo = 0, Co = 0;    // output shape
+    ConvGeom cg{};
+    ConvWeights cw{};
+    PoolGeom pg{};
+    // fc
+    double* fc_wt = nullptr;
+    int fc_ldw = 0;
+    double* bias = nullptr;
+    // bn
+    double* bn_mean = nullptr;
+    double* bn_den = nullptr;
+    double* bn_scale = nullptr;
+    double* bn_offset = nullptr;
+    bool fused_into_prev = false;      // bn applied in the previous conv's epilogue
+    int fused_bn = -1;                 // conv: index of the bn layer it applies
+};
+
+struct nnvb_net {
+    nnvb_ctx* ctx = nullptr;
+    std::vector<Layer> layers;
+    std::vector<void*> owned;          // device allocations
+    int64_t in_shape[3] = {0, 0, 0};
+    int64_t out_shape[3] = {0, 0, 0};
+    int n_relu = 0;
+};
+
+struct ReluLayerRecord {
+    int64_t N = 0;
+    int64_t K = 0;                       // new columns over the batch
+    int64_t n_dead = 0;
+    int64_t cols_after = 0;
+    std::vector<int64_t> new_off;        // [nq+1] host copy of the per-query scan
+    std::vector<int64_t> P_in;           // [nq] predicates entering the layer
+    DevBuf idx, q, c, l, u;              // per new column
+    DevBuf G, G_off;                     // crossing rows (keep_constraints)
+    std::vector<int64_t> h_G_off;
+    DevBuf lb, ub;                       // [nq][N] (keep_layer_bounds)
+    bool has_G = false, has_bounds = false;
+    void release() {
+        idx.release(); q.release(); c.release(); l.release(); u.release();
+        G.release(); G_off.release(); lb.release(); ub.release();
+    }
+};
+
+struct nnvb_batch {
+    nnvb_net* net = nullptr;
+    int nq = 0;
+    int kind = 0;                        // 0 unset, 1 bounds form, 2 star form
+    int64_t N0 = 0, ld0 = 0;
+    // host staging
+    PinnedBuf h_in;                      // bounds: [nq][2][N0]; star: V [ld0 x ncols0]
+    std::vector<int64_t> P0;             // generators per query
+    std::vector<char> is_set;
+    std::vector<std::vector<double>> h_pl, h_pu, h_C, h_d;   // star form / constraints
+    std::vector<int64_t> m0;
+    std::vector<std::vector<double>> h_V;                    // star form staging per query
+    // device inputs
+    DevBuf d_in;                         // bounds or V
+    DevBuf d_in_meta;                    // star form: pl, pu
+    bool uploaded = false;
+    // working state
+    DevBuf col_q, pl, pu, col_pos;
+    DevBuf qcol_off[2], qcol_idx[2];
+    int list_cur = 0;
+    DevBuf chunk_beg, chunk_end, q_chunk_off, partial;
+    DevBuf lb, ub, state, rank, blk_cross, q_cross, q_dead, q_new_off, gen_off;
+    DevBuf tmp;                          // gathers for downloads
+    std::vector<int64_t> h_qcol_off;     // [nq+1]
+    int64_t ncols = 0;
+    int64_t N = 0, ld = 0;
+    int64_t shape[3] = {0, 0, 0};
+    double* V = nullptr;                 // current generator matrix (device)
+    bool reached = false;
+    nnvb_opts opts{};
+    std::vector<std::unique_ptr<ReluLayerRecord>> relu;
+    // final output ranges cache
+    bool have_out_ranges = false;
+};
+
+namespace {
+
+template <typename T>
+int upload_vec(nnvb_net* net, const std::vector<T>& v, T** out) {
+    void* d = nullptr;
+    size_t bytes = std::max<size_t>(v.size() * sizeof(T), 16);
+    NNVB_CUDA(cudaMalloc(&d, bytes));
+    net->owned.push_back(d);
+    if (!v.empty()) NNVB_CUDA(cudaMemcpy(d, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice));
+    *out = static_cast<T*>(d);
+    return NNVB_OK;
+}
+
+int capacity_error(const char* what, size_t need, size_t have) {
+    set_error("%s needs %zu bytes, generator buffer holds %zu", what, need, have);
+    return NNVB_E_CAPACITY;
+}
+
+int sync(nnvb_ctx* ctx) {
+    NNVB_CUDA(cudaStreamSynchronize(ctx->stream));
+    ctx->scratch_off = 0;   // every staged upload has landed
+    return NNVB_OK;
+}
+
+// Async H2D of a small host array through the context's pinned scratch.  Space
+// is handed out linearly and only recycled after a stream sync, so uploads that
+// are still in flight are never overwritten.
+int h2d_small(nnvb_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    if (bytes == 0) return NNVB_OK;
+    size_t o = (ctx->scratch_off + 63) / 64 * 64;
+    if (o + bytes > ctx->scratch.cap) {
+        NNVB_TRY(sync(ctx));
+        NNVB_TRY(ctx->scratch.ensure(std::max<size_t>(2 * bytes, 1 << 22)));
+        o = 0;
+    }
+    memcpy(static_cast<char*>(ctx->scratch.p) + o, src, bytes);
+    NNVB_CUDA(cudaMemcpyAsync(dst, static_cast<char*>(ctx->scratch.p) + o, bytes, cudaMemcpyHostToDevice,
+                              ctx->stream));
+    ctx->scratch_off = o + bytes;
+    return NNVB_OK;
+}
+
+__global__ void gather_cols_kernel(int64_t N, int64_t ld, const double* __restrict__ V, int center_col,
+                                   const int32_t* __restrict__ list, int64_t P, double* __restrict__ out) {
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    for (int64_t t = blockIdx.y; t <= P; t += gridDim.y) {
+        const int64_t col = t == 0 ? center_col : list[t - 1];
+        out[t * N + i] = V[col * ld + i];
+    }
+}
+
+__global__ void gather_vec_kernel(int64_t P, const int32_t* __restrict__ list, const double* __restrict__ a,
+                                  const double* __restrict__ b, double* __restrict__ out) {
+    const int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= P) return;
+    out[t] = a[list[t]];
+    out[P + t] = b[list[t]];
+}
+
+}  // namespace
+
+// ===========================================================================
+// C ABI
+
+extern "C" {
+
+const char* nnvb_last_error(void) { return g_err; }
+
+const char* nnvb_strerror(int status) {
+    switch (status) {
+        case NNVB_OK: return "ok";
+        case NNVB_E_ARG: return "invalid argument";
+        case NNVB_E_CUDA: return "CUDA runtime error";
+        case NNVB_E_CAPACITY: return "set outgrew the device arena";
+        case NNVB_E_STATE: return "call order violated";
+        case NNVB_E_UNSUPPORTED: return "unsupported layer or option";
+        default: return "unknown status";
+    }
+}
+
+int nnvb_abi_version(void) { return 1; }
+
+int nnvb_init(int device, size_t arena_bytes, nnvb_ctx** out) {
+    NNVB_REQUIRE(out != nullptr, "nnvb_init: out is NULL");
+    *out = nullptr;
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess || ndev == 0) {
+        set_error("no CUDA device available (%s); this engine has no CPU path",
+                  e != cudaSuccess ? cudaGetErrorString(e) : "device count 0");
+        cudaGetLastError();
+        return NNVB_E_CUDA;
+    }
+    NNVB_REQUIRE(device >= 0 && device < ndev, "nnvb_init: device %d out of range (%d devices)", device, ndev);
+    NNVB_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    NNVB_CUDA(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10) {
+        set_error("device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+        return NNVB_E_UNSUPPORTED;
+    }
+    auto ctx = new nnvb_ctx();
+    ctx->device = device;
+    NNVB_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+    if (arena_bytes == 0) {
+        size_t free_b = 0, total_b = 0;
+        NNVB_CUDA(cudaMemGetInfo(&free_b, &total_b));
+        arena_bytes = free_b / 2;
+    }
+    arena_bytes = arena_bytes / 512 * 512;
+    e = cudaMalloc(reinterpret_cast<void**>(&ctx->arena), arena_bytes);
+    if (e != cudaSuccess) {
+        set_error("arena allocation of %zu bytes failed: %s", arena_bytes, cudaGetErrorString(e));
+        cudaGetLastError();
+        cudaStreamDestroy(ctx->stream);
+        delete ctx;
+        return NNVB_E_CAPACITY;
+    }
+    ctx->arena_bytes = arena_bytes;
+    int s = ctx->scratch.ensure(1 << 22);
+    if (s != NNVB_OK) return s;
+    *out = ctx;
+    return NNVB_OK;
+}
+
+int nnvb_destroy(nnvb_ctx* ctx) {
+    if (!ctx) return NNVB_OK;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    ctx->scratch.release();
+    if (ctx->arena) cudaFree(ctx->arena);
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return NNVB_OK;
+}
+
+void* nnvb_stream(nnvb_ctx* ctx) { return ctx ? static_cast<void*>(ctx->stream) : nullptr; }
+int64_t nnvb_launch_count(nnvb_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+// ---------------------------------------------------------------------------
+// network
+
+int nnvb_net_create(nnvb_ctx* ctx, const nnvb_layer_desc* layers, int n_layers, int64_t in_h, int64_t in_w,
+                    int64_t in_c, nnvb_net** out) {
+    NNVB_REQUIRE(ctx && out && (layers || n_layers == 0), "nnvb_net_create: NULL argument");
+    NNVB_REQUIRE(in_h > 0 && in_w > 0 && in_c > 0, "nnvb_net_create: bad input shape");
+    *out = nullptr;
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    std::unique_ptr<nnvb_net> net(new nnvb_net());
+    net->ctx = ctx;
+    net->in_shape[0] = in_h; net->in_shape[1] = in_w; net->in_shape[2] = in_c;
+    int64_t H = in_h, W = in_w, C = in_c;
+    auto fail = [&](int s) {
+        for (void* p : net->owned) cudaFree(p);
+        return s;
+    };
+    for (int li = 0; li < n_layers; ++li) {
+        const nnvb_layer_desc& d = layers[li];
+        Layer L;
+        L.type = d.type;
+        L.H = H; L.W = W; L.C = C;
+        switch (d.type) {
+            case NNVB_LAYER_CONV2D: {
+                if (!(d.W && d.b && d.kh > 0 && d.kw > 0 && d.cin > 0 && d.cout > 0 && d.stride[0] > 0 &&
+                      d.stride[1] > 0 && d.dilation[0] > 0 && d.dilation[1] > 0)) {
+                    set_error("layer %d (conv2d): bad parameters", li);
+                    return fail(NNVB_E_ARG);
+                }
+                if (d.cin != C) {
+                    // Conv2DLayer.m:571-573
+                    set_error("layer %d: input set contains %lld channels while the convolutional layer has %d channels",
+                              li, (long long)C, d.cin);
+                    return fail(NNVB_E_ARG);
+                }
+                ConvGeom& g = L.cg;
+                g.H = (int)H; g.W = (int)W; g.Cin = (int)C;
+                g.kh = d.kh; g.kw = d.kw; g.Cout = d.cout;
+                g.pad_t = d.pad[0]; g.pad_l = d.pad[2];
+                g.sh = d.stride[0]; g.sw = d.stride[1];
+                g.dh = d.dilation[0]; g.dw = d.dilation[1];
+                const int64_t hp = H + d.pad[0] + d.pad[1], wp = W + d.pad[2] + d.pad[3];
+                const int64_t ho = (hp - int64_t(d.kh - 1) * g.dh - 1);
+                const int64_t wo = (wp - int64_t(d.kw - 1) * g.dw - 1);
+                if (ho < 0 || wo < 0) {
+                    set_error("layer %d (conv2d): filter larger than padded input", li);
+                    return fail(NNVB_E_ARG);
+                }
+                g.Ho = int(ho / g.sh + 1);
+                g.Wo = int(wo / g.sw + 1);
+                L.Ho = g.Ho; L.Wo = g.Wo; L.Co = g.Cout;
+                int bn_tile, cs, n_tiles, n_chunks;
+                const size_t nd = conv_weights_doubles(g, &bn_tile, &cs, &n_tiles, &n_chunks);
+                std::vector<double> arranged(nd);
+                conv_arrange_weights(g, d.W, arranged.data(), bn_tile, cs, n_tiles, n_chunks);
+                int s = upload_vec(net.get(), arranged, &L.cw.w);
+                if (s) return fail(s);
+                std::vector<double> bias(d.b, d.b + d.cout);
+                s = upload_vec(net.get(), bias, &L.cw.bias);
+                if (s) return fail(s);
+                L.cw.bn_tile = bn_tile; L.cw.cs = cs; L.cw.n_tiles = n_tiles; L.cw.n_chunks = n_chunks;
+                break;
+            }
+            case NNVB_LAYER_FC: {
+                const int64_t In = H * W * C;
+                if (!(d.W && d.b && d.cout > 0)) {
+                    set_error("layer %d (fc): bad parameters", li);
+                    return fail(NNVB_E_ARG);
+                }
+                if (d.cin != In) {
+                    // FullyConnectedLayer.m:307-309
+                    set_error("layer %d: inconsistency between the size of the input image (%lld) and the InputSize of the layer (%d)",
+                              li, (long long)In, d.cin);
+                    return fail(NNVB_E_ARG);
+                }
+                const int Out = d.cout;
+                const int ldw = (int)round_up(Out, 8);
+                const int64_t In_pad = round_up(In, 16);
+                std::vector<double> wt(size_t(In_pad) * ldw, 0.0);
+                for (int64_t k = 0; k < In; ++k)
+                    for (int o = 0; o < Out; ++o) wt[size_t(k) * ldw + o] = d.W[size_t(o) + size_t(Out) * k];
+                int s = upload_vec(net.get(), wt, &L.fc_wt);
+                if (s) return fail(s);
+                std::vector<double> bias(d.b, d.b + Out);
+                s = upload_vec(net.get(), bias, &L.bias);
+                if (s) return fail(s);
+                L.fc_ldw = ldw;
+                L.Ho = 1; L.Wo = 1; L.Co = Out;
+                break;
+            }
+            case NNVB_LAYER_BN: {
+                if (!(d.bn_mean && d.bn_var && d.bn_scale && d.bn_offset)) {
+                    set_error("layer %d (bn): missing parameters", li);
+                    return fail(NNVB_E_ARG);
+                }
+                // parameters per channel; a 1x1xN set takes N parameters (BatchNormalizationLayer.m:289-302)
+                const int64_t nch = C;
+                if (d.cout != 0 && d.cout != nch) {
+                    set_error("layer %d (bn): %d channels of parameters for a set with %lld channels", li, d.cout,
+                              (long long)nch);
+                    return fail(NNVB_E_ARG);
+                }
+                std::vector<double> mean(d.bn_mean, d.bn_mean + nch), den(nch), scale(d.bn_scale, d.bn_scale + nch),
+                    offset(d.bn_offset, d.bn_offset + nch);
+                for (int64_t c = 0; c < nch; ++c) den[c] = std::sqrt(d.bn_var[c] + d.bn_eps);
+                int s = upload_vec(net.get(), mean, &L.bn_mean);
+                if (!s) s = upload_vec(net.get(), den, &L.bn_den);
+                if (!s) s = upload_vec(net.get(), scale, &L.bn_scale);
+                if (!s) s = upload_vec(net.get(), offset, &L.bn_offset);
+                if (s) return fail(s);
+                L.Ho = H; L.Wo = W; L.Co = C;
+                if (!net->layers.empty() && net->layers.back().type == NNVB_LAYER_CONV2D &&
+                    net->layers.back().fused_bn < 0) {
+                    L.fused_into_prev = true;
+                    net->layers.back().fused_bn = li;
+                }
+                break;
+            }
+            case NNVB_LAYER_AVGPOOL2D: {
+                if (!(d.pool[0] > 0 && d.pool[1] > 0 && d.stride[0] > 0 && d.stride[1] > 0)) {
+                    set_error("layer %d (avgpool): bad parameters", li);
+                    return fail(NNVB_E_ARG);
+                }
+                PoolGeom& g = L.pg;
+                g.H = (int)H; g.W = (int)W; g.C = (int)C;
+                g.ph = d.pool[0]; g.pw = d.pool[1];
+                g.sh = d.stride[0]; g.sw = d.stride[1];
+                g.pad_t = d.pad[0]; g.pad_l = d.pad[2];
+                const int64_t hp = H + d.pad[0] + d.pad[1], wp = W + d.pad[2] + d.pad[3];
+                if (hp < g.ph || wp < g.pw) {
+                    set_error("layer %d (avgpool): window larger than padded input", li);
+                    return fail(NNVB_E_ARG);
+                }
+                g.Ho = int((hp - g.ph) / g.sh + 1);
+                g.Wo = int((wp - g.pw) / g.sw + 1);
+                L.Ho = g.Ho; L.Wo = g.Wo; L.Co = C;
+                break;
+            }
+            case NNVB_LAYER_RELU:
+                L.Ho = H; L.Wo = W; L.Co = C;
+                net->n_relu += 1;
+                break;
+            default:
+                set_error("layer %d: type %d is outside the approx-star path of this engine", li, d.type);
+                return fail(NNVB_E_UNSUPPORTED);
+        }
+        H = L.Ho; W = L.Wo; C = L.Co;
+        net->layers.push_back(L);
+    }
+    net->out_shape[0] = H; net->out_shape[1] = W; net->out_shape[2] = C;
+    *out = net.release();
+    return NNVB_OK;
+}
+
+int nnvb_net_destroy(nnvb_net* net) {
+    if (!net) return NNVB_OK;
+    cudaSetDevice(net->ctx->device);
+    cudaStreamSynchronize(net->ctx->stream);
+    for (void* p : net->owned) cudaFree(p);
+    delete net;
+    return NNVB_OK;
+}
+
+int nnvb_net_out_shape(const nnvb_net* net, int64_t shape[3]) {
+    NNVB_REQUIRE(net && shape, "nnvb_net_out_shape: NULL argument");
+    for (int i = 0; i < 3; ++i) shape[i] = net->out_shape[i];
+    return NNVB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// batches
+
+int nnvb_batch_create(nnvb_net* net, int n_queries, nnvb_batch** out) {
+    NNVB_REQUIRE(net && out, "nnvb_batch_create: NULL argument");
+    NNVB_REQUIRE(n_queries > 0, "nnvb_batch_create: need at least one query");
+    auto b = new nnvb_batch();
+    b->net = net;
+    b->nq = n_queries;
+    b->N0 = net->in_shape[0] * net->in_shape[1] * net->in_shape[2];
+    b->ld0 = lead_dim(b->N0);
+    b->P0.assign(n_queries, 0);
+    b->is_set.assign(n_queries, 0);
+    b->h_pl.resize(n_queries); b->h_pu.resize(n_queries);
+    b->h_C.resize(n_queries); b->h_d.resize(n_queries);
+    b->h_V.resize(n_queries);
+    b->m0.assign(n_queries, 0);
+    *out = b;
+    return NNVB_OK;
+}
+
+int nnvb_batch_destroy(nnvb_batch* b) {
+    if (!b) return NNVB_OK;
+    nnvb_ctx* ctx = b->net->ctx;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    b->h_in.release();
+    DevBuf* bufs[] = {&b->d_in, &b->d_in_meta, &b->col_q, &b->pl, &b->pu, &b->col_pos, &b->qcol_off[0],
+                      &b->qcol_off[1], &b->qcol_idx[0], &b->qcol_idx[1], &b->chunk_beg, &b->chunk_end,
+                      &b->q_chunk_off, &b->partial, &b->lb, &b->ub, &b->state, &b->rank, &b->blk_cross,
+                      &b->q_cross, &b->q_dead, &b->q_new_off, &b->gen_off, &b->tmp};
+    for (DevBuf* d : bufs) d->release();
+    for (auto& r : b->relu) r->release();
+    delete b;
+    return NNVB_OK;
+}
+
+int nnvb_batch_set_bounds(nnvb_batch* b, int q, const double* lb, const double* ub) {
+    NNVB_REQUIRE(b && lb && ub, "nnvb_batch_set_bounds: NULL argument");
+    NNVB_REQUIRE(q >= 0 && q < b->nq, "nnvb_batch_set_bounds: query %d out of range", q);
+    NNVB_REQUIRE(b->kind == 0 || b->kind == 1, "nnvb_batch_set_bounds: batch already holds star-form queries");
+    b->kind = 1;
+    const int64_t N = b->N0;
+    NNVB_TRY(b->h_in.ensure(size_t(b->nq) * 2 * N * sizeof(double), true));
+    double* dst = b->h_in.as<double>() + size_t(q) * 2 * N;
+    memcpy(dst, lb, N * sizeof(double));
+    memcpy(dst + N, ub, N * sizeof(double));
+    int64_t P = 0;
+    for (int64_t i = 0; i < N; ++i) {
+        if (!(lb[i] <= ub[i])) {
+            set_error("nnvb_batch_set_bounds: lb > ub (or NaN) at entry %lld", (long long)i);
+            return NNVB_E_ARG;
+        }
+        P += (0.5 * (ub[i] - lb[i]) != 0.0 || N == 1) ? 1 : 0;
+    }
+    b->P0[q] = P;
+    b->m0[q] = 1;                       // Star(lb,ub): C = zeros(1,P), d = 0 (Star.m:229-230)
+    b->h_C[q].assign(size_t(P), 0.0);
+    b->h_d[q].assign(1, 0.0);
+    b->is_set[q] = 1;
+    b->uploaded = false;
+    b->reached = false;
+    return NNVB_OK;
+}
+
+int nnvb_batch_set_star(nnvb_batch* b, int q, int64_t P, const double* V, const double* pl, const double* pu,
+                        int64_t m, const double* Cmat, const double* d) {
+    NNVB_REQUIRE(b && V, "nnvb_batch_set_star: NULL argument");
+    NNVB_REQUIRE(q >= 0 && q < b->nq, "nnvb_batch_set_star: query %d out of range", q);
+    NNVB_REQUIRE(P >= 0 && m >= 0, "nnvb_batch_set_star: negative size");
+    NNVB_REQUIRE(P == 0 || (pl && pu), "nnvb_batch_set_star: predicate bounds missing");
+    NNVB_REQUIRE(m == 0 || (Cmat && d), "nnvb_batch_set_star: constraint arrays missing");
+    NNVB_REQUIRE(b->kind == 0 || b->kind == 2, "nnvb_batch_set_star: batch already holds bounds-form queries");
+    b->kind = 2;
+    const int64_t N = b->N0;
+    b->h_V[q].assign(V, V + size_t(N) * (P + 1));
+    b->h_pl[q].assign(pl, pl + P);
+    b->h_pu[q].assign(pu, pu + P);
+    for (int64_t j = 0; j < P; ++j) {
+        if (!(pl[j] <= pu[j])) {
+            set_error("nnvb_batch_set_star: pred_lb > pred_ub (or NaN) at predicate %lld", (long long)j);
+            return NNVB_E_ARG;
+        }
+    }
+    b->h_C[q].assign(Cmat, Cmat + size_t(m) * P);
+    b->h_d[q].assign(d, d + m);
+    b->P0[q] = P;
+    b->m0[q] = m;
+    b->is_set[q] = 1;
+    b->uploaded = false;
+    b->reached = false;
+    return NNVB_OK;
+}
+
+int nnvb_batch_upload(nnvb_batch* b) {
+    NNVB_REQUIRE(b, "nnvb_batch_upload: NULL argument");
+    nnvb_ctx* ctx = b->net->ctx;
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    for (int q = 0; q < b->nq; ++q) {
+        if (!b->is_set[q]) {
+            set_error("nnvb_batch_upload: query %d was never set", q);
+            return NNVB_E_STATE;
+        }
+    }
+    const int64_t N = b->N0;
+    if (b->kind == 1) {
+        const size_t bytes = size_t(b->nq) * 2 * N * sizeof(double);
+        NNVB_TRY(b->d_in.ensure(bytes, ctx->stream));
+        NNVB_CUDA(cudaMemcpyAsync(b->d_in.p, b->h_in.p, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    } else {
+        // arrange the batch as one matrix: centres first, then each query's generators
+        int64_t ncols = b->nq;
+        for (int q = 0; q < b->nq; ++q) ncols += b->P0[q];
+        const size_t vbytes = size_t(b->ld0) * ncols * sizeof(double);
+        const size_t mbytes = size_t(ncols) * 2 * sizeof(double);
+        NNVB_TRY(b->h_in.ensure(vbytes + mbytes));
+        double* hv = b->h_in.as<double>();
+        double* hm = hv + size_t(b->ld0) * ncols;
+        int64_t col = b->nq;
+        for (int q = 0; q < b->nq; ++q) {
+            const double* src = b->h_V[q].data();
+            memcpy(hv + size_t(q) * b->ld0, src, N * sizeof(double));
+            hm[q] = 0.0; hm[ncols + q] = 0.0;
+            for (int64_t j = 0; j < b->P0[q]; ++j, ++col) {
+                memcpy(hv + size_t(col) * b->ld0, src + size_t(N) * (j + 1), N * sizeof(double));
+                hm[col] = b->h_pl[q][j];
+                hm[ncols + col] = b->h_pu[q][j];
+            }
+        }
+        NNVB_TRY(b->d_in.ensure(vbytes, ctx->stream));
+        NNVB_TRY(b->d_in_meta.ensure(mbytes, ctx->stream));
+        NNVB_CUDA(cudaMemcpyAsync(b->d_in.p, hv, vbytes, cudaMemcpyHostToDevice, ctx->stream));
+        NNVB_CUDA(cudaMemcpyAsync(b->d_in_meta.p, hm, mbytes, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    b->uploaded = true;
+    b->reached = false;
+    return NNVB_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// the layer loop
+
+namespace {
+
+int ensure_col_meta(nnvb_batch* b, int64_t cols) {
+    cudaStream_t st = b->net->ctx->stream;
+    NNVB_TRY(b->col_q.ensure(size_t(cols) * sizeof(int32_t), st, true));
+    NNVB_TRY(b->pl.ensure(size_t(cols) * sizeof(double), st, true));
+    NNVB_TRY(b->pu.ensure(size_t(cols) * sizeof(double), st, true));
+    NNVB_TRY(b->col_pos.ensure(size_t(cols) * sizeof(int64_t), st, true));
+    for (int i = 0; i < 2; ++i) {
+        NNVB_TRY(b->qcol_idx[i].ensure(size_t(cols) * sizeof(int32_t), st, true));
+        NNVB_TRY(b->qcol_off[i].ensure(size_t(b->nq + 1) * sizeof(int64_t), st, true));
+    }
+    return NNVB_OK;
+}
+
+int init_sets(nnvb_batch* b) {
+    nnvb_ctx* ctx = b->net->ctx;
+    cudaStream_t st = ctx->stream;
+    const int nq = b->nq;
+    const int64_t N = b->N0, ld = b->ld0;
+    int64_t ncols = nq;
+    b->h_qcol_off.assign(nq + 1, 0);
+    std::vector<int64_t> gen_off(nq + 1);
+    for (int q = 0; q < nq; ++q) {
+        gen_off[q] = ncols;
+        b->h_qcol_off[q] = ncols - nq;
+        ncols += b->P0[q];
+    }
+    gen_off[nq] = ncols;
+    b->h_qcol_off[nq] = ncols - nq;
+    NNVB_REQUIRE(ncols < (int64_t(1) << 31), "batch has too many generator columns (%lld)", (long long)ncols);
+    NNVB_TRY(ensure_col_meta(b, ncols));
+    b->list_cur = 0;
+    NNVB_TRY(h2d_small(ctx, b->qcol_off[0].p, b->h_qcol_off.data(), sizeof(int64_t) * (nq + 1)));
+    if (b->kind == 1) {
+        const size_t need = size_t(ld) * ncols * sizeof(double);
+        if (need > ctx->vbuf_bytes()) return capacity_error("input set", need, ctx->vbuf_bytes());
+        NNVB_TRY(b->gen_off.ensure(sizeof(int64_t) * (nq + 1), st));
+        NNVB_TRY(h2d_small(ctx, b->gen_off.p, gen_off.data(), sizeof(int64_t) * (nq + 1)));
+        double* V = ctx->vbuf(0);
+        NNVB_CUDA(cudaMemsetAsync(V, 0, need, st));
+        NNVB_TRY(launch_build_from_bounds(st, nq, N, ld, b->d_in.as<double>(), b->gen_off.as<int64_t>(), V,
+                                          b->col_q.as<int32_t>(), b->pl.as<double>(), b->pu.as<double>(),
+                                          b->qcol_idx[0].as<int32_t>(), b->col_pos.as<int64_t>(), &ctx->launches));
+        b->V = V;
+    } else {
+        // metadata is a pure function of the staged queries
+        std::vector<int32_t> col_q(ncols), list(ncols - nq);
+        std::vector<int64_t> col_pos(ncols, 0);
+        int64_t col = nq;
+        for (int q = 0; q < nq; ++q) {
+            col_q[q] = q;
+            for (int64_t j = 0; j < b->P0[q]; ++j, ++col) {
+                col_q[col] = q;
+                col_pos[col] = j;
+                list[col - nq] = int32_t(col);
+            }
+        }
+        NNVB_TRY(h2d_small(ctx, b->col_q.p, col_q.data(), sizeof(int32_t) * ncols));
+        NNVB_TRY(h2d_small(ctx, b->col_pos.p, col_pos.data(), sizeof(int64_t) * ncols));
+        NNVB_TRY(h2d_small(ctx, b->qcol_idx[0].p, list.data(), sizeof(int32_t) * (ncols - nq)));
+        NNVB_CUDA(cudaMemcpyAsync(b->pl.p, b->d_in_meta.p, sizeof(double) * ncols, cudaMemcpyDeviceToDevice, st));
+        NNVB_CUDA(cudaMemcpyAsync(b->pu.p, b->d_in_meta.as<double>() + ncols, sizeof(double) * ncols,
+                                  cudaMemcpyDeviceToDevice, st));
+        b->V = b->d_in.as<double>();      // read-only; in-place layers copy it first
+    }
+    b->ncols = ncols;
+    b->N = N;
+    b->ld = ld;
+    for (int i = 0; i < 3; ++i) b->shape[i] = b->net->in_shape[i];
+    return NNVB_OK;
+}
+
+// the buffer the next out-of-place layer writes to
+double* other_vbuf(nnvb_batch* b) {
+    nnvb_ctx* ctx = b->net->ctx;
+    return b->V == ctx->vbuf(0) ? ctx->vbuf(1) : ctx->vbuf(0);
+}
+
+int make_writable(nnvb_batch* b, int64_t extra_cols) {
+    nnvb_ctx* ctx = b->net->ctx;
+    const size_t need = size_t(b->ld) * (b->ncols + extra_cols) * sizeof(double);
+    if (need > ctx->vbuf_bytes()) return capacity_error("generator matrix", need, ctx->vbuf_bytes());
+    if (b->V != ctx->vbuf(0) && b->V != ctx->vbuf(1)) {
+        double* dst = ctx->vbuf(0);
+        NNVB_CUDA(cudaMemcpyAsync(dst, b->V, size_t(b->ld) * b->ncols * sizeof(double), cudaMemcpyDeviceToDevice,
+                                  ctx->stream));
+        b->V = dst;
+    }
+    return NNVB_OK;
+}
+
+int relu_step(nnvb_batch* b, ReluLayerRecord* rec) {
+    nnvb_ctx* ctx = b->net->ctx;
+    cudaStream_t st = ctx->stream;
+    const int nq = b->nq;
+    const int64_t N = b->N, ld = b->ld;
+    NNVB_TRY(make_writable(b, 0));
+
+    // chunk list: split every query's column list so that the grid fills the GPU
+    const int64_t row_blocks = N >= 256 ? ceil_div(ceil_div(N, 2), 256) : ceil_div(N, 32);
+    const int64_t total_P = b->h_qcol_off[nq];
+    const int64_t want_chunks = std::max<int64_t>(1, ceil_div(148 * 16, row_blocks));
+    int64_t CH = std::max<int64_t>(32, ceil_div(total_P, want_chunks));
+    CH = std::min<int64_t>(CH, 1024);
+    std::vector<int64_t> cbeg, cend;
+    std::vector<int32_t> qoff(nq + 1);
+    for (int q = 0; q < nq; ++q) {
+        qoff[q] = (int32_t)cbeg.size();
+        for (int64_t p0 = b->h_qcol_off[q]; p0 < b->h_qcol_off[q + 1]; p0 += CH) {
+            cbeg.push_back(p0);
+            cend.push_back(std::min(p0 + CH, b->h_qcol_off[q + 1]));
+        }
+    }
+    qoff[nq] = (int32_t)cbeg.size();
+    const int n_chunks = (int)cbeg.size();
+    NNVB_TRY(b->chunk_beg.ensure(sizeof(int64_t) * std::max(n_chunks, 1), st));
+    NNVB_TRY(b->chunk_end.ensure(sizeof(int64_t) * std::max(n_chunks, 1), st));
+    NNVB_TRY(b->q_chunk_off.ensure(sizeof(int32_t) * (nq + 1), st));
+    NNVB_TRY(b->partial.ensure(sizeof(double) * 2 * N * std::max(n_chunks, 1), st));
+    NNVB_TRY(h2d_small(ctx, b->chunk_beg.p, cbeg.data(), sizeof(int64_t) * n_chunks));
+    NNVB_TRY(h2d_small(ctx, b->chunk_end.p, cend.data(), sizeof(int64_t) * n_chunks));
+    NNVB_TRY(h2d_small(ctx, b->q_chunk_off.p, qoff.data(), sizeof(int32_t) * (nq + 1)));
+
+    const int nblk = relu_blocks_per_query(N);
+    DevBuf& lbbuf = b->opts.keep_layer_bounds ? rec->lb : b->lb;
+    DevBuf& ubbuf = b->opts.keep_layer_bounds ? rec->ub : b->ub;
+    NNVB_TRY(lbbuf.ensure(sizeof(double) * nq * N, st));
+    NNVB_TRY(ubbuf.ensure(sizeof(double) * nq * N, st));
+    rec->has_bounds = b->opts.keep_layer_bounds != 0;
+    NNVB_TRY(b->state.ensure(size_t(nq) * N, st));
+    NNVB_TRY(b->rank.ensure(sizeof(int32_t) * nq * N, st));
+    NNVB_TRY(b->blk_cross.ensure(sizeof(int32_t) * nq * nblk, st));
+    NNVB_TRY(b->q_cross.ensure(sizeof(int64_t) * nq, st));
+    NNVB_TRY(b->q_dead.ensure(sizeof(int64_t) * nq, st));
+    NNVB_TRY(b->q_new_off.ensure(sizeof(int64_t) * (nq + 1), st));
+
+    ReluWork w{};
+    w.nq = nq; w.N = N; w.ld = ld; w.V = b->V;
+    w.qcol_off = b->qcol_off[b->list_cur].as<int64_t>();
+    w.qcol_idx = b->qcol_idx[b->list_cur].as<int32_t>();
+    w.pl = b->pl.as<double>(); w.pu = b->pu.as<double>();
+    w.n_chunks = n_chunks;
+    w.chunk_beg = b->chunk_beg.as<int64_t>(); w.chunk_end = b->chunk_end.as<int64_t>();
+    w.q_chunk_off = b->q_chunk_off.as<int32_t>();
+    w.partial = b->partial.as<double>();
+    w.lb = lbbuf.as<double>(); w.ub = ubbuf.as<double>();
+    w.state = b->state.as<uint8_t>(); w.rank = b->rank.as<int32_t>();
+    w.blk_cross = b->blk_cross.as<int32_t>();
+    w.q_cross = b->q_cross.as<int64_t>(); w.q_dead = b->q_dead.as<int64_t>();
+    w.q_new_off = b->q_new_off.as<int64_t>();
+
+    NNVB_TRY(launch_estimate_ranges(st, w, &ctx->launches));
+    NNVB_TRY(launch_classify_scan(st, w, &ctx->launches));
+
+    // the crossing counts decide every size from here on: one host round trip per ReLU layer
+    rec->new_off.resize(nq + 1);
+    std::vector<int64_t> dead(nq);
+    NNVB_CUDA(cudaMemcpyAsync(rec->new_off.data(), w.q_new_off, sizeof(int64_t) * (nq + 1), cudaMemcpyDeviceToHost, st));
+    NNVB_CUDA(cudaMemcpyAsync(dead.data(), w.q_dead, sizeof(int64_t) * nq, cudaMemcpyDeviceToHost, st));
+    NNVB_TRY(sync(ctx));
+    const int64_t K = rec->new_off[nq];
+    rec->N = N;
+    rec->K = K;
+    rec->n_dead = 0;
+    for (int q = 0; q < nq; ++q) rec->n_dead += dead[q];
+    rec->P_in.resize(nq);
+    for (int q = 0; q < nq; ++q) rec->P_in[q] = b->h_qcol_off[q + 1] - b->h_qcol_off[q];
+
+    const int64_t ncols_old = b->ncols;
+    NNVB_REQUIRE(ncols_old + K < (int64_t(1) << 31), "batch has too many generator columns");
+    {
+        const size_t need = size_t(ld) * (ncols_old + K) * sizeof(double);
+        if (need > ctx->vbuf_bytes()) return capacity_error("ReLU layer output", need, ctx->vbuf_bytes());
+    }
+    NNVB_TRY(ensure_col_meta(b, ncols_old + K));
+    // pointers may have moved
+    w.qcol_off = b->qcol_off[b->list_cur].as<int64_t>();
+    w.qcol_idx = b->qcol_idx[b->list_cur].as<int32_t>();
+    w.pl = b->pl.as<double>(); w.pu = b->pu.as<double>();
+
+    const size_t kk = size_t(std::max<int64_t>(K, 1));
+    NNVB_TRY(rec->idx.ensure(sizeof(int32_t) * kk, st));
+    NNVB_TRY(rec->q.ensure(sizeof(int32_t) * kk, st));
+    NNVB_TRY(rec->c.ensure(sizeof(double) * kk, st));
+    NNVB_TRY(rec->l.ensure(sizeof(double) * kk, st));
+    NNVB_TRY(rec->u.ensure(sizeof(double) * kk, st));
+    ReluRecord r{};
+    r.idx = rec->idx.as<int32_t>(); r.q = rec->q.as<int32_t>();
+    r.c = rec->c.as<double>(); r.l = rec->l.as<double>(); r.u = rec->u.as<double>();
+    rec->has_G = false;
+    if (b->opts.keep_constraints) {
+        rec->h_G_off.assign(nq + 1, 0);
+        for (int q = 0; q < nq; ++q)
+            rec->h_G_off[q + 1] = rec->h_G_off[q] + (rec->new_off[q + 1] - rec->new_off[q]) * rec->P_in[q];
+        NNVB_TRY(rec->G.ensure(sizeof(double) * std::max<int64_t>(rec->h_G_off[nq], 1), st));
+        NNVB_TRY(rec->G_off.ensure(sizeof(int64_t) * (nq + 1), st));
+        NNVB_TRY(h2d_small(ctx, rec->G_off.p, rec->h_G_off.data(), sizeof(int64_t) * (nq + 1)));
+        r.G = rec->G.as<double>();
+        r.G_off = rec->G_off.as<int64_t>();
+        rec->has_G = true;
+    }
+    if (K > 0) NNVB_TRY(launch_rank_cross(st, w, r, &ctx->launches));
+    if (K > 0 || rec->n_dead > 0)
+        NNVB_TRY(launch_relu_zero_rows(st, w, ncols_old, b->col_q.as<int32_t>(), r, b->col_pos.as<int64_t>(),
+                                       &ctx->launches));
+    const int nxt = 1 - b->list_cur;
+    NNVB_TRY(launch_relu_append(st, w, ncols_old, K, r, b->col_q.as<int32_t>(), b->pl.as<double>(),
+                                b->pu.as<double>(), b->col_pos.as<int64_t>(), b->qcol_off[nxt].as<int64_t>(),
+                                b->qcol_idx[nxt].as<int32_t>(), &ctx->launches));
+    b->list_cur = nxt;
+    for (int q = 0; q <= nq; ++q) b->h_qcol_off[q] += rec->new_off[q];
+    b->ncols = ncols_old + K;
+    rec->cols_after = b->ncols;
+    return NNVB_OK;
+}
+
+int run_layers(nnvb_batch* b) {
+    nnvb_net* net = b->net;
+    nnvb_ctx* ctx = net->ctx;
+    cudaStream_t st = ctx->stream;
+    int relu_i = 0;
+    for (size_t li = 0; li < net->layers.size(); ++li) {
+        const Layer& L = net->layers[li];
+        const int64_t Nout = L.Ho * L.Wo * L.Co;
+        const int64_t ld_out = lead_dim(Nout);
+        if (L.type == NNVB_LAYER_CONV2D || L.type == NNVB_LAYER_FC || L.type == NNVB_LAYER_AVGPOOL2D) {
+            const size_t need = size_t(ld_out) * b->ncols * sizeof(double);
+            if (need > ctx->vbuf_bytes()) return capacity_error("layer output", need, ctx->vbuf_bytes());
+            double* out = other_vbuf(b);
+            if (L.type == NNVB_LAYER_CONV2D) {
+                ChanAffine bn{nullptr, nullptr, nullptr, nullptr};
+                if (L.fused_bn >= 0) {
+                    const Layer& B = net->layers[L.fused_bn];
+                    bn = ChanAffine{B.bn_mean, B.bn_den, B.bn_scale, B.bn_offset};
+                }
+                NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, b->V, b->ld, out, ld_out, b->ncols, b->nq,
+                                         &ctx->launches));
+            } else if (L.type == NNVB_LAYER_FC) {
+                NNVB_TRY(launch_fc_f64(st, int(L.H * L.W * L.C), int(L.Co), L.fc_wt, L.fc_ldw, L.bias, b->V, b->ld,
+                                       out, ld_out, b->ncols, b->nq, &ctx->launches));
+            } else {
+                NNVB_TRY(launch_avgpool_f64(st, L.pg, b->V, b->ld, out, ld_out, b->ncols, &ctx->launches));
+            }
+            b->V = out;
+            b->N = Nout;
+            b->ld = ld_out;
+        } else if (L.type == NNVB_LAYER_BN) {
+            if (!L.fused_into_prev) {
+                NNVB_TRY(make_writable(b, 0));
+                ChanAffine bn{L.bn_mean, L.bn_den, L.bn_scale, L.bn_offset};
+                NNVB_TRY(launch_bn_f64(st, bn, L.H * L.W, b->N, b->V, b->ld, b->ncols, b->nq, &ctx->launches));
+            }
+        } else if (L.type == NNVB_LAYER_RELU) {
+            NNVB_TRY(relu_step(b, b->relu[relu_i].get()));
+            ++relu_i;
+        }
+        b->shape[0] = L.Ho; b->shape[1] = L.Wo; b->shape[2] = L.Co;
+    }
+    return NNVB_OK;
+}
+
+int check_reached(const nnvb_batch* b, int q) {
+    if (!b) { set_error("NULL batch"); return NNVB_E_ARG; }
+    if (!b->reached) { set_error("results requested before nnvb_batch_reach succeeded"); return NNVB_E_STATE; }
+    if (q < 0 || q >= b->nq) { set_error("query %d out of range", q); return NNVB_E_ARG; }
+    return NNVB_OK;
+}
+
+// Star.estimateRanges of the current set into b->lb / b->ub (no classification side effects kept)
+int output_ranges(nnvb_batch* b) {
+    if (b->have_out_ranges) return NNVB_OK;
+    nnvb_ctx* ctx = b->net->ctx;
+    cudaStream_t st = ctx->stream;
+    const int nq = b->nq;
+    const int64_t N = b->N;
+    std::vector<int64_t> cbeg(nq), cend(nq);
+    std::vector<int32_t> qoff(nq + 1);
+    for (int q = 0; q < nq; ++q) { cbeg[q] = b->h_qcol_off[q]; cend[q] = b->h_qcol_off[q + 1]; qoff[q] = q; }
+    qoff[nq] = nq;
+    NNVB_TRY(b->chunk_beg.ensure(sizeof(int64_t) * nq, st));
+    NNVB_TRY(b->chunk_end.ensure(sizeof(int64_t) * nq, st));
+    NNVB_TRY(b->q_chunk_off.ensure(sizeof(int32_t) * (nq + 1), st));
+    NNVB_TRY(b->partial.ensure(sizeof(double) * 2 * N * nq, st));
+    NNVB_TRY(h2d_small(ctx, b->chunk_beg.p, cbeg.data(), sizeof(int64_t) * nq));
+    NNVB_TRY(h2d_small(ctx, b->chunk_end.p, cend.data(), sizeof(int64_t) * nq));
+    NNVB_TRY(h2d_small(ctx, b->q_chunk_off.p, qoff.data(), sizeof(int32_t) * (nq + 1)));
+    const int nblk = relu_blocks_per_query(N);
+    NNVB_TRY(b->lb.ensure(sizeof(double) * nq * N, st));
+    NNVB_TRY(b->ub.ensure(sizeof(double) * nq * N, st));
+    NNVB_TRY(b->state.ensure(size_t(nq) * N, st));
+    NNVB_TRY(b->blk_cross.ensure(sizeof(int32_t) * nq * nblk, st));
+    NNVB_TRY(b->q_cross.ensure(sizeof(int64_t) * nq, st));
+    NNVB_TRY(b->q_dead.ensure(sizeof(int64_t) * nq, st));
+    NNVB_TRY(b->q_new_off.ensure(sizeof(int64_t) * (nq + 1), st));
+    ReluWork w{};
+    w.nq = nq; w.N = N; w.ld = b->ld; w.V = b->V;
+    w.qcol_off = b->qcol_off[b->list_cur].as<int64_t>();
+    w.qcol_idx = b->qcol_idx[b->list_cur].as<int32_t>();
+    w.pl = b->pl.as<double>(); w.pu = b->pu.as<double>();
+    w.n_chunks = nq;
+    w.chunk_beg = b->chunk_beg.as<int64_t>(); w.chunk_end = b->chunk_end.as<int64_t>();
+    w.q_chunk_off = b->q_chunk_off.as<int32_t>();
+    w.partial = b->partial.as<double>();
+    w.lb = b->lb.as<double>(); w.ub = b->ub.as<double>();
+    w.state = b->state.as<uint8_t>();
+    w.blk_cross = b->blk_cross.as<int32_t>();
+    w.q_cross = b->q_cross.as<int64_t>(); w.q_dead = b->q_dead.as<int64_t>();
+    w.q_new_off = b->q_new_off.as<int64_t>();
+    NNVB_TRY(launch_estimate_ranges(st, w, &ctx->launches));
+    NNVB_TRY(launch_classify_scan(st, w, &ctx->launches));
+    b->have_out_ranges = true;
+    return NNVB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int nnvb_batch_reach(nnvb_batch* b, const nnvb_opts* opts) {
+    NNVB_REQUIRE(b, "nnvb_batch_reach: NULL argument");
+    if (!b->uploaded) {
+        set_error("nnvb_batch_reach: call nnvb_batch_upload first");
+        return NNVB_E_STATE;
+    }
+    nnvb_ctx* ctx = b->net->ctx;
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    b->opts = opts ? *opts : nnvb_opts{};
+    b->reached = false;
+    b->have_out_ranges = false;
+    while ((int)b->relu.size() < b->net->n_relu) b->relu.emplace_back(new ReluLayerRecord());
+    NNVB_TRY(init_sets(b));
+    NNVB_TRY(run_layers(b));
+    b->reached = true;
+    return NNVB_OK;
+}
+
+int nnvb_batch_out_dims(const nnvb_batch* b, int q, int64_t* P, int64_t* m) {
+    NNVB_TRY(check_reached(b, q));
+    const int64_t Pq = b->h_qcol_off[q + 1] - b->h_qcol_off[q];
+    if (P) *P = Pq;
+    if (m) {
+        int64_t mm = b->m0[q];
+        for (auto& r : b->relu) mm += 3 * (r->new_off[q + 1] - r->new_off[q]);
+        *m = mm;
+    }
+    return NNVB_OK;
+}
+
+int nnvb_batch_get_V(nnvb_batch* b, int q, double* V) {
+    NNVB_TRY(check_reached(b, q));
+    NNVB_REQUIRE(V, "nnvb_batch_get_V: NULL output");
+    nnvb_ctx* ctx = b->net->ctx;
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    const int64_t P = b->h_qcol_off[q + 1] - b->h_qcol_off[q];
+    const size_t bytes = size_t(b->N) * (P + 1) * sizeof(double);
+    NNVB_TRY(b->tmp.ensure(bytes, ctx->stream));
+    dim3 grid((unsigned)ceil_div(b->N, 256), (unsigned)std::min<int64_t>(P + 1, 32768));
+    gather_cols_kernel<<<grid, 256, 0, ctx->stream>>>(b->N, b->ld, b->V, q,
+                                                      b->qcol_idx[b->list_cur].as<int32_t>() + b->h_qcol_off[q], P,
+                                                      b->tmp.as<double>());
+    NNVB_CUDA(cudaGetLastError());
+    ctx->launches += 1;
+    NNVB_CUDA(cudaMemcpyAsync(V, b->tmp.p, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    return sync(ctx);
+}
+
+int nnvb_batch_get_pred_bounds(nnvb_batch* b, int q, double* pl, double* pu) {
+    NNVB_TRY(check_reached(b, q));
+    nnvb_ctx* ctx = b->net->ctx;
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    const int64_t P = b->h_qcol_off[q + 1] - b->h_qcol_off[q];
+    if (P == 0) return NNVB_OK;
+    NNVB_REQUIRE(pl && pu, "nnvb_batch_get_pred_bounds: NULL output");
+    NNVB_TRY(b->tmp.ensure(sizeof(double) * 2 * P, ctx->stream));
+    gather_vec_kernel<<<(unsigned)ceil_div(P, 256), 256, 0, ctx->stream>>>(
+        P, b->qcol_idx[b->list_cur].as<int32_t>() + b->h_qcol_off[q], b->pl.as<double>(), b->pu.as<double>(),
+        b->tmp.as<double>());
+    NNVB_CUDA(cudaGetLastError());
+    ctx->launches += 1;
+    NNVB_CUDA(cudaMemcpyAsync(pl, b->tmp.p, sizeof(double) * P, cudaMemcpyDeviceToHost, ctx->stream));
+    NNVB_CUDA(cudaMemcpyAsync(pu, b->tmp.as<double>() + P, sizeof(double) * P, cudaMemcpyDeviceToHost, ctx->stream));
+    return sync(ctx);
+}
+
+int nnvb_batch_get_ranges(nnvb_batch* b, int q, double* lb, double* ub) {
+    NNVB_TRY(check_reached(b, q));
+    NNVB_REQUIRE(lb && ub, "nnvb_batch_get_ranges: NULL output");
+    nnvb_ctx* ctx = b->net->ctx;
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    NNVB_TRY(output_ranges(b));
+    NNVB_CUDA(cudaMemcpyAsync(lb, b->lb.as<double>() + size_t(q) * b->N, sizeof(double) * b->N,
+                              cudaMemcpyDeviceToHost, ctx->stream));
+    NNVB_CUDA(cudaMemcpyAsync(ub, b->ub.as<double>() + size_t(q) * b->N, sizeof(double) * b->N,
+                              cudaMemcpyDeviceToHost, ctx->stream));
+    return sync(ctx);
+}
+
+int nnvb_batch_relu_layers(const nnvb_batch* b, int* n) {
+    NNVB_REQUIRE(b && n, "nnvb_batch_relu_layers: NULL argument");
+    *n = b->net->n_relu;
+    return NNVB_OK;
+}
+
+int nnvb_batch_relu_stats(const nnvb_batch* b, int relu_layer, nnvb_relu_stats* stt) {
+    NNVB_TRY(check_reached(b, 0));
+    NNVB_REQUIRE(stt && relu_layer >= 0 && relu_layer < b->net->n_relu, "nnvb_batch_relu_stats: bad argument");
+    const ReluLayerRecord& r = *b->relu[relu_layer];
+    stt->n_neurons = r.N;
+    stt->n_cross = r.K;
+    stt->n_dead = r.n_dead;
+    stt->cols_after = r.cols_after;
+    return NNVB_OK;
+}
+
+int nnvb_batch_get_crossing(nnvb_batch* b, int q, int relu_layer, int64_t* k, int64_t* idx, double* lb, double* ub) {
+    NNVB_TRY(check_reached(b, q));
+    NNVB_REQUIRE(relu_layer >= 0 && relu_layer < b->net->n_relu, "nnvb_batch_get_crossing: bad layer");
+    nnvb_ctx* ctx = b->net->ctx;
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    ReluLayerRecord& r = *b->relu[relu_layer];
+    const int64_t c0 = r.new_off[q], kq = r.new_off[q + 1] - c0;
+    if (k) *k = kq;
+    if (kq == 0 || (!idx && !lb && !ub)) return NNVB_OK;
+    std::vector<int32_t> h_idx(kq);
+    NNVB_CUDA(cudaMemcpyAsync(h_idx.data(), r.idx.as<int32_t>() + c0, sizeof(int32_t) * kq, cudaMemcpyDeviceToHost,
+                              ctx->stream));
+    if (lb) NNVB_CUDA(cudaMemcpyAsync(lb, r.l.as<double>() + c0, sizeof(double) * kq, cudaMemcpyDeviceToHost, ctx->stream));
+    if (ub) NNVB_CUDA(cudaMemcpyAsync(ub, r.u.as<double>() + c0, sizeof(double) * kq, cudaMemcpyDeviceToHost, ctx->stream));
+    NNVB_TRY(sync(ctx));
+    if (idx) for (int64_t t = 0; t < kq; ++t) idx[t] = h_idx[t];
+    return NNVB_OK;
+}
+
+int nnvb_batch_get_layer_ranges(nnvb_batch* b, int q, int relu_layer, double* lb, double* ub) {
+    NNVB_TRY(check_reached(b, q));
+    NNVB_REQUIRE(relu_layer >= 0 && relu_layer < b->net->n_relu && lb && ub, "nnvb_batch_get_layer_ranges: bad argument");
+    ReluLayerRecord& r = *b->relu[relu_layer];
+    if (!r.has_bounds) {
+        set_error("layer bounds were not kept: set opts.keep_layer_bounds");
+        return NNVB_E_STATE;
+    }
+    nnvb_ctx* ctx = b->net->ctx;
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    NNVB_CUDA(cudaMemcpyAsync(lb, r.lb.as<double>() + size_t(q) * r.N, sizeof(double) * r.N, cudaMemcpyDeviceToHost, ctx->stream));
+    NNVB_CUDA(cudaMemcpyAsync(ub, r.ub.as<double>() + size_t(q) * r.N, sizeof(double) * r.N, cudaMemcpyDeviceToHost, ctx->stream));
+    return sync(ctx);
+}
+
+int nnvb_batch_get_constraints(nnvb_batch* b, int q, double* Cmat, double* d) {
+    NNVB_TRY(check_reached(b, q));
+    NNVB_REQUIRE(Cmat && d, "nnvb_batch_get_constraints: NULL output");
+    nnvb_ctx* ctx = b->net->ctx;
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    int64_t P = 0, m = 0;
+    NNVB_TRY(nnvb_batch_out_dims(b, q, &P, &m));
+    std::fill(Cmat, Cmat + size_t(m) * P, 0.0);
+    // rows of the input set: [C0 0]
+    const int64_t m0 = b->m0[q], P0 = b->P0[q];
+    for (int64_t j = 0; j < P0; ++j)
+        for (int64_t r = 0; r < m0; ++r) Cmat[size_t(j) * m + r] = b->h_C[q][size_t(j) * m0 + r];
+    for (int64_t r = 0; r < m0; ++r) d[r] = b->h_d[q][r];
+    int64_t row = m0;
+    for (auto& rp : b->relu) {
+        ReluLayerRecord& r = *rp;
+        const int64_t c0 = r.new_off[q], k = r.new_off[q + 1] - c0, Pin = r.P_in[q];
+        if (k == 0) continue;
+        if (!r.has_G) {
+            set_error("constraint rows were not kept: set opts.keep_constraints");
+            return NNVB_E_STATE;
+        }
+        std::vector<double> G(size_t(k) * Pin), c(k), l(k), u(k);
+        if (Pin > 0)
+            NNVB_CUDA(cudaMemcpyAsync(G.data(), r.G.as<double>() + r.h_G_off[q], sizeof(double) * k * Pin,
+                                      cudaMemcpyDeviceToHost, ctx->stream));
+        NNVB_CUDA(cudaMemcpyAsync(c.data(), r.c.as<double>() + c0, sizeof(double) * k, cudaMemcpyDeviceToHost, ctx->stream));
+        NNVB_CUDA(cudaMemcpyAsync(l.data(), r.l.as<double>() + c0, sizeof(double) * k, cudaMemcpyDeviceToHost, ctx->stream));
+        NNVB_CUDA(cudaMemcpyAsync(u.data(), r.u.as<double>() + c0, sizeof(double) * k, cudaMemcpyDeviceToHost, ctx->stream));
+        NNVB_TRY(sync(ctx));
+        // PosLin.m:711-735: C1 = [0 -I], d1 = 0; C2 = [G -I], d2 = -c; C3 = [-a.*G I], d3 = a.*c - a.*l
+        for (int64_t t = 0; t < k; ++t) {
+            const double a = u[t] / (u[t] - l[t]);
+            const double bb = a * l[t];
+            const int64_t newcol = Pin + t;
+            Cmat[size_t(newcol) * m + row + t] = -1.0;
+            Cmat[size_t(newcol) * m + row + k + t] = -1.0;
+            Cmat[size_t(newcol) * m + row + 2 * k + t] = 1.0;
+            d[row + t] = 0.0;
+            d[row + k + t] = -c[t];
+            d[row + 2 * k + t] = a * c[t] - bb;
+            for (int64_t j = 0; j < Pin; ++j) {
+                const double gv = G[size_t(j) * k + t];
+                Cmat[size_t(j) * m + row + k + t] = gv;
+                Cmat[size_t(j) * m + row + 2 * k + t] = -a * gv;
+            }
+        }
+        row += 3 * k;
+    }
+    return NNVB_OK;
+}
+
+int nnvb_batch_halfspace_margins(nnvb_batch* b, int q, const double* G, const double* g, int nh, double* margin_lo,
+                                 int* status) {
+    NNVB_TRY(check_reached(b, q));
+    NNVB_REQUIRE(G && g && nh > 0 && margin_lo, "nnvb_batch_halfspace_margins: bad argument");
+    nnvb_ctx* ctx = b->net->ctx;
+    cudaStream_t st = ctx->stream;
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    const int64_t Nout = b->N;
+    // row-major [nh][Nout] copy of the column-major G
+    std::vector<double> Gr(size_t(nh) * Nout);
+    for (int h = 0; h < nh; ++h)
+        for (int64_t o = 0; o < Nout; ++o) Gr[size_t(h) * Nout + o] = G[size_t(h) + size_t(nh) * o];
+    const size_t gb = sizeof(double) * nh * Nout, sb = sizeof(double) * nh;
+    NNVB_TRY(b->tmp.ensure(gb + 2 * sb + 64, st));
+    double* dG = b->tmp.as<double>();
+    double* dg = dG + size_t(nh) * Nout;
+    double* dm = dg + nh;
+    NNVB_TRY(h2d_small(ctx, dG, Gr.data(), gb));
+    NNVB_TRY(h2d_small(ctx, dg, g, sb));
+    NNVB_TRY(launch_halfspace_margins(st, 1, q, Nout, b->ld, b->V, b->qcol_off[b->list_cur].as<int64_t>(),
+                                      b->qcol_idx[b->list_cur].as<int32_t>(), b->pl.as<double>(), b->pu.as<double>(),
+                                      dG, dg, nh, dm, &ctx->launches));
+    NNVB_CUDA(cudaMemcpyAsync(margin_lo, dm, sb, cudaMemcpyDeviceToHost, st));
+    NNVB_TRY(sync(ctx));
+    if (status)
+        for (int h = 0; h < nh; ++h) status[h] = margin_lo[h] > 0.0 ? NNVB_VERDICT_EMPTY : NNVB_UNDECIDED;
+    return NNVB_OK;
+}
+
+int nnvb_batch_verify_robust(nnvb_batch* b, const int32_t* target, int kind, int* verdict, int* status,
+                             double* margin_lo) {
+    NNVB_TRY(check_reached(b, 0));
+    NNVB_REQUIRE(target && verdict, "nnvb_batch_verify_robust: NULL argument");
+    NNVB_REQUIRE(kind == 0 || kind == 1, "nnvb_batch_verify_robust: kind must be 0 ('max') or 1 ('min')");
+    nnvb_ctx* ctx = b->net->ctx;
+    cudaStream_t st = ctx->stream;
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    const int nq = b->nq;
+    const int64_t Nout = b->N;
+    NNVB_REQUIRE(Nout >= 2, "nnvb_batch_verify_robust: output size must be >= 2");
+    const int nh = int(Nout - 1);
+    // NN.robustness_set (NN.m:1352-1367): rows over i != target; 'max': e_t - e_i, 'min': e_i - e_t
+    std::vector<double> G(size_t(nq) * nh * Nout, 0.0), g(size_t(nq) * nh, 0.0);
+    for (int q = 0; q < nq; ++q) {
+        const int t = target[q];
+        NNVB_REQUIRE(t >= 0 && t < Nout, "target idx must be less than the output size of the NN (query %d: %d)", q, t);
+        int h = 0;
+        for (int i = 0; i < Nout; ++i) {
+            if (i == t) continue;
+            double* row = G.data() + (size_t(q) * nh + h) * Nout;
+            if (kind == 0) { row[i] = -1.0; row[t] = 1.0; }
+            else { row[i] = 1.0; row[t] = -1.0; }
+            ++h;
+        }
+    }
+    const size_t gb = sizeof(double) * G.size(), sb = sizeof(double) * g.size();
+    NNVB_TRY(b->tmp.ensure(gb + 2 * sb + 64, st));
+    double* dG = b->tmp.as<double>();
+    double* dg = dG + G.size();
+    double* dm = dg + g.size();
+    NNVB_CUDA(cudaMemcpyAsync(dG, G.data(), gb, cudaMemcpyHostToDevice, st));
+    NNVB_CUDA(cudaMemsetAsync(dg, 0, sb, st));
+    NNVB_TRY(launch_halfspace_margins(st, nq, 0, Nout, b->ld, b->V, b->qcol_off[b->list_cur].as<int64_t>(),
+                                      b->qcol_idx[b->list_cur].as<int32_t>(), b->pl.as<double>(), b->pu.as<double>(),
+                                      dG, dg, nh, dm, &ctx->launches));
+    std::vector<double> hm(g.size());
+    NNVB_CUDA(cudaMemcpyAsync(hm.data(), dm, sb, cudaMemcpyDeviceToHost, st));
+    NNVB_TRY(sync(ctx));
+    for (int q = 0; q < nq; ++q) {
+        bool all_empty = true;
+        for (int h = 0; h < nh; ++h) {
+            const double mv = hm[size_t(q) * nh + h];
+            const bool empty = mv > 0.0;
+            all_empty = all_empty && empty;
+            if (status) status[size_t(q) * nh + h] = empty ? NNVB_VERDICT_EMPTY : NNVB_UNDECIDED;
+            if (margin_lo) margin_lo[size_t(q) * nh + h] = mv;
+        }
+        verdict[q] = all_empty ? NNVB_VERDICT_EMPTY : NNVB_UNDECIDED;
+    }
+    return NNVB_OK;
+}
+
+// ---------------------------------------------------------------------------
+// single-layer entry points, built on the batch machinery
+
+int nnvb_layer_apply(nnvb_ctx* ctx, const nnvb_layer_desc* layer, int64_t H, int64_t W, int64_t C, int64_t ncols,
+                     const double* V_in, double* V_out, int64_t out_shape[3]) {
+    NNVB_REQUIRE(ctx && layer && V_in && V_out, "nnvb_layer_apply: NULL argument");
+    NNVB_REQUIRE(ncols >= 1, "nnvb_layer_apply: a set has at least its centre column");
+    NNVB_REQUIRE(layer->type != NNVB_LAYER_RELU, "nnvb_layer_apply: use a one-layer network for ReLU (it changes the predicate count)");
+    nnvb_net* net = nullptr;
+    NNVB_TRY(nnvb_net_create(ctx, layer, 1, H, W, C, &net));
+    nnvb_batch* b = nullptr;
+    int s = nnvb_batch_create(net, 1, &b);
+    const int64_t P = ncols - 1;
+    std::vector<double> pl(size_t(P), -1.0), pu(size_t(P), 1.0);
+    if (!s) s = nnvb_batch_set_star(b, 0, P, V_in, pl.data(), pu.data(), 0, nullptr, nullptr);
+    if (!s) s = nnvb_batch_upload(b);
+    if (!s) s = nnvb_batch_reach(b, nullptr);
+    if (!s) s = nnvb_batch_get_V(b, 0, V_out);
+    if (!s && out_shape) s = nnvb_net_out_shape(net, out_shape);
+    nnvb_batch_destroy(b);
+    nnvb_net_destroy(net);
+    return s;
+}
+
+int nnvb_estimate_ranges(nnvb_ctx* ctx, int64_t N, int64_t P, const double* V, const double* pl, const double* pu,
+                         double* lb, double* ub) {
+    NNVB_REQUIRE(ctx && V && lb && ub, "nnvb_estimate_ranges: NULL argument");
+    nnvb_net* net = nullptr;
+    NNVB_TRY(nnvb_net_create(ctx, nullptr, 0, N, 1, 1, &net));
+    nnvb_batch* b = nullptr;
+    int s = nnvb_batch_create(net, 1, &b);
+    std::vector<double> dl, du;
+    if (P > 0 && (!pl || !pu)) {       // Star.m:1091-1096: empty predicate bounds default to [-1, 1]
+        dl.assign(size_t(P), -1.0);
+        du.assign(size_t(P), 1.0);
+        pl = dl.data();
+        pu = du.data();
+    }
+    if (!s) s = nnvb_batch_set_star(b, 0, P, V, pl, pu, 0, nullptr, nullptr);
+    if (!s) s = nnvb_batch_upload(b);
+    if (!s) s = nnvb_batch_reach(b, nullptr);
+    if (!s) s = nnvb_batch_get_ranges(b, 0, lb, ub);
+    nnvb_batch_destroy(b);
+    nnvb_net_destroy(net);
+    return s;
+}
+
+}  // extern "C"

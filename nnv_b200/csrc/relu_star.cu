@@ -1,0 +1,454 @@
+// The LP-free PosLin (ReLU) approx-star step on a batch of star sets:
+//   1. Star.estimateRanges (Star.m:1078-1106): lb/ub of every neuron from the
+//      predicate box,
+//   2. classification (PosLin.m:1594,1598): dead = ub <= 0, crossing = lb < 0 & ub > 0,
+//      and a warp-ballot prefix scan that ranks the crossing neurons of each query
+//      in ascending linear index,
+//   3. Star.resetRow + multipleStepReachStarApprox_at_one (Star.m:1449-1450,
+//      PosLin.m:698-740): zero dead and crossing rows of every existing column,
+//      append a one-hot column per crossing neuron with predicate range [0, ub],
+//      and save the crossing rows (before zeroing) that make up the new
+//      constraint rows.
+// All of it is HBM-bandwidth work: V is read once for the bounds and touched
+// once more where rows are cleared.
+#include "common.cuh"
+
+namespace nnvb {
+
+namespace {
+
+// ---------------------------------------------------------------------------
+// 1. partial bound sums.  A chunk is a run of one query's generator columns
+//    (positions [beg,end) of its predicate-ordered column list).  Every thread
+//    owns two adjacent rows and walks the chunk's columns in order, so the sum
+//    of a chunk has a fixed order; chunks are combined in order by the finalize
+//    kernel.  lo += max(v,0)*pl + min(v,0)*pu ; hi += max(v,0)*pu + min(v,0)*pl.
+template <int UNROLL>
+__global__ void __launch_bounds__(256)
+range_partial_rows2_kernel(int64_t N, int64_t ld, const double* __restrict__ V,
+                           const int32_t* __restrict__ qcol_idx, const double* __restrict__ pl,
+                           const double* __restrict__ pu, const int64_t* __restrict__ chunk_beg,
+                           const int64_t* __restrict__ chunk_end, double* __restrict__ partial) {
+    const int chunk = blockIdx.x;
+    const int64_t i = (int64_t(blockIdx.y) * blockDim.x + threadIdx.x) * 2;
+    if (i >= N) return;
+    const bool two = i + 1 < N;
+    const int64_t beg = chunk_beg[chunk], end = chunk_end[chunk];
+    double lo0 = 0.0, hi0 = 0.0, lo1 = 0.0, hi1 = 0.0;
+    int64_t pos = beg;
+    if (two) {
+        for (; pos + UNROLL <= end; pos += UNROLL) {
+            double2 v[UNROLL];
+            double a[UNROLL], b[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int64_t col = qcol_idx[pos + u];
+                v[u] = __ldcs(reinterpret_cast<const double2*>(V + col * ld + i));
+                a[u] = pl[col];
+                b[u] = pu[col];
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const double p0 = fmax(v[u].x, 0.0), n0 = fmin(v[u].x, 0.0);
+                const double p1 = fmax(v[u].y, 0.0), n1 = fmin(v[u].y, 0.0);
+                lo0 = fma(p0, a[u], lo0); lo0 = fma(n0, b[u], lo0);
+                hi0 = fma(p0, b[u], hi0); hi0 = fma(n0, a[u], hi0);
+                lo1 = fma(p1, a[u], lo1); lo1 = fma(n1, b[u], lo1);
+                hi1 = fma(p1, b[u], hi1); hi1 = fma(n1, a[u], hi1);
+            }
+        }
+    }
+    for (; pos < end; ++pos) {
+        const int64_t col = qcol_idx[pos];
+        const double a = pl[col], b = pu[col];
+        const double x = V[col * ld + i];
+        const double p0 = fmax(x, 0.0), n0 = fmin(x, 0.0);
+        lo0 = fma(p0, a, lo0); lo0 = fma(n0, b, lo0);
+        hi0 = fma(p0, b, hi0); hi0 = fma(n0, a, hi0);
+        if (two) {
+            const double y = V[col * ld + i + 1];
+            const double p1 = fmax(y, 0.0), n1 = fmin(y, 0.0);
+            lo1 = fma(p1, a, lo1); lo1 = fma(n1, b, lo1);
+            hi1 = fma(p1, b, hi1); hi1 = fma(n1, a, hi1);
+        }
+    }
+    double* plo = partial + int64_t(chunk) * 2 * N;
+    double* phi = plo + N;
+    plo[i] = lo0;
+    phi[i] = hi0;
+    if (two) { plo[i + 1] = lo1; phi[i + 1] = hi1; }
+}
+
+// Narrow sets (few rows, many columns): a warp owns 32 rows, the 8 warps of a
+// block split the chunk's columns round-robin and are combined in warp order.
+__global__ void __launch_bounds__(256)
+range_partial_narrow_kernel(int64_t N, int64_t ld, const double* __restrict__ V,
+                            const int32_t* __restrict__ qcol_idx, const double* __restrict__ pl,
+                            const double* __restrict__ pu, const int64_t* __restrict__ chunk_beg,
+                            const int64_t* __restrict__ chunk_end, double* __restrict__ partial) {
+    const int chunk = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t i = int64_t(blockIdx.y) * 32 + lane;
+    const int64_t beg = chunk_beg[chunk], end = chunk_end[chunk];
+    double lo = 0.0, hi = 0.0;
+    if (i < N) {
+        for (int64_t pos = beg + warp; pos < end; pos += 8) {
+            const int64_t col = qcol_idx[pos];
+            const double a = pl[col], b = pu[col];
+            const double x = V[col * ld + i];
+            const double p0 = fmax(x, 0.0), n0 = fmin(x, 0.0);
+            lo = fma(p0, a, lo); lo = fma(n0, b, lo);
+            hi = fma(p0, b, hi); hi = fma(n0, a, hi);
+        }
+    }
+    __shared__ double slo[8][32], shi[8][32];
+    slo[warp][lane] = lo;
+    shi[warp][lane] = hi;
+    __syncthreads();
+    if (warp == 0 && i < N) {
+        double l = 0.0, h = 0.0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) { l += slo[w][lane]; h += shi[w][lane]; }
+        double* plo = partial + int64_t(chunk) * 2 * N;
+        plo[i] = l;
+        plo[N + i] = h;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// 2a. finalize bounds and classify.  grid = (nq, row blocks of FIN_ROWS).
+constexpr int FIN_THREADS = 256;
+constexpr int FIN_ROWS = 1024;   // rows per block (4 per thread)
+
+__global__ void __launch_bounds__(FIN_THREADS)
+range_finalize_kernel(int64_t N, int64_t ld, const double* __restrict__ V,
+                      const int32_t* __restrict__ q_chunk_off, const double* __restrict__ partial,
+                      double* __restrict__ lb, double* __restrict__ ub, uint8_t* __restrict__ state,
+                      int32_t* __restrict__ blk_cross, unsigned long long* __restrict__ q_dead, int nblk) {
+    const int q = blockIdx.x;
+    const int c0 = q_chunk_off[q], c1 = q_chunk_off[q + 1];
+    int n_cross = 0, n_dead = 0;
+    for (int r = 0; r < FIN_ROWS / FIN_THREADS; ++r) {
+        const int64_t i = int64_t(blockIdx.y) * FIN_ROWS + r * FIN_THREADS + threadIdx.x;
+        if (i >= N) break;
+        const double c = V[int64_t(q) * ld + i];     // centre column of query q is column q
+        double lo = 0.0, hi = 0.0;
+        for (int ch = c0; ch < c1; ++ch) {
+            const double* pp = partial + int64_t(ch) * 2 * N;
+            lo += pp[i];
+            hi += pp[N + i];
+        }
+        const double l = c + lo, u = c + hi;
+        lb[int64_t(q) * N + i] = l;
+        ub[int64_t(q) * N + i] = u;
+        uint8_t s = 0;
+        if (u <= 0.0) { s = 1; ++n_dead; }
+        else if (l < 0.0 && u > 0.0) { s = 2; ++n_cross; }
+        state[int64_t(q) * N + i] = s;
+    }
+    // block totals (integer: order-free)
+    __shared__ int sc[FIN_THREADS / 32], sd[FIN_THREADS / 32];
+    for (int o = 16; o; o >>= 1) {
+        n_cross += __shfl_down_sync(0xffffffffu, n_cross, o);
+        n_dead += __shfl_down_sync(0xffffffffu, n_dead, o);
+    }
+    if ((threadIdx.x & 31) == 0) { sc[threadIdx.x >> 5] = n_cross; sd[threadIdx.x >> 5] = n_dead; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tc = 0, td = 0;
+        for (int w = 0; w < FIN_THREADS / 32; ++w) { tc += sc[w]; td += sd[w]; }
+        blk_cross[int64_t(q) * nblk + blockIdx.y] = tc;
+        if (td) atomicAdd(q_dead + q, (unsigned long long)td);
+    }
+}
+
+// 2b. per query: exclusive scan of its block counts; total -> q_cross[q].
+__global__ void scan_blocks_kernel(int nblk, int32_t* __restrict__ blk_cross, int64_t* __restrict__ q_cross) {
+    const int q = blockIdx.x;
+    int32_t* b = blk_cross + int64_t(q) * nblk;
+    __shared__ int warp_tot[32];
+    __shared__ int carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int base = 0; base < nblk; base += blockDim.x) {
+        const int i = base + threadIdx.x;
+        const int v = i < nblk ? b[i] : 0;
+        int inc = v;
+        for (int o = 1; o < 32; o <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += n;
+        }
+        if (lane == 31) warp_tot[warp] = inc;
+        __syncthreads();
+        int before = carry;
+        for (int w = 0; w < warp; ++w) before += warp_tot[w];
+        if (i < nblk) b[i] = before + inc - v;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int tot = 0;
+            for (int w = 0; w < nw; ++w) tot += warp_tot[w];
+            carry += tot;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) q_cross[q] = carry;
+}
+
+// 2c. exclusive scan over queries (single block): q_new_off[0..nq].
+__global__ void scan_queries_kernel(int nq, const int64_t* __restrict__ q_cross, int64_t* __restrict__ q_new_off) {
+    __shared__ long long warp_tot[32];
+    __shared__ long long carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int base = 0; base < nq; base += blockDim.x) {
+        const int i = base + threadIdx.x;
+        const long long v = i < nq ? q_cross[i] : 0;
+        long long inc = v;
+        for (int o = 1; o < 32; o <<= 1) {
+            const long long n = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += n;
+        }
+        if (lane == 31) warp_tot[warp] = inc;
+        __syncthreads();
+        long long before = carry;
+        for (int w = 0; w < warp; ++w) before += warp_tot[w];
+        if (i < nq) q_new_off[i] = before + inc - v;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            long long tot = 0;
+            for (int w = 0; w < nw; ++w) tot += warp_tot[w];
+            carry += tot;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) q_new_off[nq] = carry;
+}
+
+// 2d. rank crossing neurons (ascending index within the query) with a warp
+// ballot scan, and write the per-new-column record.
+__global__ void __launch_bounds__(FIN_THREADS)
+rank_cross_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const uint8_t* __restrict__ state,
+                  const double* __restrict__ lb, const double* __restrict__ ub,
+                  const int32_t* __restrict__ blk_off, int nblk, const int64_t* __restrict__ q_new_off,
+                  int32_t* __restrict__ rank, int32_t* __restrict__ rec_idx, int32_t* __restrict__ rec_q,
+                  double* __restrict__ rec_c, double* __restrict__ rec_l, double* __restrict__ rec_u) {
+    const int q = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ int warp_cnt[FIN_THREADS / 32];
+    int running = blk_off[int64_t(q) * nblk + blockIdx.y];
+    const int64_t new0 = q_new_off[q];
+    for (int r = 0; r < FIN_ROWS / FIN_THREADS; ++r) {
+        const int64_t i = int64_t(blockIdx.y) * FIN_ROWS + r * FIN_THREADS + threadIdx.x;
+        const bool is_cross = i < N && state[int64_t(q) * N + i] == 2;
+        const unsigned bal = __ballot_sync(0xffffffffu, is_cross);
+        if (lane == 0) warp_cnt[warp] = __popc(bal);
+        __syncthreads();
+        int before = running;
+        int tot = 0;
+        for (int w = 0; w < FIN_THREADS / 32; ++w) {
+            if (w < warp) before += warp_cnt[w];
+            tot += warp_cnt[w];
+        }
+        if (is_cross) {
+            const int rk = before + __popc(bal & ((1u << lane) - 1u));
+            rank[int64_t(q) * N + i] = rk;
+            const int64_t c = new0 + rk;
+            rec_idx[c] = int32_t(i);
+            rec_q[c] = q;
+            rec_c[c] = V[int64_t(q) * ld + i];
+            rec_l[c] = lb[int64_t(q) * N + i];
+            rec_u[c] = ub[int64_t(q) * N + i];
+        }
+        running += tot;
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------
+// 3a. clear dead and crossing rows in every existing column; copy the crossing
+// rows of generator columns into the layer's constraint record first.
+// grid = (row blocks, column walkers).
+__global__ void __launch_bounds__(256)
+zero_rows_kernel(int nq, int64_t N, int64_t ld, double* __restrict__ V, int64_t ncols,
+                 const int32_t* __restrict__ col_q, const uint8_t* __restrict__ state,
+                 const int32_t* __restrict__ rank, double* __restrict__ rec_G,
+                 const int64_t* __restrict__ rec_off, const int64_t* __restrict__ q_new_off,
+                 const int64_t* __restrict__ col_pos) {
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    for (int64_t j = blockIdx.y; j < ncols; j += gridDim.y) {
+        const int q = col_q[j];
+        const uint8_t s = state[int64_t(q) * N + i];
+        if (s == 0) continue;
+        double* p = V + j * ld + i;
+        if (s == 2 && rec_G != nullptr && j >= nq) {
+            const int64_t kq = q_new_off[q + 1] - q_new_off[q];
+            rec_G[rec_off[q] + col_pos[j] * kq + rank[int64_t(q) * N + i]] = *p;
+        }
+        *p = 0.0;
+    }
+}
+
+// 3b. one-hot columns for the crossing neurons (the block was zero filled) and
+// their predicate range [0, ub].
+__global__ void append_cols_kernel(int64_t K, int64_t ld, double* __restrict__ V, int64_t ncols_old,
+                                   const int32_t* __restrict__ rec_idx, const int32_t* __restrict__ rec_q,
+                                   const double* __restrict__ rec_u, const int64_t* __restrict__ q_new_off,
+                                   const int64_t* __restrict__ qcol_off, int32_t* __restrict__ col_q,
+                                   double* __restrict__ pl, double* __restrict__ pu,
+                                   int64_t* __restrict__ col_pos) {
+    const int64_t c = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (c >= K) return;
+    const int64_t col = ncols_old + c;
+    const int q = rec_q[c];
+    V[col * ld + rec_idx[c]] = 1.0;
+    col_q[col] = q;
+    pl[col] = 0.0;
+    pu[col] = rec_u[c];
+    col_pos[col] = (qcol_off[q + 1] - qcol_off[q]) + (c - q_new_off[q]);
+}
+
+// 3c. new predicate-ordered column lists: old list of the query, then its new columns.
+__global__ void rebuild_lists_kernel(int nq, const int64_t* __restrict__ qcol_off,
+                                     const int32_t* __restrict__ qcol_idx,
+                                     const int64_t* __restrict__ q_new_off, int64_t ncols_old,
+                                     int64_t* __restrict__ new_off, int32_t* __restrict__ new_idx) {
+    const int q = blockIdx.x;
+    const int64_t o0 = qcol_off[q], o1 = qcol_off[q + 1];
+    const int64_t n0 = q_new_off[q], n1 = q_new_off[q + 1];
+    const int64_t dst = o0 + n0;
+    for (int64_t t = threadIdx.x; t < o1 - o0; t += blockDim.x) new_idx[dst + t] = qcol_idx[o0 + t];
+    for (int64_t t = threadIdx.x; t < n1 - n0; t += blockDim.x)
+        new_idx[dst + (o1 - o0) + t] = int32_t(ncols_old + n0 + t);
+    if (threadIdx.x == 0) {
+        new_off[q] = dst;
+        if (q == nq - 1) new_off[nq] = o1 + n1;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Halfspace rows and their minimum over the predicate box.
+// block = one (query, halfspace); lanes stride over the query's columns.
+__global__ void __launch_bounds__(256)
+halfspace_margin_kernel(int q_base, int64_t Nout, int64_t ld, const double* __restrict__ V,
+                        const int64_t* __restrict__ qcol_off, const int32_t* __restrict__ qcol_idx,
+                        const double* __restrict__ pl, const double* __restrict__ pu,
+                        const double* __restrict__ G, const double* __restrict__ g, int nh,
+                        double* __restrict__ margin) {
+    const int bq = blockIdx.x, h = blockIdx.y;
+    const int q = q_base + bq;
+    const double* Gr = G + (int64_t(bq) * nh + h) * Nout;
+    double acc = 0.0;
+    const int64_t o0 = qcol_off[q], o1 = qcol_off[q + 1];
+    for (int64_t pos = o0 + threadIdx.x; pos < o1; pos += blockDim.x) {
+        const int64_t col = qcol_idx[pos];
+        const double* v = V + col * ld;
+        double r = 0.0;
+        for (int64_t o = 0; o < Nout; ++o) r = fma(Gr[o], v[o], r);
+        acc += fmin(r * pl[col], r * pu[col]);
+    }
+    __shared__ double s[256];
+    s[threadIdx.x] = acc;
+    __syncthreads();
+    for (int o = 128; o; o >>= 1) {
+        if (threadIdx.x < o) s[threadIdx.x] += s[threadIdx.x + o];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        const double* v = V + int64_t(q) * ld;
+        double r = 0.0;
+        for (int64_t o = 0; o < Nout; ++o) r = fma(Gr[o], v[o], r);
+        margin[int64_t(bq) * nh + h] = (r - g[int64_t(bq) * nh + h]) + s[0];
+    }
+}
+
+}  // namespace
+
+int launch_estimate_ranges(cudaStream_t st, const ReluWork& w, int64_t* launches) {
+    if (w.n_chunks > 0) {
+        if (w.N >= 256) {
+            dim3 grid((unsigned)w.n_chunks, (unsigned)ceil_div(ceil_div(w.N, 2), 256));
+            range_partial_rows2_kernel<4><<<grid, 256, 0, st>>>(w.N, w.ld, w.V, w.qcol_idx, w.pl, w.pu,
+                                                               w.chunk_beg, w.chunk_end, w.partial);
+        } else {
+            dim3 grid((unsigned)w.n_chunks, (unsigned)ceil_div(w.N, 32));
+            range_partial_narrow_kernel<<<grid, 256, 0, st>>>(w.N, w.ld, w.V, w.qcol_idx, w.pl, w.pu,
+                                                              w.chunk_beg, w.chunk_end, w.partial);
+        }
+        NNVB_CUDA(cudaGetLastError());
+        if (launches) *launches += 1;
+    }
+    return NNVB_OK;
+}
+
+int relu_blocks_per_query(int64_t N) { return (int)ceil_div(N, FIN_ROWS); }
+
+int launch_classify_scan(cudaStream_t st, const ReluWork& w, int64_t* launches) {
+    const int nblk = relu_blocks_per_query(w.N);
+    NNVB_CUDA(cudaMemsetAsync(w.q_dead, 0, sizeof(int64_t) * w.nq, st));
+    dim3 grid((unsigned)w.nq, (unsigned)nblk);
+    range_finalize_kernel<<<grid, FIN_THREADS, 0, st>>>(w.N, w.ld, w.V, w.q_chunk_off, w.partial, w.lb,
+                                                        w.ub, w.state, w.blk_cross,
+                                                        reinterpret_cast<unsigned long long*>(w.q_dead), nblk);
+    NNVB_CUDA(cudaGetLastError());
+    scan_blocks_kernel<<<w.nq, 256, 0, st>>>(nblk, w.blk_cross, w.q_cross);
+    NNVB_CUDA(cudaGetLastError());
+    scan_queries_kernel<<<1, 1024, 0, st>>>(w.nq, w.q_cross, w.q_new_off);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 3;
+    return NNVB_OK;
+}
+
+int launch_rank_cross(cudaStream_t st, const ReluWork& w, const ReluRecord& rec, int64_t* launches) {
+    const int nblk = relu_blocks_per_query(w.N);
+    dim3 grid((unsigned)w.nq, (unsigned)nblk);
+    rank_cross_kernel<<<grid, FIN_THREADS, 0, st>>>(w.N, w.ld, w.V, w.state, w.lb, w.ub, w.blk_cross, nblk,
+                                                    w.q_new_off, w.rank, rec.idx, rec.q, rec.c, rec.l, rec.u);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_relu_zero_rows(cudaStream_t st, const ReluWork& w, int64_t ncols, const int32_t* col_q,
+                          const ReluRecord& rec, const int64_t* col_pos, int64_t* launches) {
+    dim3 grid((unsigned)ceil_div(w.N, 256), (unsigned)std::min<int64_t>(ncols, 32768));
+    zero_rows_kernel<<<grid, 256, 0, st>>>(w.nq, w.N, w.ld, w.V, ncols, col_q, w.state, w.rank, rec.G,
+                                           rec.G_off, w.q_new_off, col_pos);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, int64_t K,
+                       const ReluRecord& rec, int32_t* col_q, double* pl, double* pu, int64_t* col_pos,
+                       int64_t* new_qcol_off, int32_t* new_qcol_idx, int64_t* launches) {
+    if (K > 0) {
+        NNVB_CUDA(cudaMemsetAsync(w.V + ncols_old * w.ld, 0, sizeof(double) * w.ld * K, st));
+        append_cols_kernel<<<(unsigned)ceil_div(K, 256), 256, 0, st>>>(K, w.ld, w.V, ncols_old, rec.idx, rec.q,
+                                                                      rec.u, w.q_new_off, w.qcol_off, col_q,
+                                                                      pl, pu, col_pos);
+        NNVB_CUDA(cudaGetLastError());
+        if (launches) *launches += 1;
+    }
+    rebuild_lists_kernel<<<w.nq, 128, 0, st>>>(w.nq, w.qcol_off, w.qcol_idx, w.q_new_off, ncols_old,
+                                               new_qcol_off, new_qcol_idx);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_halfspace_margins(cudaStream_t st, int nq, int q_base, int64_t Nout, int64_t ld, const double* V,
+                             const int64_t* qcol_off, const int32_t* qcol_idx, const double* pl,
+                             const double* pu, const double* G, const double* g, int nh,
+                             double* margin, int64_t* launches) {
+    if (nq <= 0 || nh <= 0) return NNVB_OK;
+    dim3 grid((unsigned)nq, (unsigned)nh);
+    halfspace_margin_kernel<<<grid, 256, 0, st>>>(q_base, Nout, ld, V, qcol_off, qcol_idx, pl, pu, G, g, nh, margin);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+}  // namespace nnvb

@@ -1,0 +1,548 @@
+"""Reference-shaped host API over the CUDA engine.
+
+Class and method names, argument meaning and error behaviour follow the
+reference's MATLAB classes for the approx-star path, so that a script written
+against ``NN.reach(inputSet, reachOptions)`` / ``NN.verify_robustness`` reads
+the same here:
+
+    NN                         code/nnv/engine/nn/NN.m
+    ImageStar / Star           code/nnv/engine/set/ImageStar.m, Star.m
+    HalfSpace                  code/nnv/engine/set/HalfSpace.m
+    Conv2DLayer, FullyConnectedLayer, BatchNormalizationLayer,
+    AveragePooling2DLayer, ReluLayer
+                               code/nnv/engine/nn/layers/*.m
+    verify_specification       code/nnv/engine/utils/verify_specification.m
+
+All set arithmetic runs on the GPU through libnnvb200.so.  The one step that
+stays on the host is the feasibility LP of Star.isEmptySet for halfspaces the
+device tests leave undecided; the reference hands that LP to linprog/glpk
+(lpsolver.m), this module hands it to HiGHS.
+"""
+from __future__ import annotations
+
+import time
+
+import numpy as np
+import scipy.sparse as sp
+from scipy.optimize import linprog
+
+from . import _lib as L
+from .engine import Batch, Context, Network
+
+__all__ = ["NN", "ImageStar", "Star", "HalfSpace", "Conv2DLayer", "FullyConnectedLayer",
+           "BatchNormalizationLayer", "AveragePooling2DLayer", "ReluLayer", "verify_specification",
+           "default_context"]
+
+_ctx = None
+
+
+def default_context(device=0, arena_bytes=0):
+    """Process-wide engine context (created on first use)."""
+    global _ctx
+    if _ctx is None:
+        _ctx = Context(device, arena_bytes)
+    return _ctx
+
+
+# --------------------------------------------------------------------------- sets
+
+
+class ImageStar:
+    """ImageStar.m:47-94.  ``ImageStar(lb, ub)`` (ImageStar.m:302-343) or
+    ``ImageStar(V, C, d, pred_lb, pred_ub)`` (ImageStar.m:172-227)."""
+
+    def __init__(self, *args):
+        self.im_lb = self.im_ub = None
+        self._lazy = None
+        if len(args) == 2:
+            lb = np.asarray(args[0], dtype=np.float64)
+            ub = np.asarray(args[1], dtype=np.float64)
+            if lb.size == 0:
+                raise ValueError("Invalid lower bound image")
+            if ub.size == 0:
+                raise ValueError("Invalid upper bound image")
+            if lb.shape != ub.shape:
+                raise ValueError("Inconsistency between lower bound image and upper bound image")
+            if lb.ndim == 2:
+                lb, ub = lb[:, :, None], ub[:, :, None]
+            self.im_lb, self.im_ub = lb, ub
+            self.height, self.width, self.numChannel = lb.shape
+            n = lb.size
+            lbv, ubv = lb.reshape(n, order="F"), ub.reshape(n, order="F")
+            nz = np.nonzero(0.5 * (ubv - lbv) != 0)[0] if n > 1 else np.arange(1)
+            self.numPred = len(nz)
+            self._V = None                      # built on demand: centre + diag of half widths
+            self._C = np.zeros((1, self.numPred))
+            self.d = np.zeros(1)
+            self.pred_lb = -np.ones(self.numPred)
+            self.pred_ub = np.ones(self.numPred)
+        elif len(args) == 5:
+            V, Cm, d, pl, pu = args
+            V = np.asfortranarray(np.asarray(V, dtype=np.float64))
+            if V.ndim == 3:
+                V = V[:, :, :, None]
+            if V.ndim != 4:
+                raise ValueError("Invalid basis matrix")
+            Cm = np.atleast_2d(np.asarray(Cm, dtype=np.float64))
+            d = np.asarray(d, dtype=np.float64).ravel()
+            pl = np.asarray(pl, dtype=np.float64).ravel()
+            pu = np.asarray(pu, dtype=np.float64).ravel()
+            if Cm.size and Cm.shape[0] != d.size:
+                raise ValueError("Inconsistent dimension between constraint matrix and constraint vector")
+            if Cm.size and Cm.shape[1] != V.shape[3] - 1:
+                raise ValueError("Inconsistent dimension between the basis matrix and the constraint matrix")
+            if pl.size != pu.size or pl.size != V.shape[3] - 1:
+                raise ValueError("Number of predicates is different from the size of the lower bound or upper bound predicate vector")
+            self.height, self.width, self.numChannel = V.shape[:3]
+            self.numPred = V.shape[3] - 1
+            self._V, self._C, self.d, self.pred_lb, self.pred_ub = V, Cm, d, pl, pu
+        else:
+            raise ValueError("Invalid number of input arguments, (2 or 5)")
+
+    # V and C may live on the device until somebody asks for them
+    @property
+    def V(self):
+        if self._V is None:
+            if self._lazy is not None:
+                self._V = self._lazy[0].get_V(self._lazy[1])
+            else:
+                n = self.height * self.width * self.numChannel
+                lbv = self.im_lb.reshape(n, order="F")
+                ubv = self.im_ub.reshape(n, order="F")
+                vec = 0.5 * (ubv - lbv)
+                nz = np.nonzero(vec != 0)[0] if n > 1 else np.arange(1)
+                M = np.zeros((n, len(nz) + 1), order="F")
+                M[:, 0] = 0.5 * (lbv + ubv)
+                M[nz, np.arange(1, len(nz) + 1)] = vec[nz]
+                self._V = M.reshape(self.height, self.width, self.numChannel, -1, order="F")
+        return self._V
+
+    @property
+    def C(self):
+        if self._C is None and self._lazy is not None:
+            self._C, self.d = self._lazy[0].get_constraints(self._lazy[1])
+        return self._C
+
+    def toStar(self):
+        """ImageStar.m:569-592."""
+        n = self.height * self.width * self.numChannel
+        S = Star(self.V.reshape(n, -1, order="F"), self.C, self.d, self.pred_lb, self.pred_ub)
+        return S
+
+    def estimateRanges(self, ctx=None):
+        """ImageStar.estimateRanges (ImageStar.m:836-885); returns images lb, ub."""
+        lb, ub = self.toStar().estimateRanges(ctx)
+        shp = (self.height, self.width, self.numChannel)
+        return lb.reshape(shp, order="F"), ub.reshape(shp, order="F")
+
+    def _query(self):
+        if self._V is None and self.im_lb is not None and self._lazy is None:
+            return {"lb": self.im_lb, "ub": self.im_ub}
+        return {"V": self.V, "C": self.C, "d": self.d, "pl": self.pred_lb, "pu": self.pred_ub}
+
+
+class Star:
+    """Star.m:13-24.  ``Star(lb, ub)`` (Star.m:220-237) or ``Star(V, C, d, pred_lb, pred_ub)``
+    (Star.m:151-191)."""
+
+    def __init__(self, *args):
+        if len(args) == 2:
+            lb = np.asarray(args[0], dtype=np.float64).ravel()
+            ub = np.asarray(args[1], dtype=np.float64).ravel()
+            if lb.size != ub.size:
+                raise ValueError("Inconsistent dimensions between lb and ub")
+            I = ImageStar(lb.reshape(-1, 1, 1), ub.reshape(-1, 1, 1))
+            self.V = I.V.reshape(lb.size, -1, order="F")
+            self.C, self.d = I.C, I.d
+            self.predicate_lb, self.predicate_ub = I.pred_lb, I.pred_ub
+            self.state_lb, self.state_ub = lb, ub
+        elif len(args) in (3, 5):
+            V = np.asfortranarray(np.atleast_2d(np.asarray(args[0], dtype=np.float64)))
+            Cm = np.atleast_2d(np.asarray(args[1], dtype=np.float64))
+            d = np.asarray(args[2], dtype=np.float64).ravel()
+            if Cm.size and V.shape[1] != Cm.shape[1] + 1:
+                raise ValueError("Inconsistency between basic matrix and constraint matrix")
+            if Cm.size and Cm.shape[0] != d.size:
+                raise ValueError("Inconsistency between constraint matrix and constraint vector")
+            self.V, self.C, self.d = V, Cm, d
+            if len(args) == 5:
+                self.predicate_lb = np.asarray(args[3], dtype=np.float64).ravel()
+                self.predicate_ub = np.asarray(args[4], dtype=np.float64).ravel()
+                if self.predicate_lb.size != V.shape[1] - 1 or self.predicate_ub.size != V.shape[1] - 1:
+                    raise ValueError("Inconsistency between number of predicate variables and predicate lower- or upper-bounds vector")
+            else:
+                self.predicate_lb = np.zeros(0)
+                self.predicate_ub = np.zeros(0)
+            self.state_lb = self.state_ub = None
+        else:
+            raise ValueError("Invalid number of input arguments (should be 2, 3 or 5)")
+        self.dim = self.V.shape[0]
+        self.nVar = self.V.shape[1] - 1
+
+    def toImageStar(self, height, width, numChannel):
+        """Star.m:1398-1418."""
+        if self.dim != height * width * numChannel:
+            raise ValueError("Inconsistent dimension in the ImageStar and the original Star set")
+        pl, pu = self._pred_bounds()
+        return ImageStar(self.V.reshape(height, width, numChannel, -1, order="F"), self.C, self.d, pl, pu)
+
+    def _pred_bounds(self):
+        if self.predicate_lb.size == 0 and self.nVar > 0:      # Star.m:1091-1096
+            return -np.ones(self.nVar), np.ones(self.nVar)
+        return self.predicate_lb, self.predicate_ub
+
+    def estimateRanges(self, ctx=None):
+        """Star.estimateRanges, Star.m:1078-1106 (on the GPU)."""
+        ctx = ctx or default_context()
+        pl, pu = self._pred_bounds()
+        return ctx.estimate_ranges(self.V, pl, pu)
+
+    def affineMap(self, W, b=None):
+        """Star.affineMap, Star.m:313-343 (on the GPU as a one-layer network)."""
+        W = np.atleast_2d(np.asarray(W, dtype=np.float64))
+        if W.shape[1] != self.dim:
+            raise ValueError("Inconsistency between the affine mapping matrix and dimension of the star set")
+        b = np.zeros(W.shape[0]) if b is None else np.asarray(b, dtype=np.float64).ravel()
+        if b.size != W.shape[0]:
+            raise ValueError("Inconsistency between the mapping vec and mapping matrix")
+        out = default_context().layer_apply({"type": "fc", "W": W, "b": b}, self.V.reshape(self.dim, 1, 1, -1, order="F"))
+        return Star(out.reshape(W.shape[0], -1, order="F"), self.C, self.d, self.predicate_lb, self.predicate_ub)
+
+    def intersectHalfSpace(self, H, g):
+        """Star.intersectHalfSpace, Star.m:555-589; returns None when empty."""
+        H = np.atleast_2d(np.asarray(H, dtype=np.float64))
+        g = np.asarray(g, dtype=np.float64).reshape(-1)
+        if H.shape[0] != g.size:
+            raise ValueError("Inconsistent dimension between Halfspace matrix and halfspace vector")
+        if H.shape[1] != self.dim:
+            raise ValueError("Inconsistent dimension between halfspace and star set")
+        C1 = H @ self.V[:, 1:]
+        d1 = g - H @ self.V[:, 0]
+        Cn = np.vstack([self.C, C1]) if np.size(self.C) else C1
+        dn = np.concatenate([self.d, d1]) if np.size(self.C) else d1
+        S = Star(self.V, Cn, dn, self.predicate_lb, self.predicate_ub)
+        return None if S.isEmptySet() else S
+
+    def isEmptySet(self):
+        """Star.isEmptySet, Star.m:1216-1232."""
+        return _lp_is_empty(sp.csr_matrix(self.C), self.d, self.predicate_lb, self.predicate_ub)
+
+    def _query(self):
+        pl, pu = self._pred_bounds()
+        return {"V": self.V.reshape(self.dim, 1, 1, -1, order="F"), "C": self.C, "d": self.d, "pl": pl, "pu": pu}
+
+
+class HalfSpace:
+    """HalfSpace.m:14-32: the set G x <= g."""
+
+    def __init__(self, G, g):
+        G = np.atleast_2d(np.asarray(G, dtype=np.float64))
+        g = np.asarray(g, dtype=np.float64).reshape(-1)
+        if G.shape[0] != g.size:
+            raise ValueError("Inconsistent dimension between half-space matrix and half-space vector")
+        self.G, self.g, self.dim = G, g, G.shape[1]
+
+
+def _lp_is_empty(Cs, d, pl, pu):
+    """lpsolver(f=0, C, d, [], [], pl, pu, 'linprog', 'emptySet') (lpsolver.m): the
+    box-only closed form (:34-49), else a feasibility LP.  Exit mapping of
+    Star.m:1224-1230: feasible -> not empty, infeasible -> empty, else error."""
+    d = np.asarray(d, dtype=np.float64).ravel()
+    P = Cs.shape[1]
+    if Cs.nnz == 0 and pl.size and np.all(np.isfinite(pl)) and np.all(np.isfinite(pu)) and np.all(d >= 0):
+        return False
+    bounds = list(zip(pl, pu)) if pl.size else [(None, None)] * P
+    res = linprog(np.zeros(P), A_ub=Cs, b_ub=d, bounds=bounds, method="highs")
+    if res.status == 0:
+        return False
+    if res.status == 2:
+        return True
+    raise RuntimeError("Error, exitflag = %d (%s)" % (res.status, res.message))
+
+
+# ------------------------------------------------------------------------- layers
+
+
+class _Layer:
+    Name = ""
+
+    def _desc(self):
+        raise NotImplementedError
+
+    def reach(self, in_set, method="approx-star", option=None, relaxFactor=0, dis_opt=None, lp_solver="linprog"):
+        """The reference's 6-argument layer contract; one set or a list of sets."""
+        sets = in_set if isinstance(in_set, (list, tuple)) else [in_set]
+        shape = _set_shape(sets[0])
+        net = NN([self], input_shape=shape)
+        out = [net.reach(s, {"reachMethod": method, "relaxFactor": relaxFactor}) for s in sets]
+        return out if isinstance(in_set, (list, tuple)) else out[0]
+
+
+class Conv2DLayer(_Layer):
+    """Conv2DLayer.m:84-144 — Weights[kh,kw,Cin,Cout], Bias[1,1,Cout], PaddingSize [t b l r]."""
+
+    def __init__(self, Weights, Bias, PaddingSize=(0, 0, 0, 0), Stride=(1, 1), DilationFactor=(1, 1), Name="conv2d"):
+        W = np.asarray(Weights, dtype=np.float64)
+        if W.ndim == 2:
+            W = W[:, :, None, None]
+        if W.ndim == 3:
+            W = W[:, :, :, None]
+        b = np.asarray(Bias, dtype=np.float64).ravel()
+        if b.size != W.shape[3]:
+            raise ValueError("Inconsistency between filter weights and filter biases")
+        if len(PaddingSize) != 4:
+            raise ValueError("Invalid padding size")
+        self.Weights, self.Bias = W, b
+        self.PaddingSize, self.Stride, self.DilationFactor = tuple(PaddingSize), tuple(Stride), tuple(DilationFactor)
+        self.NumChannels, self.NumFilters, self.FilterSize = W.shape[2], W.shape[3], W.shape[:2]
+        self.Name = Name
+
+    def _desc(self):
+        return {"type": "conv2d", "W": self.Weights, "b": self.Bias, "pad": self.PaddingSize,
+                "stride": self.Stride, "dilation": self.DilationFactor}
+
+
+class FullyConnectedLayer(_Layer):
+    """FullyConnectedLayer.m:56-66 — Weights[Out,In], Bias[Out,1]."""
+
+    def __init__(self, Weights, Bias, Name="fc"):
+        W = np.atleast_2d(np.asarray(Weights, dtype=np.float64))
+        b = np.asarray(Bias, dtype=np.float64).ravel()
+        if b.size != W.shape[0]:
+            raise ValueError("Inconsistent dimension between the weight matrix and bias vector")
+        self.Weights, self.Bias = W, b
+        self.OutputSize, self.InputSize = W.shape
+        self.Name = Name
+
+    def _desc(self):
+        return {"type": "fc", "W": self.Weights, "b": self.Bias}
+
+
+class BatchNormalizationLayer(_Layer):
+    """BatchNormalizationLayer.m:14,72-77 — name/value constructor."""
+
+    def __init__(self, **kw):
+        self.Name = kw.get("Name", "bn")
+        self.TrainedMean = np.asarray(kw["TrainedMean"], dtype=np.float64).ravel()
+        self.TrainedVariance = np.asarray(kw["TrainedVariance"], dtype=np.float64).ravel()
+        self.Scale = np.asarray(kw["Scale"], dtype=np.float64).ravel()
+        self.Offset = np.asarray(kw["Offset"], dtype=np.float64).ravel()
+        self.Epsilon = float(kw.get("Epsilon", 1e-5))
+        self.NumChannels = int(kw.get("NumChannels", self.TrainedMean.size))
+
+    def _desc(self):
+        return {"type": "bn", "mean": self.TrainedMean, "var": self.TrainedVariance, "scale": self.Scale,
+                "offset": self.Offset, "eps": self.Epsilon}
+
+
+class AveragePooling2DLayer(_Layer):
+    """AveragePooling2DLayer.m:109-131 — PoolSize, Stride, PaddingSize."""
+
+    def __init__(self, PoolSize=(2, 2), Stride=(1, 1), PaddingSize=(0, 0, 0, 0), Name="average_pooling_2d"):
+        if len(PoolSize) != 2 or len(Stride) != 2 or len(PaddingSize) != 4:
+            raise ValueError("Invalid pooling parameters")
+        self.PoolSize, self.Stride, self.PaddingSize, self.Name = tuple(PoolSize), tuple(Stride), tuple(PaddingSize), Name
+
+    def _desc(self):
+        return {"type": "avgpool", "pool": self.PoolSize, "stride": self.Stride, "pad": self.PaddingSize}
+
+
+class ReluLayer(_Layer):
+    """ReluLayer.m — PosLin applied to every neuron."""
+
+    def __init__(self, Name="relu"):
+        self.Name = Name
+
+    def _desc(self):
+        return {"type": "relu"}
+
+
+def _set_shape(s):
+    if isinstance(s, ImageStar):
+        return (s.height, s.width, s.numChannel)
+    if isinstance(s, Star):
+        return (s.dim, 1, 1)
+    raise TypeError('Wrong input set type. Input set must be of type "Star" or "ImageStar"')
+
+
+_LP_FREE_RELAX = ("relax-star-range", "relax-star-area", "relax-star-bound", "relax-star-ub",
+                  "relax-star-random", "relax-star-static")
+
+
+def _validate_reach_options(opts):
+    """The part of NN.validate_reach_options (NN.m:1203-1233) this engine honours.
+    Only the LP-free bound mode exists: 'approx-star' (estimated ranges) or a
+    'relax-star-*' method with relaxFactor = 1."""
+    opts = dict(opts or {})
+    method = opts.get("reachMethod", "approx-star")
+    rf = opts.get("relaxFactor", 1 if method in _LP_FREE_RELAX else 0)
+    if method == "approx-star":
+        if opts.get("bounds", "estimate") != "estimate":
+            raise NotImplementedError("only bounds='estimate' (LP-free ranges) is implemented for approx-star")
+    elif method in _LP_FREE_RELAX:
+        if rf != 1:
+            raise NotImplementedError("relax-star methods are implemented for relaxFactor = 1 only (no LP)")
+    else:
+        raise NotImplementedError("reachMethod %r is outside this engine (approx-star / relax-star-* only)" % (method,))
+    if not (0 <= rf <= 1):
+        raise ValueError("Invalid relaxFactor. The value of relax factor must be between 0 and 1")
+    opts["reachMethod"], opts["relaxFactor"] = method, rf
+    return opts
+
+
+# ---------------------------------------------------------------------------- NN
+
+
+class NN:
+    """NN.m — network container, reach driver and robustness API.
+
+    ``layers`` is a list of layer objects (or neutral layer dicts);
+    ``input_shape`` may be given up front, else it is taken from the first set.
+    """
+
+    def __init__(self, layers, input_shape=None, Name="nn", ctx=None):
+        self.Layers = list(layers)
+        self.numLayers = len(self.Layers)
+        self.Name = Name
+        self.ctx = ctx
+        self._nets = {}
+        self.reachTime = []
+        self.reachStats = []
+        self.reachMethod = "approx-star"
+        self.relaxFactor = 0
+        self.lp_solver = "linprog"
+        self.input_shape = tuple(input_shape) if input_shape is not None else None
+        self.exactReach = False          # approx methods never promote unknown -> not robust (NN.m:539-543)
+
+    def _layer_dicts(self):
+        return [l if isinstance(l, dict) else l._desc() for l in self.Layers]
+
+    def _network(self, shape):
+        shape = tuple(int(x) for x in shape)
+        if shape not in self._nets:
+            self._nets[shape] = Network(self.ctx or default_context(), self._layer_dicts(), shape)
+        return self._nets[shape]
+
+    @property
+    def OutputSize(self):
+        last = [l for l in self._layer_dicts() if l["type"] == "fc"]
+        return last[-1]["W"].shape[0] if last else 0
+
+    # -- reach -----------------------------------------------------------------
+    def reach_batch(self, inputSets, reachOptions=None, keep_constraints=False, keep_layer_bounds=False):
+        """Push a list of input sets through the network together; returns the Batch
+        (device-resident results).  Array-of-sets form of NN.reach."""
+        _validate_reach_options(reachOptions)
+        shape = _set_shape(inputSets[0])
+        for s in inputSets:
+            if _set_shape(s) != shape:
+                raise ValueError("all input sets of a batch must have the same shape")
+        net = self._network(shape)
+        b = Batch(net, [s._query() for s in inputSets])
+        t0 = time.perf_counter()
+        b.upload()
+        b.reach(keep_constraints=keep_constraints, keep_layer_bounds=keep_layer_bounds)
+        self.reachTime = [time.perf_counter() - t0]
+        self.reachStats = b.relu_stats()
+        return b
+
+    def reach(self, inputSet, reachOptions=None):
+        """NN.reach (NN.m:189-278): returns the output set (ImageStar for image
+        input, Star for vector input).  V and C are fetched from the device when
+        first read."""
+        if not isinstance(inputSet, (Star, ImageStar)):
+            raise TypeError('Wrong input set type. Input set must be of type "Star" or "ImageStar"')
+        opts = _validate_reach_options(reachOptions)
+        self.reachMethod, self.relaxFactor = opts["reachMethod"], opts["relaxFactor"]
+        b = self.reach_batch([inputSet], opts, keep_constraints=True)
+        return _result_set(b, 0, isinstance(inputSet, Star))
+
+    # -- robustness ------------------------------------------------------------
+    def robustness_set(self, target, class_type="max"):
+        """NN.robustness_set (NN.m:1334-1368); ``target`` is 1-based like the reference."""
+        outSize = self.OutputSize
+        if outSize == 0:
+            raise ValueError("Output size is set to 0, but it must be >= 1")
+        if target > outSize or target < 1:
+            raise ValueError("Target idx must be less than or equal to the output size of the NN.")
+        G = np.delete(np.eye(outSize), target - 1, axis=0)
+        if class_type == "max":
+            G = -G
+            G[:, target - 1] = 1.0
+        elif class_type == "min":
+            G[:, target - 1] = -1.0
+        else:
+            raise ValueError("class_type must be 'max' or 'min'")
+        return [HalfSpace(G[i], 0.0) for i in range(G.shape[0])]
+
+    def checkRobust(self, outputSet, target):
+        """NN.checkRobust (NN.m:617-648)."""
+        sets = outputSet if isinstance(outputSet, (list, tuple)) else [outputSet]
+        R = [s if isinstance(s, Star) else s.toStar() for s in sets]
+        if not isinstance(target, (HalfSpace, list, tuple)):
+            if np.isscalar(target):
+                target = self.robustness_set(int(target), "max")
+            else:
+                raise ValueError("Target must be a HalfSpace (unsafe/not robust region) or as a scalar determining the output label target.")
+        return verify_specification(R, target)
+
+    def verify_robustness(self, inputSet, reachOptions, target):
+        """NN.verify_robustness (NN.m:651-667): 1 robust, 2 unknown (0 is never
+        produced by an over-approximating method).  ``target`` is the 1-based label
+        or HalfSpace(s)."""
+        if np.isscalar(target):
+            return int(self.verify_robustness_batch([inputSet], reachOptions, [int(target)])[0])
+        R = self.reach(inputSet, reachOptions)
+        return self.checkRobust(R, target)
+
+    def verify_robustness_batch(self, inputSets, reachOptions, targets, class_type="max", stats=None):
+        """verify_robustness over a list of sets with 1-based label targets.
+
+        Device side: reach, then the box minimum of every halfspace row (a
+        positive minimum proves the intersection empty).  Host side, only for
+        the halfspaces left undecided: the feasibility LP of Star.isEmptySet on
+        the constraint system of that query, re-reached with constraint records
+        kept."""
+        b = self.reach_batch(inputSets, reachOptions)
+        t0 = np.asarray(targets, dtype=np.int64) - 1
+        verdict, status, _ = b.verify_robust(t0, class_type)
+        result = np.where(verdict == L.VERDICT_EMPTY, 1, 0).astype(np.int64)
+        undecided = np.nonzero(verdict != L.VERDICT_EMPTY)[0]
+        if stats is not None:
+            stats["n_prefilter"] = int((verdict == L.VERDICT_EMPTY).sum())
+            stats["n_lp_queries"] = int(len(undecided))
+        b.close()
+        for q in undecided:
+            # one query at a time keeps the constraint records small
+            bq = self.reach_batch([inputSets[q]], reachOptions, keep_constraints=True)
+            S = _result_set(bq, 0, True)
+            hs = self.robustness_set(int(targets[q]), class_type)
+            open_rows = np.nonzero(status[q] != L.VERDICT_EMPTY)[0]
+            result[q] = verify_specification([S], [hs[i] for i in open_rows])
+            bq.close()
+        return result
+
+
+def _result_set(b, q, as_star):
+    P, m = b.out_dims(q)
+    h, w, c = b.net.out_shape
+    pl, pu = b.get_pred_bounds(q)
+    V = b.get_V(q)
+    Cm, d = b.get_constraints(q)
+    if as_star:
+        return Star(V.reshape(h * w * c, -1, order="F"), Cm, d, pl, pu)
+    return ImageStar(V, Cm, d, pl, pu)
+
+
+def verify_specification(reachSet, property):
+    """verify_specification.m:36-79: OR over halfspaces, AND over sets; 1 iff every
+    intersection is empty, 2 at the first non-empty one."""
+    R = reachSet if isinstance(reachSet, (list, tuple)) else [reachSet]
+    prop = property if isinstance(property, (list, tuple)) else [property]
+    for hs in prop:
+        for S in R:
+            if not isinstance(S, Star):
+                S = S.toStar()
+            if S.intersectHalfSpace(hs.G, hs.g) is not None:
+                return 2
+    return 1

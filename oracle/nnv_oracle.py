@@ -1,0 +1,365 @@
+"""CPU restatement of the reference's approx-star (estimated-bounds) path.
+
+TEST INFRASTRUCTURE ONLY.  This module is the checker for the CUDA engine:
+only the tests, the smoke check and the benchmark's CPU-baseline leg may
+import it.  The shipped package never does.
+
+Parity status: the reference is MATLAB-only and cannot run where this code
+runs, so the restatement is pinned (a) against the reference's own known-answer
+tests and stored ``.mat`` baselines for the individual operations (fixtures in
+tests/golden/reference_kats.npz) and (b) by following the reference source
+function by function, cited below.  No reference test stores approx-star
+generator tensors, bounds, crossing sets or verdicts at non-toy size, so parity
+of the composed pipeline beyond those fixtures is unpinned.
+
+All arithmetic is FP64 NumPy in the reference's operation order where the
+order is visible in its source.  Arrays use MATLAB index semantics: image
+tensors are ``[H, W, C, P+1]``; flattening is column-major (h fastest).
+
+Bounds mode: the estimated (LP-free) ranges of Star.estimateRanges drive the
+ReLU step, i.e. PosLin.reach_relaxed_star_static with relaxFactor = 1
+(code/nnv/engine/nn/funcs/PosLin.m:1588-1646), which is also
+PosLin.reach_star_approx2 (:747-857) with its two LP calls replaced by the
+estimates.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import scipy.sparse as sp
+from scipy.optimize import linprog
+
+# --------------------------------------------------------------------------
+# set types
+
+
+@dataclass
+class ImageStar:
+    """code/nnv/engine/set/ImageStar.m:47-94 (fields) — V[H,W,C,P+1], C[m,P],
+    d[m], pred_lb/pred_ub[P].  A vector Star (Star.m:13-24) is the same object
+    with shape (N,1,1); ImageStar.toStar / Star.toImageStar (ImageStar.m:569-592,
+    Star.m:1398-1418) are reshapes."""
+    V: np.ndarray
+    C: object          # scipy.sparse.csr_matrix [m, P]
+    d: np.ndarray
+    pl: np.ndarray
+    pu: np.ndarray
+    trace: list = field(default_factory=list)   # one dict per ReLU layer
+
+    @property
+    def shape(self):
+        return self.V.shape[:3]
+
+    @property
+    def P(self):
+        return self.V.shape[3] - 1
+
+    def mat(self):
+        """N x (P+1) matrix view (column-major flatten of each slice)."""
+        h, w, c, p1 = self.V.shape
+        return self.V.reshape(h * w * c, p1, order="F")
+
+
+def star_from_bounds(lb, ub):
+    """ImageStar(lb_im, ub_im): ImageStar.m:302-343 -> Star(lb,ub) Star.m:220-237
+    -> Box Box.m:16-58 (centre (lb+ub)/2, generators diag((ub-lb)/2) with all-zero
+    columns removed) -> Zono.toStar Zono.m:301-309 (pred in [-1,1]); the Star
+    ctor then installs C = zeros(1,P), d = 0."""
+    lb = np.asarray(lb, dtype=np.float64)
+    ub = np.asarray(ub, dtype=np.float64)
+    if lb.ndim == 1:
+        lb = lb.reshape(-1, 1, 1)
+        ub = ub.reshape(-1, 1, 1)
+    if lb.ndim == 2:
+        lb = lb[:, :, None]
+        ub = ub[:, :, None]
+    h, w, c = lb.shape
+    n = h * w * c
+    lbv = lb.reshape(n, order="F")
+    ubv = ub.reshape(n, order="F")
+    center = 0.5 * (lbv + ubv)
+    vec = 0.5 * (ubv - lbv)
+    nz = np.nonzero(vec != 0)[0]
+    if n == 1:          # numel(gens) > 1 guard in Box.m:41
+        nz = np.arange(1)
+    P = len(nz)
+    M = np.zeros((n, P + 1), order="F")
+    M[:, 0] = center
+    M[nz, np.arange(1, P + 1)] = vec[nz]
+    V = M.reshape(h, w, c, P + 1, order="F")
+    return ImageStar(V, sp.csr_matrix((1, P)), np.zeros(1), -np.ones(P), np.ones(P))
+
+
+def star_from_query(q):
+    """Build the input set of a workload query (see nnv_b200/configs.py)."""
+    if "lb" in q:
+        return star_from_bounds(q["lb"], q["ub"])
+    V = np.asfortranarray(np.asarray(q["V"], dtype=np.float64))
+    if V.ndim == 2:
+        V = V.reshape(V.shape[0], 1, 1, V.shape[1], order="F")
+    return ImageStar(V, sp.csr_matrix(np.atleast_2d(q["C"])), np.asarray(q["d"], float).ravel(),
+                     np.asarray(q["pl"], float).ravel(), np.asarray(q["pu"], float).ravel())
+
+
+# --------------------------------------------------------------------------
+# affine layers
+
+
+def zero_pad(x, pad):
+    """Conv2DLayer.get_zero_padding_input, Conv2DLayer.m:1064-1108."""
+    t, b, l, r = pad
+    width = [(t, b), (l, r)] + [(0, 0)] * (x.ndim - 2)
+    return np.pad(x, width)
+
+
+def conv_out_size(hp, k, dil, stride):
+    """Conv2DLayer.get_size_featureMap, Conv2DLayer.m:1227-1228 (hp = padded size)."""
+    return (hp - (k - 1) * dil - 1) // stride + 1
+
+
+def conv2d_slices(X, W, pad, stride, dilation, chunk=32):
+    """Cross-correlation of every slice X[:,:,:,j] with W[kh,kw,Cin,Cout]; the
+    arithmetic of Conv2DLayer.compute_featureMap (Conv2DLayer.m:1111-1204)
+    extended over channels and filters as dlconv does at :591-592.  No bias."""
+    kh, kw, cin, cout = W.shape
+    assert X.shape[2] == cin
+    Xp = zero_pad(X, pad)
+    sh, sw = stride
+    dh, dw = dilation
+    ho = conv_out_size(Xp.shape[0], kh, dh, sh)
+    wo = conv_out_size(Xp.shape[1], kw, dw, sw)
+    ncol = X.shape[3]
+    out = np.zeros((ho, wo, cout, ncol), order="F")
+    for c0 in range(0, ncol, chunk):
+        c1 = min(ncol, c0 + chunk)
+        cols = np.empty((ho, wo, c1 - c0, kh, kw, cin))
+        for i in range(kh):
+            for j in range(kw):
+                patch = Xp[i * dh: i * dh + (ho - 1) * sh + 1: sh,
+                           j * dw: j * dw + (wo - 1) * sw + 1: sw, :, c0:c1]
+                cols[:, :, :, i, j, :] = patch.transpose(0, 1, 3, 2)
+        A = cols.reshape(ho * wo * (c1 - c0), kh * kw * cin)
+        Wc = W.reshape(kh * kw * cin, cout)      # rows (kh, kw, ci), ci fastest, like A's columns
+        Y = A @ Wc
+        out[:, :, :, c0:c1] = Y.reshape(ho, wo, c1 - c0, cout).transpose(0, 1, 3, 2)
+    return out
+
+
+def conv2d_reach(S, L):
+    """Conv2DLayer.reach_star_single_input, Conv2DLayer.m:559-601,780: bias on
+    slice 0 only; C, d, predicate bounds unchanged."""
+    Y = conv2d_slices(S.V, L["W"], L["pad"], L["stride"], L["dilation"])
+    Y[:, :, :, 0] += np.asarray(L["b"]).reshape(1, 1, -1)
+    return ImageStar(np.asfortranarray(Y), S.C, S.d, S.pl, S.pu, S.trace)
+
+
+def fc_reach(S, L):
+    """FullyConnectedLayer.reach_star_single_input, FullyConnectedLayer.m:295-317
+    (ImageStar branch) / Star.affineMap Star.m:313-343: V' = W*reshape(V,N,P+1),
+    bias added to column 1.  Result is a 1x1xOut image."""
+    M = L["W"] @ S.mat()
+    M[:, 0] += L["b"]
+    out = M.shape[0]
+    return ImageStar(np.asfortranarray(M.reshape(1, 1, out, -1, order="F")), S.C, S.d, S.pl, S.pu, S.trace)
+
+
+def bn_reach(S, L):
+    """BatchNormalizationLayer.reach_star_single_input ImageStar branch,
+    BatchNormalizationLayer.m:305-328: four per-channel passes —
+    c -= mean; (c,G) = ((c,G).*1)/sqrt(var+eps); (c,G) .*= scale; c += offset."""
+    V = S.V.copy(order="F")
+    h, w, c, _ = V.shape
+    if len(L["mean"]) != c:
+        # BatchNormalizationLayer.m:289-302: 1x1xN set with N parameters
+        assert h == 1 and w == 1
+    mean = np.asarray(L["mean"]).reshape(1, 1, -1)
+    V[:, :, :, 0] = V[:, :, :, 0] - mean
+    den = np.sqrt(np.asarray(L["var"]) + L["eps"]).reshape(1, 1, -1, 1)
+    V = (V * 1.0) / den
+    V = V * np.asarray(L["scale"]).reshape(1, 1, -1, 1)
+    V[:, :, :, 0] = V[:, :, :, 0] + np.asarray(L["offset"]).reshape(1, 1, -1)
+    return ImageStar(np.asfortranarray(V), S.C, S.d, S.pl, S.pu, S.trace)
+
+
+def avgpool_slices(X, pool, stride, pad):
+    """AveragePooling2DLayer.compute_averageMap, AveragePooling2DLayer.m:316-393:
+    zero-pad, sum the window row by row, divide by ph*pw (padding counted)."""
+    ph, pw = pool
+    sh, sw = stride
+    Xp = zero_pad(X, pad)
+    ho = (Xp.shape[0] - ph) // sh + 1
+    wo = (Xp.shape[1] - pw) // sw + 1
+    acc = np.zeros((ho, wo) + X.shape[2:], order="F")
+    for i in range(ph):
+        for j in range(pw):
+            acc = acc + Xp[i: i + (ho - 1) * sh + 1: sh, j: j + (wo - 1) * sw + 1: sw]
+    return acc / (ph * pw)
+
+
+def avgpool_reach(S, L):
+    """AveragePooling2DLayer.reach_star_single_input, AveragePooling2DLayer.m:424-438:
+    pool every slice of V (centre and generators)."""
+    Y = avgpool_slices(S.V, L["pool"], L["stride"], L["pad"])
+    return ImageStar(np.asfortranarray(Y), S.C, S.d, S.pl, S.pu, S.trace)
+
+
+# --------------------------------------------------------------------------
+# ReLU approx step
+
+
+def estimate_ranges(M, pl, pu):
+    """Star.estimateRanges, Star.m:1078-1106: four products formed separately,
+    lb = c + pos*pl + neg*pu, ub = c + pos*pu + neg*pl (in that order)."""
+    G = M[:, 1:]
+    pos = np.maximum(G, 0.0)
+    neg = np.minimum(G, 0.0)
+    if pl.size == 0:
+        pl = -np.ones(G.shape[1])
+        pu = np.ones(G.shape[1])
+    xmin1 = pos @ pl
+    xmax1 = pos @ pu
+    xmin2 = neg @ pu
+    xmax2 = neg @ pl
+    lb = M[:, 0] + xmin1 + xmin2
+    ub = M[:, 0] + xmax1 + xmax2
+    return lb, ub
+
+
+def relu_reach(S, keep_constraints=True):
+    """ReluLayer.reach_star_single_input (ReluLayer.m:103-118) -> PosLin.reach with
+    the LP-free construction: PosLin.m:1588-1646 at relaxFactor = 1, built from
+    Star.estimateRanges (Star.m:1078-1106), Star.resetRow (Star.m:1442-1461) and
+    PosLin.multipleStepReachStarApprox_at_one (PosLin.m:685-742)."""
+    h, w, c, p1 = S.V.shape
+    N = h * w * c
+    P = p1 - 1
+    M = S.mat()
+    lb, ub = estimate_ranges(M, S.pl, S.pu)
+    dead = np.nonzero(ub <= 0)[0]                      # map1
+    cross = np.nonzero((lb < 0) & (ub > 0))[0]         # map2 (ascending linear index)
+    k = len(cross)
+    lbc = lb[cross]
+    ubc = ub[cross]
+    In = M.copy(order="F")
+    In[dead, :] = 0.0                                  # resetRow
+    c_idx = In[cross, 0].copy()                        # pre-zeroing rows of the crossing neurons
+    G_idx = In[cross, 1:].copy()
+    V1 = In
+    V1[cross, :] = 0.0
+    newM = np.zeros((N, P + 1 + k), order="F")
+    newM[:, :P + 1] = V1
+    newM[cross, P + 1 + np.arange(k)] = 1.0
+    a = ubc / (ubc - lbc)
+    b = a * lbc
+    new_pl = np.concatenate([S.pl, np.zeros(k)])
+    new_pu = np.concatenate([S.pu, ubc])
+    if keep_constraints:
+        Ik = sp.identity(k, format="csr")
+        Gs = sp.csr_matrix(G_idx)
+        aG = sp.csr_matrix(G_idx * (-a)[:, None])
+        m0 = S.C.shape[0]
+        C0 = sp.hstack([S.C, sp.csr_matrix((m0, k))], format="csr")
+        C1 = sp.hstack([sp.csr_matrix((k, P)), -Ik], format="csr")
+        C2 = sp.hstack([Gs, -Ik], format="csr")
+        C3 = sp.hstack([aG, Ik], format="csr")
+        newC = sp.vstack([C0, C1, C2, C3], format="csr")
+        newd = np.concatenate([S.d, np.zeros(k), -c_idx, a * c_idx - b])
+    else:
+        newC, newd = S.C, S.d
+    trace = S.trace + [{"N": N, "lb": lb, "ub": ub, "dead": dead, "cross": cross,
+                        "P_in": P, "P_out": P + k}]
+    return ImageStar(newM.reshape(h, w, c, P + 1 + k, order="F"), newC, newd, new_pl, new_pu, trace)
+
+
+# --------------------------------------------------------------------------
+# network driver and verdict
+
+
+def reach(layers, S, keep_constraints=True):
+    """NN.reach_noConns layer loop, NN.m:1529-1551."""
+    for L in layers:
+        t = L["type"]
+        if t == "conv2d":
+            S = conv2d_reach(S, L)
+        elif t == "fc":
+            S = fc_reach(S, L)
+        elif t == "bn":
+            S = bn_reach(S, L)
+        elif t == "avgpool":
+            S = avgpool_reach(S, L)
+        elif t == "relu":
+            S = relu_reach(S, keep_constraints)
+        else:
+            raise ValueError(t)
+    return S
+
+
+def robustness_set(n_out, target, class_type="max"):
+    """NN.robustness_set, NN.m:1334-1368 (target 0-based here): n_out-1 halfspaces
+    G x <= 0; 'max': x_target - x_i <= 0 ... encoded as row e_target - e_i;
+    'min': row e_i - e_target."""
+    G = np.eye(n_out)
+    G = np.delete(G, target, axis=0)
+    if class_type == "max":
+        G = -G
+        G[:, target] = 1.0
+    elif class_type == "min":
+        G[:, target] = -1.0
+    else:
+        raise ValueError(class_type)
+    return G, np.zeros(G.shape[0])
+
+
+def is_empty_set(C, d, pl, pu):
+    """Star.isEmptySet, Star.m:1216-1232 -> lpsolver(0, C, d, [], [], pl, pu)
+    (lpsolver.m:99-128; box-only closed form :34-49).  HiGHS stands in for
+    linprog/glpk."""
+    C = sp.csr_matrix(C)
+    d = np.asarray(d, float).ravel()
+    P = C.shape[1]
+    if C.nnz == 0 and pl.size and np.all(np.isfinite(pl)) and np.all(np.isfinite(pu)) and np.all(d >= 0):
+        return False                                   # box-only fast path: feasible
+    bounds = list(zip(pl, pu)) if pl.size else [(None, None)] * P
+    res = linprog(np.zeros(P), A_ub=C, b_ub=d, bounds=bounds, method="highs")
+    if res.status == 0:
+        return False
+    if res.status == 2:
+        return True
+    raise RuntimeError("LP solver status %d: %s" % (res.status, res.message))
+
+
+def intersect_halfspace_system(S, H, g):
+    """Star.intersectHalfSpace, Star.m:555-589: C1 = H*V(:,2:end),
+    d1 = g - H*V(:,1); returns the stacked system ([C; C1], [d; d1])."""
+    M = S.mat()
+    H = np.atleast_2d(H)
+    C1 = H @ M[:, 1:]
+    d1 = np.asarray(g, float).ravel() - H @ M[:, 0]
+    newC = sp.vstack([S.C, sp.csr_matrix(C1)], format="csr")
+    newd = np.concatenate([S.d, d1])
+    return newC, newd
+
+
+def verify_specification(S, G, g):
+    """verify_specification.m:36-79 with NN.checkRobust (NN.m:617-648): OR over
+    halfspaces; 1 iff every intersection is empty, 2 at the first non-empty."""
+    for i in range(G.shape[0]):
+        C, d = intersect_halfspace_system(S, G[i:i + 1], g[i:i + 1])
+        if not is_empty_set(C, d, S.pl, S.pu):
+            return 2
+    return 1
+
+
+def verify_robustness(layers, q, keep_trace=False):
+    """NN.verify_robustness, NN.m:651-667, for one workload query."""
+    S = reach(layers, star_from_query(q))
+    n_out = S.mat().shape[0]
+    G, g = robustness_set(n_out, q["target"], q.get("spec", "max"))
+    v = verify_specification(S, G, g)
+    return (v, S) if keep_trace else v
+
+
+def output_ranges(S):
+    """Star.estimateRanges of the final set."""
+    return estimate_ranges(S.mat(), S.pl, S.pu)
