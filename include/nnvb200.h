@@ -114,6 +114,24 @@ void* nnvb_stream(nnvb_ctx* ctx);
 /* Number of kernels this library has launched on the context so far. */
 int64_t nnvb_launch_count(nnvb_ctx* ctx);
 
+/* Device time per kernel family, the counterpart of the reference's per-layer
+ * tic/toc record obj.reachTime (NN.m:1542-1545).  While enabled, every launch
+ * group is bracketed by CUDA events on the context stream.  nnvb_profile_read
+ * returns, since the last enable: accumulated milliseconds, kernels launched,
+ * and the algorithmic work of those launches — floating-point operations for the
+ * contractions (2*Ho*Wo*Cout*kh*kw*Cin*columns, 2*Out*In*columns), bytes for
+ * the bandwidth-bound families (each tensor read or written once). */
+#define NNVB_PROF_CONV 0      /* Conv2D implicit GEMM (+ fused BatchNormalization) */
+#define NNVB_PROF_FC 1        /* FullyConnected GEMM */
+#define NNVB_PROF_BN 2        /* stand-alone BatchNormalization */
+#define NNVB_PROF_AVGPOOL 3   /* AveragePooling2D */
+#define NNVB_PROF_RANGES 4    /* Star.estimateRanges + classification scans */
+#define NNVB_PROF_RELAX 5     /* row clearing, column append, list rebuild */
+#define NNVB_PROF_VERIFY 6    /* halfspace rows, box minimum, witness pass */
+#define NNVB_PROF_FAMILIES 7
+int nnvb_profile_enable(nnvb_ctx* ctx, int on);
+int nnvb_profile_read(nnvb_ctx* ctx, int family, double* ms, int64_t* launches, double* work);
+
 /* ---- network ------------------------------------------------------------ */
 
 /* Copy the layer parameters to the device once and pre-arrange them for the
@@ -188,7 +206,16 @@ int nnvb_batch_get_layer_ranges(nnvb_batch* b, int q, int relu_layer, double* lb
  * intersection is empty (robust / safe), 2 = some intersection is non-empty
  * (unknown for an over-approximation).  NNVB_UNDECIDED marks a halfspace the
  * device-side tests could not settle; the caller finishes it with the
- * feasibility LP of Star.isEmptySet (Star.m:1216-1232). */
+ * feasibility LP of Star.isEmptySet (Star.m:1216-1232).
+ *
+ * Two device-side tests run per halfspace row G_h x <= g_h:
+ *   - the minimum of G_h x - g_h over the output set's predicate box; a
+ *     positive minimum proves the intersection empty (NNVB_VERDICT_EMPTY);
+ *   - a witness: a point of the output set (input predicates at a corner of
+ *     their box, each ReLU predicate at the lower envelope max(0,x) or on the
+ *     chord of its triangle, whichever lowers the row) evaluated by a forward
+ *     pass; a point inside the halfspace proves it non-empty
+ *     (NNVB_VERDICT_NONEMPTY).  The witness needs opts.keep_layer_bounds. */
 #define NNVB_VERDICT_EMPTY 1
 #define NNVB_VERDICT_NONEMPTY 2
 #define NNVB_UNDECIDED (-1)
@@ -196,15 +223,16 @@ int nnvb_batch_get_layer_ranges(nnvb_batch* b, int q, int relu_layer, double* lb
 /* For query q and halfspaces G x <= g (G is [nh x N_out] column-major): the
  * minimum of G x - g over the output set's predicate box, one value per
  * halfspace.  A positive value proves Star.intersectHalfSpace (Star.m:555-589)
- * empty without an LP.  status[h] receives NNVB_VERDICT_EMPTY or NNVB_UNDECIDED. */
+ * empty without an LP.  status[h] receives NNVB_VERDICT_EMPTY,
+ * NNVB_VERDICT_NONEMPTY or NNVB_UNDECIDED. */
 int nnvb_batch_halfspace_margins(nnvb_batch* b, int q, const double* G, const double* g,
                                  int nh, double* margin_lo, int* status);
 
 /* Robustness form of the same test for the whole batch: for query q the
  * halfspaces are NN.robustness_set(target[q], kind) (NN.m:1334-1368), kind 0 =
  * 'max', 1 = 'min'.  status is [n_queries x (N_out-1)] row-major per query;
- * margin_lo likewise (may be NULL).  verdict[q] = 1 when all are empty, else
- * NNVB_UNDECIDED. */
+ * margin_lo likewise (may be NULL).  verdict[q] = 1 when all rows are empty, 2
+ * when some row is proven non-empty, else NNVB_UNDECIDED. */
 int nnvb_batch_verify_robust(nnvb_batch* b, const int32_t* target, int kind,
                              int* verdict, int* status, double* margin_lo);
 

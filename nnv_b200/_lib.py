@@ -22,6 +22,8 @@ NNVB_E_UNSUPPORTED = 5
 
 LAYER_CONV2D, LAYER_FC, LAYER_BN, LAYER_AVGPOOL2D, LAYER_RELU = 1, 2, 3, 4, 5
 
+PROF_FAMILIES = ("conv", "fc", "bn", "avgpool", "ranges", "relax", "verify")
+
 VERDICT_EMPTY = 1
 VERDICT_NONEMPTY = 2
 UNDECIDED = -1
@@ -72,6 +74,8 @@ SIGNATURES = {
     "nnvb_abi_version": (C.c_int, []),
     "nnvb_stream": (C.c_void_p, [C.c_void_p]),
     "nnvb_launch_count": (C.c_int64, [C.c_void_p]),
+    "nnvb_profile_enable": (C.c_int, [C.c_void_p, C.c_int]),
+    "nnvb_profile_read": (C.c_int, [C.c_void_p, C.c_int, c_double_p, c_int64_p, c_double_p]),
     "nnvb_net_create": (C.c_int, [C.c_void_p, C.POINTER(LayerDesc), C.c_int, C.c_int64, C.c_int64, C.c_int64,
                                   C.POINTER(C.c_void_p)]),
     "nnvb_net_destroy": (C.c_int, [C.c_void_p]),

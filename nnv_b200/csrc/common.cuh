@@ -151,13 +151,25 @@ int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, in
                        const ReluRecord& rec, int32_t* col_q, double* pl, double* pu, int64_t* col_pos,
                        int64_t* new_qcol_off, int32_t* new_qcol_idx, int64_t* launches);
 
-// Halfspace rows: r[h][col] = sum_o G[h][o] * V[o][col], then the box minimum.
-// Block b handles query q_base + b; G, g and margin are indexed by b.
-int launch_halfspace_margins(cudaStream_t st, int nq, int q_base, int64_t Nout, int64_t ld, const double* V,
-                             const int64_t* qcol_off, const int32_t* qcol_idx, const double* pl,
-                             const double* pu, const double* G /*[nq][nh][Nout]*/,
-                             const double* g /*[nq][nh]*/, int nh, double* margin /*[nq][nh]*/,
+// Halfspace rows against output sets; see relu_star.cu.  Pair p tests row G[p] (length Nout)
+// with offset g[p] on query pair_q[p]; margin[p] = box minimum of G x - g (nullable);
+// r_out (nullable) receives the predicate coefficients of pair p at r_off[p] + position.
+int launch_halfspace_pairs(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t Nout, int64_t ld,
+                           const double* V, const int64_t* qcol_off, const int32_t* qcol_idx, const double* pl,
+                           const double* pu, const double* G, const double* g, double* margin, double* r_out,
+                           const int64_t* r_off, int64_t* launches);
+// Witness search kernels (one point per pair, X is [ld x n_pairs]).
+int launch_witness_x0_bounds(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t N, int64_t ld,
+                             const double* lbub, const double* r, const int64_t* r_off, double* X,
                              int64_t* launches);
+int launch_witness_x0_star(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t N, int64_t ld, int64_t ld0,
+                           const double* V0, const int64_t* gen0, const double* pl0, const double* pu0,
+                           const double* r, const int64_t* r_off, double* X, int64_t* launches);
+int launch_witness_relu(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t N, int64_t ld, double* X,
+                        const double* lb, const double* ub, const int32_t* rank, const int64_t* P_in,
+                        const double* r, const int64_t* r_off, int64_t* launches);
+int launch_witness_value(cudaStream_t st, int n_pairs, int64_t Nout, int64_t ld, const double* X, const double* G,
+                         const double* g, double* value, double* scale, int64_t* launches);
 
 // Build the dense input set of a bounds-form query batch.
 int launch_build_from_bounds(cudaStream_t st, int nq, int64_t N, int64_t ld, const double* lbub,

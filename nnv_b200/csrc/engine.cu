@@ -92,6 +92,14 @@ struct nnvb_ctx {
     int64_t launches = 0;
     PinnedBuf scratch;      // small host->device traffic of the layer loop
     size_t scratch_off = 0; // bytes of `scratch` handed out since the last stream sync
+    // per-kernel-family device timing (off by default)
+    bool prof_on = false;
+    struct ProfRec { int fam; cudaEvent_t a, b; double work; };
+    std::vector<ProfRec> prof_recs;
+    std::vector<cudaEvent_t> prof_pool;
+    double prof_ms[NNVB_PROF_FAMILIES] = {0};
+    double prof_work[NNVB_PROF_FAMILIES] = {0};
+    int64_t prof_launches[NNVB_PROF_FAMILIES] = {0};
     double* vbuf(int i) const { return reinterpret_cast<double*>(arena + (arena_bytes / 2 / 256 * 256) * i); }
     size_t vbuf_bytes() const { return arena_bytes / 2 / 256 * 256; }
 };
@@ -135,11 +143,11 @@ struct ReluLayerRecord {
     DevBuf idx, q, c, l, u;              // per new column
     DevBuf G, G_off;                     // crossing rows (keep_constraints)
     std::vector<int64_t> h_G_off;
-    DevBuf lb, ub;                       // [nq][N] (keep_layer_bounds)
+    DevBuf lb, ub, rank, P_in_dev;       // [nq][N] bounds and crossing ranks, [nq] P_in (keep_layer_bounds)
     bool has_G = false, has_bounds = false;
     void release() {
         idx.release(); q.release(); c.release(); l.release(); u.release();
-        G.release(); G_off.release(); lb.release(); ub.release();
+        G.release(); G_off.release(); lb.release(); ub.release(); rank.release(); P_in_dev.release();
     }
 };
 
@@ -154,6 +162,7 @@ struct nnvb_batch {
     std::vector<char> is_set;
     std::vector<std::vector<double>> h_pl, h_pu, h_C, h_d;   // star form / constraints
     std::vector<int64_t> m0;
+    std::vector<char> box_implies_C;     // every row of the input constraints holds on the whole predicate box
     std::vector<std::vector<double>> h_V;                    // star form staging per query
     // device inputs
     DevBuf d_in;                         // bounds or V
@@ -166,6 +175,7 @@ struct nnvb_batch {
     DevBuf chunk_beg, chunk_end, q_chunk_off, partial;
     DevBuf lb, ub, state, rank, blk_cross, q_cross, q_dead, q_new_off, gen_off;
     DevBuf tmp;                          // gathers for downloads
+    DevBuf hs_G, hs_g, hs_q, hs_margin, hs_r, hs_roff, hs_val, hs_scale, wit[2];   // halfspace tests
     std::vector<int64_t> h_qcol_off;     // [nq+1]
     int64_t ncols = 0;
     int64_t N = 0, ld = 0;
@@ -179,6 +189,46 @@ struct nnvb_batch {
 };
 
 namespace {
+
+// Scoped device timer for one kernel family: records an event pair on the stream
+// around the launches issued while it lives.  No-op unless profiling is enabled.
+struct ProfScope {
+    nnvb_ctx* ctx;
+    int fam;
+    double work;
+    int64_t l0;
+    cudaEvent_t a = nullptr, b = nullptr;
+    ProfScope(nnvb_ctx* c, int f, double w) : ctx(c), fam(f), work(w), l0(c->launches) {
+        if (!ctx->prof_on) return;
+        auto get = [&]() {
+            cudaEvent_t e = nullptr;
+            if (!ctx->prof_pool.empty()) { e = ctx->prof_pool.back(); ctx->prof_pool.pop_back(); }
+            else cudaEventCreate(&e);
+            return e;
+        };
+        a = get(); b = get();
+        cudaEventRecord(a, ctx->stream);
+    }
+    ~ProfScope() {
+        if (!a) return;
+        cudaEventRecord(b, ctx->stream);
+        ctx->prof_recs.push_back({fam, a, b, work});
+        ctx->prof_launches[fam] += ctx->launches - l0;
+    }
+};
+
+void prof_drain(nnvb_ctx* ctx) {
+    for (auto& r : ctx->prof_recs) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) {
+            ctx->prof_ms[r.fam] += ms;
+            ctx->prof_work[r.fam] += r.work;
+        }
+        ctx->prof_pool.push_back(r.a);
+        ctx->prof_pool.push_back(r.b);
+    }
+    ctx->prof_recs.clear();
+}
 
 template <typename T>
 int upload_vec(nnvb_net* net, const std::vector<T>& v, T** out) {
@@ -199,6 +249,7 @@ int capacity_error(const char* what, size_t need, size_t have) {
 int sync(nnvb_ctx* ctx) {
     NNVB_CUDA(cudaStreamSynchronize(ctx->stream));
     ctx->scratch_off = 0;   // every staged upload has landed
+    if (!ctx->prof_recs.empty()) prof_drain(ctx);
     return NNVB_OK;
 }
 
@@ -309,9 +360,30 @@ int nnvb_destroy(nnvb_ctx* ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     ctx->scratch.release();
+    prof_drain(ctx);
+    for (cudaEvent_t e : ctx->prof_pool) cudaEventDestroy(e);
     if (ctx->arena) cudaFree(ctx->arena);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
+    return NNVB_OK;
+}
+
+int nnvb_profile_enable(nnvb_ctx* ctx, int on) {
+    NNVB_REQUIRE(ctx, "nnvb_profile_enable: NULL context");
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    NNVB_TRY(sync(ctx));
+    ctx->prof_on = on != 0;
+    for (int f = 0; f < NNVB_PROF_FAMILIES; ++f) { ctx->prof_ms[f] = 0; ctx->prof_work[f] = 0; ctx->prof_launches[f] = 0; }
+    return NNVB_OK;
+}
+
+int nnvb_profile_read(nnvb_ctx* ctx, int family, double* ms, int64_t* launches, double* work) {
+    NNVB_REQUIRE(ctx && family >= 0 && family < NNVB_PROF_FAMILIES, "nnvb_profile_read: bad argument");
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    NNVB_TRY(sync(ctx));
+    if (ms) *ms = ctx->prof_ms[family];
+    if (launches) *launches = ctx->prof_launches[family];
+    if (work) *work = ctx->prof_work[family];
     return NNVB_OK;
 }
 
@@ -504,6 +576,7 @@ int nnvb_batch_create(nnvb_net* net, int n_queries, nnvb_batch** out) {
     b->h_C.resize(n_queries); b->h_d.resize(n_queries);
     b->h_V.resize(n_queries);
     b->m0.assign(n_queries, 0);
+    b->box_implies_C.assign(n_queries, 1);
     *out = b;
     return NNVB_OK;
 }
@@ -517,7 +590,8 @@ int nnvb_batch_destroy(nnvb_batch* b) {
     DevBuf* bufs[] = {&b->d_in, &b->d_in_meta, &b->col_q, &b->pl, &b->pu, &b->col_pos, &b->qcol_off[0],
                       &b->qcol_off[1], &b->qcol_idx[0], &b->qcol_idx[1], &b->chunk_beg, &b->chunk_end,
                       &b->q_chunk_off, &b->partial, &b->lb, &b->ub, &b->state, &b->rank, &b->blk_cross,
-                      &b->q_cross, &b->q_dead, &b->q_new_off, &b->gen_off, &b->tmp};
+                      &b->q_cross, &b->q_dead, &b->q_new_off, &b->gen_off, &b->tmp, &b->hs_G, &b->hs_g, &b->hs_q,
+                      &b->hs_margin, &b->hs_r, &b->hs_roff, &b->hs_val, &b->hs_scale, &b->wit[0], &b->wit[1]};
     for (DevBuf* d : bufs) d->release();
     for (auto& r : b->relu) r->release();
     delete b;
@@ -573,6 +647,18 @@ int nnvb_batch_set_star(nnvb_batch* b, int q, int64_t P, const double* V, const 
     }
     b->h_C[q].assign(Cmat, Cmat + size_t(m) * P);
     b->h_d[q].assign(d, d + m);
+    // a witness at a corner of the predicate box is a point of the set only if the
+    // set's own constraints hold on the whole box
+    bool implied = true;
+    for (int64_t r = 0; r < m && implied; ++r) {
+        double mx = 0.0;
+        for (int64_t j = 0; j < P; ++j) {
+            const double c = Cmat[size_t(j) * m + r];
+            mx += std::max(c * pl[j], c * pu[j]);
+        }
+        implied = mx <= d[r] + 1e-12 * (1.0 + std::fabs(d[r]));
+    }
+    b->box_implies_C[q] = implied ? 1 : 0;
     b->P0[q] = P;
     b->m0[q] = m;
     b->is_set[q] = 1;
@@ -762,7 +848,8 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec) {
     NNVB_TRY(ubbuf.ensure(sizeof(double) * nq * N, st));
     rec->has_bounds = b->opts.keep_layer_bounds != 0;
     NNVB_TRY(b->state.ensure(size_t(nq) * N, st));
-    NNVB_TRY(b->rank.ensure(sizeof(int32_t) * nq * N, st));
+    DevBuf& rankbuf = b->opts.keep_layer_bounds ? rec->rank : b->rank;
+    NNVB_TRY(rankbuf.ensure(sizeof(int32_t) * nq * N, st));
     NNVB_TRY(b->blk_cross.ensure(sizeof(int32_t) * nq * nblk, st));
     NNVB_TRY(b->q_cross.ensure(sizeof(int64_t) * nq, st));
     NNVB_TRY(b->q_dead.ensure(sizeof(int64_t) * nq, st));
@@ -778,13 +865,18 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec) {
     w.q_chunk_off = b->q_chunk_off.as<int32_t>();
     w.partial = b->partial.as<double>();
     w.lb = lbbuf.as<double>(); w.ub = ubbuf.as<double>();
-    w.state = b->state.as<uint8_t>(); w.rank = b->rank.as<int32_t>();
+    w.state = b->state.as<uint8_t>(); w.rank = rankbuf.as<int32_t>();
     w.blk_cross = b->blk_cross.as<int32_t>();
     w.q_cross = b->q_cross.as<int64_t>(); w.q_dead = b->q_dead.as<int64_t>();
     w.q_new_off = b->q_new_off.as<int64_t>();
 
-    NNVB_TRY(launch_estimate_ranges(st, w, &ctx->launches));
-    NNVB_TRY(launch_classify_scan(st, w, &ctx->launches));
+    {
+        // Star.estimateRanges: V read once, predicate bounds, lb/ub written
+        ProfScope ps(ctx, NNVB_PROF_RANGES,
+                     8.0 * double(N) * double(b->ncols) + 16.0 * double(b->ncols - nq) + 16.0 * double(N) * nq);
+        NNVB_TRY(launch_estimate_ranges(st, w, &ctx->launches));
+        NNVB_TRY(launch_classify_scan(st, w, &ctx->launches));
+    }
 
     // the crossing counts decide every size from here on: one host round trip per ReLU layer
     rec->new_off.resize(nq + 1);
@@ -799,6 +891,10 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec) {
     for (int q = 0; q < nq; ++q) rec->n_dead += dead[q];
     rec->P_in.resize(nq);
     for (int q = 0; q < nq; ++q) rec->P_in[q] = b->h_qcol_off[q + 1] - b->h_qcol_off[q];
+    if (b->opts.keep_layer_bounds) {
+        NNVB_TRY(rec->P_in_dev.ensure(sizeof(int64_t) * nq, st));
+        NNVB_TRY(h2d_small(ctx, rec->P_in_dev.p, rec->P_in.data(), sizeof(int64_t) * nq));
+    }
 
     const int64_t ncols_old = b->ncols;
     NNVB_REQUIRE(ncols_old + K < (int64_t(1) << 31), "batch has too many generator columns");
@@ -833,14 +929,22 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec) {
         r.G_off = rec->G_off.as<int64_t>();
         rec->has_G = true;
     }
-    if (K > 0) NNVB_TRY(launch_rank_cross(st, w, r, &ctx->launches));
-    if (K > 0 || rec->n_dead > 0)
-        NNVB_TRY(launch_relu_zero_rows(st, w, ncols_old, b->col_q.as<int32_t>(), r, b->col_pos.as<int64_t>(),
-                                       &ctx->launches));
+    // relaxation: lb/ub read, dead and crossing rows cleared in every column of their query,
+    // one-hot columns and their predicate bounds written
     const int nxt = 1 - b->list_cur;
-    NNVB_TRY(launch_relu_append(st, w, ncols_old, K, r, b->col_q.as<int32_t>(), b->pl.as<double>(),
-                                b->pu.as<double>(), b->col_pos.as<int64_t>(), b->qcol_off[nxt].as<int64_t>(),
-                                b->qcol_idx[nxt].as<int32_t>(), &ctx->launches));
+    double relax_bytes = 16.0 * double(N) * nq + 8.0 * double(N) * double(K) + 16.0 * double(K);
+    for (int q = 0; q < nq; ++q)
+        relax_bytes += 8.0 * double(dead[q] + rec->new_off[q + 1] - rec->new_off[q]) * double(rec->P_in[q] + 1);
+    {
+        ProfScope ps(ctx, NNVB_PROF_RELAX, relax_bytes);
+        if (K > 0) NNVB_TRY(launch_rank_cross(st, w, r, &ctx->launches));
+        if (K > 0 || rec->n_dead > 0)
+            NNVB_TRY(launch_relu_zero_rows(st, w, ncols_old, b->col_q.as<int32_t>(), r, b->col_pos.as<int64_t>(),
+                                           &ctx->launches));
+        NNVB_TRY(launch_relu_append(st, w, ncols_old, K, r, b->col_q.as<int32_t>(), b->pl.as<double>(),
+                                    b->pu.as<double>(), b->col_pos.as<int64_t>(), b->qcol_off[nxt].as<int64_t>(),
+                                    b->qcol_idx[nxt].as<int32_t>(), &ctx->launches));
+    }
     b->list_cur = nxt;
     for (int q = 0; q <= nq; ++q) b->h_qcol_off[q] += rec->new_off[q];
     b->ncols = ncols_old + K;
@@ -867,12 +971,15 @@ int run_layers(nnvb_batch* b) {
                     const Layer& B = net->layers[L.fused_bn];
                     bn = ChanAffine{B.bn_mean, B.bn_den, B.bn_scale, B.bn_offset};
                 }
+                ProfScope ps(ctx, NNVB_PROF_CONV, 2.0 * L.cg.Ho * L.cg.Wo * L.cg.Cout * L.cg.kh * L.cg.kw * L.cg.Cin * double(b->ncols));
                 NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, b->V, b->ld, out, ld_out, b->ncols, b->nq,
                                          &ctx->launches));
             } else if (L.type == NNVB_LAYER_FC) {
+                ProfScope ps(ctx, NNVB_PROF_FC, 2.0 * double(L.Co) * double(L.H * L.W * L.C) * double(b->ncols));
                 NNVB_TRY(launch_fc_f64(st, int(L.H * L.W * L.C), int(L.Co), L.fc_wt, L.fc_ldw, L.bias, b->V, b->ld,
                                        out, ld_out, b->ncols, b->nq, &ctx->launches));
             } else {
+                ProfScope ps(ctx, NNVB_PROF_AVGPOOL, 8.0 * double(b->N + Nout) * double(b->ncols));
                 NNVB_TRY(launch_avgpool_f64(st, L.pg, b->V, b->ld, out, ld_out, b->ncols, &ctx->launches));
             }
             b->V = out;
@@ -882,6 +989,7 @@ int run_layers(nnvb_batch* b) {
             if (!L.fused_into_prev) {
                 NNVB_TRY(make_writable(b, 0));
                 ChanAffine bn{L.bn_mean, L.bn_den, L.bn_scale, L.bn_offset};
+                ProfScope ps(ctx, NNVB_PROF_BN, 16.0 * double(b->N) * double(b->ncols));
                 NNVB_TRY(launch_bn_f64(st, bn, L.H * L.W, b->N, b->V, b->ld, b->ncols, b->nq, &ctx->launches));
             }
         } else if (L.type == NNVB_LAYER_RELU) {
@@ -943,6 +1051,149 @@ int output_ranges(nnvb_batch* b) {
     NNVB_TRY(launch_estimate_ranges(st, w, &ctx->launches));
     NNVB_TRY(launch_classify_scan(st, w, &ctx->launches));
     b->have_out_ranges = true;
+    return NNVB_OK;
+}
+
+// Run the affine layers and the relaxed ReLU over witness points X [ld x n] (one per pair).
+int witness_forward(nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, int64_t* ldx, const double* d_r,
+                    const int64_t* d_roff) {
+    nnvb_net* net = b->net;
+    nnvb_ctx* ctx = net->ctx;
+    cudaStream_t st = ctx->stream;
+    double* cur = b->wit[0].as<double>();
+    double* oth = b->wit[1].as<double>();
+    int64_t N = b->N0, ld = b->ld0;
+    int relu_i = 0;
+    for (size_t li = 0; li < net->layers.size(); ++li) {
+        const Layer& L = net->layers[li];
+        const int64_t Nout = L.Ho * L.Wo * L.Co;
+        const int64_t ld_out = lead_dim(Nout);
+        if (L.type == NNVB_LAYER_CONV2D) {
+            ChanAffine bn{nullptr, nullptr, nullptr, nullptr};
+            if (L.fused_bn >= 0) {
+                const Layer& B = net->layers[L.fused_bn];
+                bn = ChanAffine{B.bn_mean, B.bn_den, B.bn_scale, B.bn_offset};
+            }
+            NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, cur, ld, oth, ld_out, n, n, &ctx->launches));
+            std::swap(cur, oth); N = Nout; ld = ld_out;
+        } else if (L.type == NNVB_LAYER_FC) {
+            NNVB_TRY(launch_fc_f64(st, int(L.H * L.W * L.C), int(L.Co), L.fc_wt, L.fc_ldw, L.bias, cur, ld, oth, ld_out, n,
+                                   n, &ctx->launches));
+            std::swap(cur, oth); N = Nout; ld = ld_out;
+        } else if (L.type == NNVB_LAYER_AVGPOOL2D) {
+            NNVB_TRY(launch_avgpool_f64(st, L.pg, cur, ld, oth, ld_out, n, &ctx->launches));
+            std::swap(cur, oth); N = Nout; ld = ld_out;
+        } else if (L.type == NNVB_LAYER_BN) {
+            if (!L.fused_into_prev) {
+                ChanAffine bn{L.bn_mean, L.bn_den, L.bn_scale, L.bn_offset};
+                NNVB_TRY(launch_bn_f64(st, bn, L.H * L.W, N, cur, ld, n, n, &ctx->launches));
+            }
+        } else if (L.type == NNVB_LAYER_RELU) {
+            ReluLayerRecord& r = *b->relu[relu_i++];
+            NNVB_TRY(launch_witness_relu(st, n, d_pair_q, N, ld, cur, r.lb.as<double>(), r.ub.as<double>(),
+                                         r.rank.as<int32_t>(), r.P_in_dev.as<int64_t>(), d_r, d_roff, &ctx->launches));
+        }
+    }
+    *X = cur;
+    *ldx = ld;
+    return NNVB_OK;
+}
+
+// Test halfspace rows against the reached sets: pair p = (query pair_q[p], row G[p], offset g[p]).
+// status: EMPTY when the box minimum of the row is positive; NONEMPTY when the greedy witness
+// point lies inside the halfspace (needs the layer bounds kept during reach); else UNDECIDED.
+int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vector<double>& G,
+               const std::vector<double>& g, std::vector<double>& margin, std::vector<int>& status) {
+    nnvb_ctx* ctx = b->net->ctx;
+    cudaStream_t st = ctx->stream;
+    const int n = (int)pair_q.size();
+    const int64_t Nout = b->N;
+    margin.assign(n, 0.0);
+    status.assign(n, NNVB_UNDECIDED);
+    if (n == 0) return NNVB_OK;
+    ProfScope ps(ctx, NNVB_PROF_VERIFY, 0.0);
+    NNVB_TRY(b->hs_G.ensure(sizeof(double) * n * Nout, st));
+    NNVB_TRY(b->hs_g.ensure(sizeof(double) * n, st));
+    NNVB_TRY(b->hs_q.ensure(sizeof(int32_t) * n, st));
+    NNVB_TRY(b->hs_margin.ensure(sizeof(double) * n, st));
+    NNVB_CUDA(cudaMemcpyAsync(b->hs_G.p, G.data(), sizeof(double) * n * Nout, cudaMemcpyHostToDevice, st));
+    NNVB_CUDA(cudaMemcpyAsync(b->hs_g.p, g.data(), sizeof(double) * n, cudaMemcpyHostToDevice, st));
+    NNVB_CUDA(cudaMemcpyAsync(b->hs_q.p, pair_q.data(), sizeof(int32_t) * n, cudaMemcpyHostToDevice, st));
+    const int64_t* qoff = b->qcol_off[b->list_cur].as<int64_t>();
+    const int32_t* qidx = b->qcol_idx[b->list_cur].as<int32_t>();
+    NNVB_TRY(launch_halfspace_pairs(st, n, b->hs_q.as<int32_t>(), Nout, b->ld, b->V, qoff, qidx, b->pl.as<double>(),
+                                    b->pu.as<double>(), b->hs_G.as<double>(), b->hs_g.as<double>(),
+                                    b->hs_margin.as<double>(), nullptr, nullptr, &ctx->launches));
+    NNVB_CUDA(cudaMemcpyAsync(margin.data(), b->hs_margin.p, sizeof(double) * n, cudaMemcpyDeviceToHost, st));
+    NNVB_TRY(sync(ctx));
+    std::vector<int> open;
+    for (int p = 0; p < n; ++p) {
+        if (margin[p] > 0.0) status[p] = NNVB_VERDICT_EMPTY;
+        else if (b->box_implies_C[pair_q[p]]) open.push_back(p);
+    }
+    bool have_bounds = true;
+    for (int i = 0; i < b->net->n_relu; ++i) have_bounds = have_bounds && b->relu[i]->has_bounds;
+    if (open.empty() || !have_bounds) return NNVB_OK;
+
+    // witness points for the open pairs, in chunks that bound the scratch memory
+    int64_t max_ld = b->ld0;
+    for (const Layer& L : b->net->layers) max_ld = std::max(max_ld, lead_dim(L.Ho * L.Wo * L.Co));
+    const int64_t chunk_cap = std::max<int64_t>(1, (int64_t(1) << 31) / (max_ld * 8));
+    for (size_t c0 = 0; c0 < open.size(); c0 += chunk_cap) {
+        const int m = (int)std::min<size_t>(chunk_cap, open.size() - c0);
+        std::vector<int32_t> pq(m);
+        std::vector<double> Gc(size_t(m) * Nout), gc(m);
+        std::vector<int64_t> roff(m + 1, 0);
+        for (int i = 0; i < m; ++i) {
+            const int p = open[c0 + i];
+            pq[i] = pair_q[p];
+            gc[i] = g[p];
+            std::copy(G.begin() + size_t(p) * Nout, G.begin() + size_t(p + 1) * Nout, Gc.begin() + size_t(i) * Nout);
+            roff[i + 1] = roff[i] + (b->h_qcol_off[pq[i] + 1] - b->h_qcol_off[pq[i]]);
+        }
+        NNVB_TRY(b->hs_r.ensure(sizeof(double) * std::max<int64_t>(roff[m], 1), st));
+        NNVB_TRY(b->hs_roff.ensure(sizeof(int64_t) * (m + 1), st));
+        NNVB_TRY(b->hs_val.ensure(sizeof(double) * m, st));
+        NNVB_TRY(b->hs_scale.ensure(sizeof(double) * m, st));
+        NNVB_TRY(b->wit[0].ensure(sizeof(double) * max_ld * m, st));
+        NNVB_TRY(b->wit[1].ensure(sizeof(double) * max_ld * m, st));
+        NNVB_CUDA(cudaMemcpyAsync(b->hs_G.p, Gc.data(), sizeof(double) * m * Nout, cudaMemcpyHostToDevice, st));
+        NNVB_CUDA(cudaMemcpyAsync(b->hs_g.p, gc.data(), sizeof(double) * m, cudaMemcpyHostToDevice, st));
+        NNVB_CUDA(cudaMemcpyAsync(b->hs_q.p, pq.data(), sizeof(int32_t) * m, cudaMemcpyHostToDevice, st));
+        NNVB_CUDA(cudaMemcpyAsync(b->hs_roff.p, roff.data(), sizeof(int64_t) * (m + 1), cudaMemcpyHostToDevice, st));
+        NNVB_TRY(launch_halfspace_pairs(st, m, b->hs_q.as<int32_t>(), Nout, b->ld, b->V, qoff, qidx, b->pl.as<double>(),
+                                        b->pu.as<double>(), b->hs_G.as<double>(), b->hs_g.as<double>(), nullptr,
+                                        b->hs_r.as<double>(), b->hs_roff.as<int64_t>(), &ctx->launches));
+        if (b->kind == 1) {
+            NNVB_TRY(launch_witness_x0_bounds(st, m, b->hs_q.as<int32_t>(), b->N0, b->ld0, b->d_in.as<double>(),
+                                              b->hs_r.as<double>(), b->hs_roff.as<int64_t>(), b->wit[0].as<double>(),
+                                              &ctx->launches));
+        } else {
+            int64_t ncols0 = b->nq;
+            std::vector<int64_t> gen0(b->nq + 1);
+            for (int q = 0; q < b->nq; ++q) { gen0[q] = ncols0; ncols0 += b->P0[q]; }
+            gen0[b->nq] = ncols0;
+            NNVB_TRY(b->gen_off.ensure(sizeof(int64_t) * (b->nq + 1), st));
+            NNVB_CUDA(cudaMemcpyAsync(b->gen_off.p, gen0.data(), sizeof(int64_t) * (b->nq + 1), cudaMemcpyHostToDevice, st));
+            NNVB_TRY(launch_witness_x0_star(st, m, b->hs_q.as<int32_t>(), b->N0, b->ld0, b->ld0, b->d_in.as<double>(),
+                                            b->gen_off.as<int64_t>(), b->d_in_meta.as<double>(),
+                                            b->d_in_meta.as<double>() + ncols0, b->hs_r.as<double>(),
+                                            b->hs_roff.as<int64_t>(), b->wit[0].as<double>(), &ctx->launches));
+        }
+        double* X = nullptr;
+        int64_t ldx = 0;
+        NNVB_TRY(witness_forward(b, m, b->hs_q.as<int32_t>(), &X, &ldx, b->hs_r.as<double>(), b->hs_roff.as<int64_t>()));
+        NNVB_TRY(launch_witness_value(st, m, Nout, ldx, X, b->hs_G.as<double>(), b->hs_g.as<double>(),
+                                      b->hs_val.as<double>(), b->hs_scale.as<double>(), &ctx->launches));
+        std::vector<double> val(m), scale(m);
+        NNVB_CUDA(cudaMemcpyAsync(val.data(), b->hs_val.p, sizeof(double) * m, cudaMemcpyDeviceToHost, st));
+        NNVB_CUDA(cudaMemcpyAsync(scale.data(), b->hs_scale.p, sizeof(double) * m, cudaMemcpyDeviceToHost, st));
+        NNVB_TRY(sync(ctx));
+        // accept only points clearly inside the halfspace: well beyond the feasibility
+        // tolerance of an LP solver deciding the same question
+        for (int i = 0; i < m; ++i)
+            if (val[i] < -1e-6 * (1.0 + scale[i])) status[open[c0 + i]] = NNVB_VERDICT_NONEMPTY;
+    }
     return NNVB_OK;
 }
 
@@ -1136,28 +1387,19 @@ int nnvb_batch_halfspace_margins(nnvb_batch* b, int q, const double* G, const do
                                  int* status) {
     NNVB_TRY(check_reached(b, q));
     NNVB_REQUIRE(G && g && nh > 0 && margin_lo, "nnvb_batch_halfspace_margins: bad argument");
-    nnvb_ctx* ctx = b->net->ctx;
-    cudaStream_t st = ctx->stream;
-    NNVB_CUDA(cudaSetDevice(ctx->device));
+    NNVB_CUDA(cudaSetDevice(b->net->ctx->device));
     const int64_t Nout = b->N;
     // row-major [nh][Nout] copy of the column-major G
-    std::vector<double> Gr(size_t(nh) * Nout);
+    std::vector<double> Gr(size_t(nh) * Nout), gv(g, g + nh), margin;
     for (int h = 0; h < nh; ++h)
         for (int64_t o = 0; o < Nout; ++o) Gr[size_t(h) * Nout + o] = G[size_t(h) + size_t(nh) * o];
-    const size_t gb = sizeof(double) * nh * Nout, sb = sizeof(double) * nh;
-    NNVB_TRY(b->tmp.ensure(gb + 2 * sb + 64, st));
-    double* dG = b->tmp.as<double>();
-    double* dg = dG + size_t(nh) * Nout;
-    double* dm = dg + nh;
-    NNVB_TRY(h2d_small(ctx, dG, Gr.data(), gb));
-    NNVB_TRY(h2d_small(ctx, dg, g, sb));
-    NNVB_TRY(launch_halfspace_margins(st, 1, q, Nout, b->ld, b->V, b->qcol_off[b->list_cur].as<int64_t>(),
-                                      b->qcol_idx[b->list_cur].as<int32_t>(), b->pl.as<double>(), b->pu.as<double>(),
-                                      dG, dg, nh, dm, &ctx->launches));
-    NNVB_CUDA(cudaMemcpyAsync(margin_lo, dm, sb, cudaMemcpyDeviceToHost, st));
-    NNVB_TRY(sync(ctx));
-    if (status)
-        for (int h = 0; h < nh; ++h) status[h] = margin_lo[h] > 0.0 ? NNVB_VERDICT_EMPTY : NNVB_UNDECIDED;
+    std::vector<int32_t> pq(nh, q);
+    std::vector<int> st;
+    NNVB_TRY(test_pairs(b, pq, Gr, gv, margin, st));
+    for (int h = 0; h < nh; ++h) {
+        margin_lo[h] = margin[h];
+        if (status) status[h] = st[h];
+    }
     return NNVB_OK;
 }
 
@@ -1166,15 +1408,14 @@ int nnvb_batch_verify_robust(nnvb_batch* b, const int32_t* target, int kind, int
     NNVB_TRY(check_reached(b, 0));
     NNVB_REQUIRE(target && verdict, "nnvb_batch_verify_robust: NULL argument");
     NNVB_REQUIRE(kind == 0 || kind == 1, "nnvb_batch_verify_robust: kind must be 0 ('max') or 1 ('min')");
-    nnvb_ctx* ctx = b->net->ctx;
-    cudaStream_t st = ctx->stream;
-    NNVB_CUDA(cudaSetDevice(ctx->device));
+    NNVB_CUDA(cudaSetDevice(b->net->ctx->device));
     const int nq = b->nq;
     const int64_t Nout = b->N;
     NNVB_REQUIRE(Nout >= 2, "nnvb_batch_verify_robust: output size must be >= 2");
     const int nh = int(Nout - 1);
     // NN.robustness_set (NN.m:1352-1367): rows over i != target; 'max': e_t - e_i, 'min': e_i - e_t
-    std::vector<double> G(size_t(nq) * nh * Nout, 0.0), g(size_t(nq) * nh, 0.0);
+    std::vector<double> G(size_t(nq) * nh * Nout, 0.0), g(size_t(nq) * nh, 0.0), margin;
+    std::vector<int32_t> pq(size_t(nq) * nh);
     for (int q = 0; q < nq; ++q) {
         const int t = target[q];
         NNVB_REQUIRE(t >= 0 && t < Nout, "target idx must be less than the output size of the NN (query %d: %d)", q, t);
@@ -1184,32 +1425,22 @@ int nnvb_batch_verify_robust(nnvb_batch* b, const int32_t* target, int kind, int
             double* row = G.data() + (size_t(q) * nh + h) * Nout;
             if (kind == 0) { row[i] = -1.0; row[t] = 1.0; }
             else { row[i] = 1.0; row[t] = -1.0; }
+            pq[size_t(q) * nh + h] = q;
             ++h;
         }
     }
-    const size_t gb = sizeof(double) * G.size(), sb = sizeof(double) * g.size();
-    NNVB_TRY(b->tmp.ensure(gb + 2 * sb + 64, st));
-    double* dG = b->tmp.as<double>();
-    double* dg = dG + G.size();
-    double* dm = dg + g.size();
-    NNVB_CUDA(cudaMemcpyAsync(dG, G.data(), gb, cudaMemcpyHostToDevice, st));
-    NNVB_CUDA(cudaMemsetAsync(dg, 0, sb, st));
-    NNVB_TRY(launch_halfspace_margins(st, nq, 0, Nout, b->ld, b->V, b->qcol_off[b->list_cur].as<int64_t>(),
-                                      b->qcol_idx[b->list_cur].as<int32_t>(), b->pl.as<double>(), b->pu.as<double>(),
-                                      dG, dg, nh, dm, &ctx->launches));
-    std::vector<double> hm(g.size());
-    NNVB_CUDA(cudaMemcpyAsync(hm.data(), dm, sb, cudaMemcpyDeviceToHost, st));
-    NNVB_TRY(sync(ctx));
+    std::vector<int> st;
+    NNVB_TRY(test_pairs(b, pq, G, g, margin, st));
     for (int q = 0; q < nq; ++q) {
-        bool all_empty = true;
+        bool all_empty = true, any_nonempty = false;
         for (int h = 0; h < nh; ++h) {
-            const double mv = hm[size_t(q) * nh + h];
-            const bool empty = mv > 0.0;
-            all_empty = all_empty && empty;
-            if (status) status[size_t(q) * nh + h] = empty ? NNVB_VERDICT_EMPTY : NNVB_UNDECIDED;
-            if (margin_lo) margin_lo[size_t(q) * nh + h] = mv;
+            const int s = st[size_t(q) * nh + h];
+            all_empty = all_empty && s == NNVB_VERDICT_EMPTY;
+            any_nonempty = any_nonempty || s == NNVB_VERDICT_NONEMPTY;
+            if (status) status[size_t(q) * nh + h] = s;
+            if (margin_lo) margin_lo[size_t(q) * nh + h] = margin[size_t(q) * nh + h];
         }
-        verdict[q] = all_empty ? NNVB_VERDICT_EMPTY : NNVB_UNDECIDED;
+        verdict[q] = any_nonempty ? NNVB_VERDICT_NONEMPTY : (all_empty ? NNVB_VERDICT_EMPTY : NNVB_UNDECIDED);
     }
     return NNVB_OK;
 }

@@ -329,17 +329,23 @@ __global__ void rebuild_lists_kernel(int nq, const int64_t* __restrict__ qcol_of
 }
 
 // ---------------------------------------------------------------------------
-// Halfspace rows and their minimum over the predicate box.
-// block = one (query, halfspace); lanes stride over the query's columns.
+// Halfspace rows and their minimum over the predicate box.  A "pair" is one
+// halfspace row G_p x <= g_p tested against the output set of query pair_q[p].
+// r_p[pos] = G_p . V[:, col(pos)] is the coefficient of predicate `pos` in the
+// halfspace row of Star.intersectHalfSpace (Star.m:576); the minimum of
+// G_p x - g_p over the predicate box is (G_p c - g_p) + sum_pos min(r*pl, r*pu).
+// block = one pair; lanes stride over the query's columns.  r_out (optional)
+// receives the coefficients at r_off[p] + pos.
 __global__ void __launch_bounds__(256)
-halfspace_margin_kernel(int q_base, int64_t Nout, int64_t ld, const double* __restrict__ V,
-                        const int64_t* __restrict__ qcol_off, const int32_t* __restrict__ qcol_idx,
-                        const double* __restrict__ pl, const double* __restrict__ pu,
-                        const double* __restrict__ G, const double* __restrict__ g, int nh,
-                        double* __restrict__ margin) {
-    const int bq = blockIdx.x, h = blockIdx.y;
-    const int q = q_base + bq;
-    const double* Gr = G + (int64_t(bq) * nh + h) * Nout;
+halfspace_pairs_kernel(const int32_t* __restrict__ pair_q, int64_t Nout, int64_t ld,
+                       const double* __restrict__ V, const int64_t* __restrict__ qcol_off,
+                       const int32_t* __restrict__ qcol_idx, const double* __restrict__ pl,
+                       const double* __restrict__ pu, const double* __restrict__ G,
+                       const double* __restrict__ g, double* __restrict__ margin,
+                       double* __restrict__ r_out, const int64_t* __restrict__ r_off) {
+    const int p = blockIdx.x;
+    const int q = pair_q[p];
+    const double* Gr = G + int64_t(p) * Nout;
     double acc = 0.0;
     const int64_t o0 = qcol_off[q], o1 = qcol_off[q + 1];
     for (int64_t pos = o0 + threadIdx.x; pos < o1; pos += blockDim.x) {
@@ -348,6 +354,7 @@ halfspace_margin_kernel(int q_base, int64_t Nout, int64_t ld, const double* __re
         double r = 0.0;
         for (int64_t o = 0; o < Nout; ++o) r = fma(Gr[o], v[o], r);
         acc += fmin(r * pl[col], r * pu[col]);
+        if (r_out) r_out[r_off[p] + (pos - o0)] = r;
     }
     __shared__ double s[256];
     s[threadIdx.x] = acc;
@@ -356,12 +363,137 @@ halfspace_margin_kernel(int q_base, int64_t Nout, int64_t ld, const double* __re
         if (threadIdx.x < o) s[threadIdx.x] += s[threadIdx.x + o];
         __syncthreads();
     }
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 0 && margin) {
         const double* v = V + int64_t(q) * ld;
         double r = 0.0;
         for (int64_t o = 0; o < Nout; ++o) r = fma(Gr[o], v[o], r);
-        margin[int64_t(bq) * nh + h] = (r - g[int64_t(bq) * nh + h]) + s[0];
+        margin[p] = (r - g[p]) + s[0];
     }
+}
+
+// ---------------------------------------------------------------------------
+// Witness search: a point of the output set inside a halfspace proves the
+// intersection non-empty.  Every point of an approx-star set is reached by
+// picking the input predicates in their box and, neuron by neuron, a value of
+// each new predicate between the lower envelope max(0,x) and the chord
+// a*(x-l) of the triangle relaxation (PosLin.m:716-735); the greedy choice
+// takes whichever end lowers the halfspace row, judged by the sign of the
+// predicate's coefficient r.
+
+// x0 for ImageStar(lb,ub) queries: entry i sits at lb or ub according to the
+// sign of the coefficient of its predicate.  One block per pair.
+__global__ void __launch_bounds__(256)
+witness_x0_bounds_kernel(const int32_t* __restrict__ pair_q, int64_t N, int64_t ld,
+                         const double* __restrict__ lbub, const double* __restrict__ r,
+                         const int64_t* __restrict__ r_off, double* __restrict__ X) {
+    const int p = blockIdx.x;
+    const int q = pair_q[p];
+    const double* lb = lbub + int64_t(q) * 2 * N;
+    const double* ub = lb + N;
+    const double* rp = r + r_off[p];
+    __shared__ int warp_cnt[8];
+    __shared__ int64_t running;
+    if (threadIdx.x == 0) running = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int64_t base = 0; base < N; base += blockDim.x) {
+        const int64_t i = base + threadIdx.x;
+        double l = 0.0, u = 0.0;
+        bool has = false;
+        if (i < N) {
+            l = lb[i];
+            u = ub[i];
+            has = (0.5 * (u - l) != 0.0) || N == 1;
+        }
+        const unsigned bal = __ballot_sync(0xffffffffu, has);
+        if (lane == 0) warp_cnt[warp] = __popc(bal);
+        __syncthreads();
+        int before = 0, total = 0;
+        for (int w = 0; w < 8; ++w) {
+            if (w < warp) before += warp_cnt[w];
+            total += warp_cnt[w];
+        }
+        if (i < N) {
+            double x = 0.5 * (l + u);
+            if (has) {
+                const int64_t pos = running + before + __popc(bal & ((1u << lane) - 1u));
+                const double hw = 0.5 * (u - l);
+                x = rp[pos] > 0.0 ? x - hw : x + hw;       // predicate at -1 or +1
+            }
+            X[int64_t(p) * ld + i] = x;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) running += total;
+        __syncthreads();
+    }
+}
+
+// x0 for general star queries: x0 = c + sum_j alpha_j G0_j with alpha_j = pl_j if
+// r_j > 0 else pu_j.  V0 is the uploaded input matrix (centres first, then each
+// query's generators from column gen0[q]).  grid = (pairs, row blocks).
+__global__ void __launch_bounds__(256)
+witness_x0_star_kernel(const int32_t* __restrict__ pair_q, int64_t N, int64_t ld, int64_t ld0,
+                       const double* __restrict__ V0, const int64_t* __restrict__ gen0,
+                       const double* __restrict__ pl0, const double* __restrict__ pu0,
+                       const double* __restrict__ r, const int64_t* __restrict__ r_off,
+                       double* __restrict__ X) {
+    const int p = blockIdx.x;
+    const int q = pair_q[p];
+    const int64_t i = int64_t(blockIdx.y) * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const double* rp = r + r_off[p];
+    const int64_t c0 = gen0[q], c1 = gen0[q + 1];
+    double x = V0[int64_t(q) * ld0 + i];
+    for (int64_t col = c0; col < c1; ++col) {
+        const double a = rp[col - c0] > 0.0 ? pl0[col] : pu0[col];
+        x = fma(a, V0[col * ld0 + i], x);
+    }
+    X[int64_t(p) * ld + i] = x;
+}
+
+// relaxed ReLU on the witness points of one layer, in place.
+__global__ void __launch_bounds__(256)
+witness_relu_kernel(const int32_t* __restrict__ pair_q, int64_t N, int64_t ld, double* __restrict__ X,
+                    const double* __restrict__ lb, const double* __restrict__ ub,
+                    const int32_t* __restrict__ rank, const int64_t* __restrict__ P_in,
+                    const double* __restrict__ r, const int64_t* __restrict__ r_off) {
+    const int p = blockIdx.x;
+    const int q = pair_q[p];
+    const int64_t i = int64_t(blockIdx.y) * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    const double l = lb[int64_t(q) * N + i], u = ub[int64_t(q) * N + i];
+    double* px = X + int64_t(p) * ld + i;
+    const double x = *px;
+    double y = x;
+    if (u <= 0.0) {
+        y = 0.0;
+    } else if (l < 0.0) {
+        const double lo = fmax(x, 0.0);
+        const double rr = r[r_off[p] + P_in[q] + rank[int64_t(q) * N + i]];
+        if (rr < 0.0) {
+            const double a = u / (u - l);
+            y = fmax(lo, a * x - a * l);
+        } else {
+            y = lo;
+        }
+    }
+    *px = y;
+}
+
+// value[p] = G_p . x_p - g_p and a magnitude for the acceptance tolerance.
+__global__ void witness_value_kernel(int n_pairs, int64_t Nout, int64_t ld, const double* __restrict__ X,
+                                     const double* __restrict__ G, const double* __restrict__ g,
+                                     double* __restrict__ value, double* __restrict__ scale) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= n_pairs) return;
+    double v = 0.0, s = 0.0;
+    for (int64_t o = 0; o < Nout; ++o) {
+        const double t = G[int64_t(p) * Nout + o] * X[int64_t(p) * ld + o];
+        v += t;
+        s += fabs(t);
+    }
+    value[p] = v - g[p];
+    scale[p] = s + fabs(g[p]);
 }
 
 }  // namespace
@@ -439,13 +571,50 @@ int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, in
     return NNVB_OK;
 }
 
-int launch_halfspace_margins(cudaStream_t st, int nq, int q_base, int64_t Nout, int64_t ld, const double* V,
-                             const int64_t* qcol_off, const int32_t* qcol_idx, const double* pl,
-                             const double* pu, const double* G, const double* g, int nh,
-                             double* margin, int64_t* launches) {
-    if (nq <= 0 || nh <= 0) return NNVB_OK;
-    dim3 grid((unsigned)nq, (unsigned)nh);
-    halfspace_margin_kernel<<<grid, 256, 0, st>>>(q_base, Nout, ld, V, qcol_off, qcol_idx, pl, pu, G, g, nh, margin);
+int launch_halfspace_pairs(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t Nout, int64_t ld,
+                           const double* V, const int64_t* qcol_off, const int32_t* qcol_idx, const double* pl,
+                           const double* pu, const double* G, const double* g, double* margin, double* r_out,
+                           const int64_t* r_off, int64_t* launches) {
+    if (n_pairs <= 0) return NNVB_OK;
+    halfspace_pairs_kernel<<<n_pairs, 256, 0, st>>>(pair_q, Nout, ld, V, qcol_off, qcol_idx, pl, pu, G, g, margin,
+                                                    r_out, r_off);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_witness_x0_bounds(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t N, int64_t ld,
+                             const double* lbub, const double* r, const int64_t* r_off, double* X,
+                             int64_t* launches) {
+    witness_x0_bounds_kernel<<<n_pairs, 256, 0, st>>>(pair_q, N, ld, lbub, r, r_off, X);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_witness_x0_star(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t N, int64_t ld, int64_t ld0,
+                           const double* V0, const int64_t* gen0, const double* pl0, const double* pu0,
+                           const double* r, const int64_t* r_off, double* X, int64_t* launches) {
+    dim3 grid((unsigned)n_pairs, (unsigned)ceil_div(N, 256));
+    witness_x0_star_kernel<<<grid, 256, 0, st>>>(pair_q, N, ld, ld0, V0, gen0, pl0, pu0, r, r_off, X);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_witness_relu(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t N, int64_t ld, double* X,
+                        const double* lb, const double* ub, const int32_t* rank, const int64_t* P_in,
+                        const double* r, const int64_t* r_off, int64_t* launches) {
+    dim3 grid((unsigned)n_pairs, (unsigned)ceil_div(N, 256));
+    witness_relu_kernel<<<grid, 256, 0, st>>>(pair_q, N, ld, X, lb, ub, rank, P_in, r, r_off);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_witness_value(cudaStream_t st, int n_pairs, int64_t Nout, int64_t ld, const double* X, const double* G,
+                         const double* g, double* value, double* scale, int64_t* launches) {
+    witness_value_kernel<<<(unsigned)ceil_div(n_pairs, 128), 128, 0, st>>>(n_pairs, Nout, ld, X, G, g, value, scale);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;

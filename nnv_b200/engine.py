@@ -50,6 +50,20 @@ class Context:
     def launch_count(self):
         return int(self.lib.nnvb_launch_count(self.handle))
 
+    def profile_enable(self, on=True):
+        """Start (and zero) or stop the per-kernel-family device timers."""
+        L.check(self.lib.nnvb_profile_enable(self.handle, int(bool(on))), "nnvb_profile_enable")
+
+    def profile_read(self):
+        """{family: {"ms", "launches", "work"}} accumulated since profile_enable."""
+        out = {}
+        for i, name in enumerate(L.PROF_FAMILIES):
+            ms, n, work = C.c_double(), C.c_int64(), C.c_double()
+            L.check(self.lib.nnvb_profile_read(self.handle, i, C.byref(ms), C.byref(n), C.byref(work)),
+                    "nnvb_profile_read")
+            out[name] = {"ms": ms.value, "launches": n.value, "work": work.value}
+        return out
+
     # single-layer entry points ------------------------------------------------
     def layer_apply(self, layer, V):
         """Apply one affine layer to V[H,W,C,ncols]; returns the output tensor."""

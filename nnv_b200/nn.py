@@ -498,18 +498,21 @@ class NN:
     def verify_robustness_batch(self, inputSets, reachOptions, targets, class_type="max", stats=None):
         """verify_robustness over a list of sets with 1-based label targets.
 
-        Device side: reach, then the box minimum of every halfspace row (a
-        positive minimum proves the intersection empty).  Host side, only for
-        the halfspaces left undecided: the feasibility LP of Star.isEmptySet on
-        the constraint system of that query, re-reached with constraint records
-        kept."""
-        b = self.reach_batch(inputSets, reachOptions)
+        Device side: reach, then for every halfspace row of the robustness
+        specification (a) its minimum over the output set's predicate box — a
+        positive minimum proves the intersection empty — and (b) a greedy
+        witness point of the output set — a point inside the halfspace proves it
+        non-empty.  Host side, only for queries still undecided: the feasibility
+        LP of Star.isEmptySet on the open rows, on the constraint system of that
+        query re-reached with constraint records kept."""
+        b = self.reach_batch(inputSets, reachOptions, keep_layer_bounds=True)
         t0 = np.asarray(targets, dtype=np.int64) - 1
         verdict, status, _ = b.verify_robust(t0, class_type)
-        result = np.where(verdict == L.VERDICT_EMPTY, 1, 0).astype(np.int64)
-        undecided = np.nonzero(verdict != L.VERDICT_EMPTY)[0]
+        result = np.where(verdict == L.VERDICT_EMPTY, 1, np.where(verdict == L.VERDICT_NONEMPTY, 2, 0)).astype(np.int64)
+        undecided = np.nonzero(verdict == L.UNDECIDED)[0]
         if stats is not None:
             stats["n_prefilter"] = int((verdict == L.VERDICT_EMPTY).sum())
+            stats["n_witness"] = int((verdict == L.VERDICT_NONEMPTY).sum())
             stats["n_lp_queries"] = int(len(undecided))
         b.close()
         for q in undecided:
@@ -517,7 +520,7 @@ class NN:
             bq = self.reach_batch([inputSets[q]], reachOptions, keep_constraints=True)
             S = _result_set(bq, 0, True)
             hs = self.robustness_set(int(targets[q]), class_type)
-            open_rows = np.nonzero(status[q] != L.VERDICT_EMPTY)[0]
+            open_rows = np.nonzero(status[q] == L.UNDECIDED)[0]
             result[q] = verify_specification([S], [hs[i] for i in open_rows])
             bq.close()
         return result

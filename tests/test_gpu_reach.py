@@ -1,0 +1,198 @@
+"""End-to-end parity of the CUDA reach (through the C ABI and the reference-shaped
+host API) against the CPU oracle and the committed fixtures: generator tensors,
+predicate bounds, constraint systems and output ranges within 1e-9 relative;
+crossing-neuron index lists, predicate counts and verdicts identical."""
+import numpy as np
+import pytest
+
+from nnv_b200 import nn
+from nnv_b200.configs import forward_concrete, make_config
+from nnv_b200.engine import Batch, Network
+from oracle import nnv_oracle as O
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-9
+CASES = [("fc5", False, 6), ("cnn28", True, 3), ("cnn32", True, 3), ("bright28", True, 4), ("vgg224", True, 1)]
+
+
+def _rel(a, b):
+    return np.abs(a - b).max() / max(np.abs(b).max(), 1e-300)
+
+
+@pytest.mark.parametrize("name,small,nq", CASES)
+def test_reach_parity_vs_oracle(ctx, golden, name, small, nq):
+    cfg = make_config(name, n_queries=nq, small=small)
+    net = Network(ctx, cfg["layers"], cfg["in_shape"])
+    b = Batch(net, cfg["queries"])
+    b.upload()
+    b.reach(keep_constraints=True, keep_layer_bounds=True)
+    for q, qu in enumerate(cfg["queries"]):
+        S = O.reach(cfg["layers"], O.star_from_query(qu))
+        V = b.get_V(q)
+        assert V.shape == S.V.shape
+        assert _rel(V, S.V) < TOL
+        lb, ub = b.get_ranges(q)
+        rl, ru = O.output_ranges(S)
+        scale = max(np.abs(rl).max(), np.abs(ru).max())
+        assert np.abs(lb - rl).max() / scale < TOL and np.abs(ub - ru).max() / scale < TOL
+        assert np.allclose(lb, golden["%s_q%d_lb" % (name, q)], rtol=0, atol=TOL * scale)
+        assert np.allclose(ub, golden["%s_q%d_ub" % (name, q)], rtol=0, atol=TOL * scale)
+        for li, t in enumerate(S.trace):
+            idx, cl, cu = b.get_crossing(q, li)
+            assert np.array_equal(idx, t["cross"])                       # bit-exact index work
+            assert np.array_equal(idx, golden["%s_q%d_cross%d" % (name, q, li)])
+            bscale = max(np.abs(t["lb"]).max(), np.abs(t["ub"]).max())
+            assert np.abs(cl - t["lb"][t["cross"]]).max(initial=0) / bscale < TOL
+            assert np.abs(cu - t["ub"][t["cross"]]).max(initial=0) / bscale < TOL
+            ll, lu = b.get_layer_ranges(q, li, t["N"])
+            assert np.abs(ll - t["lb"]).max() / bscale < TOL and np.abs(lu - t["ub"]).max() / bscale < TOL
+            assert np.array_equal(np.nonzero(lu <= 0)[0], t["dead"])
+        pl, pu = b.get_pred_bounds(q)
+        assert np.array_equal(pl, S.pl) and _rel(pu, S.pu) < TOL
+        Cm, d = b.get_constraints(q)
+        Cd = S.C.toarray()
+        assert Cm.shape == Cd.shape and _rel(Cm, Cd) < TOL and np.abs(d - S.d).max() <= TOL * max(np.abs(S.d).max(), 1)
+        P, m = b.out_dims(q)
+        assert P == S.P and m == S.C.shape[0]
+    stats = b.relu_stats()
+    assert len(stats) == sum(1 for l in cfg["layers"] if l["type"] == "relu")
+    b.close()
+    net.close()
+
+
+def test_reach_is_deterministic_and_batch_invariant(ctx):
+    cfg = make_config("cnn32", n_queries=3, small=True)
+    net = Network(ctx, cfg["layers"], cfg["in_shape"])
+    b = Batch(net, cfg["queries"])
+    b.upload()
+    b.reach()
+    first = [b.get_V(q) for q in range(3)]
+    b.reach()                                                # same uploaded inputs, second pass
+    for q in range(3):
+        assert np.array_equal(b.get_V(q), first[q])
+    b.close()
+    for q in range(3):                                       # one query at a time
+        b1 = Batch(net, [cfg["queries"][q]])
+        b1.upload()
+        b1.reach()
+        assert np.array_equal(b1.get_V(0), first[q])
+        b1.close()
+    net.close()
+
+
+@pytest.mark.parametrize("name,small,nq", [("fc5", False, 6), ("cnn28", True, 3), ("cnn32", True, 3), ("bright28", True, 4)])
+def test_verdicts_match_oracle(ctx, golden, name, small, nq):
+    cfg = make_config(name, n_queries=nq, small=small)
+    net = nn.NN(cfg["layers"], ctx=ctx)
+    sets = []
+    for qu in cfg["queries"]:
+        if "lb" in qu:
+            sets.append(nn.ImageStar(qu["lb"], qu["ub"]))
+        else:
+            sets.append(nn.ImageStar(qu["V"], qu["C"], qu["d"], qu["pl"], qu["pu"]))
+    targets = [qu["target"] + 1 for qu in cfg["queries"]]
+    kind = cfg["queries"][0]["spec"]
+    stats = {}
+    got = net.verify_robustness_batch(sets, {"reachMethod": "approx-star"}, targets, kind, stats)
+    assert np.array_equal(got, golden[name + "_verdicts"])
+    assert stats["n_prefilter"] + stats["n_witness"] + stats["n_lp_queries"] == nq
+
+
+def test_reference_shaped_api_single_set(ctx):
+    cfg = make_config("cnn28", n_queries=1, small=True)
+    qu = cfg["queries"][0]
+    layers = []
+    for L in cfg["layers"]:
+        if L["type"] == "conv2d":
+            layers.append(nn.Conv2DLayer(L["W"], L["b"], L["pad"], L["stride"], L["dilation"]))
+        elif L["type"] == "fc":
+            layers.append(nn.FullyConnectedLayer(L["W"], L["b"]))
+        elif L["type"] == "relu":
+            layers.append(nn.ReluLayer())
+    net = nn.NN(layers, ctx=ctx)
+    I = nn.ImageStar(qu["lb"], qu["ub"])
+    R = net.reach(I, {"reachMethod": "relax-star-area", "relaxFactor": 1})
+    S = O.reach(cfg["layers"], O.star_from_query(qu))
+    assert isinstance(R, nn.ImageStar) and R.numPred == S.P
+    assert _rel(R.V, S.V) < TOL and _rel(R.C, S.C.toarray()) < TOL
+    assert net.verify_robustness(I, {"reachMethod": "approx-star"}, qu["target"] + 1) == O.verify_robustness(cfg["layers"], qu)
+    # layer-level reach contract: L.reach(set, method)
+    R1 = layers[0].reach(I, "approx-star")
+    assert _rel(R1.V, O.conv2d_reach(O.star_from_query(qu), cfg["layers"][0]).V) < TOL
+
+
+def test_relu_layer_reach_kat(ctx, kats):
+    # code/nnv/tests/nn/layers/ReluLayer/test_layers_relu.m:36-55 through ReluLayer.reach
+    IM, LB, UB = kats["relu_reach_IM"], kats["relu_reach_LB"], kats["relu_reach_UB"]
+    R = nn.ReluLayer().reach(nn.ImageStar(IM + LB, IM + UB), "approx-star")
+    S = O.relu_reach(O.star_from_bounds(IM + LB, IM + UB))
+    assert R.numPred == 7 and np.array_equal(R.V, S.V)
+    assert np.allclose(R.C, S.C.toarray(), rtol=1e-12, atol=1e-15) and np.allclose(R.d, S.d, rtol=1e-12, atol=1e-15)
+    # all-positive and all-negative stars (code/nnv/tests/soundness/test_regression_reachability.m:47-79)
+    for sign in (1, -1):
+        c = sign * np.array([2., 3., 4.])
+        St = nn.Star(np.hstack([c[:, None], 0.1 * np.eye(3)]), np.vstack([np.eye(3), -np.eye(3)]), 0.5 * np.ones(6),
+                     -0.5 * np.ones(3), 0.5 * np.ones(3))
+        Rs = nn.ReluLayer().reach(St, "approx-star")
+        assert isinstance(Rs, nn.Star) and Rs.nVar == 3
+        assert np.abs(Rs.V[:, 0] - np.maximum(c, 0)).max() < 1e-10
+
+
+def test_soundness_by_sampling_on_gpu(ctx):
+    cfg = make_config("cnn32", n_queries=2, small=True)
+    net = Network(ctx, cfg["layers"], cfg["in_shape"])
+    b = Batch(net, cfg["queries"])
+    b.upload()
+    b.reach()
+    rng = np.random.default_rng(3)
+    for q, qu in enumerate(cfg["queries"]):
+        lb, ub = b.get_ranges(q)
+        for _ in range(8):
+            x = rng.uniform(qu["lb"], qu["ub"])
+            y = forward_concrete(cfg["layers"], x)
+            assert np.all(y >= lb - 1e-9) and np.all(y <= ub + 1e-9)
+    b.close()
+    net.close()
+
+
+def test_edge_cases(ctx):
+    from nnv_b200._lib import NNVError
+    # a point set (no generators) through a whole network
+    cfg = make_config("cnn28", n_queries=1, small=True)
+    x = cfg["queries"][0]["lb"]
+    net = Network(ctx, cfg["layers"], cfg["in_shape"])
+    b = Batch(net, [{"lb": x, "ub": x}])
+    b.upload()
+    b.reach(keep_constraints=True)
+    assert b.out_dims(0) == (0, 1)
+    lb, ub = b.get_ranges(0)
+    y = forward_concrete(cfg["layers"], x)
+    assert np.abs(lb - y).max() < 1e-12 and np.array_equal(lb, ub)
+    # results before reach, bad query index, unset query
+    b2 = Batch(net, n_queries=2)
+    b2.set_bounds(0, x, x)
+    with pytest.raises(NNVError, match="never set"):
+        b2.upload()
+    with pytest.raises(NNVError):
+        b2.get_ranges(0)
+    with pytest.raises(NNVError, match="lb > ub"):
+        b2.set_bounds(1, x + 1, x)
+    b.close()
+    b2.close()
+    net.close()
+
+
+def test_capacity_error_is_reported_not_fatal():
+    from nnv_b200._lib import NNVError, NNVB_E_CAPACITY
+    from nnv_b200.engine import Context
+    small_ctx = Context(0, 1 << 20)                         # 1 MiB arena
+    cfg = make_config("cnn28", n_queries=4)
+    net = Network(small_ctx, cfg["layers"], cfg["in_shape"])
+    b = Batch(net, cfg["queries"])
+    b.upload()
+    with pytest.raises(NNVError) as ei:
+        b.reach()
+    assert ei.value.status == NNVB_E_CAPACITY
+    b.close()
+    net.close()
+    small_ctx.close()

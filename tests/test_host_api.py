@@ -1,0 +1,108 @@
+"""Host-side mirror of the reference API (no GPU needed): constructors, their
+error behaviour, the robustness specification and option validation."""
+import numpy as np
+import pytest
+
+from nnv_b200 import nn
+from nnv_b200.configs import make_config, out_shape
+from oracle import nnv_oracle as O
+
+
+def test_imagestar_from_bounds_matches_oracle():
+    rng = np.random.default_rng(0)
+    lb = rng.uniform(size=(4, 3, 2))
+    ub = lb + rng.uniform(size=(4, 3, 2)) * (rng.uniform(size=(4, 3, 2)) > 0.3)
+    I = nn.ImageStar(lb, ub)
+    S = O.star_from_bounds(lb, ub)
+    assert I.numPred == S.P
+    assert np.array_equal(I.V, S.V)
+    assert np.array_equal(I.pred_lb, S.pl) and np.array_equal(I.pred_ub, S.pu)
+    assert I.C.shape == (1, S.P) and not I.C.any() and np.array_equal(I.d, [0.0])
+    St = I.toStar()
+    assert St.dim == 24 and St.nVar == S.P and np.array_equal(St.V, S.mat())
+
+
+def test_imagestar_constructor_errors():
+    with pytest.raises(ValueError, match="Inconsistency between lower bound image and upper bound image"):
+        nn.ImageStar(np.zeros((2, 2, 1)), np.zeros((2, 3, 1)))
+    with pytest.raises(ValueError, match="Invalid number of input arguments"):
+        nn.ImageStar(np.zeros((2, 2, 1)))
+    V = np.zeros((2, 2, 1, 3))
+    with pytest.raises(ValueError, match="constraint matrix"):
+        nn.ImageStar(V, np.zeros((1, 5)), np.zeros(1), -np.ones(2), np.ones(2))
+    with pytest.raises(ValueError, match="predicate"):
+        nn.ImageStar(V, np.zeros((1, 2)), np.zeros(1), -np.ones(3), np.ones(3))
+
+
+def test_star_constructor_errors():
+    with pytest.raises(ValueError, match="Inconsistency between basic matrix and constraint matrix"):
+        nn.Star(np.zeros((2, 3)), np.zeros((1, 3)), np.zeros(1))
+    with pytest.raises(ValueError, match="constraint vector"):
+        nn.Star(np.zeros((2, 3)), np.zeros((2, 2)), np.zeros(1))
+    with pytest.raises(ValueError, match="Inconsistent dimensions between lb and ub"):
+        nn.Star(np.zeros(2), np.zeros(3))
+    S = nn.Star(np.array([0., -1.]), np.array([1., 1.]))
+    assert S.dim == 2 and S.nVar == 2
+    with pytest.raises(ValueError, match="Inconsistent dimension in the ImageStar"):
+        S.toImageStar(3, 1, 1)
+
+
+def test_layer_constructor_errors():
+    with pytest.raises(ValueError, match="filter weights and filter biases"):
+        nn.Conv2DLayer(np.zeros((3, 3, 1, 2)), np.zeros(3))
+    with pytest.raises(ValueError, match="Invalid padding size"):
+        nn.Conv2DLayer(np.zeros((3, 3, 1, 2)), np.zeros(2), PaddingSize=(1, 1))
+    with pytest.raises(ValueError, match="weight matrix and bias vector"):
+        nn.FullyConnectedLayer(np.zeros((2, 3)), np.zeros(3))
+    with pytest.raises(ValueError):
+        nn.AveragePooling2DLayer((2,), (2, 2))
+
+
+def test_robustness_set_matches_reference_construction():
+    net = nn.NN([nn.FullyConnectedLayer(np.zeros((4, 3)), np.zeros(4))])
+    for kind in ("max", "min"):
+        for t in range(1, 5):
+            hs = net.robustness_set(t, kind)
+            G = np.vstack([h.G for h in hs])
+            Go, go = O.robustness_set(4, t - 1, kind)
+            assert np.array_equal(G, Go) and all(h.g[0] == 0 for h in hs)
+    # NN.m:1343-1345
+    with pytest.raises(ValueError, match="Target idx must be less than or equal"):
+        net.robustness_set(5)
+
+
+def test_reach_option_validation():
+    v = nn._validate_reach_options
+    assert v(None)["reachMethod"] == "approx-star"
+    assert v({"reachMethod": "relax-star-area", "relaxFactor": 1})["relaxFactor"] == 1
+    with pytest.raises(NotImplementedError):
+        v({"reachMethod": "exact-star"})
+    with pytest.raises(NotImplementedError):
+        v({"reachMethod": "relax-star-range", "relaxFactor": 0.5})
+    with pytest.raises(TypeError, match="Wrong input set type"):
+        nn.NN([nn.ReluLayer()]).reach(np.zeros(3))
+
+
+def test_halfspace_and_lp_emptiness(kats):
+    H = nn.HalfSpace([[1.0, 0.0]], [0.5])
+    assert H.dim == 2
+    with pytest.raises(ValueError):
+        nn.HalfSpace(np.zeros((2, 2)), np.zeros(3))
+    # stored baseline of the reference's isEmptySet test
+    S = nn.Star(kats["empty_S_V"], kats["empty_S_C"], kats["empty_S_d"].ravel())
+    S1 = nn.Star(kats["empty_S1_V"], kats["empty_S1_C"], kats["empty_S1_d"].ravel())
+    assert S.isEmptySet() == bool(kats["empty_b_nonempty"][0, 0])
+    assert S1.isEmptySet() == bool(kats["empty_b_empty"][0, 0])
+
+
+def test_config_shapes():
+    for name in ("fc5", "cnn28", "cnn32", "bright28"):
+        cfg = make_config(name, n_queries=1, small=(name != "fc5"))
+        h, w, c = out_shape(cfg["layers"], cfg["in_shape"])
+        assert (h, w) == (1, 1) and c in (5, 10)
+    cfg = make_config("cnn28", n_queries=1)
+    fc = [l for l in cfg["layers"] if l["type"] == "fc"][0]
+    assert fc["W"].shape == (128, 2704)          # 13 x 13 x 16 after the stride-2 convolution
+    cfg = make_config("cnn32", n_queries=1)
+    fc = [l for l in cfg["layers"] if l["type"] == "fc"][0]
+    assert fc["W"].shape == (256, 4096)
