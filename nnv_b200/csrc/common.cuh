@@ -71,6 +71,7 @@ struct ConvWeights {
 struct ChanAffine {
     const double* mean;
     const double* den;      // sqrt(var + eps)
+    const double* rden;     // 1 / den, used where the affine is fused behind a contraction
     const double* scale;
     const double* offset;
 };

@@ -22,6 +22,7 @@
 #include "mma_f64.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 #include <vector>
 
 namespace nnvb {
@@ -45,12 +46,11 @@ struct ConvParams {
     int64_t col_groups;    // ceil(ncols / NJ)
 };
 
-template <int WM_TILES, int WN_TILES, int WARPS_M, int WARPS_N, int STAGES>
-__global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, 1)
+template <int WM_TILES, int WN_TILES, int WARPS_M, int WARPS_N, int STAGES, int MIN_BLOCKS>
+__global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MIN_BLOCKS)
 conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double* __restrict__ bias,
                 const ChanAffine bn, const double* __restrict__ Vin, int64_t ld_in,
                 double* __restrict__ Vout, int64_t ld_out, int64_t ncols, int64_t n_center) {
-    constexpr int BM = WARPS_M * WM_TILES * 16;
     constexpr int BN = WARPS_N * WN_TILES * 8;
     constexpr int THREADS = WARPS_M * WARPS_N * 32;
     constexpr int NWARPS = WARPS_M * WARPS_N;
@@ -58,7 +58,8 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
     extern __shared__ __align__(16) double smem[];
     double* halo = smem;                                  // [STAGES][halo_stage]
     double* wts = smem + STAGES * p.halo_stage;           // [STAGES][w_stage]
-    int* gtab = reinterpret_cast<int*>(wts + STAGES * p.w_stage);   // [plane]
+    double* chan = wts + STAGES * p.w_stage;              // [5][BN]: bias, mean, 1/den, scale, offset
+    int* gtab = reinterpret_cast<int*>(chan + 5 * BN);    // [plane]
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -94,6 +95,17 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
             off = int(jl * ld_in) + hi + H * wi;
         gtab[r] = off;
     }
+    // per-channel epilogue constants of this channel tile
+    const bool has_bn = bn.rden != nullptr;
+    for (int c = tid; c < BN; c += THREADS) {
+        const int co = n0 + c;
+        const bool ok = co < p.g.Cout;
+        chan[c] = ok ? bias[co] : 0.0;
+        chan[BN + c] = (ok && has_bn) ? bn.mean[co] : 0.0;
+        chan[2 * BN + c] = (ok && has_bn) ? bn.rden[co] : 1.0;
+        chan[3 * BN + c] = (ok && has_bn) ? bn.scale[co] : 1.0;
+        chan[4 * BN + c] = (ok && has_bn) ? bn.offset[co] : 0.0;
+    }
     __syncthreads();
 
     const double* in_base = Vin + j0 * ld_in;
@@ -120,7 +132,9 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
     };
 
     // shared-memory base of the rows this lane owns in each m16 tile
+    // and where its outputs go (relative to column j0, channel 0; -1 = nothing to store)
     int rowbase[WM_TILES][2];
+    int outoff[WM_TILES][2];
 #pragma unroll
     for (int mi = 0; mi < WM_TILES; ++mi) {
 #pragma unroll
@@ -131,6 +145,9 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
             int rem = m - jl * per_col;
             int owl = rem / p.TH;
             int ohl = rem - owl * p.TH;
+            const int oh = oh0 + ohl, ow = ow0 + owl;
+            const bool ok = jl < p.NJ && oh < p.g.Ho && ow < p.g.Wo && j0 + jl < ncols;
+            outoff[mi][half] = ok ? int(jl * ld_out) + oh + p.g.Ho * ow : -1;
             if (jl >= p.NJ) { jl = 0; owl = 0; ohl = 0; }   // padding rows read a valid address
             rowbase[mi][half] = jl * (p.HH * p.HW) + (owl * p.g.sw) * p.HH + ohl * p.g.sh;
         }
@@ -192,39 +209,32 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
     }
     cp_async_wait<0>();
 
-    // epilogue
-    const int Ho = p.g.Ho, Wo = p.g.Wo, Cout = p.g.Cout;
-    const int64_t hw_out = int64_t(Ho) * Wo;
+    // epilogue: bias on the centre columns, the fused per-channel affine
+    // ((x - mean) * (1/den)) * scale + offset in the reference's order, one
+    // 8-byte store per element (8 lanes cover 64 contiguous bytes along h)
+    const int64_t hw_out = int64_t(p.g.Ho) * p.g.Wo;
+    const int per_col = p.TH * p.TW;
+    double* out_base = Vout + j0 * ld_out;
 #pragma unroll
     for (int mi = 0; mi < WM_TILES; ++mi) {
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
+            const int off = outoff[mi][half];
+            if (off < 0) continue;
             const int m = wm * WM_TILES * 16 + mi * 16 + g + half * 8;
-            const int per_col = p.TH * p.TW;
-            const int jl = m / per_col;
-            const int rem = m - jl * per_col;
-            const int owl = rem / p.TH;
-            const int ohl = rem - owl * p.TH;
-            const int oh = oh0 + ohl, ow = ow0 + owl;
-            const int64_t j = j0 + jl;
-            if (jl >= p.NJ || oh >= Ho || ow >= Wo || j >= ncols) continue;
-            const bool is_center = j < n_center;
-            double* dst = Vout + j * ld_out + oh + int64_t(Ho) * ow;
+            const bool is_center = j0 + m / per_col < n_center;
+            double* dst = out_base + off;
 #pragma unroll
             for (int ni = 0; ni < WN_TILES; ++ni) {
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    const int co = n0 + wn * WN_TILES * 8 + ni * 8 + 2 * t + e;
-                    if (co >= Cout) continue;
+                    const int c = wn * WN_TILES * 8 + ni * 8 + 2 * t + e;
+                    if (n0 + c >= p.g.Cout) continue;
                     double v = acc[mi][ni][half * 2 + e];
-                    if (is_center) v += bias[co];
-                    if (bn.den != nullptr) {
-                        if (is_center) v = v - bn.mean[co];
-                        v = (v * 1.0) / bn.den[co];
-                        v = v * bn.scale[co];
-                        if (is_center) v = v + bn.offset[co];
-                    }
-                    dst[hw_out * co] = v;
+                    if (is_center) v = (v + chan[c]) - chan[BN + c];
+                    v = (v * chan[2 * BN + c]) * chan[3 * BN + c];
+                    if (is_center) v += chan[4 * BN + c];
+                    dst[hw_out * (n0 + c)] = v;
                 }
             }
         }
@@ -260,13 +270,23 @@ void pick_tile(const ConvGeom& g, int BM, int* TH, int* TW, int* NJ) {
     }
 }
 
+template <int WM_TILES, int WN_TILES, int WARPS_M, int WARPS_N, int STAGES, int MIN_BLOCKS>
+int launch_variant(cudaStream_t st, const ConvParams& p, dim3 grid, size_t smem, const ConvWeights& w,
+                   const ChanAffine& bn, const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
+                   int64_t ncols, int64_t n_center) {
+    auto kern = conv_f64_kernel<WM_TILES, WN_TILES, WARPS_M, WARPS_N, STAGES, MIN_BLOCKS>;
+    NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, WARPS_M * WARPS_N * 32, smem, st>>>(p, w.w, w.bias, bn, Vin, ld_in, Vout, ld_out, ncols, n_center);
+    NNVB_CUDA(cudaGetLastError());
+    return NNVB_OK;
+}
+
 template <int WM_TILES, int WN_TILES, int WARPS_M, int WARPS_N>
 int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
                const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out, int64_t ncols,
                int64_t n_center) {
     constexpr int BM = WARPS_M * WM_TILES * 16;
     constexpr int BN = WARPS_N * WN_TILES * 8;
-    constexpr int THREADS = WARPS_M * WARPS_N * 32;
     ConvParams p;
     p.g = g;
     pick_tile(g, BM, &p.TH, &p.TW, &p.NJ);
@@ -286,12 +306,12 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
         set_error("conv: weight arrangement (%d) does not match kernel tile (%d)", w.bn_tile, BN);
         return NNVB_E_ARG;
     }
-    if (int64_t(p.NJ) * ld_in >= (int64_t(1) << 31)) {
+    if (int64_t(p.NJ) * std::max(ld_in, ld_out) >= (int64_t(1) << 31)) {
         set_error("conv: column stride too large for the tile offset table");
         return NNVB_E_UNSUPPORTED;
     }
     const size_t stage_bytes = size_t(p.halo_stage + p.w_stage) * sizeof(double);
-    const size_t tab_bytes = size_t(p.plane) * sizeof(int);
+    const size_t fixed_bytes = size_t(5 * BN) * sizeof(double) + size_t(p.plane) * sizeof(int);
     const size_t limit = 227 * 1024;
     const int64_t blocks = p.col_groups * p.n_th * p.n_tw;
     if (blocks >= (int64_t(1) << 31)) {
@@ -299,23 +319,23 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
         return NNVB_E_UNSUPPORTED;
     }
     dim3 grid((unsigned)blocks, (unsigned)w.n_tiles);
-    if (3 * stage_bytes + tab_bytes <= limit) {
-        auto kern = conv_f64_kernel<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 3>;
-        const size_t smem = 3 * stage_bytes + tab_bytes;
-        NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<grid, THREADS, smem, st>>>(p, w.w, w.bias, bn, Vin, ld_in, Vout, ld_out, ncols, n_center);
-    } else if (2 * stage_bytes + tab_bytes <= limit) {
-        auto kern = conv_f64_kernel<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 2>;
-        const size_t smem = 2 * stage_bytes + tab_bytes;
-        NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<grid, THREADS, smem, st>>>(p, w.w, w.bias, bn, Vin, ld_in, Vout, ld_out, ncols, n_center);
-    } else {
-        set_error("conv: filter %dx%d with stride (%d,%d) needs %zu bytes of shared memory per stage",
-                  g.kh, g.kw, g.sh, g.sw, stage_bytes);
-        return NNVB_E_UNSUPPORTED;
-    }
-    NNVB_CUDA(cudaGetLastError());
-    return NNVB_OK;
+    // Two resident CTAs per SM (one runs its epilogue while the other contracts) when two
+    // double-buffered CTAs fit in shared memory; else one CTA with a 3- or 2-deep ring.
+    static const int variant = getenv("NNVB_CONV_VARIANT") ? atoi(getenv("NNVB_CONV_VARIANT")) : 0;
+    const size_t two = 2 * stage_bytes + fixed_bytes;
+    const size_t three = 3 * stage_bytes + fixed_bytes;
+    if ((variant == 0 || variant == 2) && 2 * (two + 1024) <= limit)
+        return launch_variant<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 2, 2>(st, p, grid, two, w, bn, Vin, ld_in, Vout,
+                                                                         ld_out, ncols, n_center);
+    if (three <= limit)
+        return launch_variant<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 3, 1>(st, p, grid, three, w, bn, Vin, ld_in, Vout,
+                                                                         ld_out, ncols, n_center);
+    if (two <= limit)
+        return launch_variant<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 2, 1>(st, p, grid, two, w, bn, Vin, ld_in, Vout,
+                                                                         ld_out, ncols, n_center);
+    set_error("conv: filter %dx%d with stride (%d,%d) needs %zu bytes of shared memory per stage", g.kh, g.kw, g.sh,
+              g.sw, stage_bytes);
+    return NNVB_E_UNSUPPORTED;
 }
 
 }  // namespace

@@ -84,6 +84,46 @@ struct PinnedBuf {
 
 using namespace nnvb;
 
+struct ReluLayerRecord {
+    int64_t N = 0;
+    int64_t K = 0;                       // new columns over the batch
+    int64_t n_dead = 0;
+    int64_t cols_after = 0;
+    std::vector<int64_t> new_off;        // [nq+1] host copy of the per-query scan
+    std::vector<int64_t> P_in;           // [nq] predicates entering the layer
+    DevBuf idx, q, c, l, u;              // per new column
+    DevBuf G, G_off;                     // crossing rows (keep_constraints)
+    std::vector<int64_t> h_G_off;
+    DevBuf lb, ub, rank, P_in_dev;       // [nq][N] bounds and crossing ranks, [nq] P_in (keep_layer_bounds)
+    bool has_G = false, has_bounds = false;
+    void release() {
+        idx.release(); q.release(); c.release(); l.release(); u.release();
+        G.release(); G_off.release(); lb.release(); ub.release(); rank.release(); P_in_dev.release();
+    }
+};
+
+// Working memory of a reach.  It belongs to the context: every batch of the
+// context reuses it, so a steady-state reach allocates nothing, and the results
+// of a batch stay readable until another batch of the same context is reached.
+struct WorkBufs {
+    DevBuf col_q, pl, pu, col_pos;
+    DevBuf qcol_off[2], qcol_idx[2];
+    DevBuf chunk_beg, chunk_end, q_chunk_off, partial;
+    DevBuf lb, ub, state, rank, blk_cross, q_cross, q_dead, q_new_off, gen_off;
+    DevBuf tmp;                          // gathers for downloads
+    DevBuf hs_G, hs_g, hs_q, hs_margin, hs_r, hs_roff, hs_val, hs_scale, wit[2];   // halfspace tests
+    std::vector<std::unique_ptr<ReluLayerRecord>> relu;
+    void release() {
+        DevBuf* bufs[] = {&col_q, &pl, &pu, &col_pos, &qcol_off[0], &qcol_off[1], &qcol_idx[0], &qcol_idx[1],
+                          &chunk_beg, &chunk_end, &q_chunk_off, &partial, &lb, &ub, &state, &rank, &blk_cross,
+                          &q_cross, &q_dead, &q_new_off, &gen_off, &tmp, &hs_G, &hs_g, &hs_q, &hs_margin, &hs_r,
+                          &hs_roff, &hs_val, &hs_scale, &wit[0], &wit[1]};
+        for (DevBuf* d : bufs) d->release();
+        for (auto& r : relu) r->release();
+        relu.clear();
+    }
+};
+
 struct nnvb_ctx {
     int device = 0;
     cudaStream_t stream = nullptr;
@@ -92,6 +132,8 @@ struct nnvb_ctx {
     int64_t launches = 0;
     PinnedBuf scratch;      // small host->device traffic of the layer loop
     size_t scratch_off = 0; // bytes of `scratch` handed out since the last stream sync
+    WorkBufs work;
+    const void* result_owner = nullptr;   // the batch whose results the work buffers and the arena hold
     // per-kernel-family device timing (off by default)
     bool prof_on = false;
     struct ProfRec { int fam; cudaEvent_t a, b; double work; };
@@ -118,6 +160,7 @@ struct Layer {
     // bn
     double* bn_mean = nullptr;
     double* bn_den = nullptr;
+    double* bn_rden = nullptr;
     double* bn_scale = nullptr;
     double* bn_offset = nullptr;
     bool fused_into_prev = false;      // bn applied in the previous conv's epilogue
@@ -131,24 +174,6 @@ struct nnvb_net {
     int64_t in_shape[3] = {0, 0, 0};
     int64_t out_shape[3] = {0, 0, 0};
     int n_relu = 0;
-};
-
-struct ReluLayerRecord {
-    int64_t N = 0;
-    int64_t K = 0;                       // new columns over the batch
-    int64_t n_dead = 0;
-    int64_t cols_after = 0;
-    std::vector<int64_t> new_off;        // [nq+1] host copy of the per-query scan
-    std::vector<int64_t> P_in;           // [nq] predicates entering the layer
-    DevBuf idx, q, c, l, u;              // per new column
-    DevBuf G, G_off;                     // crossing rows (keep_constraints)
-    std::vector<int64_t> h_G_off;
-    DevBuf lb, ub, rank, P_in_dev;       // [nq][N] bounds and crossing ranks, [nq] P_in (keep_layer_bounds)
-    bool has_G = false, has_bounds = false;
-    void release() {
-        idx.release(); q.release(); c.release(); l.release(); u.release();
-        G.release(); G_off.release(); lb.release(); ub.release(); rank.release(); P_in_dev.release();
-    }
 };
 
 struct nnvb_batch {
@@ -168,14 +193,9 @@ struct nnvb_batch {
     DevBuf d_in;                         // bounds or V
     DevBuf d_in_meta;                    // star form: pl, pu
     bool uploaded = false;
-    // working state
-    DevBuf col_q, pl, pu, col_pos;
-    DevBuf qcol_off[2], qcol_idx[2];
+    // working state: the buffers live in the context (one reach at a time per context)
+    WorkBufs* wk = nullptr;
     int list_cur = 0;
-    DevBuf chunk_beg, chunk_end, q_chunk_off, partial;
-    DevBuf lb, ub, state, rank, blk_cross, q_cross, q_dead, q_new_off, gen_off;
-    DevBuf tmp;                          // gathers for downloads
-    DevBuf hs_G, hs_g, hs_q, hs_margin, hs_r, hs_roff, hs_val, hs_scale, wit[2];   // halfspace tests
     std::vector<int64_t> h_qcol_off;     // [nq+1]
     int64_t ncols = 0;
     int64_t N = 0, ld = 0;
@@ -183,7 +203,6 @@ struct nnvb_batch {
     double* V = nullptr;                 // current generator matrix (device)
     bool reached = false;
     nnvb_opts opts{};
-    std::vector<std::unique_ptr<ReluLayerRecord>> relu;
     // final output ranges cache
     bool have_out_ranges = false;
 };
@@ -360,6 +379,7 @@ int nnvb_destroy(nnvb_ctx* ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     ctx->scratch.release();
+    ctx->work.release();
     prof_drain(ctx);
     for (cudaEvent_t e : ctx->prof_pool) cudaEventDestroy(e);
     if (ctx->arena) cudaFree(ctx->arena);
@@ -497,6 +517,9 @@ int nnvb_net_create(nnvb_ctx* ctx, const nnvb_layer_desc* layers, int n_layers, 
                 for (int64_t c = 0; c < nch; ++c) den[c] = std::sqrt(d.bn_var[c] + d.bn_eps);
                 int s = upload_vec(net.get(), mean, &L.bn_mean);
                 if (!s) s = upload_vec(net.get(), den, &L.bn_den);
+                std::vector<double> rden(nch);
+                for (int64_t c = 0; c < nch; ++c) rden[c] = 1.0 / den[c];
+                if (!s) s = upload_vec(net.get(), rden, &L.bn_rden);
                 if (!s) s = upload_vec(net.get(), scale, &L.bn_scale);
                 if (!s) s = upload_vec(net.get(), offset, &L.bn_offset);
                 if (s) return fail(s);
@@ -577,6 +600,7 @@ int nnvb_batch_create(nnvb_net* net, int n_queries, nnvb_batch** out) {
     b->h_V.resize(n_queries);
     b->m0.assign(n_queries, 0);
     b->box_implies_C.assign(n_queries, 1);
+    b->wk = &net->ctx->work;
     *out = b;
     return NNVB_OK;
 }
@@ -587,13 +611,9 @@ int nnvb_batch_destroy(nnvb_batch* b) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     b->h_in.release();
-    DevBuf* bufs[] = {&b->d_in, &b->d_in_meta, &b->col_q, &b->pl, &b->pu, &b->col_pos, &b->qcol_off[0],
-                      &b->qcol_off[1], &b->qcol_idx[0], &b->qcol_idx[1], &b->chunk_beg, &b->chunk_end,
-                      &b->q_chunk_off, &b->partial, &b->lb, &b->ub, &b->state, &b->rank, &b->blk_cross,
-                      &b->q_cross, &b->q_dead, &b->q_new_off, &b->gen_off, &b->tmp, &b->hs_G, &b->hs_g, &b->hs_q,
-                      &b->hs_margin, &b->hs_r, &b->hs_roff, &b->hs_val, &b->hs_scale, &b->wit[0], &b->wit[1]};
-    for (DevBuf* d : bufs) d->release();
-    for (auto& r : b->relu) r->release();
+    b->d_in.release();
+    b->d_in_meta.release();
+    if (ctx->result_owner == b) ctx->result_owner = nullptr;
     delete b;
     return NNVB_OK;
 }
@@ -721,13 +741,13 @@ namespace {
 
 int ensure_col_meta(nnvb_batch* b, int64_t cols) {
     cudaStream_t st = b->net->ctx->stream;
-    NNVB_TRY(b->col_q.ensure(size_t(cols) * sizeof(int32_t), st, true));
-    NNVB_TRY(b->pl.ensure(size_t(cols) * sizeof(double), st, true));
-    NNVB_TRY(b->pu.ensure(size_t(cols) * sizeof(double), st, true));
-    NNVB_TRY(b->col_pos.ensure(size_t(cols) * sizeof(int64_t), st, true));
+    NNVB_TRY(b->wk->col_q.ensure(size_t(cols) * sizeof(int32_t), st, true));
+    NNVB_TRY(b->wk->pl.ensure(size_t(cols) * sizeof(double), st, true));
+    NNVB_TRY(b->wk->pu.ensure(size_t(cols) * sizeof(double), st, true));
+    NNVB_TRY(b->wk->col_pos.ensure(size_t(cols) * sizeof(int64_t), st, true));
     for (int i = 0; i < 2; ++i) {
-        NNVB_TRY(b->qcol_idx[i].ensure(size_t(cols) * sizeof(int32_t), st, true));
-        NNVB_TRY(b->qcol_off[i].ensure(size_t(b->nq + 1) * sizeof(int64_t), st, true));
+        NNVB_TRY(b->wk->qcol_idx[i].ensure(size_t(cols) * sizeof(int32_t), st, true));
+        NNVB_TRY(b->wk->qcol_off[i].ensure(size_t(b->nq + 1) * sizeof(int64_t), st, true));
     }
     return NNVB_OK;
 }
@@ -750,17 +770,17 @@ int init_sets(nnvb_batch* b) {
     NNVB_REQUIRE(ncols < (int64_t(1) << 31), "batch has too many generator columns (%lld)", (long long)ncols);
     NNVB_TRY(ensure_col_meta(b, ncols));
     b->list_cur = 0;
-    NNVB_TRY(h2d_small(ctx, b->qcol_off[0].p, b->h_qcol_off.data(), sizeof(int64_t) * (nq + 1)));
+    NNVB_TRY(h2d_small(ctx, b->wk->qcol_off[0].p, b->h_qcol_off.data(), sizeof(int64_t) * (nq + 1)));
     if (b->kind == 1) {
         const size_t need = size_t(ld) * ncols * sizeof(double);
         if (need > ctx->vbuf_bytes()) return capacity_error("input set", need, ctx->vbuf_bytes());
-        NNVB_TRY(b->gen_off.ensure(sizeof(int64_t) * (nq + 1), st));
-        NNVB_TRY(h2d_small(ctx, b->gen_off.p, gen_off.data(), sizeof(int64_t) * (nq + 1)));
+        NNVB_TRY(b->wk->gen_off.ensure(sizeof(int64_t) * (nq + 1), st));
+        NNVB_TRY(h2d_small(ctx, b->wk->gen_off.p, gen_off.data(), sizeof(int64_t) * (nq + 1)));
         double* V = ctx->vbuf(0);
         NNVB_CUDA(cudaMemsetAsync(V, 0, need, st));
-        NNVB_TRY(launch_build_from_bounds(st, nq, N, ld, b->d_in.as<double>(), b->gen_off.as<int64_t>(), V,
-                                          b->col_q.as<int32_t>(), b->pl.as<double>(), b->pu.as<double>(),
-                                          b->qcol_idx[0].as<int32_t>(), b->col_pos.as<int64_t>(), &ctx->launches));
+        NNVB_TRY(launch_build_from_bounds(st, nq, N, ld, b->d_in.as<double>(), b->wk->gen_off.as<int64_t>(), V,
+                                          b->wk->col_q.as<int32_t>(), b->wk->pl.as<double>(), b->wk->pu.as<double>(),
+                                          b->wk->qcol_idx[0].as<int32_t>(), b->wk->col_pos.as<int64_t>(), &ctx->launches));
         b->V = V;
     } else {
         // metadata is a pure function of the staged queries
@@ -775,11 +795,11 @@ int init_sets(nnvb_batch* b) {
                 list[col - nq] = int32_t(col);
             }
         }
-        NNVB_TRY(h2d_small(ctx, b->col_q.p, col_q.data(), sizeof(int32_t) * ncols));
-        NNVB_TRY(h2d_small(ctx, b->col_pos.p, col_pos.data(), sizeof(int64_t) * ncols));
-        NNVB_TRY(h2d_small(ctx, b->qcol_idx[0].p, list.data(), sizeof(int32_t) * (ncols - nq)));
-        NNVB_CUDA(cudaMemcpyAsync(b->pl.p, b->d_in_meta.p, sizeof(double) * ncols, cudaMemcpyDeviceToDevice, st));
-        NNVB_CUDA(cudaMemcpyAsync(b->pu.p, b->d_in_meta.as<double>() + ncols, sizeof(double) * ncols,
+        NNVB_TRY(h2d_small(ctx, b->wk->col_q.p, col_q.data(), sizeof(int32_t) * ncols));
+        NNVB_TRY(h2d_small(ctx, b->wk->col_pos.p, col_pos.data(), sizeof(int64_t) * ncols));
+        NNVB_TRY(h2d_small(ctx, b->wk->qcol_idx[0].p, list.data(), sizeof(int32_t) * (ncols - nq)));
+        NNVB_CUDA(cudaMemcpyAsync(b->wk->pl.p, b->d_in_meta.p, sizeof(double) * ncols, cudaMemcpyDeviceToDevice, st));
+        NNVB_CUDA(cudaMemcpyAsync(b->wk->pu.p, b->d_in_meta.as<double>() + ncols, sizeof(double) * ncols,
                                   cudaMemcpyDeviceToDevice, st));
         b->V = b->d_in.as<double>();      // read-only; in-place layers copy it first
     }
@@ -833,42 +853,42 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec) {
     }
     qoff[nq] = (int32_t)cbeg.size();
     const int n_chunks = (int)cbeg.size();
-    NNVB_TRY(b->chunk_beg.ensure(sizeof(int64_t) * std::max(n_chunks, 1), st));
-    NNVB_TRY(b->chunk_end.ensure(sizeof(int64_t) * std::max(n_chunks, 1), st));
-    NNVB_TRY(b->q_chunk_off.ensure(sizeof(int32_t) * (nq + 1), st));
-    NNVB_TRY(b->partial.ensure(sizeof(double) * 2 * N * std::max(n_chunks, 1), st));
-    NNVB_TRY(h2d_small(ctx, b->chunk_beg.p, cbeg.data(), sizeof(int64_t) * n_chunks));
-    NNVB_TRY(h2d_small(ctx, b->chunk_end.p, cend.data(), sizeof(int64_t) * n_chunks));
-    NNVB_TRY(h2d_small(ctx, b->q_chunk_off.p, qoff.data(), sizeof(int32_t) * (nq + 1)));
+    NNVB_TRY(b->wk->chunk_beg.ensure(sizeof(int64_t) * std::max(n_chunks, 1), st));
+    NNVB_TRY(b->wk->chunk_end.ensure(sizeof(int64_t) * std::max(n_chunks, 1), st));
+    NNVB_TRY(b->wk->q_chunk_off.ensure(sizeof(int32_t) * (nq + 1), st));
+    NNVB_TRY(b->wk->partial.ensure(sizeof(double) * 2 * N * std::max(n_chunks, 1), st));
+    NNVB_TRY(h2d_small(ctx, b->wk->chunk_beg.p, cbeg.data(), sizeof(int64_t) * n_chunks));
+    NNVB_TRY(h2d_small(ctx, b->wk->chunk_end.p, cend.data(), sizeof(int64_t) * n_chunks));
+    NNVB_TRY(h2d_small(ctx, b->wk->q_chunk_off.p, qoff.data(), sizeof(int32_t) * (nq + 1)));
 
     const int nblk = relu_blocks_per_query(N);
-    DevBuf& lbbuf = b->opts.keep_layer_bounds ? rec->lb : b->lb;
-    DevBuf& ubbuf = b->opts.keep_layer_bounds ? rec->ub : b->ub;
+    DevBuf& lbbuf = b->opts.keep_layer_bounds ? rec->lb : b->wk->lb;
+    DevBuf& ubbuf = b->opts.keep_layer_bounds ? rec->ub : b->wk->ub;
     NNVB_TRY(lbbuf.ensure(sizeof(double) * nq * N, st));
     NNVB_TRY(ubbuf.ensure(sizeof(double) * nq * N, st));
     rec->has_bounds = b->opts.keep_layer_bounds != 0;
-    NNVB_TRY(b->state.ensure(size_t(nq) * N, st));
-    DevBuf& rankbuf = b->opts.keep_layer_bounds ? rec->rank : b->rank;
+    NNVB_TRY(b->wk->state.ensure(size_t(nq) * N, st));
+    DevBuf& rankbuf = b->opts.keep_layer_bounds ? rec->rank : b->wk->rank;
     NNVB_TRY(rankbuf.ensure(sizeof(int32_t) * nq * N, st));
-    NNVB_TRY(b->blk_cross.ensure(sizeof(int32_t) * nq * nblk, st));
-    NNVB_TRY(b->q_cross.ensure(sizeof(int64_t) * nq, st));
-    NNVB_TRY(b->q_dead.ensure(sizeof(int64_t) * nq, st));
-    NNVB_TRY(b->q_new_off.ensure(sizeof(int64_t) * (nq + 1), st));
+    NNVB_TRY(b->wk->blk_cross.ensure(sizeof(int32_t) * nq * nblk, st));
+    NNVB_TRY(b->wk->q_cross.ensure(sizeof(int64_t) * nq, st));
+    NNVB_TRY(b->wk->q_dead.ensure(sizeof(int64_t) * nq, st));
+    NNVB_TRY(b->wk->q_new_off.ensure(sizeof(int64_t) * (nq + 1), st));
 
     ReluWork w{};
     w.nq = nq; w.N = N; w.ld = ld; w.V = b->V;
-    w.qcol_off = b->qcol_off[b->list_cur].as<int64_t>();
-    w.qcol_idx = b->qcol_idx[b->list_cur].as<int32_t>();
-    w.pl = b->pl.as<double>(); w.pu = b->pu.as<double>();
+    w.qcol_off = b->wk->qcol_off[b->list_cur].as<int64_t>();
+    w.qcol_idx = b->wk->qcol_idx[b->list_cur].as<int32_t>();
+    w.pl = b->wk->pl.as<double>(); w.pu = b->wk->pu.as<double>();
     w.n_chunks = n_chunks;
-    w.chunk_beg = b->chunk_beg.as<int64_t>(); w.chunk_end = b->chunk_end.as<int64_t>();
-    w.q_chunk_off = b->q_chunk_off.as<int32_t>();
-    w.partial = b->partial.as<double>();
+    w.chunk_beg = b->wk->chunk_beg.as<int64_t>(); w.chunk_end = b->wk->chunk_end.as<int64_t>();
+    w.q_chunk_off = b->wk->q_chunk_off.as<int32_t>();
+    w.partial = b->wk->partial.as<double>();
     w.lb = lbbuf.as<double>(); w.ub = ubbuf.as<double>();
-    w.state = b->state.as<uint8_t>(); w.rank = rankbuf.as<int32_t>();
-    w.blk_cross = b->blk_cross.as<int32_t>();
-    w.q_cross = b->q_cross.as<int64_t>(); w.q_dead = b->q_dead.as<int64_t>();
-    w.q_new_off = b->q_new_off.as<int64_t>();
+    w.state = b->wk->state.as<uint8_t>(); w.rank = rankbuf.as<int32_t>();
+    w.blk_cross = b->wk->blk_cross.as<int32_t>();
+    w.q_cross = b->wk->q_cross.as<int64_t>(); w.q_dead = b->wk->q_dead.as<int64_t>();
+    w.q_new_off = b->wk->q_new_off.as<int64_t>();
 
     {
         // Star.estimateRanges: V read once, predicate bounds, lb/ub written
@@ -904,9 +924,9 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec) {
     }
     NNVB_TRY(ensure_col_meta(b, ncols_old + K));
     // pointers may have moved
-    w.qcol_off = b->qcol_off[b->list_cur].as<int64_t>();
-    w.qcol_idx = b->qcol_idx[b->list_cur].as<int32_t>();
-    w.pl = b->pl.as<double>(); w.pu = b->pu.as<double>();
+    w.qcol_off = b->wk->qcol_off[b->list_cur].as<int64_t>();
+    w.qcol_idx = b->wk->qcol_idx[b->list_cur].as<int32_t>();
+    w.pl = b->wk->pl.as<double>(); w.pu = b->wk->pu.as<double>();
 
     const size_t kk = size_t(std::max<int64_t>(K, 1));
     NNVB_TRY(rec->idx.ensure(sizeof(int32_t) * kk, st));
@@ -939,11 +959,11 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec) {
         ProfScope ps(ctx, NNVB_PROF_RELAX, relax_bytes);
         if (K > 0) NNVB_TRY(launch_rank_cross(st, w, r, &ctx->launches));
         if (K > 0 || rec->n_dead > 0)
-            NNVB_TRY(launch_relu_zero_rows(st, w, ncols_old, b->col_q.as<int32_t>(), r, b->col_pos.as<int64_t>(),
+            NNVB_TRY(launch_relu_zero_rows(st, w, ncols_old, b->wk->col_q.as<int32_t>(), r, b->wk->col_pos.as<int64_t>(),
                                            &ctx->launches));
-        NNVB_TRY(launch_relu_append(st, w, ncols_old, K, r, b->col_q.as<int32_t>(), b->pl.as<double>(),
-                                    b->pu.as<double>(), b->col_pos.as<int64_t>(), b->qcol_off[nxt].as<int64_t>(),
-                                    b->qcol_idx[nxt].as<int32_t>(), &ctx->launches));
+        NNVB_TRY(launch_relu_append(st, w, ncols_old, K, r, b->wk->col_q.as<int32_t>(), b->wk->pl.as<double>(),
+                                    b->wk->pu.as<double>(), b->wk->col_pos.as<int64_t>(), b->wk->qcol_off[nxt].as<int64_t>(),
+                                    b->wk->qcol_idx[nxt].as<int32_t>(), &ctx->launches));
     }
     b->list_cur = nxt;
     for (int q = 0; q <= nq; ++q) b->h_qcol_off[q] += rec->new_off[q];
@@ -966,10 +986,10 @@ int run_layers(nnvb_batch* b) {
             if (need > ctx->vbuf_bytes()) return capacity_error("layer output", need, ctx->vbuf_bytes());
             double* out = other_vbuf(b);
             if (L.type == NNVB_LAYER_CONV2D) {
-                ChanAffine bn{nullptr, nullptr, nullptr, nullptr};
+                ChanAffine bn{nullptr, nullptr, nullptr, nullptr, nullptr};
                 if (L.fused_bn >= 0) {
                     const Layer& B = net->layers[L.fused_bn];
-                    bn = ChanAffine{B.bn_mean, B.bn_den, B.bn_scale, B.bn_offset};
+                    bn = ChanAffine{B.bn_mean, B.bn_den, B.bn_rden, B.bn_scale, B.bn_offset};
                 }
                 ProfScope ps(ctx, NNVB_PROF_CONV, 2.0 * L.cg.Ho * L.cg.Wo * L.cg.Cout * L.cg.kh * L.cg.kw * L.cg.Cin * double(b->ncols));
                 NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, b->V, b->ld, out, ld_out, b->ncols, b->nq,
@@ -988,12 +1008,12 @@ int run_layers(nnvb_batch* b) {
         } else if (L.type == NNVB_LAYER_BN) {
             if (!L.fused_into_prev) {
                 NNVB_TRY(make_writable(b, 0));
-                ChanAffine bn{L.bn_mean, L.bn_den, L.bn_scale, L.bn_offset};
+                ChanAffine bn{L.bn_mean, L.bn_den, L.bn_rden, L.bn_scale, L.bn_offset};
                 ProfScope ps(ctx, NNVB_PROF_BN, 16.0 * double(b->N) * double(b->ncols));
                 NNVB_TRY(launch_bn_f64(st, bn, L.H * L.W, b->N, b->V, b->ld, b->ncols, b->nq, &ctx->launches));
             }
         } else if (L.type == NNVB_LAYER_RELU) {
-            NNVB_TRY(relu_step(b, b->relu[relu_i].get()));
+            NNVB_TRY(relu_step(b, b->wk->relu[relu_i].get()));
             ++relu_i;
         }
         b->shape[0] = L.Ho; b->shape[1] = L.Wo; b->shape[2] = L.Co;
@@ -1004,11 +1024,15 @@ int run_layers(nnvb_batch* b) {
 int check_reached(const nnvb_batch* b, int q) {
     if (!b) { set_error("NULL batch"); return NNVB_E_ARG; }
     if (!b->reached) { set_error("results requested before nnvb_batch_reach succeeded"); return NNVB_E_STATE; }
+    if (b->net->ctx->result_owner != b) {
+        set_error("the results of this batch were overwritten by a later reach on the same context");
+        return NNVB_E_STATE;
+    }
     if (q < 0 || q >= b->nq) { set_error("query %d out of range", q); return NNVB_E_ARG; }
     return NNVB_OK;
 }
 
-// Star.estimateRanges of the current set into b->lb / b->ub (no classification side effects kept)
+// Star.estimateRanges of the current set into b->wk->lb / b->wk->ub (no classification side effects kept)
 int output_ranges(nnvb_batch* b) {
     if (b->have_out_ranges) return NNVB_OK;
     nnvb_ctx* ctx = b->net->ctx;
@@ -1019,35 +1043,35 @@ int output_ranges(nnvb_batch* b) {
     std::vector<int32_t> qoff(nq + 1);
     for (int q = 0; q < nq; ++q) { cbeg[q] = b->h_qcol_off[q]; cend[q] = b->h_qcol_off[q + 1]; qoff[q] = q; }
     qoff[nq] = nq;
-    NNVB_TRY(b->chunk_beg.ensure(sizeof(int64_t) * nq, st));
-    NNVB_TRY(b->chunk_end.ensure(sizeof(int64_t) * nq, st));
-    NNVB_TRY(b->q_chunk_off.ensure(sizeof(int32_t) * (nq + 1), st));
-    NNVB_TRY(b->partial.ensure(sizeof(double) * 2 * N * nq, st));
-    NNVB_TRY(h2d_small(ctx, b->chunk_beg.p, cbeg.data(), sizeof(int64_t) * nq));
-    NNVB_TRY(h2d_small(ctx, b->chunk_end.p, cend.data(), sizeof(int64_t) * nq));
-    NNVB_TRY(h2d_small(ctx, b->q_chunk_off.p, qoff.data(), sizeof(int32_t) * (nq + 1)));
+    NNVB_TRY(b->wk->chunk_beg.ensure(sizeof(int64_t) * nq, st));
+    NNVB_TRY(b->wk->chunk_end.ensure(sizeof(int64_t) * nq, st));
+    NNVB_TRY(b->wk->q_chunk_off.ensure(sizeof(int32_t) * (nq + 1), st));
+    NNVB_TRY(b->wk->partial.ensure(sizeof(double) * 2 * N * nq, st));
+    NNVB_TRY(h2d_small(ctx, b->wk->chunk_beg.p, cbeg.data(), sizeof(int64_t) * nq));
+    NNVB_TRY(h2d_small(ctx, b->wk->chunk_end.p, cend.data(), sizeof(int64_t) * nq));
+    NNVB_TRY(h2d_small(ctx, b->wk->q_chunk_off.p, qoff.data(), sizeof(int32_t) * (nq + 1)));
     const int nblk = relu_blocks_per_query(N);
-    NNVB_TRY(b->lb.ensure(sizeof(double) * nq * N, st));
-    NNVB_TRY(b->ub.ensure(sizeof(double) * nq * N, st));
-    NNVB_TRY(b->state.ensure(size_t(nq) * N, st));
-    NNVB_TRY(b->blk_cross.ensure(sizeof(int32_t) * nq * nblk, st));
-    NNVB_TRY(b->q_cross.ensure(sizeof(int64_t) * nq, st));
-    NNVB_TRY(b->q_dead.ensure(sizeof(int64_t) * nq, st));
-    NNVB_TRY(b->q_new_off.ensure(sizeof(int64_t) * (nq + 1), st));
+    NNVB_TRY(b->wk->lb.ensure(sizeof(double) * nq * N, st));
+    NNVB_TRY(b->wk->ub.ensure(sizeof(double) * nq * N, st));
+    NNVB_TRY(b->wk->state.ensure(size_t(nq) * N, st));
+    NNVB_TRY(b->wk->blk_cross.ensure(sizeof(int32_t) * nq * nblk, st));
+    NNVB_TRY(b->wk->q_cross.ensure(sizeof(int64_t) * nq, st));
+    NNVB_TRY(b->wk->q_dead.ensure(sizeof(int64_t) * nq, st));
+    NNVB_TRY(b->wk->q_new_off.ensure(sizeof(int64_t) * (nq + 1), st));
     ReluWork w{};
     w.nq = nq; w.N = N; w.ld = b->ld; w.V = b->V;
-    w.qcol_off = b->qcol_off[b->list_cur].as<int64_t>();
-    w.qcol_idx = b->qcol_idx[b->list_cur].as<int32_t>();
-    w.pl = b->pl.as<double>(); w.pu = b->pu.as<double>();
+    w.qcol_off = b->wk->qcol_off[b->list_cur].as<int64_t>();
+    w.qcol_idx = b->wk->qcol_idx[b->list_cur].as<int32_t>();
+    w.pl = b->wk->pl.as<double>(); w.pu = b->wk->pu.as<double>();
     w.n_chunks = nq;
-    w.chunk_beg = b->chunk_beg.as<int64_t>(); w.chunk_end = b->chunk_end.as<int64_t>();
-    w.q_chunk_off = b->q_chunk_off.as<int32_t>();
-    w.partial = b->partial.as<double>();
-    w.lb = b->lb.as<double>(); w.ub = b->ub.as<double>();
-    w.state = b->state.as<uint8_t>();
-    w.blk_cross = b->blk_cross.as<int32_t>();
-    w.q_cross = b->q_cross.as<int64_t>(); w.q_dead = b->q_dead.as<int64_t>();
-    w.q_new_off = b->q_new_off.as<int64_t>();
+    w.chunk_beg = b->wk->chunk_beg.as<int64_t>(); w.chunk_end = b->wk->chunk_end.as<int64_t>();
+    w.q_chunk_off = b->wk->q_chunk_off.as<int32_t>();
+    w.partial = b->wk->partial.as<double>();
+    w.lb = b->wk->lb.as<double>(); w.ub = b->wk->ub.as<double>();
+    w.state = b->wk->state.as<uint8_t>();
+    w.blk_cross = b->wk->blk_cross.as<int32_t>();
+    w.q_cross = b->wk->q_cross.as<int64_t>(); w.q_dead = b->wk->q_dead.as<int64_t>();
+    w.q_new_off = b->wk->q_new_off.as<int64_t>();
     NNVB_TRY(launch_estimate_ranges(st, w, &ctx->launches));
     NNVB_TRY(launch_classify_scan(st, w, &ctx->launches));
     b->have_out_ranges = true;
@@ -1060,8 +1084,8 @@ int witness_forward(nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, i
     nnvb_net* net = b->net;
     nnvb_ctx* ctx = net->ctx;
     cudaStream_t st = ctx->stream;
-    double* cur = b->wit[0].as<double>();
-    double* oth = b->wit[1].as<double>();
+    double* cur = b->wk->wit[0].as<double>();
+    double* oth = b->wk->wit[1].as<double>();
     int64_t N = b->N0, ld = b->ld0;
     int relu_i = 0;
     for (size_t li = 0; li < net->layers.size(); ++li) {
@@ -1069,10 +1093,10 @@ int witness_forward(nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, i
         const int64_t Nout = L.Ho * L.Wo * L.Co;
         const int64_t ld_out = lead_dim(Nout);
         if (L.type == NNVB_LAYER_CONV2D) {
-            ChanAffine bn{nullptr, nullptr, nullptr, nullptr};
+            ChanAffine bn{nullptr, nullptr, nullptr, nullptr, nullptr};
             if (L.fused_bn >= 0) {
                 const Layer& B = net->layers[L.fused_bn];
-                bn = ChanAffine{B.bn_mean, B.bn_den, B.bn_scale, B.bn_offset};
+                bn = ChanAffine{B.bn_mean, B.bn_den, B.bn_rden, B.bn_scale, B.bn_offset};
             }
             NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, cur, ld, oth, ld_out, n, n, &ctx->launches));
             std::swap(cur, oth); N = Nout; ld = ld_out;
@@ -1085,11 +1109,11 @@ int witness_forward(nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, i
             std::swap(cur, oth); N = Nout; ld = ld_out;
         } else if (L.type == NNVB_LAYER_BN) {
             if (!L.fused_into_prev) {
-                ChanAffine bn{L.bn_mean, L.bn_den, L.bn_scale, L.bn_offset};
+                ChanAffine bn{L.bn_mean, L.bn_den, L.bn_rden, L.bn_scale, L.bn_offset};
                 NNVB_TRY(launch_bn_f64(st, bn, L.H * L.W, N, cur, ld, n, n, &ctx->launches));
             }
         } else if (L.type == NNVB_LAYER_RELU) {
-            ReluLayerRecord& r = *b->relu[relu_i++];
+            ReluLayerRecord& r = *b->wk->relu[relu_i++];
             NNVB_TRY(launch_witness_relu(st, n, d_pair_q, N, ld, cur, r.lb.as<double>(), r.ub.as<double>(),
                                          r.rank.as<int32_t>(), r.P_in_dev.as<int64_t>(), d_r, d_roff, &ctx->launches));
         }
@@ -1112,19 +1136,19 @@ int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vec
     status.assign(n, NNVB_UNDECIDED);
     if (n == 0) return NNVB_OK;
     ProfScope ps(ctx, NNVB_PROF_VERIFY, 0.0);
-    NNVB_TRY(b->hs_G.ensure(sizeof(double) * n * Nout, st));
-    NNVB_TRY(b->hs_g.ensure(sizeof(double) * n, st));
-    NNVB_TRY(b->hs_q.ensure(sizeof(int32_t) * n, st));
-    NNVB_TRY(b->hs_margin.ensure(sizeof(double) * n, st));
-    NNVB_CUDA(cudaMemcpyAsync(b->hs_G.p, G.data(), sizeof(double) * n * Nout, cudaMemcpyHostToDevice, st));
-    NNVB_CUDA(cudaMemcpyAsync(b->hs_g.p, g.data(), sizeof(double) * n, cudaMemcpyHostToDevice, st));
-    NNVB_CUDA(cudaMemcpyAsync(b->hs_q.p, pair_q.data(), sizeof(int32_t) * n, cudaMemcpyHostToDevice, st));
-    const int64_t* qoff = b->qcol_off[b->list_cur].as<int64_t>();
-    const int32_t* qidx = b->qcol_idx[b->list_cur].as<int32_t>();
-    NNVB_TRY(launch_halfspace_pairs(st, n, b->hs_q.as<int32_t>(), Nout, b->ld, b->V, qoff, qidx, b->pl.as<double>(),
-                                    b->pu.as<double>(), b->hs_G.as<double>(), b->hs_g.as<double>(),
-                                    b->hs_margin.as<double>(), nullptr, nullptr, &ctx->launches));
-    NNVB_CUDA(cudaMemcpyAsync(margin.data(), b->hs_margin.p, sizeof(double) * n, cudaMemcpyDeviceToHost, st));
+    NNVB_TRY(b->wk->hs_G.ensure(sizeof(double) * n * Nout, st));
+    NNVB_TRY(b->wk->hs_g.ensure(sizeof(double) * n, st));
+    NNVB_TRY(b->wk->hs_q.ensure(sizeof(int32_t) * n, st));
+    NNVB_TRY(b->wk->hs_margin.ensure(sizeof(double) * n, st));
+    NNVB_CUDA(cudaMemcpyAsync(b->wk->hs_G.p, G.data(), sizeof(double) * n * Nout, cudaMemcpyHostToDevice, st));
+    NNVB_CUDA(cudaMemcpyAsync(b->wk->hs_g.p, g.data(), sizeof(double) * n, cudaMemcpyHostToDevice, st));
+    NNVB_CUDA(cudaMemcpyAsync(b->wk->hs_q.p, pair_q.data(), sizeof(int32_t) * n, cudaMemcpyHostToDevice, st));
+    const int64_t* qoff = b->wk->qcol_off[b->list_cur].as<int64_t>();
+    const int32_t* qidx = b->wk->qcol_idx[b->list_cur].as<int32_t>();
+    NNVB_TRY(launch_halfspace_pairs(st, n, b->wk->hs_q.as<int32_t>(), Nout, b->ld, b->V, qoff, qidx, b->wk->pl.as<double>(),
+                                    b->wk->pu.as<double>(), b->wk->hs_G.as<double>(), b->wk->hs_g.as<double>(),
+                                    b->wk->hs_margin.as<double>(), nullptr, nullptr, &ctx->launches));
+    NNVB_CUDA(cudaMemcpyAsync(margin.data(), b->wk->hs_margin.p, sizeof(double) * n, cudaMemcpyDeviceToHost, st));
     NNVB_TRY(sync(ctx));
     std::vector<int> open;
     for (int p = 0; p < n; ++p) {
@@ -1132,7 +1156,7 @@ int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vec
         else if (b->box_implies_C[pair_q[p]]) open.push_back(p);
     }
     bool have_bounds = true;
-    for (int i = 0; i < b->net->n_relu; ++i) have_bounds = have_bounds && b->relu[i]->has_bounds;
+    for (int i = 0; i < b->net->n_relu; ++i) have_bounds = have_bounds && b->wk->relu[i]->has_bounds;
     if (open.empty() || !have_bounds) return NNVB_OK;
 
     // witness points for the open pairs, in chunks that bound the scratch memory
@@ -1151,43 +1175,43 @@ int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vec
             std::copy(G.begin() + size_t(p) * Nout, G.begin() + size_t(p + 1) * Nout, Gc.begin() + size_t(i) * Nout);
             roff[i + 1] = roff[i] + (b->h_qcol_off[pq[i] + 1] - b->h_qcol_off[pq[i]]);
         }
-        NNVB_TRY(b->hs_r.ensure(sizeof(double) * std::max<int64_t>(roff[m], 1), st));
-        NNVB_TRY(b->hs_roff.ensure(sizeof(int64_t) * (m + 1), st));
-        NNVB_TRY(b->hs_val.ensure(sizeof(double) * m, st));
-        NNVB_TRY(b->hs_scale.ensure(sizeof(double) * m, st));
-        NNVB_TRY(b->wit[0].ensure(sizeof(double) * max_ld * m, st));
-        NNVB_TRY(b->wit[1].ensure(sizeof(double) * max_ld * m, st));
-        NNVB_CUDA(cudaMemcpyAsync(b->hs_G.p, Gc.data(), sizeof(double) * m * Nout, cudaMemcpyHostToDevice, st));
-        NNVB_CUDA(cudaMemcpyAsync(b->hs_g.p, gc.data(), sizeof(double) * m, cudaMemcpyHostToDevice, st));
-        NNVB_CUDA(cudaMemcpyAsync(b->hs_q.p, pq.data(), sizeof(int32_t) * m, cudaMemcpyHostToDevice, st));
-        NNVB_CUDA(cudaMemcpyAsync(b->hs_roff.p, roff.data(), sizeof(int64_t) * (m + 1), cudaMemcpyHostToDevice, st));
-        NNVB_TRY(launch_halfspace_pairs(st, m, b->hs_q.as<int32_t>(), Nout, b->ld, b->V, qoff, qidx, b->pl.as<double>(),
-                                        b->pu.as<double>(), b->hs_G.as<double>(), b->hs_g.as<double>(), nullptr,
-                                        b->hs_r.as<double>(), b->hs_roff.as<int64_t>(), &ctx->launches));
+        NNVB_TRY(b->wk->hs_r.ensure(sizeof(double) * std::max<int64_t>(roff[m], 1), st));
+        NNVB_TRY(b->wk->hs_roff.ensure(sizeof(int64_t) * (m + 1), st));
+        NNVB_TRY(b->wk->hs_val.ensure(sizeof(double) * m, st));
+        NNVB_TRY(b->wk->hs_scale.ensure(sizeof(double) * m, st));
+        NNVB_TRY(b->wk->wit[0].ensure(sizeof(double) * max_ld * m, st));
+        NNVB_TRY(b->wk->wit[1].ensure(sizeof(double) * max_ld * m, st));
+        NNVB_CUDA(cudaMemcpyAsync(b->wk->hs_G.p, Gc.data(), sizeof(double) * m * Nout, cudaMemcpyHostToDevice, st));
+        NNVB_CUDA(cudaMemcpyAsync(b->wk->hs_g.p, gc.data(), sizeof(double) * m, cudaMemcpyHostToDevice, st));
+        NNVB_CUDA(cudaMemcpyAsync(b->wk->hs_q.p, pq.data(), sizeof(int32_t) * m, cudaMemcpyHostToDevice, st));
+        NNVB_CUDA(cudaMemcpyAsync(b->wk->hs_roff.p, roff.data(), sizeof(int64_t) * (m + 1), cudaMemcpyHostToDevice, st));
+        NNVB_TRY(launch_halfspace_pairs(st, m, b->wk->hs_q.as<int32_t>(), Nout, b->ld, b->V, qoff, qidx, b->wk->pl.as<double>(),
+                                        b->wk->pu.as<double>(), b->wk->hs_G.as<double>(), b->wk->hs_g.as<double>(), nullptr,
+                                        b->wk->hs_r.as<double>(), b->wk->hs_roff.as<int64_t>(), &ctx->launches));
         if (b->kind == 1) {
-            NNVB_TRY(launch_witness_x0_bounds(st, m, b->hs_q.as<int32_t>(), b->N0, b->ld0, b->d_in.as<double>(),
-                                              b->hs_r.as<double>(), b->hs_roff.as<int64_t>(), b->wit[0].as<double>(),
+            NNVB_TRY(launch_witness_x0_bounds(st, m, b->wk->hs_q.as<int32_t>(), b->N0, b->ld0, b->d_in.as<double>(),
+                                              b->wk->hs_r.as<double>(), b->wk->hs_roff.as<int64_t>(), b->wk->wit[0].as<double>(),
                                               &ctx->launches));
         } else {
             int64_t ncols0 = b->nq;
             std::vector<int64_t> gen0(b->nq + 1);
             for (int q = 0; q < b->nq; ++q) { gen0[q] = ncols0; ncols0 += b->P0[q]; }
             gen0[b->nq] = ncols0;
-            NNVB_TRY(b->gen_off.ensure(sizeof(int64_t) * (b->nq + 1), st));
-            NNVB_CUDA(cudaMemcpyAsync(b->gen_off.p, gen0.data(), sizeof(int64_t) * (b->nq + 1), cudaMemcpyHostToDevice, st));
-            NNVB_TRY(launch_witness_x0_star(st, m, b->hs_q.as<int32_t>(), b->N0, b->ld0, b->ld0, b->d_in.as<double>(),
-                                            b->gen_off.as<int64_t>(), b->d_in_meta.as<double>(),
-                                            b->d_in_meta.as<double>() + ncols0, b->hs_r.as<double>(),
-                                            b->hs_roff.as<int64_t>(), b->wit[0].as<double>(), &ctx->launches));
+            NNVB_TRY(b->wk->gen_off.ensure(sizeof(int64_t) * (b->nq + 1), st));
+            NNVB_CUDA(cudaMemcpyAsync(b->wk->gen_off.p, gen0.data(), sizeof(int64_t) * (b->nq + 1), cudaMemcpyHostToDevice, st));
+            NNVB_TRY(launch_witness_x0_star(st, m, b->wk->hs_q.as<int32_t>(), b->N0, b->ld0, b->ld0, b->d_in.as<double>(),
+                                            b->wk->gen_off.as<int64_t>(), b->d_in_meta.as<double>(),
+                                            b->d_in_meta.as<double>() + ncols0, b->wk->hs_r.as<double>(),
+                                            b->wk->hs_roff.as<int64_t>(), b->wk->wit[0].as<double>(), &ctx->launches));
         }
         double* X = nullptr;
         int64_t ldx = 0;
-        NNVB_TRY(witness_forward(b, m, b->hs_q.as<int32_t>(), &X, &ldx, b->hs_r.as<double>(), b->hs_roff.as<int64_t>()));
-        NNVB_TRY(launch_witness_value(st, m, Nout, ldx, X, b->hs_G.as<double>(), b->hs_g.as<double>(),
-                                      b->hs_val.as<double>(), b->hs_scale.as<double>(), &ctx->launches));
+        NNVB_TRY(witness_forward(b, m, b->wk->hs_q.as<int32_t>(), &X, &ldx, b->wk->hs_r.as<double>(), b->wk->hs_roff.as<int64_t>()));
+        NNVB_TRY(launch_witness_value(st, m, Nout, ldx, X, b->wk->hs_G.as<double>(), b->wk->hs_g.as<double>(),
+                                      b->wk->hs_val.as<double>(), b->wk->hs_scale.as<double>(), &ctx->launches));
         std::vector<double> val(m), scale(m);
-        NNVB_CUDA(cudaMemcpyAsync(val.data(), b->hs_val.p, sizeof(double) * m, cudaMemcpyDeviceToHost, st));
-        NNVB_CUDA(cudaMemcpyAsync(scale.data(), b->hs_scale.p, sizeof(double) * m, cudaMemcpyDeviceToHost, st));
+        NNVB_CUDA(cudaMemcpyAsync(val.data(), b->wk->hs_val.p, sizeof(double) * m, cudaMemcpyDeviceToHost, st));
+        NNVB_CUDA(cudaMemcpyAsync(scale.data(), b->wk->hs_scale.p, sizeof(double) * m, cudaMemcpyDeviceToHost, st));
         NNVB_TRY(sync(ctx));
         // accept only points clearly inside the halfspace: well beyond the feasibility
         // tolerance of an LP solver deciding the same question
@@ -1212,7 +1236,8 @@ int nnvb_batch_reach(nnvb_batch* b, const nnvb_opts* opts) {
     b->opts = opts ? *opts : nnvb_opts{};
     b->reached = false;
     b->have_out_ranges = false;
-    while ((int)b->relu.size() < b->net->n_relu) b->relu.emplace_back(new ReluLayerRecord());
+    ctx->result_owner = b;
+    while ((int)b->wk->relu.size() < b->net->n_relu) b->wk->relu.emplace_back(new ReluLayerRecord());
     NNVB_TRY(init_sets(b));
     NNVB_TRY(run_layers(b));
     b->reached = true;
@@ -1225,7 +1250,10 @@ int nnvb_batch_out_dims(const nnvb_batch* b, int q, int64_t* P, int64_t* m) {
     if (P) *P = Pq;
     if (m) {
         int64_t mm = b->m0[q];
-        for (auto& r : b->relu) mm += 3 * (r->new_off[q + 1] - r->new_off[q]);
+        for (int i = 0; i < b->net->n_relu; ++i) {
+            const ReluLayerRecord& r = *b->wk->relu[i];
+            mm += 3 * (r.new_off[q + 1] - r.new_off[q]);
+        }
         *m = mm;
     }
     return NNVB_OK;
@@ -1238,14 +1266,14 @@ int nnvb_batch_get_V(nnvb_batch* b, int q, double* V) {
     NNVB_CUDA(cudaSetDevice(ctx->device));
     const int64_t P = b->h_qcol_off[q + 1] - b->h_qcol_off[q];
     const size_t bytes = size_t(b->N) * (P + 1) * sizeof(double);
-    NNVB_TRY(b->tmp.ensure(bytes, ctx->stream));
+    NNVB_TRY(b->wk->tmp.ensure(bytes, ctx->stream));
     dim3 grid((unsigned)ceil_div(b->N, 256), (unsigned)std::min<int64_t>(P + 1, 32768));
     gather_cols_kernel<<<grid, 256, 0, ctx->stream>>>(b->N, b->ld, b->V, q,
-                                                      b->qcol_idx[b->list_cur].as<int32_t>() + b->h_qcol_off[q], P,
-                                                      b->tmp.as<double>());
+                                                      b->wk->qcol_idx[b->list_cur].as<int32_t>() + b->h_qcol_off[q], P,
+                                                      b->wk->tmp.as<double>());
     NNVB_CUDA(cudaGetLastError());
     ctx->launches += 1;
-    NNVB_CUDA(cudaMemcpyAsync(V, b->tmp.p, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    NNVB_CUDA(cudaMemcpyAsync(V, b->wk->tmp.p, bytes, cudaMemcpyDeviceToHost, ctx->stream));
     return sync(ctx);
 }
 
@@ -1256,14 +1284,14 @@ int nnvb_batch_get_pred_bounds(nnvb_batch* b, int q, double* pl, double* pu) {
     const int64_t P = b->h_qcol_off[q + 1] - b->h_qcol_off[q];
     if (P == 0) return NNVB_OK;
     NNVB_REQUIRE(pl && pu, "nnvb_batch_get_pred_bounds: NULL output");
-    NNVB_TRY(b->tmp.ensure(sizeof(double) * 2 * P, ctx->stream));
+    NNVB_TRY(b->wk->tmp.ensure(sizeof(double) * 2 * P, ctx->stream));
     gather_vec_kernel<<<(unsigned)ceil_div(P, 256), 256, 0, ctx->stream>>>(
-        P, b->qcol_idx[b->list_cur].as<int32_t>() + b->h_qcol_off[q], b->pl.as<double>(), b->pu.as<double>(),
-        b->tmp.as<double>());
+        P, b->wk->qcol_idx[b->list_cur].as<int32_t>() + b->h_qcol_off[q], b->wk->pl.as<double>(), b->wk->pu.as<double>(),
+        b->wk->tmp.as<double>());
     NNVB_CUDA(cudaGetLastError());
     ctx->launches += 1;
-    NNVB_CUDA(cudaMemcpyAsync(pl, b->tmp.p, sizeof(double) * P, cudaMemcpyDeviceToHost, ctx->stream));
-    NNVB_CUDA(cudaMemcpyAsync(pu, b->tmp.as<double>() + P, sizeof(double) * P, cudaMemcpyDeviceToHost, ctx->stream));
+    NNVB_CUDA(cudaMemcpyAsync(pl, b->wk->tmp.p, sizeof(double) * P, cudaMemcpyDeviceToHost, ctx->stream));
+    NNVB_CUDA(cudaMemcpyAsync(pu, b->wk->tmp.as<double>() + P, sizeof(double) * P, cudaMemcpyDeviceToHost, ctx->stream));
     return sync(ctx);
 }
 
@@ -1273,9 +1301,9 @@ int nnvb_batch_get_ranges(nnvb_batch* b, int q, double* lb, double* ub) {
     nnvb_ctx* ctx = b->net->ctx;
     NNVB_CUDA(cudaSetDevice(ctx->device));
     NNVB_TRY(output_ranges(b));
-    NNVB_CUDA(cudaMemcpyAsync(lb, b->lb.as<double>() + size_t(q) * b->N, sizeof(double) * b->N,
+    NNVB_CUDA(cudaMemcpyAsync(lb, b->wk->lb.as<double>() + size_t(q) * b->N, sizeof(double) * b->N,
                               cudaMemcpyDeviceToHost, ctx->stream));
-    NNVB_CUDA(cudaMemcpyAsync(ub, b->ub.as<double>() + size_t(q) * b->N, sizeof(double) * b->N,
+    NNVB_CUDA(cudaMemcpyAsync(ub, b->wk->ub.as<double>() + size_t(q) * b->N, sizeof(double) * b->N,
                               cudaMemcpyDeviceToHost, ctx->stream));
     return sync(ctx);
 }
@@ -1289,7 +1317,7 @@ int nnvb_batch_relu_layers(const nnvb_batch* b, int* n) {
 int nnvb_batch_relu_stats(const nnvb_batch* b, int relu_layer, nnvb_relu_stats* stt) {
     NNVB_TRY(check_reached(b, 0));
     NNVB_REQUIRE(stt && relu_layer >= 0 && relu_layer < b->net->n_relu, "nnvb_batch_relu_stats: bad argument");
-    const ReluLayerRecord& r = *b->relu[relu_layer];
+    const ReluLayerRecord& r = *b->wk->relu[relu_layer];
     stt->n_neurons = r.N;
     stt->n_cross = r.K;
     stt->n_dead = r.n_dead;
@@ -1302,7 +1330,7 @@ int nnvb_batch_get_crossing(nnvb_batch* b, int q, int relu_layer, int64_t* k, in
     NNVB_REQUIRE(relu_layer >= 0 && relu_layer < b->net->n_relu, "nnvb_batch_get_crossing: bad layer");
     nnvb_ctx* ctx = b->net->ctx;
     NNVB_CUDA(cudaSetDevice(ctx->device));
-    ReluLayerRecord& r = *b->relu[relu_layer];
+    ReluLayerRecord& r = *b->wk->relu[relu_layer];
     const int64_t c0 = r.new_off[q], kq = r.new_off[q + 1] - c0;
     if (k) *k = kq;
     if (kq == 0 || (!idx && !lb && !ub)) return NNVB_OK;
@@ -1319,7 +1347,7 @@ int nnvb_batch_get_crossing(nnvb_batch* b, int q, int relu_layer, int64_t* k, in
 int nnvb_batch_get_layer_ranges(nnvb_batch* b, int q, int relu_layer, double* lb, double* ub) {
     NNVB_TRY(check_reached(b, q));
     NNVB_REQUIRE(relu_layer >= 0 && relu_layer < b->net->n_relu && lb && ub, "nnvb_batch_get_layer_ranges: bad argument");
-    ReluLayerRecord& r = *b->relu[relu_layer];
+    ReluLayerRecord& r = *b->wk->relu[relu_layer];
     if (!r.has_bounds) {
         set_error("layer bounds were not kept: set opts.keep_layer_bounds");
         return NNVB_E_STATE;
@@ -1345,8 +1373,8 @@ int nnvb_batch_get_constraints(nnvb_batch* b, int q, double* Cmat, double* d) {
         for (int64_t r = 0; r < m0; ++r) Cmat[size_t(j) * m + r] = b->h_C[q][size_t(j) * m0 + r];
     for (int64_t r = 0; r < m0; ++r) d[r] = b->h_d[q][r];
     int64_t row = m0;
-    for (auto& rp : b->relu) {
-        ReluLayerRecord& r = *rp;
+    for (int ri = 0; ri < b->net->n_relu; ++ri) {
+        ReluLayerRecord& r = *b->wk->relu[ri];
         const int64_t c0 = r.new_off[q], k = r.new_off[q + 1] - c0, Pin = r.P_in[q];
         if (k == 0) continue;
         if (!r.has_G) {
