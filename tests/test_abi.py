@@ -65,3 +65,16 @@ def test_null_arguments_are_rejected():
     assert lib.nnvb_destroy(None) == _lib.NNVB_OK
     assert lib.nnvb_net_destroy(None) == _lib.NNVB_OK
     assert lib.nnvb_batch_destroy(None) == _lib.NNVB_OK
+
+
+def test_mex_gateway_compiles_against_stub_header():
+    # the MEX gateway is shipped as source; check that it is valid C++ against the documented MEX API
+    import shutil
+    import subprocess
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("no g++")
+    src = os.path.join(ROOT, "nnv_b200", "csrc", "nnvb200_mex.cpp")
+    r = subprocess.run([gxx, "-std=c++17", "-fsyntax-only", "-Wall", "-I", os.path.join(ROOT, "include", "mex_stub"), src],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
