@@ -252,6 +252,31 @@ int nnvb_layer_apply(nnvb_ctx* ctx, const nnvb_layer_desc* layer,
 int nnvb_estimate_ranges(nnvb_ctx* ctx, int64_t N, int64_t P, const double* V,
                          const double* pl, const double* pu, double* lb, double* ub);
 
+/* ---- allocation-free entry point ------------------------------------------ */
+
+/* No counterpart in the reference: it exists for hosts that cannot let this
+ * library allocate device memory — a MATLAB session whose gpuArray pool owns the
+ * GPU, or a service with a fixed pre-sized arena — and therefore only lend it
+ * pointers.  Computes Star.estimateRanges like nnvb_estimate_ranges, but every
+ * pointer is a DEVICE pointer supplied by the caller and the call performs no
+ * cudaMalloc/cudaFree (nor any allocating library call): its scratch is a fixed
+ * array of NNVB_NOALLOC_SCRATCH_DOUBLES doubles (4 MiB) inside the loaded
+ * module, held by every GPU that loads the library until the process exits.
+ *   V_dev   [ld x (P+1)] column-major, column 0 = centre, ld >= N
+ *   pl_dev, pu_dev  [P] predicate bounds;  lb_dev, ub_dev  [N] outputs
+ *   stream  a cudaStream_t (NULL = default stream); the call returns after
+ *           enqueueing two kernels on it.
+ * Limit: 2*N <= NNVB_NOALLOC_SCRATCH_DOUBLES (N <= 262144); larger sets are
+ * refused with NNVB_E_CAPACITY and a message.  The current device is used.  The
+ * first call on a device looks up the scratch address (cudaGetSymbolAddress);
+ * make that first call before starting any stream capture.  All calls on a
+ * device share the scratch: calls that overlap on the GPU race, so issue them on
+ * one stream or otherwise one after the other.  Nothing in the scratch needs to
+ * be cleared between calls. */
+#define NNVB_NOALLOC_SCRATCH_DOUBLES 524288
+int nnvb_estimate_ranges_noalloc(void* stream, int64_t N, int64_t P, const double* V_dev, int64_t ld,
+                                 const double* pl_dev, const double* pu_dev, double* lb_dev, double* ub_dev);
+
 #ifdef __cplusplus
 }
 #endif

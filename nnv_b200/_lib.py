@@ -104,6 +104,9 @@ SIGNATURES = {
                                    c_double_p, c_double_p, c_int64_p]),
     "nnvb_estimate_ranges": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, c_double_p, c_double_p, c_double_p,
                                        c_double_p, c_double_p]),
+    # device pointers travel as integers (c_void_p)
+    "nnvb_estimate_ranges_noalloc": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,
+                                               C.c_void_p, C.c_void_p, C.c_void_p]),
 }
 
 _lib = None
