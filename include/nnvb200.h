@@ -132,6 +132,30 @@ int64_t nnvb_launch_count(nnvb_ctx* ctx);
 int nnvb_profile_enable(nnvb_ctx* ctx, int on);
 int nnvb_profile_read(nnvb_ctx* ctx, int family, double* ms, int64_t* launches, double* work);
 
+/* ---- one set sharded over several GPUs ----------------------------------- */
+
+/* Generator sharding: a single large set is split along its predicate
+ * (generator) dimension over `world` processes, one GPU each.  Rank r holds the
+ * generator columns whose position in the predicate order is = r (mod world);
+ * the centre is replicated.  Every affine layer works on the local columns; in
+ * the ReLU step each rank reduces its own columns to partial bound sums, the
+ * sums are added over the ranks through the hook below, and every rank then
+ * classifies the same numbers, clears its own columns' rows and materialises
+ * the new columns numbered = r (mod world).  The reference has no counterpart
+ * (its only parallel axis is parfor over independent sets, NN.m:1371-1413).
+ *
+ * The hook must sum `count` doubles at device pointer `dev_buf` over all ranks
+ * in place (an NCCL all-reduce), ordered after prior work on `stream` (a
+ * cudaStream_t) and before later work on it; it returns 0 on success.  It is
+ * called from nnvb_batch_reach and the result getters of a sharded context, at
+ * the same points on every rank.  Call nnvb_set_shard before creating batches.
+ * With world > 1: nnvb_batch_out_dims reports sizes over all ranks; get_V and
+ * get_pred_bounds fill only this rank's columns (centre on rank 0) into the
+ * full-size output, zeros elsewhere, so the sum over ranks is the set;
+ * constraint records (keep_constraints, get_constraints) are not available. */
+typedef int (*nnvb_allreduce_fn)(void* user, double* dev_buf, int64_t count, void* stream);
+int nnvb_set_shard(nnvb_ctx* ctx, int rank, int world, nnvb_allreduce_fn fn, void* user);
+
 /* ---- network ------------------------------------------------------------ */
 
 /* Copy the layer parameters to the device once and pre-arrange them for the

@@ -56,6 +56,10 @@ class ReluStats(C.Structure):
     _fields_ = [("n_neurons", C.c_int64), ("n_cross", C.c_int64), ("n_dead", C.c_int64), ("cols_after", C.c_int64)]
 
 
+# int (*nnvb_allreduce_fn)(void* user, double* dev_buf, int64_t count, void* stream)
+ALLREDUCE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p)
+
+
 class NNVError(RuntimeError):
     """A non-zero status from the C ABI; ``status`` holds the nnvb_status code."""
 
@@ -76,6 +80,7 @@ SIGNATURES = {
     "nnvb_launch_count": (C.c_int64, [C.c_void_p]),
     "nnvb_profile_enable": (C.c_int, [C.c_void_p, C.c_int]),
     "nnvb_profile_read": (C.c_int, [C.c_void_p, C.c_int, c_double_p, c_int64_p, c_double_p]),
+    "nnvb_set_shard": (C.c_int, [C.c_void_p, C.c_int, C.c_int, ALLREDUCE_FN, C.c_void_p]),
     "nnvb_net_create": (C.c_int, [C.c_void_p, C.POINTER(LayerDesc), C.c_int, C.c_int64, C.c_int64, C.c_int64,
                                   C.POINTER(C.c_void_p)]),
     "nnvb_net_destroy": (C.c_int, [C.c_void_p]),

@@ -141,16 +141,21 @@ struct ReluRecord {
 };
 int relu_blocks_per_query(int64_t N);
 int launch_estimate_ranges(cudaStream_t st, const ReluWork& w, int64_t* launches);
-int launch_classify_scan(cudaStream_t st, const ReluWork& w, int64_t* launches);
+// Sharded generators: per-query sums of the chunk partials (no centre), [nq][2][N].
+int launch_reduce_chunks(cudaStream_t st, const ReluWork& w, double* sums, int64_t* launches);
+// sums = nullptr: combine the chunk partials directly; else classify from the (all-reduced) sums.
+int launch_classify_scan(cudaStream_t st, const ReluWork& w, const double* sums, int64_t* launches);
 int launch_rank_cross(cudaStream_t st, const ReluWork& w, const ReluRecord& rec, int64_t* launches);
 // Zero dead and crossing rows in all existing columns; save crossing rows.
 int launch_relu_zero_rows(cudaStream_t st, const ReluWork& w, int64_t ncols, const int32_t* col_q,
                           const ReluRecord& rec, const int64_t* col_pos, int64_t* launches);
 // Append one one-hot column per crossing neuron with its predicate bounds and
 // rebuild the per-query column lists.
-int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, int64_t K,
-                       const ReluRecord& rec, int32_t* col_q, double* pl, double* pu, int64_t* col_pos,
-                       int64_t* new_qcol_off, int32_t* new_qcol_idx, int64_t* launches);
+// (rank, world) = generator shard; K_loc = new columns this rank holds; P_in = predicates per
+// query entering the layer over all ranks (nullptr when unsharded).
+int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, int64_t K_loc, int rank, int world,
+                       const int64_t* P_in, const ReluRecord& rec, int32_t* col_q, double* pl, double* pu,
+                       int64_t* col_pos, int64_t* new_qcol_off, int32_t* new_qcol_idx, int64_t* launches);
 
 // Halfspace rows against output sets; see relu_star.cu.  Pair p tests row G[p] (length Nout)
 // with offset g[p] on query pair_q[p]; margin[p] = box minimum of G x - g (nullable);
@@ -158,14 +163,15 @@ int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, in
 int launch_halfspace_pairs(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t Nout, int64_t ld,
                            const double* V, const int64_t* qcol_off, const int32_t* qcol_idx, const double* pl,
                            const double* pu, const double* G, const double* g, double* margin, double* r_out,
-                           const int64_t* r_off, int64_t* launches);
+                           const int64_t* r_off, const int64_t* col_pos, int add_center, int64_t* launches);
 // Witness search kernels (one point per pair, X is [ld x n_pairs]).
 int launch_witness_x0_bounds(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t N, int64_t ld,
                              const double* lbub, const double* r, const int64_t* r_off, double* X,
                              int64_t* launches);
 int launch_witness_x0_star(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t N, int64_t ld, int64_t ld0,
                            const double* V0, const int64_t* gen0, const double* pl0, const double* pu0,
-                           const double* r, const int64_t* r_off, double* X, int64_t* launches);
+                           const double* r, const int64_t* r_off, const int64_t* pos0, int add_center, double* X,
+                           int64_t* launches);
 int launch_witness_relu(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t N, int64_t ld, double* X,
                         const double* lb, const double* ub, const int32_t* rank, const int64_t* P_in,
                         const double* r, const int64_t* r_off, int64_t* launches);
@@ -174,7 +180,7 @@ int launch_witness_value(cudaStream_t st, int n_pairs, int64_t Nout, int64_t ld,
 
 // Build the dense input set of a bounds-form query batch.
 int launch_build_from_bounds(cudaStream_t st, int nq, int64_t N, int64_t ld, const double* lbub,
-                             const int64_t* q_gen_off, double* V, int32_t* col_q, double* pl,
+                             const int64_t* q_gen_off, int rank, int world, double* V, int32_t* col_q, double* pl,
                              double* pu, int32_t* qcol_idx, int64_t* col_pos, int64_t* launches);
 int launch_count_bounds(cudaStream_t st, int nq, int64_t N, const double* lbub, int64_t* q_count,
                         int64_t* launches);

@@ -98,7 +98,8 @@ __global__ void count_bounds_kernel(int64_t N, const double* __restrict__ lbub, 
 // centre = (lb+ub)/2; the r-th entry with nonzero half width gets generator
 // column q_gen_off[q] + r holding that half width at its row (columns are zeroed
 // beforehand).  Order of generators = ascending linear index, as diag() gives it.
-__global__ void build_from_bounds_kernel(int nq, int64_t N, int64_t ld, const double* __restrict__ lbub,
+__global__ void build_from_bounds_kernel(int nq, int rank, int world, int64_t N, int64_t ld,
+                                         const double* __restrict__ lbub,
                                          const int64_t* __restrict__ q_gen_off, double* __restrict__ V,
                                          int32_t* __restrict__ col_q, double* __restrict__ pl,
                                          double* __restrict__ pu, int32_t* __restrict__ qcol_idx,
@@ -131,13 +132,14 @@ __global__ void build_from_bounds_kernel(int nq, int64_t N, int64_t ld, const do
         int total = 0;
         for (int w = 0; w < nwarp; ++w) total += warp_cnt[w];
         const int64_t r = running + before + __popc(bal & ((1u << lane) - 1u));
-        if (has) {
-            const int64_t col = gen0 + r;
+        if (has && r % world == rank) {           // generator r of the query lives on rank r % world
+            const int64_t t = r / world;
+            const int64_t col = gen0 + t;
             V[col * ld + i] = hw;
             col_q[col] = q;
             pl[col] = -1.0;
             pu[col] = 1.0;
-            qcol_idx[list0 + r] = int32_t(col);
+            qcol_idx[list0 + t] = int32_t(col);
             col_pos[col] = r;
         }
         __syncthreads();
@@ -181,9 +183,10 @@ int launch_count_bounds(cudaStream_t st, int nq, int64_t N, const double* lbub, 
 }
 
 int launch_build_from_bounds(cudaStream_t st, int nq, int64_t N, int64_t ld, const double* lbub,
-                             const int64_t* q_gen_off, double* V, int32_t* col_q, double* pl,
+                             const int64_t* q_gen_off, int rank, int world, double* V, int32_t* col_q, double* pl,
                              double* pu, int32_t* qcol_idx, int64_t* col_pos, int64_t* launches) {
-    build_from_bounds_kernel<<<nq, 256, 0, st>>>(nq, N, ld, lbub, q_gen_off, V, col_q, pl, pu, qcol_idx, col_pos);
+    build_from_bounds_kernel<<<nq, 256, 0, st>>>(nq, rank, world, N, ld, lbub, q_gen_off, V, col_q, pl, pu, qcol_idx,
+                                                 col_pos);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;

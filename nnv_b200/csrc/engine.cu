@@ -108,14 +108,14 @@ struct ReluLayerRecord {
 struct WorkBufs {
     DevBuf col_q, pl, pu, col_pos;
     DevBuf qcol_off[2], qcol_idx[2];
-    DevBuf chunk_beg, chunk_end, q_chunk_off, partial;
+    DevBuf chunk_beg, chunk_end, q_chunk_off, partial, sums;
     DevBuf lb, ub, state, rank, blk_cross, q_cross, q_dead, q_new_off, gen_off;
     DevBuf tmp;                          // gathers for downloads
     DevBuf hs_G, hs_g, hs_q, hs_margin, hs_r, hs_roff, hs_val, hs_scale, wit[2];   // halfspace tests
     std::vector<std::unique_ptr<ReluLayerRecord>> relu;
     void release() {
         DevBuf* bufs[] = {&col_q, &pl, &pu, &col_pos, &qcol_off[0], &qcol_off[1], &qcol_idx[0], &qcol_idx[1],
-                          &chunk_beg, &chunk_end, &q_chunk_off, &partial, &lb, &ub, &state, &rank, &blk_cross,
+                          &chunk_beg, &chunk_end, &q_chunk_off, &partial, &sums, &lb, &ub, &state, &rank, &blk_cross,
                           &q_cross, &q_dead, &q_new_off, &gen_off, &tmp, &hs_G, &hs_g, &hs_q, &hs_margin, &hs_r,
                           &hs_roff, &hs_val, &hs_scale, &wit[0], &wit[1]};
         for (DevBuf* d : bufs) d->release();
@@ -133,6 +133,10 @@ struct nnvb_ctx {
     PinnedBuf scratch;      // small host->device traffic of the layer loop
     size_t scratch_off = 0; // bytes of `scratch` handed out since the last stream sync
     WorkBufs work;
+    // generator sharding over ranks (world == 1: off)
+    int rank = 0, world = 1;
+    nnvb_allreduce_fn ar_fn = nullptr;
+    void* ar_user = nullptr;
     const void* result_owner = nullptr;   // the batch whose results the work buffers and the arena hold
     // per-kernel-family device timing (off by default)
     bool prof_on = false;
@@ -183,7 +187,10 @@ struct nnvb_batch {
     int64_t N0 = 0, ld0 = 0;
     // host staging
     PinnedBuf h_in;                      // bounds: [nq][2][N0]; star: V [ld0 x ncols0]
-    std::vector<int64_t> P0;             // generators per query
+    std::vector<int64_t> P0;             // generators per query (over all ranks)
+    std::vector<int64_t> P0_loc;         // ... held by this rank (== P0 when the generators are not sharded)
+    std::vector<int64_t> h_Pglob;        // predicates per query over all ranks, after the layers run so far
+    DevBuf d_in_pos;                     // star form: predicate position of each uploaded generator column
     std::vector<char> is_set;
     std::vector<std::vector<double>> h_pl, h_pu, h_C, h_d;   // star form / constraints
     std::vector<int64_t> m0;
@@ -208,6 +215,9 @@ struct nnvb_batch {
 };
 
 namespace {
+
+// number of indices r in [0, n) with r % world == rank
+inline int64_t shard_count(int64_t n, int rank, int world) { return n > rank ? (n - rank + world - 1) / world : 0; }
 
 // Scoped device timer for one kernel family: records an event pair on the stream
 // around the launches issued while it lives.  No-op unless profiling is enabled.
@@ -290,22 +300,31 @@ int h2d_small(nnvb_ctx* ctx, void* dst, const void* src, size_t bytes) {
     return NNVB_OK;
 }
 
+// Copy the centre (center_col >= 0) and the P_loc listed columns into out[N x (P+1)], each generator
+// at its position in the query's predicate order (out is zero filled beforehand).
 __global__ void gather_cols_kernel(int64_t N, int64_t ld, const double* __restrict__ V, int center_col,
-                                   const int32_t* __restrict__ list, int64_t P, double* __restrict__ out) {
+                                   const int32_t* __restrict__ list, const int64_t* __restrict__ col_pos,
+                                   int64_t P_loc, double* __restrict__ out) {
     const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i >= N) return;
-    for (int64_t t = blockIdx.y; t <= P; t += gridDim.y) {
-        const int64_t col = t == 0 ? center_col : list[t - 1];
-        out[t * N + i] = V[col * ld + i];
+    for (int64_t t = blockIdx.y; t <= P_loc; t += gridDim.y) {
+        if (t == 0) {
+            if (center_col >= 0) out[i] = V[int64_t(center_col) * ld + i];
+        } else {
+            const int64_t col = list[t - 1];
+            out[(1 + col_pos[col]) * N + i] = V[col * ld + i];
+        }
     }
 }
 
-__global__ void gather_vec_kernel(int64_t P, const int32_t* __restrict__ list, const double* __restrict__ a,
+__global__ void gather_vec_kernel(int64_t P_loc, int64_t P, const int32_t* __restrict__ list,
+                                  const int64_t* __restrict__ col_pos, const double* __restrict__ a,
                                   const double* __restrict__ b, double* __restrict__ out) {
     const int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (t >= P) return;
-    out[t] = a[list[t]];
-    out[P + t] = b[list[t]];
+    if (t >= P_loc) return;
+    const int64_t pos = col_pos[list[t]];
+    out[pos] = a[list[t]];
+    out[P + pos] = b[list[t]];
 }
 
 }  // namespace
@@ -404,6 +423,18 @@ int nnvb_profile_read(nnvb_ctx* ctx, int family, double* ms, int64_t* launches, 
     if (ms) *ms = ctx->prof_ms[family];
     if (launches) *launches = ctx->prof_launches[family];
     if (work) *work = ctx->prof_work[family];
+    return NNVB_OK;
+}
+
+int nnvb_set_shard(nnvb_ctx* ctx, int rank, int world, nnvb_allreduce_fn fn, void* user) {
+    NNVB_REQUIRE(ctx, "nnvb_set_shard: NULL context");
+    NNVB_REQUIRE(world >= 1 && rank >= 0 && rank < world, "nnvb_set_shard: rank %d of %d", rank, world);
+    NNVB_REQUIRE(world == 1 || fn != nullptr, "nnvb_set_shard: an all-reduce hook is required when world > 1");
+    ctx->rank = rank;
+    ctx->world = world;
+    ctx->ar_fn = fn;
+    ctx->ar_user = user;
+    ctx->result_owner = nullptr;
     return NNVB_OK;
 }
 
@@ -594,6 +625,8 @@ int nnvb_batch_create(nnvb_net* net, int n_queries, nnvb_batch** out) {
     b->N0 = net->in_shape[0] * net->in_shape[1] * net->in_shape[2];
     b->ld0 = lead_dim(b->N0);
     b->P0.assign(n_queries, 0);
+    b->P0_loc.assign(n_queries, 0);
+    b->h_Pglob.assign(n_queries, 0);
     b->is_set.assign(n_queries, 0);
     b->h_pl.resize(n_queries); b->h_pu.resize(n_queries);
     b->h_C.resize(n_queries); b->h_d.resize(n_queries);
@@ -613,6 +646,7 @@ int nnvb_batch_destroy(nnvb_batch* b) {
     b->h_in.release();
     b->d_in.release();
     b->d_in_meta.release();
+    b->d_in_pos.release();
     if (ctx->result_owner == b) ctx->result_owner = nullptr;
     delete b;
     return NNVB_OK;
@@ -702,30 +736,41 @@ int nnvb_batch_upload(nnvb_batch* b) {
         const size_t bytes = size_t(b->nq) * 2 * N * sizeof(double);
         NNVB_TRY(b->d_in.ensure(bytes, ctx->stream));
         NNVB_CUDA(cudaMemcpyAsync(b->d_in.p, b->h_in.p, bytes, cudaMemcpyHostToDevice, ctx->stream));
+        for (int q = 0; q < b->nq; ++q) b->P0_loc[q] = shard_count(b->P0[q], ctx->rank, ctx->world);
     } else {
         // arrange the batch as one matrix: centres first, then each query's generators
+        // (with sharded generators: only the columns j with j % world == rank)
+        const int rank = ctx->rank, world = ctx->world;
         int64_t ncols = b->nq;
-        for (int q = 0; q < b->nq; ++q) ncols += b->P0[q];
+        for (int q = 0; q < b->nq; ++q) {
+            b->P0_loc[q] = shard_count(b->P0[q], rank, world);
+            ncols += b->P0_loc[q];
+        }
         const size_t vbytes = size_t(b->ld0) * ncols * sizeof(double);
         const size_t mbytes = size_t(ncols) * 2 * sizeof(double);
-        NNVB_TRY(b->h_in.ensure(vbytes + mbytes));
+        const size_t pbytes = size_t(ncols) * sizeof(int64_t);
+        NNVB_TRY(b->h_in.ensure(vbytes + mbytes + pbytes));
         double* hv = b->h_in.as<double>();
         double* hm = hv + size_t(b->ld0) * ncols;
+        int64_t* hp = reinterpret_cast<int64_t*>(hm + 2 * ncols);
         int64_t col = b->nq;
         for (int q = 0; q < b->nq; ++q) {
             const double* src = b->h_V[q].data();
             memcpy(hv + size_t(q) * b->ld0, src, N * sizeof(double));
-            hm[q] = 0.0; hm[ncols + q] = 0.0;
-            for (int64_t j = 0; j < b->P0[q]; ++j, ++col) {
+            hm[q] = 0.0; hm[ncols + q] = 0.0; hp[q] = 0;
+            for (int64_t j = rank; j < b->P0[q]; j += world, ++col) {
                 memcpy(hv + size_t(col) * b->ld0, src + size_t(N) * (j + 1), N * sizeof(double));
                 hm[col] = b->h_pl[q][j];
                 hm[ncols + col] = b->h_pu[q][j];
+                hp[col] = j;
             }
         }
         NNVB_TRY(b->d_in.ensure(vbytes, ctx->stream));
         NNVB_TRY(b->d_in_meta.ensure(mbytes, ctx->stream));
+        NNVB_TRY(b->d_in_pos.ensure(pbytes, ctx->stream));
         NNVB_CUDA(cudaMemcpyAsync(b->d_in.p, hv, vbytes, cudaMemcpyHostToDevice, ctx->stream));
         NNVB_CUDA(cudaMemcpyAsync(b->d_in_meta.p, hm, mbytes, cudaMemcpyHostToDevice, ctx->stream));
+        NNVB_CUDA(cudaMemcpyAsync(b->d_in_pos.p, hp, pbytes, cudaMemcpyHostToDevice, ctx->stream));
     }
     b->uploaded = true;
     b->reached = false;
@@ -738,6 +783,21 @@ int nnvb_batch_upload(nnvb_batch* b) {
 // the layer loop
 
 namespace {
+
+// Sum a device buffer over the ranks of a generator-sharded run (identity when unsharded).
+int allreduce(nnvb_ctx* ctx, double* buf, int64_t count) {
+    if (ctx->world <= 1 || count <= 0) return NNVB_OK;
+    if (!ctx->ar_fn) {
+        set_error("generator sharding is on but no all-reduce hook is installed");
+        return NNVB_E_STATE;
+    }
+    const int rc = ctx->ar_fn(ctx->ar_user, buf, count, static_cast<void*>(ctx->stream));
+    if (rc != 0) {
+        set_error("the all-reduce hook failed with code %d", rc);
+        return NNVB_E_CUDA;
+    }
+    return NNVB_OK;
+}
 
 int ensure_col_meta(nnvb_batch* b, int64_t cols) {
     cudaStream_t st = b->net->ctx->stream;
@@ -763,7 +823,8 @@ int init_sets(nnvb_batch* b) {
     for (int q = 0; q < nq; ++q) {
         gen_off[q] = ncols;
         b->h_qcol_off[q] = ncols - nq;
-        ncols += b->P0[q];
+        ncols += b->P0_loc[q];
+        b->h_Pglob[q] = b->P0[q];
     }
     gen_off[nq] = ncols;
     b->h_qcol_off[nq] = ncols - nq;
@@ -778,25 +839,24 @@ int init_sets(nnvb_batch* b) {
         NNVB_TRY(h2d_small(ctx, b->wk->gen_off.p, gen_off.data(), sizeof(int64_t) * (nq + 1)));
         double* V = ctx->vbuf(0);
         NNVB_CUDA(cudaMemsetAsync(V, 0, need, st));
-        NNVB_TRY(launch_build_from_bounds(st, nq, N, ld, b->d_in.as<double>(), b->wk->gen_off.as<int64_t>(), V,
+        NNVB_TRY(launch_build_from_bounds(st, nq, N, ld, b->d_in.as<double>(), b->wk->gen_off.as<int64_t>(), ctx->rank,
+                                          ctx->world, V,
                                           b->wk->col_q.as<int32_t>(), b->wk->pl.as<double>(), b->wk->pu.as<double>(),
                                           b->wk->qcol_idx[0].as<int32_t>(), b->wk->col_pos.as<int64_t>(), &ctx->launches));
         b->V = V;
     } else {
         // metadata is a pure function of the staged queries
         std::vector<int32_t> col_q(ncols), list(ncols - nq);
-        std::vector<int64_t> col_pos(ncols, 0);
         int64_t col = nq;
         for (int q = 0; q < nq; ++q) {
             col_q[q] = q;
-            for (int64_t j = 0; j < b->P0[q]; ++j, ++col) {
+            for (int64_t t = 0; t < b->P0_loc[q]; ++t, ++col) {
                 col_q[col] = q;
-                col_pos[col] = j;
                 list[col - nq] = int32_t(col);
             }
         }
         NNVB_TRY(h2d_small(ctx, b->wk->col_q.p, col_q.data(), sizeof(int32_t) * ncols));
-        NNVB_TRY(h2d_small(ctx, b->wk->col_pos.p, col_pos.data(), sizeof(int64_t) * ncols));
+        NNVB_CUDA(cudaMemcpyAsync(b->wk->col_pos.p, b->d_in_pos.p, sizeof(int64_t) * ncols, cudaMemcpyDeviceToDevice, st));
         NNVB_TRY(h2d_small(ctx, b->wk->qcol_idx[0].p, list.data(), sizeof(int32_t) * (ncols - nq)));
         NNVB_CUDA(cudaMemcpyAsync(b->wk->pl.p, b->d_in_meta.p, sizeof(double) * ncols, cudaMemcpyDeviceToDevice, st));
         NNVB_CUDA(cudaMemcpyAsync(b->wk->pu.p, b->d_in_meta.as<double>() + ncols, sizeof(double) * ncols,
@@ -895,7 +955,16 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec) {
         ProfScope ps(ctx, NNVB_PROF_RANGES,
                      8.0 * double(N) * double(b->ncols) + 16.0 * double(b->ncols - nq) + 16.0 * double(N) * nq);
         NNVB_TRY(launch_estimate_ranges(st, w, &ctx->launches));
-        NNVB_TRY(launch_classify_scan(st, w, &ctx->launches));
+        if (ctx->world > 1) {
+            // sharded generators: every rank holds part of each sum; add them over the ranks, then
+            // all ranks classify the same numbers
+            NNVB_TRY(b->wk->sums.ensure(sizeof(double) * 2 * N * nq, st));
+            NNVB_TRY(launch_reduce_chunks(st, w, b->wk->sums.as<double>(), &ctx->launches));
+            NNVB_TRY(allreduce(ctx, b->wk->sums.as<double>(), int64_t(2) * N * nq));
+            NNVB_TRY(launch_classify_scan(st, w, b->wk->sums.as<double>(), &ctx->launches));
+        } else {
+            NNVB_TRY(launch_classify_scan(st, w, nullptr, &ctx->launches));
+        }
     }
 
     // the crossing counts decide every size from here on: one host round trip per ReLU layer
@@ -910,19 +979,25 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec) {
     rec->n_dead = 0;
     for (int q = 0; q < nq; ++q) rec->n_dead += dead[q];
     rec->P_in.resize(nq);
-    for (int q = 0; q < nq; ++q) rec->P_in[q] = b->h_qcol_off[q + 1] - b->h_qcol_off[q];
-    if (b->opts.keep_layer_bounds) {
+    for (int q = 0; q < nq; ++q) rec->P_in[q] = b->h_Pglob[q];     // predicates entering the layer, over all ranks
+    const int rank = ctx->rank, world = ctx->world;
+    if (world > 1 && b->opts.keep_constraints) {
+        set_error("constraint records are not available with sharded generators");
+        return NNVB_E_UNSUPPORTED;
+    }
+    const int64_t K_loc = shard_count(K, rank, world);
+    if (b->opts.keep_layer_bounds || world > 1) {
         NNVB_TRY(rec->P_in_dev.ensure(sizeof(int64_t) * nq, st));
         NNVB_TRY(h2d_small(ctx, rec->P_in_dev.p, rec->P_in.data(), sizeof(int64_t) * nq));
     }
 
     const int64_t ncols_old = b->ncols;
-    NNVB_REQUIRE(ncols_old + K < (int64_t(1) << 31), "batch has too many generator columns");
+    NNVB_REQUIRE(ncols_old + K_loc < (int64_t(1) << 31), "batch has too many generator columns");
     {
-        const size_t need = size_t(ld) * (ncols_old + K) * sizeof(double);
+        const size_t need = size_t(ld) * (ncols_old + K_loc) * sizeof(double);
         if (need > ctx->vbuf_bytes()) return capacity_error("ReLU layer output", need, ctx->vbuf_bytes());
     }
-    NNVB_TRY(ensure_col_meta(b, ncols_old + K));
+    NNVB_TRY(ensure_col_meta(b, ncols_old + K_loc));
     // pointers may have moved
     w.qcol_off = b->wk->qcol_off[b->list_cur].as<int64_t>();
     w.qcol_idx = b->wk->qcol_idx[b->list_cur].as<int32_t>();
@@ -952,22 +1027,27 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec) {
     // relaxation: lb/ub read, dead and crossing rows cleared in every column of their query,
     // one-hot columns and their predicate bounds written
     const int nxt = 1 - b->list_cur;
-    double relax_bytes = 16.0 * double(N) * nq + 8.0 * double(N) * double(K) + 16.0 * double(K);
+    double relax_bytes = 16.0 * double(N) * nq + 8.0 * double(N) * double(K_loc) + 16.0 * double(K_loc);
     for (int q = 0; q < nq; ++q)
-        relax_bytes += 8.0 * double(dead[q] + rec->new_off[q + 1] - rec->new_off[q]) * double(rec->P_in[q] + 1);
+        relax_bytes += 8.0 * double(dead[q] + rec->new_off[q + 1] - rec->new_off[q]) *
+                       double(b->h_qcol_off[q + 1] - b->h_qcol_off[q] + 1);
     {
         ProfScope ps(ctx, NNVB_PROF_RELAX, relax_bytes);
         if (K > 0) NNVB_TRY(launch_rank_cross(st, w, r, &ctx->launches));
         if (K > 0 || rec->n_dead > 0)
             NNVB_TRY(launch_relu_zero_rows(st, w, ncols_old, b->wk->col_q.as<int32_t>(), r, b->wk->col_pos.as<int64_t>(),
                                            &ctx->launches));
-        NNVB_TRY(launch_relu_append(st, w, ncols_old, K, r, b->wk->col_q.as<int32_t>(), b->wk->pl.as<double>(),
-                                    b->wk->pu.as<double>(), b->wk->col_pos.as<int64_t>(), b->wk->qcol_off[nxt].as<int64_t>(),
-                                    b->wk->qcol_idx[nxt].as<int32_t>(), &ctx->launches));
+        NNVB_TRY(launch_relu_append(st, w, ncols_old, K_loc, rank, world,
+                                    world > 1 ? rec->P_in_dev.as<int64_t>() : nullptr, r, b->wk->col_q.as<int32_t>(),
+                                    b->wk->pl.as<double>(), b->wk->pu.as<double>(), b->wk->col_pos.as<int64_t>(),
+                                    b->wk->qcol_off[nxt].as<int64_t>(), b->wk->qcol_idx[nxt].as<int32_t>(),
+                                    &ctx->launches));
     }
     b->list_cur = nxt;
-    for (int q = 0; q <= nq; ++q) b->h_qcol_off[q] += rec->new_off[q];
-    b->ncols = ncols_old + K;
+    // local lists grow by the new columns this rank holds: those numbered c = rank (mod world)
+    for (int q = 0; q <= nq; ++q) b->h_qcol_off[q] += shard_count(rec->new_off[q], rank, world);
+    for (int q = 0; q < nq; ++q) b->h_Pglob[q] += rec->new_off[q + 1] - rec->new_off[q];
+    b->ncols = ncols_old + K_loc;
     rec->cols_after = b->ncols;
     return NNVB_OK;
 }
@@ -1073,7 +1153,14 @@ int output_ranges(nnvb_batch* b) {
     w.q_cross = b->wk->q_cross.as<int64_t>(); w.q_dead = b->wk->q_dead.as<int64_t>();
     w.q_new_off = b->wk->q_new_off.as<int64_t>();
     NNVB_TRY(launch_estimate_ranges(st, w, &ctx->launches));
-    NNVB_TRY(launch_classify_scan(st, w, &ctx->launches));
+    if (ctx->world > 1) {
+        NNVB_TRY(b->wk->sums.ensure(sizeof(double) * 2 * N * nq, st));
+        NNVB_TRY(launch_reduce_chunks(st, w, b->wk->sums.as<double>(), &ctx->launches));
+        NNVB_TRY(allreduce(ctx, b->wk->sums.as<double>(), int64_t(2) * N * nq));
+        NNVB_TRY(launch_classify_scan(st, w, b->wk->sums.as<double>(), &ctx->launches));
+    } else {
+        NNVB_TRY(launch_classify_scan(st, w, nullptr, &ctx->launches));
+    }
     b->have_out_ranges = true;
     return NNVB_OK;
 }
@@ -1145,9 +1232,12 @@ int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vec
     NNVB_CUDA(cudaMemcpyAsync(b->wk->hs_q.p, pair_q.data(), sizeof(int32_t) * n, cudaMemcpyHostToDevice, st));
     const int64_t* qoff = b->wk->qcol_off[b->list_cur].as<int64_t>();
     const int32_t* qidx = b->wk->qcol_idx[b->list_cur].as<int32_t>();
+    const int add_center = ctx->rank == 0 ? 1 : 0;      // with sharded generators the centre term is added once
     NNVB_TRY(launch_halfspace_pairs(st, n, b->wk->hs_q.as<int32_t>(), Nout, b->ld, b->V, qoff, qidx, b->wk->pl.as<double>(),
                                     b->wk->pu.as<double>(), b->wk->hs_G.as<double>(), b->wk->hs_g.as<double>(),
-                                    b->wk->hs_margin.as<double>(), nullptr, nullptr, &ctx->launches));
+                                    b->wk->hs_margin.as<double>(), nullptr, nullptr, b->wk->col_pos.as<int64_t>(),
+                                    add_center, &ctx->launches));
+    NNVB_TRY(allreduce(ctx, b->wk->hs_margin.as<double>(), n));
     NNVB_CUDA(cudaMemcpyAsync(margin.data(), b->wk->hs_margin.p, sizeof(double) * n, cudaMemcpyDeviceToHost, st));
     NNVB_TRY(sync(ctx));
     std::vector<int> open;
@@ -1173,7 +1263,7 @@ int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vec
             pq[i] = pair_q[p];
             gc[i] = g[p];
             std::copy(G.begin() + size_t(p) * Nout, G.begin() + size_t(p + 1) * Nout, Gc.begin() + size_t(i) * Nout);
-            roff[i + 1] = roff[i] + (b->h_qcol_off[pq[i] + 1] - b->h_qcol_off[pq[i]]);
+            roff[i + 1] = roff[i] + b->h_Pglob[pq[i]];
         }
         NNVB_TRY(b->wk->hs_r.ensure(sizeof(double) * std::max<int64_t>(roff[m], 1), st));
         NNVB_TRY(b->wk->hs_roff.ensure(sizeof(int64_t) * (m + 1), st));
@@ -1185,9 +1275,13 @@ int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vec
         NNVB_CUDA(cudaMemcpyAsync(b->wk->hs_g.p, gc.data(), sizeof(double) * m, cudaMemcpyHostToDevice, st));
         NNVB_CUDA(cudaMemcpyAsync(b->wk->hs_q.p, pq.data(), sizeof(int32_t) * m, cudaMemcpyHostToDevice, st));
         NNVB_CUDA(cudaMemcpyAsync(b->wk->hs_roff.p, roff.data(), sizeof(int64_t) * (m + 1), cudaMemcpyHostToDevice, st));
+        if (ctx->world > 1) NNVB_CUDA(cudaMemsetAsync(b->wk->hs_r.p, 0, sizeof(double) * roff[m], st));
         NNVB_TRY(launch_halfspace_pairs(st, m, b->wk->hs_q.as<int32_t>(), Nout, b->ld, b->V, qoff, qidx, b->wk->pl.as<double>(),
                                         b->wk->pu.as<double>(), b->wk->hs_G.as<double>(), b->wk->hs_g.as<double>(), nullptr,
-                                        b->wk->hs_r.as<double>(), b->wk->hs_roff.as<int64_t>(), &ctx->launches));
+                                        b->wk->hs_r.as<double>(), b->wk->hs_roff.as<int64_t>(),
+                                        b->wk->col_pos.as<int64_t>(), add_center, &ctx->launches));
+        // every rank needs the coefficients of all predicates: each one wrote its own columns' entries
+        NNVB_TRY(allreduce(ctx, b->wk->hs_r.as<double>(), roff[m]));
         if (b->kind == 1) {
             NNVB_TRY(launch_witness_x0_bounds(st, m, b->wk->hs_q.as<int32_t>(), b->N0, b->ld0, b->d_in.as<double>(),
                                               b->wk->hs_r.as<double>(), b->wk->hs_roff.as<int64_t>(), b->wk->wit[0].as<double>(),
@@ -1195,14 +1289,17 @@ int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vec
         } else {
             int64_t ncols0 = b->nq;
             std::vector<int64_t> gen0(b->nq + 1);
-            for (int q = 0; q < b->nq; ++q) { gen0[q] = ncols0; ncols0 += b->P0[q]; }
+            for (int q = 0; q < b->nq; ++q) { gen0[q] = ncols0; ncols0 += b->P0_loc[q]; }
             gen0[b->nq] = ncols0;
             NNVB_TRY(b->wk->gen_off.ensure(sizeof(int64_t) * (b->nq + 1), st));
             NNVB_CUDA(cudaMemcpyAsync(b->wk->gen_off.p, gen0.data(), sizeof(int64_t) * (b->nq + 1), cudaMemcpyHostToDevice, st));
+            // x0 = c + sum_j alpha_j G0_j: local generators here, summed over the ranks, centre added by rank 0
             NNVB_TRY(launch_witness_x0_star(st, m, b->wk->hs_q.as<int32_t>(), b->N0, b->ld0, b->ld0, b->d_in.as<double>(),
                                             b->wk->gen_off.as<int64_t>(), b->d_in_meta.as<double>(),
                                             b->d_in_meta.as<double>() + ncols0, b->wk->hs_r.as<double>(),
-                                            b->wk->hs_roff.as<int64_t>(), b->wk->wit[0].as<double>(), &ctx->launches));
+                                            b->wk->hs_roff.as<int64_t>(), b->d_in_pos.as<int64_t>(), add_center,
+                                            b->wk->wit[0].as<double>(), &ctx->launches));
+            NNVB_TRY(allreduce(ctx, b->wk->wit[0].as<double>(), b->ld0 * int64_t(m)));
         }
         double* X = nullptr;
         int64_t ldx = 0;
@@ -1246,7 +1343,7 @@ int nnvb_batch_reach(nnvb_batch* b, const nnvb_opts* opts) {
 
 int nnvb_batch_out_dims(const nnvb_batch* b, int q, int64_t* P, int64_t* m) {
     NNVB_TRY(check_reached(b, q));
-    const int64_t Pq = b->h_qcol_off[q + 1] - b->h_qcol_off[q];
+    const int64_t Pq = b->h_Pglob[q];      // over all ranks when the generators are sharded
     if (P) *P = Pq;
     if (m) {
         int64_t mm = b->m0[q];
@@ -1264,13 +1361,15 @@ int nnvb_batch_get_V(nnvb_batch* b, int q, double* V) {
     NNVB_REQUIRE(V, "nnvb_batch_get_V: NULL output");
     nnvb_ctx* ctx = b->net->ctx;
     NNVB_CUDA(cudaSetDevice(ctx->device));
-    const int64_t P = b->h_qcol_off[q + 1] - b->h_qcol_off[q];
+    const int64_t P = b->h_Pglob[q];
+    const int64_t P_loc = b->h_qcol_off[q + 1] - b->h_qcol_off[q];
     const size_t bytes = size_t(b->N) * (P + 1) * sizeof(double);
     NNVB_TRY(b->wk->tmp.ensure(bytes, ctx->stream));
-    dim3 grid((unsigned)ceil_div(b->N, 256), (unsigned)std::min<int64_t>(P + 1, 32768));
-    gather_cols_kernel<<<grid, 256, 0, ctx->stream>>>(b->N, b->ld, b->V, q,
-                                                      b->wk->qcol_idx[b->list_cur].as<int32_t>() + b->h_qcol_off[q], P,
-                                                      b->wk->tmp.as<double>());
+    if (ctx->world > 1) NNVB_CUDA(cudaMemsetAsync(b->wk->tmp.p, 0, bytes, ctx->stream));
+    dim3 grid((unsigned)ceil_div(b->N, 256), (unsigned)std::min<int64_t>(P_loc + 1, 32768));
+    gather_cols_kernel<<<grid, 256, 0, ctx->stream>>>(b->N, b->ld, b->V, ctx->rank == 0 ? q : -1,
+                                                      b->wk->qcol_idx[b->list_cur].as<int32_t>() + b->h_qcol_off[q],
+                                                      b->wk->col_pos.as<int64_t>(), P_loc, b->wk->tmp.as<double>());
     NNVB_CUDA(cudaGetLastError());
     ctx->launches += 1;
     NNVB_CUDA(cudaMemcpyAsync(V, b->wk->tmp.p, bytes, cudaMemcpyDeviceToHost, ctx->stream));
@@ -1281,15 +1380,19 @@ int nnvb_batch_get_pred_bounds(nnvb_batch* b, int q, double* pl, double* pu) {
     NNVB_TRY(check_reached(b, q));
     nnvb_ctx* ctx = b->net->ctx;
     NNVB_CUDA(cudaSetDevice(ctx->device));
-    const int64_t P = b->h_qcol_off[q + 1] - b->h_qcol_off[q];
+    const int64_t P = b->h_Pglob[q];
+    const int64_t P_loc = b->h_qcol_off[q + 1] - b->h_qcol_off[q];
     if (P == 0) return NNVB_OK;
     NNVB_REQUIRE(pl && pu, "nnvb_batch_get_pred_bounds: NULL output");
     NNVB_TRY(b->wk->tmp.ensure(sizeof(double) * 2 * P, ctx->stream));
-    gather_vec_kernel<<<(unsigned)ceil_div(P, 256), 256, 0, ctx->stream>>>(
-        P, b->wk->qcol_idx[b->list_cur].as<int32_t>() + b->h_qcol_off[q], b->wk->pl.as<double>(), b->wk->pu.as<double>(),
-        b->wk->tmp.as<double>());
-    NNVB_CUDA(cudaGetLastError());
-    ctx->launches += 1;
+    if (ctx->world > 1) NNVB_CUDA(cudaMemsetAsync(b->wk->tmp.p, 0, sizeof(double) * 2 * P, ctx->stream));
+    if (P_loc > 0) {
+        gather_vec_kernel<<<(unsigned)ceil_div(P_loc, 256), 256, 0, ctx->stream>>>(
+            P_loc, P, b->wk->qcol_idx[b->list_cur].as<int32_t>() + b->h_qcol_off[q], b->wk->col_pos.as<int64_t>(),
+            b->wk->pl.as<double>(), b->wk->pu.as<double>(), b->wk->tmp.as<double>());
+        NNVB_CUDA(cudaGetLastError());
+        ctx->launches += 1;
+    }
     NNVB_CUDA(cudaMemcpyAsync(pl, b->wk->tmp.p, sizeof(double) * P, cudaMemcpyDeviceToHost, ctx->stream));
     NNVB_CUDA(cudaMemcpyAsync(pu, b->wk->tmp.as<double>() + P, sizeof(double) * P, cudaMemcpyDeviceToHost, ctx->stream));
     return sync(ctx);
@@ -1363,6 +1466,10 @@ int nnvb_batch_get_constraints(nnvb_batch* b, int q, double* Cmat, double* d) {
     NNVB_TRY(check_reached(b, q));
     NNVB_REQUIRE(Cmat && d, "nnvb_batch_get_constraints: NULL output");
     nnvb_ctx* ctx = b->net->ctx;
+    if (ctx->world > 1) {
+        set_error("constraint records are not available with sharded generators");
+        return NNVB_E_UNSUPPORTED;
+    }
     NNVB_CUDA(cudaSetDevice(ctx->device));
     int64_t P = 0, m = 0;
     NNVB_TRY(nnvb_batch_out_dims(b, q, &P, &m));

@@ -292,39 +292,104 @@ zero_rows_kernel(int nq, int64_t N, int64_t ld, double* __restrict__ V, int64_t 
 }
 
 // 3b. one-hot columns for the crossing neurons (the block was zero filled) and
-// their predicate range [0, ub].
-__global__ void append_cols_kernel(int64_t K, int64_t ld, double* __restrict__ V, int64_t ncols_old,
-                                   const int32_t* __restrict__ rec_idx, const int32_t* __restrict__ rec_q,
-                                   const double* __restrict__ rec_u, const int64_t* __restrict__ q_new_off,
-                                   const int64_t* __restrict__ qcol_off, int32_t* __restrict__ col_q,
+// their predicate range [0, ub].  With the generators sharded over `world`
+// ranks, new column c (numbered over the whole batch) lives on rank c % world;
+// this rank materialises its K_loc columns t -> c = rank + t*world.
+__global__ void append_cols_kernel(int64_t K_loc, int rank, int world, int64_t ld, double* __restrict__ V,
+                                   int64_t ncols_old, const int32_t* __restrict__ rec_idx,
+                                   const int32_t* __restrict__ rec_q, const double* __restrict__ rec_u,
+                                   const int64_t* __restrict__ q_new_off, const int64_t* __restrict__ qcol_off,
+                                   const int64_t* __restrict__ P_in, int32_t* __restrict__ col_q,
                                    double* __restrict__ pl, double* __restrict__ pu,
                                    int64_t* __restrict__ col_pos) {
-    const int64_t c = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (c >= K) return;
-    const int64_t col = ncols_old + c;
+    const int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= K_loc) return;
+    const int64_t c = rank + t * world;
+    const int64_t col = ncols_old + t;
     const int q = rec_q[c];
     V[col * ld + rec_idx[c]] = 1.0;
     col_q[col] = q;
     pl[col] = 0.0;
     pu[col] = rec_u[c];
-    col_pos[col] = (qcol_off[q + 1] - qcol_off[q]) + (c - q_new_off[q]);
+    // position in the query's predicate order (over all ranks)
+    const int64_t p_in = P_in ? P_in[q] : (qcol_off[q + 1] - qcol_off[q]);
+    col_pos[col] = p_in + (c - q_new_off[q]);
 }
 
-// 3c. new predicate-ordered column lists: old list of the query, then its new columns.
-__global__ void rebuild_lists_kernel(int nq, const int64_t* __restrict__ qcol_off,
+// 3c. new predicate-ordered column lists: old list of the query, then its new
+// columns held by this rank (global numbers c = rank mod world within the query's range).
+__global__ void rebuild_lists_kernel(int nq, int rank, int world, const int64_t* __restrict__ qcol_off,
                                      const int32_t* __restrict__ qcol_idx,
                                      const int64_t* __restrict__ q_new_off, int64_t ncols_old,
                                      int64_t* __restrict__ new_off, int32_t* __restrict__ new_idx) {
     const int q = blockIdx.x;
     const int64_t o0 = qcol_off[q], o1 = qcol_off[q + 1];
     const int64_t n0 = q_new_off[q], n1 = q_new_off[q + 1];
-    const int64_t dst = o0 + n0;
+    // local new columns before / inside this query's range: t = (c - rank) / world for c = rank (mod world)
+    auto first_t = [&](int64_t n) { return n <= rank ? int64_t(0) : (n - rank + world - 1) / world; };
+    const int64_t t0 = first_t(n0), t1 = first_t(n1);
+    const int64_t dst = o0 + t0;
     for (int64_t t = threadIdx.x; t < o1 - o0; t += blockDim.x) new_idx[dst + t] = qcol_idx[o0 + t];
-    for (int64_t t = threadIdx.x; t < n1 - n0; t += blockDim.x)
-        new_idx[dst + (o1 - o0) + t] = int32_t(ncols_old + n0 + t);
+    for (int64_t t = threadIdx.x; t < t1 - t0; t += blockDim.x)
+        new_idx[dst + (o1 - o0) + t] = int32_t(ncols_old + t0 + t);
     if (threadIdx.x == 0) {
         new_off[q] = dst;
-        if (q == nq - 1) new_off[nq] = o1 + n1;
+        if (q == nq - 1) new_off[nq] = o1 + t1;
+    }
+}
+
+// Sharded generators: sum the chunk partials of each query (no centre) so that
+// the ranks can add their sums before classifying.  grid = (nq, row blocks).
+__global__ void __launch_bounds__(FIN_THREADS)
+reduce_chunks_kernel(int64_t N, const int32_t* __restrict__ q_chunk_off, const double* __restrict__ partial,
+                     double* __restrict__ sums) {
+    const int q = blockIdx.x;
+    const int c0 = q_chunk_off[q], c1 = q_chunk_off[q + 1];
+    for (int r = 0; r < FIN_ROWS / FIN_THREADS; ++r) {
+        const int64_t i = int64_t(blockIdx.y) * FIN_ROWS + r * FIN_THREADS + threadIdx.x;
+        if (i >= N) break;
+        double lo = 0.0, hi = 0.0;
+        for (int ch = c0; ch < c1; ++ch) {
+            const double* pp = partial + int64_t(ch) * 2 * N;
+            lo += pp[i];
+            hi += pp[N + i];
+        }
+        sums[(int64_t(q) * 2) * N + i] = lo;
+        sums[(int64_t(q) * 2 + 1) * N + i] = hi;
+    }
+}
+
+// ... and classify from the combined sums (same outputs as range_finalize_kernel).
+__global__ void __launch_bounds__(FIN_THREADS)
+classify_sums_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const double* __restrict__ sums,
+                     double* __restrict__ lb, double* __restrict__ ub, uint8_t* __restrict__ state,
+                     int32_t* __restrict__ blk_cross, unsigned long long* __restrict__ q_dead, int nblk) {
+    const int q = blockIdx.x;
+    int n_cross = 0, n_dead = 0;
+    for (int r = 0; r < FIN_ROWS / FIN_THREADS; ++r) {
+        const int64_t i = int64_t(blockIdx.y) * FIN_ROWS + r * FIN_THREADS + threadIdx.x;
+        if (i >= N) break;
+        const double c = V[int64_t(q) * ld + i];
+        const double l = c + sums[(int64_t(q) * 2) * N + i], u = c + sums[(int64_t(q) * 2 + 1) * N + i];
+        lb[int64_t(q) * N + i] = l;
+        ub[int64_t(q) * N + i] = u;
+        uint8_t s = 0;
+        if (u <= 0.0) { s = 1; ++n_dead; }
+        else if (l < 0.0 && u > 0.0) { s = 2; ++n_cross; }
+        state[int64_t(q) * N + i] = s;
+    }
+    __shared__ int sc[FIN_THREADS / 32], sd[FIN_THREADS / 32];
+    for (int o = 16; o; o >>= 1) {
+        n_cross += __shfl_down_sync(0xffffffffu, n_cross, o);
+        n_dead += __shfl_down_sync(0xffffffffu, n_dead, o);
+    }
+    if ((threadIdx.x & 31) == 0) { sc[threadIdx.x >> 5] = n_cross; sd[threadIdx.x >> 5] = n_dead; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tc = 0, td = 0;
+        for (int w = 0; w < FIN_THREADS / 32; ++w) { tc += sc[w]; td += sd[w]; }
+        blk_cross[int64_t(q) * nblk + blockIdx.y] = tc;
+        if (td) atomicAdd(q_dead + q, (unsigned long long)td);
     }
 }
 
@@ -342,7 +407,8 @@ halfspace_pairs_kernel(const int32_t* __restrict__ pair_q, int64_t Nout, int64_t
                        const int32_t* __restrict__ qcol_idx, const double* __restrict__ pl,
                        const double* __restrict__ pu, const double* __restrict__ G,
                        const double* __restrict__ g, double* __restrict__ margin,
-                       double* __restrict__ r_out, const int64_t* __restrict__ r_off) {
+                       double* __restrict__ r_out, const int64_t* __restrict__ r_off,
+                       const int64_t* __restrict__ col_pos, int add_center) {
     const int p = blockIdx.x;
     const int q = pair_q[p];
     const double* Gr = G + int64_t(p) * Nout;
@@ -354,7 +420,7 @@ halfspace_pairs_kernel(const int32_t* __restrict__ pair_q, int64_t Nout, int64_t
         double r = 0.0;
         for (int64_t o = 0; o < Nout; ++o) r = fma(Gr[o], v[o], r);
         acc += fmin(r * pl[col], r * pu[col]);
-        if (r_out) r_out[r_off[p] + (pos - o0)] = r;
+        if (r_out) r_out[r_off[p] + col_pos[col]] = r;     // position in the query's predicate order
     }
     __shared__ double s[256];
     s[threadIdx.x] = acc;
@@ -364,10 +430,13 @@ halfspace_pairs_kernel(const int32_t* __restrict__ pair_q, int64_t Nout, int64_t
         __syncthreads();
     }
     if (threadIdx.x == 0 && margin) {
-        const double* v = V + int64_t(q) * ld;
         double r = 0.0;
-        for (int64_t o = 0; o < Nout; ++o) r = fma(Gr[o], v[o], r);
-        margin[p] = (r - g[p]) + s[0];
+        if (add_center) {                      // with sharded generators only one rank adds the centre term
+            const double* v = V + int64_t(q) * ld;
+            for (int64_t o = 0; o < Nout; ++o) r = fma(Gr[o], v[o], r);
+            r -= g[p];
+        }
+        margin[p] = r + s[0];
     }
 }
 
@@ -436,16 +505,16 @@ witness_x0_star_kernel(const int32_t* __restrict__ pair_q, int64_t N, int64_t ld
                        const double* __restrict__ V0, const int64_t* __restrict__ gen0,
                        const double* __restrict__ pl0, const double* __restrict__ pu0,
                        const double* __restrict__ r, const int64_t* __restrict__ r_off,
-                       double* __restrict__ X) {
+                       const int64_t* __restrict__ pos0, int add_center, double* __restrict__ X) {
     const int p = blockIdx.x;
     const int q = pair_q[p];
     const int64_t i = int64_t(blockIdx.y) * blockDim.x + threadIdx.x;
     if (i >= N) return;
     const double* rp = r + r_off[p];
     const int64_t c0 = gen0[q], c1 = gen0[q + 1];
-    double x = V0[int64_t(q) * ld0 + i];
+    double x = add_center ? V0[int64_t(q) * ld0 + i] : 0.0;
     for (int64_t col = c0; col < c1; ++col) {
-        const double a = rp[col - c0] > 0.0 ? pl0[col] : pu0[col];
+        const double a = rp[pos0[col]] > 0.0 ? pl0[col] : pu0[col];
         x = fma(a, V0[col * ld0 + i], x);
     }
     X[int64_t(p) * ld + i] = x;
@@ -517,13 +586,26 @@ int launch_estimate_ranges(cudaStream_t st, const ReluWork& w, int64_t* launches
 
 int relu_blocks_per_query(int64_t N) { return (int)ceil_div(N, FIN_ROWS); }
 
-int launch_classify_scan(cudaStream_t st, const ReluWork& w, int64_t* launches) {
+int launch_reduce_chunks(cudaStream_t st, const ReluWork& w, double* sums, int64_t* launches) {
+    const int nblk = relu_blocks_per_query(w.N);
+    dim3 grid((unsigned)w.nq, (unsigned)nblk);
+    reduce_chunks_kernel<<<grid, FIN_THREADS, 0, st>>>(w.N, w.q_chunk_off, w.partial, sums);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_classify_scan(cudaStream_t st, const ReluWork& w, const double* sums, int64_t* launches) {
     const int nblk = relu_blocks_per_query(w.N);
     NNVB_CUDA(cudaMemsetAsync(w.q_dead, 0, sizeof(int64_t) * w.nq, st));
     dim3 grid((unsigned)w.nq, (unsigned)nblk);
-    range_finalize_kernel<<<grid, FIN_THREADS, 0, st>>>(w.N, w.ld, w.V, w.q_chunk_off, w.partial, w.lb,
-                                                        w.ub, w.state, w.blk_cross,
-                                                        reinterpret_cast<unsigned long long*>(w.q_dead), nblk);
+    if (sums)
+        classify_sums_kernel<<<grid, FIN_THREADS, 0, st>>>(w.N, w.ld, w.V, sums, w.lb, w.ub, w.state, w.blk_cross,
+                                                           reinterpret_cast<unsigned long long*>(w.q_dead), nblk);
+    else
+        range_finalize_kernel<<<grid, FIN_THREADS, 0, st>>>(w.N, w.ld, w.V, w.q_chunk_off, w.partial, w.lb,
+                                                            w.ub, w.state, w.blk_cross,
+                                                            reinterpret_cast<unsigned long long*>(w.q_dead), nblk);
     NNVB_CUDA(cudaGetLastError());
     scan_blocks_kernel<<<w.nq, 256, 0, st>>>(nblk, w.blk_cross, w.q_cross);
     NNVB_CUDA(cudaGetLastError());
@@ -553,18 +635,18 @@ int launch_relu_zero_rows(cudaStream_t st, const ReluWork& w, int64_t ncols, con
     return NNVB_OK;
 }
 
-int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, int64_t K,
-                       const ReluRecord& rec, int32_t* col_q, double* pl, double* pu, int64_t* col_pos,
-                       int64_t* new_qcol_off, int32_t* new_qcol_idx, int64_t* launches) {
-    if (K > 0) {
-        NNVB_CUDA(cudaMemsetAsync(w.V + ncols_old * w.ld, 0, sizeof(double) * w.ld * K, st));
-        append_cols_kernel<<<(unsigned)ceil_div(K, 256), 256, 0, st>>>(K, w.ld, w.V, ncols_old, rec.idx, rec.q,
-                                                                      rec.u, w.q_new_off, w.qcol_off, col_q,
-                                                                      pl, pu, col_pos);
+int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, int64_t K_loc, int rank, int world,
+                       const int64_t* P_in, const ReluRecord& rec, int32_t* col_q, double* pl, double* pu,
+                       int64_t* col_pos, int64_t* new_qcol_off, int32_t* new_qcol_idx, int64_t* launches) {
+    if (K_loc > 0) {
+        NNVB_CUDA(cudaMemsetAsync(w.V + ncols_old * w.ld, 0, sizeof(double) * w.ld * K_loc, st));
+        append_cols_kernel<<<(unsigned)ceil_div(K_loc, 256), 256, 0, st>>>(K_loc, rank, world, w.ld, w.V, ncols_old,
+                                                                          rec.idx, rec.q, rec.u, w.q_new_off,
+                                                                          w.qcol_off, P_in, col_q, pl, pu, col_pos);
         NNVB_CUDA(cudaGetLastError());
         if (launches) *launches += 1;
     }
-    rebuild_lists_kernel<<<w.nq, 128, 0, st>>>(w.nq, w.qcol_off, w.qcol_idx, w.q_new_off, ncols_old,
+    rebuild_lists_kernel<<<w.nq, 128, 0, st>>>(w.nq, rank, world, w.qcol_off, w.qcol_idx, w.q_new_off, ncols_old,
                                                new_qcol_off, new_qcol_idx);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
@@ -574,10 +656,10 @@ int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, in
 int launch_halfspace_pairs(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t Nout, int64_t ld,
                            const double* V, const int64_t* qcol_off, const int32_t* qcol_idx, const double* pl,
                            const double* pu, const double* G, const double* g, double* margin, double* r_out,
-                           const int64_t* r_off, int64_t* launches) {
+                           const int64_t* r_off, const int64_t* col_pos, int add_center, int64_t* launches) {
     if (n_pairs <= 0) return NNVB_OK;
     halfspace_pairs_kernel<<<n_pairs, 256, 0, st>>>(pair_q, Nout, ld, V, qcol_off, qcol_idx, pl, pu, G, g, margin,
-                                                    r_out, r_off);
+                                                    r_out, r_off, col_pos, add_center);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;
@@ -594,9 +676,10 @@ int launch_witness_x0_bounds(cudaStream_t st, int n_pairs, const int32_t* pair_q
 
 int launch_witness_x0_star(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t N, int64_t ld, int64_t ld0,
                            const double* V0, const int64_t* gen0, const double* pl0, const double* pu0,
-                           const double* r, const int64_t* r_off, double* X, int64_t* launches) {
+                           const double* r, const int64_t* r_off, const int64_t* pos0, int add_center, double* X,
+                           int64_t* launches) {
     dim3 grid((unsigned)n_pairs, (unsigned)ceil_div(N, 256));
-    witness_x0_star_kernel<<<grid, 256, 0, st>>>(pair_q, N, ld, ld0, V0, gen0, pl0, pu0, r, r_off, X);
+    witness_x0_star_kernel<<<grid, 256, 0, st>>>(pair_q, N, ld, ld0, V0, gen0, pl0, pu0, r, r_off, pos0, add_center, X);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;

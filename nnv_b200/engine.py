@@ -50,6 +50,14 @@ class Context:
     def launch_count(self):
         return int(self.lib.nnvb_launch_count(self.handle))
 
+    def set_shard(self, rank, world, group=None):
+        """Shard the generators of every later batch over ``world`` ranks (this process is
+        ``rank``); the partial bound sums are added with torch.distributed on ``group``."""
+        from .sharding import make_allreduce_hook
+        self._hook = make_allreduce_hook(group) if world > 1 else L.ALLREDUCE_FN(0)
+        L.check(self.lib.nnvb_set_shard(self.handle, int(rank), int(world), self._hook, None), "nnvb_set_shard")
+        self.rank, self.world = int(rank), int(world)
+
     def profile_enable(self, on=True):
         """Start (and zero) or stop the per-kernel-family device timers."""
         L.check(self.lib.nnvb_profile_enable(self.handle, int(bool(on))), "nnvb_profile_enable")
