@@ -35,16 +35,18 @@ def main():
         for q, qu in enumerate(cfg["queries"]):
             S = O.reach(cfg["layers"], O.star_from_query(qu))
             P, _ = b.out_dims(q)
-            Vt = torch.from_numpy(b.get_V(q)).cuda()
+            Vloc = b.get_V(q)
+            Vt = torch.from_numpy(np.ascontiguousarray(Vloc.reshape(-1, order="F"))).cuda()
             dist.all_reduce(Vt)
+            Vsum = Vt.cpu().numpy().reshape(Vloc.shape, order="F")
             pl, pu = b.get_pred_bounds(q)
             pt = torch.from_numpy(np.stack([pl, pu])).cuda()
             dist.all_reduce(pt)
             lb, ub = b.get_ranges(q)
             rl, ru = O.output_ranges(S)
             scale = max(np.abs(rl).max(), np.abs(ru).max())
-            good = P == S.P and Vt.shape == S.V.shape
-            good = good and np.abs(Vt.cpu().numpy() - S.V).max() / np.abs(S.V).max() < 1e-9
+            good = P == S.P and Vsum.shape == S.V.shape
+            good = good and np.abs(Vsum - S.V).max() / np.abs(S.V).max() < 1e-9
             good = good and np.abs(lb - rl).max() / scale < 1e-9 and np.abs(ub - ru).max() / scale < 1e-9
             good = good and np.array_equal(pt[0].cpu().numpy(), S.pl)
             good = good and np.abs(pt[1].cpu().numpy() - S.pu).max() <= 1e-9 * max(1.0, np.abs(S.pu).max())
