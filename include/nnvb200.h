@@ -128,7 +128,8 @@ int64_t nnvb_launch_count(nnvb_ctx* ctx);
 #define NNVB_PROF_RANGES 4    /* Star.estimateRanges + classification scans */
 #define NNVB_PROF_RELAX 5     /* row clearing, column append, list rebuild */
 #define NNVB_PROF_VERIFY 6    /* halfspace rows, box minimum, witness pass */
-#define NNVB_PROF_FAMILIES 7
+#define NNVB_PROF_ONEHOT 7    /* images of the unit-vector columns a ReLU step appended (bytes written) */
+#define NNVB_PROF_FAMILIES 8
 int nnvb_profile_enable(nnvb_ctx* ctx, int on);
 int nnvb_profile_read(nnvb_ctx* ctx, int family, double* ms, int64_t* launches, double* work);
 

@@ -22,7 +22,7 @@ NNVB_E_UNSUPPORTED = 5
 
 LAYER_CONV2D, LAYER_FC, LAYER_BN, LAYER_AVGPOOL2D, LAYER_RELU = 1, 2, 3, 4, 5
 
-PROF_FAMILIES = ("conv", "fc", "bn", "avgpool", "ranges", "relax", "verify")
+PROF_FAMILIES = ("conv", "fc", "bn", "avgpool", "ranges", "relax", "verify", "onehot")
 
 VERDICT_EMPTY = 1
 VERDICT_NONEMPTY = 2

@@ -76,14 +76,31 @@ struct ChanAffine {
     const double* offset;
 };
 
+// Rows that a ReLU step cleared but did not zero in memory: for columns j < ncols, row i of column j
+// reads as zero when state[col_q[j]*N + i] != 0.  state == nullptr: no mask.
+struct RowMask {
+    const uint8_t* state;
+    const int32_t* col_q;
+    int64_t ncols;
+    int64_t N;
+};
+
 size_t conv_weights_doubles(const ConvGeom& g, int* bn_tile, int* cs, int* n_tiles, int* n_chunks);
 // Host-side re-layout of W[kh,kw,Cin,Cout] (column-major) into the kernel's layout.
 void conv_arrange_weights(const ConvGeom& g, const double* W, double* dst, int bn_tile, int cs,
                           int n_tiles, int n_chunks);
 
 int launch_conv_f64(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
-                    const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
+                    const RowMask& mask, const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
                     int64_t ncols, int64_t n_center, int64_t* launches);
+
+// Images of the one-hot columns a ReLU step appended (column t of this rank is batch-wide column
+// c_first + t*c_step, the unit vector of neuron rec_idx[c]); written to Vout[ld_out x K_loc].
+int launch_conv_onehot(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
+                       const int32_t* rec_idx, int64_t c_first, int64_t c_step, int64_t K_loc, double* Vout,
+                       int64_t ld_out, int64_t* launches);
+int launch_fc_onehot(cudaStream_t st, int Out, const double* Wt, int ldw, const int32_t* rec_idx, int64_t c_first,
+                     int64_t c_step, int64_t K_loc, double* Vout, int64_t ld_out, int64_t* launches);
 
 // FC: Vout[Out x ncols] = W * Vin[In x ncols]; bias (and the optional affine) on
 // the first n_center columns.  Wt is the device copy arranged [In_pad][ldw]
@@ -101,8 +118,10 @@ struct PoolGeom {
     int H, W, C, Ho, Wo;
     int ph, pw, sh, sw, pad_t, pad_l;
 };
-int launch_avgpool_f64(cudaStream_t st, const PoolGeom& g, const double* Vin, int64_t ld_in,
+int launch_avgpool_f64(cudaStream_t st, const PoolGeom& g, const RowMask& mask, const double* Vin, int64_t ld_in,
                        double* Vout, int64_t ld_out, int64_t ncols, int64_t* launches);
+int launch_avgpool_onehot(cudaStream_t st, const PoolGeom& g, const int32_t* rec_idx, int64_t c_first,
+                          int64_t c_step, int64_t K_loc, double* Vout, int64_t ld_out, int64_t* launches);
 
 // ReLU approx-star step; see relu_star.cu.  All pointers are device pointers.
 struct ReluWork {
@@ -153,8 +172,9 @@ int launch_relu_zero_rows(cudaStream_t st, const ReluWork& w, int64_t ncols, con
 // rebuild the per-query column lists.
 // (rank, world) = generator shard; K_loc = new columns this rank holds; P_in = predicates per
 // query entering the layer over all ranks (nullptr when unsharded).
+// materialize = false leaves the new columns implicit (only their metadata is written).
 int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, int64_t K_loc, int rank, int world,
-                       const int64_t* P_in, const ReluRecord& rec, int32_t* col_q, double* pl, double* pu,
+                       bool materialize, const int64_t* P_in, const ReluRecord& rec, int32_t* col_q, double* pl, double* pu,
                        int64_t* col_pos, int64_t* new_qcol_off, int32_t* new_qcol_idx, int64_t* launches);
 
 // Halfspace rows against output sets; see relu_star.cu.  Pair p tests row G[p] (length Nout)

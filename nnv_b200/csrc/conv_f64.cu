@@ -49,7 +49,7 @@ struct ConvParams {
 template <int WM_TILES, int WN_TILES, int WARPS_M, int WARPS_N, int STAGES, int MIN_BLOCKS>
 __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MIN_BLOCKS)
 conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double* __restrict__ bias,
-                const ChanAffine bn, const double* __restrict__ Vin, int64_t ld_in,
+                const ChanAffine bn, const RowMask mask, const double* __restrict__ Vin, int64_t ld_in,
                 double* __restrict__ Vout, int64_t ld_out, int64_t ncols, int64_t n_center) {
     constexpr int BN = WARPS_N * WN_TILES * 8;
     constexpr int THREADS = WARPS_M * WARPS_N * 32;
@@ -60,6 +60,7 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
     double* wts = smem + STAGES * p.halo_stage;           // [STAGES][w_stage]
     double* chan = wts + STAGES * p.w_stage;              // [5][BN]: bias, mean, 1/den, scale, offset
     int* gtab = reinterpret_cast<int*>(chan + 5 * BN);    // [plane]
+    int* mtab = gtab + p.plane;                           // [plane] row-state offset, -1 = column not masked
 
     const int tid = threadIdx.x;
     const int lane = tid & 31;
@@ -90,10 +91,14 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
         const int hl = r2 - wl * p.HH;
         const int hi = oh0 * p.g.sh - p.g.pad_t + hl;
         const int wi = ow0 * p.g.sw - p.g.pad_l + wl;
-        int off = -1;
-        if (hi >= 0 && hi < H && wi >= 0 && wi < W && j0 + jl < ncols)
+        int off = -1, moff = -1;
+        if (hi >= 0 && hi < H && wi >= 0 && wi < W && j0 + jl < ncols) {
             off = int(jl * ld_in) + hi + H * wi;
+            // rows cleared by the preceding ReLU step are masked here instead of being zeroed in memory
+            if (mask.state != nullptr && j0 + jl < mask.ncols) moff = int(mask.col_q[j0 + jl] * mask.N) + hi + H * wi;
+        }
         gtab[r] = off;
+        mtab[r] = moff;
     }
     // per-channel epilogue constants of this channel tile
     const bool has_bn = bn.rden != nullptr;
@@ -120,10 +125,33 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
             const bool ci_ok = ci < p.g.Cin;
             const double* src_c = in_base + int64_t(ci_ok ? ci : 0) * hw_in;
             double* dst_c = hs + cil * p.PS;
-            for (int r = lane; r < p.plane; r += 32) {
-                const int off = gtab[r];
-                const bool ok = ci_ok && off >= 0;
-                cp_async8(dst_c + r, ok ? (src_c + off) : Vin, ok ? 8 : 0);
+            if (mask.state == nullptr) {
+                for (int r = lane; r < p.plane; r += 32) {
+                    const int off = gtab[r];
+                    const bool ok = ci_ok && off >= 0;
+                    cp_async8(dst_c + r, ok ? (src_c + off) : Vin, ok ? 8 : 0);
+                }
+            } else {
+                // four elements per lane at a time, so that the row-state loads are in flight together
+                const uint8_t* st_c = mask.state + int64_t(ci_ok ? ci : 0) * hw_in;
+                for (int r0 = lane; r0 < p.plane; r0 += 128) {
+                    int off[4];
+                    uint8_t sv[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int r = r0 + 32 * u;
+                        off[u] = (r < p.plane && ci_ok) ? gtab[r] : -1;
+                        const int moff = (r < p.plane && ci_ok) ? mtab[r] : -1;
+                        sv[u] = moff >= 0 ? st_c[moff] : uint8_t(0);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int r = r0 + 32 * u;
+                        if (r >= p.plane) break;
+                        const bool ok = off[u] >= 0 && sv[u] == 0;
+                        cp_async8(dst_c + r, ok ? (src_c + off[u]) : Vin, ok ? 8 : 0);
+                    }
+                }
             }
         }
         double* ws = wts + stage * p.w_stage;
@@ -241,6 +269,41 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
     }
 }
 
+// Convolution of one-hot columns.  A column the preceding ReLU step appended is the unit vector of
+// neuron (h, w, ci); its image under the convolution is the filter footprint
+//   out(oh, ow, co) = W(kh, kw, ci, co)   wherever oh*sh - pt + kh*dh = h and ow*sw - pl + kw*dw = w,
+// times the generator part of the fused affine.  No products are formed, so the values equal what the
+// dense contraction of that column gives (every other term of its sums is a product with zero).
+// The output block is zero filled beforehand.  One block per column, lanes over (tap, output channel);
+// this rank's column t is the batch-wide column c = c_first + t*c_step with neuron rec_idx[c].
+__global__ void __launch_bounds__(128)
+conv_onehot_kernel(ConvGeom g, const double* __restrict__ Wg, int bn_tile, int cs, int n_chunks, ChanAffine bn,
+                   const int32_t* __restrict__ rec_idx, int64_t c_first, int64_t c_step,
+                   double* __restrict__ Vout, int64_t ld_out) {
+    const int64_t t = blockIdx.x;
+    const int i = rec_idx[c_first + t * c_step];
+    const int h = i % g.H;
+    const int w = (i / g.H) % g.W;
+    const int ci = i / (g.H * g.W);
+    const int taps = g.kh * g.kw;
+    const int ch = ci / KC, cil = ci % KC;
+    double* dst = Vout + t * ld_out;
+    for (int e = threadIdx.x; e < taps * g.Cout; e += blockDim.x) {
+        const int co = e % g.Cout;
+        const int tap = e / g.Cout;
+        const int khi = tap % g.kh, kwi = tap / g.kh;
+        const int hn = h + g.pad_t - khi * g.dh;
+        const int wn = w + g.pad_l - kwi * g.dw;
+        if (hn < 0 || wn < 0 || hn % g.sh != 0 || wn % g.sw != 0) continue;
+        const int oh = hn / g.sh, ow = wn / g.sw;
+        if (oh >= g.Ho || ow >= g.Wo) continue;
+        const int nt = co / bn_tile, n = co % bn_tile;
+        double v = Wg[((((int64_t(nt) * n_chunks + ch) * taps + tap) * KC + cil) * cs) + n];
+        if (bn.rden != nullptr) v = (v * bn.rden[co]) * bn.scale[co];
+        dst[oh + int64_t(g.Ho) * (ow + int64_t(g.Wo) * co)] = v;
+    }
+}
+
 int pad_stride(int n) {            // smallest s >= n with s = 4 (mod 8)
     int s = (n + 7) / 8 * 8 + 4;
     if (s - 8 >= n) s -= 8;
@@ -272,17 +335,18 @@ void pick_tile(const ConvGeom& g, int BM, int* TH, int* TW, int* NJ) {
 
 template <int WM_TILES, int WN_TILES, int WARPS_M, int WARPS_N, int STAGES, int MIN_BLOCKS>
 int launch_variant(cudaStream_t st, const ConvParams& p, dim3 grid, size_t smem, const ConvWeights& w,
-                   const ChanAffine& bn, const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
-                   int64_t ncols, int64_t n_center) {
+                   const ChanAffine& bn, const RowMask& mask, const double* Vin, int64_t ld_in, double* Vout,
+                   int64_t ld_out, int64_t ncols, int64_t n_center) {
     auto kern = conv_f64_kernel<WM_TILES, WN_TILES, WARPS_M, WARPS_N, STAGES, MIN_BLOCKS>;
     NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, WARPS_M * WARPS_N * 32, smem, st>>>(p, w.w, w.bias, bn, Vin, ld_in, Vout, ld_out, ncols, n_center);
+    kern<<<grid, WARPS_M * WARPS_N * 32, smem, st>>>(p, w.w, w.bias, bn, mask, Vin, ld_in, Vout, ld_out, ncols,
+                                                     n_center);
     NNVB_CUDA(cudaGetLastError());
     return NNVB_OK;
 }
 
 template <int WM_TILES, int WN_TILES, int WARPS_M, int WARPS_N>
-int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
+int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn, const RowMask& mask,
                const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out, int64_t ncols,
                int64_t n_center) {
     constexpr int BM = WARPS_M * WM_TILES * 16;
@@ -311,7 +375,7 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
         return NNVB_E_UNSUPPORTED;
     }
     const size_t stage_bytes = size_t(p.halo_stage + p.w_stage) * sizeof(double);
-    const size_t fixed_bytes = size_t(5 * BN) * sizeof(double) + size_t(p.plane) * sizeof(int);
+    const size_t fixed_bytes = size_t(5 * BN) * sizeof(double) + size_t(2 * p.plane) * sizeof(int);
     const size_t limit = 227 * 1024;
     const int64_t blocks = p.col_groups * p.n_th * p.n_tw;
     if (blocks >= (int64_t(1) << 31)) {
@@ -325,13 +389,13 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
     const size_t two = 2 * stage_bytes + fixed_bytes;
     const size_t three = 3 * stage_bytes + fixed_bytes;
     if ((variant == 0 || variant == 2) && 2 * (two + 1024) <= limit)
-        return launch_variant<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 2, 2>(st, p, grid, two, w, bn, Vin, ld_in, Vout,
+        return launch_variant<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 2, 2>(st, p, grid, two, w, bn, mask, Vin, ld_in, Vout,
                                                                          ld_out, ncols, n_center);
     if (three <= limit)
-        return launch_variant<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 3, 1>(st, p, grid, three, w, bn, Vin, ld_in, Vout,
+        return launch_variant<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 3, 1>(st, p, grid, three, w, bn, mask, Vin, ld_in, Vout,
                                                                          ld_out, ncols, n_center);
     if (two <= limit)
-        return launch_variant<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 2, 1>(st, p, grid, two, w, bn, Vin, ld_in, Vout,
+        return launch_variant<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 2, 1>(st, p, grid, two, w, bn, mask, Vin, ld_in, Vout,
                                                                          ld_out, ncols, n_center);
     set_error("conv: filter %dx%d with stride (%d,%d) needs %zu bytes of shared memory per stage", g.kh, g.kw, g.sh,
               g.sw, stage_bytes);
@@ -370,18 +434,30 @@ void conv_arrange_weights(const ConvGeom& g, const double* W, double* dst, int b
 }
 
 int launch_conv_f64(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
-                    const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
+                    const RowMask& mask, const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
                     int64_t ncols, int64_t n_center, int64_t* launches) {
     if (ncols <= 0) return NNVB_OK;
     int s;
     if (w.bn_tile == 16)
-        s = launch_cfg<1, 2, 8, 1>(st, g, w, bn, Vin, ld_in, Vout, ld_out, ncols, n_center);
+        s = launch_cfg<1, 2, 8, 1>(st, g, w, bn, mask, Vin, ld_in, Vout, ld_out, ncols, n_center);
     else if (w.bn_tile == 32)
-        s = launch_cfg<2, 2, 4, 2>(st, g, w, bn, Vin, ld_in, Vout, ld_out, ncols, n_center);
+        s = launch_cfg<2, 2, 4, 2>(st, g, w, bn, mask, Vin, ld_in, Vout, ld_out, ncols, n_center);
     else
-        s = launch_cfg<2, 4, 4, 2>(st, g, w, bn, Vin, ld_in, Vout, ld_out, ncols, n_center);
+        s = launch_cfg<2, 4, 4, 2>(st, g, w, bn, mask, Vin, ld_in, Vout, ld_out, ncols, n_center);
     if (s == NNVB_OK && launches) *launches += 1;
     return s;
+}
+
+int launch_conv_onehot(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
+                       const int32_t* rec_idx, int64_t c_first, int64_t c_step, int64_t K_loc, double* Vout,
+                       int64_t ld_out, int64_t* launches) {
+    if (K_loc <= 0) return NNVB_OK;
+    NNVB_CUDA(cudaMemsetAsync(Vout, 0, sizeof(double) * ld_out * K_loc, st));
+    conv_onehot_kernel<<<(unsigned)K_loc, 128, 0, st>>>(g, w.w, w.bn_tile, w.cs, w.n_chunks, bn, rec_idx, c_first,
+                                                       c_step, Vout, ld_out);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
 }
 
 }  // namespace nnvb

@@ -47,7 +47,8 @@ __global__ void bn_f64_kernel(ChanAffine bn, int64_t plane, int64_t N, double* _
 // AveragePooling2DLayer.compute_averageMap, AveragePooling2DLayer.m:316-393: window sum in
 // row-major order of the window, divided by ph*pw (zero padding counted).
 // One thread per output element of a column; grid.y walks the columns.
-__global__ void avgpool_f64_kernel(PoolGeom g, const double* __restrict__ Vin, int64_t ld_in,
+// Rows that the preceding ReLU step cleared are read as zero through `mask` (they were not zeroed in memory).
+__global__ void avgpool_f64_kernel(PoolGeom g, RowMask mask, const double* __restrict__ Vin, int64_t ld_in,
                                    double* __restrict__ Vout, int64_t ld_out, int64_t ncols) {
     const int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     const int64_t n_out = int64_t(g.Ho) * g.Wo * g.C;
@@ -61,17 +62,44 @@ __global__ void avgpool_f64_kernel(PoolGeom g, const double* __restrict__ Vin, i
     const int64_t cbase = int64_t(c) * g.H * g.W;
     for (int64_t j = blockIdx.y; j < ncols; j += gridDim.y) {
         const double* src = Vin + j * ld_in + cbase;
+        const uint8_t* st = (mask.state != nullptr && j < mask.ncols) ? mask.state + mask.col_q[j] * mask.N + cbase
+                                                                      : nullptr;
         double acc = 0.0;
         for (int a = 0; a < g.ph; ++a) {
             const int h = h0 + a;
             for (int b = 0; b < g.pw; ++b) {
                 const int w = w0 + b;
                 double v = 0.0;
-                if (h >= 0 && h < g.H && w >= 0 && w < g.W) v = src[h + int64_t(g.H) * w];
+                if (h >= 0 && h < g.H && w >= 0 && w < g.W) {
+                    const int64_t o_in = h + int64_t(g.H) * w;
+                    if (st == nullptr || st[o_in] == 0) v = src[o_in];
+                }
                 acc = acc + v;
             }
         }
         Vout[j * ld_out + o] = acc / div;
+    }
+}
+
+// Average pooling of one-hot columns (unit vector of neuron (h,w,c)): 1/(ph*pw) at every output
+// position whose window covers (h,w); the output block is zero filled beforehand.  One thread per column.
+__global__ void avgpool_onehot_kernel(PoolGeom g, const int32_t* __restrict__ rec_idx, int64_t c_first,
+                                      int64_t c_step, int64_t K_loc, double* __restrict__ Vout, int64_t ld_out) {
+    const int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= K_loc) return;
+    const int i = rec_idx[c_first + t * c_step];
+    const int h = i % g.H, w = (i / g.H) % g.W, c = i / (g.H * g.W);
+    // same arithmetic as the dense kernel on this column: a sum of zeros and a single one, then the division
+    const double val = (0.0 + 1.0) / double(g.ph * g.pw);
+    double* dst = Vout + t * ld_out + int64_t(c) * g.Ho * g.Wo;
+    for (int a = 0; a < g.ph; ++a) {
+        const int hn = h + g.pad_t - a;
+        if (hn < 0 || hn % g.sh != 0 || hn / g.sh >= g.Ho) continue;
+        for (int b = 0; b < g.pw; ++b) {
+            const int wn = w + g.pad_l - b;
+            if (wn < 0 || wn % g.sw != 0 || wn / g.sw >= g.Wo) continue;
+            dst[hn / g.sh + int64_t(g.Ho) * (wn / g.sw)] = val;
+        }
     }
 }
 
@@ -162,13 +190,24 @@ int launch_bn_f64(cudaStream_t st, const ChanAffine& bn, int64_t plane, int64_t 
     return NNVB_OK;
 }
 
-int launch_avgpool_f64(cudaStream_t st, const PoolGeom& g, const double* Vin, int64_t ld_in,
+int launch_avgpool_onehot(cudaStream_t st, const PoolGeom& g, const int32_t* rec_idx, int64_t c_first,
+                          int64_t c_step, int64_t K_loc, double* Vout, int64_t ld_out, int64_t* launches) {
+    if (K_loc <= 0) return NNVB_OK;
+    NNVB_CUDA(cudaMemsetAsync(Vout, 0, sizeof(double) * ld_out * K_loc, st));
+    avgpool_onehot_kernel<<<(unsigned)ceil_div(K_loc, 128), 128, 0, st>>>(g, rec_idx, c_first, c_step, K_loc, Vout,
+                                                                         ld_out);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_avgpool_f64(cudaStream_t st, const PoolGeom& g, const RowMask& mask, const double* Vin, int64_t ld_in,
                        double* Vout, int64_t ld_out, int64_t ncols, int64_t* launches) {
     if (ncols <= 0) return NNVB_OK;
     const int threads = 256;
     const int64_t n_out = int64_t(g.Ho) * g.Wo * g.C;
     dim3 grid((unsigned)ceil_div(n_out, threads), (unsigned)std::min<int64_t>(ncols, 65535));
-    avgpool_f64_kernel<<<grid, threads, 0, st>>>(g, Vin, ld_in, Vout, ld_out, ncols);
+    avgpool_f64_kernel<<<grid, threads, 0, st>>>(g, mask, Vin, ld_in, Vout, ld_out, ncols);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;

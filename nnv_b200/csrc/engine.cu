@@ -9,6 +9,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <string>
@@ -203,6 +204,11 @@ struct nnvb_batch {
     // working state: the buffers live in the context (one reach at a time per context)
     WorkBufs* wk = nullptr;
     int list_cur = 0;
+    // work a ReLU step left to the layer that follows it (see relu_step)
+    int64_t pend_mask_ncols = 0;         // > 0: rows with state != 0 of columns [0, n) read as zero
+    int64_t pend_mask_N = 0;
+    int64_t pend_onehot = 0;             // > 0: the last n columns are implicit unit vectors
+    ReluLayerRecord* pend_rec = nullptr; // ... of the neurons listed in this record
     std::vector<int64_t> h_qcol_off;     // [nq+1]
     int64_t ncols = 0;
     int64_t N = 0, ld = 0;
@@ -889,7 +895,9 @@ int make_writable(nnvb_batch* b, int64_t extra_cols) {
     return NNVB_OK;
 }
 
-int relu_step(nnvb_batch* b, ReluLayerRecord* rec) {
+// lazy_mask: do not clear the dead/crossing rows in memory; the next layer reads them as zero.
+// lazy_onehot: do not materialise the appended unit-vector columns; the next layer writes their images.
+int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_onehot) {
     nnvb_ctx* ctx = b->net->ctx;
     cudaStream_t st = ctx->stream;
     const int nq = b->nq;
@@ -1034,10 +1042,11 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec) {
     {
         ProfScope ps(ctx, NNVB_PROF_RELAX, relax_bytes);
         if (K > 0) NNVB_TRY(launch_rank_cross(st, w, r, &ctx->launches));
-        if (K > 0 || rec->n_dead > 0)
+        if (b->opts.keep_constraints) lazy_mask = false;     // the row-clearing kernel also saves the crossing rows
+        if ((K > 0 || rec->n_dead > 0) && !lazy_mask)
             NNVB_TRY(launch_relu_zero_rows(st, w, ncols_old, b->wk->col_q.as<int32_t>(), r, b->wk->col_pos.as<int64_t>(),
                                            &ctx->launches));
-        NNVB_TRY(launch_relu_append(st, w, ncols_old, K_loc, rank, world,
+        NNVB_TRY(launch_relu_append(st, w, ncols_old, K_loc, rank, world, !lazy_onehot,
                                     world > 1 ? rec->P_in_dev.as<int64_t>() : nullptr, r, b->wk->col_q.as<int32_t>(),
                                     b->wk->pl.as<double>(), b->wk->pu.as<double>(), b->wk->col_pos.as<int64_t>(),
                                     b->wk->qcol_off[nxt].as<int64_t>(), b->wk->qcol_idx[nxt].as<int32_t>(),
@@ -1049,6 +1058,10 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec) {
     for (int q = 0; q < nq; ++q) b->h_Pglob[q] += rec->new_off[q + 1] - rec->new_off[q];
     b->ncols = ncols_old + K_loc;
     rec->cols_after = b->ncols;
+    b->pend_mask_ncols = (lazy_mask && (K > 0 || rec->n_dead > 0)) ? ncols_old : 0;
+    b->pend_mask_N = N;
+    b->pend_onehot = lazy_onehot ? K_loc : 0;
+    b->pend_rec = rec;
     return NNVB_OK;
 }
 
@@ -1065,23 +1078,48 @@ int run_layers(nnvb_batch* b) {
             const size_t need = size_t(ld_out) * b->ncols * sizeof(double);
             if (need > ctx->vbuf_bytes()) return capacity_error("layer output", need, ctx->vbuf_bytes());
             double* out = other_vbuf(b);
+            // columns the layer contracts densely, and the unit-vector columns whose images it writes directly
+            const int64_t n_dense = b->ncols - b->pend_onehot;
+            const int64_t n_hot = b->pend_onehot;
+            const int32_t* hot_idx = n_hot > 0 ? b->pend_rec->idx.as<int32_t>() : nullptr;
+            RowMask mask{nullptr, nullptr, 0, 0};
+            if (b->pend_mask_ncols > 0)
+                mask = RowMask{b->wk->state.as<uint8_t>(), b->wk->col_q.as<int32_t>(), b->pend_mask_ncols, b->pend_mask_N};
             if (L.type == NNVB_LAYER_CONV2D) {
                 ChanAffine bn{nullptr, nullptr, nullptr, nullptr, nullptr};
                 if (L.fused_bn >= 0) {
                     const Layer& B = net->layers[L.fused_bn];
                     bn = ChanAffine{B.bn_mean, B.bn_den, B.bn_rden, B.bn_scale, B.bn_offset};
                 }
-                ProfScope ps(ctx, NNVB_PROF_CONV, 2.0 * L.cg.Ho * L.cg.Wo * L.cg.Cout * L.cg.kh * L.cg.kw * L.cg.Cin * double(b->ncols));
-                NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, b->V, b->ld, out, ld_out, b->ncols, b->nq,
-                                         &ctx->launches));
+                {
+                    ProfScope ps(ctx, NNVB_PROF_CONV,
+                                 2.0 * L.cg.Ho * L.cg.Wo * L.cg.Cout * L.cg.kh * L.cg.kw * L.cg.Cin * double(n_dense));
+                    NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, mask, b->V, b->ld, out, ld_out, n_dense, b->nq,
+                                             &ctx->launches));
+                }
+                ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(Nout) * double(n_hot));
+                NNVB_TRY(launch_conv_onehot(st, L.cg, L.cw, bn, hot_idx, ctx->rank, ctx->world, n_hot,
+                                            out + n_dense * ld_out, ld_out, &ctx->launches));
             } else if (L.type == NNVB_LAYER_FC) {
-                ProfScope ps(ctx, NNVB_PROF_FC, 2.0 * double(L.Co) * double(L.H * L.W * L.C) * double(b->ncols));
-                NNVB_TRY(launch_fc_f64(st, int(L.H * L.W * L.C), int(L.Co), L.fc_wt, L.fc_ldw, L.bias, b->V, b->ld,
-                                       out, ld_out, b->ncols, b->nq, &ctx->launches));
+                {
+                    ProfScope ps(ctx, NNVB_PROF_FC, 2.0 * double(L.Co) * double(L.H * L.W * L.C) * double(n_dense));
+                    NNVB_TRY(launch_fc_f64(st, int(L.H * L.W * L.C), int(L.Co), L.fc_wt, L.fc_ldw, L.bias, b->V, b->ld,
+                                           out, ld_out, n_dense, b->nq, &ctx->launches));
+                }
+                ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(Nout) * double(n_hot));
+                NNVB_TRY(launch_fc_onehot(st, int(L.Co), L.fc_wt, L.fc_ldw, hot_idx, ctx->rank, ctx->world, n_hot,
+                                          out + n_dense * ld_out, ld_out, &ctx->launches));
             } else {
-                ProfScope ps(ctx, NNVB_PROF_AVGPOOL, 8.0 * double(b->N + Nout) * double(b->ncols));
-                NNVB_TRY(launch_avgpool_f64(st, L.pg, b->V, b->ld, out, ld_out, b->ncols, &ctx->launches));
+                {
+                    ProfScope ps(ctx, NNVB_PROF_AVGPOOL, 8.0 * double(b->N + Nout) * double(n_dense));
+                    NNVB_TRY(launch_avgpool_f64(st, L.pg, mask, b->V, b->ld, out, ld_out, n_dense, &ctx->launches));
+                }
+                ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(Nout) * double(n_hot));
+                NNVB_TRY(launch_avgpool_onehot(st, L.pg, hot_idx, ctx->rank, ctx->world, n_hot, out + n_dense * ld_out,
+                                               ld_out, &ctx->launches));
             }
+            b->pend_mask_ncols = 0;
+            b->pend_onehot = 0;
             b->V = out;
             b->N = Nout;
             b->ld = ld_out;
@@ -1093,7 +1131,16 @@ int run_layers(nnvb_batch* b) {
                 NNVB_TRY(launch_bn_f64(st, bn, L.H * L.W, b->N, b->V, b->ld, b->ncols, b->nq, &ctx->launches));
             }
         } else if (L.type == NNVB_LAYER_RELU) {
-            NNVB_TRY(relu_step(b, b->wk->relu[relu_i].get()));
+            // what follows decides how much of the step can be left to it: a convolution or pooling layer
+            // masks the cleared rows while loading and writes the images of the new unit-vector columns;
+            // a fully connected layer does the latter only
+            static const bool eager = getenv("NNVB_EAGER_RELU") != nullptr;
+            int nt = li + 1 < net->layers.size() ? net->layers[li + 1].type : 0;
+            static const bool eager_mask = getenv("NNVB_EAGER_MASK") != nullptr;
+            const bool lazy_mask = !eager && !eager_mask && (nt == NNVB_LAYER_CONV2D || nt == NNVB_LAYER_AVGPOOL2D) &&
+                                   int64_t(b->nq) * b->N < (int64_t(1) << 31);     // the mask offsets are 32-bit
+            const bool lazy_onehot = !eager && (nt == NNVB_LAYER_CONV2D || nt == NNVB_LAYER_AVGPOOL2D || nt == NNVB_LAYER_FC);
+            NNVB_TRY(relu_step(b, b->wk->relu[relu_i].get(), lazy_mask, lazy_onehot));
             ++relu_i;
         }
         b->shape[0] = L.Ho; b->shape[1] = L.Wo; b->shape[2] = L.Co;
@@ -1185,14 +1232,14 @@ int witness_forward(nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, i
                 const Layer& B = net->layers[L.fused_bn];
                 bn = ChanAffine{B.bn_mean, B.bn_den, B.bn_rden, B.bn_scale, B.bn_offset};
             }
-            NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, cur, ld, oth, ld_out, n, n, &ctx->launches));
+            NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, RowMask{nullptr, nullptr, 0, 0}, cur, ld, oth, ld_out, n, n, &ctx->launches));
             std::swap(cur, oth); N = Nout; ld = ld_out;
         } else if (L.type == NNVB_LAYER_FC) {
             NNVB_TRY(launch_fc_f64(st, int(L.H * L.W * L.C), int(L.Co), L.fc_wt, L.fc_ldw, L.bias, cur, ld, oth, ld_out, n,
                                    n, &ctx->launches));
             std::swap(cur, oth); N = Nout; ld = ld_out;
         } else if (L.type == NNVB_LAYER_AVGPOOL2D) {
-            NNVB_TRY(launch_avgpool_f64(st, L.pg, cur, ld, oth, ld_out, n, &ctx->launches));
+            NNVB_TRY(launch_avgpool_f64(st, L.pg, RowMask{nullptr, nullptr, 0, 0}, cur, ld, oth, ld_out, n, &ctx->launches));
             std::swap(cur, oth); N = Nout; ld = ld_out;
         } else if (L.type == NNVB_LAYER_BN) {
             if (!L.fused_into_prev) {
@@ -1335,6 +1382,8 @@ int nnvb_batch_reach(nnvb_batch* b, const nnvb_opts* opts) {
     b->have_out_ranges = false;
     ctx->result_owner = b;
     while ((int)b->wk->relu.size() < b->net->n_relu) b->wk->relu.emplace_back(new ReluLayerRecord());
+    b->pend_mask_ncols = 0;
+    b->pend_onehot = 0;
     NNVB_TRY(init_sets(b));
     NNVB_TRY(run_layers(b));
     b->reached = true;

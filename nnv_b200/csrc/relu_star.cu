@@ -295,7 +295,7 @@ zero_rows_kernel(int nq, int64_t N, int64_t ld, double* __restrict__ V, int64_t 
 // their predicate range [0, ub].  With the generators sharded over `world`
 // ranks, new column c (numbered over the whole batch) lives on rank c % world;
 // this rank materialises its K_loc columns t -> c = rank + t*world.
-__global__ void append_cols_kernel(int64_t K_loc, int rank, int world, int64_t ld, double* __restrict__ V,
+__global__ void append_cols_kernel(int64_t K_loc, int rank, int world, int write_v, int64_t ld, double* __restrict__ V,
                                    int64_t ncols_old, const int32_t* __restrict__ rec_idx,
                                    const int32_t* __restrict__ rec_q, const double* __restrict__ rec_u,
                                    const int64_t* __restrict__ q_new_off, const int64_t* __restrict__ qcol_off,
@@ -307,7 +307,7 @@ __global__ void append_cols_kernel(int64_t K_loc, int rank, int world, int64_t l
     const int64_t c = rank + t * world;
     const int64_t col = ncols_old + t;
     const int q = rec_q[c];
-    V[col * ld + rec_idx[c]] = 1.0;
+    if (write_v) V[col * ld + rec_idx[c]] = 1.0;     // else the column stays implicit until the next layer
     col_q[col] = q;
     pl[col] = 0.0;
     pu[col] = rec_u[c];
@@ -636,11 +636,12 @@ int launch_relu_zero_rows(cudaStream_t st, const ReluWork& w, int64_t ncols, con
 }
 
 int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, int64_t K_loc, int rank, int world,
-                       const int64_t* P_in, const ReluRecord& rec, int32_t* col_q, double* pl, double* pu,
+                       bool materialize, const int64_t* P_in, const ReluRecord& rec, int32_t* col_q, double* pl, double* pu,
                        int64_t* col_pos, int64_t* new_qcol_off, int32_t* new_qcol_idx, int64_t* launches) {
     if (K_loc > 0) {
-        NNVB_CUDA(cudaMemsetAsync(w.V + ncols_old * w.ld, 0, sizeof(double) * w.ld * K_loc, st));
-        append_cols_kernel<<<(unsigned)ceil_div(K_loc, 256), 256, 0, st>>>(K_loc, rank, world, w.ld, w.V, ncols_old,
+        if (materialize) NNVB_CUDA(cudaMemsetAsync(w.V + ncols_old * w.ld, 0, sizeof(double) * w.ld * K_loc, st));
+        append_cols_kernel<<<(unsigned)ceil_div(K_loc, 256), 256, 0, st>>>(K_loc, rank, world, materialize ? 1 : 0,
+                                                                          w.ld, w.V, ncols_old,
                                                                           rec.idx, rec.q, rec.u, w.q_new_off,
                                                                           w.qcol_off, P_in, col_q, pl, pu, col_pos);
         NNVB_CUDA(cudaGetLastError());
