@@ -85,13 +85,23 @@ struct RowMask {
     int64_t N;
 };
 
+// Windowed columns: column j (absolute index) is exactly zero outside the input window that starts at
+// (h0[j], w0[j]) (may lie partly outside the image); wh x ww is the size of the OUTPUT patch the layer
+// computes for each such column.  h0 == nullptr: dense columns.
+struct ColWindows {
+    const int32_t* h0;
+    const int32_t* w0;
+    int wh, ww;
+};
+
 size_t conv_weights_doubles(const ConvGeom& g, int* bn_tile, int* cs, int* n_tiles, int* n_chunks);
 // Host-side re-layout of W[kh,kw,Cin,Cout] (column-major) into the kernel's layout.
 void conv_arrange_weights(const ConvGeom& g, const double* W, double* dst, int bn_tile, int cs,
                           int n_tiles, int n_chunks);
 
+// Processes columns [col_base, col_base + ncols) of Vin / Vout (pointers to column 0).
 int launch_conv_f64(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
-                    const RowMask& mask, const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
+                    const RowMask& mask, const ColWindows& win, int64_t col_base, const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
                     int64_t ncols, int64_t n_center, int64_t* launches);
 
 // Images of the one-hot columns a ReLU step appended (column t of this rank is batch-wide column
@@ -175,7 +185,8 @@ int launch_relu_zero_rows(cudaStream_t st, const ReluWork& w, int64_t ncols, con
 // materialize = false leaves the new columns implicit (only their metadata is written).
 int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, int64_t K_loc, int rank, int world,
                        bool materialize, const int64_t* P_in, const ReluRecord& rec, int32_t* col_q, double* pl, double* pu,
-                       int64_t* col_pos, int64_t* new_qcol_off, int32_t* new_qcol_idx, int64_t* launches);
+                       int64_t* col_pos, int img_h, int img_w, int32_t* win_h0, int32_t* win_w0,
+                       int64_t* new_qcol_off, int32_t* new_qcol_idx, int64_t* launches);
 
 // Halfspace rows against output sets; see relu_star.cu.  Pair p tests row G[p] (length Nout)
 // with offset g[p] on query pair_q[p]; margin[p] = box minimum of G x - g (nullable);
@@ -201,7 +212,11 @@ int launch_witness_value(cudaStream_t st, int n_pairs, int64_t Nout, int64_t ld,
 // Build the dense input set of a bounds-form query batch.
 int launch_build_from_bounds(cudaStream_t st, int nq, int64_t N, int64_t ld, const double* lbub,
                              const int64_t* q_gen_off, int rank, int world, double* V, int32_t* col_q, double* pl,
-                             double* pu, int32_t* qcol_idx, int64_t* col_pos, int64_t* launches);
+                             double* pu, int32_t* qcol_idx, int64_t* col_pos, int img_h, int img_w, int32_t* win_h0,
+                             int32_t* win_w0, int64_t* launches);
+// Move the window origins of columns [0, n) through a convolution / pooling layer.
+int launch_update_windows(cudaStream_t st, int64_t n, int32_t* h0, int32_t* w0, int pad_t, int pad_l, int ext_h,
+                          int ext_w, int sh, int sw, int64_t* launches);
 int launch_count_bounds(cudaStream_t st, int nq, int64_t N, const double* lbub, int64_t* q_count,
                         int64_t* launches);
 

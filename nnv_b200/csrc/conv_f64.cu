@@ -49,8 +49,9 @@ struct ConvParams {
 template <int WM_TILES, int WN_TILES, int WARPS_M, int WARPS_N, int STAGES, int MIN_BLOCKS>
 __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32, MIN_BLOCKS)
 conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double* __restrict__ bias,
-                const ChanAffine bn, const RowMask mask, const double* __restrict__ Vin, int64_t ld_in,
-                double* __restrict__ Vout, int64_t ld_out, int64_t ncols, int64_t n_center) {
+                const ChanAffine bn, const RowMask mask, const ColWindows win, int64_t col_base,
+                const double* __restrict__ Vin, int64_t ld_in, double* __restrict__ Vout, int64_t ld_out,
+                int64_t ncols, int64_t n_center) {
     constexpr int BN = WARPS_N * WN_TILES * 8;
     constexpr int THREADS = WARPS_M * WARPS_N * 32;
     constexpr int NWARPS = WARPS_M * WARPS_N;
@@ -83,19 +84,38 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
     const int H = p.g.H, W = p.g.W;
     const int hw_in = H * W;
 
+    // Origin of each column's output patch.  Dense columns: the spatial tile.  Windowed columns: every
+    // column is zero outside a small window [h0, h0+wh) x [w0, w0+ww) of the input; the outputs that
+    // can be non-zero form a TH x TW patch starting at ceil((h0 + pad - (k-1)*dil) / stride), and only
+    // that patch is computed (the rest of the output column was zero filled).
+    __shared__ int org_h[128], org_w[128];
+    if (tid < p.NJ) {
+        int a = oh0, b2 = ow0;
+        if (win.h0 != nullptr && j0 + tid < ncols) {
+            const int ah = win.h0[col_base + j0 + tid] + p.g.pad_t - (p.g.kh - 1) * p.g.dh;
+            const int aw = win.w0[col_base + j0 + tid] + p.g.pad_l - (p.g.kw - 1) * p.g.dw;
+            a = ah >= 0 ? (ah + p.g.sh - 1) / p.g.sh : -((-ah) / p.g.sh);
+            b2 = aw >= 0 ? (aw + p.g.sw - 1) / p.g.sw : -((-aw) / p.g.sw);
+        }
+        org_h[tid] = a;
+        org_w[tid] = b2;
+    }
+    __syncthreads();
+
     // table: halo element r -> offset in the input relative to column j0, channel 0
     for (int r = tid; r < p.plane; r += THREADS) {
         const int jl = r / (p.HH * p.HW);
         const int r2 = r - jl * (p.HH * p.HW);
         const int wl = r2 / p.HH;
         const int hl = r2 - wl * p.HH;
-        const int hi = oh0 * p.g.sh - p.g.pad_t + hl;
-        const int wi = ow0 * p.g.sw - p.g.pad_l + wl;
+        const int hi = org_h[jl] * p.g.sh - p.g.pad_t + hl;
+        const int wi = org_w[jl] * p.g.sw - p.g.pad_l + wl;
         int off = -1, moff = -1;
         if (hi >= 0 && hi < H && wi >= 0 && wi < W && j0 + jl < ncols) {
             off = int(jl * ld_in) + hi + H * wi;
             // rows cleared by the preceding ReLU step are masked here instead of being zeroed in memory
-            if (mask.state != nullptr && j0 + jl < mask.ncols) moff = int(mask.col_q[j0 + jl] * mask.N) + hi + H * wi;
+            if (mask.state != nullptr && col_base + j0 + jl < mask.ncols)
+                moff = int(mask.col_q[col_base + j0 + jl] * mask.N) + hi + H * wi;
         }
         gtab[r] = off;
         mtab[r] = moff;
@@ -113,7 +133,7 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
     }
     __syncthreads();
 
-    const double* in_base = Vin + j0 * ld_in;
+    const double* in_base = Vin + (col_base + j0) * ld_in;
     const int64_t w_block = int64_t(p.w_stage);
     const double* w_base = Wg + (int64_t(n_tile) * p.n_chunks) * w_block;
 
@@ -173,8 +193,8 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
             int rem = m - jl * per_col;
             int owl = rem / p.TH;
             int ohl = rem - owl * p.TH;
-            const int oh = oh0 + ohl, ow = ow0 + owl;
-            const bool ok = jl < p.NJ && oh < p.g.Ho && ow < p.g.Wo && j0 + jl < ncols;
+            const int oh = org_h[jl < p.NJ ? jl : 0] + ohl, ow = org_w[jl < p.NJ ? jl : 0] + owl;
+            const bool ok = jl < p.NJ && oh >= 0 && ow >= 0 && oh < p.g.Ho && ow < p.g.Wo && j0 + jl < ncols;
             outoff[mi][half] = ok ? int(jl * ld_out) + oh + p.g.Ho * ow : -1;
             if (jl >= p.NJ) { jl = 0; owl = 0; ohl = 0; }   // padding rows read a valid address
             rowbase[mi][half] = jl * (p.HH * p.HW) + (owl * p.g.sw) * p.HH + ohl * p.g.sh;
@@ -242,7 +262,7 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
     // 8-byte store per element (8 lanes cover 64 contiguous bytes along h)
     const int64_t hw_out = int64_t(p.g.Ho) * p.g.Wo;
     const int per_col = p.TH * p.TW;
-    double* out_base = Vout + j0 * ld_out;
+    double* out_base = Vout + (col_base + j0) * ld_out;
 #pragma unroll
     for (int mi = 0; mi < WM_TILES; ++mi) {
 #pragma unroll
@@ -250,7 +270,7 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
             const int off = outoff[mi][half];
             if (off < 0) continue;
             const int m = wm * WM_TILES * 16 + mi * 16 + g + half * 8;
-            const bool is_center = j0 + m / per_col < n_center;
+            const bool is_center = col_base + j0 + m / per_col < n_center;
             double* dst = out_base + off;
 #pragma unroll
             for (int ni = 0; ni < WN_TILES; ++ni) {
@@ -335,32 +355,43 @@ void pick_tile(const ConvGeom& g, int BM, int* TH, int* TW, int* NJ) {
 
 template <int WM_TILES, int WN_TILES, int WARPS_M, int WARPS_N, int STAGES, int MIN_BLOCKS>
 int launch_variant(cudaStream_t st, const ConvParams& p, dim3 grid, size_t smem, const ConvWeights& w,
-                   const ChanAffine& bn, const RowMask& mask, const double* Vin, int64_t ld_in, double* Vout,
-                   int64_t ld_out, int64_t ncols, int64_t n_center) {
+                   const ChanAffine& bn, const RowMask& mask, const ColWindows& win, int64_t col_base,
+                   const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out, int64_t ncols, int64_t n_center) {
     auto kern = conv_f64_kernel<WM_TILES, WN_TILES, WARPS_M, WARPS_N, STAGES, MIN_BLOCKS>;
     NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, WARPS_M * WARPS_N * 32, smem, st>>>(p, w.w, w.bias, bn, mask, Vin, ld_in, Vout, ld_out, ncols,
-                                                     n_center);
+    kern<<<grid, WARPS_M * WARPS_N * 32, smem, st>>>(p, w.w, w.bias, bn, mask, win, col_base, Vin, ld_in, Vout, ld_out,
+                                                     ncols, n_center);
     NNVB_CUDA(cudaGetLastError());
     return NNVB_OK;
 }
 
 template <int WM_TILES, int WN_TILES, int WARPS_M, int WARPS_N>
 int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn, const RowMask& mask,
-               const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out, int64_t ncols,
-               int64_t n_center) {
+               const ColWindows& win, int64_t col_base, const double* Vin, int64_t ld_in, double* Vout,
+               int64_t ld_out, int64_t ncols, int64_t n_center) {
     constexpr int BM = WARPS_M * WM_TILES * 16;
     constexpr int BN = WARPS_N * WN_TILES * 8;
     ConvParams p;
     p.g = g;
-    pick_tile(g, BM, &p.TH, &p.TW, &p.NJ);
+    if (win.h0 != nullptr) {
+        // one patch of wh x ww outputs per column, as many columns per tile as fit
+        if (win.wh * win.ww > BM || win.wh < 1 || win.ww < 1) {
+            set_error("conv: output window %dx%d does not fit a tile", win.wh, win.ww);
+            return NNVB_E_ARG;
+        }
+        p.TH = win.wh;
+        p.TW = win.ww;
+        p.NJ = std::min(BM / (win.wh * win.ww), 128);
+    } else {
+        pick_tile(g, BM, &p.TH, &p.TW, &p.NJ);
+    }
     p.HH = (p.TH - 1) * g.sh + (g.kh - 1) * g.dh + 1;
     p.HW = (p.TW - 1) * g.sw + (g.kw - 1) * g.dw + 1;
     p.plane = p.NJ * p.HH * p.HW;
     p.PS = pad_stride(p.plane);
     p.CS = w.cs;
-    p.n_th = (int)ceil_div(g.Ho, p.TH);
-    p.n_tw = (int)ceil_div(g.Wo, p.TW);
+    p.n_th = win.h0 != nullptr ? 1 : (int)ceil_div(g.Ho, p.TH);
+    p.n_tw = win.h0 != nullptr ? 1 : (int)ceil_div(g.Wo, p.TW);
     p.n_chunks = w.n_chunks;
     p.taps = g.kh * g.kw;
     p.halo_stage = KC * p.PS;
@@ -389,13 +420,13 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
     const size_t two = 2 * stage_bytes + fixed_bytes;
     const size_t three = 3 * stage_bytes + fixed_bytes;
     if ((variant == 0 || variant == 2) && 2 * (two + 1024) <= limit)
-        return launch_variant<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 2, 2>(st, p, grid, two, w, bn, mask, Vin, ld_in, Vout,
+        return launch_variant<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 2, 2>(st, p, grid, two, w, bn, mask, win, col_base, Vin, ld_in, Vout,
                                                                          ld_out, ncols, n_center);
     if (three <= limit)
-        return launch_variant<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 3, 1>(st, p, grid, three, w, bn, mask, Vin, ld_in, Vout,
+        return launch_variant<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 3, 1>(st, p, grid, three, w, bn, mask, win, col_base, Vin, ld_in, Vout,
                                                                          ld_out, ncols, n_center);
     if (two <= limit)
-        return launch_variant<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 2, 1>(st, p, grid, two, w, bn, mask, Vin, ld_in, Vout,
+        return launch_variant<WM_TILES, WN_TILES, WARPS_M, WARPS_N, 2, 1>(st, p, grid, two, w, bn, mask, win, col_base, Vin, ld_in, Vout,
                                                                          ld_out, ncols, n_center);
     set_error("conv: filter %dx%d with stride (%d,%d) needs %zu bytes of shared memory per stage", g.kh, g.kw, g.sh,
               g.sw, stage_bytes);
@@ -434,16 +465,16 @@ void conv_arrange_weights(const ConvGeom& g, const double* W, double* dst, int b
 }
 
 int launch_conv_f64(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
-                    const RowMask& mask, const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
-                    int64_t ncols, int64_t n_center, int64_t* launches) {
+                    const RowMask& mask, const ColWindows& win, int64_t col_base, const double* Vin, int64_t ld_in,
+                    double* Vout, int64_t ld_out, int64_t ncols, int64_t n_center, int64_t* launches) {
     if (ncols <= 0) return NNVB_OK;
     int s;
     if (w.bn_tile == 16)
-        s = launch_cfg<1, 2, 8, 1>(st, g, w, bn, mask, Vin, ld_in, Vout, ld_out, ncols, n_center);
+        s = launch_cfg<1, 2, 8, 1>(st, g, w, bn, mask, win, col_base, Vin, ld_in, Vout, ld_out, ncols, n_center);
     else if (w.bn_tile == 32)
-        s = launch_cfg<2, 2, 4, 2>(st, g, w, bn, mask, Vin, ld_in, Vout, ld_out, ncols, n_center);
+        s = launch_cfg<2, 2, 4, 2>(st, g, w, bn, mask, win, col_base, Vin, ld_in, Vout, ld_out, ncols, n_center);
     else
-        s = launch_cfg<2, 4, 4, 2>(st, g, w, bn, mask, Vin, ld_in, Vout, ld_out, ncols, n_center);
+        s = launch_cfg<2, 4, 4, 2>(st, g, w, bn, mask, win, col_base, Vin, ld_in, Vout, ld_out, ncols, n_center);
     if (s == NNVB_OK && launches) *launches += 1;
     return s;
 }

@@ -131,7 +131,8 @@ __global__ void build_from_bounds_kernel(int nq, int rank, int world, int64_t N,
                                          const int64_t* __restrict__ q_gen_off, double* __restrict__ V,
                                          int32_t* __restrict__ col_q, double* __restrict__ pl,
                                          double* __restrict__ pu, int32_t* __restrict__ qcol_idx,
-                                         int64_t* __restrict__ col_pos) {
+                                         int64_t* __restrict__ col_pos, int img_h, int img_w,
+                                         int32_t* __restrict__ win_h0, int32_t* __restrict__ win_w0) {
     const int q = blockIdx.x;
     const double* lb = lbub + int64_t(q) * 2 * N;
     const double* ub = lb + N;
@@ -169,6 +170,8 @@ __global__ void build_from_bounds_kernel(int nq, int rank, int world, int64_t N,
             pu[col] = 1.0;
             qcol_idx[list0 + t] = int32_t(col);
             col_pos[col] = r;
+            win_h0[col] = int32_t(i % img_h);            // the generator is non-zero at one pixel only
+            win_w0[col] = int32_t((i / img_h) % img_w);
         }
         __syncthreads();
         if (threadIdx.x == 0) running += total;
@@ -178,6 +181,26 @@ __global__ void build_from_bounds_kernel(int nq, int rank, int world, int64_t N,
 }
 
 }  // namespace
+
+// Window origins after a convolution or pooling layer: an input window starting at h0 can reach outputs
+// from ceil((h0 + pad - extent) / stride) on (extent = (k-1)*dilation).  One thread per column.
+__global__ void update_windows_kernel(int64_t n, int32_t* __restrict__ h0, int32_t* __restrict__ w0, int pad_t,
+                                      int pad_l, int ext_h, int ext_w, int sh, int sw) {
+    const int64_t j = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (j >= n) return;
+    const int a = h0[j] + pad_t - ext_h, b = w0[j] + pad_l - ext_w;
+    h0[j] = a >= 0 ? (a + sh - 1) / sh : -((-a) / sh);
+    w0[j] = b >= 0 ? (b + sw - 1) / sw : -((-b) / sw);
+}
+
+int launch_update_windows(cudaStream_t st, int64_t n, int32_t* h0, int32_t* w0, int pad_t, int pad_l, int ext_h,
+                          int ext_w, int sh, int sw, int64_t* launches) {
+    if (n <= 0) return NNVB_OK;
+    update_windows_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(n, h0, w0, pad_t, pad_l, ext_h, ext_w, sh, sw);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
 
 int launch_bn_f64(cudaStream_t st, const ChanAffine& bn, int64_t plane, int64_t N, double* V,
                   int64_t ld, int64_t ncols, int64_t n_center, int64_t* launches) {
@@ -223,9 +246,10 @@ int launch_count_bounds(cudaStream_t st, int nq, int64_t N, const double* lbub, 
 
 int launch_build_from_bounds(cudaStream_t st, int nq, int64_t N, int64_t ld, const double* lbub,
                              const int64_t* q_gen_off, int rank, int world, double* V, int32_t* col_q, double* pl,
-                             double* pu, int32_t* qcol_idx, int64_t* col_pos, int64_t* launches) {
+                             double* pu, int32_t* qcol_idx, int64_t* col_pos, int img_h, int img_w, int32_t* win_h0,
+                             int32_t* win_w0, int64_t* launches) {
     build_from_bounds_kernel<<<nq, 256, 0, st>>>(nq, rank, world, N, ld, lbub, q_gen_off, V, col_q, pl, pu, qcol_idx,
-                                                 col_pos);
+                                                 col_pos, img_h, img_w, win_h0, win_w0);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;

@@ -107,7 +107,7 @@ struct ReluLayerRecord {
 // context reuses it, so a steady-state reach allocates nothing, and the results
 // of a batch stay readable until another batch of the same context is reached.
 struct WorkBufs {
-    DevBuf col_q, pl, pu, col_pos;
+    DevBuf col_q, pl, pu, col_pos, win_h0, win_w0;
     DevBuf qcol_off[2], qcol_idx[2];
     DevBuf chunk_beg, chunk_end, q_chunk_off, partial, sums;
     DevBuf lb, ub, state, rank, blk_cross, q_cross, q_dead, q_new_off, gen_off;
@@ -115,7 +115,7 @@ struct WorkBufs {
     DevBuf hs_G, hs_g, hs_q, hs_margin, hs_r, hs_roff, hs_val, hs_scale, wit[2];   // halfspace tests
     std::vector<std::unique_ptr<ReluLayerRecord>> relu;
     void release() {
-        DevBuf* bufs[] = {&col_q, &pl, &pu, &col_pos, &qcol_off[0], &qcol_off[1], &qcol_idx[0], &qcol_idx[1],
+        DevBuf* bufs[] = {&col_q, &pl, &pu, &col_pos, &win_h0, &win_w0, &qcol_off[0], &qcol_off[1], &qcol_idx[0], &qcol_idx[1],
                           &chunk_beg, &chunk_end, &q_chunk_off, &partial, &sums, &lb, &ub, &state, &rank, &blk_cross,
                           &q_cross, &q_dead, &q_new_off, &gen_off, &tmp, &hs_G, &hs_g, &hs_q, &hs_margin, &hs_r,
                           &hs_roff, &hs_val, &hs_scale, &wit[0], &wit[1]};
@@ -204,6 +204,11 @@ struct nnvb_batch {
     // working state: the buffers live in the context (one reach at a time per context)
     WorkBufs* wk = nullptr;
     int list_cur = 0;
+    // Column cohorts: runs of columns born together (centres, input generators, the columns of each
+    // ReLU layer).  A windowed cohort's columns are exactly zero outside a wh x ww window whose origin
+    // is kept per column (win_h0 / win_w0); convolutions then compute only the patch that can be non-zero.
+    struct Cohort { int64_t col0, col1; bool dense; int wh, ww; };
+    std::vector<Cohort> cohorts;
     // work a ReLU step left to the layer that follows it (see relu_step)
     int64_t pend_mask_ncols = 0;         // > 0: rows with state != 0 of columns [0, n) read as zero
     int64_t pend_mask_N = 0;
@@ -811,6 +816,8 @@ int ensure_col_meta(nnvb_batch* b, int64_t cols) {
     NNVB_TRY(b->wk->pl.ensure(size_t(cols) * sizeof(double), st, true));
     NNVB_TRY(b->wk->pu.ensure(size_t(cols) * sizeof(double), st, true));
     NNVB_TRY(b->wk->col_pos.ensure(size_t(cols) * sizeof(int64_t), st, true));
+    NNVB_TRY(b->wk->win_h0.ensure(size_t(cols) * sizeof(int32_t), st, true));
+    NNVB_TRY(b->wk->win_w0.ensure(size_t(cols) * sizeof(int32_t), st, true));
     for (int i = 0; i < 2; ++i) {
         NNVB_TRY(b->wk->qcol_idx[i].ensure(size_t(cols) * sizeof(int32_t), st, true));
         NNVB_TRY(b->wk->qcol_off[i].ensure(size_t(b->nq + 1) * sizeof(int64_t), st, true));
@@ -848,7 +855,9 @@ int init_sets(nnvb_batch* b) {
         NNVB_TRY(launch_build_from_bounds(st, nq, N, ld, b->d_in.as<double>(), b->wk->gen_off.as<int64_t>(), ctx->rank,
                                           ctx->world, V,
                                           b->wk->col_q.as<int32_t>(), b->wk->pl.as<double>(), b->wk->pu.as<double>(),
-                                          b->wk->qcol_idx[0].as<int32_t>(), b->wk->col_pos.as<int64_t>(), &ctx->launches));
+                                          b->wk->qcol_idx[0].as<int32_t>(), b->wk->col_pos.as<int64_t>(),
+                                          int(b->net->in_shape[0]), int(b->net->in_shape[1]),
+                                          b->wk->win_h0.as<int32_t>(), b->wk->win_w0.as<int32_t>(), &ctx->launches));
         b->V = V;
     } else {
         // metadata is a pure function of the staged queries
@@ -873,6 +882,11 @@ int init_sets(nnvb_batch* b) {
     b->N = N;
     b->ld = ld;
     for (int i = 0; i < 3; ++i) b->shape[i] = b->net->in_shape[i];
+    // centres are dense; box generators touch one pixel each; general generators are taken as dense
+    static const bool no_windows = getenv("NNVB_NO_WINDOWS") != nullptr;
+    b->cohorts.clear();
+    b->cohorts.push_back({0, nq, true, 0, 0});
+    if (ncols > nq) b->cohorts.push_back({nq, ncols, b->kind != 1 || no_windows, 1, 1});
     return NNVB_OK;
 }
 
@@ -1049,8 +1063,9 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
         NNVB_TRY(launch_relu_append(st, w, ncols_old, K_loc, rank, world, !lazy_onehot,
                                     world > 1 ? rec->P_in_dev.as<int64_t>() : nullptr, r, b->wk->col_q.as<int32_t>(),
                                     b->wk->pl.as<double>(), b->wk->pu.as<double>(), b->wk->col_pos.as<int64_t>(),
-                                    b->wk->qcol_off[nxt].as<int64_t>(), b->wk->qcol_idx[nxt].as<int32_t>(),
-                                    &ctx->launches));
+                                    int(b->shape[0]), int(b->shape[1]), b->wk->win_h0.as<int32_t>(),
+                                    b->wk->win_w0.as<int32_t>(), b->wk->qcol_off[nxt].as<int64_t>(),
+                                    b->wk->qcol_idx[nxt].as<int32_t>(), &ctx->launches));
     }
     b->list_cur = nxt;
     // local lists grow by the new columns this rank holds: those numbered c = rank (mod world)
@@ -1062,6 +1077,8 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
     b->pend_mask_N = N;
     b->pend_onehot = lazy_onehot ? K_loc : 0;
     b->pend_rec = rec;
+    static const bool no_windows = getenv("NNVB_NO_WINDOWS") != nullptr;
+    if (K_loc > 0) b->cohorts.push_back({ncols_old, ncols_old + K_loc, no_windows, 1, 1});
     return NNVB_OK;
 }
 
@@ -1091,11 +1108,27 @@ int run_layers(nnvb_batch* b) {
                     const Layer& B = net->layers[L.fused_bn];
                     bn = ChanAffine{B.bn_mean, B.bn_den, B.bn_rden, B.bn_scale, B.bn_offset};
                 }
-                {
-                    ProfScope ps(ctx, NNVB_PROF_CONV,
-                                 2.0 * L.cg.Ho * L.cg.Wo * L.cg.Cout * L.cg.kh * L.cg.kw * L.cg.Cin * double(n_dense));
-                    NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, mask, b->V, b->ld, out, ld_out, n_dense, b->nq,
-                                             &ctx->launches));
+                // one launch per cohort: dense cohorts are tiled over the whole image, windowed cohorts
+                // compute one small output patch per column (the rest of their output stays zero)
+                const double per_pos = 2.0 * L.cg.Cout * L.cg.kh * L.cg.kw * L.cg.Cin;
+                for (auto& co : b->cohorts) {
+                    const int64_t c1 = std::min(co.col1, n_dense);
+                    if (c1 <= co.col0) continue;
+                    const int wh = (co.wh - 1 + (L.cg.kh - 1) * L.cg.dh) / L.cg.sh + 1;
+                    const int ww = (co.ww - 1 + (L.cg.kw - 1) * L.cg.dw) / L.cg.sw + 1;
+                    const bool windowed = !co.dense && wh * ww <= 128 && 2 * wh * ww <= L.cg.Ho * L.cg.Wo;
+                    if (windowed) {
+                        NNVB_CUDA(cudaMemsetAsync(out + co.col0 * ld_out, 0, sizeof(double) * ld_out * (c1 - co.col0), st));
+                        ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * wh * ww * double(c1 - co.col0));
+                        ColWindows win{b->wk->win_h0.as<int32_t>(), b->wk->win_w0.as<int32_t>(), wh, ww};
+                        NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, mask, win, co.col0, b->V, b->ld, out, ld_out,
+                                                 c1 - co.col0, b->nq, &ctx->launches));
+                    } else {
+                        ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * L.cg.Ho * L.cg.Wo * double(c1 - co.col0));
+                        ColWindows win{nullptr, nullptr, 0, 0};
+                        NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, mask, win, co.col0, b->V, b->ld, out, ld_out,
+                                                 c1 - co.col0, b->nq, &ctx->launches));
+                    }
                 }
                 ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(Nout) * double(n_hot));
                 NNVB_TRY(launch_conv_onehot(st, L.cg, L.cw, bn, hot_idx, ctx->rank, ctx->world, n_hot,
@@ -1117,6 +1150,26 @@ int run_layers(nnvb_batch* b) {
                 ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(Nout) * double(n_hot));
                 NNVB_TRY(launch_avgpool_onehot(st, L.pg, hot_idx, ctx->rank, ctx->world, n_hot, out + n_dense * ld_out,
                                                ld_out, &ctx->launches));
+            }
+            // windows of the output tensor
+            if (L.type == NNVB_LAYER_FC) {
+                for (auto& co : b->cohorts) co.dense = true;
+            } else {
+                const bool cv = L.type == NNVB_LAYER_CONV2D;
+                const int eh = cv ? (L.cg.kh - 1) * L.cg.dh : L.pg.ph - 1, ew = cv ? (L.cg.kw - 1) * L.cg.dw : L.pg.pw - 1;
+                const int sh = cv ? L.cg.sh : L.pg.sh, sw = cv ? L.cg.sw : L.pg.sw;
+                const int pt = cv ? L.cg.pad_t : L.pg.pad_t, pl_ = cv ? L.cg.pad_l : L.pg.pad_l;
+                bool any = false;
+                for (auto& co : b->cohorts) {
+                    if (co.dense) continue;
+                    co.wh = (co.wh - 1 + eh) / sh + 1;
+                    co.ww = (co.ww - 1 + ew) / sw + 1;
+                    if (co.wh * co.ww > 128 || 2 * co.wh * co.ww > L.Ho * L.Wo) co.dense = true;
+                    else any = true;
+                }
+                if (any)
+                    NNVB_TRY(launch_update_windows(st, b->ncols, b->wk->win_h0.as<int32_t>(), b->wk->win_w0.as<int32_t>(), pt,
+                                                   pl_, eh, ew, sh, sw, &ctx->launches));
             }
             b->pend_mask_ncols = 0;
             b->pend_onehot = 0;
@@ -1232,7 +1285,7 @@ int witness_forward(nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, i
                 const Layer& B = net->layers[L.fused_bn];
                 bn = ChanAffine{B.bn_mean, B.bn_den, B.bn_rden, B.bn_scale, B.bn_offset};
             }
-            NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, RowMask{nullptr, nullptr, 0, 0}, cur, ld, oth, ld_out, n, n, &ctx->launches));
+            NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, RowMask{nullptr, nullptr, 0, 0}, ColWindows{nullptr, nullptr, 0, 0}, 0, cur, ld, oth, ld_out, n, n, &ctx->launches));
             std::swap(cur, oth); N = Nout; ld = ld_out;
         } else if (L.type == NNVB_LAYER_FC) {
             NNVB_TRY(launch_fc_f64(st, int(L.H * L.W * L.C), int(L.Co), L.fc_wt, L.fc_ldw, L.bias, cur, ld, oth, ld_out, n,

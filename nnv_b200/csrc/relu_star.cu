@@ -301,7 +301,8 @@ __global__ void append_cols_kernel(int64_t K_loc, int rank, int world, int write
                                    const int64_t* __restrict__ q_new_off, const int64_t* __restrict__ qcol_off,
                                    const int64_t* __restrict__ P_in, int32_t* __restrict__ col_q,
                                    double* __restrict__ pl, double* __restrict__ pu,
-                                   int64_t* __restrict__ col_pos) {
+                                   int64_t* __restrict__ col_pos, int img_h, int img_w,
+                                   int32_t* __restrict__ win_h0, int32_t* __restrict__ win_w0) {
     const int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (t >= K_loc) return;
     const int64_t c = rank + t * world;
@@ -314,6 +315,8 @@ __global__ void append_cols_kernel(int64_t K_loc, int rank, int world, int write
     // position in the query's predicate order (over all ranks)
     const int64_t p_in = P_in ? P_in[q] : (qcol_off[q + 1] - qcol_off[q]);
     col_pos[col] = p_in + (c - q_new_off[q]);
+    win_h0[col] = rec_idx[c] % img_h;                  // a unit vector: non-zero at one pixel
+    win_w0[col] = (rec_idx[c] / img_h) % img_w;
 }
 
 // 3c. new predicate-ordered column lists: old list of the query, then its new
@@ -637,13 +640,15 @@ int launch_relu_zero_rows(cudaStream_t st, const ReluWork& w, int64_t ncols, con
 
 int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, int64_t K_loc, int rank, int world,
                        bool materialize, const int64_t* P_in, const ReluRecord& rec, int32_t* col_q, double* pl, double* pu,
-                       int64_t* col_pos, int64_t* new_qcol_off, int32_t* new_qcol_idx, int64_t* launches) {
+                       int64_t* col_pos, int img_h, int img_w, int32_t* win_h0, int32_t* win_w0,
+                       int64_t* new_qcol_off, int32_t* new_qcol_idx, int64_t* launches) {
     if (K_loc > 0) {
         if (materialize) NNVB_CUDA(cudaMemsetAsync(w.V + ncols_old * w.ld, 0, sizeof(double) * w.ld * K_loc, st));
         append_cols_kernel<<<(unsigned)ceil_div(K_loc, 256), 256, 0, st>>>(K_loc, rank, world, materialize ? 1 : 0,
                                                                           w.ld, w.V, ncols_old,
                                                                           rec.idx, rec.q, rec.u, w.q_new_off,
-                                                                          w.qcol_off, P_in, col_q, pl, pu, col_pos);
+                                                                          w.qcol_off, P_in, col_q, pl, pu, col_pos, img_h,
+                                                                          img_w, win_h0, win_w0);
         NNVB_CUDA(cudaGetLastError());
         if (launches) *launches += 1;
     }
