@@ -86,13 +86,15 @@ struct RowMask {
 };
 
 // Windowed columns: column j (absolute index) is exactly zero outside the input window that starts at
-// (h0[j], w0[j]) (may lie partly outside the image); wh x ww is the size of the OUTPUT patch the layer
-// computes for each such column.  h0 == nullptr: dense columns.
+// (box[j].x, box[j].y) (may lie partly outside the image); wh x ww is the size of the OUTPUT patch the layer
+// computes for each such column.  box == nullptr: dense columns.
 struct ColWindows {
-    const int32_t* h0;
-    const int32_t* w0;
+    const int4* box;        // per column {h0, w0, wh, ww} of its input window
     int wh, ww;
 };
+// A window that covers any image (dense columns).
+#define NNVB_DENSE_ORIGIN (-(1 << 20))
+#define NNVB_DENSE_EXTENT (1 << 21)
 
 size_t conv_weights_doubles(const ConvGeom& g, int* bn_tile, int* cs, int* n_tiles, int* n_chunks);
 // Host-side re-layout of W[kh,kw,Cin,Cout] (column-major) into the kernel's layout.
@@ -109,6 +111,18 @@ int launch_conv_f64(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, co
 int launch_conv_onehot(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
                        const int32_t* rec_idx, int64_t c_first, int64_t c_step, int64_t K_loc, double* Vout,
                        int64_t ld_out, int64_t* launches);
+// FC on windowed columns [col0, col0+n) (all with an wh x ww window in the H x W x C input; origins in box):
+// only the weight rows of each column's window are contracted.  scratch: fc_gather_scratch_ints() int32.
+size_t fc_gather_scratch_ints(int64_t n, int H, int W, int wh, int ww);
+bool fc_gather_fits(int C, int wh, int ww);
+int launch_fc_gather(cudaStream_t st, int H, int W, int C, int wh, int ww, int Out, const double* Wt, int ldw,
+                     const int4* box, int64_t col0, int64_t n, const double* Vin, int64_t ld_in, double* Vout,
+                     int64_t ld_out, int32_t* scratch, int64_t* launches);
+// FC for a few columns that are all points (bias on every column); used for witness points.
+size_t fc_skinny_scratch_doubles(int In, int Out, int ncols);
+int launch_fc_skinny(cudaStream_t st, int In, int Out, const double* Wt, int ldw, const double* bias,
+                     const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out, int ncols, double* scratch,
+                     int64_t* launches);
 int launch_fc_onehot(cudaStream_t st, int Out, const double* Wt, int ldw, const int32_t* rec_idx, int64_t c_first,
                      int64_t c_step, int64_t K_loc, double* Vout, int64_t ld_out, int64_t* launches);
 
@@ -142,6 +156,10 @@ struct ReluWork {
     const int32_t* qcol_idx;   // predicate-ordered generator columns of each query
     const double* pl;          // [ncols] predicate bounds by column
     const double* pu;
+    const int4* box;           // [ncols] window of each column (nullptr: read every column everywhere)
+    int4* gbox;                // scratch, one int4 per 16 entries of qcol_idx (joint windows)
+    int64_t n_list;            // entries of qcol_idx over all queries
+    int img_h, img_w;          // image height / width of the current tensor (rows are h-fastest)
     // chunk list for the bound reduction
     int n_chunks;
     const int64_t* chunk_beg;  // [n_chunks] positions in qcol_idx
@@ -185,7 +203,7 @@ int launch_relu_zero_rows(cudaStream_t st, const ReluWork& w, int64_t ncols, con
 // materialize = false leaves the new columns implicit (only their metadata is written).
 int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, int64_t K_loc, int rank, int world,
                        bool materialize, const int64_t* P_in, const ReluRecord& rec, int32_t* col_q, double* pl, double* pu,
-                       int64_t* col_pos, int img_h, int img_w, int32_t* win_h0, int32_t* win_w0,
+                       int64_t* col_pos, int img_h, int img_w, int4* box,
                        int64_t* new_qcol_off, int32_t* new_qcol_idx, int64_t* launches);
 
 // Halfspace rows against output sets; see relu_star.cu.  Pair p tests row G[p] (length Nout)
@@ -212,11 +230,18 @@ int launch_witness_value(cudaStream_t st, int n_pairs, int64_t Nout, int64_t ld,
 // Build the dense input set of a bounds-form query batch.
 int launch_build_from_bounds(cudaStream_t st, int nq, int64_t N, int64_t ld, const double* lbub,
                              const int64_t* q_gen_off, int rank, int world, double* V, int32_t* col_q, double* pl,
-                             double* pu, int32_t* qcol_idx, int64_t* col_pos, int img_h, int img_w, int32_t* win_h0,
-                             int32_t* win_w0, int64_t* launches);
-// Move the window origins of columns [0, n) through a convolution / pooling layer.
-int launch_update_windows(cudaStream_t st, int64_t n, int32_t* h0, int32_t* w0, int pad_t, int pad_l, int ext_h,
+                             double* pu, int32_t* qcol_idx, int64_t* col_pos, int img_h, int img_w, int4* box,
+                             int64_t* launches);
+// Move the windows of columns [0, n) through a convolution / pooling layer (extent = (k-1)*dilation).
+int launch_update_windows(cudaStream_t st, int64_t n, int4* box, int pad_t, int pad_l, int ext_h,
                           int ext_w, int sh, int sw, int64_t* launches);
+// Mark columns [0, n) as dense (a window that covers any image).
+int launch_fill_dense_windows(cudaStream_t st, int64_t n, int4* box, int64_t* launches);
+// Average pooling of windowed columns [col_base, col_base+ncols): only the win.wh x win.ww output patch of
+// each column is computed (the output block is zero filled by the caller).
+int launch_avgpool_windowed(cudaStream_t st, const PoolGeom& g, const RowMask& mask, const ColWindows& win,
+                            int64_t col_base, const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
+                            int64_t ncols, int64_t* launches);
 int launch_count_bounds(cudaStream_t st, int nq, int64_t N, const double* lbub, int64_t* q_count,
                         int64_t* launches);
 

@@ -91,9 +91,10 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
     __shared__ int org_h[128], org_w[128];
     if (tid < p.NJ) {
         int a = oh0, b2 = ow0;
-        if (win.h0 != nullptr && j0 + tid < ncols) {
-            const int ah = win.h0[col_base + j0 + tid] + p.g.pad_t - (p.g.kh - 1) * p.g.dh;
-            const int aw = win.w0[col_base + j0 + tid] + p.g.pad_l - (p.g.kw - 1) * p.g.dw;
+        if (win.box != nullptr && j0 + tid < ncols) {
+            const int4 bx = win.box[col_base + j0 + tid];
+            const int ah = bx.x + p.g.pad_t - (p.g.kh - 1) * p.g.dh;
+            const int aw = bx.y + p.g.pad_l - (p.g.kw - 1) * p.g.dw;
             a = ah >= 0 ? (ah + p.g.sh - 1) / p.g.sh : -((-ah) / p.g.sh);
             b2 = aw >= 0 ? (aw + p.g.sw - 1) / p.g.sw : -((-aw) / p.g.sw);
         }
@@ -373,7 +374,7 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
     constexpr int BN = WARPS_N * WN_TILES * 8;
     ConvParams p;
     p.g = g;
-    if (win.h0 != nullptr) {
+    if (win.box != nullptr) {
         // one patch of wh x ww outputs per column, as many columns per tile as fit
         if (win.wh * win.ww > BM || win.wh < 1 || win.ww < 1) {
             set_error("conv: output window %dx%d does not fit a tile", win.wh, win.ww);
@@ -390,8 +391,8 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
     p.plane = p.NJ * p.HH * p.HW;
     p.PS = pad_stride(p.plane);
     p.CS = w.cs;
-    p.n_th = win.h0 != nullptr ? 1 : (int)ceil_div(g.Ho, p.TH);
-    p.n_tw = win.h0 != nullptr ? 1 : (int)ceil_div(g.Wo, p.TW);
+    p.n_th = win.box != nullptr ? 1 : (int)ceil_div(g.Ho, p.TH);
+    p.n_tw = win.box != nullptr ? 1 : (int)ceil_div(g.Wo, p.TW);
     p.n_chunks = w.n_chunks;
     p.taps = g.kh * g.kw;
     p.halo_stage = KC * p.PS;

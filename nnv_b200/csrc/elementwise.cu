@@ -132,7 +132,7 @@ __global__ void build_from_bounds_kernel(int nq, int rank, int world, int64_t N,
                                          int32_t* __restrict__ col_q, double* __restrict__ pl,
                                          double* __restrict__ pu, int32_t* __restrict__ qcol_idx,
                                          int64_t* __restrict__ col_pos, int img_h, int img_w,
-                                         int32_t* __restrict__ win_h0, int32_t* __restrict__ win_w0) {
+                                         int4* __restrict__ box) {
     const int q = blockIdx.x;
     const double* lb = lbub + int64_t(q) * 2 * N;
     const double* ub = lb + N;
@@ -170,33 +170,102 @@ __global__ void build_from_bounds_kernel(int nq, int rank, int world, int64_t N,
             pu[col] = 1.0;
             qcol_idx[list0 + t] = int32_t(col);
             col_pos[col] = r;
-            win_h0[col] = int32_t(i % img_h);            // the generator is non-zero at one pixel only
-            win_w0[col] = int32_t((i / img_h) % img_w);
+            box[col] = make_int4(int(i % img_h), int((i / img_h) % img_w), 1, 1);   // non-zero at one pixel only
         }
         __syncthreads();
         if (threadIdx.x == 0) running += total;
         __syncthreads();
     }
-    if (threadIdx.x == 0) { col_q[q] = q; pl[q] = 0.0; pu[q] = 0.0; }
+    if (threadIdx.x == 0) {
+        col_q[q] = q; pl[q] = 0.0; pu[q] = 0.0;
+        box[q] = make_int4(NNVB_DENSE_ORIGIN, NNVB_DENSE_ORIGIN, NNVB_DENSE_EXTENT, NNVB_DENSE_EXTENT);
+    }
 }
 
 }  // namespace
 
 // Window origins after a convolution or pooling layer: an input window starting at h0 can reach outputs
 // from ceil((h0 + pad - extent) / stride) on (extent = (k-1)*dilation).  One thread per column.
-__global__ void update_windows_kernel(int64_t n, int32_t* __restrict__ h0, int32_t* __restrict__ w0, int pad_t,
-                                      int pad_l, int ext_h, int ext_w, int sh, int sw) {
+__global__ void update_windows_kernel(int64_t n, int4* __restrict__ box, int pad_t, int pad_l, int ext_h, int ext_w,
+                                      int sh, int sw) {
     const int64_t j = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (j >= n) return;
-    const int a = h0[j] + pad_t - ext_h, b = w0[j] + pad_l - ext_w;
-    h0[j] = a >= 0 ? (a + sh - 1) / sh : -((-a) / sh);
-    w0[j] = b >= 0 ? (b + sw - 1) / sw : -((-b) / sw);
+    int4 bx = box[j];
+    const int a = bx.x + pad_t - ext_h, b = bx.y + pad_l - ext_w;
+    bx.x = a >= 0 ? (a + sh - 1) / sh : -((-a) / sh);
+    bx.y = b >= 0 ? (b + sw - 1) / sw : -((-b) / sw);
+    bx.z = (bx.z - 1 + ext_h) / sh + 1;
+    bx.w = (bx.w - 1 + ext_w) / sw + 1;
+    box[j] = bx;
 }
 
-int launch_update_windows(cudaStream_t st, int64_t n, int32_t* h0, int32_t* w0, int pad_t, int pad_l, int ext_h,
+__global__ void fill_dense_windows_kernel(int64_t n, int4* __restrict__ box) {
+    const int64_t j = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (j < n) box[j] = make_int4(NNVB_DENSE_ORIGIN, NNVB_DENSE_ORIGIN, NNVB_DENSE_EXTENT, NNVB_DENSE_EXTENT);
+}
+
+// Windowed average pooling: thread per (column, channel, patch position); same window sum as the dense kernel.
+__global__ void avgpool_windowed_kernel(PoolGeom g, RowMask mask, ColWindows win, int64_t col_base, int64_t ncols,
+                                        const double* __restrict__ Vin, int64_t ld_in, double* __restrict__ Vout,
+                                        int64_t ld_out) {
+    const int per_col = win.wh * win.ww * g.C;
+    const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= ncols * per_col) return;
+    const int64_t j = col_base + e / per_col;
+    int r = int(e % per_col);
+    const int ohl = r % win.wh;
+    r /= win.wh;
+    const int owl = r % win.ww;
+    const int c = r / win.ww;
+    const int4 bx = win.box[j];
+    const int a = bx.x + g.pad_t - (g.ph - 1), b2 = bx.y + g.pad_l - (g.pw - 1);
+    const int oh = (a >= 0 ? (a + g.sh - 1) / g.sh : -((-a) / g.sh)) + ohl;
+    const int ow = (b2 >= 0 ? (b2 + g.sw - 1) / g.sw : -((-b2) / g.sw)) + owl;
+    if (oh < 0 || ow < 0 || oh >= g.Ho || ow >= g.Wo) return;
+    const int64_t cbase = int64_t(c) * g.H * g.W;
+    const double* src = Vin + j * ld_in + cbase;
+    const uint8_t* st = (mask.state != nullptr && j < mask.ncols) ? mask.state + mask.col_q[j] * mask.N + cbase : nullptr;
+    const int h0 = oh * g.sh - g.pad_t, w0 = ow * g.sw - g.pad_l;
+    double acc = 0.0;
+    for (int aa = 0; aa < g.ph; ++aa) {
+        const int h = h0 + aa;
+        for (int bb = 0; bb < g.pw; ++bb) {
+            const int w = w0 + bb;
+            double v = 0.0;
+            if (h >= 0 && h < g.H && w >= 0 && w < g.W) {
+                const int64_t o_in = h + int64_t(g.H) * w;
+                if (st == nullptr || st[o_in] == 0) v = src[o_in];
+            }
+            acc = acc + v;
+        }
+    }
+    Vout[j * ld_out + oh + int64_t(g.Ho) * (ow + int64_t(g.Wo) * c)] = acc / double(g.ph * g.pw);
+}
+
+int launch_avgpool_windowed(cudaStream_t st, const PoolGeom& g, const RowMask& mask, const ColWindows& win,
+                            int64_t col_base, const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
+                            int64_t ncols, int64_t* launches) {
+    if (ncols <= 0) return NNVB_OK;
+    const int64_t total = ncols * win.wh * win.ww * g.C;
+    avgpool_windowed_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(g, mask, win, col_base, ncols, Vin, ld_in,
+                                                                           Vout, ld_out);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_fill_dense_windows(cudaStream_t st, int64_t n, int4* box, int64_t* launches) {
+    if (n <= 0) return NNVB_OK;
+    fill_dense_windows_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(n, box);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_update_windows(cudaStream_t st, int64_t n, int4* box, int pad_t, int pad_l, int ext_h,
                           int ext_w, int sh, int sw, int64_t* launches) {
     if (n <= 0) return NNVB_OK;
-    update_windows_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(n, h0, w0, pad_t, pad_l, ext_h, ext_w, sh, sw);
+    update_windows_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(n, box, pad_t, pad_l, ext_h, ext_w, sh, sw);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;
@@ -246,10 +315,10 @@ int launch_count_bounds(cudaStream_t st, int nq, int64_t N, const double* lbub, 
 
 int launch_build_from_bounds(cudaStream_t st, int nq, int64_t N, int64_t ld, const double* lbub,
                              const int64_t* q_gen_off, int rank, int world, double* V, int32_t* col_q, double* pl,
-                             double* pu, int32_t* qcol_idx, int64_t* col_pos, int img_h, int img_w, int32_t* win_h0,
-                             int32_t* win_w0, int64_t* launches) {
+                             double* pu, int32_t* qcol_idx, int64_t* col_pos, int img_h, int img_w, int4* box,
+                             int64_t* launches) {
     build_from_bounds_kernel<<<nq, 256, 0, st>>>(nq, rank, world, N, ld, lbub, q_gen_off, V, col_q, pl, pu, qcol_idx,
-                                                 col_pos, img_h, img_w, win_h0, win_w0);
+                                                 col_pos, img_h, img_w, box);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;

@@ -107,17 +107,19 @@ struct ReluLayerRecord {
 // context reuses it, so a steady-state reach allocates nothing, and the results
 // of a batch stay readable until another batch of the same context is reached.
 struct WorkBufs {
-    DevBuf col_q, pl, pu, col_pos, win_h0, win_w0;
+    DevBuf col_q, pl, pu, col_pos, box;      // box: int4 {h0, w0, wh, ww} window of each column
     DevBuf qcol_off[2], qcol_idx[2];
     DevBuf chunk_beg, chunk_end, q_chunk_off, partial, sums;
     DevBuf lb, ub, state, rank, blk_cross, q_cross, q_dead, q_new_off, gen_off;
     DevBuf tmp;                          // gathers for downloads
+    DevBuf fcg;                          // column grouping of the window-gathered FC
+    DevBuf gbox;                         // joint windows of groups of list entries (bound reduction)
     DevBuf hs_G, hs_g, hs_q, hs_margin, hs_r, hs_roff, hs_val, hs_scale, wit[2];   // halfspace tests
     std::vector<std::unique_ptr<ReluLayerRecord>> relu;
     void release() {
-        DevBuf* bufs[] = {&col_q, &pl, &pu, &col_pos, &win_h0, &win_w0, &qcol_off[0], &qcol_off[1], &qcol_idx[0], &qcol_idx[1],
+        DevBuf* bufs[] = {&col_q, &pl, &pu, &col_pos, &box, &qcol_off[0], &qcol_off[1], &qcol_idx[0], &qcol_idx[1],
                           &chunk_beg, &chunk_end, &q_chunk_off, &partial, &sums, &lb, &ub, &state, &rank, &blk_cross,
-                          &q_cross, &q_dead, &q_new_off, &gen_off, &tmp, &hs_G, &hs_g, &hs_q, &hs_margin, &hs_r,
+                          &q_cross, &q_dead, &q_new_off, &gen_off, &tmp, &fcg, &gbox, &hs_G, &hs_g, &hs_q, &hs_margin, &hs_r,
                           &hs_roff, &hs_val, &hs_scale, &wit[0], &wit[1]};
         for (DevBuf* d : bufs) d->release();
         for (auto& r : relu) r->release();
@@ -816,8 +818,7 @@ int ensure_col_meta(nnvb_batch* b, int64_t cols) {
     NNVB_TRY(b->wk->pl.ensure(size_t(cols) * sizeof(double), st, true));
     NNVB_TRY(b->wk->pu.ensure(size_t(cols) * sizeof(double), st, true));
     NNVB_TRY(b->wk->col_pos.ensure(size_t(cols) * sizeof(int64_t), st, true));
-    NNVB_TRY(b->wk->win_h0.ensure(size_t(cols) * sizeof(int32_t), st, true));
-    NNVB_TRY(b->wk->win_w0.ensure(size_t(cols) * sizeof(int32_t), st, true));
+    NNVB_TRY(b->wk->box.ensure(size_t(cols) * sizeof(int4), st, true));
     for (int i = 0; i < 2; ++i) {
         NNVB_TRY(b->wk->qcol_idx[i].ensure(size_t(cols) * sizeof(int32_t), st, true));
         NNVB_TRY(b->wk->qcol_off[i].ensure(size_t(b->nq + 1) * sizeof(int64_t), st, true));
@@ -857,7 +858,7 @@ int init_sets(nnvb_batch* b) {
                                           b->wk->col_q.as<int32_t>(), b->wk->pl.as<double>(), b->wk->pu.as<double>(),
                                           b->wk->qcol_idx[0].as<int32_t>(), b->wk->col_pos.as<int64_t>(),
                                           int(b->net->in_shape[0]), int(b->net->in_shape[1]),
-                                          b->wk->win_h0.as<int32_t>(), b->wk->win_w0.as<int32_t>(), &ctx->launches));
+                                          b->wk->box.as<int4>(), &ctx->launches));
         b->V = V;
     } else {
         // metadata is a pure function of the staged queries
@@ -876,6 +877,7 @@ int init_sets(nnvb_batch* b) {
         NNVB_CUDA(cudaMemcpyAsync(b->wk->pl.p, b->d_in_meta.p, sizeof(double) * ncols, cudaMemcpyDeviceToDevice, st));
         NNVB_CUDA(cudaMemcpyAsync(b->wk->pu.p, b->d_in_meta.as<double>() + ncols, sizeof(double) * ncols,
                                   cudaMemcpyDeviceToDevice, st));
+        NNVB_TRY(launch_fill_dense_windows(st, ncols, b->wk->box.as<int4>(), &ctx->launches));
         b->V = b->d_in.as<double>();      // read-only; in-place layers copy it first
     }
     b->ncols = ncols;
@@ -885,8 +887,12 @@ int init_sets(nnvb_batch* b) {
     // centres are dense; box generators touch one pixel each; general generators are taken as dense
     static const bool no_windows = getenv("NNVB_NO_WINDOWS") != nullptr;
     b->cohorts.clear();
-    b->cohorts.push_back({0, nq, true, 0, 0});
-    if (ncols > nq) b->cohorts.push_back({nq, ncols, b->kind != 1 || no_windows, 1, 1});
+    const int BIG = 1 << 20;      // window size of columns that are dense from the start
+    b->cohorts.push_back({0, nq, true, BIG, BIG});
+    if (ncols > nq) {
+        const bool dense0 = b->kind != 1;
+        b->cohorts.push_back({nq, ncols, dense0 || no_windows, dense0 ? BIG : 1, dense0 ? BIG : 1});
+    }
     return NNVB_OK;
 }
 
@@ -962,6 +968,15 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
     w.qcol_off = b->wk->qcol_off[b->list_cur].as<int64_t>();
     w.qcol_idx = b->wk->qcol_idx[b->list_cur].as<int32_t>();
     w.pl = b->wk->pl.as<double>(); w.pu = b->wk->pu.as<double>();
+    static const bool no_skip = getenv("NNVB_NO_RANGE_SKIP") != nullptr;
+    bool skip_useful = false;     // some cohort's windows cover at most half of the image
+    for (auto& co : b->cohorts)
+        skip_useful = skip_useful || 2 * int64_t(co.wh) * co.ww <= b->shape[0] * b->shape[1];
+    w.box = (no_skip || !skip_useful) ? nullptr : b->wk->box.as<int4>();
+    w.n_list = b->h_qcol_off[nq];
+    NNVB_TRY(b->wk->gbox.ensure(sizeof(int4) * size_t(w.n_list / 16 + 2), st));
+    w.gbox = b->wk->gbox.as<int4>();
+    w.img_h = int(b->shape[0]); w.img_w = int(b->shape[1]);
     w.n_chunks = n_chunks;
     w.chunk_beg = b->wk->chunk_beg.as<int64_t>(); w.chunk_end = b->wk->chunk_end.as<int64_t>();
     w.q_chunk_off = b->wk->q_chunk_off.as<int32_t>();
@@ -1063,8 +1078,8 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
         NNVB_TRY(launch_relu_append(st, w, ncols_old, K_loc, rank, world, !lazy_onehot,
                                     world > 1 ? rec->P_in_dev.as<int64_t>() : nullptr, r, b->wk->col_q.as<int32_t>(),
                                     b->wk->pl.as<double>(), b->wk->pu.as<double>(), b->wk->col_pos.as<int64_t>(),
-                                    int(b->shape[0]), int(b->shape[1]), b->wk->win_h0.as<int32_t>(),
-                                    b->wk->win_w0.as<int32_t>(), b->wk->qcol_off[nxt].as<int64_t>(),
+                                    int(b->shape[0]), int(b->shape[1]), b->wk->box.as<int4>(),
+                                    b->wk->qcol_off[nxt].as<int64_t>(),
                                     b->wk->qcol_idx[nxt].as<int32_t>(), &ctx->launches));
     }
     b->list_cur = nxt;
@@ -1120,12 +1135,12 @@ int run_layers(nnvb_batch* b) {
                     if (windowed) {
                         NNVB_CUDA(cudaMemsetAsync(out + co.col0 * ld_out, 0, sizeof(double) * ld_out * (c1 - co.col0), st));
                         ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * wh * ww * double(c1 - co.col0));
-                        ColWindows win{b->wk->win_h0.as<int32_t>(), b->wk->win_w0.as<int32_t>(), wh, ww};
+                        ColWindows win{b->wk->box.as<int4>(), wh, ww};
                         NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, mask, win, co.col0, b->V, b->ld, out, ld_out,
                                                  c1 - co.col0, b->nq, &ctx->launches));
                     } else {
                         ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * L.cg.Ho * L.cg.Wo * double(c1 - co.col0));
-                        ColWindows win{nullptr, nullptr, 0, 0};
+                        ColWindows win{nullptr, 0, 0};
                         NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, mask, win, co.col0, b->V, b->ld, out, ld_out,
                                                  c1 - co.col0, b->nq, &ctx->launches));
                     }
@@ -1134,18 +1149,57 @@ int run_layers(nnvb_batch* b) {
                 NNVB_TRY(launch_conv_onehot(st, L.cg, L.cw, bn, hot_idx, ctx->rank, ctx->world, n_hot,
                                             out + n_dense * ld_out, ld_out, &ctx->launches));
             } else if (L.type == NNVB_LAYER_FC) {
-                {
-                    ProfScope ps(ctx, NNVB_PROF_FC, 2.0 * double(L.Co) * double(L.H * L.W * L.C) * double(n_dense));
-                    NNVB_TRY(launch_fc_f64(st, int(L.H * L.W * L.C), int(L.Co), L.fc_wt, L.fc_ldw, L.bias, b->V, b->ld,
-                                           out, ld_out, n_dense, b->nq, &ctx->launches));
+                // one launch per cohort: windowed cohorts contract only the weight rows of their windows
+                static const bool no_fcg = getenv("NNVB_NO_FC_GATHER") != nullptr;
+                const int In = int(L.H * L.W * L.C);
+                for (auto& co : b->cohorts) {
+                    const int64_t c1 = std::min(co.col1, n_dense);
+                    if (c1 <= co.col0) continue;
+                    const int64_t n = c1 - co.col0;
+                    const bool gather = !no_fcg && !co.dense && 2 * co.wh * co.ww <= L.H * L.W &&
+                                        fc_gather_fits(int(L.C), co.wh, co.ww);
+                    if (gather) {
+                        NNVB_TRY(b->wk->fcg.ensure(sizeof(int32_t) * fc_gather_scratch_ints(n, int(L.H), int(L.W), co.wh, co.ww), st));
+                        ProfScope ps(ctx, NNVB_PROF_FC, 2.0 * double(L.Co) * double(L.C) * co.wh * co.ww * double(n));
+                        NNVB_TRY(launch_fc_gather(st, int(L.H), int(L.W), int(L.C), co.wh, co.ww, int(L.Co), L.fc_wt, L.fc_ldw,
+                                                  b->wk->box.as<int4>(), co.col0, n, b->V, b->ld, out, ld_out,
+                                                  b->wk->fcg.as<int32_t>(), &ctx->launches));
+                    } else {
+                        ProfScope ps(ctx, NNVB_PROF_FC, 2.0 * double(L.Co) * double(In) * double(n));
+                        NNVB_TRY(launch_fc_f64(st, In, int(L.Co), L.fc_wt, L.fc_ldw, L.bias, b->V + co.col0 * b->ld, b->ld,
+                                               out + co.col0 * ld_out, ld_out, n, std::max<int64_t>(0, b->nq - co.col0),
+                                               &ctx->launches));
+                    }
                 }
                 ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(Nout) * double(n_hot));
                 NNVB_TRY(launch_fc_onehot(st, int(L.Co), L.fc_wt, L.fc_ldw, hot_idx, ctx->rank, ctx->world, n_hot,
                                           out + n_dense * ld_out, ld_out, &ctx->launches));
             } else {
-                {
-                    ProfScope ps(ctx, NNVB_PROF_AVGPOOL, 8.0 * double(b->N + Nout) * double(n_dense));
-                    NNVB_TRY(launch_avgpool_f64(st, L.pg, mask, b->V, b->ld, out, ld_out, n_dense, &ctx->launches));
+                for (auto& co : b->cohorts) {
+                    const int64_t c1 = std::min(co.col1, n_dense);
+                    if (c1 <= co.col0) continue;
+                    const int wh = (co.wh - 1 + L.pg.ph - 1) / L.pg.sh + 1;
+                    const int ww = (co.ww - 1 + L.pg.pw - 1) / L.pg.sw + 1;
+                    const bool windowed = !co.dense && wh * ww <= 128 && 2 * wh * ww <= L.pg.Ho * L.pg.Wo;
+                    if (windowed) {
+                        NNVB_CUDA(cudaMemsetAsync(out + co.col0 * ld_out, 0, sizeof(double) * ld_out * (c1 - co.col0), st));
+                        // bytes: the input windows read, the whole output column written (zero fill + patch)
+                        ProfScope ps(ctx, NNVB_PROF_AVGPOOL,
+                                     8.0 * (double(co.wh) * co.ww * L.pg.C + double(Nout)) * double(c1 - co.col0));
+                        ColWindows win{b->wk->box.as<int4>(), wh, ww};
+                        NNVB_TRY(launch_avgpool_windowed(st, L.pg, mask, win, co.col0, b->V, b->ld, out, ld_out,
+                                                         c1 - co.col0, &ctx->launches));
+                    } else {
+                        ProfScope ps(ctx, NNVB_PROF_AVGPOOL, 8.0 * double(b->N + Nout) * double(c1 - co.col0));
+                        // the kernel numbers columns from 0: shift the mask to the cohort's first column
+                        RowMask m2 = mask;
+                        if (m2.state != nullptr) {
+                            m2.col_q += co.col0;
+                            m2.ncols = std::max<int64_t>(0, mask.ncols - co.col0);
+                        }
+                        NNVB_TRY(launch_avgpool_f64(st, L.pg, m2, b->V + co.col0 * b->ld, b->ld, out + co.col0 * ld_out,
+                                                    ld_out, c1 - co.col0, &ctx->launches));
+                    }
                 }
                 ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(Nout) * double(n_hot));
                 NNVB_TRY(launch_avgpool_onehot(st, L.pg, hot_idx, ctx->rank, ctx->world, n_hot, out + n_dense * ld_out,
@@ -1153,7 +1207,8 @@ int run_layers(nnvb_batch* b) {
             }
             // windows of the output tensor
             if (L.type == NNVB_LAYER_FC) {
-                for (auto& co : b->cohorts) co.dense = true;
+                for (auto& co : b->cohorts) { co.dense = true; co.wh = co.ww = 1 << 20; }
+                NNVB_TRY(launch_fill_dense_windows(st, b->ncols, b->wk->box.as<int4>(), &ctx->launches));
             } else {
                 const bool cv = L.type == NNVB_LAYER_CONV2D;
                 const int eh = cv ? (L.cg.kh - 1) * L.cg.dh : L.pg.ph - 1, ew = cv ? (L.cg.kw - 1) * L.cg.dw : L.pg.pw - 1;
@@ -1161,15 +1216,16 @@ int run_layers(nnvb_batch* b) {
                 const int pt = cv ? L.cg.pad_t : L.pg.pad_t, pl_ = cv ? L.cg.pad_l : L.pg.pad_l;
                 bool any = false;
                 for (auto& co : b->cohorts) {
+                    // sizes are tracked for dense cohorts too: they still steer the bound reduction
+                    co.wh = std::min((co.wh - 1 + eh) / sh + 1, 1 << 20);
+                    co.ww = std::min((co.ww - 1 + ew) / sw + 1, 1 << 20);
                     if (co.dense) continue;
-                    co.wh = (co.wh - 1 + eh) / sh + 1;
-                    co.ww = (co.ww - 1 + ew) / sw + 1;
-                    if (co.wh * co.ww > 128 || 2 * co.wh * co.ww > L.Ho * L.Wo) co.dense = true;
+                    if (int64_t(co.wh) * co.ww > 128 || 2 * int64_t(co.wh) * co.ww > L.Ho * L.Wo) co.dense = true;
                     else any = true;
                 }
-                if (any)
-                    NNVB_TRY(launch_update_windows(st, b->ncols, b->wk->win_h0.as<int32_t>(), b->wk->win_w0.as<int32_t>(), pt,
-                                                   pl_, eh, ew, sh, sw, &ctx->launches));
+                (void)any;      // the boxes also steer the bound reduction, so they are kept for every column
+                NNVB_TRY(launch_update_windows(st, b->ncols, b->wk->box.as<int4>(), pt, pl_, eh, ew, sh, sw,
+                                               &ctx->launches));
             }
             b->pend_mask_ncols = 0;
             b->pend_onehot = 0;
@@ -1285,11 +1341,17 @@ int witness_forward(nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, i
                 const Layer& B = net->layers[L.fused_bn];
                 bn = ChanAffine{B.bn_mean, B.bn_den, B.bn_rden, B.bn_scale, B.bn_offset};
             }
-            NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, RowMask{nullptr, nullptr, 0, 0}, ColWindows{nullptr, nullptr, 0, 0}, 0, cur, ld, oth, ld_out, n, n, &ctx->launches));
+            NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, RowMask{nullptr, nullptr, 0, 0}, ColWindows{nullptr, 0, 0}, 0, cur, ld, oth, ld_out, n, n, &ctx->launches));
             std::swap(cur, oth); N = Nout; ld = ld_out;
         } else if (L.type == NNVB_LAYER_FC) {
-            NNVB_TRY(launch_fc_f64(st, int(L.H * L.W * L.C), int(L.Co), L.fc_wt, L.fc_ldw, L.bias, cur, ld, oth, ld_out, n,
-                                   n, &ctx->launches));
+            if (n <= 96) {
+                const int In = int(L.H * L.W * L.C);
+                NNVB_TRY(b->wk->tmp.ensure(sizeof(double) * fc_skinny_scratch_doubles(In, int(L.Co), n), st));
+                NNVB_TRY(launch_fc_skinny(st, In, int(L.Co), L.fc_wt, L.fc_ldw, L.bias, cur, ld, oth, ld_out, n,
+                                          b->wk->tmp.as<double>(), &ctx->launches));
+            } else
+                NNVB_TRY(launch_fc_f64(st, int(L.H * L.W * L.C), int(L.Co), L.fc_wt, L.fc_ldw, L.bias, cur, ld, oth, ld_out,
+                                       n, n, &ctx->launches));
             std::swap(cur, oth); N = Nout; ld = ld_out;
         } else if (L.type == NNVB_LAYER_AVGPOOL2D) {
             NNVB_TRY(launch_avgpool_f64(st, L.pg, RowMask{nullptr, nullptr, 0, 0}, cur, ld, oth, ld_out, n, &ctx->launches));

@@ -203,6 +203,59 @@ int launch_fc_f64(cudaStream_t st, int In, int Out, const double* Wt, int ldw, c
 }
 
 namespace {
+// FullyConnected on a handful of columns (the witness points of the halfspace test): the tensor-core
+// tiles would be almost empty and the K loop of a single tile is latency bound.  Here block (x, y) owns
+// 32 outputs and a slice of 256 input rows: the slice of up to 8 columns is staged in shared memory,
+// each lane keeps one output, the 8 warps split the slice and are combined in warp order, and the
+// slice sums go to partial[slice][column][output]; a second kernel adds the slices in order plus the
+// bias (every column is a point).
+constexpr int SK_ROWS = 256;
+__global__ void __launch_bounds__(256)
+fc_skinny_kernel(int In, int Out, const double* __restrict__ Wt, int ldw, const double* __restrict__ Vin,
+                 int64_t ld_in, int ncols, double* __restrict__ partial) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int o = blockIdx.x * 32 + lane;
+    const int k0 = blockIdx.y * SK_ROWS;
+    __shared__ double vs[8][SK_ROWS];
+    __shared__ double red[8][8][33];
+    for (int c0 = 0; c0 < ncols; c0 += 8) {
+        const int nc = min(8, ncols - c0);
+        for (int e = threadIdx.x; e < 8 * SK_ROWS; e += 256) {
+            const int c = e / SK_ROWS, k = e % SK_ROWS;
+            vs[c][k] = (c < nc && k0 + k < In) ? Vin[int64_t(c0 + c) * ld_in + k0 + k] : 0.0;
+        }
+        __syncthreads();
+        double acc[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[c] = 0.0;
+        for (int kk = warp * 32; kk < warp * 32 + 32; ++kk) {
+            const double wv = (o < Out && k0 + kk < In) ? Wt[int64_t(k0 + kk) * ldw + o] : 0.0;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) acc[c] = fma(wv, vs[c][kk], acc[c]);
+        }
+#pragma unroll
+        for (int c = 0; c < 8; ++c) red[warp][c][lane] = acc[c];
+        __syncthreads();
+        for (int c = warp; c < nc; c += 8) {
+            double v = 0.0;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) v += red[w][c][lane];
+            if (o < Out) partial[(int64_t(blockIdx.y) * ncols + c0 + c) * Out + o] = v;
+        }
+        __syncthreads();
+    }
+}
+
+__global__ void fc_skinny_reduce_kernel(int Out, int ncols, int n_slices, const double* __restrict__ partial,
+                                        const double* __restrict__ bias, double* __restrict__ Vout, int64_t ld_out) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= ncols * Out) return;
+    const int c = e / Out, o = e % Out;
+    double v = 0.0;
+    for (int s = 0; s < n_slices; ++s) v += partial[(int64_t(s) * ncols + c) * Out + o];
+    Vout[int64_t(c) * ld_out + o] = v + bias[o];
+}
+
 // FullyConnected image of one-hot columns: W * e_i = W(:, i), i.e. row i of the transposed weight copy.
 __global__ void fc_onehot_kernel(int Out, const double* __restrict__ Wt, int ldw, const int32_t* __restrict__ rec_idx,
                                  int64_t c_first, int64_t c_step, double* __restrict__ Vout, int64_t ld_out) {
@@ -212,6 +265,249 @@ __global__ void fc_onehot_kernel(int Out, const double* __restrict__ Wt, int ldw
     for (int o = threadIdx.x; o < Out; o += blockDim.x) dst[o] = src[o];
 }
 }  // namespace
+
+namespace {
+
+// ---------------------------------------------------------------------------------------------------
+// FullyConnected on windowed columns.  A column that is zero outside an wh x ww window of the H x W x C
+// input only needs the C*wh*ww weight rows of that window:  out = sum_{rows in window} W(:, row) * v(row).
+// Columns are grouped by window origin (counting sort on the device), every tile of 128 columns shares
+// one origin and therefore one list of rows, and the contraction runs over that list only — the same
+// DMMA tiles as the dense kernel with gathered operands.  Values equal the dense product (the skipped
+// terms are products with zero), up to the order of the remaining additions.
+
+// key of a window origin; h0 in [-(wh-1), H-1], w0 in [-(ww-1), W-1]
+__device__ __forceinline__ int fcg_key(int4 bx, int wh, int ww, int KH, int nbins) {
+    int k = (bx.x + wh - 1) + KH * (bx.y + ww - 1);
+    return k < 0 ? 0 : (k >= nbins ? nbins - 1 : k);
+}
+
+__global__ void fcg_hist_kernel(int64_t col0, int64_t n, const int4* __restrict__ box, int wh, int ww, int KH,
+                                int nbins, int32_t* __restrict__ hist) {
+    const int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t < n) atomicAdd(hist + fcg_key(box[col0 + t], wh, ww, KH, nbins), 1);
+}
+
+// one thread: bin offsets and the tile table (a tile = up to 128 columns of one bin)
+__global__ void fcg_tiles_kernel(int nbins, const int32_t* __restrict__ hist, int32_t* __restrict__ bin_start,
+                                 int32_t* __restrict__ cursor, int32_t* __restrict__ tile_key,
+                                 int32_t* __restrict__ tile_start, int32_t* __restrict__ tile_count,
+                                 int32_t* __restrict__ n_tiles) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int off = 0, nt = 0;
+    for (int b = 0; b < nbins; ++b) {
+        bin_start[b] = off;
+        cursor[b] = 0;
+        const int cnt = hist[b];
+        for (int s0 = 0; s0 < cnt; s0 += 128) {
+            tile_key[nt] = b;
+            tile_start[nt] = off + s0;
+            tile_count[nt] = cnt - s0 < 128 ? cnt - s0 : 128;
+            ++nt;
+        }
+        off += cnt;
+    }
+    *n_tiles = nt;
+}
+
+__global__ void fcg_scatter_kernel(int64_t col0, int64_t n, const int4* __restrict__ box, int wh, int ww, int KH,
+                                   int nbins, const int32_t* __restrict__ bin_start, int32_t* __restrict__ cursor,
+                                   int32_t* __restrict__ perm) {
+    const int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= n) return;
+    const int key = fcg_key(box[col0 + t], wh, ww, KH, nbins);
+    perm[bin_start[key] + atomicAdd(cursor + key, 1)] = int32_t(col0 + t);
+}
+
+constexpr int FCG_WM = 2, FCG_WN = 8, FCG_WARPS_M = 4, FCG_WARPS_N = 2;
+
+__global__ void __launch_bounds__(256, 1)
+fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad, int Out,
+                 const double* __restrict__ Wt, int ldw, const double* __restrict__ Vin, int64_t ld_in,
+                 double* __restrict__ Vout, int64_t ld_out, const int32_t* __restrict__ tile_key,
+                 const int32_t* __restrict__ tile_start, const int32_t* __restrict__ tile_count,
+                 const int32_t* __restrict__ n_tiles, const int32_t* __restrict__ perm) {
+    using Cfg = FcCfg<FCG_WM, FCG_WN, FCG_WARPS_M, FCG_WARPS_N>;
+    if (int(blockIdx.x) >= *n_tiles) return;
+    extern __shared__ __align__(16) double smem[];
+    double* As = smem;
+    double* Bs = smem + FC_STAGES * Cfg::A_STAGE;
+    int* rows_s = reinterpret_cast<int*>(Bs + FC_STAGES * Cfg::B_STAGE);   // [Kt_pad] input row of k, -1 = none
+    int* cols_s = rows_s + Kt_pad;                                          // [128] column of tile row m, -1 = none
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp % FCG_WARPS_M, wn = warp / FCG_WARPS_M;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.y * Cfg::BN;
+
+    const int key = tile_key[blockIdx.x];
+    const int h0 = key % KH - (wh - 1), w0 = key / KH - (ww - 1);
+    const int start = tile_start[blockIdx.x], count = tile_count[blockIdx.x];
+    for (int m = tid; m < Cfg::BM; m += Cfg::THREADS) cols_s[m] = m < count ? perm[start + m] : -1;
+    for (int k = tid; k < Kt_pad; k += Cfg::THREADS) {
+        int row = -1;
+        if (k < Kt) {
+            const int hl = k % wh, r2 = k / wh;
+            const int wl = r2 % ww, c = r2 / ww;
+            const int h = h0 + hl, w = w0 + wl;
+            if (h >= 0 && h < H && w >= 0 && w < W) row = h + H * (w + W * c);
+        }
+        rows_s[k] = row;
+    }
+    __syncthreads();
+
+    auto load_stage = [&](int stage, int kt) {
+        const int k0 = kt * FC_BK;
+        double* a = As + stage * Cfg::A_STAGE;
+        double* b = Bs + stage * Cfg::B_STAGE;
+        for (int c = tid; c < Cfg::BM * FC_BK; c += Cfg::THREADS) {
+            const int m = c / FC_BK, kk = c % FC_BK;
+            const int row = rows_s[k0 + kk], col = cols_s[m];
+            const bool ok = row >= 0 && col >= 0;
+            cp_async8(a + m * FC_AST + kk, ok ? Vin + int64_t(col) * ld_in + row : Vin, ok ? 8 : 0);
+        }
+        for (int c = tid; c < FC_BK * (Cfg::BN / 2); c += Cfg::THREADS) {
+            const int kr = c / (Cfg::BN / 2), nc = c % (Cfg::BN / 2);
+            const int n = n0 + 2 * nc;
+            const int row = rows_s[k0 + kr];
+            const bool ok = row >= 0 && n < ldw;
+            cp_async16(b + kr * Cfg::BST + 2 * nc, ok ? Wt + int64_t(row) * ldw + n : Wt, ok ? 16 : 0);
+        }
+    };
+
+    double acc[FCG_WM][FCG_WN][4];
+#pragma unroll
+    for (int mi = 0; mi < FCG_WM; ++mi)
+#pragma unroll
+        for (int ni = 0; ni < FCG_WN; ++ni)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) acc[mi][ni][r] = 0.0;
+
+    const int KT = Kt_pad / FC_BK;
+#pragma unroll
+    for (int s = 0; s < FC_STAGES - 1; ++s) {
+        if (s < KT) load_stage(s, s);
+        cp_async_commit();
+    }
+    for (int kt = 0; kt < KT; ++kt) {
+        cp_async_wait<FC_STAGES - 2>();
+        __syncthreads();
+        {
+            const int nk = kt + FC_STAGES - 1;
+            if (nk < KT) load_stage(nk % FC_STAGES, nk);
+            cp_async_commit();
+        }
+        const double* a = As + (kt % FC_STAGES) * Cfg::A_STAGE + (wm * FCG_WM * 16 + g) * FC_AST + t;
+        const double* b = Bs + (kt % FC_STAGES) * Cfg::B_STAGE + t * Cfg::BST + wn * FCG_WN * 8 + g;
+#pragma unroll
+        for (int kk = 0; kk < FC_BK; kk += 8) {
+            double af[FCG_WM][4];
+            double bf[FCG_WN][2];
+#pragma unroll
+            for (int mi = 0; mi < FCG_WM; ++mi) {
+                const double* p = a + mi * 16 * FC_AST + kk;
+                af[mi][0] = p[0];
+                af[mi][1] = p[8 * FC_AST];
+                af[mi][2] = p[4];
+                af[mi][3] = p[8 * FC_AST + 4];
+            }
+#pragma unroll
+            for (int ni = 0; ni < FCG_WN; ++ni) {
+                const double* p = b + kk * Cfg::BST + ni * 8;
+                bf[ni][0] = p[0];
+                bf[ni][1] = p[4 * Cfg::BST];
+            }
+#pragma unroll
+            for (int mi = 0; mi < FCG_WM; ++mi)
+#pragma unroll
+                for (int ni = 0; ni < FCG_WN; ++ni) dmma_16x8x8(acc[mi][ni], af[mi], bf[ni]);
+        }
+    }
+    cp_async_wait<0>();
+
+#pragma unroll
+    for (int mi = 0; mi < FCG_WM; ++mi) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int col = cols_s[wm * FCG_WM * 16 + mi * 16 + g + half * 8];
+            if (col < 0) continue;
+            double* dst = Vout + int64_t(col) * ld_out;
+#pragma unroll
+            for (int ni = 0; ni < FCG_WN; ++ni) {
+                const int o = n0 + wn * FCG_WN * 8 + ni * 8 + 2 * t;
+                if (o >= Out) continue;
+                if (o + 1 < Out)
+                    *reinterpret_cast<double2*>(dst + o) = make_double2(acc[mi][ni][half * 2], acc[mi][ni][half * 2 + 1]);
+                else
+                    dst[o] = acc[mi][ni][half * 2];
+            }
+        }
+    }
+}
+
+}  // namespace
+
+size_t fc_gather_scratch_ints(int64_t n, int H, int W, int wh, int ww) {
+    const int64_t nbins = int64_t(H + wh - 1) * (W + ww - 1);
+    const int64_t max_tiles = ceil_div(n, 128) + nbins;
+    return size_t(3 * nbins + 3 * max_tiles + n + 8);
+}
+
+bool fc_gather_fits(int C, int wh, int ww) { return round_up(int64_t(C) * wh * ww, FC_BK) <= 16384; }
+
+int launch_fc_gather(cudaStream_t st, int H, int W, int C, int wh, int ww, int Out, const double* Wt, int ldw,
+                     const int4* box, int64_t col0, int64_t n, const double* Vin, int64_t ld_in, double* Vout,
+                     int64_t ld_out, int32_t* scratch, int64_t* launches) {
+    if (n <= 0) return NNVB_OK;
+    using Cfg = FcCfg<FCG_WM, FCG_WN, FCG_WARPS_M, FCG_WARPS_N>;
+    const int KH = H + wh - 1;
+    const int nbins = KH * (W + ww - 1);
+    const int64_t max_tiles = ceil_div(n, 128) + nbins;
+    int32_t* hist = scratch;
+    int32_t* bin_start = hist + nbins;
+    int32_t* cursor = bin_start + nbins;
+    int32_t* tile_key = cursor + nbins;
+    int32_t* tile_start = tile_key + max_tiles;
+    int32_t* tile_count = tile_start + max_tiles;
+    int32_t* n_tiles = tile_count + max_tiles;
+    int32_t* perm = n_tiles + 8;
+    NNVB_CUDA(cudaMemsetAsync(hist, 0, sizeof(int32_t) * nbins, st));
+    fcg_hist_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(col0, n, box, wh, ww, KH, nbins, hist);
+    fcg_tiles_kernel<<<1, 32, 0, st>>>(nbins, hist, bin_start, cursor, tile_key, tile_start, tile_count, n_tiles);
+    fcg_scatter_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(col0, n, box, wh, ww, KH, nbins, bin_start, cursor, perm);
+    const int Kt = C * wh * ww;
+    const int Kt_pad = (int)round_up(Kt, FC_BK);
+    const size_t smem = Cfg::SMEM + size_t(Kt_pad + 128) * sizeof(int);
+    static bool attr_set = false;
+    if (!attr_set) {
+        NNVB_CUDA(cudaFuncSetAttribute(fc_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(Cfg::SMEM + size_t(16384 + 128) * sizeof(int))));
+        attr_set = true;
+    }
+    dim3 grid((unsigned)max_tiles, (unsigned)ceil_div(Out, Cfg::BN));
+    fc_gather_kernel<<<grid, Cfg::THREADS, smem, st>>>(H, W, C, wh, ww, KH, Kt, Kt_pad, Out, Wt, ldw, Vin, ld_in, Vout,
+                                                      ld_out, tile_key, tile_start, tile_count, n_tiles, perm);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 4;
+    return NNVB_OK;
+}
+
+size_t fc_skinny_scratch_doubles(int In, int Out, int ncols) { return size_t(ceil_div(In, SK_ROWS)) * ncols * Out; }
+
+int launch_fc_skinny(cudaStream_t st, int In, int Out, const double* Wt, int ldw, const double* bias,
+                     const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out, int ncols, double* scratch,
+                     int64_t* launches) {
+    if (ncols <= 0) return NNVB_OK;
+    const int n_slices = (int)ceil_div(In, SK_ROWS);
+    dim3 grid((unsigned)ceil_div(Out, 32), (unsigned)n_slices);
+    fc_skinny_kernel<<<grid, 256, 0, st>>>(In, Out, Wt, ldw, Vin, ld_in, ncols, scratch);
+    NNVB_CUDA(cudaGetLastError());
+    fc_skinny_reduce_kernel<<<(unsigned)ceil_div(int64_t(ncols) * Out, 256), 256, 0, st>>>(Out, ncols, n_slices, scratch,
+                                                                                           bias, Vout, ld_out);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 2;
+    return NNVB_OK;
+}
 
 int launch_fc_onehot(cudaStream_t st, int Out, const double* Wt, int ldw, const int32_t* rec_idx, int64_t c_first,
                      int64_t c_step, int64_t K_loc, double* Vout, int64_t ld_out, int64_t* launches) {

@@ -49,12 +49,12 @@ range_partial_rows2_kernel(int64_t N, int64_t ld, const double* __restrict__ V,
             }
 #pragma unroll
             for (int u = 0; u < UNROLL; ++u) {
-                const double p0 = fmax(v[u].x, 0.0), n0 = fmin(v[u].x, 0.0);
-                const double p1 = fmax(v[u].y, 0.0), n1 = fmin(v[u].y, 0.0);
-                lo0 = fma(p0, a[u], lo0); lo0 = fma(n0, b[u], lo0);
-                hi0 = fma(p0, b[u], hi0); hi0 = fma(n0, a[u], hi0);
-                lo1 = fma(p1, a[u], lo1); lo1 = fma(n1, b[u], lo1);
-                hi1 = fma(p1, b[u], hi1); hi1 = fma(n1, a[u], hi1);
+                // max(v,0)*pl + min(v,0)*pu == v * (v > 0 ? pl : pu): one product per bound
+                const bool s0 = v[u].x > 0.0, s1 = v[u].y > 0.0;
+                lo0 = fma(v[u].x, s0 ? a[u] : b[u], lo0);
+                hi0 = fma(v[u].x, s0 ? b[u] : a[u], hi0);
+                lo1 = fma(v[u].y, s1 ? a[u] : b[u], lo1);
+                hi1 = fma(v[u].y, s1 ? b[u] : a[u], hi1);
             }
         }
     }
@@ -77,6 +77,101 @@ range_partial_rows2_kernel(int64_t N, int64_t ld, const double* __restrict__ V,
     plo[i] = lo0;
     phi[i] = hi0;
     if (two) { plo[i + 1] = lo1; phi[i + 1] = hi1; }
+}
+
+// The same partial sums with window skipping.  A column is exactly zero outside its window box[col], so it
+// adds nothing to the rows of a warp whose 64 rows (one channel, pixel columns wA..wB) lie outside it;
+// skipping it leaves the sums unchanged (the skipped terms are products with zero).  The test is uniform
+// over the warp.  Four candidate columns at a time: their index and window loads are in flight together,
+// then the loads of those that hit; the sums are still formed in column order.
+__global__ void __launch_bounds__(256, 3)
+range_partial_skip_kernel(int64_t N, int64_t ld, const double* __restrict__ V,
+                          const int32_t* __restrict__ qcol_idx, const double* __restrict__ pl,
+                          const double* __restrict__ pu, const int64_t* __restrict__ chunk_beg,
+                          const int64_t* __restrict__ chunk_end, double* __restrict__ partial,
+                          const int4* __restrict__ box, const int4* __restrict__ gbox, int img_h, int img_w) {
+    const int chunk = blockIdx.x;
+    const int64_t i = (int64_t(blockIdx.y) * blockDim.x + threadIdx.x) * 2;
+    if (i >= N) return;
+    const bool two = i + 1 < N;
+    const int64_t beg = chunk_beg[chunk], end = chunk_end[chunk];
+    double lo0 = 0.0, hi0 = 0.0, lo1 = 0.0, hi1 = 0.0;
+    const int64_t wr0 = (int64_t(blockIdx.y) * blockDim.x + (threadIdx.x & ~31)) * 2;
+    const int64_t wr1 = wr0 + 63 < N ? wr0 + 63 : N - 1;
+    const int64_t hw = int64_t(img_h) * img_w;
+    // rows of the warp: one channel plane, pixel columns wA..wB (rows hA..hB when it is a single column);
+    // a warp that straddles two planes tests nothing away
+    int wA = 0, wB = 1 << 29, hA = 0, hB = 1 << 29;
+    if (wr0 / hw == wr1 / hw) {
+        const int o0 = int(wr0 % hw), o1 = int(wr1 % hw);
+        wA = o0 / img_h;
+        wB = o1 / img_h;
+        hA = wA == wB ? o0 - wA * img_h : 0;
+        hB = wA == wB ? o1 - wB * img_h : img_h - 1;
+    } else {
+        wA = -(1 << 29);
+        hA = -(1 << 29);
+    }
+    // Columns are listed in the order of the pixels / neurons they come from, so 16 consecutive list
+    // entries lie close together: their joint bounding box gbox[g] = {w_lo, w_hi, h_lo, h_hi} (exclusive
+    // ends) prunes most of the list with one test per group.
+    for (int64_t grp = beg / 16; grp * 16 < end; ++grp) {
+      const int4 gb = gbox[grp];
+      if (gb.x > wB || gb.y <= wA || gb.z > hB || gb.w <= hA) continue;
+      const int64_t gp0 = grp * 16 > beg ? grp * 16 : beg;
+      const int64_t gp1 = grp * 16 + 16 < end ? grp * 16 + 16 : end;
+      for (int64_t pos = gp0; pos < gp1; pos += 4) {
+        int64_t cand[4];
+        int4 bx[4];
+        bool hit[4];
+        double2 v[4];
+        double a[4], b[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) cand[u] = pos + u < gp1 ? int64_t(qcol_idx[pos + u]) : int64_t(-1);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) bx[u] = cand[u] >= 0 ? box[cand[u]] : make_int4(0, 0, 0, 0);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            hit[u] = cand[u] >= 0 && !(bx[u].y > wB || bx[u].y + bx[u].w <= wA || bx[u].x > hB || bx[u].x + bx[u].z <= hA);
+            if (hit[u]) {
+                v[u] = two ? __ldcs(reinterpret_cast<const double2*>(V + cand[u] * ld + i))
+                           : make_double2(V[cand[u] * ld + i], 0.0);
+                a[u] = pl[cand[u]];
+                b[u] = pu[cand[u]];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (hit[u]) {
+                // max(v,0)*pl + min(v,0)*pu == v * (v > 0 ? pl : pu): one product per bound
+                const bool s0 = v[u].x > 0.0, s1 = v[u].y > 0.0;
+                lo0 = fma(v[u].x, s0 ? a[u] : b[u], lo0);
+                hi0 = fma(v[u].x, s0 ? b[u] : a[u], hi0);
+                lo1 = fma(v[u].y, s1 ? a[u] : b[u], lo1);
+                hi1 = fma(v[u].y, s1 ? b[u] : a[u], hi1);
+            }
+        }
+      }
+    }
+    double* plo = partial + int64_t(chunk) * 2 * N;
+    double* phi = plo + N;
+    plo[i] = lo0;
+    phi[i] = hi0;
+    if (two) { plo[i + 1] = lo1; phi[i + 1] = hi1; }
+}
+
+// Joint bounding box {w_lo, w_hi, h_lo, h_hi} (exclusive ends) of every 16 consecutive list entries.
+__global__ void group_boxes_kernel(int64_t n_list, const int32_t* __restrict__ qcol_idx, const int4* __restrict__ box,
+                                   int4* __restrict__ gbox) {
+    const int64_t g = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (g * 16 >= n_list) return;
+    int wl = 1 << 30, wh = -(1 << 30), hl = 1 << 30, hh = -(1 << 30);
+    for (int64_t p = g * 16; p < g * 16 + 16 && p < n_list; ++p) {
+        const int4 b = box[qcol_idx[p]];
+        wl = min(wl, b.y); wh = max(wh, b.y + b.w);
+        hl = min(hl, b.x); hh = max(hh, b.x + b.z);
+    }
+    gbox[g] = make_int4(wl, wh, hl, hh);
 }
 
 // Narrow sets (few rows, many columns): a warp owns 32 rows, the 8 warps of a
@@ -118,7 +213,7 @@ range_partial_narrow_kernel(int64_t N, int64_t ld, const double* __restrict__ V,
 // ---------------------------------------------------------------------------
 // 2a. finalize bounds and classify.  grid = (nq, row blocks of FIN_ROWS).
 constexpr int FIN_THREADS = 256;
-constexpr int FIN_ROWS = 1024;   // rows per block (4 per thread)
+constexpr int FIN_ROWS = 256;    // rows per block (1 per thread)
 
 __global__ void __launch_bounds__(FIN_THREADS)
 range_finalize_kernel(int64_t N, int64_t ld, const double* __restrict__ V,
@@ -133,7 +228,19 @@ range_finalize_kernel(int64_t N, int64_t ld, const double* __restrict__ V,
         if (i >= N) break;
         const double c = V[int64_t(q) * ld + i];     // centre column of query q is column q
         double lo = 0.0, hi = 0.0;
-        for (int ch = c0; ch < c1; ++ch) {
+        int ch = c0;
+        for (; ch + 8 <= c1; ch += 8) {            // eight chunk partials in flight, added in chunk order
+            double a[8], bq[8];
+#pragma unroll
+            for (int u8 = 0; u8 < 8; ++u8) {
+                const double* pp = partial + int64_t(ch + u8) * 2 * N;
+                a[u8] = pp[i];
+                bq[u8] = pp[N + i];
+            }
+#pragma unroll
+            for (int u8 = 0; u8 < 8; ++u8) { lo += a[u8]; hi += bq[u8]; }
+        }
+        for (; ch < c1; ++ch) {
             const double* pp = partial + int64_t(ch) * 2 * N;
             lo += pp[i];
             hi += pp[N + i];
@@ -301,8 +408,7 @@ __global__ void append_cols_kernel(int64_t K_loc, int rank, int world, int write
                                    const int64_t* __restrict__ q_new_off, const int64_t* __restrict__ qcol_off,
                                    const int64_t* __restrict__ P_in, int32_t* __restrict__ col_q,
                                    double* __restrict__ pl, double* __restrict__ pu,
-                                   int64_t* __restrict__ col_pos, int img_h, int img_w,
-                                   int32_t* __restrict__ win_h0, int32_t* __restrict__ win_w0) {
+                                   int64_t* __restrict__ col_pos, int img_h, int img_w, int4* __restrict__ box) {
     const int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (t >= K_loc) return;
     const int64_t c = rank + t * world;
@@ -315,8 +421,7 @@ __global__ void append_cols_kernel(int64_t K_loc, int rank, int world, int write
     // position in the query's predicate order (over all ranks)
     const int64_t p_in = P_in ? P_in[q] : (qcol_off[q + 1] - qcol_off[q]);
     col_pos[col] = p_in + (c - q_new_off[q]);
-    win_h0[col] = rec_idx[c] % img_h;                  // a unit vector: non-zero at one pixel
-    win_w0[col] = (rec_idx[c] / img_h) % img_w;
+    box[col] = make_int4(rec_idx[c] % img_h, (rec_idx[c] / img_h) % img_w, 1, 1);   // a unit vector: one pixel
 }
 
 // 3c. new predicate-ordered column lists: old list of the query, then its new
@@ -574,8 +679,16 @@ int launch_estimate_ranges(cudaStream_t st, const ReluWork& w, int64_t* launches
     if (w.n_chunks > 0) {
         if (w.N >= 256) {
             dim3 grid((unsigned)w.n_chunks, (unsigned)ceil_div(ceil_div(w.N, 2), 256));
-            range_partial_rows2_kernel<4><<<grid, 256, 0, st>>>(w.N, w.ld, w.V, w.qcol_idx, w.pl, w.pu,
-                                                               w.chunk_beg, w.chunk_end, w.partial);
+            if (w.box != nullptr) {
+                group_boxes_kernel<<<(unsigned)ceil_div(ceil_div(w.n_list, 16), 128), 128, 0, st>>>(w.n_list, w.qcol_idx,
+                                                                                                   w.box, w.gbox);
+                if (launches) *launches += 1;
+                range_partial_skip_kernel<<<grid, 256, 0, st>>>(w.N, w.ld, w.V, w.qcol_idx, w.pl, w.pu, w.chunk_beg,
+                                                                w.chunk_end, w.partial, w.box, w.gbox, w.img_h, w.img_w);
+            }
+            else
+                range_partial_rows2_kernel<4><<<grid, 256, 0, st>>>(w.N, w.ld, w.V, w.qcol_idx, w.pl, w.pu,
+                                                                   w.chunk_beg, w.chunk_end, w.partial);
         } else {
             dim3 grid((unsigned)w.n_chunks, (unsigned)ceil_div(w.N, 32));
             range_partial_narrow_kernel<<<grid, 256, 0, st>>>(w.N, w.ld, w.V, w.qcol_idx, w.pl, w.pu,
@@ -640,7 +753,7 @@ int launch_relu_zero_rows(cudaStream_t st, const ReluWork& w, int64_t ncols, con
 
 int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, int64_t K_loc, int rank, int world,
                        bool materialize, const int64_t* P_in, const ReluRecord& rec, int32_t* col_q, double* pl, double* pu,
-                       int64_t* col_pos, int img_h, int img_w, int32_t* win_h0, int32_t* win_w0,
+                       int64_t* col_pos, int img_h, int img_w, int4* box,
                        int64_t* new_qcol_off, int32_t* new_qcol_idx, int64_t* launches) {
     if (K_loc > 0) {
         if (materialize) NNVB_CUDA(cudaMemsetAsync(w.V + ncols_old * w.ld, 0, sizeof(double) * w.ld * K_loc, st));
@@ -648,7 +761,7 @@ int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, in
                                                                           w.ld, w.V, ncols_old,
                                                                           rec.idx, rec.q, rec.u, w.q_new_off,
                                                                           w.qcol_off, P_in, col_q, pl, pu, col_pos, img_h,
-                                                                          img_w, win_h0, win_w0);
+                                                                          img_w, box);
         NNVB_CUDA(cudaGetLastError());
         if (launches) *launches += 1;
     }
