@@ -271,7 +271,7 @@ namespace {
 // ---------------------------------------------------------------------------------------------------
 // FullyConnected on windowed columns.  A column that is zero outside an wh x ww window of the H x W x C
 // input only needs the C*wh*ww weight rows of that window:  out = sum_{rows in window} W(:, row) * v(row).
-// Columns are grouped by window origin (counting sort on the device), every tile of 128 columns shares
+// Columns are grouped by window origin (counting sort on the device), every tile of 32 columns shares
 // one origin and therefore one list of rows, and the contraction runs over that list only — the same
 // DMMA tiles as the dense kernel with gathered operands.  Values equal the dense product (the skipped
 // terms are products with zero), up to the order of the remaining additions.
@@ -288,8 +288,8 @@ __global__ void fcg_hist_kernel(int64_t col0, int64_t n, const int4* __restrict_
     if (t < n) atomicAdd(hist + fcg_key(box[col0 + t], wh, ww, KH, nbins), 1);
 }
 
-// one thread: bin offsets and the tile table (a tile = up to 128 columns of one bin)
-__global__ void fcg_tiles_kernel(int nbins, const int32_t* __restrict__ hist, int32_t* __restrict__ bin_start,
+// one thread: bin offsets and the tile table (a tile = up to tile_cols columns of one bin)
+__global__ void fcg_tiles_kernel(int nbins, int tile_cols, const int32_t* __restrict__ hist, int32_t* __restrict__ bin_start,
                                  int32_t* __restrict__ cursor, int32_t* __restrict__ tile_key,
                                  int32_t* __restrict__ tile_start, int32_t* __restrict__ tile_count,
                                  int32_t* __restrict__ n_tiles) {
@@ -299,10 +299,10 @@ __global__ void fcg_tiles_kernel(int nbins, const int32_t* __restrict__ hist, in
         bin_start[b] = off;
         cursor[b] = 0;
         const int cnt = hist[b];
-        for (int s0 = 0; s0 < cnt; s0 += 128) {
+        for (int s0 = 0; s0 < cnt; s0 += tile_cols) {
             tile_key[nt] = b;
             tile_start[nt] = off + s0;
-            tile_count[nt] = cnt - s0 < 128 ? cnt - s0 : 128;
+            tile_count[nt] = cnt - s0 < tile_cols ? cnt - s0 : tile_cols;
             ++nt;
         }
         off += cnt;
@@ -319,7 +319,10 @@ __global__ void fcg_scatter_kernel(int64_t col0, int64_t n, const int4* __restri
     perm[bin_start[key] + atomicAdd(cursor + key, 1)] = int32_t(col0 + t);
 }
 
-constexpr int FCG_WM = 2, FCG_WN = 8, FCG_WARPS_M = 4, FCG_WARPS_N = 2;
+// Tiles of 32 columns x 256 outputs: columns sharing a window origin come in small groups (tens), so a
+// short M tile keeps the tiles full; the weight rows of a tile are then re-read from L2 once per 32 columns.
+constexpr int FCG_WM = 1, FCG_WN = 8, FCG_WARPS_M = 2, FCG_WARPS_N = 4;
+constexpr int FCG_BM = FCG_WARPS_M * FCG_WM * 16;
 
 __global__ void __launch_bounds__(256, 1)
 fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad, int Out,
@@ -333,7 +336,7 @@ fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad
     double* As = smem;
     double* Bs = smem + FC_STAGES * Cfg::A_STAGE;
     int* rows_s = reinterpret_cast<int*>(Bs + FC_STAGES * Cfg::B_STAGE);   // [Kt_pad] input row of k, -1 = none
-    int* cols_s = rows_s + Kt_pad;                                          // [128] column of tile row m, -1 = none
+    int* cols_s = rows_s + Kt_pad;                                          // [BM] column of tile row m, -1 = none
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wm = warp % FCG_WARPS_M, wn = warp / FCG_WARPS_M;
@@ -449,7 +452,7 @@ fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad
 
 size_t fc_gather_scratch_ints(int64_t n, int H, int W, int wh, int ww) {
     const int64_t nbins = int64_t(H + wh - 1) * (W + ww - 1);
-    const int64_t max_tiles = ceil_div(n, 128) + nbins;
+    const int64_t max_tiles = ceil_div(n, FCG_BM) + nbins;
     return size_t(3 * nbins + 3 * max_tiles + n + 8);
 }
 
@@ -462,7 +465,7 @@ int launch_fc_gather(cudaStream_t st, int H, int W, int C, int wh, int ww, int O
     using Cfg = FcCfg<FCG_WM, FCG_WN, FCG_WARPS_M, FCG_WARPS_N>;
     const int KH = H + wh - 1;
     const int nbins = KH * (W + ww - 1);
-    const int64_t max_tiles = ceil_div(n, 128) + nbins;
+    const int64_t max_tiles = ceil_div(n, FCG_BM) + nbins;
     int32_t* hist = scratch;
     int32_t* bin_start = hist + nbins;
     int32_t* cursor = bin_start + nbins;
@@ -473,7 +476,7 @@ int launch_fc_gather(cudaStream_t st, int H, int W, int C, int wh, int ww, int O
     int32_t* perm = n_tiles + 8;
     NNVB_CUDA(cudaMemsetAsync(hist, 0, sizeof(int32_t) * nbins, st));
     fcg_hist_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(col0, n, box, wh, ww, KH, nbins, hist);
-    fcg_tiles_kernel<<<1, 32, 0, st>>>(nbins, hist, bin_start, cursor, tile_key, tile_start, tile_count, n_tiles);
+    fcg_tiles_kernel<<<1, 32, 0, st>>>(nbins, FCG_BM, hist, bin_start, cursor, tile_key, tile_start, tile_count, n_tiles);
     fcg_scatter_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(col0, n, box, wh, ww, KH, nbins, bin_start, cursor, perm);
     const int Kt = C * wh * ww;
     const int Kt_pad = (int)round_up(Kt, FC_BK);
