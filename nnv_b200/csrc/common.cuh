@@ -85,9 +85,10 @@ struct RowMask {
     int64_t N;
 };
 
-// Windowed columns: column j (absolute index) is exactly zero outside the input window that starts at
-// (box[j].x, box[j].y) (may lie partly outside the image); wh x ww is the size of the OUTPUT patch the layer
-// computes for each such column.  box == nullptr: dense columns.
+// Column windows: column j (absolute index) is exactly zero outside its input window box[j] = {h0, w0, h
+// extent, w extent} (may lie partly outside the image).  Memory outside a window may hold stale data, so
+// every reader treats it as zero.  wh x ww > 0 is the size of the OUTPUT patch a windowed launch computes
+// for each column; wh == 0 asks for the whole output image (dense launch).  box == nullptr: no windows.
 struct ColWindows {
     const int4* box;        // per column {h0, w0, wh, ww} of its input window
     int wh, ww;
@@ -108,9 +109,14 @@ int launch_conv_f64(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, co
 
 // Images of the one-hot columns a ReLU step appended (column t of this rank is batch-wide column
 // c_first + t*c_step, the unit vector of neuron rec_idx[c]); written to Vout[ld_out x K_loc].
+// zero_fill: clear the whole output block first (else only the columns' output windows are written).
 int launch_conv_onehot(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
                        const int32_t* rec_idx, int64_t c_first, int64_t c_step, int64_t K_loc, double* Vout,
-                       int64_t ld_out, int64_t* launches);
+                       int64_t ld_out, bool zero_fill, int64_t* launches);
+// Writes zero to every entry of columns [col0, col0+n) of V (an H x W x C image per column) that lies
+// outside the column's window box[col]: afterwards the columns can be read without window tests.
+int launch_zero_outside_windows(cudaStream_t st, int H, int W, int C, const int4* box, int64_t col0, int64_t n,
+                                double* V, int64_t ld, int64_t* launches);
 // FC on windowed columns [col0, col0+n) (all with an wh x ww window in the H x W x C input; origins in box):
 // only the weight rows of each column's window are contracted.  scratch: fc_gather_scratch_ints() int32.
 size_t fc_gather_scratch_ints(int64_t n, int H, int W, int wh, int ww);
@@ -142,10 +148,13 @@ struct PoolGeom {
     int H, W, C, Ho, Wo;
     int ph, pw, sh, sw, pad_t, pad_l;
 };
-int launch_avgpool_f64(cudaStream_t st, const PoolGeom& g, const RowMask& mask, const double* Vin, int64_t ld_in,
-                       double* Vout, int64_t ld_out, int64_t ncols, int64_t* launches);
+// box (nullable): per-column input windows, indexed like Vin's columns; entries outside count as zero.
+int launch_avgpool_f64(cudaStream_t st, const PoolGeom& g, const RowMask& mask, const int4* box, const double* Vin,
+                       int64_t ld_in, double* Vout, int64_t ld_out, int64_t ncols, int64_t* launches);
+// zero_fill: clear the whole output block first (else only the columns' output windows are written).
 int launch_avgpool_onehot(cudaStream_t st, const PoolGeom& g, const int32_t* rec_idx, int64_t c_first,
-                          int64_t c_step, int64_t K_loc, double* Vout, int64_t ld_out, int64_t* launches);
+                          int64_t c_step, int64_t K_loc, double* Vout, int64_t ld_out, bool zero_fill,
+                          int64_t* launches);
 
 // ReLU approx-star step; see relu_star.cu.  All pointers are device pointers.
 struct ReluWork {
@@ -212,7 +221,9 @@ int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, in
 int launch_halfspace_pairs(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t Nout, int64_t ld,
                            const double* V, const int64_t* qcol_off, const int32_t* qcol_idx, const double* pl,
                            const double* pu, const double* G, const double* g, double* margin, double* r_out,
-                           const int64_t* r_off, const int64_t* col_pos, int add_center, int64_t* launches);
+                           const int64_t* r_off, const int64_t* col_pos, int add_center, double* part,
+                           int64_t* launches);
+constexpr int HS_SPLIT = 32;     // slices of a query's column list; `part` holds n_pairs * HS_SPLIT doubles
 // Witness search kernels (one point per pair, X is [ld x n_pairs]).
 int launch_witness_x0_bounds(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t N, int64_t ld,
                              const double* lbub, const double* r, const int64_t* r_off, double* X,

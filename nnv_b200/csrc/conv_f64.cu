@@ -87,12 +87,15 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
     // Origin of each column's output patch.  Dense columns: the spatial tile.  Windowed columns: every
     // column is zero outside a small window [h0, h0+wh) x [w0, w0+ww) of the input; the outputs that
     // can be non-zero form a TH x TW patch starting at ceil((h0 + pad - (k-1)*dil) / stride), and only
-    // that patch is computed (the rest of the output column was zero filled).
+    // that patch is computed and written; the rest of the output column is left as it is.
     __shared__ int org_h[128], org_w[128];
+    __shared__ int4 in_box[128];
     if (tid < p.NJ) {
         int a = oh0, b2 = ow0;
-        if (win.box != nullptr && j0 + tid < ncols) {
-            const int4 bx = win.box[col_base + j0 + tid];
+        int4 bx = make_int4(NNVB_DENSE_ORIGIN, NNVB_DENSE_ORIGIN, NNVB_DENSE_EXTENT, NNVB_DENSE_EXTENT);
+        if (win.box != nullptr && j0 + tid < ncols) bx = win.box[col_base + j0 + tid];
+        in_box[tid] = bx;
+        if (win.wh > 0 && j0 + tid < ncols) {
             const int ah = bx.x + p.g.pad_t - (p.g.kh - 1) * p.g.dh;
             const int aw = bx.y + p.g.pad_l - (p.g.kw - 1) * p.g.dw;
             a = ah >= 0 ? (ah + p.g.sh - 1) / p.g.sh : -((-ah) / p.g.sh);
@@ -112,7 +115,11 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
         const int hi = org_h[jl] * p.g.sh - p.g.pad_t + hl;
         const int wi = org_w[jl] * p.g.sw - p.g.pad_l + wl;
         int off = -1, moff = -1;
-        if (hi >= 0 && hi < H && wi >= 0 && wi < W && j0 + jl < ncols) {
+        // Outside its window a column is zero by construction; the memory there may hold stale data (the
+        // producer wrote the window only), so such elements are zero filled like the padding.
+        const int4 ib = in_box[jl];
+        const bool in_win = unsigned(hi - ib.x) < unsigned(ib.z) && unsigned(wi - ib.y) < unsigned(ib.w);
+        if (hi >= 0 && hi < H && wi >= 0 && wi < W && j0 + jl < ncols && in_win) {
             off = int(jl * ld_in) + hi + H * wi;
             // rows cleared by the preceding ReLU step are masked here instead of being zeroed in memory
             if (mask.state != nullptr && col_base + j0 + jl < mask.ncols)
@@ -295,8 +302,10 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
 //   out(oh, ow, co) = W(kh, kw, ci, co)   wherever oh*sh - pt + kh*dh = h and ow*sw - pl + kw*dw = w,
 // times the generator part of the fused affine.  No products are formed, so the values equal what the
 // dense contraction of that column gives (every other term of its sums is a product with zero).
-// The output block is zero filled beforehand.  One block per column, lanes over (tap, output channel);
-// this rank's column t is the batch-wide column c = c_first + t*c_step with neuron rec_idx[c].
+// Every entry of the column's output window (origin and extent as update_windows_kernel derives them from
+// a 1x1 input window) is written, zeros included; nothing outside it is touched.  One block per column,
+// lanes over (window position, output channel); this rank's column t is the batch-wide column
+// c = c_first + t*c_step with neuron rec_idx[c].
 __global__ void __launch_bounds__(128)
 conv_onehot_kernel(ConvGeom g, const double* __restrict__ Wg, int bn_tile, int cs, int n_chunks, ChanAffine bn,
                    const int32_t* __restrict__ rec_idx, int64_t c_first, int64_t c_step,
@@ -308,19 +317,26 @@ conv_onehot_kernel(ConvGeom g, const double* __restrict__ Wg, int bn_tile, int c
     const int ci = i / (g.H * g.W);
     const int taps = g.kh * g.kw;
     const int ch = ci / KC, cil = ci % KC;
+    const int eh = (g.kh - 1) * g.dh, ew = (g.kw - 1) * g.dw;
+    const int wh = eh / g.sh + 1, ww = ew / g.sw + 1;
+    const int ah = h + g.pad_t - eh, aw = w + g.pad_l - ew;
+    const int org_h = ah >= 0 ? (ah + g.sh - 1) / g.sh : -((-ah) / g.sh);
+    const int org_w = aw >= 0 ? (aw + g.sw - 1) / g.sw : -((-aw) / g.sw);
     double* dst = Vout + t * ld_out;
-    for (int e = threadIdx.x; e < taps * g.Cout; e += blockDim.x) {
+    for (int e = threadIdx.x; e < wh * ww * g.Cout; e += blockDim.x) {
         const int co = e % g.Cout;
-        const int tap = e / g.Cout;
-        const int khi = tap % g.kh, kwi = tap / g.kh;
-        const int hn = h + g.pad_t - khi * g.dh;
-        const int wn = w + g.pad_l - kwi * g.dw;
-        if (hn < 0 || wn < 0 || hn % g.sh != 0 || wn % g.sw != 0) continue;
-        const int oh = hn / g.sh, ow = wn / g.sw;
-        if (oh >= g.Ho || ow >= g.Wo) continue;
-        const int nt = co / bn_tile, n = co % bn_tile;
-        double v = Wg[((((int64_t(nt) * n_chunks + ch) * taps + tap) * KC + cil) * cs) + n];
-        if (bn.rden != nullptr) v = (v * bn.rden[co]) * bn.scale[co];
+        const int pos = e / g.Cout;
+        const int oh = org_h + pos % wh, ow = org_w + pos / wh;
+        if (oh < 0 || ow < 0 || oh >= g.Ho || ow >= g.Wo) continue;
+        // the tap that maps output (oh, ow) to input (h, w), if there is one
+        const int dh_ = h + g.pad_t - oh * g.sh, dw_ = w + g.pad_l - ow * g.sw;
+        double v = 0.0;
+        if (dh_ >= 0 && dw_ >= 0 && dh_ % g.dh == 0 && dw_ % g.dw == 0 && dh_ / g.dh < g.kh && dw_ / g.dw < g.kw) {
+            const int tap = dh_ / g.dh + g.kh * (dw_ / g.dw);
+            const int nt = co / bn_tile, n = co % bn_tile;
+            v = Wg[((((int64_t(nt) * n_chunks + ch) * taps + tap) * KC + cil) * cs) + n];
+            if (bn.rden != nullptr) v = (v * bn.rden[co]) * bn.scale[co];
+        }
         dst[oh + int64_t(g.Ho) * (ow + int64_t(g.Wo) * co)] = v;
     }
 }
@@ -360,6 +376,8 @@ int launch_variant(cudaStream_t st, const ConvParams& p, dim3 grid, size_t smem,
                    const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out, int64_t ncols, int64_t n_center) {
     auto kern = conv_f64_kernel<WM_TILES, WN_TILES, WARPS_M, WARPS_N, STAGES, MIN_BLOCKS>;
     NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // ask for the largest shared-memory carve-out so that MIN_BLOCKS CTAs really are resident
+    NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     kern<<<grid, WARPS_M * WARPS_N * 32, smem, st>>>(p, w.w, w.bias, bn, mask, win, col_base, Vin, ld_in, Vout, ld_out,
                                                      ncols, n_center);
     NNVB_CUDA(cudaGetLastError());
@@ -374,7 +392,7 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
     constexpr int BN = WARPS_N * WN_TILES * 8;
     ConvParams p;
     p.g = g;
-    if (win.box != nullptr) {
+    if (win.wh > 0) {
         // one patch of wh x ww outputs per column, as many columns per tile as fit
         if (win.wh * win.ww > BM || win.wh < 1 || win.ww < 1) {
             set_error("conv: output window %dx%d does not fit a tile", win.wh, win.ww);
@@ -391,8 +409,8 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
     p.plane = p.NJ * p.HH * p.HW;
     p.PS = pad_stride(p.plane);
     p.CS = w.cs;
-    p.n_th = win.box != nullptr ? 1 : (int)ceil_div(g.Ho, p.TH);
-    p.n_tw = win.box != nullptr ? 1 : (int)ceil_div(g.Wo, p.TW);
+    p.n_th = win.wh > 0 ? 1 : (int)ceil_div(g.Ho, p.TH);
+    p.n_tw = win.wh > 0 ? 1 : (int)ceil_div(g.Wo, p.TW);
     p.n_chunks = w.n_chunks;
     p.taps = g.kh * g.kw;
     p.halo_stage = KC * p.PS;
@@ -482,9 +500,9 @@ int launch_conv_f64(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, co
 
 int launch_conv_onehot(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
                        const int32_t* rec_idx, int64_t c_first, int64_t c_step, int64_t K_loc, double* Vout,
-                       int64_t ld_out, int64_t* launches) {
+                       int64_t ld_out, bool zero_fill, int64_t* launches) {
     if (K_loc <= 0) return NNVB_OK;
-    NNVB_CUDA(cudaMemsetAsync(Vout, 0, sizeof(double) * ld_out * K_loc, st));
+    if (zero_fill) NNVB_CUDA(cudaMemsetAsync(Vout, 0, sizeof(double) * ld_out * K_loc, st));
     conv_onehot_kernel<<<(unsigned)K_loc, 128, 0, st>>>(g, w.w, w.bn_tile, w.cs, w.n_chunks, bn, rec_idx, c_first,
                                                        c_step, Vout, ld_out);
     NNVB_CUDA(cudaGetLastError());

@@ -48,7 +48,8 @@ __global__ void bn_f64_kernel(ChanAffine bn, int64_t plane, int64_t N, double* _
 // row-major order of the window, divided by ph*pw (zero padding counted).
 // One thread per output element of a column; grid.y walks the columns.
 // Rows that the preceding ReLU step cleared are read as zero through `mask` (they were not zeroed in memory).
-__global__ void avgpool_f64_kernel(PoolGeom g, RowMask mask, const double* __restrict__ Vin, int64_t ld_in,
+__global__ void avgpool_f64_kernel(PoolGeom g, RowMask mask, const int4* __restrict__ box,
+                                   const double* __restrict__ Vin, int64_t ld_in,
                                    double* __restrict__ Vout, int64_t ld_out, int64_t ncols) {
     const int64_t o = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     const int64_t n_out = int64_t(g.Ho) * g.Wo * g.C;
@@ -64,13 +65,17 @@ __global__ void avgpool_f64_kernel(PoolGeom g, RowMask mask, const double* __res
         const double* src = Vin + j * ld_in + cbase;
         const uint8_t* st = (mask.state != nullptr && j < mask.ncols) ? mask.state + mask.col_q[j] * mask.N + cbase
                                                                       : nullptr;
+        // entries outside the column's window count as zero whatever the memory holds there
+        const int4 bx = box != nullptr ? box[j]
+                                       : make_int4(NNVB_DENSE_ORIGIN, NNVB_DENSE_ORIGIN, NNVB_DENSE_EXTENT, NNVB_DENSE_EXTENT);
         double acc = 0.0;
         for (int a = 0; a < g.ph; ++a) {
             const int h = h0 + a;
             for (int b = 0; b < g.pw; ++b) {
                 const int w = w0 + b;
                 double v = 0.0;
-                if (h >= 0 && h < g.H && w >= 0 && w < g.W) {
+                if (h >= 0 && h < g.H && w >= 0 && w < g.W && unsigned(h - bx.x) < unsigned(bx.z) &&
+                    unsigned(w - bx.y) < unsigned(bx.w)) {
                     const int64_t o_in = h + int64_t(g.H) * w;
                     if (st == nullptr || st[o_in] == 0) v = src[o_in];
                 }
@@ -82,25 +87,31 @@ __global__ void avgpool_f64_kernel(PoolGeom g, RowMask mask, const double* __res
 }
 
 // Average pooling of one-hot columns (unit vector of neuron (h,w,c)): 1/(ph*pw) at every output
-// position whose window covers (h,w); the output block is zero filled beforehand.  One thread per column.
+// position of channel c whose window covers (h,w).  Every entry of the column's output window (all
+// channels; origin and extent as update_windows_kernel derives them from a 1x1 input window) is written,
+// zeros included; nothing outside it is touched.  One thread per (column, window entry).
 __global__ void avgpool_onehot_kernel(PoolGeom g, const int32_t* __restrict__ rec_idx, int64_t c_first,
                                       int64_t c_step, int64_t K_loc, double* __restrict__ Vout, int64_t ld_out) {
-    const int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (t >= K_loc) return;
+    const int wh = (g.ph - 1) / g.sh + 1, ww = (g.pw - 1) / g.sw + 1;
+    const int per_col = wh * ww * g.C;
+    const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= K_loc * per_col) return;
+    const int64_t t = e / per_col;
+    int r = int(e % per_col);
+    const int cc = r % g.C;            // channel fastest: the writes of a column spread over its channel planes
+    r /= g.C;
+    const int ohl = r % wh, owl = r / wh;
     const int i = rec_idx[c_first + t * c_step];
     const int h = i % g.H, w = (i / g.H) % g.W, c = i / (g.H * g.W);
+    const int ah = h + g.pad_t - (g.ph - 1), aw = w + g.pad_l - (g.pw - 1);
+    const int oh = (ah >= 0 ? (ah + g.sh - 1) / g.sh : -((-ah) / g.sh)) + ohl;
+    const int ow = (aw >= 0 ? (aw + g.sw - 1) / g.sw : -((-aw) / g.sw)) + owl;
+    if (oh < 0 || ow < 0 || oh >= g.Ho || ow >= g.Wo) return;
+    const int h0 = oh * g.sh - g.pad_t, w0 = ow * g.sw - g.pad_l;
+    const bool covers = cc == c && h >= h0 && h < h0 + g.ph && w >= w0 && w < w0 + g.pw;
     // same arithmetic as the dense kernel on this column: a sum of zeros and a single one, then the division
-    const double val = (0.0 + 1.0) / double(g.ph * g.pw);
-    double* dst = Vout + t * ld_out + int64_t(c) * g.Ho * g.Wo;
-    for (int a = 0; a < g.ph; ++a) {
-        const int hn = h + g.pad_t - a;
-        if (hn < 0 || hn % g.sh != 0 || hn / g.sh >= g.Ho) continue;
-        for (int b = 0; b < g.pw; ++b) {
-            const int wn = w + g.pad_l - b;
-            if (wn < 0 || wn % g.sw != 0 || wn / g.sw >= g.Wo) continue;
-            dst[hn / g.sh + int64_t(g.Ho) * (wn / g.sw)] = val;
-        }
-    }
+    const double val = covers ? (0.0 + 1.0) / double(g.ph * g.pw) : 0.0;
+    Vout[t * ld_out + oh + int64_t(g.Ho) * (ow + int64_t(g.Wo) * cc)] = val;
 }
 
 // Number of generators of ImageStar(lb,ub): entries with ub != lb (Box.m:36-43).
@@ -232,7 +243,8 @@ __global__ void avgpool_windowed_kernel(PoolGeom g, RowMask mask, ColWindows win
         for (int bb = 0; bb < g.pw; ++bb) {
             const int w = w0 + bb;
             double v = 0.0;
-            if (h >= 0 && h < g.H && w >= 0 && w < g.W) {
+            if (h >= 0 && h < g.H && w >= 0 && w < g.W && unsigned(h - bx.x) < unsigned(bx.z) &&
+                unsigned(w - bx.y) < unsigned(bx.w)) {
                 const int64_t o_in = h + int64_t(g.H) * w;
                 if (st == nullptr || st[o_in] == 0) v = src[o_in];
             }
@@ -249,6 +261,32 @@ int launch_avgpool_windowed(cudaStream_t st, const PoolGeom& g, const RowMask& m
     const int64_t total = ncols * win.wh * win.ww * g.C;
     avgpool_windowed_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(g, mask, win, col_base, ncols, Vin, ld_in,
                                                                            Vout, ld_out);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+// Zero outside the windows: thread per pair of rows, blockIdx.y strides over the columns.
+__global__ void zero_outside_windows_kernel(int H, int W, int C, const int4* __restrict__ box, int64_t col0, int64_t n,
+                                            double* __restrict__ V, int64_t ld) {
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t N = int64_t(H) * W * C;
+    if (i >= N) return;
+    const int o = int(i % (int64_t(H) * W));
+    const int h = o % H, w = o / H;
+    for (int64_t j = blockIdx.y; j < n; j += gridDim.y) {
+        const int4 bx = box[col0 + j];
+        const bool inside = unsigned(h - bx.x) < unsigned(bx.z) && unsigned(w - bx.y) < unsigned(bx.w);
+        if (!inside) V[(col0 + j) * ld + i] = 0.0;
+    }
+}
+
+int launch_zero_outside_windows(cudaStream_t st, int H, int W, int C, const int4* box, int64_t col0, int64_t n,
+                                double* V, int64_t ld, int64_t* launches) {
+    if (n <= 0) return NNVB_OK;
+    const int64_t N = int64_t(H) * W * C;
+    dim3 grid((unsigned)ceil_div(N, 256), (unsigned)std::min<int64_t>(n, 16384));
+    zero_outside_windows_kernel<<<grid, 256, 0, st>>>(H, W, C, box, col0, n, V, ld);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;
@@ -283,23 +321,25 @@ int launch_bn_f64(cudaStream_t st, const ChanAffine& bn, int64_t plane, int64_t 
 }
 
 int launch_avgpool_onehot(cudaStream_t st, const PoolGeom& g, const int32_t* rec_idx, int64_t c_first,
-                          int64_t c_step, int64_t K_loc, double* Vout, int64_t ld_out, int64_t* launches) {
+                          int64_t c_step, int64_t K_loc, double* Vout, int64_t ld_out, bool zero_fill,
+                          int64_t* launches) {
     if (K_loc <= 0) return NNVB_OK;
-    NNVB_CUDA(cudaMemsetAsync(Vout, 0, sizeof(double) * ld_out * K_loc, st));
-    avgpool_onehot_kernel<<<(unsigned)ceil_div(K_loc, 128), 128, 0, st>>>(g, rec_idx, c_first, c_step, K_loc, Vout,
-                                                                         ld_out);
+    if (zero_fill) NNVB_CUDA(cudaMemsetAsync(Vout, 0, sizeof(double) * ld_out * K_loc, st));
+    const int64_t per_col = int64_t((g.ph - 1) / g.sh + 1) * ((g.pw - 1) / g.sw + 1) * g.C;
+    avgpool_onehot_kernel<<<(unsigned)ceil_div(K_loc * per_col, 256), 256, 0, st>>>(g, rec_idx, c_first, c_step, K_loc,
+                                                                                   Vout, ld_out);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;
 }
 
-int launch_avgpool_f64(cudaStream_t st, const PoolGeom& g, const RowMask& mask, const double* Vin, int64_t ld_in,
-                       double* Vout, int64_t ld_out, int64_t ncols, int64_t* launches) {
+int launch_avgpool_f64(cudaStream_t st, const PoolGeom& g, const RowMask& mask, const int4* box, const double* Vin,
+                       int64_t ld_in, double* Vout, int64_t ld_out, int64_t ncols, int64_t* launches) {
     if (ncols <= 0) return NNVB_OK;
     const int threads = 256;
     const int64_t n_out = int64_t(g.Ho) * g.Wo * g.C;
     dim3 grid((unsigned)ceil_div(n_out, threads), (unsigned)std::min<int64_t>(ncols, 65535));
-    avgpool_f64_kernel<<<grid, threads, 0, st>>>(g, mask, Vin, ld_in, Vout, ld_out, ncols);
+    avgpool_f64_kernel<<<grid, threads, 0, st>>>(g, mask, box, Vin, ld_in, Vout, ld_out, ncols);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;

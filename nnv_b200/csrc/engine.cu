@@ -209,7 +209,9 @@ struct nnvb_batch {
     // Column cohorts: runs of columns born together (centres, input generators, the columns of each
     // ReLU layer).  A windowed cohort's columns are exactly zero outside a wh x ww window whose origin
     // is kept per column (win_h0 / win_w0); convolutions then compute only the patch that can be non-zero.
-    struct Cohort { int64_t col0, col1; bool dense; int wh, ww; };
+    // clean: the memory outside the columns' windows is known to hold zeros (false after a windowed launch
+    // that wrote the windows only; readers then go by the windows, see ensure_clean)
+    struct Cohort { int64_t col0, col1; bool dense; int wh, ww; bool clean = true; };
     std::vector<Cohort> cohorts;
     // work a ReLU step left to the layer that follows it (see relu_step)
     int64_t pend_mask_ncols = 0;         // > 0: rows with state != 0 of columns [0, n) read as zero
@@ -917,6 +919,23 @@ int make_writable(nnvb_batch* b, int64_t extra_cols) {
 
 // lazy_mask: do not clear the dead/crossing rows in memory; the next layer reads them as zero.
 // lazy_onehot: do not materialise the appended unit-vector columns; the next layer writes their images.
+// Windowed launches write the columns' windows only.  A reader that does not go by the windows first has
+// the rest of those columns cleared.
+int ensure_clean(nnvb_batch* b, nnvb_batch::Cohort& co) {
+    if (co.clean) return NNVB_OK;
+    nnvb_ctx* ctx = b->net->ctx;
+    NNVB_TRY(launch_zero_outside_windows(ctx->stream, int(b->shape[0]), int(b->shape[1]), int(b->shape[2]),
+                                         b->wk->box.as<int4>(), co.col0, co.col1 - co.col0, b->V, b->ld, &ctx->launches));
+    co.clean = true;
+    return NNVB_OK;
+}
+
+// windowed launches skip the zero fill of their output columns unless the caller wants the constraint rows
+bool lazy_fill(const nnvb_batch* b) {
+    static const bool always_fill = getenv("NNVB_ZERO_FILL") != nullptr;
+    return !always_fill && !b->opts.keep_constraints;
+}
+
 int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_onehot) {
     nnvb_ctx* ctx = b->net->ctx;
     cudaStream_t st = ctx->stream;
@@ -930,6 +949,10 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
     const int64_t want_chunks = std::max<int64_t>(1, ceil_div(148 * 16, row_blocks));
     int64_t CH = std::max<int64_t>(32, ceil_div(total_P, want_chunks));
     CH = std::min<int64_t>(CH, 1024);
+    // the classify kernel adds a query's chunk partials one after the other: at most 96 chunks per query
+    int64_t max_P = 0;
+    for (int q = 0; q < nq; ++q) max_P = std::max(max_P, b->h_qcol_off[q + 1] - b->h_qcol_off[q]);
+    CH = std::max(CH, ceil_div(max_P, int64_t(96)));
     std::vector<int64_t> cbeg, cend;
     std::vector<int32_t> qoff(nq + 1);
     for (int q = 0; q < nq; ++q) {
@@ -973,6 +996,10 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
     for (auto& co : b->cohorts)
         skip_useful = skip_useful || 2 * int64_t(co.wh) * co.ww <= b->shape[0] * b->shape[1];
     w.box = (no_skip || !skip_useful) ? nullptr : b->wk->box.as<int4>();
+    // only the window-pruned reduction of wide sets tests every entry against its window; the constraint
+    // rows kept for the caller are gathered without such tests as well
+    if (w.box == nullptr || N < 256 || b->opts.keep_constraints)
+        for (auto& co : b->cohorts) NNVB_TRY(ensure_clean(b, co));
     w.n_list = b->h_qcol_off[nq];
     NNVB_TRY(b->wk->gbox.ensure(sizeof(int4) * size_t(w.n_list / 16 + 2), st));
     w.gbox = b->wk->gbox.as<int4>();
@@ -989,8 +1016,14 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
 
     {
         // Star.estimateRanges: V read once, predicate bounds, lb/ub written
-        ProfScope ps(ctx, NNVB_PROF_RANGES,
-                     8.0 * double(N) * double(b->ncols) + 16.0 * double(b->ncols - nq) + 16.0 * double(N) * nq);
+        // bytes: the columns' windows (all of a dense column) read once, predicate bounds, lb/ub written
+        double v_bytes = 0.0;
+        for (auto& co : b->cohorts) {
+            const double px = w.box != nullptr ? std::min(double(co.wh) * co.ww, double(b->shape[0] * b->shape[1]))
+                                               : double(b->shape[0] * b->shape[1]);
+            v_bytes += 8.0 * px * double(b->shape[2]) * double(co.col1 - co.col0);
+        }
+        ProfScope ps(ctx, NNVB_PROF_RANGES, v_bytes + 16.0 * double(b->ncols - nq) + 16.0 * double(N) * nq);
         NNVB_TRY(launch_estimate_ranges(st, w, &ctx->launches));
         if (ctx->world > 1) {
             // sharded generators: every rank holds part of each sum; add them over the ranks, then
@@ -1110,6 +1143,7 @@ int run_layers(nnvb_batch* b) {
             const size_t need = size_t(ld_out) * b->ncols * sizeof(double);
             if (need > ctx->vbuf_bytes()) return capacity_error("layer output", need, ctx->vbuf_bytes());
             double* out = other_vbuf(b);
+            const bool lazy = lazy_fill(b);
             // columns the layer contracts densely, and the unit-vector columns whose images it writes directly
             const int64_t n_dense = b->ncols - b->pend_onehot;
             const int64_t n_hot = b->pend_onehot;
@@ -1133,21 +1167,25 @@ int run_layers(nnvb_batch* b) {
                     const int ww = (co.ww - 1 + (L.cg.kw - 1) * L.cg.dw) / L.cg.sw + 1;
                     const bool windowed = !co.dense && wh * ww <= 128 && 2 * wh * ww <= L.cg.Ho * L.cg.Wo;
                     if (windowed) {
-                        NNVB_CUDA(cudaMemsetAsync(out + co.col0 * ld_out, 0, sizeof(double) * ld_out * (c1 - co.col0), st));
+                        if (!lazy) NNVB_CUDA(cudaMemsetAsync(out + co.col0 * ld_out, 0, sizeof(double) * ld_out * (c1 - co.col0), st));
                         ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * wh * ww * double(c1 - co.col0));
                         ColWindows win{b->wk->box.as<int4>(), wh, ww};
                         NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, mask, win, co.col0, b->V, b->ld, out, ld_out,
                                                  c1 - co.col0, b->nq, &ctx->launches));
+                        co.clean = !lazy;
                     } else {
                         ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * L.cg.Ho * L.cg.Wo * double(c1 - co.col0));
-                        ColWindows win{nullptr, 0, 0};
+                        ColWindows win{b->wk->box.as<int4>(), 0, 0};     // whole images; the windows mask the reads
                         NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, mask, win, co.col0, b->V, b->ld, out, ld_out,
                                                  c1 - co.col0, b->nq, &ctx->launches));
+                        co.clean = true;
                     }
                 }
-                ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(Nout) * double(n_hot));
+                ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(lazy ? L.cg.kh * L.cg.kw * L.cg.Cout : Nout) * double(n_hot));
                 NNVB_TRY(launch_conv_onehot(st, L.cg, L.cw, bn, hot_idx, ctx->rank, ctx->world, n_hot,
-                                            out + n_dense * ld_out, ld_out, &ctx->launches));
+                                            out + n_dense * ld_out, ld_out, !lazy, &ctx->launches));
+                for (auto& co : b->cohorts)
+                    if (co.col0 >= n_dense) co.clean = !lazy;
             } else if (L.type == NNVB_LAYER_FC) {
                 // one launch per cohort: windowed cohorts contract only the weight rows of their windows
                 static const bool no_fcg = getenv("NNVB_NO_FC_GATHER") != nullptr;
@@ -1164,7 +1202,15 @@ int run_layers(nnvb_batch* b) {
                         NNVB_TRY(launch_fc_gather(st, int(L.H), int(L.W), int(L.C), co.wh, co.ww, int(L.Co), L.fc_wt, L.fc_ldw,
                                                   b->wk->box.as<int4>(), co.col0, n, b->V, b->ld, out, ld_out,
                                                   b->wk->fcg.as<int32_t>(), &ctx->launches));
+                    } else if (co.col1 <= b->nq && n <= 32 && In >= 1024) {
+                        // a few centre columns: slice the contraction over the grid instead of two fat tiles
+                        ProfScope ps(ctx, NNVB_PROF_FC, 2.0 * double(L.Co) * double(In) * double(n));
+                        NNVB_TRY(b->wk->tmp.ensure(sizeof(double) * fc_skinny_scratch_doubles(In, int(L.Co), int(n)), st));
+                        NNVB_TRY(launch_fc_skinny(st, In, int(L.Co), L.fc_wt, L.fc_ldw, L.bias, b->V + co.col0 * b->ld, b->ld,
+                                                  out + co.col0 * ld_out, ld_out, int(n), b->wk->tmp.as<double>(),
+                                                  &ctx->launches));
                     } else {
+                        NNVB_TRY(ensure_clean(b, co));
                         ProfScope ps(ctx, NNVB_PROF_FC, 2.0 * double(L.Co) * double(In) * double(n));
                         NNVB_TRY(launch_fc_f64(st, In, int(L.Co), L.fc_wt, L.fc_ldw, L.bias, b->V + co.col0 * b->ld, b->ld,
                                                out + co.col0 * ld_out, ld_out, n, std::max<int64_t>(0, b->nq - co.col0),
@@ -1182,13 +1228,15 @@ int run_layers(nnvb_batch* b) {
                     const int ww = (co.ww - 1 + L.pg.pw - 1) / L.pg.sw + 1;
                     const bool windowed = !co.dense && wh * ww <= 128 && 2 * wh * ww <= L.pg.Ho * L.pg.Wo;
                     if (windowed) {
-                        NNVB_CUDA(cudaMemsetAsync(out + co.col0 * ld_out, 0, sizeof(double) * ld_out * (c1 - co.col0), st));
-                        // bytes: the input windows read, the whole output column written (zero fill + patch)
+                        if (!lazy) NNVB_CUDA(cudaMemsetAsync(out + co.col0 * ld_out, 0, sizeof(double) * ld_out * (c1 - co.col0), st));
+                        // bytes: the input windows read, the output windows (with a zero fill: columns) written
                         ProfScope ps(ctx, NNVB_PROF_AVGPOOL,
-                                     8.0 * (double(co.wh) * co.ww * L.pg.C + double(Nout)) * double(c1 - co.col0));
+                                     8.0 * (double(co.wh) * co.ww * L.pg.C + (lazy ? double(wh) * ww * L.pg.C : double(Nout))) *
+                                         double(c1 - co.col0));
                         ColWindows win{b->wk->box.as<int4>(), wh, ww};
                         NNVB_TRY(launch_avgpool_windowed(st, L.pg, mask, win, co.col0, b->V, b->ld, out, ld_out,
                                                          c1 - co.col0, &ctx->launches));
+                        co.clean = !lazy;
                     } else {
                         ProfScope ps(ctx, NNVB_PROF_AVGPOOL, 8.0 * double(b->N + Nout) * double(c1 - co.col0));
                         // the kernel numbers columns from 0: shift the mask to the cohort's first column
@@ -1197,17 +1245,20 @@ int run_layers(nnvb_batch* b) {
                             m2.col_q += co.col0;
                             m2.ncols = std::max<int64_t>(0, mask.ncols - co.col0);
                         }
-                        NNVB_TRY(launch_avgpool_f64(st, L.pg, m2, b->V + co.col0 * b->ld, b->ld, out + co.col0 * ld_out,
-                                                    ld_out, c1 - co.col0, &ctx->launches));
+                        NNVB_TRY(launch_avgpool_f64(st, L.pg, m2, b->wk->box.as<int4>() + co.col0, b->V + co.col0 * b->ld, b->ld,
+                                                    out + co.col0 * ld_out, ld_out, c1 - co.col0, &ctx->launches));
+                        co.clean = true;
                     }
                 }
-                ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(Nout) * double(n_hot));
+                ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(lazy ? L.pg.C : Nout) * double(n_hot));
                 NNVB_TRY(launch_avgpool_onehot(st, L.pg, hot_idx, ctx->rank, ctx->world, n_hot, out + n_dense * ld_out,
-                                               ld_out, &ctx->launches));
+                                               ld_out, !lazy, &ctx->launches));
+                for (auto& co : b->cohorts)
+                    if (co.col0 >= n_dense) co.clean = !lazy;
             }
             // windows of the output tensor
             if (L.type == NNVB_LAYER_FC) {
-                for (auto& co : b->cohorts) { co.dense = true; co.wh = co.ww = 1 << 20; }
+                for (auto& co : b->cohorts) { co.dense = true; co.clean = true; co.wh = co.ww = 1 << 20; }
                 NNVB_TRY(launch_fill_dense_windows(st, b->ncols, b->wk->box.as<int4>(), &ctx->launches));
             } else {
                 const bool cv = L.type == NNVB_LAYER_CONV2D;
@@ -1254,6 +1305,8 @@ int run_layers(nnvb_batch* b) {
         }
         b->shape[0] = L.Ho; b->shape[1] = L.Wo; b->shape[2] = L.Co;
     }
+    // the readers of the final set (downloads, output ranges, halfspace rows) take whole columns
+    for (auto& co : b->cohorts) NNVB_TRY(ensure_clean(b, co));
     return NNVB_OK;
 }
 
@@ -1354,7 +1407,7 @@ int witness_forward(nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, i
                                        n, n, &ctx->launches));
             std::swap(cur, oth); N = Nout; ld = ld_out;
         } else if (L.type == NNVB_LAYER_AVGPOOL2D) {
-            NNVB_TRY(launch_avgpool_f64(st, L.pg, RowMask{nullptr, nullptr, 0, 0}, cur, ld, oth, ld_out, n, &ctx->launches));
+            NNVB_TRY(launch_avgpool_f64(st, L.pg, RowMask{nullptr, nullptr, 0, 0}, nullptr, cur, ld, oth, ld_out, n, &ctx->launches));
             std::swap(cur, oth); N = Nout; ld = ld_out;
         } else if (L.type == NNVB_LAYER_BN) {
             if (!L.fused_into_prev) {
@@ -1388,7 +1441,7 @@ int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vec
     NNVB_TRY(b->wk->hs_G.ensure(sizeof(double) * n * Nout, st));
     NNVB_TRY(b->wk->hs_g.ensure(sizeof(double) * n, st));
     NNVB_TRY(b->wk->hs_q.ensure(sizeof(int32_t) * n, st));
-    NNVB_TRY(b->wk->hs_margin.ensure(sizeof(double) * n, st));
+    NNVB_TRY(b->wk->hs_margin.ensure(sizeof(double) * n * (1 + HS_SPLIT), st));
     NNVB_CUDA(cudaMemcpyAsync(b->wk->hs_G.p, G.data(), sizeof(double) * n * Nout, cudaMemcpyHostToDevice, st));
     NNVB_CUDA(cudaMemcpyAsync(b->wk->hs_g.p, g.data(), sizeof(double) * n, cudaMemcpyHostToDevice, st));
     NNVB_CUDA(cudaMemcpyAsync(b->wk->hs_q.p, pair_q.data(), sizeof(int32_t) * n, cudaMemcpyHostToDevice, st));
@@ -1398,7 +1451,7 @@ int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vec
     NNVB_TRY(launch_halfspace_pairs(st, n, b->wk->hs_q.as<int32_t>(), Nout, b->ld, b->V, qoff, qidx, b->wk->pl.as<double>(),
                                     b->wk->pu.as<double>(), b->wk->hs_G.as<double>(), b->wk->hs_g.as<double>(),
                                     b->wk->hs_margin.as<double>(), nullptr, nullptr, b->wk->col_pos.as<int64_t>(),
-                                    add_center, &ctx->launches));
+                                    add_center, b->wk->hs_margin.as<double>() + n, &ctx->launches));
     NNVB_TRY(allreduce(ctx, b->wk->hs_margin.as<double>(), n));
     NNVB_CUDA(cudaMemcpyAsync(margin.data(), b->wk->hs_margin.p, sizeof(double) * n, cudaMemcpyDeviceToHost, st));
     NNVB_TRY(sync(ctx));
@@ -1441,7 +1494,7 @@ int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vec
         NNVB_TRY(launch_halfspace_pairs(st, m, b->wk->hs_q.as<int32_t>(), Nout, b->ld, b->V, qoff, qidx, b->wk->pl.as<double>(),
                                         b->wk->pu.as<double>(), b->wk->hs_G.as<double>(), b->wk->hs_g.as<double>(), nullptr,
                                         b->wk->hs_r.as<double>(), b->wk->hs_roff.as<int64_t>(),
-                                        b->wk->col_pos.as<int64_t>(), add_center, &ctx->launches));
+                                        b->wk->col_pos.as<int64_t>(), add_center, nullptr, &ctx->launches));
         // every rank needs the coefficients of all predicates: each one wrote its own columns' entries
         NNVB_TRY(allreduce(ctx, b->wk->hs_r.as<double>(), roff[m]));
         if (b->kind == 1) {

@@ -79,7 +79,8 @@ range_partial_rows2_kernel(int64_t N, int64_t ld, const double* __restrict__ V,
     if (two) { plo[i + 1] = lo1; phi[i + 1] = hi1; }
 }
 
-// The same partial sums with window skipping.  A column is exactly zero outside its window box[col], so it
+// The same partial sums with window skipping.  A column is exactly zero outside its window box[col] (the
+// memory there need not be: entries outside the window are replaced by zero), so it
 // adds nothing to the rows of a warp whose 64 rows (one channel, pixel columns wA..wB) lie outside it;
 // skipping it leaves the sums unchanged (the skipped terms are products with zero).  The test is uniform
 // over the warp.  Four candidate columns at a time: their index and window loads are in flight together,
@@ -99,6 +100,10 @@ range_partial_skip_kernel(int64_t N, int64_t ld, const double* __restrict__ V,
     const int64_t wr0 = (int64_t(blockIdx.y) * blockDim.x + (threadIdx.x & ~31)) * 2;
     const int64_t wr1 = wr0 + 63 < N ? wr0 + 63 : N - 1;
     const int64_t hw = int64_t(img_h) * img_w;
+    // pixel of this thread's rows i and i+1: memory outside a column's window may hold stale data, so an
+    // entry counts only when its pixel lies inside the window (it is zero otherwise)
+    const int px0 = int(i % hw), px1 = int((i + 1) % hw);
+    const int h0 = px0 % img_h, w0 = px0 / img_h, h1 = px1 % img_h, w1 = px1 / img_h;
     // rows of the warp: one channel plane, pixel columns wA..wB (rows hA..hB when it is a single column);
     // a warp that straddles two planes tests nothing away
     int wA = 0, wB = 1 << 29, hA = 0, hB = 1 << 29;
@@ -138,6 +143,10 @@ range_partial_skip_kernel(int64_t N, int64_t ld, const double* __restrict__ V,
                            : make_double2(V[cand[u] * ld + i], 0.0);
                 a[u] = pl[cand[u]];
                 b[u] = pu[cand[u]];
+                const bool in0 = unsigned(h0 - bx[u].x) < unsigned(bx[u].z) && unsigned(w0 - bx[u].y) < unsigned(bx[u].w);
+                const bool in1 = unsigned(h1 - bx[u].x) < unsigned(bx[u].z) && unsigned(w1 - bx[u].y) < unsigned(bx[u].w);
+                v[u].x = in0 ? v[u].x : 0.0;
+                v[u].y = in1 ? v[u].y : 0.0;
             }
         }
 #pragma unroll
@@ -514,14 +523,16 @@ halfspace_pairs_kernel(const int32_t* __restrict__ pair_q, int64_t Nout, int64_t
                        const double* __restrict__ V, const int64_t* __restrict__ qcol_off,
                        const int32_t* __restrict__ qcol_idx, const double* __restrict__ pl,
                        const double* __restrict__ pu, const double* __restrict__ G,
-                       const double* __restrict__ g, double* __restrict__ margin,
                        double* __restrict__ r_out, const int64_t* __restrict__ r_off,
-                       const int64_t* __restrict__ col_pos, int add_center) {
+                       const int64_t* __restrict__ col_pos, double* __restrict__ part) {
     const int p = blockIdx.x;
     const int q = pair_q[p];
     const double* Gr = G + int64_t(p) * Nout;
     double acc = 0.0;
-    const int64_t o0 = qcol_off[q], o1 = qcol_off[q + 1];
+    // blockIdx.y takes one contiguous slice of the query's column list
+    const int64_t q0 = qcol_off[q], q1 = qcol_off[q + 1];
+    const int64_t per = (q1 - q0 + gridDim.y - 1) / gridDim.y;
+    const int64_t o0 = q0 + per * blockIdx.y, o1 = min(q1, o0 + per);
     for (int64_t pos = o0 + threadIdx.x; pos < o1; pos += blockDim.x) {
         const int64_t col = qcol_idx[pos];
         const double* v = V + col * ld;
@@ -537,15 +548,26 @@ halfspace_pairs_kernel(const int32_t* __restrict__ pair_q, int64_t Nout, int64_t
         if (threadIdx.x < o) s[threadIdx.x] += s[threadIdx.x + o];
         __syncthreads();
     }
-    if (threadIdx.x == 0 && margin) {
-        double r = 0.0;
-        if (add_center) {                      // with sharded generators only one rank adds the centre term
-            const double* v = V + int64_t(q) * ld;
-            for (int64_t o = 0; o < Nout; ++o) r = fma(Gr[o], v[o], r);
-            r -= g[p];
-        }
-        margin[p] = r + s[0];
+    if (threadIdx.x == 0 && part) part[int64_t(p) * gridDim.y + blockIdx.y] = s[0];
+}
+
+// margin[p] = (centre term) + the slices' partial minima, added in slice order.
+__global__ void halfspace_margin_kernel(int n_pairs, int n_split, const int32_t* __restrict__ pair_q, int64_t Nout,
+                                        int64_t ld, const double* __restrict__ V, const double* __restrict__ G,
+                                        const double* __restrict__ g, const double* __restrict__ part,
+                                        double* __restrict__ margin, int add_center) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= n_pairs) return;
+    double r = 0.0;
+    if (add_center) {                          // with sharded generators only one rank adds the centre term
+        const double* Gr = G + int64_t(p) * Nout;
+        const double* v = V + int64_t(pair_q[p]) * ld;
+        for (int64_t o = 0; o < Nout; ++o) r = fma(Gr[o], v[o], r);
+        r -= g[p];
     }
+    double sum = 0.0;
+    for (int s = 0; s < n_split; ++s) sum += part[int64_t(p) * n_split + s];
+    margin[p] = r + sum;
 }
 
 // ---------------------------------------------------------------------------
@@ -775,12 +797,24 @@ int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, in
 int launch_halfspace_pairs(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t Nout, int64_t ld,
                            const double* V, const int64_t* qcol_off, const int32_t* qcol_idx, const double* pl,
                            const double* pu, const double* G, const double* g, double* margin, double* r_out,
-                           const int64_t* r_off, const int64_t* col_pos, int add_center, int64_t* launches) {
+                           const int64_t* r_off, const int64_t* col_pos, int add_center, double* part,
+                           int64_t* launches) {
     if (n_pairs <= 0) return NNVB_OK;
-    halfspace_pairs_kernel<<<n_pairs, 256, 0, st>>>(pair_q, Nout, ld, V, qcol_off, qcol_idx, pl, pu, G, g, margin,
-                                                    r_out, r_off, col_pos, add_center);
+    if (margin != nullptr && part == nullptr) {
+        set_error("halfspace_pairs: margins need the partial-sum scratch");
+        return NNVB_E_ARG;
+    }
+    dim3 grid((unsigned)n_pairs, HS_SPLIT);
+    halfspace_pairs_kernel<<<grid, 256, 0, st>>>(pair_q, Nout, ld, V, qcol_off, qcol_idx, pl, pu, G, r_out, r_off,
+                                                 col_pos, margin ? part : nullptr);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
+    if (margin) {
+        halfspace_margin_kernel<<<(n_pairs + 127) / 128, 128, 0, st>>>(n_pairs, HS_SPLIT, pair_q, Nout, ld, V, G, g, part,
+                                                                       margin, add_center);
+        NNVB_CUDA(cudaGetLastError());
+        if (launches) *launches += 1;
+    }
     return NNVB_OK;
 }
 
