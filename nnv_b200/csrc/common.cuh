@@ -157,6 +157,22 @@ int launch_avgpool_onehot(cudaStream_t st, const PoolGeom& g, const int32_t* rec
                           int64_t* launches);
 
 // ReLU approx-star step; see relu_star.cu.  All pointers are device pointers.
+// A cohort of windowed columns [col0, col0+n): every column is zero outside a wh x ww window.  The bound
+// reduction sorts them by window origin into KH x KW bins per query (KH = H + wh - 1: every origin whose
+// window meets the image) and then visits, for each pixel, only the columns whose window covers it.
+struct WinCohort {
+    int64_t col0, n;
+    int wh, ww, KH, KW;
+    int64_t bin_base;          // offset of its [nq][KH*KW + 1] table in the bin arrays
+};
+constexpr int MAX_WIN_COHORTS = 16;
+constexpr int MAX_WIN_EXTENT = 32;       // largest window side handled this way
+struct WinCohorts {
+    int n;
+    WinCohort c[MAX_WIN_COHORTS];
+};
+size_t range_windows_scratch_ints(const WinCohorts& wc, int nq, int64_t ncols);
+
 struct ReluWork {
     int nq;
     int64_t N, ld;
@@ -165,10 +181,13 @@ struct ReluWork {
     const int32_t* qcol_idx;   // predicate-ordered generator columns of each query
     const double* pl;          // [ncols] predicate bounds by column
     const double* pu;
-    const int4* box;           // [ncols] window of each column (nullptr: read every column everywhere)
-    int4* gbox;                // scratch, one int4 per 16 entries of qcol_idx (joint windows)
-    int64_t n_list;            // entries of qcol_idx over all queries
-    int img_h, img_w;          // image height / width of the current tensor (rows are h-fastest)
+    const int4* box;           // [ncols] window of each column
+    const int32_t* col_q;      // [ncols] query of each column
+    int img_h, img_w, img_c;   // shape of the current tensor (rows are h-fastest, then w, then c)
+    // cohorts whose columns are reduced through their windows (their columns are in no chunk)
+    WinCohorts win;
+    int32_t* win_scratch;      // range_windows_scratch_ints() int32
+    const int32_t* win_seg;    // [win.n][nq] first column of query q in windowed cohort k
     // chunk list for the bound reduction
     int n_chunks;
     const int64_t* chunk_beg;  // [n_chunks] positions in qcol_idx

@@ -211,7 +211,8 @@ struct nnvb_batch {
     // is kept per column (win_h0 / win_w0); convolutions then compute only the patch that can be non-zero.
     // clean: the memory outside the columns' windows is known to hold zeros (false after a windowed launch
     // that wrote the windows only; readers then go by the windows, see ensure_clean)
-    struct Cohort { int64_t col0, col1; bool dense; int wh, ww; bool clean = true; };
+    // qn: columns per query (they are stored query by query; empty for the centres)
+    struct Cohort { int64_t col0, col1; bool dense; int wh, ww; bool clean = true; std::vector<int64_t> qn; };
     std::vector<Cohort> cohorts;
     // work a ReLU step left to the layer that follows it (see relu_step)
     int64_t pend_mask_ncols = 0;         // > 0: rows with state != 0 of columns [0, n) read as zero
@@ -890,10 +891,11 @@ int init_sets(nnvb_batch* b) {
     static const bool no_windows = getenv("NNVB_NO_WINDOWS") != nullptr;
     b->cohorts.clear();
     const int BIG = 1 << 20;      // window size of columns that are dense from the start
-    b->cohorts.push_back({0, nq, true, BIG, BIG});
+    b->cohorts.push_back({0, nq, true, BIG, BIG, true, {}});
     if (ncols > nq) {
         const bool dense0 = b->kind != 1;
-        b->cohorts.push_back({nq, ncols, dense0 || no_windows, dense0 ? BIG : 1, dense0 ? BIG : 1});
+        b->cohorts.push_back({nq, ncols, dense0 || no_windows, dense0 ? BIG : 1, dense0 ? BIG : 1, true,
+                              std::vector<int64_t>(b->P0_loc.begin(), b->P0_loc.end())});
     }
     return NNVB_OK;
 }
@@ -943,24 +945,72 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
     const int64_t N = b->N, ld = b->ld;
     NNVB_TRY(make_writable(b, 0));
 
-    // chunk list: split every query's column list so that the grid fills the GPU
+    // Cohorts reduced through their windows: narrow windows on a wide set (see range_windows_kernel).
+    static const bool no_skip = getenv("NNVB_NO_RANGE_SKIP") != nullptr;
+    const int64_t img_h = b->shape[0], img_w = b->shape[1], img_c = b->shape[2];
+    WinCohorts wc{};
+    std::vector<char> is_win(b->cohorts.size(), 0);
+    std::vector<int32_t> win_seg;
+    {
+        int64_t bin_base = 0;
+        for (size_t k = 0; k < b->cohorts.size(); ++k) {
+            auto& co = b->cohorts[k];
+            const bool ok = !no_skip && !co.qn.empty() && N >= 256 && img_h * img_w * img_c == N && img_c <= 1024 &&
+                            co.wh <= MAX_WIN_EXTENT && co.ww <= MAX_WIN_EXTENT &&
+                            2 * int64_t(co.wh) * co.ww <= img_h * img_w && wc.n < MAX_WIN_COHORTS &&
+                            !b->opts.keep_constraints && co.col1 > co.col0;
+            if (!ok) continue;
+            is_win[k] = 1;
+            WinCohort& d = wc.c[wc.n++];
+            d.col0 = co.col0; d.n = co.col1 - co.col0;
+            d.wh = co.wh; d.ww = co.ww;
+            d.KH = int(img_h) + co.wh - 1; d.KW = int(img_w) + co.ww - 1;
+            d.bin_base = bin_base;
+            bin_base += int64_t(nq) * (int64_t(d.KH) * d.KW + 1);
+            int64_t c = co.col0;
+            for (int q = 0; q < nq; ++q) { win_seg.push_back(int32_t(c)); c += co.qn[q]; }
+        }
+    }
+    // every other cohort is read as whole columns
+    for (size_t k = 0; k < b->cohorts.size(); ++k)
+        if (!is_win[k]) NNVB_TRY(ensure_clean(b, b->cohorts[k]));
+
+    // chunk list: split the rest of every query's column list so that the grid fills the GPU; the windowed
+    // cohorts of a query share one more chunk, its last
     const int64_t row_blocks = N >= 256 ? ceil_div(ceil_div(N, 2), 256) : ceil_div(N, 32);
-    const int64_t total_P = b->h_qcol_off[nq];
+    int64_t total_P = 0, max_P = 0;
+    for (int q = 0; q < nq; ++q) {
+        int64_t pq = 0;
+        for (size_t k = 0; k < b->cohorts.size(); ++k)
+            if (!is_win[k] && !b->cohorts[k].qn.empty()) pq += b->cohorts[k].qn[q];
+        total_P += pq;
+        max_P = std::max(max_P, pq);
+    }
     const int64_t want_chunks = std::max<int64_t>(1, ceil_div(148 * 16, row_blocks));
     int64_t CH = std::max<int64_t>(32, ceil_div(total_P, want_chunks));
     CH = std::min<int64_t>(CH, 1024);
     // the classify kernel adds a query's chunk partials one after the other: at most 96 chunks per query
-    int64_t max_P = 0;
-    for (int q = 0; q < nq; ++q) max_P = std::max(max_P, b->h_qcol_off[q + 1] - b->h_qcol_off[q]);
     CH = std::max(CH, ceil_div(max_P, int64_t(96)));
     std::vector<int64_t> cbeg, cend;
     std::vector<int32_t> qoff(nq + 1);
     for (int q = 0; q < nq; ++q) {
         qoff[q] = (int32_t)cbeg.size();
-        for (int64_t p0 = b->h_qcol_off[q]; p0 < b->h_qcol_off[q + 1]; p0 += CH) {
-            cbeg.push_back(p0);
-            cend.push_back(std::min(p0 + CH, b->h_qcol_off[q + 1]));
+        int64_t pos = b->h_qcol_off[q];          // the list of a query holds its cohorts one after the other
+        for (size_t k = 0; k < b->cohorts.size(); ++k) {
+            if (b->cohorts[k].qn.empty()) continue;
+            const int64_t pend = pos + b->cohorts[k].qn[q];
+            if (!is_win[k])
+                for (int64_t p0 = pos; p0 < pend; p0 += CH) {
+                    cbeg.push_back(p0);
+                    cend.push_back(std::min(p0 + CH, pend));
+                }
+            pos = pend;
         }
+        if (pos != b->h_qcol_off[q + 1]) {
+            set_error("internal: cohort sizes of query %d do not add up to its column list", q);
+            return NNVB_E_STATE;
+        }
+        if (wc.n > 0) { cbeg.push_back(0); cend.push_back(0); }
     }
     qoff[nq] = (int32_t)cbeg.size();
     const int n_chunks = (int)cbeg.size();
@@ -991,19 +1041,18 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
     w.qcol_off = b->wk->qcol_off[b->list_cur].as<int64_t>();
     w.qcol_idx = b->wk->qcol_idx[b->list_cur].as<int32_t>();
     w.pl = b->wk->pl.as<double>(); w.pu = b->wk->pu.as<double>();
-    static const bool no_skip = getenv("NNVB_NO_RANGE_SKIP") != nullptr;
-    bool skip_useful = false;     // some cohort's windows cover at most half of the image
-    for (auto& co : b->cohorts)
-        skip_useful = skip_useful || 2 * int64_t(co.wh) * co.ww <= b->shape[0] * b->shape[1];
-    w.box = (no_skip || !skip_useful) ? nullptr : b->wk->box.as<int4>();
-    // only the window-pruned reduction of wide sets tests every entry against its window; the constraint
-    // rows kept for the caller are gathered without such tests as well
-    if (w.box == nullptr || N < 256 || b->opts.keep_constraints)
-        for (auto& co : b->cohorts) NNVB_TRY(ensure_clean(b, co));
-    w.n_list = b->h_qcol_off[nq];
-    NNVB_TRY(b->wk->gbox.ensure(sizeof(int4) * size_t(w.n_list / 16 + 2), st));
-    w.gbox = b->wk->gbox.as<int4>();
-    w.img_h = int(b->shape[0]); w.img_w = int(b->shape[1]);
+    w.box = b->wk->box.as<int4>();
+    w.col_q = b->wk->col_q.as<int32_t>();
+    w.img_h = int(img_h); w.img_w = int(img_w); w.img_c = int(img_c);
+    w.win = wc;
+    if (wc.n > 0) {
+        const size_t ints = range_windows_scratch_ints(wc, nq, b->ncols);
+        NNVB_TRY(b->wk->gbox.ensure(sizeof(int32_t) * (ints + win_seg.size()), st));
+        w.win_scratch = b->wk->gbox.as<int32_t>();
+        int32_t* seg_dev = w.win_scratch + ints;
+        NNVB_TRY(h2d_small(ctx, seg_dev, win_seg.data(), sizeof(int32_t) * win_seg.size()));
+        w.win_seg = seg_dev;
+    }
     w.n_chunks = n_chunks;
     w.chunk_beg = b->wk->chunk_beg.as<int64_t>(); w.chunk_end = b->wk->chunk_end.as<int64_t>();
     w.q_chunk_off = b->wk->q_chunk_off.as<int32_t>();
@@ -1019,9 +1068,9 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
         // bytes: the columns' windows (all of a dense column) read once, predicate bounds, lb/ub written
         double v_bytes = 0.0;
         for (auto& co : b->cohorts) {
-            const double px = w.box != nullptr ? std::min(double(co.wh) * co.ww, double(b->shape[0] * b->shape[1]))
-                                               : double(b->shape[0] * b->shape[1]);
-            v_bytes += 8.0 * px * double(b->shape[2]) * double(co.col1 - co.col0);
+            const size_t k = size_t(&co - b->cohorts.data());
+            const double px = is_win[k] ? double(co.wh) * co.ww : double(img_h * img_w);
+            v_bytes += 8.0 * px * double(img_c) * double(co.col1 - co.col0);
         }
         ProfScope ps(ctx, NNVB_PROF_RANGES, v_bytes + 16.0 * double(b->ncols - nq) + 16.0 * double(N) * nq);
         NNVB_TRY(launch_estimate_ranges(st, w, &ctx->launches));
@@ -1126,7 +1175,12 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
     b->pend_onehot = lazy_onehot ? K_loc : 0;
     b->pend_rec = rec;
     static const bool no_windows = getenv("NNVB_NO_WINDOWS") != nullptr;
-    if (K_loc > 0) b->cohorts.push_back({ncols_old, ncols_old + K_loc, no_windows, 1, 1});
+    if (K_loc > 0) {
+        std::vector<int64_t> qn(nq);
+        for (int q = 0; q < nq; ++q)
+            qn[q] = shard_count(rec->new_off[q + 1], rank, world) - shard_count(rec->new_off[q], rank, world);
+        b->cohorts.push_back({ncols_old, ncols_old + K_loc, no_windows, 1, 1, true, std::move(qn)});
+    }
     return NNVB_OK;
 }
 

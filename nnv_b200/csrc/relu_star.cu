@@ -79,108 +79,227 @@ range_partial_rows2_kernel(int64_t N, int64_t ld, const double* __restrict__ V,
     if (two) { plo[i + 1] = lo1; phi[i + 1] = hi1; }
 }
 
-// The same partial sums with window skipping.  A column is exactly zero outside its window box[col] (the
-// memory there need not be: entries outside the window are replaced by zero), so it
-// adds nothing to the rows of a warp whose 64 rows (one channel, pixel columns wA..wB) lie outside it;
-// skipping it leaves the sums unchanged (the skipped terms are products with zero).  The test is uniform
-// over the warp.  Four candidate columns at a time: their index and window loads are in flight together,
-// then the loads of those that hit; the sums are still formed in column order.
-__global__ void __launch_bounds__(256, 3)
-range_partial_skip_kernel(int64_t N, int64_t ld, const double* __restrict__ V,
-                          const int32_t* __restrict__ qcol_idx, const double* __restrict__ pl,
-                          const double* __restrict__ pu, const int64_t* __restrict__ chunk_beg,
-                          const int64_t* __restrict__ chunk_end, double* __restrict__ partial,
-                          const int4* __restrict__ box, const int4* __restrict__ gbox, int img_h, int img_w) {
-    const int chunk = blockIdx.x;
-    const int64_t i = (int64_t(blockIdx.y) * blockDim.x + threadIdx.x) * 2;
-    if (i >= N) return;
-    const bool two = i + 1 < N;
-    const int64_t beg = chunk_beg[chunk], end = chunk_end[chunk];
-    double lo0 = 0.0, hi0 = 0.0, lo1 = 0.0, hi1 = 0.0;
-    const int64_t wr0 = (int64_t(blockIdx.y) * blockDim.x + (threadIdx.x & ~31)) * 2;
-    const int64_t wr1 = wr0 + 63 < N ? wr0 + 63 : N - 1;
-    const int64_t hw = int64_t(img_h) * img_w;
-    // pixel of this thread's rows i and i+1: memory outside a column's window may hold stale data, so an
-    // entry counts only when its pixel lies inside the window (it is zero otherwise)
-    const int px0 = int(i % hw), px1 = int((i + 1) % hw);
-    const int h0 = px0 % img_h, w0 = px0 / img_h, h1 = px1 % img_h, w1 = px1 / img_h;
-    // rows of the warp: one channel plane, pixel columns wA..wB (rows hA..hB when it is a single column);
-    // a warp that straddles two planes tests nothing away
-    int wA = 0, wB = 1 << 29, hA = 0, hB = 1 << 29;
-    if (wr0 / hw == wr1 / hw) {
-        const int o0 = int(wr0 % hw), o1 = int(wr1 % hw);
-        wA = o0 / img_h;
-        wB = o1 / img_h;
-        hA = wA == wB ? o0 - wA * img_h : 0;
-        hB = wA == wB ? o1 - wB * img_h : img_h - 1;
-    } else {
-        wA = -(1 << 29);
-        hA = -(1 << 29);
-    }
-    // Columns are listed in the order of the pixels / neurons they come from, so 16 consecutive list
-    // entries lie close together: their joint bounding box gbox[g] = {w_lo, w_hi, h_lo, h_hi} (exclusive
-    // ends) prunes most of the list with one test per group.
-    for (int64_t grp = beg / 16; grp * 16 < end; ++grp) {
-      const int4 gb = gbox[grp];
-      if (gb.x > wB || gb.y <= wA || gb.z > hB || gb.w <= hA) continue;
-      const int64_t gp0 = grp * 16 > beg ? grp * 16 : beg;
-      const int64_t gp1 = grp * 16 + 16 < end ? grp * 16 + 16 : end;
-      for (int64_t pos = gp0; pos < gp1; pos += 4) {
-        int64_t cand[4];
-        int4 bx[4];
-        bool hit[4];
-        double2 v[4];
-        double a[4], b[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) cand[u] = pos + u < gp1 ? int64_t(qcol_idx[pos + u]) : int64_t(-1);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) bx[u] = cand[u] >= 0 ? box[cand[u]] : make_int4(0, 0, 0, 0);
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            hit[u] = cand[u] >= 0 && !(bx[u].y > wB || bx[u].y + bx[u].w <= wA || bx[u].x > hB || bx[u].x + bx[u].z <= hA);
-            if (hit[u]) {
-                v[u] = two ? __ldcs(reinterpret_cast<const double2*>(V + cand[u] * ld + i))
-                           : make_double2(V[cand[u] * ld + i], 0.0);
-                a[u] = pl[cand[u]];
-                b[u] = pu[cand[u]];
-                const bool in0 = unsigned(h0 - bx[u].x) < unsigned(bx[u].z) && unsigned(w0 - bx[u].y) < unsigned(bx[u].w);
-                const bool in1 = unsigned(h1 - bx[u].x) < unsigned(bx[u].z) && unsigned(w1 - bx[u].y) < unsigned(bx[u].w);
-                v[u].x = in0 ? v[u].x : 0.0;
-                v[u].y = in1 ? v[u].y : 0.0;
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            if (hit[u]) {
-                // max(v,0)*pl + min(v,0)*pu == v * (v > 0 ? pl : pu): one product per bound
-                const bool s0 = v[u].x > 0.0, s1 = v[u].y > 0.0;
-                lo0 = fma(v[u].x, s0 ? a[u] : b[u], lo0);
-                hi0 = fma(v[u].x, s0 ? b[u] : a[u], hi0);
-                lo1 = fma(v[u].y, s1 ? a[u] : b[u], lo1);
-                hi1 = fma(v[u].y, s1 ? b[u] : a[u], hi1);
-            }
-        }
-      }
-    }
-    double* plo = partial + int64_t(chunk) * 2 * N;
-    double* phi = plo + N;
-    plo[i] = lo0;
-    phi[i] = hi0;
-    if (two) { plo[i + 1] = lo1; phi[i + 1] = hi1; }
+// ---------------------------------------------------------------------------
+// Windowed columns.  A column of a windowed cohort is exactly zero outside its window box[col] (the memory
+// there may hold stale data), so it adds to the bounds of the pixels inside that window only.  The columns
+// of each (query, cohort) are sorted by window origin; a block then takes a strip of TH pixels of one pixel
+// column (all channels) and visits the columns whose origin lies in the ww x (TH + wh - 1) bins that can
+// cover the strip: a few contiguous runs of the sorted order.  The sums are formed in that order (cohort,
+// origin column, origin row, column index), which does not depend on the schedule.
+//
+// 1. count the columns of every (cohort, query, origin bin)
+__global__ void win_hist_kernel(WinCohorts wc, int nq, const int4* __restrict__ box, const int32_t* __restrict__ col_q,
+                                int32_t* __restrict__ bins) {
+    const WinCohort co = wc.c[blockIdx.y];
+    const int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= co.n) return;
+    const int64_t col = co.col0 + t;
+    const int4 bx = box[col];
+    const int bh = bx.x + co.wh - 1, bw = bx.y + co.ww - 1;
+    if (bh < 0 || bw < 0 || bh >= co.KH || bw >= co.KW) return;        // window off the image: an all-zero column
+    atomicAdd(bins + co.bin_base + int64_t(col_q[col]) * (co.KH * co.KW + 1) + bh + co.KH * bw, 1);
 }
 
-// Joint bounding box {w_lo, w_hi, h_lo, h_hi} (exclusive ends) of every 16 consecutive list entries.
-__global__ void group_boxes_kernel(int64_t n_list, const int32_t* __restrict__ qcol_idx, const int4* __restrict__ box,
-                                   int4* __restrict__ gbox) {
-    const int64_t g = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (g * 16 >= n_list) return;
-    int wl = 1 << 30, wh = -(1 << 30), hl = 1 << 30, hh = -(1 << 30);
-    for (int64_t p = g * 16; p < g * 16 + 16 && p < n_list; ++p) {
-        const int4 b = box[qcol_idx[p]];
-        wl = min(wl, b.y); wh = max(wh, b.y + b.w);
-        hl = min(hl, b.x); hh = max(hh, b.x + b.z);
+// 2. exclusive scan of each (cohort, query) table in place; entry KH*KW receives the total
+__global__ void __launch_bounds__(256) win_scan_kernel(WinCohorts wc, int32_t* __restrict__ bins) {
+    const WinCohort co = wc.c[blockIdx.y];
+    const int nb = co.KH * co.KW + 1;
+    int32_t* b = bins + co.bin_base + int64_t(blockIdx.x) * nb;
+    __shared__ int warp_tot[8];
+    __shared__ int carry;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int base = 0; base < nb; base += 256) {
+        const int i = base + threadIdx.x;
+        const int v = i < nb ? b[i] : 0;
+        int inc = v;
+        for (int o = 1; o < 32; o <<= 1) {
+            const int n = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= o) inc += n;
+        }
+        if (lane == 31) warp_tot[warp] = inc;
+        __syncthreads();
+        int before = carry;
+        for (int w2 = 0; w2 < warp; ++w2) before += warp_tot[w2];
+        if (i < nb) b[i] = before + inc - v;
+        __syncthreads();
+        if (threadIdx.x == 255) carry = before + inc;
+        __syncthreads();
     }
-    gbox[g] = make_int4(wl, wh, hl, hh);
+}
+
+// 3. scatter the columns into their bins (any order within a bin) ...
+__global__ void win_scatter_kernel(WinCohorts wc, int nq, const int4* __restrict__ box, const int32_t* __restrict__ col_q,
+                                   const int32_t* __restrict__ bins, int32_t* __restrict__ cursor,
+                                   const int32_t* __restrict__ seg, int32_t* __restrict__ tmp) {
+    const WinCohort co = wc.c[blockIdx.y];
+    const int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= co.n) return;
+    const int64_t col = co.col0 + t;
+    const int4 bx = box[col];
+    const int bh = bx.x + co.wh - 1, bw = bx.y + co.ww - 1;
+    if (bh < 0 || bw < 0 || bh >= co.KH || bw >= co.KW) return;
+    const int q = col_q[col];
+    const int64_t e = co.bin_base + int64_t(q) * (co.KH * co.KW + 1) + bh + co.KH * bw;
+    const int slot = bins[e] + atomicAdd(cursor + e, 1);
+    tmp[seg[blockIdx.y * nq + q] + slot] = int32_t(col);
+}
+
+// 4. ... and order every bin by column index: an entry's place is the number of smaller entries in its bin
+__global__ void win_rank_kernel(WinCohorts wc, int nq, const int4* __restrict__ box, const int32_t* __restrict__ col_q,
+                                const int32_t* __restrict__ bins, const int32_t* __restrict__ seg,
+                                const int32_t* __restrict__ tmp, int32_t* __restrict__ perm) {
+    const WinCohort co = wc.c[blockIdx.y];
+    const int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= co.n) return;
+    const int64_t col = co.col0 + t;
+    const int4 bx = box[col];
+    const int bh = bx.x + co.wh - 1, bw = bx.y + co.ww - 1;
+    if (bh < 0 || bw < 0 || bh >= co.KH || bw >= co.KW) return;
+    const int q = col_q[col];
+    const int64_t e = co.bin_base + int64_t(q) * (co.KH * co.KW + 1) + bh + co.KH * bw;
+    const int s0 = seg[blockIdx.y * nq + q];
+    const int b0 = bins[e], b1 = bins[e + 1];
+    int rank = 0;
+    for (int i = b0; i < b1; ++i) rank += tmp[s0 + i] < int32_t(col) ? 1 : 0;
+    perm[s0 + b0 + rank] = int32_t(col);
+}
+
+// 5. the partial sums of the windowed cohorts: one chunk (the last) per query.
+//    grid = (strips, nq); a thread owns RPT rows (pixel of the strip, channel), pixel fastest.
+constexpr int RW_THREADS = 256;
+constexpr int RW_RPT = 4;
+constexpr int RW_MAX_RUNS = MAX_WIN_COHORTS * MAX_WIN_EXTENT;
+__global__ void __launch_bounds__(RW_THREADS)
+range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const double* __restrict__ pl,
+                     const double* __restrict__ pu, const int4* __restrict__ box, int H, int W, int C, int TH, int nq,
+                     WinCohorts wc, const int32_t* __restrict__ bins, const int32_t* __restrict__ perm,
+                     const int32_t* __restrict__ seg, const int32_t* __restrict__ q_chunk_off,
+                     double* __restrict__ partial) {
+    const int q = blockIdx.y;
+    const int n_th = (H + TH - 1) / TH;
+    const int w = blockIdx.x / n_th;
+    const int hT = (blockIdx.x % n_th) * TH;
+
+    __shared__ int run_src[RW_MAX_RUNS];      // first sorted entry of the run (index into perm)
+    __shared__ int run_pre[RW_MAX_RUNS + 1];  // candidates before the run
+    __shared__ int run_wh[RW_MAX_RUNS];
+    __shared__ int n_runs_s;
+    __shared__ int s_col[RW_THREADS], s_h0[RW_THREADS], s_wh[RW_THREADS];
+    __shared__ double s_pl[RW_THREADS], s_pu[RW_THREADS];
+
+    // runs: for every cohort and every origin column bw that can cover pixel column w, the bins of the
+    // origin rows that can cover some pixel of the strip.  Slot k*MAX_WIN_EXTENT + d holds origin column
+    // w + d of cohort k; the non-empty slots are then packed in slot order.
+    for (int slot = threadIdx.x; slot < wc.n * MAX_WIN_EXTENT; slot += RW_THREADS) {
+        const int k = slot / MAX_WIN_EXTENT, d = slot % MAX_WIN_EXTENT;
+        const WinCohort& co = wc.c[k];
+        int src = 0, len = 0;
+        const int bw = w + d;
+        if (d < co.ww && bw < co.KW) {
+            const int32_t* b = bins + co.bin_base + int64_t(q) * (co.KH * co.KW + 1) + co.KH * bw;
+            const int bh_hi = min(hT + TH - 1 + co.wh - 1, co.KH - 1);
+            const int s0 = b[hT], s1 = b[bh_hi + 1];            // origin rows hT - wh + 1 .. hT + TH - 1
+            src = seg[k * nq + q] + s0;
+            len = s1 - s0;
+        }
+        run_src[slot] = src;
+        run_wh[slot] = len;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int r = 0, total = 0;
+        for (int k = 0; k < wc.n; ++k) {
+            const int ww = wc.c[k].ww, wh = wc.c[k].wh;
+            for (int d = 0; d < ww; ++d) {
+                const int slot = k * MAX_WIN_EXTENT + d;
+                const int src = run_src[slot], len = run_wh[slot];
+                if (len <= 0) continue;
+                // r <= slot: packing in place never overwrites an unread slot
+                run_src[r] = src;
+                run_pre[r] = total;
+                run_wh[r] = wh;
+                total += len;
+                ++r;
+            }
+        }
+        run_pre[r] = total;
+        n_runs_s = r;
+    }
+    __syncthreads();
+    const int n_runs = n_runs_s;
+    const int total = run_pre[n_runs];
+
+    // rows of this thread
+    int64_t row[RW_RPT];
+    int hh[RW_RPT];
+    double lo[RW_RPT], hi[RW_RPT];
+#pragma unroll
+    for (int r = 0; r < RW_RPT; ++r) {
+        const int idx = threadIdx.x + r * RW_THREADS;
+        const int pix = idx % TH, c = idx / TH;
+        hh[r] = hT + pix;
+        row[r] = (c < C && hh[r] < H) ? hh[r] + int64_t(H) * (w + int64_t(W) * c) : int64_t(-1);
+        lo[r] = 0.0;
+        hi[r] = 0.0;
+    }
+
+    for (int base = 0; base < total; base += RW_THREADS) {
+        const int i = base + threadIdx.x;
+        if (i < total) {
+            int a = 0, b2 = n_runs - 1;                 // last run with run_pre <= i
+            while (a < b2) {
+                const int m = (a + b2 + 1) >> 1;
+                if (run_pre[m] <= i) a = m; else b2 = m - 1;
+            }
+            const int col = perm[run_src[a] + (i - run_pre[a])];
+            s_col[threadIdx.x] = col;
+            s_h0[threadIdx.x] = box[col].x;
+            s_wh[threadIdx.x] = run_wh[a];
+            s_pl[threadIdx.x] = pl[col];
+            s_pu[threadIdx.x] = pu[col];
+        }
+        __syncthreads();
+        const int cnt = min(RW_THREADS, total - base);
+#pragma unroll
+        for (int r = 0; r < RW_RPT; ++r) {
+            if (row[r] < 0) continue;
+            int j = 0;
+            for (; j + 4 <= cnt; j += 4) {              // four loads in flight, added in candidate order
+                double v[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const bool in = unsigned(hh[r] - s_h0[j + u]) < unsigned(s_wh[j + u]);
+                    v[u] = in ? __ldcs(V + int64_t(s_col[j + u]) * ld + row[r]) : 0.0;
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    // max(v,0)*pl + min(v,0)*pu == v * (v > 0 ? pl : pu): one product per bound
+                    const bool pos = v[u] > 0.0;
+                    lo[r] = fma(v[u], pos ? s_pl[j + u] : s_pu[j + u], lo[r]);
+                    hi[r] = fma(v[u], pos ? s_pu[j + u] : s_pl[j + u], hi[r]);
+                }
+            }
+            for (; j < cnt; ++j) {
+                const bool in = unsigned(hh[r] - s_h0[j]) < unsigned(s_wh[j]);
+                const double v = in ? __ldcs(V + int64_t(s_col[j]) * ld + row[r]) : 0.0;
+                const bool pos = v > 0.0;
+                lo[r] = fma(v, pos ? s_pl[j] : s_pu[j], lo[r]);
+                hi[r] = fma(v, pos ? s_pu[j] : s_pl[j], hi[r]);
+            }
+        }
+        __syncthreads();
+    }
+
+    double* plo = partial + int64_t(q_chunk_off[q + 1] - 1) * 2 * N;
+    double* phi = plo + N;
+#pragma unroll
+    for (int r = 0; r < RW_RPT; ++r) {
+        if (row[r] < 0) continue;
+        plo[row[r]] = lo[r];
+        phi[row[r]] = hi[r];
+    }
 }
 
 // Narrow sets (few rows, many columns): a warp owns 32 rows, the 8 warps of a
@@ -697,20 +816,18 @@ __global__ void witness_value_kernel(int n_pairs, int64_t Nout, int64_t ld, cons
 
 }  // namespace
 
+size_t range_windows_scratch_ints(const WinCohorts& wc, int nq, int64_t ncols) {
+    size_t bins = 0;
+    for (int k = 0; k < wc.n; ++k) bins += size_t(nq) * (size_t(wc.c[k].KH) * wc.c[k].KW + 1);
+    return 2 * bins + 2 * size_t(ncols) + 16;      // bins, cursors, unsorted and sorted columns
+}
+
 int launch_estimate_ranges(cudaStream_t st, const ReluWork& w, int64_t* launches) {
     if (w.n_chunks > 0) {
         if (w.N >= 256) {
             dim3 grid((unsigned)w.n_chunks, (unsigned)ceil_div(ceil_div(w.N, 2), 256));
-            if (w.box != nullptr) {
-                group_boxes_kernel<<<(unsigned)ceil_div(ceil_div(w.n_list, 16), 128), 128, 0, st>>>(w.n_list, w.qcol_idx,
-                                                                                                   w.box, w.gbox);
-                if (launches) *launches += 1;
-                range_partial_skip_kernel<<<grid, 256, 0, st>>>(w.N, w.ld, w.V, w.qcol_idx, w.pl, w.pu, w.chunk_beg,
-                                                                w.chunk_end, w.partial, w.box, w.gbox, w.img_h, w.img_w);
-            }
-            else
-                range_partial_rows2_kernel<4><<<grid, 256, 0, st>>>(w.N, w.ld, w.V, w.qcol_idx, w.pl, w.pu,
-                                                                   w.chunk_beg, w.chunk_end, w.partial);
+            range_partial_rows2_kernel<4><<<grid, 256, 0, st>>>(w.N, w.ld, w.V, w.qcol_idx, w.pl, w.pu,
+                                                               w.chunk_beg, w.chunk_end, w.partial);
         } else {
             dim3 grid((unsigned)w.n_chunks, (unsigned)ceil_div(w.N, 32));
             range_partial_narrow_kernel<<<grid, 256, 0, st>>>(w.N, w.ld, w.V, w.qcol_idx, w.pl, w.pu,
@@ -718,6 +835,38 @@ int launch_estimate_ranges(cudaStream_t st, const ReluWork& w, int64_t* launches
         }
         NNVB_CUDA(cudaGetLastError());
         if (launches) *launches += 1;
+    }
+    if (w.win.n > 0) {
+        // the last chunk of every query (empty in the chunk list, so zero by now) takes the windowed cohorts
+        size_t n_bins = 0;
+        int64_t max_n = 0, ncols = 0;
+        for (int k = 0; k < w.win.n; ++k) {
+            n_bins += size_t(w.nq) * (size_t(w.win.c[k].KH) * w.win.c[k].KW + 1);
+            max_n = std::max(max_n, w.win.c[k].n);
+            ncols = std::max(ncols, w.win.c[k].col0 + w.win.c[k].n);
+        }
+        int32_t* bins = w.win_scratch;
+        int32_t* cursor = bins + n_bins;
+        int32_t* tmp = cursor + n_bins;
+        int32_t* perm = tmp + ncols;
+        NNVB_CUDA(cudaMemsetAsync(bins, 0, sizeof(int32_t) * 2 * n_bins, st));
+        dim3 gcol((unsigned)ceil_div(max_n, 256), (unsigned)w.win.n);
+        win_hist_kernel<<<gcol, 256, 0, st>>>(w.win, w.nq, w.box, w.col_q, bins);
+        win_scan_kernel<<<dim3((unsigned)w.nq, (unsigned)w.win.n), 256, 0, st>>>(w.win, bins);
+        win_scatter_kernel<<<gcol, 256, 0, st>>>(w.win, w.nq, w.box, w.col_q, bins, cursor, w.win_seg, tmp);
+        win_rank_kernel<<<gcol, 256, 0, st>>>(w.win, w.nq, w.box, w.col_q, bins, w.win_seg, tmp, perm);
+        // strip height: a thread per (pixel, channel) where the channels allow it
+        int TH = std::max(1, std::min(w.img_h, RW_THREADS / std::max(1, w.img_c)));
+        if (int64_t(TH) * w.img_c > int64_t(RW_THREADS) * RW_RPT) {
+            set_error("range_windows: %d channels exceed the rows a block owns", w.img_c);
+            return NNVB_E_UNSUPPORTED;
+        }
+        dim3 grid((unsigned)(ceil_div(w.img_h, TH) * w.img_w), (unsigned)w.nq);
+        range_windows_kernel<<<grid, RW_THREADS, 0, st>>>(w.N, w.ld, w.V, w.pl, w.pu, w.box, w.img_h, w.img_w, w.img_c,
+                                                          TH, w.nq, w.win, bins, perm, w.win_seg, w.q_chunk_off,
+                                                          w.partial);
+        NNVB_CUDA(cudaGetLastError());
+        if (launches) *launches += 5;
     }
     return NNVB_OK;
 }
