@@ -102,6 +102,12 @@ size_t conv_weights_doubles(const ConvGeom& g, int* bn_tile, int* cs, int* n_til
 void conv_arrange_weights(const ConvGeom& g, const double* W, double* dst, int bn_tile, int cs,
                           int n_tiles, int n_chunks);
 
+// Windowed generator columns (no centres) with the taps that read outside the wh_in x ww_in input window
+// skipped; see conv_win_f64.cu.  *done stays false, and nothing is launched, for geometries it does not
+// cover (the caller then uses launch_conv_f64).
+int launch_conv_win(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn, const RowMask& mask,
+                    const ColWindows& win, int wh_in, int ww_in, int64_t col_base, const double* Vin, int64_t ld_in,
+                    double* Vout, int64_t ld_out, int64_t ncols, bool* done, int64_t* launches);
 // Processes columns [col_base, col_base + ncols) of Vin / Vout (pointers to column 0).
 int launch_conv_f64(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
                     const RowMask& mask, const ColWindows& win, int64_t col_base, const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,

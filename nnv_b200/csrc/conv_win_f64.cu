@@ -1,0 +1,311 @@
+// Convolution of windowed columns, FP64 on the DMMA pipe (sm_100a).
+//
+// A windowed column is zero outside a small wh_in x ww_in window of the input image, so its image
+// under a unit-stride convolution is zero outside a (wh_in + kh - 1) x (ww_in + kw - 1) patch.  The
+// dense kernel (conv_f64.cu) computes such a patch with the output positions as the rows of its
+// tiles and runs every filter tap for every row, although for the rows near the patch border most
+// taps read outside the input window: about half of its products are with structural zeros.
+//
+// Here the rows of an MMA tile are 16 COLUMNS at the same patch position.  All columns of a cohort
+// share the window geometry, so whether tap (khi, kwi) of patch position (oh, ow) reads inside the
+// input window is the same for the 16 rows of a tile, and the taps that do not are skipped
+// altogether.  A block owns 16*WARPS_M columns, one patch column ow and up to 8 patch rows; warp
+// (wm, wn) owns 16 columns and 8 output channels and keeps one accumulator tile per patch row.
+// An input row fragment is loaded once and used by the (up to kh) taps that pair it with different
+// output rows.
+//
+// Conv2DLayer.reach_star_single_input (Conv2DLayer.m:1110-1137) applies the layer to the centre
+// with bias and to every generator without; this kernel is used for generator columns only.
+#include <algorithm>
+
+#include "common.cuh"
+#include "mma_f64.cuh"
+
+namespace nnvb {
+namespace {
+
+constexpr int KC = 8;               // input channels per pipeline stage, as conv_arrange_weights lays them out
+constexpr int CW_TH = 8;            // patch rows per block
+constexpr int CW_THREADS = 512;
+constexpr int CW_STAGES = 2;
+
+struct ConvWinParams {
+    ConvGeom g;
+    int wh_in, ww_in, wh_out, ww_out;
+    int n_ohb;                      // row blocks per patch
+    int ni_s;                       // input rows staged per origin column
+    int CSI;                        // stride between the channels of a staged input row (doubles)
+    int CS;                         // weight channel stride (doubles)
+    int in_stage, w_stage;          // doubles per stage
+    int n_chunks;
+    int ncol;                       // columns per block
+    int OSTR, CSTR;                 // epilogue staging strides: patch row, column (doubles)
+    int tab_cap;                    // table entries
+    int tail;                       // doubles before the constants and tables
+};
+
+template <int KH, int WARPS_M, int WARPS_N>
+__global__ void __launch_bounds__(CW_THREADS, 1)
+conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const ChanAffine bn, const RowMask mask,
+                const int4* __restrict__ box, int64_t col_base, const double* __restrict__ Vin, int64_t ld_in,
+                double* __restrict__ Vout, int64_t ld_out, int64_t ncols) {
+    static_assert(WARPS_M * WARPS_N * 32 == CW_THREADS, "16 warps");
+    constexpr int BN = WARPS_N * 8;
+    constexpr int NI = CW_TH + KH - 1;              // input rows that can meet the block's output rows
+
+    extern __shared__ __align__(16) double smem[];
+    double* in_s = smem;                                        // [STAGES][in_stage]
+    double* wts = smem + CW_STAGES * p.in_stage;                // [STAGES][w_stage]
+    double* chan = smem + p.tail;                               // [2][BN]: 1/den, scale
+    int* goff = reinterpret_cast<int*>(chan + 2 * BN);          // [tab_cap] input offset, -1 = zero
+    int* soff = goff + p.tab_cap;                               // [tab_cap] staging offset
+    int* moff = soff + p.tab_cap;                               // [tab_cap] row-state offset, -1 = none
+    int4* s_box = reinterpret_cast<int4*>(moff + p.tab_cap);    // [ncol]
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int wm = warp % WARPS_M;
+    const int wn = warp / WARPS_M;
+    const int g = lane >> 2;
+    const int t = lane & 3;
+
+    const int per = p.ww_out * p.n_ohb;
+    const int64_t cg = blockIdx.x / per;
+    const int rem = int(blockIdx.x % per);
+    const int owl = rem / p.n_ohb;
+    const int ohb = rem % p.n_ohb;
+    const int64_t j0 = cg * p.ncol;
+    const int n_tile = blockIdx.y;
+    const int n0 = n_tile * BN;
+    const int H = p.g.H, W = p.g.W;
+    const int hw_in = H * W;
+    const int KW = p.g.kw;
+    const int ext_h = KH - 1, ext_w = KW - 1;
+
+    // input rows i (relative to ih_base) that lie in the window, and the output rows of this block
+    const int ih_base = ohb * CW_TH - ext_h;
+    const int i_lo = max(0, -ih_base);
+    const int i_hi = min(NI, p.wh_in - ih_base);
+    const int n_i = i_hi - i_lo;
+    const int th_cnt = min(CW_TH, p.wh_out - ohb * CW_TH);
+    // origin columns kwi whose input column owl + kwi - ext_w lies in the window
+    const int kw_lo = max(0, ext_w - owl);
+    const int kw_hi = min(KW, p.ww_in + ext_w - owl);
+    const int n_kw = kw_hi - kw_lo;
+
+    for (int c = tid; c < p.ncol; c += CW_THREADS) {
+        int4 bx = make_int4(0, 0, 0, 0);
+        if (j0 + c < ncols) bx = box[col_base + j0 + c];
+        s_box[c] = bx;
+    }
+    const bool has_bn = bn.rden != nullptr;
+    for (int c = tid; c < BN; c += CW_THREADS) {
+        const int co = n0 + c;
+        const bool ok = co < p.g.Cout && has_bn;
+        chan[c] = ok ? bn.rden[co] : 1.0;
+        chan[BN + c] = ok ? bn.scale[co] : 1.0;
+    }
+    __syncthreads();
+
+    // table: entry e = (column, origin column, input row), input row fastest (contiguous in memory)
+    const int n_e = p.ncol * n_kw * n_i;
+    for (int e = tid; e < n_e; e += CW_THREADS) {
+        const int i_idx = e % n_i;
+        const int e2 = e / n_i;
+        const int kwi = kw_lo + e2 % n_kw;
+        const int col = e2 / n_kw;
+        const int4 bx = s_box[col];
+        const int hi = bx.x + ih_base + i_lo + i_idx;
+        const int wi = bx.y + owl + kwi - ext_w;
+        int off = -1, mo = -1;
+        if (hi >= 0 && hi < H && wi >= 0 && wi < W && j0 + col < ncols) {
+            off = int(col * ld_in) + hi + H * wi;
+            if (mask.state != nullptr && col_base + j0 + col < mask.ncols)
+                mo = int(mask.col_q[col_base + j0 + col] * mask.N) + hi + H * wi;
+        }
+        goff[e] = off;
+        moff[e] = mo;
+        soff[e] = ((kwi * p.ni_s + i_idx) * KC) * p.CSI + col;
+    }
+    __syncthreads();
+
+    const double* in_base = Vin + (col_base + j0) * ld_in;
+    const double* w_base = Wg + (int64_t(n_tile) * p.n_chunks) * p.w_stage;
+
+    auto load_stage = [&](int stage, int chunk) {
+        double* is = in_s + stage * p.in_stage;
+        // warp w fetches channel w % 8 of the chunk; the two warps of a channel split the table
+        const int cil = warp & 7;
+        const int ci = chunk * KC + cil;
+        const bool ci_ok = ci < p.g.Cin;
+        const double* src_c = in_base + int64_t(ci_ok ? ci : 0) * hw_in;
+        const uint8_t* st_c = mask.state != nullptr ? mask.state + int64_t(ci_ok ? ci : 0) * hw_in : nullptr;
+        double* dst_c = is + cil * p.CSI;
+        for (int e0 = (warp >> 3) * 32 + lane; e0 < n_e; e0 += 256) {
+            int off[4], so[4];
+            uint8_t sv[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int e = e0 + 64 * u;
+                off[u] = (e < n_e && ci_ok) ? goff[e] : -1;
+                so[u] = e < n_e ? soff[e] : -1;
+                const int mo = (e < n_e && ci_ok && st_c != nullptr) ? moff[e] : -1;
+                sv[u] = mo >= 0 ? st_c[mo] : uint8_t(0);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (so[u] < 0) continue;
+                const bool ok = off[u] >= 0 && sv[u] == 0;
+                cp_async8(dst_c + so[u], ok ? (src_c + off[u]) : Vin, ok ? 8 : 0);
+            }
+        }
+        double* ws = wts + stage * p.w_stage;
+        const double* wsrc = w_base + int64_t(chunk) * p.w_stage;
+        for (int c = tid; c < p.w_stage / 2; c += CW_THREADS) cp_async16(ws + 2 * c, wsrc + 2 * c, 16);
+    };
+
+    double acc[CW_TH][4];
+#pragma unroll
+    for (int o = 0; o < CW_TH; ++o)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) acc[o][r] = 0.0;
+
+    const int NCH = p.n_chunks;
+    load_stage(0, 0);
+    cp_async_commit();
+    for (int ch = 0; ch < NCH; ++ch) {
+        cp_async_wait<0>();
+        __syncthreads();
+        if (ch + 1 < NCH) load_stage((ch + 1) & 1, ch + 1);
+        cp_async_commit();
+        const double* is = in_s + (ch & 1) * p.in_stage + t * p.CSI + wm * 16 + g;   // row = column g, k = channel t
+        const double* ws = wts + (ch & 1) * p.w_stage + t * p.CS + wn * 8 + g;      // k = channel t, n = g
+        for (int kwi = kw_lo; kwi < kw_hi; ++kwi) {
+            double bf[KH][2];
+#pragma unroll
+            for (int khi = 0; khi < KH; ++khi) {
+                const double* wt = ws + (khi + KH * kwi) * (KC * p.CS);     // tap index: kh fastest
+                bf[khi][0] = wt[0];
+                bf[khi][1] = wt[4 * p.CS];
+            }
+            const double* a_col = is + (kwi * p.ni_s - i_lo) * (KC * p.CSI);
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                if (i < i_lo || i >= i_hi) continue;
+                const double* a = a_col + i * (KC * p.CSI);
+                double af[4];
+                af[0] = a[0];
+                af[1] = a[8];
+                af[2] = a[4 * p.CSI];
+                af[3] = a[4 * p.CSI + 8];
+                // input row i meets output row i - khi through tap khi
+#pragma unroll
+                for (int khi = 0; khi < KH; ++khi) {
+                    const int o = i - khi;
+                    if (o >= 0 && o < CW_TH) {
+                        if (o < th_cnt) dmma_16x8x8(acc[o], af, bf[khi]);
+                    }
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();        // every warp is done with the stages: they become the output staging area
+
+    // epilogue 1: accumulators -> staging [column][patch row][channel]; 16-byte stores
+    double* out_s = smem;
+    {
+        const int c_lo = wm * 16 + g;
+#pragma unroll
+        for (int o = 0; o < CW_TH; ++o) {
+            const int nn = wn * 8 + 2 * t;
+            const double r0 = chan[nn], s0 = chan[BN + nn], r1 = chan[nn + 1], s1 = chan[BN + nn + 1];
+            double2 lo2 = make_double2((acc[o][0] * r0) * s0, (acc[o][1] * r1) * s1);
+            double2 hi2 = make_double2((acc[o][2] * r0) * s0, (acc[o][3] * r1) * s1);
+            *reinterpret_cast<double2*>(out_s + c_lo * p.CSTR + o * p.OSTR + nn) = lo2;
+            *reinterpret_cast<double2*>(out_s + (c_lo + 8) * p.CSTR + o * p.OSTR + nn) = hi2;
+        }
+    }
+    __syncthreads();
+    // epilogue 2: staging -> memory; 8 lanes write the 8 patch rows of one (column, channel): 64 contiguous bytes
+    {
+        const int o = lane & 7;
+        const int sub = lane >> 3;
+        const int64_t hw_out = int64_t(p.g.Ho) * p.g.Wo;
+        const int n_pairs = p.ncol * BN;
+        for (int base = warp * 4; base < n_pairs; base += (CW_THREADS / 32) * 4) {
+            const int pair = base + sub;
+            const int col = pair / BN, n = pair % BN;
+            if (j0 + col >= ncols || n0 + n >= p.g.Cout || o >= th_cnt) continue;
+            const int4 bx = s_box[col];
+            const int oh = bx.x + p.g.pad_t - ext_h + ohb * CW_TH + o;
+            const int ow = bx.y + p.g.pad_l - ext_w + owl;
+            if (oh < 0 || oh >= p.g.Ho || ow < 0 || ow >= p.g.Wo) continue;
+            Vout[(col_base + j0 + col) * ld_out + oh + int64_t(p.g.Ho) * ow + hw_out * (n0 + n)] =
+                out_s[col * p.CSTR + o * p.OSTR + n];
+        }
+    }
+}
+
+template <int KH, int WARPS_M, int WARPS_N>
+int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn, const RowMask& mask,
+               const ColWindows& win, int wh_in, int ww_in, int64_t col_base, const double* Vin, int64_t ld_in,
+               double* Vout, int64_t ld_out, int64_t ncols, bool* done) {
+    constexpr int BN = WARPS_N * 8;
+    ConvWinParams p;
+    p.g = g;
+    p.wh_in = wh_in; p.ww_in = ww_in;
+    p.wh_out = win.wh; p.ww_out = win.ww;
+    p.n_ohb = (int)ceil_div(win.wh, CW_TH);
+    p.ni_s = std::min(wh_in, CW_TH + KH - 1);
+    p.ncol = 16 * WARPS_M;
+    p.CSI = p.ncol + 4;             // = 4 (mod 16): the four channel rows of a fragment fall on distinct banks
+    p.CS = w.cs;
+    p.in_stage = g.kw * p.ni_s * KC * p.CSI;
+    p.w_stage = g.kh * g.kw * KC * p.CS;
+    p.n_chunks = w.n_chunks;
+    p.OSTR = BN + 2;
+    p.CSTR = CW_TH * p.OSTR + 8;
+    if (p.CSTR % 16 != 8) p.CSTR += (8 - p.CSTR % 16 + 16) % 16;
+    p.tab_cap = p.ncol * g.kw * p.ni_s;
+    // the output staging area reuses the pipeline stages; the constants and tables follow the larger of the two
+    const size_t pipe = size_t(CW_STAGES) * (p.in_stage + p.w_stage) * sizeof(double);
+    const size_t stage_out = size_t(p.ncol) * p.CSTR * sizeof(double);
+    p.tail = int(std::max(pipe, stage_out) / sizeof(double));
+    const size_t smem = std::max(pipe, stage_out) + size_t(2 * BN) * sizeof(double) +
+                        size_t(3 * p.tab_cap) * sizeof(int) + size_t(p.ncol) * sizeof(int4);
+    if (smem > 227 * 1024) return NNVB_OK;
+    if (int64_t(p.ncol) * std::max(ld_in, ld_out) >= (int64_t(1) << 31)) return NNVB_OK;
+    const int64_t blocks = ceil_div(ncols, p.ncol) * p.ww_out * p.n_ohb;
+    if (blocks >= (int64_t(1) << 31)) return NNVB_OK;
+    auto kern = conv_win_kernel<KH, WARPS_M, WARPS_N>;
+    NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((unsigned)blocks, (unsigned)w.n_tiles);
+    kern<<<grid, CW_THREADS, smem, st>>>(p, w.w, bn, mask, win.box, col_base, Vin, ld_in, Vout, ld_out, ncols);
+    NNVB_CUDA(cudaGetLastError());
+    *done = true;
+    return NNVB_OK;
+}
+
+}  // namespace
+
+// Windowed convolution with tap skipping.  *done is set when the launch was made; it stays false (and
+// nothing is launched) for geometries this kernel does not cover: the caller then uses launch_conv_f64.
+int launch_conv_win(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn, const RowMask& mask,
+                    const ColWindows& win, int wh_in, int ww_in, int64_t col_base, const double* Vin, int64_t ld_in,
+                    double* Vout, int64_t ld_out, int64_t ncols, bool* done, int64_t* launches) {
+    *done = false;
+    if (ncols <= 0) { *done = true; return NNVB_OK; }
+    if (g.sh != 1 || g.sw != 1 || g.dh != 1 || g.dw != 1 || g.kh != 3 || g.kw > 7 || win.box == nullptr) return NNVB_OK;
+    if (win.wh != wh_in + g.kh - 1 || win.ww != ww_in + g.kw - 1) return NNVB_OK;
+    int rc = NNVB_OK;
+    if (w.bn_tile == 64)
+        rc = launch_cfg<3, 2, 8>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, done);
+    else if (w.bn_tile == 32)
+        rc = launch_cfg<3, 4, 4>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, done);
+    if (rc == NNVB_OK && *done && launches) *launches += 1;
+    return rc;
+}
+
+}  // namespace nnvb

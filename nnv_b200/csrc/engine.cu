@@ -254,6 +254,13 @@ struct ProfScope {
         a = get(); b = get();
         cudaEventRecord(a, ctx->stream);
     }
+    // nothing was launched after all: the scope records no work
+    void cancel() {
+        if (!a) return;
+        ctx->prof_pool.push_back(a);
+        ctx->prof_pool.push_back(b);
+        a = b = nullptr;
+    }
     ~ProfScope() {
         if (!a) return;
         cudaEventRecord(b, ctx->stream);
@@ -1222,10 +1229,22 @@ int run_layers(nnvb_batch* b) {
                     const bool windowed = !co.dense && wh * ww <= 128 && 2 * wh * ww <= L.cg.Ho * L.cg.Wo;
                     if (windowed) {
                         if (!lazy) NNVB_CUDA(cudaMemsetAsync(out + co.col0 * ld_out, 0, sizeof(double) * ld_out * (c1 - co.col0), st));
-                        ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * wh * ww * double(c1 - co.col0));
                         ColWindows win{b->wk->box.as<int4>(), wh, ww};
-                        NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, mask, win, co.col0, b->V, b->ld, out, ld_out,
-                                                 c1 - co.col0, b->nq, &ctx->launches));
+                        // generator columns: the kernel that skips the taps falling outside the input window
+                        // (its products: kh*kw per input position), else the patch-tiled kernel (per output position)
+                        static const bool no_conv_win = getenv("NNVB_NO_CONV_WIN") != nullptr;
+                        bool done = false;
+                        if (!no_conv_win && co.col0 >= b->nq) {
+                            ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * co.wh * co.ww * double(c1 - co.col0));
+                            NNVB_TRY(launch_conv_win(st, L.cg, L.cw, bn, mask, win, co.wh, co.ww, co.col0, b->V, b->ld, out,
+                                                     ld_out, c1 - co.col0, &done, &ctx->launches));
+                            if (!done) ps.cancel();
+                        }
+                        if (!done) {
+                            ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * wh * ww * double(c1 - co.col0));
+                            NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, mask, win, co.col0, b->V, b->ld, out, ld_out,
+                                                     c1 - co.col0, b->nq, &ctx->launches));
+                        }
                         co.clean = !lazy;
                     } else {
                         ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * L.cg.Ho * L.cg.Wo * double(c1 - co.col0));
