@@ -35,6 +35,8 @@ struct ConvWinParams {
     int n_ohb;                      // row blocks per patch
     int ni_s;                       // input rows staged per origin column
     int CSI;                        // stride between the channels of a staged input row (doubles)
+    int RS;                         // stride between staged input rows: 8 channels and one double, so that
+                                    // the rows a warp fetches together fall on different banks
     int CS;                         // weight channel stride (doubles)
     int in_stage, w_stage;          // doubles per stage
     int n_chunks;
@@ -126,7 +128,7 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
         }
         goff[e] = off;
         moff[e] = mo;
-        soff[e] = ((kwi * p.ni_s + i_idx) * KC) * p.CSI + col;
+        soff[e] = (kwi * p.ni_s + i_idx) * p.RS + col;
     }
     __syncthreads();
 
@@ -171,14 +173,7 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
 #pragma unroll
         for (int r = 0; r < 4; ++r) acc[o][r] = 0.0;
 
-    const int NCH = p.n_chunks;
-    load_stage(0, 0);
-    cp_async_commit();
-    for (int ch = 0; ch < NCH; ++ch) {
-        cp_async_wait<0>();
-        __syncthreads();
-        if (ch + 1 < NCH) load_stage((ch + 1) & 1, ch + 1);
-        cp_async_commit();
+    auto compute = [&](int ch) {
         const double* is = in_s + (ch & 1) * p.in_stage + t * p.CSI + wm * 16 + g;   // row = column g, k = channel t
         const double* ws = wts + (ch & 1) * p.w_stage + t * p.CS + wn * 8 + g;      // k = channel t, n = g
         for (int kwi = kw_lo; kwi < kw_hi; ++kwi) {
@@ -189,11 +184,11 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
                 bf[khi][0] = wt[0];
                 bf[khi][1] = wt[4 * p.CS];
             }
-            const double* a_col = is + (kwi * p.ni_s - i_lo) * (KC * p.CSI);
+            const double* a_col = is + (kwi * p.ni_s - i_lo) * p.RS;
 #pragma unroll
             for (int i = 0; i < NI; ++i) {
                 if (i < i_lo || i >= i_hi) continue;
-                const double* a = a_col + i * (KC * p.CSI);
+                const double* a = a_col + i * p.RS;
                 double af[4];
                 af[0] = a[0];
                 af[1] = a[8];
@@ -209,6 +204,21 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
                 }
             }
         }
+    };
+
+    const int NCH = p.n_chunks;
+    load_stage(0, 0);
+    cp_async_commit();
+    // Half of the warps fetch the next stage before their products, the other half after: while one half
+    // waits on its table and row-state loads the other keeps the DMMA pipe busy.
+    const bool load_first = (warp >> 3) == 0;
+    for (int ch = 0; ch < NCH; ++ch) {
+        cp_async_wait<0>();
+        __syncthreads();
+        if (load_first && ch + 1 < NCH) load_stage((ch + 1) & 1, ch + 1);
+        compute(ch);
+        if (!load_first && ch + 1 < NCH) load_stage((ch + 1) & 1, ch + 1);
+        cp_async_commit();
     }
     cp_async_wait<0>();
     __syncthreads();        // every warp is done with the stages: they become the output staging area
@@ -262,7 +272,8 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
     p.ncol = 16 * WARPS_M;
     p.CSI = p.ncol + 4;             // = 4 (mod 16): the four channel rows of a fragment fall on distinct banks
     p.CS = w.cs;
-    p.in_stage = g.kw * p.ni_s * KC * p.CSI;
+    p.RS = KC * p.CSI + 1;
+    p.in_stage = (g.kw * p.ni_s * p.RS + 1) / 2 * 2;        // even: the weights behind it are fetched 16 bytes at a time
     p.w_stage = g.kh * g.kw * KC * p.CS;
     p.n_chunks = w.n_chunks;
     p.OSTR = BN + 2;
