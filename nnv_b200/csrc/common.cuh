@@ -178,6 +178,7 @@ struct WinCohorts {
     WinCohort c[MAX_WIN_COHORTS];
 };
 size_t range_windows_scratch_ints(const WinCohorts& wc, int nq, int64_t ncols);
+int range_windows_slices(int H, int W, int C, int nq);
 
 struct ReluWork {
     int nq;
@@ -192,6 +193,7 @@ struct ReluWork {
     int img_h, img_w, img_c;   // shape of the current tensor (rows are h-fastest, then w, then c)
     // cohorts whose columns are reduced through their windows (their columns are in no chunk)
     WinCohorts win;
+    int win_slices;            // chunks per query the windowed cohorts fill (range_windows_slices())
     int32_t* win_scratch;      // range_windows_scratch_ints() int32
     const int32_t* win_seg;    // [win.n][nq] first column of query q in windowed cohort k
     // chunk list for the bound reduction

@@ -978,12 +978,13 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
             for (int q = 0; q < nq; ++q) { win_seg.push_back(int32_t(c)); c += co.qn[q]; }
         }
     }
+    const int win_slices = wc.n > 0 ? range_windows_slices(int(img_h), int(img_w), int(img_c), nq) : 0;
     // every other cohort is read as whole columns
     for (size_t k = 0; k < b->cohorts.size(); ++k)
         if (!is_win[k]) NNVB_TRY(ensure_clean(b, b->cohorts[k]));
 
     // chunk list: split the rest of every query's column list so that the grid fills the GPU; the windowed
-    // cohorts of a query share one more chunk, its last
+    // cohorts of a query fill a few more chunks, its last
     const int64_t row_blocks = N >= 256 ? ceil_div(ceil_div(N, 2), 256) : ceil_div(N, 32);
     int64_t total_P = 0, max_P = 0;
     for (int q = 0; q < nq; ++q) {
@@ -1017,7 +1018,7 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
             set_error("internal: cohort sizes of query %d do not add up to its column list", q);
             return NNVB_E_STATE;
         }
-        if (wc.n > 0) { cbeg.push_back(0); cend.push_back(0); }
+        for (int sl = 0; sl < win_slices; ++sl) { cbeg.push_back(0); cend.push_back(0); }
     }
     qoff[nq] = (int32_t)cbeg.size();
     const int n_chunks = (int)cbeg.size();
@@ -1052,6 +1053,7 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
     w.col_q = b->wk->col_q.as<int32_t>();
     w.img_h = int(img_h); w.img_w = int(img_w); w.img_c = int(img_c);
     w.win = wc;
+    w.win_slices = win_slices;
     if (wc.n > 0) {
         const size_t ints = range_windows_scratch_ints(wc, nq, b->ncols);
         NNVB_TRY(b->wk->gbox.ensure(sizeof(int32_t) * (ints + win_seg.size()), st));

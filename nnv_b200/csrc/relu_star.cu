@@ -177,6 +177,7 @@ range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const 
                      WinCohorts wc, const int32_t* __restrict__ bins, const int32_t* __restrict__ perm,
                      const int32_t* __restrict__ seg, const int32_t* __restrict__ q_chunk_off,
                      double* __restrict__ partial) {
+    // blockIdx.z takes one slice of the strip's candidate list and fills one of the query's last gridDim.z chunks
     const int q = blockIdx.y;
     const int n_th = (H + TH - 1) / TH;
     const int w = blockIdx.x / n_th;
@@ -230,6 +231,8 @@ range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const 
     __syncthreads();
     const int n_runs = n_runs_s;
     const int total = run_pre[n_runs];
+    const int per_slice = (total + gridDim.z - 1) / gridDim.z;
+    const int c_lo = min(total, per_slice * int(blockIdx.z)), c_hi = min(total, c_lo + per_slice);
 
     // rows of this thread
     int64_t row[RW_RPT];
@@ -245,9 +248,9 @@ range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const 
         hi[r] = 0.0;
     }
 
-    for (int base = 0; base < total; base += RW_THREADS) {
+    for (int base = c_lo; base < c_hi; base += RW_THREADS) {
         const int i = base + threadIdx.x;
-        if (i < total) {
+        if (i < c_hi) {
             int a = 0, b2 = n_runs - 1;                 // last run with run_pre <= i
             while (a < b2) {
                 const int m = (a + b2 + 1) >> 1;
@@ -261,7 +264,7 @@ range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const 
             s_pu[threadIdx.x] = pu[col];
         }
         __syncthreads();
-        const int cnt = min(RW_THREADS, total - base);
+        const int cnt = min(RW_THREADS, c_hi - base);
 #pragma unroll
         for (int r = 0; r < RW_RPT; ++r) {
             if (row[r] < 0) continue;
@@ -292,7 +295,7 @@ range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const 
         __syncthreads();
     }
 
-    double* plo = partial + int64_t(q_chunk_off[q + 1] - 1) * 2 * N;
+    double* plo = partial + int64_t(q_chunk_off[q + 1] - int(gridDim.z) + int(blockIdx.z)) * 2 * N;
     double* phi = plo + N;
 #pragma unroll
     for (int r = 0; r < RW_RPT; ++r) {
@@ -816,6 +819,13 @@ __global__ void witness_value_kernel(int n_pairs, int64_t Nout, int64_t ld, cons
 
 }  // namespace
 
+// Slices of a strip's candidate list (each its own block and chunk): enough blocks to fill the GPU.
+int range_windows_slices(int H, int W, int C, int nq) {
+    const int TH = std::max(1, std::min(H, RW_THREADS / std::max(1, C)));
+    const int64_t blocks = ceil_div(H, TH) * int64_t(W) * nq;
+    return (int)std::max<int64_t>(1, std::min<int64_t>(8, ceil_div(4 * 148, blocks)));
+}
+
 size_t range_windows_scratch_ints(const WinCohorts& wc, int nq, int64_t ncols) {
     size_t bins = 0;
     for (int k = 0; k < wc.n; ++k) bins += size_t(nq) * (size_t(wc.c[k].KH) * wc.c[k].KW + 1);
@@ -837,7 +847,7 @@ int launch_estimate_ranges(cudaStream_t st, const ReluWork& w, int64_t* launches
         if (launches) *launches += 1;
     }
     if (w.win.n > 0) {
-        // the last chunk of every query (empty in the chunk list, so zero by now) takes the windowed cohorts
+        // the last win_slices chunks of every query (empty in the chunk list) take the windowed cohorts
         size_t n_bins = 0;
         int64_t max_n = 0, ncols = 0;
         for (int k = 0; k < w.win.n; ++k) {
@@ -861,7 +871,7 @@ int launch_estimate_ranges(cudaStream_t st, const ReluWork& w, int64_t* launches
             set_error("range_windows: %d channels exceed the rows a block owns", w.img_c);
             return NNVB_E_UNSUPPORTED;
         }
-        dim3 grid((unsigned)(ceil_div(w.img_h, TH) * w.img_w), (unsigned)w.nq);
+        dim3 grid((unsigned)(ceil_div(w.img_h, TH) * w.img_w), (unsigned)w.nq, (unsigned)w.win_slices);
         range_windows_kernel<<<grid, RW_THREADS, 0, st>>>(w.N, w.ld, w.V, w.pl, w.pu, w.box, w.img_h, w.img_w, w.img_c,
                                                           TH, w.nq, w.win, bins, perm, w.win_seg, w.q_chunk_off,
                                                           w.partial);
