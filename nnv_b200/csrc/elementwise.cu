@@ -215,52 +215,57 @@ __global__ void fill_dense_windows_kernel(int64_t n, int4* __restrict__ box) {
     if (j < n) box[j] = make_int4(NNVB_DENSE_ORIGIN, NNVB_DENSE_ORIGIN, NNVB_DENSE_EXTENT, NNVB_DENSE_EXTENT);
 }
 
-// Windowed average pooling: thread per (column, channel, patch position); same window sum as the dense kernel.
+// Windowed average pooling: a thread owns one (channel, patch position) and walks over the columns
+// (blockIdx.y strided), so the index arithmetic is done once; same window sum as the dense kernel.
 __global__ void avgpool_windowed_kernel(PoolGeom g, RowMask mask, ColWindows win, int64_t col_base, int64_t ncols,
                                         const double* __restrict__ Vin, int64_t ld_in, double* __restrict__ Vout,
                                         int64_t ld_out) {
     const int per_col = win.wh * win.ww * g.C;
-    const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (e >= ncols * per_col) return;
-    const int64_t j = col_base + e / per_col;
-    int r = int(e % per_col);
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= per_col) return;
     const int ohl = r % win.wh;
-    r /= win.wh;
-    const int owl = r % win.ww;
-    const int c = r / win.ww;
-    const int4 bx = win.box[j];
-    const int a = bx.x + g.pad_t - (g.ph - 1), b2 = bx.y + g.pad_l - (g.pw - 1);
-    const int oh = (a >= 0 ? (a + g.sh - 1) / g.sh : -((-a) / g.sh)) + ohl;
-    const int ow = (b2 >= 0 ? (b2 + g.sw - 1) / g.sw : -((-b2) / g.sw)) + owl;
-    if (oh < 0 || ow < 0 || oh >= g.Ho || ow >= g.Wo) return;
+    const int r2 = r / win.wh;
+    const int owl = r2 % win.ww;
+    const int c = r2 / win.ww;
     const int64_t cbase = int64_t(c) * g.H * g.W;
-    const double* src = Vin + j * ld_in + cbase;
-    const uint8_t* st = (mask.state != nullptr && j < mask.ncols) ? mask.state + mask.col_q[j] * mask.N + cbase : nullptr;
-    const int h0 = oh * g.sh - g.pad_t, w0 = ow * g.sw - g.pad_l;
-    double acc = 0.0;
-    for (int aa = 0; aa < g.ph; ++aa) {
-        const int h = h0 + aa;
-        for (int bb = 0; bb < g.pw; ++bb) {
-            const int w = w0 + bb;
-            double v = 0.0;
-            if (h >= 0 && h < g.H && w >= 0 && w < g.W && unsigned(h - bx.x) < unsigned(bx.z) &&
-                unsigned(w - bx.y) < unsigned(bx.w)) {
-                const int64_t o_in = h + int64_t(g.H) * w;
-                if (st == nullptr || st[o_in] == 0) v = src[o_in];
+    const int64_t obase = int64_t(g.Ho) * g.Wo * c;
+    const double div = double(g.ph * g.pw);
+    for (int64_t jj = blockIdx.y; jj < ncols; jj += gridDim.y) {
+        const int64_t j = col_base + jj;
+        const int4 bx = win.box[j];
+        const int a = bx.x + g.pad_t - (g.ph - 1), b2 = bx.y + g.pad_l - (g.pw - 1);
+        const int oh = (a >= 0 ? (a + g.sh - 1) / g.sh : -((-a) / g.sh)) + ohl;
+        const int ow = (b2 >= 0 ? (b2 + g.sw - 1) / g.sw : -((-b2) / g.sw)) + owl;
+        if (oh < 0 || ow < 0 || oh >= g.Ho || ow >= g.Wo) continue;
+        const double* src = Vin + j * ld_in + cbase;
+        const uint8_t* st = (mask.state != nullptr && j < mask.ncols) ? mask.state + mask.col_q[j] * mask.N + cbase : nullptr;
+        const int h0 = oh * g.sh - g.pad_t, w0 = ow * g.sw - g.pad_l;
+        double acc = 0.0;
+        for (int aa = 0; aa < g.ph; ++aa) {
+            const int h = h0 + aa;
+            for (int bb = 0; bb < g.pw; ++bb) {
+                const int w = w0 + bb;
+                double v = 0.0;
+                if (h >= 0 && h < g.H && w >= 0 && w < g.W && unsigned(h - bx.x) < unsigned(bx.z) &&
+                    unsigned(w - bx.y) < unsigned(bx.w)) {
+                    const int64_t o_in = h + int64_t(g.H) * w;
+                    if (st == nullptr || st[o_in] == 0) v = src[o_in];
+                }
+                acc = acc + v;
             }
-            acc = acc + v;
         }
+        Vout[j * ld_out + oh + int64_t(g.Ho) * ow + obase] = acc / div;
     }
-    Vout[j * ld_out + oh + int64_t(g.Ho) * (ow + int64_t(g.Wo) * c)] = acc / double(g.ph * g.pw);
 }
 
 int launch_avgpool_windowed(cudaStream_t st, const PoolGeom& g, const RowMask& mask, const ColWindows& win,
                             int64_t col_base, const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
                             int64_t ncols, int64_t* launches) {
     if (ncols <= 0) return NNVB_OK;
-    const int64_t total = ncols * win.wh * win.ww * g.C;
-    avgpool_windowed_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(g, mask, win, col_base, ncols, Vin, ld_in,
-                                                                           Vout, ld_out);
+    const int per_col = win.wh * win.ww * g.C;
+    const int threads = per_col >= 256 ? 256 : 128;
+    dim3 grid((unsigned)ceil_div(per_col, threads), (unsigned)std::min<int64_t>(ncols, 8192));
+    avgpool_windowed_kernel<<<grid, threads, 0, st>>>(g, mask, win, col_base, ncols, Vin, ld_in, Vout, ld_out);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;

@@ -985,7 +985,7 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
 
     // chunk list: split the rest of every query's column list so that the grid fills the GPU; the windowed
     // cohorts of a query fill a few more chunks, its last
-    const int64_t row_blocks = N >= 256 ? ceil_div(ceil_div(N, 2), 256) : ceil_div(N, 32);
+    const int64_t row_blocks = N >= 2048 ? ceil_div(ceil_div(N, 2), 256) : ceil_div(N, 32);
     int64_t total_P = 0, max_P = 0;
     for (int q = 0; q < nq; ++q) {
         int64_t pq = 0;

@@ -834,7 +834,7 @@ size_t range_windows_scratch_ints(const WinCohorts& wc, int nq, int64_t ncols) {
 
 int launch_estimate_ranges(cudaStream_t st, const ReluWork& w, int64_t* launches) {
     if (w.n_chunks > 0) {
-        if (w.N >= 256) {
+        if (w.N >= 2048) {
             dim3 grid((unsigned)w.n_chunks, (unsigned)ceil_div(ceil_div(w.N, 2), 256));
             range_partial_rows2_kernel<4><<<grid, 256, 0, st>>>(w.N, w.ld, w.V, w.qcol_idx, w.pl, w.pu,
                                                                w.chunk_beg, w.chunk_end, w.partial);
