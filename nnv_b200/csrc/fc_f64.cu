@@ -19,6 +19,7 @@ namespace {
 
 constexpr int FC_BK = 16;
 constexpr int FC_STAGES = 3;
+constexpr int FCG_STAGES = 2;     // gathered FC: two stages, so that two blocks fit on an SM
 constexpr int FC_AST = FC_BK + 4;   // A row stride in shared memory (doubles)
 
 template <int WM_TILES, int WN_TILES, int WARPS_M, int WARPS_N>
@@ -323,8 +324,10 @@ __global__ void fcg_scatter_kernel(int64_t col0, int64_t n, const int4* __restri
 // short M tile keeps the tiles full; the weight rows of a tile are then re-read from L2 once per 32 columns.
 constexpr int FCG_WM = 1, FCG_WN = 8, FCG_WARPS_M = 2, FCG_WARPS_N = 4;
 constexpr int FCG_BM = FCG_WARPS_M * FCG_WM * 16;
+constexpr size_t FCG_SMEM = size_t(FCG_STAGES) * (FcCfg<FCG_WM, FCG_WN, FCG_WARPS_M, FCG_WARPS_N>::A_STAGE +
+                                                  FcCfg<FCG_WM, FCG_WN, FCG_WARPS_M, FCG_WARPS_N>::B_STAGE) * sizeof(double);
 
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(256, 2)
 fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad, int Out,
                  const double* __restrict__ Wt, int ldw, const double* __restrict__ Vin, int64_t ld_in,
                  double* __restrict__ Vout, int64_t ld_out, const int32_t* __restrict__ tile_key,
@@ -334,8 +337,8 @@ fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad
     if (int(blockIdx.x) >= *n_tiles) return;
     extern __shared__ __align__(16) double smem[];
     double* As = smem;
-    double* Bs = smem + FC_STAGES * Cfg::A_STAGE;
-    int* rows_s = reinterpret_cast<int*>(Bs + FC_STAGES * Cfg::B_STAGE);   // [Kt_pad] input row of k, -1 = none
+    double* Bs = smem + FCG_STAGES * Cfg::A_STAGE;
+    int* rows_s = reinterpret_cast<int*>(Bs + FCG_STAGES * Cfg::B_STAGE);   // [Kt_pad] input row of k, -1 = none
     int* cols_s = rows_s + Kt_pad;                                          // [BM] column of tile row m, -1 = none
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -388,20 +391,20 @@ fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad
 
     const int KT = Kt_pad / FC_BK;
 #pragma unroll
-    for (int s = 0; s < FC_STAGES - 1; ++s) {
+    for (int s = 0; s < FCG_STAGES - 1; ++s) {
         if (s < KT) load_stage(s, s);
         cp_async_commit();
     }
     for (int kt = 0; kt < KT; ++kt) {
-        cp_async_wait<FC_STAGES - 2>();
+        cp_async_wait<FCG_STAGES - 2>();
         __syncthreads();
         {
-            const int nk = kt + FC_STAGES - 1;
-            if (nk < KT) load_stage(nk % FC_STAGES, nk);
+            const int nk = kt + FCG_STAGES - 1;
+            if (nk < KT) load_stage(nk % FCG_STAGES, nk);
             cp_async_commit();
         }
-        const double* a = As + (kt % FC_STAGES) * Cfg::A_STAGE + (wm * FCG_WM * 16 + g) * FC_AST + t;
-        const double* b = Bs + (kt % FC_STAGES) * Cfg::B_STAGE + t * Cfg::BST + wn * FCG_WN * 8 + g;
+        const double* a = As + (kt % FCG_STAGES) * Cfg::A_STAGE + (wm * FCG_WM * 16 + g) * FC_AST + t;
+        const double* b = Bs + (kt % FCG_STAGES) * Cfg::B_STAGE + t * Cfg::BST + wn * FCG_WN * 8 + g;
 #pragma unroll
         for (int kk = 0; kk < FC_BK; kk += 8) {
             double af[FCG_WM][4];
@@ -480,11 +483,13 @@ int launch_fc_gather(cudaStream_t st, int H, int W, int C, int wh, int ww, int O
     fcg_scatter_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(col0, n, box, wh, ww, KH, nbins, bin_start, cursor, perm);
     const int Kt = C * wh * ww;
     const int Kt_pad = (int)round_up(Kt, FC_BK);
-    const size_t smem = Cfg::SMEM + size_t(Kt_pad + 128) * sizeof(int);
+    const size_t smem = FCG_SMEM + size_t(Kt_pad + 128) * sizeof(int);
     static bool attr_set = false;
     if (!attr_set) {
         NNVB_CUDA(cudaFuncSetAttribute(fc_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)(Cfg::SMEM + size_t(16384 + 128) * sizeof(int))));
+                                       (int)(FCG_SMEM + size_t(16384 + 128) * sizeof(int))));
+        NNVB_CUDA(cudaFuncSetAttribute(fc_gather_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                       cudaSharedmemCarveoutMaxShared));
         attr_set = true;
     }
     dim3 grid((unsigned)max_tiles, (unsigned)ceil_div(Out, Cfg::BN));

@@ -274,7 +274,7 @@ range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const 
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const bool in = unsigned(hh[r] - s_h0[j + u]) < unsigned(s_wh[j + u]);
-                    v[u] = in ? __ldcs(V + int64_t(s_col[j + u]) * ld + row[r]) : 0.0;
+                    v[u] = in ? V[int64_t(s_col[j + u]) * ld + row[r]] : 0.0;
                 }
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
@@ -286,7 +286,7 @@ range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const 
             }
             for (; j < cnt; ++j) {
                 const bool in = unsigned(hh[r] - s_h0[j]) < unsigned(s_wh[j]);
-                const double v = in ? __ldcs(V + int64_t(s_col[j]) * ld + row[r]) : 0.0;
+                const double v = in ? V[int64_t(s_col[j]) * ld + row[r]] : 0.0;
                 const bool pos = v > 0.0;
                 lo[r] = fma(v, pos ? s_pl[j] : s_pu[j], lo[r]);
                 hi[r] = fma(v, pos ? s_pu[j] : s_pl[j], hi[r]);
@@ -820,8 +820,14 @@ __global__ void witness_value_kernel(int n_pairs, int64_t Nout, int64_t ld, cons
 }  // namespace
 
 // Slices of a strip's candidate list (each its own block and chunk): enough blocks to fill the GPU.
+// Strip height: at least 8 pixels (64 contiguous bytes per channel) where the block's rows allow it.
+static int rw_strip_height(int H, int C) {
+    const int cap = std::max(1, std::min(H, RW_THREADS * RW_RPT / std::max(1, C)));
+    return std::min(cap, std::max(8, RW_THREADS / std::max(1, C)));
+}
+
 int range_windows_slices(int H, int W, int C, int nq) {
-    const int TH = std::max(1, std::min(H, RW_THREADS / std::max(1, C)));
+    const int TH = rw_strip_height(H, C);
     const int64_t blocks = ceil_div(H, TH) * int64_t(W) * nq;
     return (int)std::max<int64_t>(1, std::min<int64_t>(8, ceil_div(4 * 148, blocks)));
 }
@@ -866,7 +872,7 @@ int launch_estimate_ranges(cudaStream_t st, const ReluWork& w, int64_t* launches
         win_scatter_kernel<<<gcol, 256, 0, st>>>(w.win, w.nq, w.box, w.col_q, bins, cursor, w.win_seg, tmp);
         win_rank_kernel<<<gcol, 256, 0, st>>>(w.win, w.nq, w.box, w.col_q, bins, w.win_seg, tmp, perm);
         // strip height: a thread per (pixel, channel) where the channels allow it
-        int TH = std::max(1, std::min(w.img_h, RW_THREADS / std::max(1, w.img_c)));
+        const int TH = rw_strip_height(w.img_h, w.img_c);
         if (int64_t(TH) * w.img_c > int64_t(RW_THREADS) * RW_RPT) {
             set_error("range_windows: %d channels exceed the rows a block owns", w.img_c);
             return NNVB_E_UNSUPPORTED;
