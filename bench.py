@@ -274,8 +274,6 @@ def run_ours(args):
             best = min(best, e0.elapsed_time(e1))
         dgemm_tflops = 2.0 * n ** 3 / (best * 1e-3) / 1e12
         del a, bb
-        relu_ms = prof["ranges"]["ms"] + prof["relax"]["ms"]
-        relu_gbs = (prof["ranges"]["work"] + prof["relax"]["work"]) / (relu_ms * 1e-3) / 1e9 if relu_ms > 0 else 0.0
         peaks = {}
         try:
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -284,9 +282,16 @@ def run_ours(args):
         hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
         hbm_src = "MEASURED_PEAKS.json hbm_gbs" if peaks else "fallback 6650 GB/s"
         dgemm_src = "cuBLAS DGEMM 6144^3 measured in this run (burst, best of 6)"
-        kernels = {"conv": "conv_f64_kernel (FP64 DMMA implicit GEMM, dense and windowed launches)",
-                   "fc": "fc_f64_kernel (FP64 DMMA GEMM)", "avgpool": "avgpool_f64_kernel / avgpool_windowed_kernel",
-                   "ranges": "range_partial_rows2_kernel + range_finalize_kernel (Star.estimateRanges)"}
+        kernels = {"conv": "conv_win_kernel (windowed generator columns) + conv_f64_kernel (centres): FP64 DMMA "
+                           "implicit GEMM, useful products only",
+                   "fc": "fc_gather_kernel (windowed columns) + fc_f64_kernel / fc_skinny_kernel: FP64 DMMA GEMM",
+                   "avgpool": "avgpool_windowed_kernel / avgpool_f64_kernel (bytes of the windows)",
+                   "ranges": "range_windows_kernel + range_partial_* + range_finalize_kernel (Star.estimateRanges, "
+                             "bytes of the windows)"}
+        # DRAM bytes (read + write) of one image's convolution launches, from the ncu capture of the batch-1
+        # run summarised in profiles/conv_win_kernel_cnn32_batch1.md; the launches of a batch of B images move
+        # B times as much (every column is touched once per layer)
+        conv_dram_bytes_per_image = 578e6
 
         def roof(fam):
             f = prof[fam]
@@ -297,7 +302,8 @@ def run_ours(args):
                     "unit": "TFLOP/s" if tensor else "GB/s", "frac": ach / peak if peak else None,
                     "peak_source": dgemm_src if tensor else hbm_src, "launches": f["launches"],
                     "avg_launch_ms": f["ms"] / max(f["launches"], 1), "share_of_step": f["ms"] / dev_ms,
-                    "traffic": None}
+                    "traffic": (conv_dram_bytes_per_image * B * K / max(f["launches"], 1)) if fam == "conv" else None,
+                    "algorithmic_per_launch": f["work"] / max(f["launches"], 1)}
 
         # the roofline entry is the kernel family with the largest share of the timed region
         dominant = max(kernels, key=lambda k: prof[k]["ms"])
@@ -306,7 +312,7 @@ def run_ours(args):
             "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f64", "data": "synthetic",
             "config": {"workload": WORKLOAD, "batch_per_step": B, "distinct_batches": n_distinct,
-                       "l2": "inputs larger than L2 (generator tensors of 0.8-2.7 GB per image)",
+                       "l2": "inputs larger than L2 (the column windows one layer reads: up to 0.16 GB per image)",
                        "verdicts": {"robust": verdict_counts[1], "unknown": verdict_counts[2],
                                     "undecided_on_device": verdict_counts[-1]},
                        "columns_after_relu": [s_["cols_after"] for s_ in stats]},
@@ -316,11 +322,6 @@ def run_ours(args):
             "clocks": clocks,
             "roofline": roof(dominant),
             "roofline_other": {k: roof(k) for k in kernels if k != dominant},
-            "roofline_relu_step": {"bound": "hbm", "achieved": relu_gbs, "peak": hbm_peak, "unit": "GB/s",
-                                   "frac": relu_gbs / hbm_peak, "peak_source": hbm_src,
-                                   "note": "dense-layout algorithmic bytes of estimateRanges + relaxation over their "
-                                           "time; zero windows are skipped and row clearing is left to the next "
-                                           "layer, so this can exceed the copy rate"},
             "family_ms_per_step": {k: v["ms"] / K for k, v in prof.items()},
         }
         if world == 1 and not args.no_cpu_baseline:

@@ -120,7 +120,10 @@ int64_t nnvb_launch_count(nnvb_ctx* ctx);
  * returns, since the last enable: accumulated milliseconds, kernels launched,
  * and the algorithmic work of those launches — floating-point operations for the
  * contractions (2*Ho*Wo*Cout*kh*kw*Cin*columns, 2*Out*In*columns), bytes for
- * the bandwidth-bound families (each tensor read or written once). */
+ * the bandwidth-bound families (each tensor read or written once).  For columns
+ * that are zero outside a small window only the window counts: positions of the
+ * input window for a convolution (each meets kh*kw taps), rows of the window for
+ * an FC layer, bytes of the windows for pooling and the bound reduction. */
 #define NNVB_PROF_CONV 0      /* Conv2D implicit GEMM (+ fused BatchNormalization) */
 #define NNVB_PROF_FC 1        /* FullyConnected GEMM */
 #define NNVB_PROF_BN 2        /* stand-alone BatchNormalization */

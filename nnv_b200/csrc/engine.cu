@@ -1207,6 +1207,10 @@ int run_layers(nnvb_batch* b) {
             if (need > ctx->vbuf_bytes()) return capacity_error("layer output", need, ctx->vbuf_bytes());
             double* out = other_vbuf(b);
             const bool lazy = lazy_fill(b);
+            // test aid: fill the output buffer with NaN patterns first, so that a reader that strays outside
+            // the windows it was given shows up in the results instead of depending on what the memory held
+            static const bool poison = getenv("NNVB_POISON") != nullptr;
+            if (poison) NNVB_CUDA(cudaMemsetAsync(out, 0xFF, need, st));
             // columns the layer contracts densely, and the unit-vector columns whose images it writes directly
             const int64_t n_dense = b->ncols - b->pend_onehot;
             const int64_t n_hot = b->pend_onehot;

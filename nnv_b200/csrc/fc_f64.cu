@@ -277,10 +277,14 @@ namespace {
 // DMMA tiles as the dense kernel with gathered operands.  Values equal the dense product (the skipped
 // terms are products with zero), up to the order of the remaining additions.
 
-// key of a window origin; h0 in [-(wh-1), H-1], w0 in [-(ww-1), W-1]
+// key of a window origin; h0 in [-(wh-1), H-1], w0 in [-(ww-1), W-1].  A window that does not meet the image
+// belongs to an all-zero column (whatever its memory holds): such columns share the last bin, whose tiles
+// contract nothing and write zeros.
 __device__ __forceinline__ int fcg_key(int4 bx, int wh, int ww, int KH, int nbins) {
-    int k = (bx.x + wh - 1) + KH * (bx.y + ww - 1);
-    return k < 0 ? 0 : (k >= nbins ? nbins - 1 : k);
+    const int bh = bx.x + wh - 1, bw = bx.y + ww - 1;
+    const int KW = (nbins - 1) / KH;
+    if (bh < 0 || bh >= KH || bw < 0 || bw >= KW) return nbins - 1;
+    return bh + KH * bw;
 }
 
 __global__ void fcg_hist_kernel(int64_t col0, int64_t n, const int4* __restrict__ box, int wh, int ww, int KH,
@@ -348,11 +352,12 @@ fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad
 
     const int key = tile_key[blockIdx.x];
     const int h0 = key % KH - (wh - 1), w0 = key / KH - (ww - 1);
+    const bool null_bin = key == KH * (W + ww - 1);     // columns whose window lies off the image
     const int start = tile_start[blockIdx.x], count = tile_count[blockIdx.x];
     for (int m = tid; m < Cfg::BM; m += Cfg::THREADS) cols_s[m] = m < count ? perm[start + m] : -1;
     for (int k = tid; k < Kt_pad; k += Cfg::THREADS) {
         int row = -1;
-        if (k < Kt) {
+        if (k < Kt && !null_bin) {
             const int hl = k % wh, r2 = k / wh;
             const int wl = r2 % ww, c = r2 / ww;
             const int h = h0 + hl, w = w0 + wl;
@@ -454,7 +459,7 @@ fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad
 }  // namespace
 
 size_t fc_gather_scratch_ints(int64_t n, int H, int W, int wh, int ww) {
-    const int64_t nbins = int64_t(H + wh - 1) * (W + ww - 1);
+    const int64_t nbins = int64_t(H + wh - 1) * (W + ww - 1) + 1;
     const int64_t max_tiles = ceil_div(n, FCG_BM) + nbins;
     return size_t(3 * nbins + 3 * max_tiles + n + 8);
 }
@@ -467,7 +472,7 @@ int launch_fc_gather(cudaStream_t st, int H, int W, int C, int wh, int ww, int O
     if (n <= 0) return NNVB_OK;
     using Cfg = FcCfg<FCG_WM, FCG_WN, FCG_WARPS_M, FCG_WARPS_N>;
     const int KH = H + wh - 1;
-    const int nbins = KH * (W + ww - 1);
+    const int nbins = KH * (W + ww - 1) + 1;        // the last bin: windows off the image
     const int64_t max_tiles = ceil_div(n, FCG_BM) + nbins;
     int32_t* hist = scratch;
     int32_t* bin_start = hist + nbins;

@@ -60,6 +60,58 @@ def test_reach_parity_vs_oracle(ctx, golden, name, small, nq):
     net.close()
 
 
+@pytest.mark.parametrize("name,small,nq", CASES)
+def test_default_path_parity_vs_oracle(ctx, name, small, nq):
+    """The path a verification run takes (no constraint records): windowed layer kernels that write
+    only the columns' windows, rows cleared by masks in the next layer, implicit unit-vector columns,
+    the window-sorted bound reduction."""
+    cfg = make_config(name, n_queries=nq, small=small)
+    net = Network(ctx, cfg["layers"], cfg["in_shape"])
+    b = Batch(net, cfg["queries"])
+    b.upload()
+    b.reach(keep_layer_bounds=True)
+    for q, qu in enumerate(cfg["queries"]):
+        S = O.reach(cfg["layers"], O.star_from_query(qu))
+        V = b.get_V(q)
+        assert V.shape == S.V.shape
+        assert _rel(V, S.V) < TOL
+        lb, ub = b.get_ranges(q)
+        rl, ru = O.output_ranges(S)
+        scale = max(np.abs(rl).max(), np.abs(ru).max())
+        assert np.abs(lb - rl).max() / scale < TOL and np.abs(ub - ru).max() / scale < TOL
+        for li, t in enumerate(S.trace):
+            idx, cl, cu = b.get_crossing(q, li)
+            assert np.array_equal(idx, t["cross"])
+            bscale = max(np.abs(t["lb"]).max(), np.abs(t["ub"]).max())
+            ll, lu = b.get_layer_ranges(q, li, t["N"])
+            assert np.abs(ll - t["lb"]).max() / bscale < TOL and np.abs(lu - t["ub"]).max() / bscale < TOL
+            assert np.array_equal(np.nonzero(lu <= 0)[0], t["dead"])
+        pl, pu = b.get_pred_bounds(q)
+        assert np.array_equal(pl, S.pl) and _rel(pu, S.pu) < TOL
+    b.close()
+    net.close()
+
+
+def test_results_belong_to_the_last_reach_on_a_context(ctx):
+    from nnv_b200._lib import NNVError
+    cfg = make_config("fc5", n_queries=2)
+    net = Network(ctx, cfg["layers"], cfg["in_shape"])
+    b1 = Batch(net, cfg["queries"][:1])
+    b2 = Batch(net, cfg["queries"][1:])
+    for b in (b1, b2):
+        b.upload()
+    b1.reach()
+    b2.reach()
+    b2.get_V(0)
+    with pytest.raises(NNVError):
+        b1.get_V(0)                 # overwritten by the later reach: refused, not garbage
+    b1.reach()
+    b1.get_V(0)
+    b1.close()
+    b2.close()
+    net.close()
+
+
 def test_reach_is_deterministic_and_batch_invariant(ctx):
     cfg = make_config("cnn32", n_queries=3, small=True)
     net = Network(ctx, cfg["layers"], cfg["in_shape"])
