@@ -162,7 +162,7 @@ def run_reference(args):
             "config": {"workload": WORKLOAD, "batch_per_step": 1},
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line))
+    emit(line)
 
 
 def run_ours(args):
@@ -331,7 +331,7 @@ def run_ours(args):
                 "value": v, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
                 "sample": "1 image, layers 1-%d (%.1f%% of the image's dense contraction flops) in %.1f s, scaled to "
                           "whole queries; reach only, NumPy/OpenBLAS FP64" % (CPU_PREFIX_LAYERS, 100 * frac, tcpu)}
-        print(json.dumps(line))
+        emit(line)
     for b, _ in batches:
         b.close()
     net.close()
@@ -340,7 +340,25 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+_RESULT_FD = None
+
+
+def emit(line):
+    """The one JSON line goes to the process's original stdout; everything else printed while the bench
+    runs (library banners such as NCCL's version line) was diverted to stderr in main()."""
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main():
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=8)
