@@ -134,6 +134,10 @@ struct nnvb_ctx {
     size_t arena_bytes = 0;
     int64_t launches = 0;
     PinnedBuf scratch;      // small host->device traffic of the layer loop
+    // staging and input buffers of destroyed batches, handed to the next batches: a caller that builds a
+    // batch per call (the usual way through the host API) then allocates nothing in the steady state
+    std::vector<PinnedBuf> spare_pinned;
+    std::vector<DevBuf> spare_dev;
     size_t scratch_off = 0; // bytes of `scratch` handed out since the last stream sync
     WorkBufs work;
     // generator sharding over ranks (world == 1: off)
@@ -424,6 +428,8 @@ int nnvb_destroy(nnvb_ctx* ctx) {
     ctx->work.release();
     prof_drain(ctx);
     for (cudaEvent_t e : ctx->prof_pool) cudaEventDestroy(e);
+    for (auto& x : ctx->spare_pinned) x.release();
+    for (auto& x : ctx->spare_dev) x.release();
     if (ctx->arena) cudaFree(ctx->arena);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -657,6 +663,13 @@ int nnvb_batch_create(nnvb_net* net, int n_queries, nnvb_batch** out) {
     b->m0.assign(n_queries, 0);
     b->box_implies_C.assign(n_queries, 1);
     b->wk = &net->ctx->work;
+    nnvb_ctx* ctx = net->ctx;
+    if (!ctx->spare_pinned.empty()) { b->h_in = ctx->spare_pinned.back(); ctx->spare_pinned.pop_back(); }
+    for (DevBuf* d : {&b->d_in, &b->d_in_meta, &b->d_in_pos}) {
+        if (ctx->spare_dev.empty()) break;
+        *d = ctx->spare_dev.back();            // largest first: d_in is the big one
+        ctx->spare_dev.pop_back();
+    }
     *out = b;
     return NNVB_OK;
 }
@@ -666,10 +679,14 @@ int nnvb_batch_destroy(nnvb_batch* b) {
     nnvb_ctx* ctx = b->net->ctx;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
-    b->h_in.release();
-    b->d_in.release();
-    b->d_in_meta.release();
-    b->d_in_pos.release();
+    // keep the buffers of up to four batches for the next ones (ascending by size, so that the largest is taken first)
+    if (b->h_in.p && ctx->spare_pinned.size() < 4) ctx->spare_pinned.push_back(b->h_in);
+    else b->h_in.release();
+    for (DevBuf* d : {&b->d_in_pos, &b->d_in_meta, &b->d_in}) {
+        if (d->p && ctx->spare_dev.size() < 12) ctx->spare_dev.push_back(*d);
+        else d->release();
+    }
+    std::sort(ctx->spare_dev.begin(), ctx->spare_dev.end(), [](const DevBuf& x, const DevBuf& y) { return x.cap < y.cap; });
     if (ctx->result_owner == b) ctx->result_owner = nullptr;
     delete b;
     return NNVB_OK;
