@@ -217,6 +217,7 @@ __global__ void fill_dense_windows_kernel(int64_t n, int4* __restrict__ box) {
 
 // Windowed average pooling: a thread owns one (channel, patch position) and walks over the columns
 // (blockIdx.y strided), so the index arithmetic is done once; same window sum as the dense kernel.
+template <bool PAIRS>
 __global__ void avgpool_windowed_kernel(PoolGeom g, RowMask mask, ColWindows win, int64_t col_base, int64_t ncols,
                                         const double* __restrict__ Vin, int64_t ld_in, double* __restrict__ Vout,
                                         int64_t ld_out) {
@@ -241,17 +242,41 @@ __global__ void avgpool_windowed_kernel(PoolGeom g, RowMask mask, ColWindows win
         const uint8_t* st = (mask.state != nullptr && j < mask.ncols) ? mask.state + mask.col_q[j] * mask.N + cbase : nullptr;
         const int h0 = oh * g.sh - g.pad_t, w0 = ow * g.sw - g.pad_l;
         double acc = 0.0;
-        for (int aa = 0; aa < g.ph; ++aa) {
-            const int h = h0 + aa;
-            for (int bb = 0; bb < g.pw; ++bb) {
+        if (PAIRS) {
+            // 2x2 windows at stride 2 without padding on an even image height: the two rows of a window
+            // column are one aligned 16-byte load (and one 2-byte load of their states); the four values
+            // are added in the order of the general loop below
+            double a[2][2];         // [row][column]
+#pragma unroll
+            for (int bb = 0; bb < 2; ++bb) {
                 const int w = w0 + bb;
-                double v = 0.0;
-                if (h >= 0 && h < g.H && w >= 0 && w < g.W && unsigned(h - bx.x) < unsigned(bx.z) &&
-                    unsigned(w - bx.y) < unsigned(bx.w)) {
-                    const int64_t o_in = h + int64_t(g.H) * w;
-                    if (st == nullptr || st[o_in] == 0) v = src[o_in];
+                a[0][bb] = 0.0;
+                a[1][bb] = 0.0;
+                if (w < g.W && unsigned(w - bx.y) < unsigned(bx.w)) {
+                    const int64_t o_in = h0 + int64_t(g.H) * w;
+                    const double2 v = *reinterpret_cast<const double2*>(src + o_in);
+                    const unsigned s2 = st != nullptr ? *reinterpret_cast<const unsigned short*>(st + o_in) : 0u;
+                    if (unsigned(h0 - bx.x) < unsigned(bx.z) && (s2 & 0xffu) == 0) a[0][bb] = v.x;
+                    if (unsigned(h0 + 1 - bx.x) < unsigned(bx.z) && (s2 >> 8) == 0) a[1][bb] = v.y;
                 }
-                acc = acc + v;
+            }
+            acc = acc + a[0][0];
+            acc = acc + a[0][1];
+            acc = acc + a[1][0];
+            acc = acc + a[1][1];
+        } else {
+            for (int aa = 0; aa < g.ph; ++aa) {
+                const int h = h0 + aa;
+                for (int bb = 0; bb < g.pw; ++bb) {
+                    const int w = w0 + bb;
+                    double v = 0.0;
+                    if (h >= 0 && h < g.H && w >= 0 && w < g.W && unsigned(h - bx.x) < unsigned(bx.z) &&
+                        unsigned(w - bx.y) < unsigned(bx.w)) {
+                        const int64_t o_in = h + int64_t(g.H) * w;
+                        if (st == nullptr || st[o_in] == 0) v = src[o_in];
+                    }
+                    acc = acc + v;
+                }
             }
         }
         Vout[j * ld_out + oh + int64_t(g.Ho) * ow + obase] = acc / div;
@@ -265,7 +290,13 @@ int launch_avgpool_windowed(cudaStream_t st, const PoolGeom& g, const RowMask& m
     const int per_col = win.wh * win.ww * g.C;
     const int threads = per_col >= 256 ? 256 : 128;
     dim3 grid((unsigned)ceil_div(per_col, threads), (unsigned)std::min<int64_t>(ncols, 8192));
-    avgpool_windowed_kernel<<<grid, threads, 0, st>>>(g, mask, win, col_base, ncols, Vin, ld_in, Vout, ld_out);
+    // the state array of a query starts at q*N: N even keeps the 2-byte state loads aligned
+    const bool pairs = g.ph == 2 && g.pw == 2 && g.sh == 2 && g.sw == 2 && g.pad_t == 0 && g.pad_l == 0 &&
+                       g.H % 2 == 0 && ld_in % 2 == 0 && (mask.state == nullptr || mask.N % 2 == 0);
+    if (pairs)
+        avgpool_windowed_kernel<true><<<grid, threads, 0, st>>>(g, mask, win, col_base, ncols, Vin, ld_in, Vout, ld_out);
+    else
+        avgpool_windowed_kernel<false><<<grid, threads, 0, st>>>(g, mask, win, col_base, ncols, Vin, ld_in, Vout, ld_out);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;

@@ -113,13 +113,13 @@ struct WorkBufs {
     DevBuf lb, ub, state, rank, blk_cross, q_cross, q_dead, q_new_off, gen_off;
     DevBuf tmp;                          // gathers for downloads
     DevBuf fcg;                          // column grouping of the window-gathered FC
-    DevBuf gbox;                         // joint windows of groups of list entries (bound reduction)
+    DevBuf winsort;                      // origin bins and sorted columns of the windowed bound reduction
     DevBuf hs_G, hs_g, hs_q, hs_margin, hs_r, hs_roff, hs_val, hs_scale, wit[2];   // halfspace tests
     std::vector<std::unique_ptr<ReluLayerRecord>> relu;
     void release() {
         DevBuf* bufs[] = {&col_q, &pl, &pu, &col_pos, &box, &qcol_off[0], &qcol_off[1], &qcol_idx[0], &qcol_idx[1],
                           &chunk_beg, &chunk_end, &q_chunk_off, &partial, &sums, &lb, &ub, &state, &rank, &blk_cross,
-                          &q_cross, &q_dead, &q_new_off, &gen_off, &tmp, &fcg, &gbox, &hs_G, &hs_g, &hs_q, &hs_margin, &hs_r,
+                          &q_cross, &q_dead, &q_new_off, &gen_off, &tmp, &fcg, &winsort, &hs_G, &hs_g, &hs_q, &hs_margin, &hs_r,
                           &hs_roff, &hs_val, &hs_scale, &wit[0], &wit[1]};
         for (DevBuf* d : bufs) d->release();
         for (auto& r : relu) r->release();
@@ -212,7 +212,7 @@ struct nnvb_batch {
     int list_cur = 0;
     // Column cohorts: runs of columns born together (centres, input generators, the columns of each
     // ReLU layer).  A windowed cohort's columns are exactly zero outside a wh x ww window whose origin
-    // is kept per column (win_h0 / win_w0); convolutions then compute only the patch that can be non-zero.
+    // is kept per column (WorkBufs::box); the layer kernels then compute only the part that can be non-zero.
     // clean: the memory outside the columns' windows is known to hold zeros (false after a windowed launch
     // that wrote the windows only; readers then go by the windows, see ensure_clean)
     // qn: columns per query (they are stored query by query; empty for the centres)
@@ -1073,8 +1073,8 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
     w.win_slices = win_slices;
     if (wc.n > 0) {
         const size_t ints = range_windows_scratch_ints(wc, nq, b->ncols);
-        NNVB_TRY(b->wk->gbox.ensure(sizeof(int32_t) * (ints + win_seg.size()), st));
-        w.win_scratch = b->wk->gbox.as<int32_t>();
+        NNVB_TRY(b->wk->winsort.ensure(sizeof(int32_t) * (ints + win_seg.size()), st));
+        w.win_scratch = b->wk->winsort.as<int32_t>();
         int32_t* seg_dev = w.win_scratch + ints;
         NNVB_TRY(h2d_small(ctx, seg_dev, win_seg.data(), sizeof(int32_t) * win_seg.size()));
         w.win_seg = seg_dev;
