@@ -170,6 +170,7 @@ __global__ void win_rank_kernel(WinCohorts wc, int nq, const int4* __restrict__ 
 //    grid = (strips, nq); a thread owns RPT rows (pixel of the strip, channel), pixel fastest.
 constexpr int RW_THREADS = 256;
 constexpr int RW_RPT = 4;
+constexpr int RW_MLP = 8;            // window loads a thread keeps in flight
 constexpr int RW_MAX_RUNS = MAX_WIN_COHORTS * MAX_WIN_EXTENT;
 __global__ void __launch_bounds__(RW_THREADS)
 range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const double* __restrict__ pl,
@@ -269,15 +270,15 @@ range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const 
         for (int r = 0; r < RW_RPT; ++r) {
             if (row[r] < 0) continue;
             int j = 0;
-            for (; j + 4 <= cnt; j += 4) {              // four loads in flight, added in candidate order
-                double v[4];
+            for (; j + RW_MLP <= cnt; j += RW_MLP) {    // RW_MLP loads in flight, added in candidate order
+                double v[RW_MLP];
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < RW_MLP; ++u) {
                     const bool in = unsigned(hh[r] - s_h0[j + u]) < unsigned(s_wh[j + u]);
                     v[u] = in ? V[int64_t(s_col[j + u]) * ld + row[r]] : 0.0;
                 }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < RW_MLP; ++u) {
                     // max(v,0)*pl + min(v,0)*pu == v * (v > 0 ? pl : pu): one product per bound
                     const bool pos = v[u] > 0.0;
                     lo[r] = fma(v[u], pos ? s_pl[j + u] : s_pu[j + u], lo[r]);
