@@ -251,6 +251,27 @@ int launch_halfspace_pairs(cudaStream_t st, int n_pairs, const int32_t* pair_q, 
                            const int64_t* r_off, const int64_t* col_pos, int add_center, double* part,
                            int64_t* launches);
 constexpr int HS_SPLIT = 32;     // slices of a query's column list; `part` holds n_pairs * HS_SPLIT doubles
+// Back-substitution bound of halfspace rows through the recorded ReLU relaxations (see relu_star.cu): r holds
+// each pair's row by predicate position (as launch_halfspace_pairs writes it) and is overwritten;
+// bound[p] receives a lower bound of G x - g over the whole star set of the pair's query.
+struct BacksubLayer {
+    const double* G;            // crossing rows, per query a kq x P_in block (column-major) at G_off[q]
+    const int64_t* G_off;       // [nq+1]
+    const double* c;            // per new column: centre value, lower and upper bound of the pre-activation
+    const double* l;
+    const double* u;
+    const int64_t* new_off;     // [nq+1] first new column of each query
+    const int64_t* P_in;        // [nq] predicates entering the layer
+};
+constexpr int MAX_BACKSUB_LAYERS = 32;
+struct BacksubLayers {
+    int n;
+    BacksubLayer L[MAX_BACKSUB_LAYERS];
+};
+int launch_backsub(cudaStream_t st, const BacksubLayers& layers, int n_pairs, const int32_t* pair_q, int64_t Nout,
+                   int64_t ld, const double* V, const double* G, const double* g, double* r, const int64_t* r_off,
+                   const int64_t* qcol_off, const int32_t* qcol_idx, const double* pl, const double* pu, double* bound,
+                   int64_t* launches);
 // Witness search kernels (one point per pair, X is [ld x n_pairs]).
 int launch_witness_x0_bounds(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t N, int64_t ld,
                              const double* lbub, const double* r, const int64_t* r_off, double* X,

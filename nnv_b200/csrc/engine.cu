@@ -96,10 +96,12 @@ struct ReluLayerRecord {
     DevBuf G, G_off;                     // crossing rows (keep_constraints)
     std::vector<int64_t> h_G_off;
     DevBuf lb, ub, rank, P_in_dev;       // [nq][N] bounds and crossing ranks, [nq] P_in (keep_layer_bounds)
+    DevBuf new_off_dev;                  // [nq+1] device copy of new_off (keep_constraints)
     bool has_G = false, has_bounds = false;
     void release() {
         idx.release(); q.release(); c.release(); l.release(); u.release();
         G.release(); G_off.release(); lb.release(); ub.release(); rank.release(); P_in_dev.release();
+        new_off_dev.release();
     }
 };
 
@@ -114,13 +116,13 @@ struct WorkBufs {
     DevBuf tmp;                          // gathers for downloads
     DevBuf fcg;                          // column grouping of the window-gathered FC
     DevBuf winsort;                      // origin bins and sorted columns of the windowed bound reduction
-    DevBuf hs_G, hs_g, hs_q, hs_margin, hs_r, hs_roff, hs_val, hs_scale, wit[2];   // halfspace tests
+    DevBuf hs_G, hs_g, hs_q, hs_margin, hs_r, hs_roff, hs_val, hs_scale, hs_bound, wit[2];   // halfspace tests
     std::vector<std::unique_ptr<ReluLayerRecord>> relu;
     void release() {
         DevBuf* bufs[] = {&col_q, &pl, &pu, &col_pos, &box, &qcol_off[0], &qcol_off[1], &qcol_idx[0], &qcol_idx[1],
                           &chunk_beg, &chunk_end, &q_chunk_off, &partial, &sums, &lb, &ub, &state, &rank, &blk_cross,
                           &q_cross, &q_dead, &q_new_off, &gen_off, &tmp, &fcg, &winsort, &hs_G, &hs_g, &hs_q, &hs_margin, &hs_r,
-                          &hs_roff, &hs_val, &hs_scale, &wit[0], &wit[1]};
+                          &hs_roff, &hs_val, &hs_scale, &hs_bound, &wit[0], &wit[1]};
         for (DevBuf* d : bufs) d->release();
         for (auto& r : relu) r->release();
         relu.clear();
@@ -1131,7 +1133,7 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
         return NNVB_E_UNSUPPORTED;
     }
     const int64_t K_loc = shard_count(K, rank, world);
-    if (b->opts.keep_layer_bounds || world > 1) {
+    if (b->opts.keep_layer_bounds || b->opts.keep_constraints || world > 1) {
         NNVB_TRY(rec->P_in_dev.ensure(sizeof(int64_t) * nq, st));
         NNVB_TRY(h2d_small(ctx, rec->P_in_dev.p, rec->P_in.data(), sizeof(int64_t) * nq));
     }
@@ -1167,6 +1169,9 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
         NNVB_TRY(h2d_small(ctx, rec->G_off.p, rec->h_G_off.data(), sizeof(int64_t) * (nq + 1)));
         r.G = rec->G.as<double>();
         r.G_off = rec->G_off.as<int64_t>();
+        // the back-substitution bound of the verdict walks the records on the device
+        NNVB_TRY(rec->new_off_dev.ensure(sizeof(int64_t) * (nq + 1), st));
+        NNVB_CUDA(cudaMemcpyAsync(rec->new_off_dev.p, w.q_new_off, sizeof(int64_t) * (nq + 1), cudaMemcpyDeviceToDevice, st));
         rec->has_G = true;
     }
     // relaxation: lb/ub read, dead and crossing rows cleared in every column of their query,
@@ -1556,9 +1561,22 @@ int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vec
         if (margin[p] > 0.0) status[p] = NNVB_VERDICT_EMPTY;
         else if (b->box_implies_C[pair_q[p]]) open.push_back(p);
     }
-    bool have_bounds = true;
-    for (int i = 0; i < b->net->n_relu; ++i) have_bounds = have_bounds && b->wk->relu[i]->has_bounds;
-    if (open.empty() || !have_bounds) return NNVB_OK;
+    // the witness pass needs the bounds of every ReLU layer, the back-substitution bound its crossing rows
+    bool have_bounds = true, have_G = ctx->world == 1 && b->net->n_relu <= MAX_BACKSUB_LAYERS;
+    for (int i = 0; i < b->net->n_relu; ++i) {
+        have_bounds = have_bounds && b->wk->relu[i]->has_bounds;
+        have_G = have_G && b->wk->relu[i]->has_G;
+    }
+    if (open.empty() || (!have_bounds && !have_G)) return NNVB_OK;
+    BacksubLayers bs{};
+    if (have_G) {
+        bs.n = b->net->n_relu;
+        for (int i = 0; i < bs.n; ++i) {
+            ReluLayerRecord* rc = b->wk->relu[i].get();
+            bs.L[i] = BacksubLayer{rc->G.as<double>(), rc->G_off.as<int64_t>(), rc->c.as<double>(), rc->l.as<double>(),
+                                   rc->u.as<double>(), rc->new_off_dev.as<int64_t>(), rc->P_in_dev.as<int64_t>()};
+        }
+    }
 
     // witness points for the open pairs, in chunks that bound the scratch memory
     int64_t max_ld = b->ld0;
@@ -1593,38 +1611,56 @@ int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vec
                                         b->wk->col_pos.as<int64_t>(), add_center, nullptr, &ctx->launches));
         // every rank needs the coefficients of all predicates: each one wrote its own columns' entries
         NNVB_TRY(allreduce(ctx, b->wk->hs_r.as<double>(), roff[m]));
-        if (b->kind == 1) {
-            NNVB_TRY(launch_witness_x0_bounds(st, m, b->wk->hs_q.as<int32_t>(), b->N0, b->ld0, b->d_in.as<double>(),
-                                              b->wk->hs_r.as<double>(), b->wk->hs_roff.as<int64_t>(), b->wk->wit[0].as<double>(),
-                                              &ctx->launches));
-        } else {
-            int64_t ncols0 = b->nq;
-            std::vector<int64_t> gen0(b->nq + 1);
-            for (int q = 0; q < b->nq; ++q) { gen0[q] = ncols0; ncols0 += b->P0_loc[q]; }
-            gen0[b->nq] = ncols0;
-            NNVB_TRY(b->wk->gen_off.ensure(sizeof(int64_t) * (b->nq + 1), st));
-            NNVB_CUDA(cudaMemcpyAsync(b->wk->gen_off.p, gen0.data(), sizeof(int64_t) * (b->nq + 1), cudaMemcpyHostToDevice, st));
-            // x0 = c + sum_j alpha_j G0_j: local generators here, summed over the ranks, centre added by rank 0
-            NNVB_TRY(launch_witness_x0_star(st, m, b->wk->hs_q.as<int32_t>(), b->N0, b->ld0, b->ld0, b->d_in.as<double>(),
-                                            b->wk->gen_off.as<int64_t>(), b->d_in_meta.as<double>(),
-                                            b->d_in_meta.as<double>() + ncols0, b->wk->hs_r.as<double>(),
-                                            b->wk->hs_roff.as<int64_t>(), b->d_in_pos.as<int64_t>(), add_center,
-                                            b->wk->wit[0].as<double>(), &ctx->launches));
-            NNVB_TRY(allreduce(ctx, b->wk->wit[0].as<double>(), b->ld0 * int64_t(m)));
+        if (have_bounds) {
+            if (b->kind == 1) {
+                NNVB_TRY(launch_witness_x0_bounds(st, m, b->wk->hs_q.as<int32_t>(), b->N0, b->ld0, b->d_in.as<double>(),
+                                                  b->wk->hs_r.as<double>(), b->wk->hs_roff.as<int64_t>(), b->wk->wit[0].as<double>(),
+                                                  &ctx->launches));
+            } else {
+                int64_t ncols0 = b->nq;
+                std::vector<int64_t> gen0(b->nq + 1);
+                for (int q = 0; q < b->nq; ++q) { gen0[q] = ncols0; ncols0 += b->P0_loc[q]; }
+                gen0[b->nq] = ncols0;
+                NNVB_TRY(b->wk->gen_off.ensure(sizeof(int64_t) * (b->nq + 1), st));
+                NNVB_CUDA(cudaMemcpyAsync(b->wk->gen_off.p, gen0.data(), sizeof(int64_t) * (b->nq + 1), cudaMemcpyHostToDevice, st));
+                // x0 = c + sum_j alpha_j G0_j: local generators here, summed over the ranks, centre added by rank 0
+                NNVB_TRY(launch_witness_x0_star(st, m, b->wk->hs_q.as<int32_t>(), b->N0, b->ld0, b->ld0, b->d_in.as<double>(),
+                                                b->wk->gen_off.as<int64_t>(), b->d_in_meta.as<double>(),
+                                                b->d_in_meta.as<double>() + ncols0, b->wk->hs_r.as<double>(),
+                                                b->wk->hs_roff.as<int64_t>(), b->d_in_pos.as<int64_t>(), add_center,
+                                                b->wk->wit[0].as<double>(), &ctx->launches));
+                NNVB_TRY(allreduce(ctx, b->wk->wit[0].as<double>(), b->ld0 * int64_t(m)));
+            }
+            double* X = nullptr;
+            int64_t ldx = 0;
+            NNVB_TRY(witness_forward(b, m, b->wk->hs_q.as<int32_t>(), &X, &ldx, b->wk->hs_r.as<double>(), b->wk->hs_roff.as<int64_t>()));
+            NNVB_TRY(launch_witness_value(st, m, Nout, ldx, X, b->wk->hs_G.as<double>(), b->wk->hs_g.as<double>(),
+                                          b->wk->hs_val.as<double>(), b->wk->hs_scale.as<double>(), &ctx->launches));
         }
-        double* X = nullptr;
-        int64_t ldx = 0;
-        NNVB_TRY(witness_forward(b, m, b->wk->hs_q.as<int32_t>(), &X, &ldx, b->wk->hs_r.as<double>(), b->wk->hs_roff.as<int64_t>()));
-        NNVB_TRY(launch_witness_value(st, m, Nout, ldx, X, b->wk->hs_G.as<double>(), b->wk->hs_g.as<double>(),
-                                      b->wk->hs_val.as<double>(), b->wk->hs_scale.as<double>(), &ctx->launches));
-        std::vector<double> val(m), scale(m);
-        NNVB_CUDA(cudaMemcpyAsync(val.data(), b->wk->hs_val.p, sizeof(double) * m, cudaMemcpyDeviceToHost, st));
-        NNVB_CUDA(cudaMemcpyAsync(scale.data(), b->wk->hs_scale.p, sizeof(double) * m, cudaMemcpyDeviceToHost, st));
+        if (have_G) {
+            // after the witness pass: the bound overwrites the rows
+            NNVB_TRY(b->wk->hs_bound.ensure(sizeof(double) * m, st));
+            NNVB_TRY(launch_backsub(st, bs, m, b->wk->hs_q.as<int32_t>(), Nout, b->ld, b->V, b->wk->hs_G.as<double>(),
+                                    b->wk->hs_g.as<double>(), b->wk->hs_r.as<double>(), b->wk->hs_roff.as<int64_t>(), qoff, qidx,
+                                    b->wk->pl.as<double>(), b->wk->pu.as<double>(), b->wk->hs_bound.as<double>(),
+                                    &ctx->launches));
+        }
+        std::vector<double> val(m, 0.0), scale(m, 0.0), bound(m, 0.0);
+        if (have_bounds) {
+            NNVB_CUDA(cudaMemcpyAsync(val.data(), b->wk->hs_val.p, sizeof(double) * m, cudaMemcpyDeviceToHost, st));
+            NNVB_CUDA(cudaMemcpyAsync(scale.data(), b->wk->hs_scale.p, sizeof(double) * m, cudaMemcpyDeviceToHost, st));
+        }
+        if (have_G)
+            NNVB_CUDA(cudaMemcpyAsync(bound.data(), b->wk->hs_bound.p, sizeof(double) * m, cudaMemcpyDeviceToHost, st));
         NNVB_TRY(sync(ctx));
-        // accept only points clearly inside the halfspace: well beyond the feasibility
-        // tolerance of an LP solver deciding the same question
-        for (int i = 0; i < m; ++i)
-            if (val[i] < -1e-6 * (1.0 + scale[i])) status[open[c0 + i]] = NNVB_VERDICT_NONEMPTY;
+        for (int i = 0; i < m; ++i) {
+            const int pp = open[c0 + i];
+            // a positive lower bound over the whole set: empty, with the bound as the margin
+            if (have_G && bound[i] > 0.0) { status[pp] = NNVB_VERDICT_EMPTY; margin[pp] = bound[i]; }
+            // accept only points clearly inside the halfspace: well beyond the feasibility
+            // tolerance of an LP solver deciding the same question
+            else if (have_bounds && val[i] < -1e-6 * (1.0 + scale[i])) status[pp] = NNVB_VERDICT_NONEMPTY;
+        }
     }
     return NNVB_OK;
 }

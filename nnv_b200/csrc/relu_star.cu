@@ -694,6 +694,89 @@ __global__ void halfspace_margin_kernel(int n_pairs, int n_split, const int32_t*
 }
 
 // ---------------------------------------------------------------------------
+// Back-substitution bound.  The box minimum above treats every predicate as free in its range.  With
+// the crossing rows of every ReLU layer at hand (constraint records) the relaxation itself can be used:
+// a new predicate y of a crossing neuron with pre-activation x = c + G alpha (alpha: the predicates
+// that existed before its layer) satisfies y >= 0, y >= x and y <= a (x - l), a = u / (u - l)
+// (PosLin.m:716-735).  A term rho*y of the halfspace row is therefore bounded from below by
+// rho*lambda*x for any lambda in [0,1] when rho >= 0 (lambda = 1 if u >= -l, else 0) and by rho*a*(x - l)
+// when rho < 0.  Substituting layer by layer, last layer first, leaves a row over the input predicates
+// only, whose box minimum is a lower bound of the row over the whole star set: the minimum the
+// emptiness LP of Star.isEmptySet (Star.m:1216-1232) would have to beat.  A positive bound proves the
+// intersection empty.  One block per pair; r holds the row by predicate position and is overwritten.
+__global__ void __launch_bounds__(256)
+backsub_kernel(BacksubLayers layers, const int32_t* __restrict__ pair_q, int64_t Nout, int64_t ld,
+               const double* __restrict__ V, const double* __restrict__ Gh, const double* __restrict__ gh,
+               double* __restrict__ r, const int64_t* __restrict__ r_off, const int64_t* __restrict__ qcol_off,
+               const int32_t* __restrict__ qcol_idx, const double* __restrict__ pl, const double* __restrict__ pu,
+               double* __restrict__ bound) {
+    const int p = blockIdx.x;
+    const int q = pair_q[p];
+    double* rp = r + r_off[p];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ double red[256];
+    double konst = 0.0;                     // kept by thread 0
+    if (tid == 0) {
+        const double* Gr = Gh + int64_t(p) * Nout;
+        const double* v = V + int64_t(q) * ld;
+        for (int64_t o = 0; o < Nout; ++o) konst = fma(Gr[o], v[o], konst);
+        konst -= gh[p];
+    }
+    int64_t P_first = qcol_off[q + 1] - qcol_off[q];
+    for (int L = layers.n - 1; L >= 0; --L) {
+        const BacksubLayer& rec = layers.L[L];
+        const int64_t c0 = rec.new_off[q];
+        const int64_t kq = rec.new_off[q + 1] - c0;
+        const int64_t Pin = rec.P_in[q];
+        P_first = Pin;
+        // weights of the pre-activations, stored over the coefficients they replace
+        double part = 0.0;
+        for (int64_t t = tid; t < kq; t += 256) {
+            const double rho = rp[Pin + t];
+            const double l = rec.l[c0 + t], u = rec.u[c0 + t], c = rec.c[c0 + t];
+            double w;
+            if (rho >= 0.0) {
+                w = (u >= -l) ? rho : 0.0;
+                part += w * c;
+            } else {
+                w = rho * (u / (u - l));
+                part += w * (c - l);
+            }
+            rp[Pin + t] = w;
+        }
+        red[tid] = part;
+        __syncthreads();
+        for (int o = 128; o; o >>= 1) {
+            if (tid < o) red[tid] += red[tid + o];
+            __syncthreads();
+        }
+        if (tid == 0) konst += red[0];
+        // r[j] += sum_t w_t G[t, j]: a warp per earlier predicate, lanes over the layer's crossing neurons
+        const double* Gq = rec.G + rec.G_off[q];
+        for (int64_t j = warp; j < Pin; j += 8) {
+            double acc = 0.0;
+            for (int64_t t = lane; t < kq; t += 32) acc = fma(rp[Pin + t], Gq[j * kq + t], acc);
+            for (int o = 16; o; o >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, o);
+            if (lane == 0) rp[j] += acc;
+        }
+        __syncthreads();
+    }
+    // box minimum over what is left: the predicates of the input set
+    double part = 0.0;
+    for (int64_t j = tid; j < P_first; j += 256) {
+        const int64_t col = qcol_idx[qcol_off[q] + j];
+        part += fmin(rp[j] * pl[col], rp[j] * pu[col]);
+    }
+    red[tid] = part;
+    __syncthreads();
+    for (int o = 128; o; o >>= 1) {
+        if (tid < o) red[tid] += red[tid + o];
+        __syncthreads();
+    }
+    if (tid == 0) bound[p] = konst + red[0];
+}
+
+// ---------------------------------------------------------------------------
 // Witness search: a point of the output set inside a halfspace proves the
 // intersection non-empty.  Every point of an approx-star set is reached by
 // picking the input predicates in their box and, neuron by neuron, a value of
@@ -981,6 +1064,18 @@ int launch_halfspace_pairs(cudaStream_t st, int n_pairs, const int32_t* pair_q, 
         NNVB_CUDA(cudaGetLastError());
         if (launches) *launches += 1;
     }
+    return NNVB_OK;
+}
+
+int launch_backsub(cudaStream_t st, const BacksubLayers& layers, int n_pairs, const int32_t* pair_q, int64_t Nout,
+                   int64_t ld, const double* V, const double* G, const double* g, double* r, const int64_t* r_off,
+                   const int64_t* qcol_off, const int32_t* qcol_idx, const double* pl, const double* pu, double* bound,
+                   int64_t* launches) {
+    if (n_pairs <= 0) return NNVB_OK;
+    backsub_kernel<<<n_pairs, 256, 0, st>>>(layers, pair_q, Nout, ld, V, G, g, r, r_off, qcol_off, qcol_idx, pl, pu,
+                                            bound);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
     return NNVB_OK;
 }
 

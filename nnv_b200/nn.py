@@ -440,8 +440,12 @@ class NN:
         net = self._network(shape)
         b = Batch(net, [s._query() for s in inputSets])
         t0 = time.perf_counter()
-        b.upload()
-        b.reach(keep_constraints=keep_constraints, keep_layer_bounds=keep_layer_bounds)
+        try:
+            b.upload()
+            b.reach(keep_constraints=keep_constraints, keep_layer_bounds=keep_layer_bounds)
+        except Exception:
+            b.close()
+            raise
         self.reachTime = [time.perf_counter() - t0]
         self.reachStats = b.relu_stats()
         return b
@@ -515,13 +519,40 @@ class NN:
             stats["n_witness"] = int((verdict == L.VERDICT_NONEMPTY).sum())
             stats["n_lp_queries"] = int(len(undecided))
         b.close()
-        for q in undecided:
-            # one query at a time keeps the constraint records small
-            bq = self.reach_batch([inputSets[q]], reachOptions, keep_constraints=True)
-            S = _result_set(bq, 0, True)
-            hs = self.robustness_set(int(targets[q]), class_type)
-            open_rows = np.nonzero(status[q] == L.UNDECIDED)[0]
-            result[q] = verify_specification([S], [hs[i] for i in open_rows])
+        # Second pass, undecided queries only, with the crossing rows of every ReLU layer kept: the device
+        # then also bounds each open row by back-substitution through the recorded relaxations (decides most
+        # rows the LP would find empty), and what is still open goes to the LP on that pass's constraint system.
+        if stats is not None:
+            stats["n_backsub"] = 0
+        group = 32                      # bounds the size of the constraint records
+        for g0 in range(0, len(undecided), group):
+            qs = undecided[g0:g0 + group]
+            try:
+                bq = self.reach_batch([inputSets[q] for q in qs], reachOptions, keep_constraints=True,
+                                      keep_layer_bounds=True)
+            except L.NNVError:
+                if len(qs) == 1:
+                    raise
+                # records of the whole group do not fit: one query at a time
+                for q in qs:
+                    result[q] = self.verify_robustness_batch([inputSets[q]], reachOptions, [targets[q]], class_type)[0]
+                continue
+            v2, s2, _ = bq.verify_robust(t0[qs], class_type)
+            for k, q in enumerate(qs):
+                if v2[k] == L.VERDICT_EMPTY:
+                    result[q] = 1
+                    if stats is not None:
+                        stats["n_backsub"] += 1
+                        stats["n_lp_queries"] -= 1
+                elif v2[k] == L.VERDICT_NONEMPTY:
+                    result[q] = 2
+                    if stats is not None:
+                        stats["n_lp_queries"] -= 1
+                else:
+                    S = _result_set(bq, k, True)
+                    hs = self.robustness_set(int(targets[q]), class_type)
+                    open_rows = np.nonzero(s2[k] == L.UNDECIDED)[0]
+                    result[q] = verify_specification([S], [hs[i] for i in open_rows])
             bq.close()
         return result
 

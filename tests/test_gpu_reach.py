@@ -150,6 +150,43 @@ def test_verdicts_match_oracle(ctx, golden, name, small, nq):
     assert stats["n_prefilter"] + stats["n_witness"] + stats["n_lp_queries"] == nq
 
 
+@pytest.mark.parametrize("name,small,nq", [("cnn28", True, 6), ("cnn28", False, 10), ("bright28", True, 4),
+                                           ("cnn32", True, 3)])
+def test_device_verdicts_per_halfspace_row_are_sound(ctx, name, small, nq):
+    """Every row the device decides agrees with the emptiness LP of the oracle on that row: box minimum
+    and back-substitution bound (EMPTY), witness point (NONEMPTY).  With the crossing rows recorded the
+    back-substitution bound leaves no more rows open than the run without them."""
+    from nnv_b200 import _lib as L
+    cfg = make_config(name, n_queries=nq, small=small)
+    net = Network(ctx, cfg["layers"], cfg["in_shape"])
+    b = Batch(net, cfg["queries"])
+    b.upload()
+    tg = [qu["target"] for qu in cfg["queries"]]
+    kind = cfg["queries"][0]["spec"]
+    b.reach(keep_layer_bounds=True)
+    _, s0, _ = b.verify_robust(tg, kind)
+    s0 = np.array(s0).copy()
+    b.reach(keep_constraints=True, keep_layer_bounds=True)
+    _, s1, m1 = b.verify_robust(tg, kind)
+    s1 = np.array(s1)
+    assert (s1 == L.UNDECIDED).sum() <= (s0 == L.UNDECIDED).sum()
+    for q, qu in enumerate(cfg["queries"]):
+        S = O.reach(cfg["layers"], O.star_from_query(qu))
+        G, g = O.robustness_set(S.mat().shape[0], qu["target"], kind)
+        for i in range(G.shape[0]):
+            if s0[q][i] == L.UNDECIDED and s1[q][i] == L.UNDECIDED:
+                continue
+            C, d = O.intersect_halfspace_system(S, G[i:i + 1], g[i:i + 1])
+            empty = O.is_empty_set(C, d, S.pl, S.pu)
+            for st in (s0[q][i], s1[q][i]):
+                if st == L.VERDICT_EMPTY:
+                    assert empty, (q, i)
+                elif st == L.VERDICT_NONEMPTY:
+                    assert not empty, (q, i)
+    b.close()
+    net.close()
+
+
 def test_reference_shaped_api_single_set(ctx):
     cfg = make_config("cnn28", n_queries=1, small=True)
     qu = cfg["queries"][0]
