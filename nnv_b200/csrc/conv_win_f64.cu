@@ -108,7 +108,30 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
         chan[c] = ok ? bn.rden[co] : 1.0;
         chan[BN + c] = ok ? bn.scale[co] : 1.0;
     }
+    __shared__ unsigned row_used[WARPS_M];
+    if (tid < WARPS_M) row_used[tid] = 0u;
     __syncthreads();
+
+    // Patches near the image border hang over it.  Columns that lie next to each other in memory come from
+    // neighbouring pixels, so whole tiles agree on which patch positions are off the image: a block whose
+    // patch column is off the image for all of its columns has nothing to do, and a tile skips the patch
+    // rows that are off the image for its 16 columns.
+    bool col_on = false;
+    if (tid < p.ncol && j0 + tid < ncols) {
+        const int4 bx = s_box[tid];
+        const int ow = bx.y + p.g.pad_l - ext_w + owl;
+        col_on = ow >= 0 && ow < p.g.Wo;
+        if (col_on) {
+            unsigned m = 0u;
+            for (int o = 0; o < th_cnt; ++o) {
+                const int oh = bx.x + p.g.pad_t - ext_h + ohb * CW_TH + o;
+                if (oh >= 0 && oh < p.g.Ho) m |= 1u << o;
+            }
+            if (m) atomicOr(&row_used[tid >> 4], m);
+        }
+    }
+    if (__syncthreads_or(col_on ? 1 : 0) == 0) return;
+    const unsigned rows_on = row_used[wm];
 
     // table: entry e = (column, origin column, input row), input row fastest (contiguous in memory)
     const int n_e = p.ncol * n_kw * n_i;
@@ -199,7 +222,7 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
                 for (int khi = 0; khi < KH; ++khi) {
                     const int o = i - khi;
                     if (o >= 0 && o < CW_TH) {
-                        if (o < th_cnt) dmma_16x8x8(acc[o], af, bf[khi]);
+                        if ((rows_on >> o) & 1u) dmma_16x8x8(acc[o], af, bf[khi]);
                     }
                 }
             }

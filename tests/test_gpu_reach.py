@@ -271,6 +271,42 @@ def test_edge_cases(ctx):
     net.close()
 
 
+@pytest.mark.parametrize("tail", ["conv", "relu", "pool", "bn"])
+def test_networks_that_end_in_an_image_layer(ctx, tail):
+    """The set handed out after a convolution / ReLU / pooling / BN layer (no FC behind it) is the dense
+    tensor of the reference although the engine holds only the columns' windows at that point.  Also covers
+    strides, dilation, uneven padding and a 5x3 filter, which take the patch-tiled convolution."""
+    from nnv_b200.configs import _conv, _bn, _pool2, RELU
+    rng = np.random.default_rng(11)
+    shape = (24, 20, 3)
+    layers = [_conv(rng, 3, 3, 3, 8, (1, 1, 1, 1)), RELU, _conv(rng, 5, 3, 8, 8, (2, 1, 0, 1), (2, 1)), RELU, _pool2()]
+    layers[2]["dilation"] = (1, 2)
+    if tail == "conv":
+        layers.append(_conv(rng, 3, 3, 8, 4, (1, 1, 1, 1)))
+    elif tail == "relu":
+        layers += [_conv(rng, 3, 3, 8, 4, (1, 1, 1, 1)), RELU]
+    elif tail == "bn":
+        layers += [_conv(rng, 3, 3, 8, 4, (1, 1, 1, 1)), RELU, _bn(rng, 4)]
+    queries = []
+    for _ in range(3):
+        x = rng.uniform(0, 1, shape)
+        queries.append({"lb": np.maximum(x - 0.02, 0), "ub": np.minimum(x + 0.02, 1)})
+    net = Network(ctx, layers, shape)
+    b = Batch(net, queries)
+    b.upload()
+    b.reach()
+    for q, qu in enumerate(queries):
+        S = O.reach(layers, O.star_from_query(qu))
+        V = b.get_V(q)
+        assert V.shape == S.V.shape and _rel(V, S.V) < TOL
+        lb, ub = b.get_ranges(q)
+        rl, ru = O.output_ranges(S)
+        scale = max(np.abs(rl).max(), np.abs(ru).max())
+        assert np.abs(lb - rl).max() / scale < TOL and np.abs(ub - ru).max() / scale < TOL
+    b.close()
+    net.close()
+
+
 def test_capacity_error_is_reported_not_fatal():
     from nnv_b200._lib import NNVError, NNVB_E_CAPACITY
     from nnv_b200.engine import Context
