@@ -364,8 +364,8 @@ def main():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=8, help="input sets per step and per GPU")
-    ap.add_argument("--arena-gb", type=int, default=96)
+    ap.add_argument("--batch", type=int, default=16, help="input sets per step and per GPU")
+    ap.add_argument("--arena-gb", type=int, default=112)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -331,7 +331,7 @@ constexpr int FCG_BM = FCG_WARPS_M * FCG_WM * 16;
 constexpr size_t FCG_SMEM = size_t(FCG_STAGES) * (FcCfg<FCG_WM, FCG_WN, FCG_WARPS_M, FCG_WARPS_N>::A_STAGE +
                                                   FcCfg<FCG_WM, FCG_WN, FCG_WARPS_M, FCG_WARPS_N>::B_STAGE) * sizeof(double);
 
-__global__ void __launch_bounds__(256, 2)
+__global__ void __launch_bounds__(FCG_WARPS_M * FCG_WARPS_N * 32, FCG_WARPS_M * FCG_WARPS_N <= 8 ? 2 : 1)
 fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad, int Out,
                  const double* __restrict__ Wt, int ldw, const double* __restrict__ Vin, int64_t ld_in,
                  double* __restrict__ Vout, int64_t ld_out, const int32_t* __restrict__ tile_key,
