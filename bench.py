@@ -303,7 +303,8 @@ def run_ours(args):
                     "peak_source": dgemm_src if tensor else hbm_src, "launches": f["launches"],
                     "avg_launch_ms": f["ms"] / max(f["launches"], 1), "share_of_step": f["ms"] / dev_ms,
                     "traffic": (conv_dram_bytes_per_image * B * K / max(f["launches"], 1)) if fam == "conv" else None,
-                    "algorithmic_per_launch": f["work"] / max(f["launches"], 1)}
+                    ("algorithmic_flops_per_launch" if tensor else "algorithmic_bytes_per_launch"):
+                        f["work"] / max(f["launches"], 1)}
 
         # the roofline entry is the kernel family with the largest share of the timed region
         dominant = max(kernels, key=lambda k: prof[k]["ms"])
