@@ -307,6 +307,41 @@ def test_networks_that_end_in_an_image_layer(ctx, tail):
     net.close()
 
 
+def test_windowed_convolution_with_ragged_channel_counts(ctx):
+    """Channel counts that fill neither the 8-channel input chunks nor the 32/64-channel output tiles of the
+    windowed convolution kernel, a 3x5 filter, and image borders on every side of the windows."""
+    from nnv_b200.configs import _conv, _bn, _pool2, _fc, RELU
+    rng = np.random.default_rng(12)
+    shape = (18, 14, 3)
+    layers = [_conv(rng, 3, 3, 3, 20, (1, 1, 1, 1)), RELU,
+              _conv(rng, 3, 5, 20, 40, (1, 1, 2, 2)), _bn(rng, 40), RELU,
+              _conv(rng, 3, 3, 40, 24, (1, 1, 1, 1)), RELU, _pool2()]
+    layers += [_fc(rng, 9 * 7 * 24, 30), RELU, _fc(rng, 30, 6)]
+    queries = []
+    for k in range(3):
+        x = rng.uniform(0, 1, shape)
+        e = np.zeros(shape)
+        e[k::3, ::2, :] = 0.01                      # a third of the rows, every other pixel column
+        e[0, 0, :] = e[-1, -1, :] = e[0, -1, :] = e[-1, 0, :] = 0.01
+        queries.append({"lb": np.maximum(x - e, 0), "ub": np.minimum(x + e, 1)})
+    net = Network(ctx, layers, shape)
+    b = Batch(net, queries)
+    b.upload()
+    b.reach(keep_layer_bounds=True)
+    for q, qu in enumerate(queries):
+        S = O.reach(layers, O.star_from_query(qu))
+        V = b.get_V(q)
+        assert V.shape == S.V.shape and _rel(V, S.V) < TOL
+        for li, t in enumerate(S.trace):
+            idx, _, _ = b.get_crossing(q, li)
+            assert np.array_equal(idx, t["cross"])
+            ll, lu = b.get_layer_ranges(q, li, t["N"])
+            bscale = max(np.abs(t["lb"]).max(), np.abs(t["ub"]).max())
+            assert np.abs(ll - t["lb"]).max() / bscale < TOL and np.abs(lu - t["ub"]).max() / bscale < TOL
+    b.close()
+    net.close()
+
+
 def test_capacity_error_is_reported_not_fatal():
     from nnv_b200._lib import NNVError, NNVB_E_CAPACITY
     from nnv_b200.engine import Context
