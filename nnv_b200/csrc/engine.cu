@@ -1498,7 +1498,7 @@ int witness_forward(nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, i
             NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, RowMask{nullptr, nullptr, 0, 0}, ColWindows{nullptr, 0, 0}, 0, cur, ld, oth, ld_out, n, n, &ctx->launches));
             std::swap(cur, oth); N = Nout; ld = ld_out;
         } else if (L.type == NNVB_LAYER_FC) {
-            if (n <= 96) {
+            if (n <= 512) {      // too few columns to fill the GPU with 128-column tiles: slice the contraction instead
                 const int In = int(L.H * L.W * L.C);
                 NNVB_TRY(b->wk->tmp.ensure(sizeof(double) * fc_skinny_scratch_doubles(In, int(L.Co), n), st));
                 NNVB_TRY(launch_fc_skinny(st, In, int(L.Co), L.fc_wt, L.fc_ldw, L.bias, cur, ld, oth, ld_out, n,
