@@ -323,10 +323,13 @@ conv_onehot_kernel(ConvGeom g, const double* __restrict__ Wg, int bn_tile, int c
     const int org_h = ah >= 0 ? (ah + g.sh - 1) / g.sh : -((-ah) / g.sh);
     const int org_w = aw >= 0 ? (aw + g.sw - 1) / g.sw : -((-aw) / g.sw);
     double* dst = Vout + t * ld_out;
+    // patch rows fastest: the lanes of one (patch column, channel) write consecutive addresses
     for (int e = threadIdx.x; e < wh * ww * g.Cout; e += blockDim.x) {
-        const int co = e % g.Cout;
-        const int pos = e / g.Cout;
-        const int oh = org_h + pos % wh, ow = org_w + pos / wh;
+        const int ohl = e % wh;
+        const int e2 = e / wh;
+        const int co = e2 % g.Cout;
+        const int owl = e2 / g.Cout;
+        const int oh = org_h + ohl, ow = org_w + owl;
         if (oh < 0 || ow < 0 || oh >= g.Ho || ow >= g.Wo) continue;
         // the tap that maps output (oh, ow) to input (h, w), if there is one
         const int dh_ = h + g.pad_t - oh * g.sh, dw_ = w + g.pad_l - ow * g.sw;

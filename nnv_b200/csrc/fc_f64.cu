@@ -293,26 +293,47 @@ __global__ void fcg_hist_kernel(int64_t col0, int64_t n, const int4* __restrict_
     if (t < n) atomicAdd(hist + fcg_key(box[col0 + t], wh, ww, KH, nbins), 1);
 }
 
-// one thread: bin offsets and the tile table (a tile = up to tile_cols columns of one bin)
-__global__ void fcg_tiles_kernel(int nbins, int tile_cols, const int32_t* __restrict__ hist, int32_t* __restrict__ bin_start,
-                                 int32_t* __restrict__ cursor, int32_t* __restrict__ tile_key,
-                                 int32_t* __restrict__ tile_start, int32_t* __restrict__ tile_count,
-                                 int32_t* __restrict__ n_tiles) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
-    int off = 0, nt = 0;
-    for (int b = 0; b < nbins; ++b) {
-        bin_start[b] = off;
-        cursor[b] = 0;
-        const int cnt = hist[b];
-        for (int s0 = 0; s0 < cnt; s0 += tile_cols) {
-            tile_key[nt] = b;
-            tile_start[nt] = off + s0;
-            tile_count[nt] = cnt - s0 < tile_cols ? cnt - s0 : tile_cols;
-            ++nt;
+// bin offsets and the tile table (a tile = up to tile_cols columns of one bin)
+__global__ void __launch_bounds__(1024)
+fcg_tiles_kernel(int nbins, int tile_cols, const int32_t* __restrict__ hist, int32_t* __restrict__ bin_start,
+                 int32_t* __restrict__ cursor, int32_t* __restrict__ tile_key,
+                 int32_t* __restrict__ tile_start, int32_t* __restrict__ tile_count,
+                 int32_t* __restrict__ n_tiles) {
+    // one block: exclusive scans of the bins' column counts and tile counts (1024 bins per round, carried on)
+    __shared__ int wsum_c[32], wsum_t[32];
+    __shared__ int carry_c, carry_t;
+    if (threadIdx.x == 0) { carry_c = 0; carry_t = 0; }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int base = 0; base < nbins; base += 1024) {
+        const int b = base + threadIdx.x;
+        const int cnt = b < nbins ? hist[b] : 0;
+        const int nt = (cnt + tile_cols - 1) / tile_cols;
+        int ic = cnt, it = nt;
+        for (int o = 1; o < 32; o <<= 1) {
+            const int xc = __shfl_up_sync(0xffffffffu, ic, o), xt = __shfl_up_sync(0xffffffffu, it, o);
+            if (lane >= o) { ic += xc; it += xt; }
         }
-        off += cnt;
+        if (lane == 31) { wsum_c[warp] = ic; wsum_t[warp] = it; }
+        __syncthreads();
+        int off = carry_c, t0 = carry_t;
+        for (int w = 0; w < warp; ++w) { off += wsum_c[w]; t0 += wsum_t[w]; }
+        off += ic - cnt;
+        t0 += it - nt;
+        if (b < nbins) {
+            bin_start[b] = off;
+            cursor[b] = 0;
+            for (int k = 0; k < nt; ++k) {
+                tile_key[t0 + k] = b;
+                tile_start[t0 + k] = off + k * tile_cols;
+                tile_count[t0 + k] = min(tile_cols, cnt - k * tile_cols);
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 1023) { carry_c = off + cnt; carry_t = t0 + nt; }
+        __syncthreads();
     }
-    *n_tiles = nt;
+    if (threadIdx.x == 0) *n_tiles = carry_t;
 }
 
 __global__ void fcg_scatter_kernel(int64_t col0, int64_t n, const int4* __restrict__ box, int wh, int ww, int KH,
@@ -484,7 +505,7 @@ int launch_fc_gather(cudaStream_t st, int H, int W, int C, int wh, int ww, int O
     int32_t* perm = n_tiles + 8;
     NNVB_CUDA(cudaMemsetAsync(hist, 0, sizeof(int32_t) * nbins, st));
     fcg_hist_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(col0, n, box, wh, ww, KH, nbins, hist);
-    fcg_tiles_kernel<<<1, 32, 0, st>>>(nbins, FCG_BM, hist, bin_start, cursor, tile_key, tile_start, tile_count, n_tiles);
+    fcg_tiles_kernel<<<1, 1024, 0, st>>>(nbins, FCG_BM, hist, bin_start, cursor, tile_key, tile_start, tile_count, n_tiles);
     fcg_scatter_kernel<<<(unsigned)ceil_div(n, 256), 256, 0, st>>>(col0, n, box, wh, ww, KH, nbins, bin_start, cursor, perm);
     const int Kt = C * wh * ww;
     const int Kt_pad = (int)round_up(Kt, FC_BK);
