@@ -326,6 +326,29 @@ def run_ours(args):
                     "note": "dense algorithmic flops of the step (columns counted as full images) over the family's "
                             "time; above 1 because products with structural zeros are skipped, not executed"}
 
+        # ReLU step (Star.estimateRanges + classification + relaxation): bytes of the windows actually moved
+        # over the time of the two families, and the dense-layout figure (V read once, cleared rows and new
+        # one-hot columns written) that the windows and the work left to the next layer avoid
+        relu_ms = (prof["ranges"]["ms"] + prof["relax"]["ms"]) / K
+        # executed: the windows read by the bound reduction, lb/ub written and read back by the relaxation,
+        # the predicate bounds of the new columns (rows are not cleared and one-hot columns not written here)
+        relu_bytes = prof["ranges"]["work"] / K + sum(16.0 * s_["N"] * B + 16.0 * s_["n_cross"] for s_ in stats)
+        dense_relu = 0.0
+        for i, s_ in enumerate(stats):
+            cin, n = cols_seg[i], s_["N"]
+            dense_relu += 8.0 * n * cin + 16.0 * (cin - B) + 16.0 * n * B                      # estimateRanges
+            dense_relu += 16.0 * n * B + 8.0 * (s_["n_dead"] + s_["n_cross"]) * cin / B + 8.0 * n * s_["n_cross"] \
+                + 16.0 * s_["n_cross"]                                                          # relaxation
+        relu_step = {"bound": "hbm", "achieved": relu_bytes / (relu_ms * 1e-3) / 1e9 if relu_ms > 0 else 0.0,
+                     "peak": hbm_peak, "unit": "GB/s", "peak_source": hbm_src, "ms_per_step": relu_ms,
+                     "dense_equivalent": {"achieved": dense_relu / (relu_ms * 1e-3) / 1e9 if relu_ms > 0 else 0.0,
+                                          "unit": "GB/s",
+                                          "note": "dense-layout bytes of the step over the same time; above the "
+                                                  "copy rate because zero windows are skipped, cleared rows are "
+                                                  "masked by the next layer and one-hot columns stay implicit"}}
+        relu_step["frac"] = relu_step["achieved"] / hbm_peak
+        relu_step["dense_equivalent"]["frac"] = relu_step["dense_equivalent"]["achieved"] / hbm_peak
+
         # the roofline entry is the kernel family with the largest share of the timed region
         dominant = max(kernels, key=lambda k: prof[k]["ms"])
         line = {
@@ -344,6 +367,7 @@ def run_ours(args):
             "roofline": dict(roof(dominant), **({"dense_equivalent": dense_equiv(dominant)} if dominant in dense else {})),
             "roofline_other": {k: dict(roof(k), **({"dense_equivalent": dense_equiv(k)} if k in dense else {}))
                                for k in kernels if k != dominant},
+            "relu_step": relu_step,
             "family_ms_per_step": {k: v["ms"] / K for k, v in prof.items()},
         }
         if world == 1 and not args.no_cpu_baseline:
