@@ -236,9 +236,15 @@ int nnvb_batch_get_layer_ranges(nnvb_batch* b, int q, int relu_layer, double* lb
  * device-side tests could not settle; the caller finishes it with the
  * feasibility LP of Star.isEmptySet (Star.m:1216-1232).
  *
- * Two device-side tests run per halfspace row G_h x <= g_h:
+ * Device-side tests per halfspace row G_h x <= g_h:
  *   - the minimum of G_h x - g_h over the output set's predicate box; a
  *     positive minimum proves the intersection empty (NNVB_VERDICT_EMPTY);
+ *   - after a reach with opts.keep_constraints, a tighter lower bound of the
+ *     row over the whole set: every ReLU predicate is replaced, last layer
+ *     first, through its own relaxation rows (PosLin.m:716-735) by the affine
+ *     form of its pre-activation, and the row left over the input predicates
+ *     is minimised over their box; positive proves the intersection empty and
+ *     is returned as the margin;
  *   - a witness: a point of the output set (input predicates at a corner of
  *     their box, each ReLU predicate at the lower envelope max(0,x) or on the
  *     chord of its triangle, whichever lowers the row) evaluated by a forward
