@@ -417,6 +417,12 @@ class NN:
     def _layer_dicts(self):
         return [l if isinstance(l, dict) else l._desc() for l in self.Layers]
 
+    def close(self):
+        """Release the device copies of the weights (before the context they live in is closed)."""
+        for n in self._nets.values():
+            n.close()
+        self._nets = {}
+
     def _network(self, shape):
         shape = tuple(int(x) for x in shape)
         if shape not in self._nets:
@@ -509,7 +515,22 @@ class NN:
         non-empty.  Host side, only for queries still undecided: the feasibility
         LP of Star.isEmptySet on the open rows, on the constraint system of that
         query re-reached with constraint records kept."""
-        b = self.reach_batch(inputSets, reachOptions, keep_layer_bounds=True)
+        try:
+            b = self.reach_batch(inputSets, reachOptions, keep_layer_bounds=True)
+        except L.NNVError as e:
+            if e.status != L.NNVB_E_CAPACITY or len(inputSets) < 2:
+                raise
+            # the generator tensors of the whole list do not fit the context's arena: two halves, one after the other
+            h = len(inputSets) // 2
+            parts, part_stats = [], []
+            for sl in (slice(0, h), slice(h, None)):
+                st = {} if stats is not None else None
+                parts.append(self.verify_robustness_batch(inputSets[sl], reachOptions, list(targets[sl]), class_type, st))
+                part_stats.append(st)
+            if stats is not None:
+                for k in set(part_stats[0]) | set(part_stats[1]):
+                    stats[k] = part_stats[0].get(k, 0) + part_stats[1].get(k, 0)
+            return np.concatenate(parts)
         t0 = np.asarray(targets, dtype=np.int64) - 1
         verdict, status, _ = b.verify_robust(t0, class_type)
         result = np.where(verdict == L.VERDICT_EMPTY, 1, np.where(verdict == L.VERDICT_NONEMPTY, 2, 0)).astype(np.int64)

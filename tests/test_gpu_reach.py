@@ -342,6 +342,30 @@ def test_windowed_convolution_with_ragged_channel_counts(ctx):
     net.close()
 
 
+def test_verification_of_a_list_that_exceeds_the_arena_is_split():
+    """verify_robustness_batch halves the list when the generator tensors of all sets do not fit the arena."""
+    from nnv_b200.engine import Context
+    cfg = make_config("cnn28", n_queries=12)
+    sets = [nn.ImageStar(qu["lb"], qu["ub"]) for qu in cfg["queries"]]
+    targets = [qu["target"] + 1 for qu in cfg["queries"]]
+    big = Context(0, 2 << 30)
+    ref_stats = {}
+    ref_model = nn.NN(cfg["layers"], ctx=big)
+    ref = ref_model.verify_robustness_batch(sets, {"reachMethod": "approx-star"}, targets, "max", ref_stats)
+    ref_model.close()
+    big.close()
+    small = Context(0, 160 << 20)                    # room for a few of the twelve sets at a time
+    model = nn.NN(cfg["layers"], ctx=small)
+    with pytest.raises(Exception):
+        model.reach_batch(sets, {"reachMethod": "approx-star"})
+    stats = {}
+    got = model.verify_robustness_batch(sets, {"reachMethod": "approx-star"}, targets, "max", stats)
+    assert np.array_equal(got, ref)
+    assert stats["n_prefilter"] == ref_stats["n_prefilter"] and stats["n_witness"] == ref_stats["n_witness"]
+    model.close()
+    small.close()
+
+
 def test_capacity_error_is_reported_not_fatal():
     from nnv_b200._lib import NNVError, NNVB_E_CAPACITY
     from nnv_b200.engine import Context
