@@ -357,6 +357,100 @@ class ReluLayer(_Layer):
         return {"type": "relu"}
 
 
+class ImageInputLayer(_Layer):
+    """ImageInputLayer.m:14-46 (properties, constructor) and :121-168 (reach_star_single_input): the
+    normalisation of the input set.  It is an affine map of the input image with a positive scale, applied to
+    the set on the host before upload (generators scaled, offsets added to the centre; for a set given by
+    bounds, the bounds are mapped).  Must be the first layer."""
+
+    def __init__(self, InputSize=None, Normalization="none", Mean=None, StandardDeviation=None, Min=None, Max=None,
+                 Name="ImageInputLayer"):
+        if Normalization not in ("none", "zerocenter", "zscore", "rescale-zero-one", "rescale-symmetric"):
+            raise ValueError("The normalization method is not supported yet.")
+        self.InputSize, self.Normalization, self.Name = InputSize, Normalization, Name
+        self.Mean, self.StandardDeviation, self.Min, self.Max = Mean, StandardDeviation, Min, Max
+
+    @staticmethod
+    def _arr(x):
+        a = np.asarray(x, dtype=np.float64)
+        return a.reshape(a.shape + (1,) * (3 - a.ndim)) if a.ndim < 3 else a
+
+    def _steps(self):
+        """[(kind, value)] in the reference's order: 'add' touches the centre only, 'mul' / 'div' every slice."""
+        n = self.Normalization
+        if n == "none":
+            return []
+        if n == "zerocenter":
+            return [("add", -self._arr(self.Mean))]
+        if n == "zscore":
+            std = np.asarray(self.StandardDeviation, dtype=np.float64).reshape(1, 1, -1)
+            return [("add", -self._arr(self.Mean)), ("div", std)]
+        have = self.Min is not None and self.Max is not None
+        if n == "rescale-zero-one":
+            return [("add", -self._arr(self.Min)), ("mul", 1.0 / (float(self.Max) - float(self.Min)))] if have \
+                else [("mul", 1 / 255)]
+        if have:
+            return [("add", -self._arr(self.Min)), ("mul", 2.0 / (float(self.Max) - float(self.Min))), ("add", -1.0)]
+        return [("mul", 2 / 255), ("add", -1.0)]
+
+    def apply(self, s):
+        """The normalised copy of an input ImageStar."""
+        if not isinstance(s, ImageStar):
+            raise TypeError("Input is not an ImageStar")
+        steps = self._steps()
+        if not steps:
+            return s
+        if s.im_lb is not None and s._V is None:          # given by bounds: map the bounds (the scale is positive)
+            lb, ub = s.im_lb, s.im_ub
+            for kind, v in steps:
+                if kind == "add":
+                    lb, ub = lb + v, ub + v
+                elif kind == "mul":
+                    lb, ub = lb * v, ub * v
+                else:
+                    lb, ub = lb / v, ub / v
+            return ImageStar(lb, ub)
+        V = np.array(s.V, dtype=np.float64, copy=True)
+        for kind, v in steps:
+            if kind == "add":
+                V[..., 0] = V[..., 0] + v
+            elif kind == "mul":
+                V = V * v
+            else:
+                V = V / v[..., None]
+        return ImageStar(V, s.C, s.d, s.pred_lb, s.pred_ub)
+
+    def _desc(self):
+        return {"type": "imageinput"}
+
+
+class FlattenLayer(_Layer):
+    """FlattenLayer.m:105-164 — reshape of an H x W x C image into a vector.  The plain MATLAB type keeps the
+    column-major order (nothing to do on the device: FC layers consume that order); the Keras C-style and
+    ONNX types permute first, which is folded into the columns of the FullyConnectedLayer that follows."""
+
+    TYPES = ("nnet.cnn.layer.FlattenLayer", "nnet.keras.layer.FlattenCStyleLayer", "nnet.onnx.layer.FlattenLayer",
+             "nnet.onnx.layer.FlattenInto2dLayer", "nnet.onnx.layer.Flatten3dInto2dLayer")
+
+    def __init__(self, Name="flatten", Type="nnet.cnn.layer.FlattenLayer"):
+        if Type not in self.TYPES:
+            raise ValueError("Unknown type of flatten layer")
+        self.Name, self.Type = Name, Type
+
+    def source_index(self, shape):
+        """Column-major position in the H x W x C image of every entry of the flattened vector."""
+        h, w, c = shape
+        idx = np.arange(h * w * c).reshape((h, w, c), order="F")
+        if self.Type == "nnet.cnn.layer.FlattenLayer":
+            return idx.reshape(-1, order="F")
+        if self.Type == "nnet.keras.layer.FlattenCStyleLayer":
+            return np.transpose(idx, (2, 1, 0)).reshape(-1, order="F")
+        return np.transpose(idx, (1, 0, 2)).reshape(-1, order="F")
+
+    def _desc(self):
+        return {"type": "flatten", "kind": self.Type}
+
+
 def _set_shape(s):
     if isinstance(s, ImageStar):
         return (s.height, s.width, s.numChannel)
@@ -414,8 +508,39 @@ class NN:
         self.input_shape = tuple(input_shape) if input_shape is not None else None
         self.exactReach = False          # approx methods never promote unknown -> not robust (NN.m:539-543)
 
-    def _layer_dicts(self):
-        return [l if isinstance(l, dict) else l._desc() for l in self.Layers]
+    def _layer_dicts(self, shape=None):
+        """Neutral layer dicts for the device.  An ImageInputLayer (first layer only) is applied to the input
+        sets on the host; a FlattenLayer moves no data: the plain type is the device's own order, the
+        permuting types are folded into the weight columns of the FullyConnectedLayer right behind them."""
+        from .configs import out_shape
+        out = []
+        pending = None                       # permutation of a flatten layer waiting for its FC layer
+        for i, l in enumerate(self.Layers):
+            d = l if isinstance(l, dict) else l._desc()
+            if d["type"] == "imageinput":
+                if i != 0:
+                    raise NotImplementedError("an ImageInputLayer is supported as the first layer only")
+                continue
+            if d["type"] == "flatten":
+                if d["kind"] != "nnet.cnn.layer.FlattenLayer":
+                    if shape is None:
+                        raise ValueError("the input shape is needed to fold a permuting FlattenLayer")
+                    pending = FlattenLayer(Type=d["kind"]).source_index(shape)
+                continue
+            if pending is not None:
+                if d["type"] != "fc":
+                    raise NotImplementedError("a permuting FlattenLayer must be followed by a FullyConnectedLayer")
+                W = np.asarray(d["W"], dtype=np.float64)
+                Wp = np.empty_like(W)
+                Wp[:, pending] = W           # flattened entry k reads image entry pending[k]
+                d = dict(d, W=np.asfortranarray(Wp))
+                pending = None
+            out.append(d)
+            if shape is not None:
+                shape = out_shape([d], shape)
+        if pending is not None:
+            raise NotImplementedError("a permuting FlattenLayer must be followed by a FullyConnectedLayer")
+        return out
 
     def close(self):
         """Release the device copies of the weights (before the context they live in is closed)."""
@@ -426,19 +551,28 @@ class NN:
     def _network(self, shape):
         shape = tuple(int(x) for x in shape)
         if shape not in self._nets:
-            self._nets[shape] = Network(self.ctx or default_context(), self._layer_dicts(), shape)
+            self._nets[shape] = Network(self.ctx or default_context(), self._layer_dicts(shape), shape)
         return self._nets[shape]
 
     @property
     def OutputSize(self):
-        last = [l for l in self._layer_dicts() if l["type"] == "fc"]
-        return last[-1]["W"].shape[0] if last else 0
+        for l in reversed(self.Layers):
+            d = l if isinstance(l, dict) else l._desc()
+            if d["type"] == "fc":
+                return d["W"].shape[0]
+        return 0
 
     # -- reach -----------------------------------------------------------------
     def reach_batch(self, inputSets, reachOptions=None, keep_constraints=False, keep_layer_bounds=False):
         """Push a list of input sets through the network together; returns the Batch
         (device-resident results).  Array-of-sets form of NN.reach."""
         _validate_reach_options(reachOptions)
+        first = self.Layers[0] if self.Layers else None
+        if isinstance(first, dict) and first.get("type") == "imageinput":
+            first = ImageInputLayer(None, first.get("normalization", "none"), first.get("mean"), first.get("std"),
+                                    first.get("min"), first.get("max"))
+        if isinstance(first, ImageInputLayer):
+            inputSets = [first.apply(s) for s in inputSets]      # ImageInputLayer.m:121-168, on the host
         shape = _set_shape(inputSets[0])
         for s in inputSets:
             if _set_shape(s) != shape:

@@ -276,11 +276,78 @@ def relu_reach(S, keep_constraints=True):
 # network driver and verdict
 
 
+def image_input_reach(S, L):
+    """ImageInputLayer.reach_star_single_input, ImageInputLayer.m:121-168, with ImageStar.affineMap
+    (ImageStar.m:431-460: generators scaled, offset added to the centre).  L: {"normalization", "mean",
+    "std", "min", "max"} (the last four may be None)."""
+    V = S.V.copy()
+    norm = L.get("normalization", "none")
+
+    def arr(x):
+        a = np.asarray(x, dtype=np.float64)
+        return a.reshape(a.shape + (1,) * (3 - a.ndim)) if a.ndim < 3 else a
+
+    if norm == "none":
+        pass
+    elif norm == "zerocenter":
+        V[..., 0] = V[..., 0] + (-arr(L["mean"]))
+    elif norm == "zscore":
+        V[..., 0] = V[..., 0] + (-arr(L["mean"]))
+        std = np.asarray(L["std"], dtype=np.float64).ravel()
+        for nc in range(V.shape[2]):
+            V[:, :, nc, :] = V[:, :, nc, :] / std[nc if std.size > 1 else 0]
+    elif norm == "rescale-zero-one":
+        if L.get("min") is not None and L.get("max") is not None:
+            V[..., 0] = V[..., 0] + (-arr(L["min"]))
+            V = V * (1.0 / (float(L["max"]) - float(L["min"])))
+        else:
+            V = V * (1 / 255)
+    elif norm == "rescale-symmetric":
+        if L.get("min") is not None and L.get("max") is not None:
+            V[..., 0] = V[..., 0] + (-arr(L["min"]))
+            V = V * (2.0 / (float(L["max"]) - float(L["min"])))
+            V[..., 0] = V[..., 0] + (-1)
+        else:
+            V = V * (2 / 255)
+            V[..., 0] = V[..., 0] + (-1)
+    else:
+        raise ValueError("The normalization method is not supported yet.")
+    return ImageStar(V, S.C, S.d, S.pl, S.pu, S.trace)
+
+
+def flatten_order(shape, kind):
+    """Source index (column-major position in the H x W x C image) of every entry of the flattened vector,
+    FlattenLayer.evaluate, FlattenLayer.m:105-164.  'nnet.cnn.layer.FlattenLayer' is a plain reshape;
+    'nnet.keras.layer.FlattenCStyleLayer' permutes [3 2 1] first, the ONNX types [2 1 3]."""
+    h, w, c = shape
+    idx = np.arange(h * w * c).reshape((h, w, c), order="F")
+    if kind == "nnet.cnn.layer.FlattenLayer":
+        return idx.reshape(-1, order="F")
+    if kind == "nnet.keras.layer.FlattenCStyleLayer":
+        return np.transpose(idx, (2, 1, 0)).reshape(-1, order="F")
+    if kind in ("nnet.onnx.layer.FlattenLayer", "nnet.onnx.layer.FlattenInto2dLayer",
+                "nnet.onnx.layer.Flatten3dInto2dLayer"):
+        return np.transpose(idx, (1, 0, 2)).reshape(-1, order="F")
+    raise ValueError("Unknown type of flatten layer")
+
+
+def flatten_reach(S, L):
+    """FlattenLayer.reach_single_input (FlattenLayer.m:172-183): evaluate applied to every slice of V;
+    the result is a 1 x 1 x N ImageStar."""
+    src = flatten_order(S.shape, L["kind"])
+    M = S.mat()[src, :]
+    return ImageStar(M.reshape((1, 1, M.shape[0], M.shape[1]), order="F"), S.C, S.d, S.pl, S.pu, S.trace)
+
+
 def reach(layers, S, keep_constraints=True):
     """NN.reach_noConns layer loop, NN.m:1529-1551."""
     for L in layers:
         t = L["type"]
-        if t == "conv2d":
+        if t == "imageinput":
+            S = image_input_reach(S, L)
+        elif t == "flatten":
+            S = flatten_reach(S, L)
+        elif t == "conv2d":
             S = conv2d_reach(S, L)
         elif t == "fc":
             S = fc_reach(S, L)

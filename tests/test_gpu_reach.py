@@ -366,6 +366,35 @@ def test_verification_of_a_list_that_exceeds_the_arena_is_split():
     small.close()
 
 
+def test_image_input_and_flatten_layers_around_the_path(ctx):
+    """A network as an importer would hand it over: ImageInputLayer (zscore), convolution, ReLU, pooling, a
+    Keras C-style FlattenLayer and two FC layers, against the oracle's own restatement of those layers."""
+    from nnv_b200.configs import _conv, _fc, _pool2, RELU
+    rng = np.random.default_rng(13)
+    shape = (12, 10, 3)
+    mean = rng.uniform(0.3, 0.6, shape)
+    std = [0.2, 0.25, 0.3]
+    conv = _conv(rng, 3, 3, 3, 8, (1, 1, 1, 1))
+    fc1, fc2 = _fc(rng, 6 * 5 * 8, 20), _fc(rng, 20, 4)
+    kind = "nnet.keras.layer.FlattenCStyleLayer"
+    oracle_layers = [{"type": "imageinput", "normalization": "zscore", "mean": mean, "std": std}, conv, RELU, _pool2(),
+                     {"type": "flatten", "kind": kind}, fc1, RELU, fc2]
+    model = nn.NN([nn.ImageInputLayer(shape, "zscore", Mean=mean, StandardDeviation=std),
+                   nn.Conv2DLayer(conv["W"], conv["b"], conv["pad"], conv["stride"], conv["dilation"]), nn.ReluLayer(),
+                   nn.AveragePooling2DLayer((2, 2), (2, 2)), nn.FlattenLayer(Type=kind),
+                   nn.FullyConnectedLayer(fc1["W"], fc1["b"]), nn.ReluLayer(), nn.FullyConnectedLayer(fc2["W"], fc2["b"])],
+                  ctx=ctx)
+    for _ in range(2):
+        x = rng.uniform(0, 1, shape)
+        lb, ub = np.maximum(x - 0.01, 0), np.minimum(x + 0.01, 1)
+        S = O.reach(oracle_layers, O.star_from_bounds(lb, ub))
+        R = model.reach(nn.ImageStar(lb, ub), {"reachMethod": "approx-star"})
+        assert R.numPred == S.P
+        assert _rel(R.V.reshape(S.V.shape, order="F"), S.V) < TOL
+        assert _rel(R.C, S.C.toarray()) < TOL
+    model.close()
+
+
 def test_capacity_error_is_reported_not_fatal():
     from nnv_b200._lib import NNVError, NNVB_E_CAPACITY
     from nnv_b200.engine import Context

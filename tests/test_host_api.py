@@ -106,3 +106,52 @@ def test_config_shapes():
     cfg = make_config("cnn32", n_queries=1)
     fc = [l for l in cfg["layers"] if l["type"] == "fc"][0]
     assert fc["W"].shape == (256, 4096)
+
+
+def test_flatten_layer_types_fold_into_the_next_fc_layer():
+    """FlattenLayer.m:105-164: the plain type is the column-major order itself, the Keras C-style and ONNX
+    types permute first; the host folds the permutation into the FC weight columns."""
+    rng = np.random.default_rng(0)
+    shape = (4, 3, 2)
+    x = rng.standard_normal(shape)
+    S = O.star_from_bounds(x - 0.1, x + 0.1)
+    for kind in nn.FlattenLayer.TYPES:
+        W, b = rng.standard_normal((5, 24)), rng.standard_normal(5)
+        ref = O.reach([{"type": "flatten", "kind": kind}, {"type": "fc", "W": W, "b": b}], S)
+        folded = nn.NN([nn.FlattenLayer(Type=kind), nn.FullyConnectedLayer(W, b)])._layer_dicts(shape)
+        assert [d["type"] for d in folded] == ["fc"]
+        got = O.reach(folded, S)
+        assert np.abs(got.mat() - ref.mat()).max() < 1e-13
+    # the evaluate semantics of the permuting types on a concrete image (MATLAB permute + reshape)
+    img = np.arange(24.0).reshape(shape, order="F")
+    keras = nn.FlattenLayer(Type="nnet.keras.layer.FlattenCStyleLayer").source_index(shape)
+    assert np.array_equal(img.reshape(-1, order="F")[keras], np.transpose(img, (2, 1, 0)).reshape(-1, order="F"))
+    assert np.array_equal(img.reshape(-1, order="F")[keras], img.reshape(-1, order="C"))      # C-style order
+    with pytest.raises(NotImplementedError):
+        nn.NN([nn.FlattenLayer(Type="nnet.keras.layer.FlattenCStyleLayer"), nn.ReluLayer()])._layer_dicts(shape)
+    with pytest.raises(ValueError):
+        nn.FlattenLayer(Type="something else")
+
+
+def test_image_input_layer_normalisations_match_the_oracle():
+    """ImageInputLayer.m:121-168 on a set given by bounds and on a set given by V."""
+    rng = np.random.default_rng(1)
+    shape = (3, 4, 2)
+    x = rng.uniform(0, 255, shape)
+    lb, ub = x - 2.0, x + 2.0
+    S = O.star_from_bounds(lb, ub)
+    mean = rng.uniform(100, 150, shape)
+    cases = [("none", {}), ("zerocenter", {"Mean": mean}), ("zscore", {"Mean": mean, "StandardDeviation": [50.0, 60.0]}),
+             ("rescale-zero-one", {}), ("rescale-zero-one", {"Min": 10.0, "Max": 240.0}),
+             ("rescale-symmetric", {}), ("rescale-symmetric", {"Min": 10.0, "Max": 240.0})]
+    for norm, kw in cases:
+        L = nn.ImageInputLayer(shape, norm, **kw)
+        ref = O.image_input_reach(S, {"normalization": norm, "mean": kw.get("Mean"), "std": kw.get("StandardDeviation"),
+                                      "min": kw.get("Min"), "max": kw.get("Max")})
+        by_bounds = L.apply(nn.ImageStar(lb, ub))
+        got = O.star_from_bounds(by_bounds.im_lb, by_bounds.im_ub) if norm != "none" else S
+        assert np.abs(got.V - ref.V).max() <= 1e-12 * np.abs(ref.V).max()
+        by_V = L.apply(nn.ImageStar(S.V, S.C.toarray(), S.d, S.pl, S.pu))
+        assert np.abs(by_V.V - ref.V).max() <= 1e-12 * np.abs(ref.V).max()
+    with pytest.raises(ValueError):
+        nn.ImageInputLayer(shape, "zerophase")
