@@ -57,8 +57,10 @@ struct Err {
     bool set = false;
     void fail(const char* i, const std::string& m) { if (!set) { id = i; msg = m; set = true; } }
     void check(int status, const char* where) {
+        // a batch that does not fit the arena gets its own identifier: the caller can split the list and retry
         if (status != NNVB_OK)
-            fail("NNVB200:engine", std::string(where) + ": " + nnvb_strerror(status) + " - " + nnvb_last_error());
+            fail(status == NNVB_E_CAPACITY ? "NNVB200:capacity" : "NNVB200:engine",
+                 std::string(where) + ": " + nnvb_strerror(status) + " - " + nnvb_last_error());
     }
 };
 
