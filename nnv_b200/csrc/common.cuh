@@ -113,12 +113,18 @@ int launch_conv_f64(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, co
                     const RowMask& mask, const ColWindows& win, int64_t col_base, const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
                     int64_t ncols, int64_t n_center, int64_t* launches);
 
-// Images of the one-hot columns a ReLU step appended (column t of this rank is batch-wide column
-// c_first + t*c_step, the unit vector of neuron rec_idx[c]); written to Vout[ld_out x K_loc].
+// The one-hot columns a ReLU step appended and no layer has written to memory yet: column t of this rank
+// is scale[t] (1 where scale is null) times the unit vector of neuron idx[first + t*step].
+struct HotCols {
+    const int32_t* idx;
+    int64_t first, step;
+    const double* scale;
+};
+// Images of one-hot columns, written to Vout[ld_out x K_loc].
 // zero_fill: clear the whole output block first (else only the columns' output windows are written).
 int launch_conv_onehot(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
-                       const int32_t* rec_idx, int64_t c_first, int64_t c_step, int64_t K_loc, double* Vout,
-                       int64_t ld_out, bool zero_fill, int64_t* launches);
+                       const HotCols& hot, int64_t K_loc, double* Vout, int64_t ld_out, bool zero_fill,
+                       int64_t* launches);
 // Writes zero to every entry of columns [col0, col0+n) of V (an H x W x C image per column) that lies
 // outside the column's window box[col]: afterwards the columns can be read without window tests.
 int launch_zero_outside_windows(cudaStream_t st, int H, int W, int C, const int4* box, int64_t col0, int64_t n,
@@ -135,8 +141,8 @@ size_t fc_skinny_scratch_doubles(int In, int Out, int ncols);
 int launch_fc_skinny(cudaStream_t st, int In, int Out, const double* Wt, int ldw, const double* bias,
                      const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out, int ncols, double* scratch,
                      int64_t* launches);
-int launch_fc_onehot(cudaStream_t st, int Out, const double* Wt, int ldw, const int32_t* rec_idx, int64_t c_first,
-                     int64_t c_step, int64_t K_loc, double* Vout, int64_t ld_out, int64_t* launches);
+int launch_fc_onehot(cudaStream_t st, int Out, const double* Wt, int ldw, const HotCols& hot, int64_t K_loc,
+                     double* Vout, int64_t ld_out, int64_t* launches);
 
 // FC: Vout[Out x ncols] = W * Vin[In x ncols]; bias (and the optional affine) on
 // the first n_center columns.  Wt is the device copy arranged [In_pad][ldw]
@@ -158,9 +164,16 @@ struct PoolGeom {
 int launch_avgpool_f64(cudaStream_t st, const PoolGeom& g, const RowMask& mask, const int4* box, const double* Vin,
                        int64_t ld_in, double* Vout, int64_t ld_out, int64_t ncols, int64_t* launches);
 // zero_fill: clear the whole output block first (else only the columns' output windows are written).
-int launch_avgpool_onehot(cudaStream_t st, const PoolGeom& g, const int32_t* rec_idx, int64_t c_first,
-                          int64_t c_step, int64_t K_loc, double* Vout, int64_t ld_out, bool zero_fill,
-                          int64_t* launches);
+int launch_avgpool_onehot(cudaStream_t st, const PoolGeom& g, const HotCols& hot, int64_t K_loc, double* Vout,
+                          int64_t ld_out, bool zero_fill, int64_t* launches);
+// Pooling with windows that tile the image exactly (pool size = stride, no padding, H and W multiples of
+// it) maps a scaled one-hot column to a scaled one-hot column: neuron (h, w, c) -> (h/sh, w/sw, c), scale
+// -> (0 + scale) / (ph*pw), the value the pooling kernel computes for that column.  Writes the new neuron
+// and scale of every column to dst_idx / dst_scale (which may be hot.idx / hot.scale when first = 0, step = 1);
+// no column memory is touched.
+bool pool_keeps_onehot(const PoolGeom& g);
+int launch_pool_onehot_track(cudaStream_t st, const PoolGeom& g, const HotCols& hot, int64_t K_loc, int32_t* dst_idx,
+                             double* dst_scale, int64_t* launches);
 
 // ReLU approx-star step; see relu_star.cu.  All pointers are device pointers.
 // A cohort of windowed columns [col0, col0+n): every column is zero outside a wh x ww window.  The bound

@@ -304,14 +304,15 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
 // dense contraction of that column gives (every other term of its sums is a product with zero).
 // Every entry of the column's output window (origin and extent as update_windows_kernel derives them from
 // a 1x1 input window) is written, zeros included; nothing outside it is touched.  One block per column,
-// lanes over (window position, output channel); this rank's column t is the batch-wide column
-// c = c_first + t*c_step with neuron rec_idx[c].
+// lanes over (window position, output channel).  A column with a scale (a one-hot column that went through
+// a pooling layer) gives scale times the footprint: the one product its dense contraction would form.
 __global__ void __launch_bounds__(128)
 conv_onehot_kernel(ConvGeom g, const double* __restrict__ Wg, int bn_tile, int cs, int n_chunks, ChanAffine bn,
-                   const int32_t* __restrict__ rec_idx, int64_t c_first, int64_t c_step,
-                   double* __restrict__ Vout, int64_t ld_out) {
+                   HotCols hot, double* __restrict__ Vout, int64_t ld_out) {
     const int64_t t = blockIdx.x;
-    const int i = rec_idx[c_first + t * c_step];
+    const int i = hot.idx[hot.first + t * hot.step];
+    const bool scaled = hot.scale != nullptr;
+    const double sc = scaled ? hot.scale[t] : 1.0;
     const int h = i % g.H;
     const int w = (i / g.H) % g.W;
     const int ci = i / (g.H * g.W);
@@ -338,6 +339,7 @@ conv_onehot_kernel(ConvGeom g, const double* __restrict__ Wg, int bn_tile, int c
             const int tap = dh_ / g.dh + g.kh * (dw_ / g.dw);
             const int nt = co / bn_tile, n = co % bn_tile;
             v = Wg[((((int64_t(nt) * n_chunks + ch) * taps + tap) * KC + cil) * cs) + n];
+            if (scaled) v = v * sc;
             if (bn.rden != nullptr) v = (v * bn.rden[co]) * bn.scale[co];
         }
         dst[oh + int64_t(g.Ho) * (ow + int64_t(g.Wo) * co)] = v;
@@ -502,12 +504,12 @@ int launch_conv_f64(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, co
 }
 
 int launch_conv_onehot(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
-                       const int32_t* rec_idx, int64_t c_first, int64_t c_step, int64_t K_loc, double* Vout,
-                       int64_t ld_out, bool zero_fill, int64_t* launches) {
+                       const HotCols& hot, int64_t K_loc, double* Vout, int64_t ld_out, bool zero_fill,
+                       int64_t* launches) {
     if (K_loc <= 0) return NNVB_OK;
     if (zero_fill) NNVB_CUDA(cudaMemsetAsync(Vout, 0, sizeof(double) * ld_out * K_loc, st));
-    conv_onehot_kernel<<<(unsigned)K_loc, 128, 0, st>>>(g, w.w, w.bn_tile, w.cs, w.n_chunks, bn, rec_idx, c_first,
-                                                       c_step, Vout, ld_out);
+    conv_onehot_kernel<<<(unsigned)K_loc, 128, 0, st>>>(g, w.w, w.bn_tile, w.cs, w.n_chunks, bn, hot, Vout,
+                                                       ld_out);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;

@@ -90,8 +90,8 @@ __global__ void avgpool_f64_kernel(PoolGeom g, RowMask mask, const int4* __restr
 // position of channel c whose window covers (h,w).  Every entry of the column's output window (all
 // channels; origin and extent as update_windows_kernel derives them from a 1x1 input window) is written,
 // zeros included; nothing outside it is touched.  One thread per (column, window entry).
-__global__ void avgpool_onehot_kernel(PoolGeom g, const int32_t* __restrict__ rec_idx, int64_t c_first,
-                                      int64_t c_step, int64_t K_loc, double* __restrict__ Vout, int64_t ld_out) {
+__global__ void avgpool_onehot_kernel(PoolGeom g, HotCols hot, int64_t K_loc, double* __restrict__ Vout,
+                                      int64_t ld_out) {
     const int wh = (g.ph - 1) / g.sh + 1, ww = (g.pw - 1) / g.sw + 1;
     const int per_col = wh * ww * g.C;
     const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -101,7 +101,8 @@ __global__ void avgpool_onehot_kernel(PoolGeom g, const int32_t* __restrict__ re
     const int cc = r % g.C;            // channel fastest: the writes of a column spread over its channel planes
     r /= g.C;
     const int ohl = r % wh, owl = r / wh;
-    const int i = rec_idx[c_first + t * c_step];
+    const int i = hot.idx[hot.first + t * hot.step];
+    const double sc = hot.scale != nullptr ? hot.scale[t] : 1.0;
     const int h = i % g.H, w = (i / g.H) % g.W, c = i / (g.H * g.W);
     const int ah = h + g.pad_t - (g.ph - 1), aw = w + g.pad_l - (g.pw - 1);
     const int oh = (ah >= 0 ? (ah + g.sh - 1) / g.sh : -((-ah) / g.sh)) + ohl;
@@ -109,9 +110,22 @@ __global__ void avgpool_onehot_kernel(PoolGeom g, const int32_t* __restrict__ re
     if (oh < 0 || ow < 0 || oh >= g.Ho || ow >= g.Wo) return;
     const int h0 = oh * g.sh - g.pad_t, w0 = ow * g.sw - g.pad_l;
     const bool covers = cc == c && h >= h0 && h < h0 + g.ph && w >= w0 && w < w0 + g.pw;
-    // same arithmetic as the dense kernel on this column: a sum of zeros and a single one, then the division
-    const double val = covers ? (0.0 + 1.0) / double(g.ph * g.pw) : 0.0;
+    // same arithmetic as the dense kernel on this column: a sum of zeros and a single entry, then the division
+    const double val = covers ? (0.0 + sc) / double(g.ph * g.pw) : 0.0;
     Vout[t * ld_out + oh + int64_t(g.Ho) * (ow + int64_t(g.Wo) * cc)] = val;
+}
+
+// One-hot columns through a pooling layer whose windows tile the image: every neuron lies in exactly one
+// window, so the pooled column is again a single entry.  Only the column's neuron and scale are rewritten.
+__global__ void pool_onehot_track_kernel(PoolGeom g, HotCols hot, int64_t K_loc, int32_t* __restrict__ dst_idx,
+                                         double* __restrict__ dst_scale) {
+    const int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= K_loc) return;
+    const int i = hot.idx[hot.first + t * hot.step];
+    const double sc = hot.scale != nullptr ? hot.scale[t] : 1.0;
+    const int h = i % g.H, w = (i / g.H) % g.W, c = i / (g.H * g.W);
+    dst_idx[t] = h / g.sh + g.Ho * (w / g.sw + g.Wo * c);
+    dst_scale[t] = (0.0 + sc) / double(g.ph * g.pw);
 }
 
 // Number of generators of ImageStar(lb,ub): entries with ub != lb (Box.m:36-43).
@@ -356,14 +370,25 @@ int launch_bn_f64(cudaStream_t st, const ChanAffine& bn, int64_t plane, int64_t 
     return NNVB_OK;
 }
 
-int launch_avgpool_onehot(cudaStream_t st, const PoolGeom& g, const int32_t* rec_idx, int64_t c_first,
-                          int64_t c_step, int64_t K_loc, double* Vout, int64_t ld_out, bool zero_fill,
-                          int64_t* launches) {
+bool pool_keeps_onehot(const PoolGeom& g) {
+    return g.ph == g.sh && g.pw == g.sw && g.pad_t == 0 && g.pad_l == 0 && g.H == g.Ho * g.sh && g.W == g.Wo * g.sw;
+}
+
+int launch_pool_onehot_track(cudaStream_t st, const PoolGeom& g, const HotCols& hot, int64_t K_loc, int32_t* dst_idx,
+                             double* dst_scale, int64_t* launches) {
+    if (K_loc <= 0) return NNVB_OK;
+    pool_onehot_track_kernel<<<(unsigned)ceil_div(K_loc, 256), 256, 0, st>>>(g, hot, K_loc, dst_idx, dst_scale);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_avgpool_onehot(cudaStream_t st, const PoolGeom& g, const HotCols& hot, int64_t K_loc, double* Vout,
+                          int64_t ld_out, bool zero_fill, int64_t* launches) {
     if (K_loc <= 0) return NNVB_OK;
     if (zero_fill) NNVB_CUDA(cudaMemsetAsync(Vout, 0, sizeof(double) * ld_out * K_loc, st));
     const int64_t per_col = int64_t((g.ph - 1) / g.sh + 1) * ((g.pw - 1) / g.sw + 1) * g.C;
-    avgpool_onehot_kernel<<<(unsigned)ceil_div(K_loc * per_col, 256), 256, 0, st>>>(g, rec_idx, c_first, c_step, K_loc,
-                                                                                   Vout, ld_out);
+    avgpool_onehot_kernel<<<(unsigned)ceil_div(K_loc * per_col, 256), 256, 0, st>>>(g, hot, K_loc, Vout, ld_out);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;

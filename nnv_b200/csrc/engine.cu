@@ -116,12 +116,13 @@ struct WorkBufs {
     DevBuf tmp;                          // gathers for downloads
     DevBuf fcg;                          // column grouping of the window-gathered FC
     DevBuf winsort;                      // origin bins and sorted columns of the windowed bound reduction
+    DevBuf hot_idx, hot_scale;           // neuron and scale of one-hot columns carried through a pooling layer
     DevBuf hs_G, hs_g, hs_q, hs_margin, hs_r, hs_roff, hs_val, hs_scale, hs_bound, wit[2];   // halfspace tests
     std::vector<std::unique_ptr<ReluLayerRecord>> relu;
     void release() {
         DevBuf* bufs[] = {&col_q, &pl, &pu, &col_pos, &box, &qcol_off[0], &qcol_off[1], &qcol_idx[0], &qcol_idx[1],
                           &chunk_beg, &chunk_end, &q_chunk_off, &partial, &sums, &lb, &ub, &state, &rank, &blk_cross,
-                          &q_cross, &q_dead, &q_new_off, &gen_off, &tmp, &fcg, &winsort, &hs_G, &hs_g, &hs_q, &hs_margin, &hs_r,
+                          &q_cross, &q_dead, &q_new_off, &gen_off, &tmp, &fcg, &winsort, &hot_idx, &hot_scale, &hs_G, &hs_g, &hs_q, &hs_margin, &hs_r,
                           &hs_roff, &hs_val, &hs_scale, &hs_bound, &wit[0], &wit[1]};
         for (DevBuf* d : bufs) d->release();
         for (auto& r : relu) r->release();
@@ -224,7 +225,8 @@ struct nnvb_batch {
     int64_t pend_mask_ncols = 0;         // > 0: rows with state != 0 of columns [0, n) read as zero
     int64_t pend_mask_N = 0;
     int64_t pend_onehot = 0;             // > 0: the last n columns are implicit unit vectors
-    ReluLayerRecord* pend_rec = nullptr; // ... of the neurons listed in this record
+    ReluLayerRecord* pend_rec = nullptr; // ... of the neurons listed in this record,
+    bool pend_scaled = false;            // ... or (after a pooling layer) of wk->hot_idx, times wk->hot_scale
     std::vector<int64_t> h_qcol_off;     // [nq+1]
     int64_t ncols = 0;
     int64_t N = 0, ld = 0;
@@ -1236,7 +1238,12 @@ int run_layers(nnvb_batch* b) {
             // columns the layer contracts densely, and the unit-vector columns whose images it writes directly
             const int64_t n_dense = b->ncols - b->pend_onehot;
             const int64_t n_hot = b->pend_onehot;
-            const int32_t* hot_idx = n_hot > 0 ? b->pend_rec->idx.as<int32_t>() : nullptr;
+            HotCols hot{nullptr, 0, 1, nullptr};
+            if (n_hot > 0 && b->pend_scaled)
+                hot = HotCols{b->wk->hot_idx.as<int32_t>(), 0, 1, b->wk->hot_scale.as<double>()};
+            else if (n_hot > 0)
+                hot = HotCols{b->pend_rec->idx.as<int32_t>(), ctx->rank, ctx->world, nullptr};
+            bool keep_hot = false;          // the one-hot columns stay unwritten past this layer
             RowMask mask{nullptr, nullptr, 0, 0};
             if (b->pend_mask_ncols > 0)
                 mask = RowMask{b->wk->state.as<uint8_t>(), b->wk->col_q.as<int32_t>(), b->pend_mask_ncols, b->pend_mask_N};
@@ -1283,8 +1290,8 @@ int run_layers(nnvb_batch* b) {
                     }
                 }
                 ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(lazy ? L.cg.kh * L.cg.kw * L.cg.Cout : Nout) * double(n_hot));
-                NNVB_TRY(launch_conv_onehot(st, L.cg, L.cw, bn, hot_idx, ctx->rank, ctx->world, n_hot,
-                                            out + n_dense * ld_out, ld_out, !lazy, &ctx->launches));
+                NNVB_TRY(launch_conv_onehot(st, L.cg, L.cw, bn, hot, n_hot, out + n_dense * ld_out, ld_out, !lazy,
+                                            &ctx->launches));
                 for (auto& co : b->cohorts)
                     if (co.col0 >= n_dense) co.clean = !lazy;
             } else if (L.type == NNVB_LAYER_FC) {
@@ -1319,8 +1326,8 @@ int run_layers(nnvb_batch* b) {
                     }
                 }
                 ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(Nout) * double(n_hot));
-                NNVB_TRY(launch_fc_onehot(st, int(L.Co), L.fc_wt, L.fc_ldw, hot_idx, ctx->rank, ctx->world, n_hot,
-                                          out + n_dense * ld_out, ld_out, &ctx->launches));
+                NNVB_TRY(launch_fc_onehot(st, int(L.Co), L.fc_wt, L.fc_ldw, hot, n_hot, out + n_dense * ld_out, ld_out,
+                                          &ctx->launches));
             } else {
                 for (auto& co : b->cohorts) {
                     const int64_t c1 = std::min(co.col1, n_dense);
@@ -1351,11 +1358,26 @@ int run_layers(nnvb_batch* b) {
                         co.clean = true;
                     }
                 }
-                ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(lazy ? L.pg.C : Nout) * double(n_hot));
-                NNVB_TRY(launch_avgpool_onehot(st, L.pg, hot_idx, ctx->rank, ctx->world, n_hot, out + n_dense * ld_out,
-                                               ld_out, !lazy, &ctx->launches));
-                for (auto& co : b->cohorts)
-                    if (co.col0 >= n_dense) co.clean = !lazy;
+                // pooling windows that tile the image send a one-hot column to a scaled one-hot column: when the
+                // next layer writes the images of such columns itself, only their neurons and scales change here
+                static const bool no_hot_pool = getenv("NNVB_NO_HOT_POOL") != nullptr;
+                const int nt = li + 1 < net->layers.size() ? net->layers[li + 1].type : 0;
+                keep_hot = n_hot > 0 && lazy && !no_hot_pool && pool_keeps_onehot(L.pg) &&
+                           (nt == NNVB_LAYER_CONV2D || nt == NNVB_LAYER_FC || nt == NNVB_LAYER_AVGPOOL2D);
+                if (keep_hot) {
+                    ProfScope ps(ctx, NNVB_PROF_ONEHOT, 24.0 * double(n_hot));
+                    NNVB_TRY(b->wk->hot_idx.ensure(sizeof(int32_t) * n_hot, st));
+                    NNVB_TRY(b->wk->hot_scale.ensure(sizeof(double) * n_hot, st));
+                    NNVB_TRY(launch_pool_onehot_track(st, L.pg, hot, n_hot, b->wk->hot_idx.as<int32_t>(),
+                                                      b->wk->hot_scale.as<double>(), &ctx->launches));
+                    b->pend_scaled = true;
+                } else {
+                    ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(lazy ? L.pg.C : Nout) * double(n_hot));
+                    NNVB_TRY(launch_avgpool_onehot(st, L.pg, hot, n_hot, out + n_dense * ld_out, ld_out, !lazy,
+                                                   &ctx->launches));
+                    for (auto& co : b->cohorts)
+                        if (co.col0 >= n_dense) co.clean = !lazy;
+                }
             }
             // windows of the output tensor
             if (L.type == NNVB_LAYER_FC) {
@@ -1380,7 +1402,10 @@ int run_layers(nnvb_batch* b) {
                                                &ctx->launches));
             }
             b->pend_mask_ncols = 0;
-            b->pend_onehot = 0;
+            if (!keep_hot) {
+                b->pend_onehot = 0;
+                b->pend_scaled = false;
+            }
             b->V = out;
             b->N = Nout;
             b->ld = ld_out;
@@ -1684,6 +1709,7 @@ int nnvb_batch_reach(nnvb_batch* b, const nnvb_opts* opts) {
     while ((int)b->wk->relu.size() < b->net->n_relu) b->wk->relu.emplace_back(new ReluLayerRecord());
     b->pend_mask_ncols = 0;
     b->pend_onehot = 0;
+    b->pend_scaled = false;
     NNVB_TRY(init_sets(b));
     NNVB_TRY(run_layers(b));
     b->reached = true;

@@ -257,13 +257,19 @@ __global__ void fc_skinny_reduce_kernel(int Out, int ncols, int n_slices, const 
     Vout[int64_t(c) * ld_out + o] = v + bias[o];
 }
 
-// FullyConnected image of one-hot columns: W * e_i = W(:, i), i.e. row i of the transposed weight copy.
-__global__ void fc_onehot_kernel(int Out, const double* __restrict__ Wt, int ldw, const int32_t* __restrict__ rec_idx,
-                                 int64_t c_first, int64_t c_step, double* __restrict__ Vout, int64_t ld_out) {
+// FullyConnected image of one-hot columns: W * e_i = W(:, i), i.e. row i of the transposed weight copy,
+// times the column's scale where it has one (the single product of the dense contraction).
+__global__ void fc_onehot_kernel(int Out, const double* __restrict__ Wt, int ldw, HotCols hot,
+                                 double* __restrict__ Vout, int64_t ld_out) {
     const int64_t t = blockIdx.x;
-    const double* src = Wt + int64_t(rec_idx[c_first + t * c_step]) * ldw;
+    const double* src = Wt + int64_t(hot.idx[hot.first + t * hot.step]) * ldw;
     double* dst = Vout + t * ld_out;
-    for (int o = threadIdx.x; o < Out; o += blockDim.x) dst[o] = src[o];
+    if (hot.scale != nullptr) {
+        const double sc = hot.scale[t];
+        for (int o = threadIdx.x; o < Out; o += blockDim.x) dst[o] = src[o] * sc;
+    } else {
+        for (int o = threadIdx.x; o < Out; o += blockDim.x) dst[o] = src[o];
+    }
 }
 }  // namespace
 
@@ -543,10 +549,10 @@ int launch_fc_skinny(cudaStream_t st, int In, int Out, const double* Wt, int ldw
     return NNVB_OK;
 }
 
-int launch_fc_onehot(cudaStream_t st, int Out, const double* Wt, int ldw, const int32_t* rec_idx, int64_t c_first,
-                     int64_t c_step, int64_t K_loc, double* Vout, int64_t ld_out, int64_t* launches) {
+int launch_fc_onehot(cudaStream_t st, int Out, const double* Wt, int ldw, const HotCols& hot, int64_t K_loc,
+                     double* Vout, int64_t ld_out, int64_t* launches) {
     if (K_loc <= 0) return NNVB_OK;
-    fc_onehot_kernel<<<(unsigned)K_loc, 128, 0, st>>>(Out, Wt, ldw, rec_idx, c_first, c_step, Vout, ld_out);
+    fc_onehot_kernel<<<(unsigned)K_loc, 128, 0, st>>>(Out, Wt, ldw, hot, Vout, ld_out);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;

@@ -342,6 +342,60 @@ def test_windowed_convolution_with_ragged_channel_counts(ctx):
     net.close()
 
 
+def _pool(ph, pw, sh, sw, pad=(0, 0, 0, 0)):
+    return {"type": "avgpool", "pool": (ph, pw), "stride": (sh, sw), "pad": pad}
+
+
+@pytest.mark.parametrize("case", ["tiling", "chain", "ragged", "overlap"])
+def test_unit_vector_columns_through_pooling_layers(ctx, case):
+    """The columns a ReLU layer appends reach the layer after a pooling layer as scaled unit vectors when the
+    pooling windows tile the image (their memory is first written by that next layer); with a ragged image,
+    overlapping windows or padding they are written by the pooling layer.  Same sets either way."""
+    from nnv_b200.configs import _conv, _bn, _fc, RELU, out_shape
+    rng = np.random.default_rng(31)
+    if case == "tiling":          # ReLU -> 2x2/2 -> convolution, ReLU -> 3x2/3x2 -> FC
+        shape = (12, 12, 2)
+        layers = [_conv(rng, 3, 3, 2, 12, (1, 1, 1, 1)), RELU, _pool(2, 2, 2, 2),
+                  _conv(rng, 3, 3, 12, 10, (1, 1, 1, 1)), _bn(rng, 10), RELU, _pool(3, 2, 3, 2)]
+    elif case == "chain":         # two pooling layers in a row, the second one followed by a convolution
+        shape = (16, 8, 2)
+        layers = [_conv(rng, 3, 3, 2, 9, (1, 1, 1, 1)), RELU, _pool(2, 2, 2, 2), _pool(2, 1, 2, 1),
+                  _conv(rng, 3, 3, 9, 8, (1, 1, 1, 1)), RELU, _pool(2, 2, 2, 2)]
+    elif case == "ragged":        # 7 rows do not split into 2-row windows; the second pooling layer is padded
+        shape = (7, 9, 2)
+        layers = [_conv(rng, 3, 3, 2, 8, (1, 1, 1, 1)), RELU, _pool(2, 2, 2, 2),
+                  _conv(rng, 3, 3, 8, 8, (1, 1, 1, 1)), RELU, _pool(2, 2, 2, 2, (1, 0, 0, 0))]
+    else:                         # 3x3 windows with stride 2
+        shape = (11, 11, 2)
+        layers = [_conv(rng, 3, 3, 2, 8, (1, 1, 1, 1)), RELU, _pool(3, 3, 2, 2),
+                  _conv(rng, 3, 3, 8, 8, (1, 1, 1, 1)), RELU, _pool(2, 2, 2, 2)]
+    h, w, c = out_shape(layers, shape)
+    layers += [_fc(rng, h * w * c, 20), RELU, _fc(rng, 20, 5)]
+    queries = []
+    for k in range(2):
+        x = rng.uniform(0, 1, shape)
+        e = np.zeros(shape)
+        e[k::2, 1::3, :] = 0.05
+        queries.append({"lb": np.maximum(x - e, 0), "ub": np.minimum(x + e, 1)})
+    net = Network(ctx, layers, shape)
+    b = Batch(net, queries)
+    b.upload()
+    b.reach(keep_layer_bounds=True)
+    for q, qu in enumerate(queries):
+        S = O.reach(layers, O.star_from_query(qu))
+        V = b.get_V(q)
+        assert V.shape == S.V.shape and _rel(V, S.V) < TOL
+        assert any(len(t["cross"]) > 0 for t in S.trace[:2])
+        for li, t in enumerate(S.trace):
+            idx, _, _ = b.get_crossing(q, li)
+            assert np.array_equal(idx, t["cross"])
+            ll, lu = b.get_layer_ranges(q, li, t["N"])
+            bscale = max(np.abs(t["lb"]).max(), np.abs(t["ub"]).max())
+            assert np.abs(ll - t["lb"]).max() / bscale < TOL and np.abs(lu - t["ub"]).max() / bscale < TOL
+    b.close()
+    net.close()
+
+
 def test_verification_of_a_list_that_exceeds_the_arena_is_split():
     """verify_robustness_batch halves the list when the generator tensors of all sets do not fit the arena."""
     from nnv_b200.engine import Context
