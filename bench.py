@@ -294,8 +294,9 @@ def run_ours(args):
                              "bytes of the windows)"}
         # DRAM bytes (read + write) of one image's convolution launches, from the ncu capture of the batch-1
         # run summarised in profiles/conv_win_kernel_cnn32_batch1.md; the launches of a batch of B images move
-        # B times as much (every column is touched once per layer)
-        conv_dram_bytes_per_image = 578e6
+        # B times as much (every column is touched once per layer).  The capture's launch on the 1x1 windows of
+        # the ReLU-2 columns (51 MB) is no longer made: those columns reach the convolution as unit vectors
+        conv_dram_bytes_per_image = 530e6
 
         def roof(fam):
             f = prof[fam]
