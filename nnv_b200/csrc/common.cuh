@@ -299,11 +299,13 @@ int launch_witness_relu(cudaStream_t st, int n_pairs, const int32_t* pair_q, int
 int launch_witness_value(cudaStream_t st, int n_pairs, int64_t Nout, int64_t ld, const double* X, const double* G,
                          const double* g, double* value, double* scale, int64_t* launches);
 
-// Build the dense input set of a bounds-form query batch.
+// Build the input set of a bounds-form query batch: centres, and per generator its metadata and either
+// its column in V (hot_idx null) or its (entry, half width) pair in hot_idx / hot_scale, indexed by
+// column - nq, with the column's memory left untouched.
 int launch_build_from_bounds(cudaStream_t st, int nq, int64_t N, int64_t ld, const double* lbub,
                              const int64_t* q_gen_off, int rank, int world, double* V, int32_t* col_q, double* pl,
                              double* pu, int32_t* qcol_idx, int64_t* col_pos, int img_h, int img_w, int4* box,
-                             int64_t* launches);
+                             int32_t* hot_idx, double* hot_scale, int64_t* launches);
 // Move the windows of columns [0, n) through a convolution / pooling layer (extent = (k-1)*dilation).
 int launch_update_windows(cudaStream_t st, int64_t n, int4* box, int pad_t, int pad_l, int ext_h,
                           int ext_w, int sh, int sw, int64_t* launches);

@@ -157,7 +157,8 @@ __global__ void build_from_bounds_kernel(int nq, int rank, int world, int64_t N,
                                          int32_t* __restrict__ col_q, double* __restrict__ pl,
                                          double* __restrict__ pu, int32_t* __restrict__ qcol_idx,
                                          int64_t* __restrict__ col_pos, int img_h, int img_w,
-                                         int4* __restrict__ box) {
+                                         int4* __restrict__ box, int32_t* __restrict__ hot_idx,
+                                         double* __restrict__ hot_scale) {
     const int q = blockIdx.x;
     const double* lb = lbub + int64_t(q) * 2 * N;
     const double* ub = lb + N;
@@ -189,7 +190,12 @@ __global__ void build_from_bounds_kernel(int nq, int rank, int world, int64_t N,
         if (has && r % world == rank) {           // generator r of the query lives on rank r % world
             const int64_t t = r / world;
             const int64_t col = gen0 + t;
-            V[col * ld + i] = hw;
+            if (hot_idx != nullptr) {             // the column stays implicit: half width times a unit vector
+                hot_idx[col - nq] = int32_t(i);
+                hot_scale[col - nq] = hw;
+            } else {
+                V[col * ld + i] = hw;
+            }
             col_q[col] = q;
             pl[col] = -1.0;
             pu[col] = 1.0;
@@ -417,9 +423,9 @@ int launch_count_bounds(cudaStream_t st, int nq, int64_t N, const double* lbub, 
 int launch_build_from_bounds(cudaStream_t st, int nq, int64_t N, int64_t ld, const double* lbub,
                              const int64_t* q_gen_off, int rank, int world, double* V, int32_t* col_q, double* pl,
                              double* pu, int32_t* qcol_idx, int64_t* col_pos, int img_h, int img_w, int4* box,
-                             int64_t* launches) {
+                             int32_t* hot_idx, double* hot_scale, int64_t* launches) {
     build_from_bounds_kernel<<<nq, 256, 0, st>>>(nq, rank, world, N, ld, lbub, q_gen_off, V, col_q, pl, pu, qcol_idx,
-                                                 col_pos, img_h, img_w, box);
+                                                 col_pos, img_h, img_w, box, hot_idx, hot_scale);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;

@@ -857,6 +857,12 @@ int ensure_col_meta(nnvb_batch* b, int64_t cols) {
     return NNVB_OK;
 }
 
+// windowed launches skip the zero fill of their output columns unless the caller wants the constraint rows
+bool lazy_fill(const nnvb_batch* b) {
+    static const bool always_fill = getenv("NNVB_ZERO_FILL") != nullptr;
+    return !always_fill && !b->opts.keep_constraints;
+}
+
 int init_sets(nnvb_batch* b) {
     nnvb_ctx* ctx = b->net->ctx;
     cudaStream_t st = ctx->stream;
@@ -877,19 +883,31 @@ int init_sets(nnvb_batch* b) {
     NNVB_TRY(ensure_col_meta(b, ncols));
     b->list_cur = 0;
     NNVB_TRY(h2d_small(ctx, b->wk->qcol_off[0].p, b->h_qcol_off.data(), sizeof(int64_t) * (nq + 1)));
+    bool implicit = false;               // the generator columns are not stored: the first layer writes their images
     if (b->kind == 1) {
         const size_t need = size_t(ld) * ncols * sizeof(double);
         if (need > ctx->vbuf_bytes()) return capacity_error("input set", need, ctx->vbuf_bytes());
         NNVB_TRY(b->wk->gen_off.ensure(sizeof(int64_t) * (nq + 1), st));
         NNVB_TRY(h2d_small(ctx, b->wk->gen_off.p, gen_off.data(), sizeof(int64_t) * (nq + 1)));
         double* V = ctx->vbuf(0);
-        NNVB_CUDA(cudaMemsetAsync(V, 0, need, st));
+        // a generator of ImageStar(lb,ub) is a half width times a unit vector: when the first layer writes the
+        // images of such columns itself, they start out as (entry, half width) pairs and are never stored
+        static const bool eager = getenv("NNVB_EAGER_RELU") != nullptr;
+        const int t0 = b->net->layers.empty() ? 0 : b->net->layers[0].type;
+        implicit = !eager && lazy_fill(b) && ncols > nq && N < (int64_t(1) << 31) &&
+                   (t0 == NNVB_LAYER_CONV2D || t0 == NNVB_LAYER_FC || t0 == NNVB_LAYER_AVGPOOL2D);
+        if (implicit) {
+            NNVB_TRY(b->wk->hot_idx.ensure(sizeof(int32_t) * (ncols - nq), st));
+            NNVB_TRY(b->wk->hot_scale.ensure(sizeof(double) * (ncols - nq), st));
+        }
+        NNVB_CUDA(cudaMemsetAsync(V, 0, implicit ? size_t(ld) * nq * sizeof(double) : need, st));
         NNVB_TRY(launch_build_from_bounds(st, nq, N, ld, b->d_in.as<double>(), b->wk->gen_off.as<int64_t>(), ctx->rank,
                                           ctx->world, V,
                                           b->wk->col_q.as<int32_t>(), b->wk->pl.as<double>(), b->wk->pu.as<double>(),
                                           b->wk->qcol_idx[0].as<int32_t>(), b->wk->col_pos.as<int64_t>(),
                                           int(b->net->in_shape[0]), int(b->net->in_shape[1]),
-                                          b->wk->box.as<int4>(), &ctx->launches));
+                                          b->wk->box.as<int4>(), implicit ? b->wk->hot_idx.as<int32_t>() : nullptr,
+                                          implicit ? b->wk->hot_scale.as<double>() : nullptr, &ctx->launches));
         b->V = V;
     } else {
         // metadata is a pure function of the staged queries
@@ -914,6 +932,8 @@ int init_sets(nnvb_batch* b) {
     b->ncols = ncols;
     b->N = N;
     b->ld = ld;
+    b->pend_onehot = implicit ? ncols - nq : 0;
+    b->pend_scaled = implicit;
     for (int i = 0; i < 3; ++i) b->shape[i] = b->net->in_shape[i];
     // centres are dense; box generators touch one pixel each; general generators are taken as dense
     static const bool no_windows = getenv("NNVB_NO_WINDOWS") != nullptr;
@@ -958,12 +978,6 @@ int ensure_clean(nnvb_batch* b, nnvb_batch::Cohort& co) {
                                          b->wk->box.as<int4>(), co.col0, co.col1 - co.col0, b->V, b->ld, &ctx->launches));
     co.clean = true;
     return NNVB_OK;
-}
-
-// windowed launches skip the zero fill of their output columns unless the caller wants the constraint rows
-bool lazy_fill(const nnvb_batch* b) {
-    static const bool always_fill = getenv("NNVB_ZERO_FILL") != nullptr;
-    return !always_fill && !b->opts.keep_constraints;
 }
 
 int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_onehot) {

@@ -319,13 +319,24 @@ range_partial_narrow_kernel(int64_t N, int64_t ld, const double* __restrict__ V,
     const int64_t beg = chunk_beg[chunk], end = chunk_end[chunk];
     double lo = 0.0, hi = 0.0;
     if (i < N) {
-        for (int64_t pos = beg + warp; pos < end; pos += 8) {
-            const int64_t col = qcol_idx[pos];
-            const double a = pl[col], b = pu[col];
-            const double x = V[col * ld + i];
-            const double p0 = fmax(x, 0.0), n0 = fmin(x, 0.0);
-            lo = fma(p0, a, lo); lo = fma(n0, b, lo);
-            hi = fma(p0, b, hi); hi = fma(n0, a, hi);
+        // four of the warp's columns in flight; the sums still run in column order
+        for (int64_t pos = beg + warp; pos < end; pos += 32) {
+            double x[4], a[4], b[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int64_t pu_ = pos + 8 * u;
+                const int64_t col = pu_ < end ? qcol_idx[pu_] : -1;
+                x[u] = col >= 0 ? V[col * ld + i] : 0.0;
+                a[u] = col >= 0 ? pl[col] : 0.0;
+                b[u] = col >= 0 ? pu[col] : 0.0;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (pos + 8 * u >= end) break;
+                const double p0 = fmax(x[u], 0.0), n0 = fmin(x[u], 0.0);
+                lo = fma(p0, a[u], lo); lo = fma(n0, b[u], lo);
+                hi = fma(p0, b[u], hi); hi = fma(n0, a[u], hi);
+            }
         }
     }
     __shared__ double slo[8][32], shi[8][32];
