@@ -304,8 +304,8 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
 // dense contraction of that column gives (every other term of its sums is a product with zero).
 // Every entry of the column's output window (origin and extent as update_windows_kernel derives them from
 // a 1x1 input window) is written, zeros included; nothing outside it is touched.  One block per column,
-// lanes over (window position, output channel).  A column with a scale (a one-hot column that went through
-// a pooling layer) gives scale times the footprint: the one product its dense contraction would form.
+// lanes over (window position, output channel).  A column with a scale (a generator of a bounds-form input set,
+// a one-hot column that went through a pooling layer) gives scale times the footprint: the one product its dense contraction would form.
 __global__ void __launch_bounds__(128)
 conv_onehot_kernel(ConvGeom g, const double* __restrict__ Wg, int bn_tile, int cs, int n_chunks, ChanAffine bn,
                    HotCols hot, double* __restrict__ Vout, int64_t ld_out) {
@@ -324,25 +324,49 @@ conv_onehot_kernel(ConvGeom g, const double* __restrict__ Wg, int bn_tile, int c
     const int org_h = ah >= 0 ? (ah + g.sh - 1) / g.sh : -((-ah) / g.sh);
     const int org_w = aw >= 0 ? (aw + g.sw - 1) / g.sw : -((-aw) / g.sw);
     double* dst = Vout + t * ld_out;
+    // the tap value at output (oh, ow, co), zero where no tap maps it to input (h, w)
+    auto entry = [&](int oh, int ow, int co) -> double {
+        const int dh_ = h + g.pad_t - oh * g.sh, dw_ = w + g.pad_l - ow * g.sw;
+        if (!(dh_ >= 0 && dw_ >= 0 && dh_ % g.dh == 0 && dw_ % g.dw == 0 && dh_ / g.dh < g.kh && dw_ / g.dw < g.kw))
+            return 0.0;
+        const int tap = dh_ / g.dh + g.kh * (dw_ / g.dw);
+        const int nt = co / bn_tile, n = co % bn_tile;
+        double v = Wg[((((int64_t(nt) * n_chunks + ch) * taps + tap) * KC + cil) * cs) + n];
+        if (scaled) v = v * sc;
+        if (bn.rden != nullptr) v = (v * bn.rden[co]) * bn.scale[co];
+        return v;
+    };
+    const int lo = max(org_h, 0), hi = min(org_h + wh, g.Ho);     // window rows on the image
+    if (hi <= lo) return;
+    if (g.Ho % 4 == 0 && ld_out % 4 == 0) {
+        // whole 32-byte sectors: the aligned groups of four rows that cover the window rows are written, with
+        // zeros in the entries outside the window (which are zero in the dense tensor too); a partly written
+        // sector costs the memory system a read on top of the write
+        const int a0 = lo & ~3;
+        const int ngr = (hi - a0 + 3) / 4;
+        for (int e = threadIdx.x; e < ngr * ww * g.Cout; e += blockDim.x) {
+            const int r0 = a0 + 4 * (e % ngr);
+            const int e2 = e / ngr;
+            const int co = e2 % g.Cout;
+            const int ow = org_w + e2 / g.Cout;
+            if (ow < 0 || ow >= g.Wo) continue;
+            double v[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) v[r] = (r0 + r >= lo && r0 + r < hi) ? entry(r0 + r, ow, co) : 0.0;
+            double2* d2 = reinterpret_cast<double2*>(dst + r0 + int64_t(g.Ho) * (ow + int64_t(g.Wo) * co));
+            d2[0] = make_double2(v[0], v[1]);
+            d2[1] = make_double2(v[2], v[3]);
+        }
+        return;
+    }
     // patch rows fastest: the lanes of one (patch column, channel) write consecutive addresses
     for (int e = threadIdx.x; e < wh * ww * g.Cout; e += blockDim.x) {
-        const int ohl = e % wh;
+        const int oh = org_h + e % wh;
         const int e2 = e / wh;
         const int co = e2 % g.Cout;
-        const int owl = e2 / g.Cout;
-        const int oh = org_h + ohl, ow = org_w + owl;
+        const int ow = org_w + e2 / g.Cout;
         if (oh < 0 || ow < 0 || oh >= g.Ho || ow >= g.Wo) continue;
-        // the tap that maps output (oh, ow) to input (h, w), if there is one
-        const int dh_ = h + g.pad_t - oh * g.sh, dw_ = w + g.pad_l - ow * g.sw;
-        double v = 0.0;
-        if (dh_ >= 0 && dw_ >= 0 && dh_ % g.dh == 0 && dw_ % g.dw == 0 && dh_ / g.dh < g.kh && dw_ / g.dw < g.kw) {
-            const int tap = dh_ / g.dh + g.kh * (dw_ / g.dw);
-            const int nt = co / bn_tile, n = co % bn_tile;
-            v = Wg[((((int64_t(nt) * n_chunks + ch) * taps + tap) * KC + cil) * cs) + n];
-            if (scaled) v = v * sc;
-            if (bn.rden != nullptr) v = (v * bn.rden[co]) * bn.scale[co];
-        }
-        dst[oh + int64_t(g.Ho) * (ow + int64_t(g.Wo) * co)] = v;
+        dst[oh + int64_t(g.Ho) * (ow + int64_t(g.Wo) * co)] = entry(oh, ow, co);
     }
 }
 
