@@ -240,7 +240,7 @@ __global__ void fill_dense_windows_kernel(int64_t n, int4* __restrict__ box) {
 template <bool PAIRS>
 __global__ void avgpool_windowed_kernel(PoolGeom g, RowMask mask, ColWindows win, int64_t col_base, int64_t ncols,
                                         const double* __restrict__ Vin, int64_t ld_in, double* __restrict__ Vout,
-                                        int64_t ld_out) {
+                                        int64_t ld_out, bool pad_rows) {
     const int per_col = win.wh * win.ww * g.C;
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= per_col) return;
@@ -299,7 +299,18 @@ __global__ void avgpool_windowed_kernel(PoolGeom g, RowMask mask, ColWindows win
                 }
             }
         }
-        Vout[j * ld_out + oh + int64_t(g.Ho) * ow + obase] = acc / div;
+        double* dst = Vout + j * ld_out + int64_t(g.Ho) * ow + obase;
+        dst[oh] = acc / div;
+        if (pad_rows) {
+            // complete the 32-byte sectors at both ends of the window's run of rows with zeros (the dense
+            // tensor is zero there): a partly written sector costs the memory system a read on top of the write
+            const int first = oh - ohl;
+            const int lo = max(first, 0), hi = min(first + win.wh, g.Ho);
+            if (oh == lo)
+                for (int r = lo & ~3; r < lo; ++r) dst[r] = 0.0;
+            if (oh == hi - 1)
+                for (int r = hi; r < ((hi + 3) & ~3); ++r) dst[r] = 0.0;
+        }
     }
 }
 
@@ -313,10 +324,13 @@ int launch_avgpool_windowed(cudaStream_t st, const PoolGeom& g, const RowMask& m
     // the state array of a query starts at q*N: N even keeps the 2-byte state loads aligned
     const bool pairs = g.ph == 2 && g.pw == 2 && g.sh == 2 && g.sw == 2 && g.pad_t == 0 && g.pad_l == 0 &&
                        g.H % 2 == 0 && ld_in % 2 == 0 && (mask.state == nullptr || mask.N % 2 == 0);
+    const bool pad_rows = g.Ho % 4 == 0 && ld_out % 4 == 0;      // image columns start on sector boundaries
     if (pairs)
-        avgpool_windowed_kernel<true><<<grid, threads, 0, st>>>(g, mask, win, col_base, ncols, Vin, ld_in, Vout, ld_out);
+        avgpool_windowed_kernel<true><<<grid, threads, 0, st>>>(g, mask, win, col_base, ncols, Vin, ld_in, Vout, ld_out,
+                                                                pad_rows);
     else
-        avgpool_windowed_kernel<false><<<grid, threads, 0, st>>>(g, mask, win, col_base, ncols, Vin, ld_in, Vout, ld_out);
+        avgpool_windowed_kernel<false><<<grid, threads, 0, st>>>(g, mask, win, col_base, ncols, Vin, ld_in, Vout, ld_out,
+                                                                 pad_rows);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;
