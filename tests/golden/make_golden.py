@@ -6,7 +6,7 @@ reference_kats.npz
     Known-answer items of the reference's own test-suite for the operations on
     the approx-star path: literal inputs/expected values transcribed from its
     test files, and arrays read from its stored ``.mat`` baselines (needs the
-    reference checkout; pass its root as argv[1], default /root/reference).
+    reference checkout: pass its root as argv[1] or in NNV_REFERENCE_ROOT).
     Each key is documented with the file:line it comes from.
 
 oracle_small.npz
@@ -15,7 +15,7 @@ oracle_small.npz
     ReLU layer, verdicts.  The GPU tests compare against these as well as
     against a live oracle run.
 
-Run from the repository root:  python tests/golden/make_golden.py
+Run from the repository root:  python tests/golden/make_golden.py <reference root>
 """
 import os
 import sys
@@ -129,7 +129,9 @@ def oracle_small():
 
 
 if __name__ == "__main__":
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("NNV_REFERENCE_ROOT")
+    if not ref_root:
+        sys.exit("usage: make_golden.py <root of the reference checkout>")
     np.savez_compressed(os.path.join(HERE, "reference_kats.npz"), **reference_kats(ref_root))
     np.savez_compressed(os.path.join(HERE, "oracle_small.npz"), **oracle_small())
     for f in ("reference_kats.npz", "oracle_small.npz"):
