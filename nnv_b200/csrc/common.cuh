@@ -104,10 +104,12 @@ void conv_arrange_weights(const ConvGeom& g, const double* W, double* dst, int b
 
 // Windowed generator columns (no centres) with the taps that read outside the wh_in x ww_in input window
 // skipped; see conv_win_f64.cu.  *done stays false, and nothing is launched, for geometries it does not
-// cover (the caller then uses launch_conv_f64).
+// cover (the caller then uses launch_conv_f64).  pack (nullable): the launch also writes a window-only copy of
+// its columns there, column j (from col_base) at j*wh*ww*Cout, entry (h, w, c) of the output window at
+// ((w - w0)*wh + (h - h0))*Cout + c.
 int launch_conv_win(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn, const RowMask& mask,
                     const ColWindows& win, int wh_in, int ww_in, int64_t col_base, const double* Vin, int64_t ld_in,
-                    double* Vout, int64_t ld_out, int64_t ncols, bool* done, int64_t* launches);
+                    double* Vout, int64_t ld_out, int64_t ncols, double* pack, bool* done, int64_t* launches);
 // Processes columns [col_base, col_base + ncols) of Vin / Vout (pointers to column 0).
 int launch_conv_f64(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
                     const RowMask& mask, const ColWindows& win, int64_t col_base, const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
@@ -122,9 +124,10 @@ struct HotCols {
 };
 // Images of one-hot columns, written to Vout[ld_out x K_loc].
 // zero_fill: clear the whole output block first (else only the columns' output windows are written).
+// pack (nullable): also a window-only copy, column t at t*wh*ww*Cout, laid out as launch_conv_win's.
 int launch_conv_onehot(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
                        const HotCols& hot, int64_t K_loc, double* Vout, int64_t ld_out, bool zero_fill,
-                       int64_t* launches);
+                       double* pack, int64_t* launches);
 // Writes zero to every entry of columns [col0, col0+n) of V (an H x W x C image per column) that lies
 // outside the column's window box[col]: afterwards the columns can be read without window tests.
 int launch_zero_outside_windows(cudaStream_t st, int H, int W, int C, const int4* box, int64_t col0, int64_t n,
@@ -183,6 +186,9 @@ struct WinCohort {
     int64_t col0, n;
     int wh, ww, KH, KW;
     int64_t bin_base;          // offset of its [nq][KH*KW + 1] table in the bin arrays
+    // window-only copy of the cohort's columns (ReluWork::win_pack), or pack_off < 0: entry (h, w, c) of column j
+    // at pack_off + (j - col0)*pack_stride + ((w - w0_j)*wh + (h - h0_j))*C + c
+    int64_t pack_off, pack_stride;
 };
 constexpr int MAX_WIN_COHORTS = 16;
 constexpr int MAX_WIN_EXTENT = 32;       // largest window side handled this way
@@ -207,6 +213,7 @@ struct ReluWork {
     // cohorts whose columns are reduced through their windows (their columns are in no chunk)
     WinCohorts win;
     int win_slices;            // chunks per query the windowed cohorts fill (range_windows_slices())
+    const double* win_pack;    // window-only copies of the windowed cohorts (all of them, or null: read V)
     int32_t* win_scratch;      // range_windows_scratch_ints() int32
     const int32_t* win_seg;    // [win.n][nq] first column of query q in windowed cohort k
     // chunk list for the bound reduction

@@ -308,7 +308,7 @@ conv_f64_kernel(const ConvParams p, const double* __restrict__ Wg, const double*
 // a one-hot column that went through a pooling layer) gives scale times the footprint: the one product its dense contraction would form.
 __global__ void __launch_bounds__(128)
 conv_onehot_kernel(ConvGeom g, const double* __restrict__ Wg, int bn_tile, int cs, int n_chunks, ChanAffine bn,
-                   HotCols hot, double* __restrict__ Vout, int64_t ld_out) {
+                   HotCols hot, double* __restrict__ Vout, int64_t ld_out, double* __restrict__ pack, bool staged) {
     const int64_t t = blockIdx.x;
     const int i = hot.idx[hot.first + t * hot.step];
     const bool scaled = hot.scale != nullptr;
@@ -336,6 +336,22 @@ conv_onehot_kernel(ConvGeom g, const double* __restrict__ Wg, int bn_tile, int c
         if (bn.rden != nullptr) v = (v * bn.rden[co]) * bn.scale[co];
         return v;
     };
+    // in front of a ReLU layer: the window-only copy the bound reduction reads, channel fastest.  With room in
+    // shared memory the entries are computed once, here, and the writes below take them from there
+    extern __shared__ double sv[];
+    if (pack != nullptr) {
+        double* pk = pack + t * (int64_t(wh) * ww * g.Cout);
+        for (int e = threadIdx.x; e < wh * ww * g.Cout; e += blockDim.x) {
+            const int co = e % g.Cout, pos = e / g.Cout;
+            const double v = entry(org_h + pos % wh, org_w + pos / wh, co);
+            pk[e] = v;
+            if (staged) sv[e] = v;
+        }
+        if (staged) __syncthreads();
+    }
+    auto value = [&](int oh, int ow, int co) -> double {
+        return staged ? sv[((ow - org_w) * wh + (oh - org_h)) * g.Cout + co] : entry(oh, ow, co);
+    };
     const int lo = max(org_h, 0), hi = min(org_h + wh, g.Ho);     // window rows on the image
     if (hi <= lo) return;
     if (g.Ho % 4 == 0 && ld_out % 4 == 0) {
@@ -352,7 +368,7 @@ conv_onehot_kernel(ConvGeom g, const double* __restrict__ Wg, int bn_tile, int c
             if (ow < 0 || ow >= g.Wo) continue;
             double v[4];
 #pragma unroll
-            for (int r = 0; r < 4; ++r) v[r] = (r0 + r >= lo && r0 + r < hi) ? entry(r0 + r, ow, co) : 0.0;
+            for (int r = 0; r < 4; ++r) v[r] = (r0 + r >= lo && r0 + r < hi) ? value(r0 + r, ow, co) : 0.0;
             double2* d2 = reinterpret_cast<double2*>(dst + r0 + int64_t(g.Ho) * (ow + int64_t(g.Wo) * co));
             d2[0] = make_double2(v[0], v[1]);
             d2[1] = make_double2(v[2], v[3]);
@@ -366,7 +382,7 @@ conv_onehot_kernel(ConvGeom g, const double* __restrict__ Wg, int bn_tile, int c
         const int co = e2 % g.Cout;
         const int ow = org_w + e2 / g.Cout;
         if (oh < 0 || ow < 0 || oh >= g.Ho || ow >= g.Wo) continue;
-        dst[oh + int64_t(g.Ho) * (ow + int64_t(g.Wo) * co)] = entry(oh, ow, co);
+        dst[oh + int64_t(g.Ho) * (ow + int64_t(g.Wo) * co)] = value(oh, ow, co);
     }
 }
 
@@ -529,11 +545,14 @@ int launch_conv_f64(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, co
 
 int launch_conv_onehot(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
                        const HotCols& hot, int64_t K_loc, double* Vout, int64_t ld_out, bool zero_fill,
-                       int64_t* launches) {
+                       double* pack, int64_t* launches) {
     if (K_loc <= 0) return NNVB_OK;
     if (zero_fill) NNVB_CUDA(cudaMemsetAsync(Vout, 0, sizeof(double) * ld_out * K_loc, st));
-    conv_onehot_kernel<<<(unsigned)K_loc, 128, 0, st>>>(g, w.w, w.bn_tile, w.cs, w.n_chunks, bn, hot, Vout,
-                                                       ld_out);
+    // the window of a column: (kh-1)*dh/sh + 1 rows, likewise columns, all output channels
+    const size_t win_bytes = sizeof(double) * size_t((g.kh - 1) * g.dh / g.sh + 1) * ((g.kw - 1) * g.dw / g.sw + 1) * g.Cout;
+    const bool staged = pack != nullptr && win_bytes <= 32768;
+    conv_onehot_kernel<<<(unsigned)K_loc, 128, staged ? win_bytes : 0, st>>>(g, w.w, w.bn_tile, w.cs, w.n_chunks, bn, hot,
+                                                                            Vout, ld_out, pack, staged);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;

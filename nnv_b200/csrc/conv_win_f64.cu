@@ -42,6 +42,8 @@ struct ConvWinParams {
     int n_chunks;
     int ncol;                       // columns per block
     int OSTR, CSTR;                 // epilogue staging strides: patch row, column (doubles)
+    double* pack;                   // window-only copy of the launch's columns (null: none): entry (ohl, owl, co) of
+    int64_t pack_stride;            // column j at j*pack_stride + (owl*wh_out + ohl)*Cout + co
     int tab_cap;                    // table entries
     int tail;                       // doubles before the constants and tables
 };
@@ -279,15 +281,34 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
                 out_s[col * p.CSTR + o * p.OSTR + n];
         }
     }
+    // epilogue 3 (in front of a ReLU layer): the same tile into the window-only copy the bound reduction reads;
+    // a warp writes the channels of one (column, patch row): contiguous in the copy and in the staging area
+    if (p.pack != nullptr) {
+        constexpr int LPR = BN / 2;          // lanes per (column, patch row), two channels each
+        constexpr int RPI = 32 / LPR;        // (column, patch row) pairs per warp instruction
+        const int items = p.ncol * th_cnt;
+        const int n = 2 * (lane % LPR);
+        for (int it = warp * RPI + lane / LPR; it < items; it += (CW_THREADS / 32) * RPI) {
+            const int o = it % th_cnt, col = it / th_cnt;
+            if (j0 + col >= ncols || n0 + n >= p.g.Cout) continue;
+            const double2 v = *reinterpret_cast<const double2*>(out_s + col * p.CSTR + o * p.OSTR + n);
+            double* dst = p.pack + (j0 + col) * p.pack_stride +
+                          int64_t(owl * p.wh_out + ohb * CW_TH + o) * p.g.Cout + n0 + n;
+            if (n0 + n + 1 < p.g.Cout) *reinterpret_cast<double2*>(dst) = v;     // Cout is even: 16-byte aligned
+            else dst[0] = v.x;
+        }
+    }
 }
 
 template <int KH, int WARPS_M, int WARPS_N>
 int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn, const RowMask& mask,
                const ColWindows& win, int wh_in, int ww_in, int64_t col_base, const double* Vin, int64_t ld_in,
-               double* Vout, int64_t ld_out, int64_t ncols, bool* done) {
+               double* Vout, int64_t ld_out, int64_t ncols, double* pack, bool* done) {
     constexpr int BN = WARPS_N * 8;
     ConvWinParams p;
     p.g = g;
+    p.pack = g.Cout % 2 == 0 ? pack : nullptr;
+    p.pack_stride = int64_t(win.wh) * win.ww * g.Cout;
     p.wh_in = wh_in; p.ww_in = ww_in;
     p.wh_out = win.wh; p.ww_out = win.ww;
     p.n_ohb = (int)ceil_div(win.wh, CW_TH);
@@ -328,16 +349,16 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
 // nothing is launched) for geometries this kernel does not cover: the caller then uses launch_conv_f64.
 int launch_conv_win(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn, const RowMask& mask,
                     const ColWindows& win, int wh_in, int ww_in, int64_t col_base, const double* Vin, int64_t ld_in,
-                    double* Vout, int64_t ld_out, int64_t ncols, bool* done, int64_t* launches) {
+                    double* Vout, int64_t ld_out, int64_t ncols, double* pack, bool* done, int64_t* launches) {
     *done = false;
     if (ncols <= 0) { *done = true; return NNVB_OK; }
     if (g.sh != 1 || g.sw != 1 || g.dh != 1 || g.dw != 1 || g.kh != 3 || g.kw > 7 || win.box == nullptr) return NNVB_OK;
     if (win.wh != wh_in + g.kh - 1 || win.ww != ww_in + g.kw - 1) return NNVB_OK;
     int rc = NNVB_OK;
     if (w.bn_tile == 64)
-        rc = launch_cfg<3, 2, 8>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, done);
+        rc = launch_cfg<3, 2, 8>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, pack, done);
     else if (w.bn_tile == 32)
-        rc = launch_cfg<3, 4, 4>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, done);
+        rc = launch_cfg<3, 4, 4>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, pack, done);
     if (rc == NNVB_OK && *done && launches) *launches += 1;
     return rc;
 }

@@ -117,12 +117,13 @@ struct WorkBufs {
     DevBuf fcg;                          // column grouping of the window-gathered FC
     DevBuf winsort;                      // origin bins and sorted columns of the windowed bound reduction
     DevBuf hot_idx, hot_scale;           // neuron and scale of one-hot columns carried through a pooling layer
+    DevBuf pack;                         // window-only copies of the windowed cohorts for the bound reduction
     DevBuf hs_G, hs_g, hs_q, hs_margin, hs_r, hs_roff, hs_val, hs_scale, hs_bound, wit[2];   // halfspace tests
     std::vector<std::unique_ptr<ReluLayerRecord>> relu;
     void release() {
         DevBuf* bufs[] = {&col_q, &pl, &pu, &col_pos, &box, &qcol_off[0], &qcol_off[1], &qcol_idx[0], &qcol_idx[1],
                           &chunk_beg, &chunk_end, &q_chunk_off, &partial, &sums, &lb, &ub, &state, &rank, &blk_cross,
-                          &q_cross, &q_dead, &q_new_off, &gen_off, &tmp, &fcg, &winsort, &hot_idx, &hot_scale, &hs_G, &hs_g, &hs_q, &hs_margin, &hs_r,
+                          &q_cross, &q_dead, &q_new_off, &gen_off, &tmp, &fcg, &winsort, &hot_idx, &hot_scale, &pack, &hs_G, &hs_g, &hs_q, &hs_margin, &hs_r,
                           &hs_roff, &hs_val, &hs_scale, &hs_bound, &wit[0], &wit[1]};
         for (DevBuf* d : bufs) d->release();
         for (auto& r : relu) r->release();
@@ -219,7 +220,16 @@ struct nnvb_batch {
     // clean: the memory outside the columns' windows is known to hold zeros (false after a windowed launch
     // that wrote the windows only; readers then go by the windows, see ensure_clean)
     // qn: columns per query (they are stored query by query; empty for the centres)
-    struct Cohort { int64_t col0, col1; bool dense; int wh, ww; bool clean = true; std::vector<int64_t> qn; };
+    struct Cohort {
+        int64_t col0, col1;
+        bool dense;
+        int wh, ww;
+        bool clean = true;
+        std::vector<int64_t> qn;
+        // window-only copy of the columns in wk->pack, written by the convolution in front of a ReLU layer
+        // (offset in doubles, -1: none) for the bound reduction; stale once any layer has run
+        int64_t pack_off = -1, pack_stride = 0;
+    };
     std::vector<Cohort> cohorts;
     // work a ReLU step left to the layer that follows it (see relu_step)
     int64_t pend_mask_ncols = 0;         // > 0: rows with state != 0 of columns [0, n) read as zero
@@ -1008,6 +1018,8 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
             d.wh = co.wh; d.ww = co.ww;
             d.KH = int(img_h) + co.wh - 1; d.KW = int(img_w) + co.ww - 1;
             d.bin_base = bin_base;
+            d.pack_off = co.pack_off;
+            d.pack_stride = co.pack_stride;
             bin_base += int64_t(nq) * (int64_t(d.KH) * d.KW + 1);
             int64_t c = co.col0;
             for (int q = 0; q < nq; ++q) { win_seg.push_back(int32_t(c)); c += co.qn[q]; }
@@ -1096,7 +1108,13 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
         int32_t* seg_dev = w.win_scratch + ints;
         NNVB_TRY(h2d_small(ctx, seg_dev, win_seg.data(), sizeof(int32_t) * win_seg.size()));
         w.win_seg = seg_dev;
+        // the window-only copies are read when every windowed cohort has one
+        bool all_packed = true;
+        for (int k = 0; k < wc.n; ++k) all_packed = all_packed && wc.c[k].pack_off >= 0;
+        w.win_pack = all_packed ? b->wk->pack.as<double>() : nullptr;
     }
+    // whatever follows rewrites the tensor: the copies are stale from here on
+    for (auto& co : b->cohorts) co.pack_off = -1;
     w.n_chunks = n_chunks;
     w.chunk_beg = b->wk->chunk_beg.as<int64_t>(); w.chunk_end = b->wk->chunk_end.as<int64_t>();
     w.q_chunk_off = b->wk->q_chunk_off.as<int32_t>();
@@ -1245,6 +1263,7 @@ int run_layers(nnvb_batch* b) {
             if (need > ctx->vbuf_bytes()) return capacity_error("layer output", need, ctx->vbuf_bytes());
             double* out = other_vbuf(b);
             const bool lazy = lazy_fill(b);
+            for (auto& co : b->cohorts) co.pack_off = -1;
             // test aid: fill the output buffer with NaN patterns first, so that a reader that strays outside
             // the windows it was given shows up in the results instead of depending on what the memory held
             static const bool poison = getenv("NNVB_POISON") != nullptr;
@@ -1270,6 +1289,29 @@ int run_layers(nnvb_batch* b) {
                 // one launch per cohort: dense cohorts are tiled over the whole image, windowed cohorts
                 // compute one small output patch per column (the rest of their output stays zero)
                 const double per_pos = 2.0 * L.cg.Cout * L.cg.kh * L.cg.kw * L.cg.Cin;
+                // A ReLU layer next (behind the fused BN): the windowed launches also write a window-only,
+                // channel-fastest copy of their columns, which the bound reduction reads instead of the short
+                // runs of rows in the full-length columns
+                static const bool pack_on = getenv("NNVB_NO_PACK") == nullptr;
+                double* pack_base = nullptr;
+                int64_t pack_next = 0;
+                {
+                    const size_t nx = L.fused_bn >= 0 ? size_t(L.fused_bn) + 1 : li + 1;
+                    const bool relu_next = nx < net->layers.size() && net->layers[nx].type == NNVB_LAYER_RELU;
+                    if (pack_on && relu_next && !b->opts.keep_constraints && L.cg.Cout % 2 == 0) {
+                        int64_t tot = 0;
+                        for (auto& co : b->cohorts) {
+                            if (co.dense || co.col1 <= co.col0) continue;
+                            const int64_t wh = (co.wh - 1 + (L.cg.kh - 1) * L.cg.dh) / L.cg.sh + 1;
+                            const int64_t ww = (co.ww - 1 + (L.cg.kw - 1) * L.cg.dw) / L.cg.sw + 1;
+                            if (wh * ww <= 128) tot += (co.col1 - co.col0) * wh * ww * L.cg.Cout;
+                        }
+                        if (tot > 0) {
+                            NNVB_TRY(b->wk->pack.ensure(sizeof(double) * tot, st));
+                            pack_base = b->wk->pack.as<double>();
+                        }
+                    }
+                }
                 for (auto& co : b->cohorts) {
                     const int64_t c1 = std::min(co.col1, n_dense);
                     if (c1 <= co.col0) continue;
@@ -1286,8 +1328,14 @@ int run_layers(nnvb_batch* b) {
                         if (!no_conv_win && co.col0 >= b->nq) {
                             ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * co.wh * co.ww * double(c1 - co.col0));
                             NNVB_TRY(launch_conv_win(st, L.cg, L.cw, bn, mask, win, co.wh, co.ww, co.col0, b->V, b->ld, out,
-                                                     ld_out, c1 - co.col0, &done, &ctx->launches));
+                                                     ld_out, c1 - co.col0, pack_base ? pack_base + pack_next : nullptr,
+                                                     &done, &ctx->launches));
                             if (!done) ps.cancel();
+                            if (done && pack_base && c1 == co.col1) {
+                                co.pack_off = pack_next;
+                                co.pack_stride = int64_t(wh) * ww * L.cg.Cout;
+                                pack_next += (c1 - co.col0) * co.pack_stride;
+                            }
                         }
                         if (!done) {
                             ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * wh * ww * double(c1 - co.col0));
@@ -1304,8 +1352,19 @@ int run_layers(nnvb_batch* b) {
                     }
                 }
                 ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(lazy ? L.cg.kh * L.cg.kw * L.cg.Cout : Nout) * double(n_hot));
+                // the unit-vector columns are one cohort (the last): its copy follows the others
+                const int64_t hot_stride = int64_t((L.cg.kh - 1) * L.cg.dh / L.cg.sh + 1) *
+                                           ((L.cg.kw - 1) * L.cg.dw / L.cg.sw + 1) * L.cg.Cout;
+                const bool pack_hot = pack_base != nullptr && n_hot > 0 && !b->cohorts.empty() &&
+                                      b->cohorts.back().col0 == n_dense && b->cohorts.back().col1 == b->ncols &&
+                                      !b->cohorts.back().dense;
                 NNVB_TRY(launch_conv_onehot(st, L.cg, L.cw, bn, hot, n_hot, out + n_dense * ld_out, ld_out, !lazy,
-                                            &ctx->launches));
+                                            pack_hot ? pack_base + pack_next : nullptr, &ctx->launches));
+                if (pack_hot) {
+                    b->cohorts.back().pack_off = pack_next;
+                    b->cohorts.back().pack_stride = hot_stride;
+                    pack_next += n_hot * hot_stride;
+                }
                 for (auto& co : b->cohorts)
                     if (co.col0 >= n_dense) co.clean = !lazy;
             } else if (L.type == NNVB_LAYER_FC) {
@@ -1425,6 +1484,7 @@ int run_layers(nnvb_batch* b) {
             b->ld = ld_out;
         } else if (L.type == NNVB_LAYER_BN) {
             if (!L.fused_into_prev) {
+                for (auto& co : b->cohorts) co.pack_off = -1;
                 NNVB_TRY(make_writable(b, 0));
                 ChanAffine bn{L.bn_mean, L.bn_den, L.bn_rden, L.bn_scale, L.bn_offset};
                 ProfScope ps(ctx, NNVB_PROF_BN, 16.0 * double(b->N) * double(b->ncols));

@@ -172,6 +172,7 @@ constexpr int RW_THREADS = 256;
 constexpr int RW_RPT = 4;
 constexpr int RW_MLP = 8;            // window loads a thread keeps in flight
 constexpr int RW_MAX_RUNS = MAX_WIN_COHORTS * MAX_WIN_EXTENT;
+template <bool PACKED>
 __global__ void __launch_bounds__(RW_THREADS)
 range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const double* __restrict__ pl,
                      const double* __restrict__ pu, const int4* __restrict__ box, int H, int W, int C, int TH, int nq,
@@ -187,6 +188,8 @@ range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const 
     __shared__ int run_src[RW_MAX_RUNS];      // first sorted entry of the run (index into perm)
     __shared__ int run_pre[RW_MAX_RUNS + 1];  // candidates before the run
     __shared__ int run_wh[RW_MAX_RUNS];
+    __shared__ int run_co[PACKED ? RW_MAX_RUNS : 1];      // cohort of the run
+    __shared__ int64_t s_off[PACKED ? RW_THREADS : 1];    // packed offset of entry (h = 0, w, c = 0) of a candidate
     __shared__ int n_runs_s;
     __shared__ int s_col[RW_THREADS], s_h0[RW_THREADS], s_wh[RW_THREADS];
     __shared__ double s_pl[RW_THREADS], s_pu[RW_THREADS];
@@ -222,6 +225,7 @@ range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const 
                 run_src[r] = src;
                 run_pre[r] = total;
                 run_wh[r] = wh;
+                if (PACKED) run_co[r] = k;
                 total += len;
                 ++r;
             }
@@ -238,13 +242,16 @@ range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const 
     // rows of this thread
     int64_t row[RW_RPT];
     int hh[RW_RPT];
+    int cc[RW_RPT];
     double lo[RW_RPT], hi[RW_RPT];
 #pragma unroll
     for (int r = 0; r < RW_RPT; ++r) {
         const int idx = threadIdx.x + r * RW_THREADS;
-        const int pix = idx % TH, c = idx / TH;
+        // the window-only copies are channel-fastest: lanes along the channels there, along the pixels in V
+        const int pix = PACKED ? idx / C : idx % TH, c = PACKED ? idx % C : idx / TH;
         hh[r] = hT + pix;
-        row[r] = (c < C && hh[r] < H) ? hh[r] + int64_t(H) * (w + int64_t(W) * c) : int64_t(-1);
+        row[r] = (c < C && pix < TH && hh[r] < H) ? hh[r] + int64_t(H) * (w + int64_t(W) * c) : int64_t(-1);
+        if (PACKED) cc[r] = c;
         lo[r] = 0.0;
         hi[r] = 0.0;
     }
@@ -259,8 +266,14 @@ range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const 
             }
             const int col = perm[run_src[a] + (i - run_pre[a])];
             s_col[threadIdx.x] = col;
-            s_h0[threadIdx.x] = box[col].x;
+            const int4 bx = box[col];
+            s_h0[threadIdx.x] = bx.x;
             s_wh[threadIdx.x] = run_wh[a];
+            if (PACKED) {
+                const WinCohort& co = wc.c[run_co[a]];
+                s_off[threadIdx.x] = co.pack_off + (int64_t(col) - co.col0) * co.pack_stride +
+                                     (int64_t(w - bx.y) * co.wh - bx.x) * C;
+            }
             s_pl[threadIdx.x] = pl[col];
             s_pu[threadIdx.x] = pu[col];
         }
@@ -275,7 +288,8 @@ range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const 
 #pragma unroll
                 for (int u = 0; u < RW_MLP; ++u) {
                     const bool in = unsigned(hh[r] - s_h0[j + u]) < unsigned(s_wh[j + u]);
-                    v[u] = in ? V[int64_t(s_col[j + u]) * ld + row[r]] : 0.0;
+                    v[u] = !in ? 0.0 : PACKED ? V[s_off[j + u] + int64_t(hh[r]) * C + cc[r]]
+                                              : V[int64_t(s_col[j + u]) * ld + row[r]];
                 }
 #pragma unroll
                 for (int u = 0; u < RW_MLP; ++u) {
@@ -287,7 +301,8 @@ range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const 
             }
             for (; j < cnt; ++j) {
                 const bool in = unsigned(hh[r] - s_h0[j]) < unsigned(s_wh[j]);
-                const double v = in ? V[int64_t(s_col[j]) * ld + row[r]] : 0.0;
+                const double v = !in ? 0.0 : PACKED ? V[s_off[j] + int64_t(hh[r]) * C + cc[r]]
+                                                    : V[int64_t(s_col[j]) * ld + row[r]];
                 const bool pos = v > 0.0;
                 lo[r] = fma(v, pos ? s_pl[j] : s_pu[j], lo[r]);
                 hi[r] = fma(v, pos ? s_pu[j] : s_pl[j], hi[r]);
@@ -973,9 +988,14 @@ int launch_estimate_ranges(cudaStream_t st, const ReluWork& w, int64_t* launches
             return NNVB_E_UNSUPPORTED;
         }
         dim3 grid((unsigned)(ceil_div(w.img_h, TH) * w.img_w), (unsigned)w.nq, (unsigned)w.win_slices);
-        range_windows_kernel<<<grid, RW_THREADS, 0, st>>>(w.N, w.ld, w.V, w.pl, w.pu, w.box, w.img_h, w.img_w, w.img_c,
-                                                          TH, w.nq, w.win, bins, perm, w.win_seg, w.q_chunk_off,
-                                                          w.partial);
+        if (w.win_pack != nullptr)
+            range_windows_kernel<true><<<grid, RW_THREADS, 0, st>>>(w.N, w.ld, w.win_pack, w.pl, w.pu, w.box, w.img_h,
+                                                                    w.img_w, w.img_c, TH, w.nq, w.win, bins, perm,
+                                                                    w.win_seg, w.q_chunk_off, w.partial);
+        else
+            range_windows_kernel<false><<<grid, RW_THREADS, 0, st>>>(w.N, w.ld, w.V, w.pl, w.pu, w.box, w.img_h,
+                                                                     w.img_w, w.img_c, TH, w.nq, w.win, bins, perm,
+                                                                     w.win_seg, w.q_chunk_off, w.partial);
         NNVB_CUDA(cudaGetLastError());
         if (launches) *launches += 5;
     }
