@@ -254,13 +254,23 @@ __global__ void avgpool_windowed_kernel(PoolGeom g, RowMask mask, ColWindows win
     for (int64_t jj = blockIdx.y; jj < ncols; jj += gridDim.y) {
         const int64_t j = col_base + jj;
         const int4 bx = win.box[j];
-        const int a = bx.x + g.pad_t - (g.ph - 1), b2 = bx.y + g.pad_l - (g.pw - 1);
-        const int oh = (a >= 0 ? (a + g.sh - 1) / g.sh : -((-a) / g.sh)) + ohl;
-        const int ow = (b2 >= 0 ? (b2 + g.sw - 1) / g.sw : -((-b2) / g.sw)) + owl;
+        int oh, ow, h0, w0;
+        if (PAIRS) {        // 2x2 windows, stride 2, no padding: the same origin formula with its constants folded
+            const int a = bx.x - 1, b2 = bx.y - 1;
+            oh = (a >= 0 ? (a + 1) >> 1 : -((-a) >> 1)) + ohl;
+            ow = (b2 >= 0 ? (b2 + 1) >> 1 : -((-b2) >> 1)) + owl;
+            h0 = 2 * oh;
+            w0 = 2 * ow;
+        } else {
+            const int a = bx.x + g.pad_t - (g.ph - 1), b2 = bx.y + g.pad_l - (g.pw - 1);
+            oh = (a >= 0 ? (a + g.sh - 1) / g.sh : -((-a) / g.sh)) + ohl;
+            ow = (b2 >= 0 ? (b2 + g.sw - 1) / g.sw : -((-b2) / g.sw)) + owl;
+            h0 = oh * g.sh - g.pad_t;
+            w0 = ow * g.sw - g.pad_l;
+        }
         if (oh < 0 || ow < 0 || oh >= g.Ho || ow >= g.Wo) continue;
         const double* src = Vin + j * ld_in + cbase;
         const uint8_t* st = (mask.state != nullptr && j < mask.ncols) ? mask.state + mask.col_q[j] * mask.N + cbase : nullptr;
-        const int h0 = oh * g.sh - g.pad_t, w0 = ow * g.sw - g.pad_l;
         double acc = 0.0;
         if (PAIRS) {
             // 2x2 windows at stride 2 without padding on an even image height: the two rows of a window
@@ -300,7 +310,7 @@ __global__ void avgpool_windowed_kernel(PoolGeom g, RowMask mask, ColWindows win
             }
         }
         double* dst = Vout + j * ld_out + int64_t(g.Ho) * ow + obase;
-        dst[oh] = acc / div;
+        dst[oh] = PAIRS ? acc * 0.25 : acc / div;       // a quotient by 4 is exact either way
         if (pad_rows) {
             // complete the 32-byte sectors at both ends of the window's run of rows with zeros (the dense
             // tensor is zero there): a partly written sector costs the memory system a read on top of the write
