@@ -324,6 +324,76 @@ __global__ void avgpool_windowed_kernel(PoolGeom g, RowMask mask, ColWindows win
     }
 }
 
+// 2x2 windows at stride 2 without padding, even image height: a thread owns two vertically adjacent outputs of
+// one (patch column, channel), so the window, the pointers and the column tests of a column are worked out
+// once for both.  Per output the same four values in the same order as avgpool_windowed_kernel.
+__global__ void avgpool_windowed_2x2_kernel(PoolGeom g, RowMask mask, ColWindows win, int64_t col_base, int64_t ncols,
+                                            const double* __restrict__ Vin, int64_t ld_in, double* __restrict__ Vout,
+                                            int64_t ld_out, bool pad_rows) {
+    const int slots = (win.wh + 1) / 2;
+    const int per_col = slots * win.ww * g.C;
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= per_col) return;
+    const int ohl = 2 * (r % slots);
+    const int r2 = r / slots;
+    const int owl = r2 % win.ww;
+    const int c = r2 / win.ww;
+    const int64_t cbase = int64_t(c) * g.H * g.W;
+    const int64_t obase = int64_t(g.Ho) * g.Wo * c;
+    const bool two = ohl + 1 < win.wh;
+    for (int64_t jj = blockIdx.y; jj < ncols; jj += gridDim.y) {
+        const int64_t j = col_base + jj;
+        const int4 bx = win.box[j];
+        const int a = bx.x - 1, b2 = bx.y - 1;
+        const int first = a >= 0 ? (a + 1) >> 1 : -((-a) >> 1);         // first output row of the window
+        const int ow = (b2 >= 0 ? (b2 + 1) >> 1 : -((-b2) >> 1)) + owl;
+        const int oh0 = first + ohl;
+        const bool ok0 = oh0 >= 0 && oh0 < g.Ho, ok1 = two && oh0 + 1 >= 0 && oh0 + 1 < g.Ho;
+        if (ow < 0 || ow >= g.Wo || !(ok0 || ok1)) continue;
+        const double* src = Vin + j * ld_in + cbase;
+        const uint8_t* st = (mask.state != nullptr && j < mask.ncols) ? mask.state + mask.col_q[j] * mask.N + cbase : nullptr;
+        const int w0 = 2 * ow;
+        double v[2][2][2];          // [output][row][column]
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int h0 = 2 * (oh0 + k);
+            const bool okk = k == 0 ? ok0 : ok1;
+#pragma unroll
+            for (int bb = 0; bb < 2; ++bb) {
+                const int w = w0 + bb;
+                v[k][0][bb] = 0.0;
+                v[k][1][bb] = 0.0;
+                if (okk && w < g.W && unsigned(w - bx.y) < unsigned(bx.w)) {
+                    const int64_t o_in = h0 + int64_t(g.H) * w;
+                    const double2 x = *reinterpret_cast<const double2*>(src + o_in);
+                    const unsigned s2 = st != nullptr ? *reinterpret_cast<const unsigned short*>(st + o_in) : 0u;
+                    if (unsigned(h0 - bx.x) < unsigned(bx.z) && (s2 & 0xffu) == 0) v[k][0][bb] = x.x;
+                    if (unsigned(h0 + 1 - bx.x) < unsigned(bx.z) && (s2 >> 8) == 0) v[k][1][bb] = x.y;
+                }
+            }
+        }
+        double* dst = Vout + j * ld_out + int64_t(g.Ho) * ow + obase;
+        const int lo = max(first, 0), hi = min(first + win.wh, g.Ho);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            if (!(k == 0 ? ok0 : ok1)) continue;
+            const int oh = oh0 + k;
+            double acc = 0.0;
+            acc = acc + v[k][0][0];
+            acc = acc + v[k][0][1];
+            acc = acc + v[k][1][0];
+            acc = acc + v[k][1][1];
+            dst[oh] = acc * 0.25;           // the quotient by 4, exactly
+            if (pad_rows) {                 // whole sectors at both ends of the window's run of rows
+                if (oh == lo)
+                    for (int rr = lo & ~3; rr < lo; ++rr) dst[rr] = 0.0;
+                if (oh == hi - 1)
+                    for (int rr = hi; rr < ((hi + 3) & ~3); ++rr) dst[rr] = 0.0;
+            }
+        }
+    }
+}
+
 int launch_avgpool_windowed(cudaStream_t st, const PoolGeom& g, const RowMask& mask, const ColWindows& win,
                             int64_t col_base, const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
                             int64_t ncols, int64_t* launches) {
@@ -335,7 +405,13 @@ int launch_avgpool_windowed(cudaStream_t st, const PoolGeom& g, const RowMask& m
     const bool pairs = g.ph == 2 && g.pw == 2 && g.sh == 2 && g.sw == 2 && g.pad_t == 0 && g.pad_l == 0 &&
                        g.H % 2 == 0 && ld_in % 2 == 0 && (mask.state == nullptr || mask.N % 2 == 0);
     const bool pad_rows = g.Ho % 4 == 0 && ld_out % 4 == 0;      // image columns start on sector boundaries
-    if (pairs)
+    static const bool one_row = getenv("NNVB_POOL_ONE_ROW") != nullptr;
+    if (pairs && !one_row) {
+        const int per2 = (win.wh + 1) / 2 * win.ww * g.C;
+        const int th2 = per2 >= 256 ? 256 : 128;
+        dim3 grid2((unsigned)ceil_div(per2, th2), (unsigned)std::min<int64_t>(ncols, 8192));
+        avgpool_windowed_2x2_kernel<<<grid2, th2, 0, st>>>(g, mask, win, col_base, ncols, Vin, ld_in, Vout, ld_out, pad_rows);
+    } else if (pairs)
         avgpool_windowed_kernel<true><<<grid, threads, 0, st>>>(g, mask, win, col_base, ncols, Vin, ld_in, Vout, ld_out,
                                                                 pad_rows);
     else
