@@ -1306,10 +1306,11 @@ int run_layers(nnvb_batch* b) {
                             const int64_t ww = (co.ww - 1 + (L.cg.kw - 1) * L.cg.dw) / L.cg.sw + 1;
                             if (wh * ww <= 128) tot += (co.col1 - co.col0) * wh * ww * L.cg.Cout;
                         }
-                        if (tot > 0) {
-                            NNVB_TRY(b->wk->pack.ensure(sizeof(double) * tot, st));
+                        // an optimisation only: a copy that would take more than an eighth of the arena, or that
+                        // cannot be allocated, is left out and the bound reduction reads the columns
+                        if (tot > 0 && sizeof(double) * size_t(tot) <= ctx->arena_bytes / 8 &&
+                            b->wk->pack.ensure(sizeof(double) * tot, st) == NNVB_OK)
                             pack_base = b->wk->pack.as<double>();
-                        }
                     }
                 }
                 for (auto& co : b->cohorts) {
