@@ -55,10 +55,20 @@ typedef enum {
  *   FC       W[Out,In] column-major, b[Out]; In is indexed h-fastest
  *            (FullyConnectedLayer.m:56-66, :312)
  *   BN       mean/var/scale/offset[C], eps (BatchNormalizationLayer.m:311-327)
- *   AVGPOOL  pool[2], stride[2], pad[4]; zero padding counts in the divisor
- *            (AveragePooling2DLayer.m:378-386)
+ *   AVGPOOL  pool[2], stride[2], pad[4] (AveragePooling2DLayer.m:109-131).  The
+ *            reference averages a padded window in two different ways:
+ *            reach_star_single_input calls evaluate (:227-248), which on host
+ *            arrays is MatConvNet's vl_nnpool(..., 'Method', 'avg') — the sum is
+ *            divided by the number of window entries inside the image — and on
+ *            gpuArray inputs is avgpool with zero padding, which divides by
+ *            ph*pw like the pure-MATLAB compute_averageMap (:316-393).
+ *            avgpool_divisor selects the rule: NNVB_POOL_DIV_WINDOW (0) = ph*pw,
+ *            NNVB_POOL_DIV_INSIDE (1) = entries inside the image.  Without
+ *            padding the two agree.
  *   RELU     no parameters
  * Unused fields are ignored. */
+#define NNVB_POOL_DIV_WINDOW 0
+#define NNVB_POOL_DIV_INSIDE 1
 typedef struct {
     int32_t type;
     int32_t kh, kw, cin, cout;       /* conv: filter dims; fc: cout = Out, cin = In */
@@ -73,6 +83,8 @@ typedef struct {
     const double* bn_scale;
     const double* bn_offset;
     double bn_eps;
+    int32_t avgpool_divisor;         /* NNVB_POOL_DIV_* */
+    int32_t reserved;
 } nnvb_layer_desc;
 
 /* ---- options and statistics -------------------------------------------- */
@@ -238,13 +250,17 @@ int nnvb_batch_get_layer_ranges(nnvb_batch* b, int q, int relu_layer, double* lb
  *
  * Device-side tests per halfspace row G_h x <= g_h:
  *   - the minimum of G_h x - g_h over the output set's predicate box; a
- *     positive minimum proves the intersection empty (NNVB_VERDICT_EMPTY);
+ *     positive minimum proves the intersection empty (NNVB_VERDICT_EMPTY).
+ *     "Positive" means above 1e-6 * (1 + the sum of the magnitudes of the terms
+ *     of the minimum): the guard covers the rounding of a sum of 1e4..1e5 terms
+ *     and the feasibility tolerance of the LP solver that decides the same
+ *     question in the reference; rows nearer to zero stay undecided;
  *   - after a reach with opts.keep_constraints, a tighter lower bound of the
  *     row over the whole set: every ReLU predicate is replaced, last layer
  *     first, through its own relaxation rows (PosLin.m:716-735) by the affine
  *     form of its pre-activation, and the row left over the input predicates
- *     is minimised over their box; positive proves the intersection empty and
- *     is returned as the margin;
+ *     is minimised over their box; positive (same guard) proves the
+ *     intersection empty and is returned as the margin;
  *   - a witness: a point of the output set (input predicates at a corner of
  *     their box, each ReLU predicate at the lower envelope max(0,x) or on the
  *     chord of its triangle, whichever lowers the row) evaluated by a forward
@@ -269,6 +285,20 @@ int nnvb_batch_halfspace_margins(nnvb_batch* b, int q, const double* G, const do
  * when some row is proven non-empty, else NNVB_UNDECIDED. */
 int nnvb_batch_verify_robust(nnvb_batch* b, const int32_t* target, int kind,
                              int* verdict, int* status, double* margin_lo);
+
+/* The witness point the device builds for one halfspace row G x <= g of query
+ * q (G has N_out entries), for callers that want to check it against the
+ * constraint system of the set themselves: alpha[P] is the point's predicate
+ * vector in the reference's predicate order — input predicates at the end of
+ * their range that lowers the row, each ReLU predicate at max(0, x) or on the
+ * chord a*(x - l) of its triangle (PosLin.m:716-735) — x_out[N_out] (nullable)
+ * the network output the forward pass reached at that point, and *value
+ * (nullable) G x_out - g.  By construction x_out = c + V alpha of the output
+ * set and alpha satisfies pred_lb <= alpha <= pred_ub and C alpha <= d up to
+ * rounding.  Needs a reach with opts.keep_layer_bounds; not available with
+ * sharded generators (NNVB_E_UNSUPPORTED). */
+int nnvb_batch_halfspace_witness(nnvb_batch* b, int q, const double* G, double g,
+                                 double* alpha, double* x_out, double* value);
 
 /* ---- single-layer entry points ------------------------------------------- */
 
@@ -302,8 +332,11 @@ int nnvb_estimate_ranges(nnvb_ctx* ctx, int64_t N, int64_t P, const double* V,
  *           enqueueing two kernels on it.
  * Limit: 2*N <= NNVB_NOALLOC_SCRATCH_DOUBLES (N <= 262144); larger sets are
  * refused with NNVB_E_CAPACITY and a message.  The current device is used.  The
- * first call on a device looks up the scratch address (cudaGetSymbolAddress);
- * make that first call before starting any stream capture.  All calls on a
+ * first call on a device loads the module's device data (the 4 MiB appear
+ * on that GPU then, under lazy module loading) and looks up the scratch address
+ * (cudaGetSymbolAddress), which is cached for the life of the process and does
+ * not survive a cudaDeviceReset of that device; make that first call before
+ * starting any stream capture.  All calls on a
  * device share the scratch: calls that overlap on the GPU race, so issue them on
  * one stream or otherwise one after the other.  Nothing in the scratch needs to
  * be cleared between calls. */

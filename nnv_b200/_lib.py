@@ -22,6 +22,8 @@ NNVB_E_UNSUPPORTED = 5
 
 LAYER_CONV2D, LAYER_FC, LAYER_BN, LAYER_AVGPOOL2D, LAYER_RELU = 1, 2, 3, 4, 5
 
+POOL_DIV_WINDOW, POOL_DIV_INSIDE = 0, 1
+
 PROF_FAMILIES = ("conv", "fc", "bn", "avgpool", "ranges", "relax", "verify", "onehot")
 
 VERDICT_EMPTY = 1
@@ -45,6 +47,7 @@ class LayerDesc(C.Structure):
         ("W", c_double_p), ("b", c_double_p),
         ("bn_mean", c_double_p), ("bn_var", c_double_p), ("bn_scale", c_double_p), ("bn_offset", c_double_p),
         ("bn_eps", C.c_double),
+        ("avgpool_divisor", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
@@ -104,6 +107,8 @@ SIGNATURES = {
     "nnvb_batch_get_layer_ranges": (C.c_int, [C.c_void_p, C.c_int, C.c_int, c_double_p, c_double_p]),
     "nnvb_batch_halfspace_margins": (C.c_int, [C.c_void_p, C.c_int, c_double_p, c_double_p, C.c_int, c_double_p,
                                                c_int_p]),
+    "nnvb_batch_halfspace_witness": (C.c_int, [C.c_void_p, C.c_int, c_double_p, C.c_double, c_double_p, c_double_p,
+                                               c_double_p]),
     "nnvb_batch_verify_robust": (C.c_int, [C.c_void_p, c_int32_p, C.c_int, c_int_p, c_int_p, c_double_p]),
     "nnvb_layer_apply": (C.c_int, [C.c_void_p, C.POINTER(LayerDesc), C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                    c_double_p, c_double_p, c_int64_p]),

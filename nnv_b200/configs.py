@@ -12,7 +12,8 @@ BatchNormalizationLayer.m:72-77, AveragePooling2DLayer.m:109-131):
      "pad": (t,b,l,r), "stride": (sh,sw), "dilation": (dh,dw)}
     {"type": "fc", "W": [Out,In], "b": [Out]}          # In indexed h-fastest
     {"type": "bn", "mean","var","scale","offset": [C], "eps": float}
-    {"type": "avgpool", "pool": (ph,pw), "stride": (sh,sw), "pad": (t,b,l,r)}
+    {"type": "avgpool", "pool": (ph,pw), "stride": (sh,sw), "pad": (t,b,l,r),
+     "divisor": "inside" | "window"}    # padded windows: entries inside the image (default) or ph*pw
     {"type": "relu"}
 
 Query dicts describe one input set and its specification:
@@ -141,7 +142,13 @@ def forward_concrete(layers, x):
             for i in range(ph):
                 for j in range(pw):
                     y += xp[i: i + (ho - 1) * sh + 1: sh, j: j + (wo - 1) * sw + 1: sw, :]
-            x = y / (ph * pw)
+            if L.get("divisor", "inside") == "inside":
+                h0, w0 = np.arange(ho) * sh - pt, np.arange(wo) * sw - pl
+                nh = np.minimum(h0 + ph, x.shape[0]) - np.maximum(h0, 0)
+                nw = np.minimum(w0 + pw, x.shape[1]) - np.maximum(w0, 0)
+                x = y / np.maximum(np.outer(nh, nw), 1)[:, :, None]
+            else:
+                x = y / (ph * pw)
         elif t == "relu":
             x = np.maximum(x, 0.0)
         else:

@@ -162,7 +162,15 @@ int launch_bn_f64(cudaStream_t st, const ChanAffine& bn, int64_t plane, int64_t 
 struct PoolGeom {
     int H, W, C, Ho, Wo;
     int ph, pw, sh, sw, pad_t, pad_l;
+    int clip;               // 1: the divisor counts only the window entries inside the image (padding excluded)
 };
+// Divisor of the average for the window whose first entry is (h0, w0) in unpadded coordinates.
+__host__ __device__ inline double pool_divisor(const PoolGeom& g, int h0, int w0) {
+    if (!g.clip) return double(g.ph * g.pw);
+    const int h1 = h0 + g.ph < g.H ? h0 + g.ph : g.H, w1 = w0 + g.pw < g.W ? w0 + g.pw : g.W;
+    const int n = (h1 - (h0 > 0 ? h0 : 0)) * (w1 - (w0 > 0 ? w0 : 0));
+    return double(n > 0 ? n : 1);
+}
 // box (nullable): per-column input windows, indexed like Vin's columns; entries outside count as zero.
 int launch_avgpool_f64(cudaStream_t st, const PoolGeom& g, const RowMask& mask, const int4* box, const double* Vin,
                        int64_t ld_in, double* Vout, int64_t ld_out, int64_t ncols, int64_t* launches);
@@ -197,7 +205,7 @@ struct WinCohorts {
     WinCohort c[MAX_WIN_COHORTS];
 };
 size_t range_windows_scratch_ints(const WinCohorts& wc, int nq, int64_t ncols);
-int range_windows_slices(int H, int W, int C, int nq);
+int range_windows_slices(int H, int W, int C, int nq, int sm_count);
 
 struct ReluWork {
     int nq;
@@ -263,17 +271,19 @@ int launch_relu_append(cudaStream_t st, const ReluWork& w, int64_t ncols_old, in
                        int64_t* new_qcol_off, int32_t* new_qcol_idx, int64_t* launches);
 
 // Halfspace rows against output sets; see relu_star.cu.  Pair p tests row G[p] (length Nout)
-// with offset g[p] on query pair_q[p]; margin[p] = box minimum of G x - g (nullable);
+// with offset g[p] on query pair_q[p]; margin (nullable, 2*n_pairs doubles): margin[p] = box minimum of
+// G x - g, margin[n_pairs + p] = sum of the magnitudes of its terms;
 // r_out (nullable) receives the predicate coefficients of pair p at r_off[p] + position.
 int launch_halfspace_pairs(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t Nout, int64_t ld,
                            const double* V, const int64_t* qcol_off, const int32_t* qcol_idx, const double* pl,
                            const double* pu, const double* G, const double* g, double* margin, double* r_out,
                            const int64_t* r_off, const int64_t* col_pos, int add_center, double* part,
                            int64_t* launches);
-constexpr int HS_SPLIT = 32;     // slices of a query's column list; `part` holds n_pairs * HS_SPLIT doubles
+constexpr int HS_SPLIT = 32;     // slices of a query's column list; `part` holds 2 * n_pairs * HS_SPLIT doubles
 // Back-substitution bound of halfspace rows through the recorded ReLU relaxations (see relu_star.cu): r holds
 // each pair's row by predicate position (as launch_halfspace_pairs writes it) and is overwritten;
-// bound[p] receives a lower bound of G x - g over the whole star set of the pair's query.
+// bound[p] receives a lower bound of G x - g over the whole star set of the pair's query, bound[n_pairs + p]
+// the sum of the magnitudes of its terms.
 struct BacksubLayer {
     const double* G;            // crossing rows, per query a kq x P_in block (column-major) at G_off[q]
     const int64_t* G_off;       // [nq+1]
@@ -302,7 +312,7 @@ int launch_witness_x0_star(cudaStream_t st, int n_pairs, const int32_t* pair_q, 
                            int64_t* launches);
 int launch_witness_relu(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t N, int64_t ld, double* X,
                         const double* lb, const double* ub, const int32_t* rank, const int64_t* P_in,
-                        const double* r, const int64_t* r_off, int64_t* launches);
+                        const double* r, const int64_t* r_off, double* alpha, int64_t* launches);
 int launch_witness_value(cudaStream_t st, int n_pairs, int64_t Nout, int64_t ld, const double* X, const double* G,
                          const double* g, double* value, double* scale, int64_t* launches);
 

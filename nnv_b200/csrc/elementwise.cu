@@ -44,8 +44,9 @@ __global__ void bn_f64_kernel(ChanAffine bn, int64_t plane, int64_t N, double* _
     }
 }
 
-// AveragePooling2DLayer.compute_averageMap, AveragePooling2DLayer.m:316-393: window sum in
-// row-major order of the window, divided by ph*pw (zero padding counted).
+// AveragePooling2DLayer.evaluate, AveragePooling2DLayer.m:227-248 (semantics of compute_averageMap,
+// :316-393): window sum in row-major order of the window, divided by ph*pw or, with g.clip, by the
+// number of window entries inside the image (the two rules the reference's back ends use).
 // One thread per output element of a column; grid.y walks the columns.
 // Rows that the preceding ReLU step cleared are read as zero through `mask` (they were not zeroed in memory).
 __global__ void avgpool_f64_kernel(PoolGeom g, RowMask mask, const int4* __restrict__ box,
@@ -59,7 +60,7 @@ __global__ void avgpool_f64_kernel(PoolGeom g, RowMask mask, const int4* __restr
     const int c = int(o / (int64_t(g.Ho) * g.Wo));
     const int h0 = oh * g.sh - g.pad_t;
     const int w0 = ow * g.sw - g.pad_l;
-    const double div = double(g.ph * g.pw);
+    const double div = pool_divisor(g, h0, w0);
     const int64_t cbase = int64_t(c) * g.H * g.W;
     for (int64_t j = blockIdx.y; j < ncols; j += gridDim.y) {
         const double* src = Vin + j * ld_in + cbase;
@@ -111,7 +112,7 @@ __global__ void avgpool_onehot_kernel(PoolGeom g, HotCols hot, int64_t K_loc, do
     const int h0 = oh * g.sh - g.pad_t, w0 = ow * g.sw - g.pad_l;
     const bool covers = cc == c && h >= h0 && h < h0 + g.ph && w >= w0 && w < w0 + g.pw;
     // same arithmetic as the dense kernel on this column: a sum of zeros and a single entry, then the division
-    const double val = covers ? (0.0 + sc) / double(g.ph * g.pw) : 0.0;
+    const double val = covers ? (0.0 + sc) / pool_divisor(g, h0, w0) : 0.0;
     Vout[t * ld_out + oh + int64_t(g.Ho) * (ow + int64_t(g.Wo) * cc)] = val;
 }
 
@@ -250,7 +251,6 @@ __global__ void avgpool_windowed_kernel(PoolGeom g, RowMask mask, ColWindows win
     const int c = r2 / win.ww;
     const int64_t cbase = int64_t(c) * g.H * g.W;
     const int64_t obase = int64_t(g.Ho) * g.Wo * c;
-    const double div = double(g.ph * g.pw);
     for (int64_t jj = blockIdx.y; jj < ncols; jj += gridDim.y) {
         const int64_t j = col_base + jj;
         const int4 bx = win.box[j];
@@ -310,7 +310,7 @@ __global__ void avgpool_windowed_kernel(PoolGeom g, RowMask mask, ColWindows win
             }
         }
         double* dst = Vout + j * ld_out + int64_t(g.Ho) * ow + obase;
-        dst[oh] = PAIRS ? acc * 0.25 : acc / div;       // a quotient by 4 is exact either way
+        dst[oh] = PAIRS ? acc * 0.25 : acc / pool_divisor(g, h0, w0);       // a quotient by 4 is exact either way
         if (pad_rows) {
             // complete the 32-byte sectors at both ends of the window's run of rows with zeros (the dense
             // tensor is zero there): a partly written sector costs the memory system a read on top of the write

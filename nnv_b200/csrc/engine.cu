@@ -133,6 +133,7 @@ struct WorkBufs {
 
 struct nnvb_ctx {
     int device = 0;
+    int sm_count = 1;       // multiprocessors of the device: grids are sized in multiples of it
     cudaStream_t stream = nullptr;
     char* arena = nullptr;
     size_t arena_bytes = 0;
@@ -389,7 +390,7 @@ const char* nnvb_strerror(int status) {
     }
 }
 
-int nnvb_abi_version(void) { return 1; }
+int nnvb_abi_version(void) { return 2; }
 
 int nnvb_init(int device, size_t arena_bytes, nnvb_ctx** out) {
     NNVB_REQUIRE(out != nullptr, "nnvb_init: out is NULL");
@@ -412,6 +413,7 @@ int nnvb_init(int device, size_t arena_bytes, nnvb_ctx** out) {
     }
     auto ctx = new nnvb_ctx();
     ctx->device = device;
+    ctx->sm_count = std::max(1, prop.multiProcessorCount);
     NNVB_CUDA(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
     if (arena_bytes == 0) {
         size_t free_b = 0, total_b = 0;
@@ -615,6 +617,16 @@ int nnvb_net_create(nnvb_ctx* ctx, const nnvb_layer_desc* layers, int n_layers, 
                 g.ph = d.pool[0]; g.pw = d.pool[1];
                 g.sh = d.stride[0]; g.sw = d.stride[1];
                 g.pad_t = d.pad[0]; g.pad_l = d.pad[2];
+                if (d.avgpool_divisor != NNVB_POOL_DIV_WINDOW && d.avgpool_divisor != NNVB_POOL_DIV_INSIDE) {
+                    set_error("layer %d (avgpool): unknown divisor rule %d", li, d.avgpool_divisor);
+                    return fail(NNVB_E_ARG);
+                }
+                g.clip = d.avgpool_divisor == NNVB_POOL_DIV_INSIDE ? 1 : 0;
+                // a window that lies in the padding altogether has no entry to average
+                if (d.pad[0] >= g.ph || d.pad[1] >= g.ph || d.pad[2] >= g.pw || d.pad[3] >= g.pw) {
+                    set_error("layer %d (avgpool): padding must be smaller than the pooling window", li);
+                    return fail(NNVB_E_ARG);
+                }
                 const int64_t hp = H + d.pad[0] + d.pad[1], wp = W + d.pad[2] + d.pad[3];
                 if (hp < g.ph || wp < g.pw) {
                     set_error("layer %d (avgpool): window larger than padded input", li);
@@ -1025,7 +1037,7 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
             for (int q = 0; q < nq; ++q) { win_seg.push_back(int32_t(c)); c += co.qn[q]; }
         }
     }
-    const int win_slices = wc.n > 0 ? range_windows_slices(int(img_h), int(img_w), int(img_c), nq) : 0;
+    const int win_slices = wc.n > 0 ? range_windows_slices(int(img_h), int(img_w), int(img_c), nq, ctx->sm_count) : 0;
     // every other cohort is read as whole columns
     for (size_t k = 0; k < b->cohorts.size(); ++k)
         if (!is_win[k]) NNVB_TRY(ensure_clean(b, b->cohorts[k]));
@@ -1041,7 +1053,7 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
         total_P += pq;
         max_P = std::max(max_P, pq);
     }
-    const int64_t want_chunks = std::max<int64_t>(1, ceil_div(148 * 16, row_blocks));
+    const int64_t want_chunks = std::max<int64_t>(1, ceil_div(int64_t(ctx->sm_count) * 16, row_blocks));
     int64_t CH = std::max<int64_t>(32, ceil_div(total_P, want_chunks));
     CH = std::min<int64_t>(CH, 1024);
     // the classify kernel adds a query's chunk partials one after the other: at most 96 chunks per query
@@ -1577,7 +1589,7 @@ int output_ranges(nnvb_batch* b) {
 
 // Run the affine layers and the relaxed ReLU over witness points X [ld x n] (one per pair).
 int witness_forward(nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, int64_t* ldx, const double* d_r,
-                    const int64_t* d_roff) {
+                    const int64_t* d_roff, double* d_alpha = nullptr) {
     nnvb_net* net = b->net;
     nnvb_ctx* ctx = net->ctx;
     cudaStream_t st = ctx->stream;
@@ -1618,13 +1630,18 @@ int witness_forward(nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, i
         } else if (L.type == NNVB_LAYER_RELU) {
             ReluLayerRecord& r = *b->wk->relu[relu_i++];
             NNVB_TRY(launch_witness_relu(st, n, d_pair_q, N, ld, cur, r.lb.as<double>(), r.ub.as<double>(),
-                                         r.rank.as<int32_t>(), r.P_in_dev.as<int64_t>(), d_r, d_roff, &ctx->launches));
+                                         r.rank.as<int32_t>(), r.P_in_dev.as<int64_t>(), d_r, d_roff, d_alpha,
+                                         &ctx->launches));
         }
     }
     *X = cur;
     *ldx = ld;
     return NNVB_OK;
 }
+
+// Relative guard on "this lower bound is positive": a bound b with term magnitudes M proves emptiness only
+// when b > EMPTY_GUARD * (1 + M).
+constexpr double EMPTY_GUARD = 1e-6;
 
 // Test halfspace rows against the reached sets: pair p = (query pair_q[p], row G[p], offset g[p]).
 // status: EMPTY when the box minimum of the row is positive; NONEMPTY when the greedy witness
@@ -1642,7 +1659,7 @@ int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vec
     NNVB_TRY(b->wk->hs_G.ensure(sizeof(double) * n * Nout, st));
     NNVB_TRY(b->wk->hs_g.ensure(sizeof(double) * n, st));
     NNVB_TRY(b->wk->hs_q.ensure(sizeof(int32_t) * n, st));
-    NNVB_TRY(b->wk->hs_margin.ensure(sizeof(double) * n * (1 + HS_SPLIT), st));
+    NNVB_TRY(b->wk->hs_margin.ensure(sizeof(double) * n * (2 + 2 * HS_SPLIT), st));
     NNVB_CUDA(cudaMemcpyAsync(b->wk->hs_G.p, G.data(), sizeof(double) * n * Nout, cudaMemcpyHostToDevice, st));
     NNVB_CUDA(cudaMemcpyAsync(b->wk->hs_g.p, g.data(), sizeof(double) * n, cudaMemcpyHostToDevice, st));
     NNVB_CUDA(cudaMemcpyAsync(b->wk->hs_q.p, pair_q.data(), sizeof(int32_t) * n, cudaMemcpyHostToDevice, st));
@@ -1652,13 +1669,19 @@ int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vec
     NNVB_TRY(launch_halfspace_pairs(st, n, b->wk->hs_q.as<int32_t>(), Nout, b->ld, b->V, qoff, qidx, b->wk->pl.as<double>(),
                                     b->wk->pu.as<double>(), b->wk->hs_G.as<double>(), b->wk->hs_g.as<double>(),
                                     b->wk->hs_margin.as<double>(), nullptr, nullptr, b->wk->col_pos.as<int64_t>(),
-                                    add_center, b->wk->hs_margin.as<double>() + n, &ctx->launches));
-    NNVB_TRY(allreduce(ctx, b->wk->hs_margin.as<double>(), n));
-    NNVB_CUDA(cudaMemcpyAsync(margin.data(), b->wk->hs_margin.p, sizeof(double) * n, cudaMemcpyDeviceToHost, st));
+                                    add_center, b->wk->hs_margin.as<double>() + 2 * n, &ctx->launches));
+    NNVB_TRY(allreduce(ctx, b->wk->hs_margin.as<double>(), 2 * int64_t(n)));
+    std::vector<double> mm(2 * size_t(n));
+    NNVB_CUDA(cudaMemcpyAsync(mm.data(), b->wk->hs_margin.p, sizeof(double) * 2 * n, cudaMemcpyDeviceToHost, st));
     NNVB_TRY(sync(ctx));
+    std::copy(mm.begin(), mm.begin() + n, margin.begin());
     std::vector<int> open;
     for (int p = 0; p < n; ++p) {
-        if (margin[p] > 0.0) status[p] = NNVB_VERDICT_EMPTY;
+        // The minimum is a sum of 1e4..1e5 rounded terms in an order of its own; "positive" has to hold beyond
+        // what that rounding can move, and beyond the feasibility tolerance of the LP that decides the same
+        // question in Star.isEmptySet: the same relative guard as the witness test below.  Rows closer to zero
+        // stay undecided and go to the LP.
+        if (margin[p] > EMPTY_GUARD * (1.0 + mm[n + p])) status[p] = NNVB_VERDICT_EMPTY;
         else if (b->box_implies_C[pair_q[p]]) open.push_back(p);
     }
     // the witness pass needs the bounds of every ReLU layer, the back-substitution bound its crossing rows
@@ -1739,24 +1762,24 @@ int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vec
         }
         if (have_G) {
             // after the witness pass: the bound overwrites the rows
-            NNVB_TRY(b->wk->hs_bound.ensure(sizeof(double) * m, st));
+            NNVB_TRY(b->wk->hs_bound.ensure(sizeof(double) * 2 * m, st));
             NNVB_TRY(launch_backsub(st, bs, m, b->wk->hs_q.as<int32_t>(), Nout, b->ld, b->V, b->wk->hs_G.as<double>(),
                                     b->wk->hs_g.as<double>(), b->wk->hs_r.as<double>(), b->wk->hs_roff.as<int64_t>(), qoff, qidx,
                                     b->wk->pl.as<double>(), b->wk->pu.as<double>(), b->wk->hs_bound.as<double>(),
                                     &ctx->launches));
         }
-        std::vector<double> val(m, 0.0), scale(m, 0.0), bound(m, 0.0);
+        std::vector<double> val(m, 0.0), scale(m, 0.0), bound(2 * size_t(m), 0.0);
         if (have_bounds) {
             NNVB_CUDA(cudaMemcpyAsync(val.data(), b->wk->hs_val.p, sizeof(double) * m, cudaMemcpyDeviceToHost, st));
             NNVB_CUDA(cudaMemcpyAsync(scale.data(), b->wk->hs_scale.p, sizeof(double) * m, cudaMemcpyDeviceToHost, st));
         }
         if (have_G)
-            NNVB_CUDA(cudaMemcpyAsync(bound.data(), b->wk->hs_bound.p, sizeof(double) * m, cudaMemcpyDeviceToHost, st));
+            NNVB_CUDA(cudaMemcpyAsync(bound.data(), b->wk->hs_bound.p, sizeof(double) * 2 * m, cudaMemcpyDeviceToHost, st));
         NNVB_TRY(sync(ctx));
         for (int i = 0; i < m; ++i) {
             const int pp = open[c0 + i];
-            // a positive lower bound over the whole set: empty, with the bound as the margin
-            if (have_G && bound[i] > 0.0) { status[pp] = NNVB_VERDICT_EMPTY; margin[pp] = bound[i]; }
+            // a lower bound over the whole set that is positive beyond rounding: empty, with the bound as the margin
+            if (have_G && bound[i] > EMPTY_GUARD * (1.0 + bound[m + i])) { status[pp] = NNVB_VERDICT_EMPTY; margin[pp] = bound[i]; }
             // accept only points clearly inside the halfspace: well beyond the feasibility
             // tolerance of an LP solver deciding the same question
             else if (have_bounds && val[i] < -1e-6 * (1.0 + scale[i])) status[pp] = NNVB_VERDICT_NONEMPTY;
@@ -1984,6 +2007,85 @@ int nnvb_batch_halfspace_margins(nnvb_batch* b, int q, const double* G, const do
     for (int h = 0; h < nh; ++h) {
         margin_lo[h] = margin[h];
         if (status) status[h] = st[h];
+    }
+    return NNVB_OK;
+}
+
+int nnvb_batch_halfspace_witness(nnvb_batch* b, int q, const double* G, double g, double* alpha, double* x_out,
+                                 double* value) {
+    NNVB_TRY(check_reached(b, q));
+    NNVB_REQUIRE(G && alpha, "nnvb_batch_halfspace_witness: NULL argument");
+    nnvb_ctx* ctx = b->net->ctx;
+    if (ctx->world > 1) {
+        set_error("witness points are not handed out with sharded generators");
+        return NNVB_E_UNSUPPORTED;
+    }
+    for (int i = 0; i < b->net->n_relu; ++i)
+        if (!b->wk->relu[i]->has_bounds) {
+            set_error("layer bounds were not kept: set opts.keep_layer_bounds");
+            return NNVB_E_STATE;
+        }
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    cudaStream_t st = ctx->stream;
+    const int64_t Nout = b->N, P = b->h_Pglob[q];
+    int64_t max_ld = b->ld0;
+    for (const Layer& L : b->net->layers) max_ld = std::max(max_ld, lead_dim(L.Ho * L.Wo * L.Co));
+    const int32_t pq = q;
+    const int64_t roff[2] = {0, P};
+    NNVB_TRY(b->wk->hs_G.ensure(sizeof(double) * Nout, st));
+    NNVB_TRY(b->wk->hs_g.ensure(sizeof(double), st));
+    NNVB_TRY(b->wk->hs_q.ensure(sizeof(int32_t), st));
+    NNVB_TRY(b->wk->hs_r.ensure(sizeof(double) * 2 * std::max<int64_t>(P, 1), st));      // coefficients, then alpha
+    NNVB_TRY(b->wk->hs_roff.ensure(sizeof(int64_t) * 2, st));
+    NNVB_TRY(b->wk->hs_val.ensure(sizeof(double), st));
+    NNVB_TRY(b->wk->hs_scale.ensure(sizeof(double), st));
+    NNVB_TRY(b->wk->wit[0].ensure(sizeof(double) * max_ld, st));
+    NNVB_TRY(b->wk->wit[1].ensure(sizeof(double) * max_ld, st));
+    NNVB_TRY(h2d_small(ctx, b->wk->hs_G.p, G, sizeof(double) * Nout));
+    NNVB_TRY(h2d_small(ctx, b->wk->hs_g.p, &g, sizeof(double)));
+    NNVB_TRY(h2d_small(ctx, b->wk->hs_q.p, &pq, sizeof(int32_t)));
+    NNVB_TRY(h2d_small(ctx, b->wk->hs_roff.p, roff, sizeof(roff)));
+    double* d_r = b->wk->hs_r.as<double>();
+    double* d_alpha = d_r + std::max<int64_t>(P, 1);
+    NNVB_CUDA(cudaMemsetAsync(d_alpha, 0, sizeof(double) * P, st));
+    const int64_t* qoff = b->wk->qcol_off[b->list_cur].as<int64_t>();
+    const int32_t* qidx = b->wk->qcol_idx[b->list_cur].as<int32_t>();
+    NNVB_TRY(launch_halfspace_pairs(st, 1, b->wk->hs_q.as<int32_t>(), Nout, b->ld, b->V, qoff, qidx, b->wk->pl.as<double>(),
+                                    b->wk->pu.as<double>(), b->wk->hs_G.as<double>(), b->wk->hs_g.as<double>(), nullptr, d_r,
+                                    b->wk->hs_roff.as<int64_t>(), b->wk->col_pos.as<int64_t>(), 1, nullptr, &ctx->launches));
+    if (b->kind == 1) {
+        NNVB_TRY(launch_witness_x0_bounds(st, 1, b->wk->hs_q.as<int32_t>(), b->N0, b->ld0, b->d_in.as<double>(), d_r,
+                                          b->wk->hs_roff.as<int64_t>(), b->wk->wit[0].as<double>(), &ctx->launches));
+    } else {
+        int64_t ncols0 = b->nq;
+        std::vector<int64_t> gen0(b->nq + 1);
+        for (int k = 0; k < b->nq; ++k) { gen0[k] = ncols0; ncols0 += b->P0_loc[k]; }
+        gen0[b->nq] = ncols0;
+        NNVB_TRY(b->wk->gen_off.ensure(sizeof(int64_t) * (b->nq + 1), st));
+        NNVB_TRY(h2d_small(ctx, b->wk->gen_off.p, gen0.data(), sizeof(int64_t) * (b->nq + 1)));
+        NNVB_TRY(launch_witness_x0_star(st, 1, b->wk->hs_q.as<int32_t>(), b->N0, b->ld0, b->ld0, b->d_in.as<double>(),
+                                        b->wk->gen_off.as<int64_t>(), b->d_in_meta.as<double>(),
+                                        b->d_in_meta.as<double>() + ncols0, d_r, b->wk->hs_roff.as<int64_t>(),
+                                        b->d_in_pos.as<int64_t>(), 1, b->wk->wit[0].as<double>(), &ctx->launches));
+    }
+    double* X = nullptr;
+    int64_t ldx = 0;
+    NNVB_TRY(witness_forward(b, 1, b->wk->hs_q.as<int32_t>(), &X, &ldx, d_r, b->wk->hs_roff.as<int64_t>(), d_alpha));
+    NNVB_TRY(launch_witness_value(st, 1, Nout, ldx, X, b->wk->hs_G.as<double>(), b->wk->hs_g.as<double>(),
+                                  b->wk->hs_val.as<double>(), b->wk->hs_scale.as<double>(), &ctx->launches));
+    std::vector<double> r(size_t(std::max<int64_t>(P, 1)));
+    if (P > 0) {
+        NNVB_CUDA(cudaMemcpyAsync(r.data(), d_r, sizeof(double) * P, cudaMemcpyDeviceToHost, st));
+        NNVB_CUDA(cudaMemcpyAsync(alpha, d_alpha, sizeof(double) * P, cudaMemcpyDeviceToHost, st));
+    }
+    if (x_out) NNVB_CUDA(cudaMemcpyAsync(x_out, X, sizeof(double) * Nout, cudaMemcpyDeviceToHost, st));
+    if (value) NNVB_CUDA(cudaMemcpyAsync(value, b->wk->hs_val.p, sizeof(double), cudaMemcpyDeviceToHost, st));
+    NNVB_TRY(sync(ctx));
+    // the input predicates sit at the end of their range that lowers the row (the x0 kernels' rule)
+    const int64_t P0 = b->P0[q];
+    for (int64_t j = 0; j < P0; ++j) {
+        if (b->kind == 1) alpha[j] = r[j] > 0.0 ? -1.0 : 1.0;
+        else alpha[j] = r[j] > 0.0 ? b->h_pl[q][j] : b->h_pu[q][j];
     }
     return NNVB_OK;
 }

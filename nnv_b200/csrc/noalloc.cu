@@ -30,6 +30,7 @@ static __device__ __align__(256) double g_scratch[SCRATCH_DOUBLES];
 // only a handle; its device address comes from cudaGetSymbolAddress with that
 // device current.
 double* g_scratch_addr[MAX_DEVICES] = {nullptr};
+int g_sm_count[MAX_DEVICES] = {0};
 std::mutex g_setup_mutex;
 
 // partial[chunk][0][i] += max(v,0)*pl + min(v,0)*pu over the chunk's columns, [1] likewise with pu/pl.
@@ -87,22 +88,26 @@ extern "C" int nnvb_estimate_ranges_noalloc(void* stream, int64_t N, int64_t P, 
     NNVB_CUDA(cudaGetDevice(&dev));
     NNVB_REQUIRE(dev >= 0 && dev < MAX_DEVICES, "nnvb_estimate_ranges_noalloc: device index %d not supported", dev);
     double* scratch = nullptr;
+    int sms = 0;
     {
-        // first call on this device: look the scratch address up once
+        // first call on this device: look the scratch address (and the SM count) up once.  The address is
+        // cached for the life of the process; it does not survive a cudaDeviceReset of that device.
         std::lock_guard<std::mutex> lock(g_setup_mutex);
         if (g_scratch_addr[dev] == nullptr) {
             void* p = nullptr;
             NNVB_CUDA(cudaGetSymbolAddress(&p, g_scratch));
+            NNVB_CUDA(cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
             g_scratch_addr[dev] = static_cast<double*>(p);
         }
         scratch = g_scratch_addr[dev];
+        sms = g_sm_count[dev] > 0 ? g_sm_count[dev] : 1;
     }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     // as many column chunks as the scratch holds, at least 64 columns each, at most what fills the GPU
     int64_t max_chunks = SCRATCH_DOUBLES / (2 * N);
     int64_t want = (P + 63) / 64;
     const int64_t row_blocks = (N + 255) / 256;
-    const int64_t fill = (148 * 8 + row_blocks - 1) / row_blocks;
+    const int64_t fill = (int64_t(sms) * 8 + row_blocks - 1) / row_blocks;
     if (want > fill) want = fill;
     if (want > max_chunks) want = max_chunks;
     if (want > 65535) want = 65535;

@@ -677,7 +677,7 @@ halfspace_pairs_kernel(const int32_t* __restrict__ pair_q, int64_t Nout, int64_t
     const int p = blockIdx.x;
     const int q = pair_q[p];
     const double* Gr = G + int64_t(p) * Nout;
-    double acc = 0.0;
+    double acc = 0.0, mag = 0.0;
     // blockIdx.y takes one contiguous slice of the query's column list
     const int64_t q0 = qcol_off[q], q1 = qcol_off[q + 1];
     const int64_t per = (q1 - q0 + gridDim.y - 1) / gridDim.y;
@@ -687,36 +687,51 @@ halfspace_pairs_kernel(const int32_t* __restrict__ pair_q, int64_t Nout, int64_t
         const double* v = V + col * ld;
         double r = 0.0;
         for (int64_t o = 0; o < Nout; ++o) r = fma(Gr[o], v[o], r);
-        acc += fmin(r * pl[col], r * pu[col]);
+        const double t = fmin(r * pl[col], r * pu[col]);
+        acc += t;
+        mag += fabs(t);
         if (r_out) r_out[r_off[p] + col_pos[col]] = r;     // position in the query's predicate order
     }
-    __shared__ double s[256];
+    __shared__ double s[256], sm[256];
     s[threadIdx.x] = acc;
+    sm[threadIdx.x] = mag;
     __syncthreads();
     for (int o = 128; o; o >>= 1) {
-        if (threadIdx.x < o) s[threadIdx.x] += s[threadIdx.x + o];
+        if (threadIdx.x < o) { s[threadIdx.x] += s[threadIdx.x + o]; sm[threadIdx.x] += sm[threadIdx.x + o]; }
         __syncthreads();
     }
-    if (threadIdx.x == 0 && part) part[int64_t(p) * gridDim.y + blockIdx.y] = s[0];
+    if (threadIdx.x == 0 && part) {
+        part[(int64_t(p) * gridDim.y + blockIdx.y) * 2] = s[0];
+        part[(int64_t(p) * gridDim.y + blockIdx.y) * 2 + 1] = sm[0];
+    }
 }
 
-// margin[p] = (centre term) + the slices' partial minima, added in slice order.
+// margin[p] = (centre term) + the slices' partial minima, added in slice order; margin[n_pairs + p] = the sum
+// of the magnitudes of every term that went into it (what a rounding guard on the sign of margin[p] scales with).
 __global__ void halfspace_margin_kernel(int n_pairs, int n_split, const int32_t* __restrict__ pair_q, int64_t Nout,
                                         int64_t ld, const double* __restrict__ V, const double* __restrict__ G,
                                         const double* __restrict__ g, const double* __restrict__ part,
                                         double* __restrict__ margin, int add_center) {
     const int p = blockIdx.x * blockDim.x + threadIdx.x;
     if (p >= n_pairs) return;
-    double r = 0.0;
+    double r = 0.0, mag = 0.0;
     if (add_center) {                          // with sharded generators only one rank adds the centre term
         const double* Gr = G + int64_t(p) * Nout;
         const double* v = V + int64_t(pair_q[p]) * ld;
-        for (int64_t o = 0; o < Nout; ++o) r = fma(Gr[o], v[o], r);
+        for (int64_t o = 0; o < Nout; ++o) {
+            r = fma(Gr[o], v[o], r);
+            mag += fabs(Gr[o] * v[o]);
+        }
         r -= g[p];
+        mag += fabs(g[p]);
     }
     double sum = 0.0;
-    for (int s = 0; s < n_split; ++s) sum += part[int64_t(p) * n_split + s];
+    for (int s = 0; s < n_split; ++s) {
+        sum += part[(int64_t(p) * n_split + s) * 2];
+        mag += part[(int64_t(p) * n_split + s) * 2 + 1];
+    }
     margin[p] = r + sum;
+    margin[n_pairs + p] = mag;
 }
 
 // ---------------------------------------------------------------------------
@@ -740,13 +755,17 @@ backsub_kernel(BacksubLayers layers, const int32_t* __restrict__ pair_q, int64_t
     const int q = pair_q[p];
     double* rp = r + r_off[p];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    __shared__ double red[256];
-    double konst = 0.0;                     // kept by thread 0
+    __shared__ double red[256], redm[256];
+    double konst = 0.0, kmag = 0.0;         // kept by thread 0; kmag: magnitudes of the terms of the bound
     if (tid == 0) {
         const double* Gr = Gh + int64_t(p) * Nout;
         const double* v = V + int64_t(q) * ld;
-        for (int64_t o = 0; o < Nout; ++o) konst = fma(Gr[o], v[o], konst);
+        for (int64_t o = 0; o < Nout; ++o) {
+            konst = fma(Gr[o], v[o], konst);
+            kmag += fabs(Gr[o] * v[o]);
+        }
         konst -= gh[p];
+        kmag += fabs(gh[p]);
     }
     int64_t P_first = qcol_off[q + 1] - qcol_off[q];
     for (int L = layers.n - 1; L >= 0; --L) {
@@ -756,7 +775,7 @@ backsub_kernel(BacksubLayers layers, const int32_t* __restrict__ pair_q, int64_t
         const int64_t Pin = rec.P_in[q];
         P_first = Pin;
         // weights of the pre-activations, stored over the coefficients they replace
-        double part = 0.0;
+        double part = 0.0, pmag = 0.0;
         for (int64_t t = tid; t < kq; t += 256) {
             const double rho = rp[Pin + t];
             const double l = rec.l[c0 + t], u = rec.u[c0 + t], c = rec.c[c0 + t];
@@ -764,19 +783,22 @@ backsub_kernel(BacksubLayers layers, const int32_t* __restrict__ pair_q, int64_t
             if (rho >= 0.0) {
                 w = (u >= -l) ? rho : 0.0;
                 part += w * c;
+                pmag += fabs(w * c);
             } else {
                 w = rho * (u / (u - l));
                 part += w * (c - l);
+                pmag += fabs(w * c) + fabs(w * l);
             }
             rp[Pin + t] = w;
         }
         red[tid] = part;
+        redm[tid] = pmag;
         __syncthreads();
         for (int o = 128; o; o >>= 1) {
-            if (tid < o) red[tid] += red[tid + o];
+            if (tid < o) { red[tid] += red[tid + o]; redm[tid] += redm[tid + o]; }
             __syncthreads();
         }
-        if (tid == 0) konst += red[0];
+        if (tid == 0) { konst += red[0]; kmag += redm[0]; }
         // r[j] += sum_t w_t G[t, j]: a warp per earlier predicate, lanes over the layer's crossing neurons
         const double* Gq = rec.G + rec.G_off[q];
         for (int64_t j = warp; j < Pin; j += 8) {
@@ -788,18 +810,24 @@ backsub_kernel(BacksubLayers layers, const int32_t* __restrict__ pair_q, int64_t
         __syncthreads();
     }
     // box minimum over what is left: the predicates of the input set
-    double part = 0.0;
+    double part = 0.0, pmag = 0.0;
     for (int64_t j = tid; j < P_first; j += 256) {
         const int64_t col = qcol_idx[qcol_off[q] + j];
-        part += fmin(rp[j] * pl[col], rp[j] * pu[col]);
+        const double t = fmin(rp[j] * pl[col], rp[j] * pu[col]);
+        part += t;
+        pmag += fabs(t);
     }
     red[tid] = part;
+    redm[tid] = pmag;
     __syncthreads();
     for (int o = 128; o; o >>= 1) {
-        if (tid < o) red[tid] += red[tid + o];
+        if (tid < o) { red[tid] += red[tid + o]; redm[tid] += redm[tid + o]; }
         __syncthreads();
     }
-    if (tid == 0) bound[p] = konst + red[0];
+    if (tid == 0) {
+        bound[p] = konst + red[0];
+        bound[gridDim.x + p] = kmag + redm[0];
+    }
 }
 
 // ---------------------------------------------------------------------------
@@ -887,7 +915,7 @@ __global__ void __launch_bounds__(256)
 witness_relu_kernel(const int32_t* __restrict__ pair_q, int64_t N, int64_t ld, double* __restrict__ X,
                     const double* __restrict__ lb, const double* __restrict__ ub,
                     const int32_t* __restrict__ rank, const int64_t* __restrict__ P_in,
-                    const double* __restrict__ r, const int64_t* __restrict__ r_off) {
+                    const double* __restrict__ r, const int64_t* __restrict__ r_off, double* __restrict__ alpha) {
     const int p = blockIdx.x;
     const int q = pair_q[p];
     const int64_t i = int64_t(blockIdx.y) * blockDim.x + threadIdx.x;
@@ -907,6 +935,8 @@ witness_relu_kernel(const int32_t* __restrict__ pair_q, int64_t N, int64_t ld, d
         } else {
             y = lo;
         }
+        // the value of the neuron's new predicate at this point of the set
+        if (alpha != nullptr) alpha[r_off[p] + P_in[q] + rank[int64_t(q) * N + i]] = y;
     }
     *px = y;
 }
@@ -936,10 +966,10 @@ static int rw_strip_height(int H, int C) {
     return std::min(cap, std::max(8, RW_THREADS / std::max(1, C)));
 }
 
-int range_windows_slices(int H, int W, int C, int nq) {
+int range_windows_slices(int H, int W, int C, int nq, int sm_count) {
     const int TH = rw_strip_height(H, C);
     const int64_t blocks = ceil_div(H, TH) * int64_t(W) * nq;
-    return (int)std::max<int64_t>(1, std::min<int64_t>(8, ceil_div(4 * 148, blocks)));
+    return (int)std::max<int64_t>(1, std::min<int64_t>(8, ceil_div(4 * int64_t(sm_count), blocks)));
 }
 
 size_t range_windows_scratch_ints(const WinCohorts& wc, int nq, int64_t ncols) {
@@ -1137,9 +1167,9 @@ int launch_witness_x0_star(cudaStream_t st, int n_pairs, const int32_t* pair_q, 
 
 int launch_witness_relu(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t N, int64_t ld, double* X,
                         const double* lb, const double* ub, const int32_t* rank, const int64_t* P_in,
-                        const double* r, const int64_t* r_off, int64_t* launches) {
+                        const double* r, const int64_t* r_off, double* alpha, int64_t* launches) {
     dim3 grid((unsigned)n_pairs, (unsigned)ceil_div(N, 256));
-    witness_relu_kernel<<<grid, 256, 0, st>>>(pair_q, N, ld, X, lb, ub, rank, P_in, r, r_off);
+    witness_relu_kernel<<<grid, 256, 0, st>>>(pair_q, N, ld, X, lb, ub, rank, P_in, r, r_off, alpha);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;

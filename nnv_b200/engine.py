@@ -139,6 +139,10 @@ def make_layer_desc(layer, keep):
         d.pool = (C.c_int32 * 2)(*[int(x) for x in layer["pool"]])
         d.stride = (C.c_int32 * 2)(*[int(x) for x in layer.get("stride", layer["pool"])])
         d.pad = (C.c_int32 * 4)(*[int(x) for x in layer.get("pad", (0, 0, 0, 0))])
+        div = layer.get("divisor", "inside")
+        if div not in ("window", "inside"):
+            raise ValueError("avgpool divisor must be 'window' or 'inside'")
+        d.avgpool_divisor = L.POOL_DIV_INSIDE if div == "inside" else L.POOL_DIV_WINDOW
     elif t == "relu":
         d.type = L.LAYER_RELU
     else:
@@ -321,6 +325,18 @@ class Batch:
         L.check(self.lib.nnvb_batch_halfspace_margins(self.handle, q, _dp(G), _dp(g), nh, _dp(margin), status),
                 "nnvb_batch_halfspace_margins")
         return margin, np.array(status[:], dtype=np.int32)
+
+    def halfspace_witness(self, q, G, g):
+        """(alpha[P], x_out[N_out], G x_out - g) of the device's witness point for the row G x <= g."""
+        G = _f64(G).ravel()
+        P, _ = self.out_dims(q)
+        alpha = np.empty(P)
+        x = np.empty(G.size)
+        val = C.c_double()
+        L.check(self.lib.nnvb_batch_halfspace_witness(self.handle, q, _dp(G), float(g), _dp(alpha), _dp(x),
+                                                      C.cast(C.byref(val), L.c_double_p)),
+                "nnvb_batch_halfspace_witness")
+        return alpha, x, val.value
 
     def verify_robust(self, targets, kind="max"):
         t = np.ascontiguousarray(np.asarray(targets, dtype=np.int32).ravel())

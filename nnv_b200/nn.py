@@ -336,15 +336,25 @@ class BatchNormalizationLayer(_Layer):
 
 
 class AveragePooling2DLayer(_Layer):
-    """AveragePooling2DLayer.m:109-131 — PoolSize, Stride, PaddingSize."""
+    """AveragePooling2DLayer.m:109-131 — PoolSize, Stride, PaddingSize.
 
-    def __init__(self, PoolSize=(2, 2), Stride=(1, 1), PaddingSize=(0, 0, 0, 0), Name="average_pooling_2d"):
+    ``Divisor`` says how a window that reaches into the padding is averaged: "inside" divides by the
+    window entries inside the image, as vl_nnpool does for the reference's host arrays
+    (AveragePooling2DLayer.m:247); "window" divides by PoolSize(1)*PoolSize(2), as avgpool does for its
+    gpuArray inputs (:242-245) and as compute_averageMap (:316-393) does."""
+
+    def __init__(self, PoolSize=(2, 2), Stride=(1, 1), PaddingSize=(0, 0, 0, 0), Name="average_pooling_2d",
+                 Divisor="inside"):
         if len(PoolSize) != 2 or len(Stride) != 2 or len(PaddingSize) != 4:
             raise ValueError("Invalid pooling parameters")
+        if Divisor not in ("inside", "window"):
+            raise ValueError("Divisor must be 'inside' or 'window'")
         self.PoolSize, self.Stride, self.PaddingSize, self.Name = tuple(PoolSize), tuple(Stride), tuple(PaddingSize), Name
+        self.Divisor = Divisor
 
     def _desc(self):
-        return {"type": "avgpool", "pool": self.PoolSize, "stride": self.Stride, "pad": self.PaddingSize}
+        return {"type": "avgpool", "pool": self.PoolSize, "stride": self.Stride, "pad": self.PaddingSize,
+                "divisor": self.Divisor}
 
 
 class ReluLayer(_Layer):

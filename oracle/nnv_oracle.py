@@ -118,10 +118,39 @@ def conv_out_size(hp, k, dil, stride):
     return (hp - (k - 1) * dil - 1) // stride + 1
 
 
+CONV_BACKEND = "numpy"
+
+
+def set_conv_backend(name):
+    """"numpy" (default): im2col + GEMM written out below.  "torch": the same cross-correlation through
+    torch.nn.functional.conv2d on the CPU in FP64 (about 4x faster on large generator tensors; results agree
+    with the NumPy form to rounding, which tests/test_oracle_kats.py checks).  Used where a full-size
+    workload has to finish in a test's or a benchmark sample's time."""
+    global CONV_BACKEND
+    if name not in ("numpy", "torch"):
+        raise ValueError(name)
+    CONV_BACKEND = name
+
+
+def _conv2d_slices_torch(X, W, pad, stride, dilation, chunk=2048):
+    import torch
+    import torch.nn.functional as F
+    t, b, l, r = pad
+    w = torch.from_numpy(np.ascontiguousarray(W.transpose(3, 2, 0, 1)))          # [Cout, Cin, kh, kw]
+    outs = []
+    for c0 in range(0, X.shape[3], chunk):
+        x = torch.from_numpy(np.ascontiguousarray(X[:, :, :, c0:c0 + chunk].transpose(3, 2, 0, 1)))   # [cols, Cin, H, W]
+        x = F.pad(x, (l, r, t, b))
+        outs.append(F.conv2d(x, w, None, tuple(stride), 0, tuple(dilation)).numpy().transpose(2, 3, 1, 0))
+    return np.asfortranarray(np.concatenate(outs, axis=3))
+
+
 def conv2d_slices(X, W, pad, stride, dilation, chunk=32):
     """Cross-correlation of every slice X[:,:,:,j] with W[kh,kw,Cin,Cout]; the
     arithmetic of Conv2DLayer.compute_featureMap (Conv2DLayer.m:1111-1204)
     extended over channels and filters as dlconv does at :591-592.  No bias."""
+    if CONV_BACKEND == "torch":
+        return _conv2d_slices_torch(X, W, pad, stride, dilation)
     kh, kw, cin, cout = W.shape
     assert X.shape[2] == cin
     Xp = zero_pad(X, pad)
@@ -182,9 +211,16 @@ def bn_reach(S, L):
     return ImageStar(np.asfortranarray(V), S.C, S.d, S.pl, S.pu, S.trace)
 
 
-def avgpool_slices(X, pool, stride, pad):
+def avgpool_slices(X, pool, stride, pad, divisor="window"):
     """AveragePooling2DLayer.compute_averageMap, AveragePooling2DLayer.m:316-393:
-    zero-pad, sum the window row by row, divide by ph*pw (padding counted)."""
+    zero-pad, sum the window row by row, divide by ph*pw (padding counted) —
+    divisor="window", the rule of the pure-MATLAB map and of avgpool on gpuArray
+    inputs (AveragePooling2DLayer.m:242-245).  divisor="inside" divides by the
+    number of window entries inside the image instead: the rule of MatConvNet's
+    vl_nnpool(..., 'Method', 'avg'), which evaluate calls on host arrays (:247);
+    that routine ships as a binary only, so this rule is restated from its
+    published source (matconvnet, pooling_cpu: the accumulator is built with the
+    window clipped to the image) and is not pinned by a reference test."""
     ph, pw = pool
     sh, sw = stride
     Xp = zero_pad(X, pad)
@@ -194,13 +230,24 @@ def avgpool_slices(X, pool, stride, pad):
     for i in range(ph):
         for j in range(pw):
             acc = acc + Xp[i: i + (ho - 1) * sh + 1: sh, j: j + (wo - 1) * sw + 1: sw]
-    return acc / (ph * pw)
+    if divisor == "window":
+        return acc / (ph * pw)
+    if divisor != "inside":
+        raise ValueError(divisor)
+    H, W = X.shape[:2]
+    h0 = np.arange(ho) * sh - pad[0]
+    w0 = np.arange(wo) * sw - pad[2]
+    nh = np.minimum(h0 + ph, H) - np.maximum(h0, 0)
+    nw = np.minimum(w0 + pw, W) - np.maximum(w0, 0)
+    cnt = np.maximum(np.outer(nh, nw), 1).astype(np.float64)
+    return acc / cnt.reshape((ho, wo) + (1,) * (X.ndim - 2))
 
 
 def avgpool_reach(S, L):
     """AveragePooling2DLayer.reach_star_single_input, AveragePooling2DLayer.m:424-438:
-    pool every slice of V (centre and generators)."""
-    Y = avgpool_slices(S.V, L["pool"], L["stride"], L["pad"])
+    evaluate applied to V (centre and generators).  L["divisor"] names the rule for padded
+    windows (see avgpool_slices); the default is the host-array back end's."""
+    Y = avgpool_slices(S.V, L["pool"], L["stride"], L["pad"], L.get("divisor", "inside"))
     return ImageStar(np.asfortranarray(Y), S.C, S.d, S.pl, S.pu, S.trace)
 
 

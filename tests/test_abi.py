@@ -30,7 +30,7 @@ def test_header_symbols_exported_and_bound():
 
 def test_abi_version_and_strerror():
     lib = _lib.load()
-    assert lib.nnvb_abi_version() == 1
+    assert lib.nnvb_abi_version() == 2
     assert lib.nnvb_strerror(0) == b"ok"
     assert b"arena" in lib.nnvb_strerror(_lib.NNVB_E_CAPACITY)
 
@@ -39,7 +39,8 @@ def test_layer_desc_layout():
     # offsets the C compiler gives nnvb_layer_desc on x86-64
     assert _lib.LayerDesc.W.offset == 64
     assert _lib.LayerDesc.bn_eps.offset == 112
-    assert C.sizeof(_lib.LayerDesc) == 120
+    assert _lib.LayerDesc.avgpool_divisor.offset == 120
+    assert C.sizeof(_lib.LayerDesc) == 128
     assert C.sizeof(_lib.Opts) == 32
     assert C.sizeof(_lib.ReluStats) == 32
 

@@ -109,16 +109,18 @@ def test_bn_after_conv_is_fused_and_matches(ctx):
     assert _rel(b.get_V(0), ref) < TOL
 
 
-@pytest.mark.parametrize("shape,pool,stride,pad,ncols", [
-    ((4, 4, 1), (2, 2), (2, 2), (0, 0, 0, 0), 1),
-    ((5, 5, 3), (3, 3), (2, 2), (0, 0, 0, 0), 2),
-    ((32, 32, 32), (2, 2), (2, 2), (0, 0, 0, 0), 9),
-    ((7, 9, 2), (3, 2), (2, 1), (1, 0, 1, 1), 5),
+@pytest.mark.parametrize("shape,pool,stride,pad,ncols,divisor", [
+    ((4, 4, 1), (2, 2), (2, 2), (0, 0, 0, 0), 1, "inside"),
+    ((5, 5, 3), (3, 3), (2, 2), (0, 0, 0, 0), 2, "window"),
+    ((32, 32, 32), (2, 2), (2, 2), (0, 0, 0, 0), 9, "inside"),
+    ((7, 9, 2), (3, 2), (2, 1), (1, 0, 1, 1), 5, "window"),
+    ((7, 9, 2), (3, 2), (2, 1), (1, 0, 1, 1), 5, "inside"),
+    ((8, 8, 3), (3, 3), (2, 2), (1, 2, 2, 1), 4, "inside"),
 ])
-def test_avgpool_parity(ctx, shape, pool, stride, pad, ncols):
+def test_avgpool_parity(ctx, shape, pool, stride, pad, ncols, divisor):
     rng = np.random.default_rng(sum(shape) + ncols)
     V = rng.standard_normal(shape + (ncols,))
-    L = {"type": "avgpool", "pool": pool, "stride": stride, "pad": pad}
+    L = {"type": "avgpool", "pool": pool, "stride": stride, "pad": pad, "divisor": divisor}
     ref = O.avgpool_reach(_star(V), L).V
     got = ctx.layer_apply(L, V)
     assert got.shape == ref.shape and np.array_equal(got, ref)      # same summation order

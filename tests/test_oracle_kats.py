@@ -161,3 +161,39 @@ def test_box_to_star_construction():
     assert np.array_equal(M[:, 1], [0.5, 0, 0, 0]) and np.array_equal(M[:, 2], [0, 0, 1., 0])
     assert S.C.shape == (1, 2) and S.C.nnz == 0 and np.array_equal(S.d, [0.])
     assert np.array_equal(S.pl, [-1, -1]) and np.array_equal(S.pu, [1, 1])
+
+
+def test_avgpool_divisor_rules():
+    """Padded windows: "window" divides by ph*pw (compute_averageMap), "inside" by the entries inside the image
+    (the host-array back end of AveragePooling2DLayer.evaluate); without padding the two agree."""
+    rng = np.random.default_rng(5)
+    X = rng.standard_normal((7, 9, 2, 3))
+    pool, stride, pad = (3, 2), (2, 1), (1, 0, 1, 1)
+    Xp = np.pad(X, ((1, 0), (1, 1), (0, 0), (0, 0)))
+    ho, wo = (8 - 3) // 2 + 1, (11 - 2) // 1 + 1
+    for rule in ("window", "inside"):
+        Y = O.avgpool_slices(X, pool, stride, pad, rule)
+        assert Y.shape == (ho, wo, 2, 3)
+        for oh in range(ho):
+            for ow in range(wo):
+                win = Xp[oh * 2: oh * 2 + 3, ow: ow + 2]
+                h0, w0 = oh * 2 - 1, ow - 1
+                inside = (min(h0 + 3, 7) - max(h0, 0)) * (min(w0 + 2, 9) - max(w0, 0))
+                ref = win.sum(axis=(0, 1)) / (6 if rule == "window" else inside)
+                assert np.allclose(Y[oh, ow], ref, rtol=1e-14, atol=1e-15)
+    a = O.avgpool_slices(X, (2, 2), (2, 2), (0, 0, 0, 0), "window")
+    b = O.avgpool_slices(X, (2, 2), (2, 2), (0, 0, 0, 0), "inside")
+    assert np.array_equal(a, b)
+
+
+def test_conv_backends_agree():
+    rng = np.random.default_rng(6)
+    X = np.asfortranarray(rng.standard_normal((9, 7, 5, 40)))
+    W = rng.standard_normal((3, 2, 5, 6))
+    a = O.conv2d_slices(X, W, (1, 0, 2, 1), (2, 1), (1, 2))
+    O.set_conv_backend("torch")
+    try:
+        b = O.conv2d_slices(X, W, (1, 0, 2, 1), (2, 1), (1, 2))
+    finally:
+        O.set_conv_backend("numpy")
+    assert a.shape == b.shape and np.abs(a - b).max() <= 1e-13 * np.abs(a).max()
