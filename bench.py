@@ -1,24 +1,31 @@
 #!/usr/bin/env python
 """Benchmark of the approx-star verification path on B200.
 
-    python bench.py --gpus N --steps K --warmup W            # CUDA engine
-    python bench.py --impl reference --steps K --warmup W    # CPU restatement of the reference path
+    python bench.py --gpus N --steps K --warmup W                    # CUDA engine, all workloads
+    python bench.py --workload cnn28 ...                             # one workload as the headline line
+    python bench.py --workload vgg224 --shard generators --gpus 8    # one set sharded over the GPUs
+    python bench.py --impl reference --steps K --warmup W            # CPU restatement of the reference path
 
-Workload: the 32x32x3 CNN robustness configuration (seeded synthetic images,
-random-init FP64 weights): [conv3x3x32 -> BN -> ReLU]x2 -> avgpool2 ->
-[conv3x3x64 -> BN -> ReLU]x2 -> avgpool2 -> FC256 -> ReLU -> FC10, L-inf
-eps = 2/255 on all 3072 pixels, target = class of the centre image.
+Workloads (seeded synthetic images, random-init FP64 weights; nnv_b200/configs.py):
 
-One step = one batch of B input sets pushed through reach + the output
-halfspace test.  With N > 1 GPUs every rank verifies its own B sets per step
-(independent queries, no data-path collective), so `value` is the whole-job
-rate N*K*B / max-over-ranks time.
+    cnn32     32x32x3 CNN [conv3x3x32-BN-ReLU]x2-pool-[conv3x3x64-BN-ReLU]x2-pool-FC256-ReLU-FC10,
+              L-inf eps = 2/255 on all 3072 pixels, 128 images                    (the headline workload)
+    cnn28     28x28x1 CNN conv3x3x8-ReLU-conv3x3x16/2-ReLU-FC128-ReLU-FC10, eps = 1/255, 256 images
+    bright28  same network, one brightening predicate per image, 16384 images
+    fc5       FC 5-[50 ReLU]x6-5, box of half width 0.01, 100 queries, "output 0 is minimal"
+    vgg224    VGG16-shaped 224x224x3 network (average pools), 64 perturbed entries, 8 images
 
-value   device-resident inputs (already uploaded), device time by CUDA events
-        on the engine's stream.
-e2e     the public call NN.verify_robustness_batch on host arrays: host staging,
-        H2D copy, reach, halfspace test, D2H of the verdicts, wall clock between
-        device synchronisations.
+One step = one pass over the workload's whole query list: reach + the output halfspace test for every query,
+in sub-batches that fit the arena.  With N > 1 GPUs every rank verifies its own copy of the list per step
+(independent queries, no data-path collective), so `value` is N * K * queries / max-over-ranks time
+(weak scaling); with --shard generators ONE set per step is split along its generator dimension over the
+ranks and the partial bound sums are added over NVLink before every ReLU step (strong scaling).
+
+value   inputs already uploaded; device time by CUDA events on the engine's stream around the K steps.
+        Queries the device tests leave undecided are finished inside the timed region (second reach with
+        constraint records, back-substitution bound, host LP), so every query counted has its verdict.
+e2e     the public call NN.verify_robustness_batch on host arrays: host staging, H2D copy, reach,
+        halfspace tests, D2H of the verdicts, wall clock between device synchronisations.
 """
 from __future__ import annotations
 
@@ -37,10 +44,18 @@ sys.path.insert(0, ROOT)
 
 METRIC = "verified ImageStar queries/sec"
 UNIT = "queries/s"
-WORKLOAD = "cnn32: 32x32x3 CNN, eps=2/255 on 3072 pixels, approx-star (estimated bounds) reach + halfspace verdict"
-# Share of one image's dense contraction work done by the prefix conv1..conv2 (+BN, ReLU 1)
-# that the CPU sample runs; columns per layer of seeded image 0: 3073, 4623, 7812, 10834, 20394.
-CPU_PREFIX_LAYERS = 5
+
+# name -> (queries of the configuration, queries per engine batch, description)
+WORKLOADS = {
+    "cnn32": (128, 16, "cnn32: 32x32x3 CNN, eps=2/255 on 3072 pixels, 128 images, approx-star (estimated bounds) "
+                       "reach + halfspace verdict"),
+    "cnn28": (256, 256, "cnn28: 28x28x1 CNN, eps=1/255 on 784 pixels, 256 images, reach + verdict"),
+    "bright28": (16384, 4096, "bright28: 28x28x1 CNN, one brightening predicate per image, 16384 images, reach + verdict"),
+    "fc5": (100, 100, "fc5: FC 5-[50 ReLU]x6-5, box half-width 0.01, 100 queries, reach + verdict (output 0 minimal)"),
+    "vgg224": (8, 1, "vgg224: VGG16-shaped 224x224x3 network, 64 perturbed entries (eps=2/255), reach + verdict"),
+}
+# what the default line carries beside cnn32, with the steps they get (their steps are short)
+EXTRAS = ("cnn28", "bright28", "fc5")
 
 
 def dense_flops_per_layer(layers, in_shape, cols):
@@ -107,98 +122,435 @@ class ClockSampler:
             for nm, val in zip(names, parts[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(nm)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+        # the median under load: samples taken while the SMs were clocked up
+        busy = [x for x in sm if mx and x >= 0.5 * max(mx)] or sm
+        return {"sm_mhz": float(np.median(busy)) if busy else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_sample(layers, query, n_layers):
-    """Oracle (CPU restatement) on one image through the first n_layers layers."""
+# ------------------------------------------------------------------------------------------ CPU arm
+
+
+def _host_threads():
+    info = {"cores": os.cpu_count()}
+    try:
+        import torch
+        info["torch_threads"] = torch.get_num_threads()
+    except Exception:
+        pass
+    try:
+        from threadpoolctl import threadpool_info
+        info["blas_threads"] = max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
+    except Exception:
+        pass
+    return info
+
+
+def cpu_reference(name, budget_s=60.0):
+    """The CPU restatement of the reference path (oracle/nnv_oracle.py: NumPy/OpenBLAS FP64, convolutions
+    through torch's CPU FP64 conv2d, verdict LPs through HiGHS) on whole queries of the workload, as many as
+    fit the time budget (at least one).  Returns (queries/s, description, oracle set of query 0)."""
+    from nnv_b200.configs import make_config
     from oracle import nnv_oracle as O
+    if name == "vgg224":
+        return None, "not run: one dense 224x224 reach is hours of CPU work", None
+    n_max = {"cnn32": 1, "cnn28": 8, "bright28": 64, "fc5": 100}[name]
+    cfg = make_config(name, n_queries=n_max)
+    with_lp = name != "cnn32"
+    O.set_conv_backend("torch")
+    first = None
+    done = 0
     t0 = time.perf_counter()
-    S = O.reach(layers[:n_layers], O.star_from_query(query), keep_constraints=False)
+    try:
+        for qu in cfg["queries"]:
+            S = O.reach(cfg["layers"], O.star_from_query(qu), keep_constraints=with_lp)
+            if with_lp:
+                G, g = O.robustness_set(S.mat().shape[0], qu["target"], qu.get("spec", "max"))
+                O.verify_specification(S, G, g)
+            if first is None:
+                first = S
+            done += 1
+            if time.perf_counter() - t0 > budget_s:
+                break
+    finally:
+        O.set_conv_backend("numpy")
     dt = time.perf_counter() - t0
-    cols = [3073] + [t["P_out"] + 1 for t in S.trace]
-    return dt, cols
-
-
-def cpu_queries_per_s(cfg, reps=1):
-    """Bounded CPU sample scaled to whole queries by dense contraction work."""
-    layers = cfg["layers"]
-    times = []
-    for r in range(reps):
-        dt, cols = cpu_sample(layers, cfg["queries"][0], CPU_PREFIX_LAYERS)
-        times.append(dt)
-    # whole-image column counts of seeded image 0 (from the engine; identical in the oracle)
-    full_cols = [3073, 4623, 7812, 10834, 20394, 20650]
-    fl = dense_flops_per_layer(layers, cfg["in_shape"], full_cols)
-    total = sum(f for _, f in fl)
-    prefix = sum(f for i, f in fl if i < CPU_PREFIX_LAYERS)
-    frac = prefix / total
-    t = float(np.median(times))
-    return frac / t, t, frac
+    th = _host_threads()
+    what = "reach + verdict (HiGHS feasibility LPs)" if with_lp else \
+        ("reach only: the verdict LP of this size (about 20 650 variables, 52 700 rows, 34 M non-zeros, up to 9 "
+         "solves) is not timed, so the figure is an upper bound of the CPU rate")
+    sample = ("%d whole quer%s of the workload in %.1f s; %s; NumPy/OpenBLAS FP64 + torch CPU FP64 conv2d, %s"
+              % (done, "y" if done == 1 else "ies", dt, what,
+                 ", ".join("%s=%s" % kv for kv in sorted(th.items()))))
+    return done / dt, sample, first
 
 
 def run_reference(args):
-    from nnv_b200.configs import make_config
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cfg = make_config("cnn32", n_queries=1)
-    cores = os.cpu_count()
-    vals = []
-    for _ in range(args.warmup):
-        cpu_queries_per_s(cfg)
+    name = args.workload or "cnn32"
+    nq, sub, desc = WORKLOADS[name]
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        v, t, frac = cpu_queries_per_s(cfg)
-        vals.append(v)
+    # whole queries, timed once (a query is deterministic: further steps would repeat the same computation);
+    # each step then re-times a short prefix of query 0 (first affine layer + first ReLU step) as a stability check
+    value, sample, _ = cpu_reference(name, budget_s=90.0 if name == "cnn32" else 45.0)
+    from nnv_b200.configs import make_config
+    from oracle import nnv_oracle as O
+    cfg = make_config(name, n_queries=1)
+    prefix = 1
+    while prefix < len(cfg["layers"]) and cfg["layers"][prefix - 1]["type"] != "relu":
+        prefix += 1
+    O.set_conv_backend("torch")
+    pre = []
+    for s in range(args.warmup + args.steps):
+        t1 = time.perf_counter()
+        O.reach(cfg["layers"][:prefix], O.star_from_query(cfg["queries"][0]), keep_constraints=False)
+        if s >= args.warmup:
+            pre.append(time.perf_counter() - t1)
+    O.set_conv_backend("numpy")
     wall = time.perf_counter() - t0
-    value = float(np.mean(vals))
-    sample = ("1 image, layers 1-%d (conv1, BN, ReLU, conv2, BN: %.1f%% of the image's dense contraction flops), "
-              "scaled to whole queries; reach only, NumPy/OpenBLAS FP64" % (CPU_PREFIX_LAYERS, 100 * frac))
+    if value is None:
+        emit({"impl": "reference", "unavailable": sample})
+        return
+    sample += "; per step a re-timed prefix (layers 1-%d of query 0): median %.3f s, spread %.1f%%" % (
+        prefix, float(np.median(pre)), 100.0 * (max(pre) - min(pre)) / max(np.median(pre), 1e-12))
+    th = _host_threads()
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * wall / max(args.steps, 1),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f64", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "batch_per_step": 1},
-            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "config": {"workload": desc, "queries_per_step": nq, "batch_per_launch": sub},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": th["cores"], "kind": "port", "sample": sample,
+                             "threads": th},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     emit(line)
+
+
+# ------------------------------------------------------------------------------------------ GPU arm
+
+
+def _sets_of(nn, queries):
+    return [nn.ImageStar(q["lb"], q["ub"]) if "lb" in q else nn.ImageStar(q["V"], q["C"], q["d"], q["pl"], q["pu"])
+            for q in queries]
+
+
+def _bytes_in(q):
+    if "lb" in q:
+        return 2 * q["lb"].size * 8
+    return q["V"].size * 8 + 16 * q["pl"].size
+
+
+def run_workload(env, name, K, W, profile=False, keep_first=False):
+    """Device-resident and end-to-end rates of one workload with query sharding; returns a dict."""
+    import torch
+    from nnv_b200 import _lib as L
+    from nnv_b200 import nn
+    from nnv_b200.configs import make_config
+    from nnv_b200.engine import Batch, Network
+
+    ctx, dev, stream, barrier, world, rank = (env[k] for k in ("ctx", "dev", "stream", "barrier", "world", "rank"))
+    nq, sub, desc = WORKLOADS[name]
+    if env["args"].batch and name == (env["args"].workload or "cnn32"):
+        sub = env["args"].batch
+    cfg = make_config(name, n_queries=nq)
+    layers, shape = cfg["layers"], cfg["in_shape"]
+    kind = cfg["queries"][0].get("spec", "max")
+    # ranks start at different places of the list: every rank does the whole list per step
+    order = np.roll(np.arange(nq), -(rank * nq) // max(world, 1))
+    groups = [order[i:i + sub] for i in range(0, nq, sub)]
+    net = Network(ctx, layers, shape)
+    model = nn.NN(layers, ctx=ctx)
+    model._nets[tuple(int(x) for x in shape)] = net
+    sets_all = _sets_of(nn, cfg["queries"])
+    batches = []
+    for g in groups:
+        b = Batch(net, [cfg["queries"][i] for i in g])
+        b.upload()
+        batches.append(b)
+    targets0 = [np.array([cfg["queries"][i]["target"] for i in g], dtype=np.int32) for g in groups]
+    opts = {"reachMethod": "approx-star"}
+    counts = {"robust": 0, "unknown": 0, "second_pass": 0}
+    first = {}
+
+    def step(count):
+        for gi, (b, g) in enumerate(zip(batches, groups)):
+            b.reach(keep_layer_bounds=True)
+            v, _, _ = b.verify_robust(targets0[gi], kind)
+            if keep_first and gi == 0 and not first:
+                first["batch"] = b
+                first["cross"] = [b.get_crossing(0, li)[0] for li in range(net.n_relu)]
+                first["bounds"] = [b.get_layer_ranges(0, li, st["N"]) for li, st in enumerate(b.relu_stats())]
+                first["ranges"] = b.get_ranges(0)
+                first["query"] = int(g[0])
+            und = int((v == L.UNDECIDED).sum())
+            if und:
+                res = model.finish_verdicts([sets_all[i] for i in g], opts, targets0[gi] + 1, v, kind)
+            else:
+                res = np.where(v == L.VERDICT_EMPTY, 1, 2)
+            if count:
+                counts["robust"] += int((res == 1).sum())
+                counts["unknown"] += int((res == 2).sum())
+                counts["second_pass"] += und
+
+    step(False)                               # sizing pass: the context's working buffers reach their final size
+    for _ in range(W):
+        step(False)
+    barrier()
+    if profile:
+        ctx.profile_enable(True)
+    l0 = ctx.launch_count
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(K):
+        step(True)
+    ev1.record(stream)
+    barrier()
+    dev_ms = ev0.elapsed_time(ev1)
+    launches = ctx.launch_count - l0
+    prof = None
+    if profile:
+        prof = ctx.profile_read()
+        ctx.profile_enable(False)
+    stats = batches[-1].relu_stats()
+
+    # end to end through the public API on host arrays
+    tg1 = [t + 1 for t in targets0]
+    for gi, g in enumerate(groups[:2]):
+        model.verify_robustness_batch([sets_all[i] for i in g], opts, tg1[gi], kind)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        for gi, g in enumerate(groups):
+            model.verify_robustness_batch([sets_all[i] for i in g], opts, tg1[gi], kind)
+    torch.cuda.synchronize(dev)
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+
+    t = torch.tensor([dev_ms, e2e_ms, float(launches)], dtype=torch.float64, device=dev)
+    if world > 1:
+        import torch.distributed as dist
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        dev_ms, e2e_ms, launches = float(tmax[0]), float(tmax[1]), int(tsum[2])
+    n_out = int(np.prod(net.out_shape))
+    out = {"workload": desc, "value": world * K * nq / (dev_ms * 1e-3), "unit": UNIT, "steps": K,
+           "ms_per_step": dev_ms / K, "queries_per_step": nq, "batch_per_launch": sub,
+           "e2e": {"value": world * K * nq / (e2e_ms * 1e-3), "unit": UNIT,
+                   "h2d_bytes_per_step": int(sum(_bytes_in(q) for q in cfg["queries"])),
+                   "d2h_bytes_per_step": int(nq * (4 + (n_out - 1) * 12))},
+           "gpu_launches": launches,
+           "verdicts": {"robust": counts["robust"], "unknown": counts["unknown"], "violated": 0,
+                        "finished_by_second_pass": counts["second_pass"]},
+           "columns_after_relu": [s_["cols_after"] for s_ in stats]}
+    res = {"line": out, "prof": prof, "stats": stats, "cfg": cfg, "first": first, "dev_ms": dev_ms, "sub": sub}
+    if not keep_first:
+        for b in batches:
+            b.close()
+        model._nets = {}
+        net.close()
+    else:
+        res["cleanup"] = (batches, net, model)
+    return res
+
+
+def parity_check(first, S):
+    """Engine results of the first query of the first timed batch against the CPU oracle's run of the same
+    query: crossing sets, predicate columns, bounds per ReLU layer, output ranges."""
+    from oracle import nnv_oracle as O
+    same = all(np.array_equal(a, t["cross"]) for a, t in zip(first["cross"], S.trace))
+    rel = 0.0
+    for (lb, ub), t in zip(first["bounds"], S.trace):
+        sc = max(np.abs(t["lb"]).max(), np.abs(t["ub"]).max())
+        rel = max(rel, np.abs(lb - t["lb"]).max() / sc, np.abs(ub - t["ub"]).max() / sc)
+    rl, ru = O.output_ranges(S)
+    sc = max(np.abs(rl).max(), np.abs(ru).max())
+    out_rel = max(np.abs(first["ranges"][0] - rl).max(), np.abs(first["ranges"][1] - ru).max()) / sc
+    return {"query": first["query"], "relu_layers": len(S.trace), "crossing_sets_identical": bool(same),
+            "columns_after_relu_oracle": [t["P_out"] + 1 for t in S.trace],
+            "columns_after_relu_engine": [int(x) for x in
+                                          np.cumsum([S.trace[0]["P_in"] + 1] + [len(a) for a in first["cross"]])[1:]],
+            "max_rel_layer_bound_diff": float(rel), "max_rel_output_range_diff": float(out_rel),
+            "tolerance": 1e-9, "ok": bool(same and rel < 1e-9 and out_rel < 1e-9)}
+
+
+def measure_dgemm(torch, dev):
+    n = 6144
+    a = torch.randn(n, n, dtype=torch.float64, device=dev)
+    bb = torch.randn(n, n, dtype=torch.float64, device=dev)
+    best = 1e9
+    for _ in range(6):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        torch.matmul(a, bb)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        best = min(best, e0.elapsed_time(e1))
+    return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+
+
+def rooflines(res, K, dgemm_tflops, hbm_peak, hbm_src):
+    """Per kernel family: algorithmic work of its launches over their device time (event pairs around every
+    launch group on the engine's stream), against the DGEMM rate / the copy bandwidth."""
+    prof, stats, cfg, dev_ms, B = res["prof"], res["stats"], res["cfg"], res["dev_ms"], res["sub"]
+    layers = cfg["layers"]
+    dgemm_src = "cuBLAS DGEMM 6144^3 measured in this run (burst, best of 6); no FP64 figure is pre-measured"
+    kernels = {"conv": "conv_win_kernel (windowed generator columns) + conv_f64_kernel (centres, dense columns): FP64 "
+                       "DMMA implicit GEMM, products inside the columns' windows only; the time includes the "
+                       "window-only copies written for the bound reduction",
+               "fc": "fc_gather_kernel (windowed columns) + fc_f64_kernel / fc_skinny_kernel: FP64 DMMA GEMM",
+               "avgpool": "avgpool_windowed_kernel / avgpool_f64_kernel (bytes of the windows)",
+               "ranges": "range_windows_kernel + range_partial_* + range_finalize_kernel (Star.estimateRanges, "
+                         "bytes of the windows)"}
+
+    def roof(fam):
+        f = prof[fam]
+        tensor = fam in ("conv", "fc")
+        ach = f["work"] / (f["ms"] * 1e-3) / (1e12 if tensor else 1e9) if f["ms"] > 0 else 0.0
+        peak = dgemm_tflops if tensor else hbm_peak
+        return {"bound": "tensor" if tensor else "hbm", "kernel": kernels[fam], "achieved": ach, "peak": peak,
+                "unit": "TFLOP/s" if tensor else "GB/s", "frac": ach / peak if peak else None,
+                "peak_source": dgemm_src if tensor else hbm_src, "launches": f["launches"],
+                "avg_launch_ms": f["ms"] / max(f["launches"], 1), "share_of_step": f["ms"] / dev_ms,
+                # DRAM bytes per launch come from an ncu capture, not from this run: see the profile summaries
+                "traffic": None,
+                ("algorithmic_flops_per_launch" if tensor else "algorithmic_bytes_per_launch"):
+                    f["work"] / max(f["launches"], 1)}
+
+    # The same families against the dense algorithmic figures (every column a full image).  The engine skips
+    # the products with the structural zeros outside the columns' windows, so these exceed the pipe's peak:
+    # they say how much dense work a step stands for, not how busy the pipe is.
+    n_batches = len(range(0, res["line"]["queries_per_step"], B))
+    q0 = cfg["queries"][0]
+    p_in = int((q0["ub"] != q0["lb"]).sum()) if "lb" in q0 else int(q0["pl"].size)
+    cols_seg = [B * (1 + p_in)] + [s_["cols_after"] for s_ in stats]
+    per_layer = dense_flops_per_layer(layers, cfg["in_shape"], cols_seg)
+    dense = {"conv": n_batches * sum(f for i, f in per_layer if layers[i]["type"] == "conv2d"),
+             "fc": n_batches * sum(f for i, f in per_layer if layers[i]["type"] == "fc")}
+
+    def dense_equiv(fam):
+        ms_step = prof[fam]["ms"] / K
+        ach = dense[fam] / (ms_step * 1e-3) / 1e12 if ms_step > 0 else 0.0
+        return {"achieved": ach, "unit": "TFLOP/s", "frac": ach / dgemm_tflops,
+                "note": "dense algorithmic flops of the step (columns counted as full images, the last batch's "
+                        "column counts for every batch) over the family's time; above 1 because products with "
+                        "structural zeros are skipped, not executed"}
+
+    relu_ms = (prof["ranges"]["ms"] + prof["relax"]["ms"]) / K
+    relu_bytes = prof["ranges"]["work"] / K + n_batches * sum(16.0 * s_["N"] * B + 16.0 * s_["n_cross"] for s_ in stats)
+    dense_relu = 0.0
+    for i, s_ in enumerate(stats):
+        cin, n = cols_seg[i], s_["N"]
+        dense_relu += 8.0 * n * cin + 16.0 * (cin - B) + 16.0 * n * B
+        dense_relu += 16.0 * n * B + 8.0 * (s_["n_dead"] + s_["n_cross"]) * cin / B + 8.0 * n * s_["n_cross"] \
+            + 16.0 * s_["n_cross"]
+    dense_relu *= n_batches
+    relu_step = {"bound": "hbm", "achieved": relu_bytes / (relu_ms * 1e-3) / 1e9 if relu_ms > 0 else 0.0,
+                 "peak": hbm_peak, "unit": "GB/s", "peak_source": hbm_src, "ms_per_step": relu_ms,
+                 "dense_equivalent": {"achieved": dense_relu / (relu_ms * 1e-3) / 1e9 if relu_ms > 0 else 0.0,
+                                      "unit": "GB/s",
+                                      "note": "dense-layout bytes of the step over the same time; above the copy "
+                                              "rate because zero windows are skipped, cleared rows are masked by "
+                                              "the next layer and one-hot columns stay implicit"}}
+    relu_step["frac"] = relu_step["achieved"] / hbm_peak
+    relu_step["dense_equivalent"]["frac"] = relu_step["dense_equivalent"]["achieved"] / hbm_peak
+    dominant = max(kernels, key=lambda k: prof[k]["ms"])
+    return {"roofline": dict(roof(dominant), **({"dense_equivalent": dense_equiv(dominant)} if dominant in dense else {})),
+            "roofline_other": {k: dict(roof(k), **({"dense_equivalent": dense_equiv(k)} if k in dense else {}))
+                               for k in kernels if k != dominant},
+            "relu_step": relu_step,
+            "family_ms_per_step": {k: v["ms"] / K for k, v in prof.items()}}
+
+
+def run_sharded(env, name, K, W):
+    """One set per step, its generators split over the ranks (strong scaling); see nnv_b200/sharding.py."""
+    import torch
+    from nnv_b200 import _lib as L
+    from nnv_b200.configs import make_config
+    from nnv_b200.engine import Batch, Network
+
+    ctx, dev, stream, barrier, world, rank = (env[k] for k in ("ctx", "dev", "stream", "barrier", "world", "rank"))
+    nq, sub, desc = WORKLOADS[name]
+    n_img = min(nq, max(1, env["args"].images))
+    cfg = make_config(name, n_queries=n_img)
+    net = Network(ctx, cfg["layers"], cfg["in_shape"])
+    if world > 1:
+        ctx.set_shard_nccl(rank, world)
+    batches = []
+    for qu in cfg["queries"]:
+        b = Batch(net, [qu])
+        b.upload()
+        batches.append((b, np.array([qu["target"]], dtype=np.int32)))
+    verdicts = []
+
+    def step(s, keep):
+        b, tg = batches[s % n_img]
+        b.reach(keep_layer_bounds=True)
+        v, _, _ = b.verify_robust(tg, "max")
+        if keep:
+            verdicts.append(int(v[0]))
+
+    step(0, False)
+    for s in range(W):
+        step(s, False)
+    barrier()
+    ctx.profile_enable(True)
+    ctx.shard_stats(reset=True)
+    l0 = ctx.launch_count
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for s in range(K):
+        step(W + s, True)
+    ev1.record(stream)
+    barrier()
+    dev_ms = ev0.elapsed_time(ev1)
+    prof = ctx.profile_read()
+    ctx.profile_enable(False)
+    sh = ctx.shard_stats()
+    launches = ctx.launch_count - l0
+    stats = batches[(W + K - 1) % n_img][0].relu_stats()
+    t = torch.tensor([dev_ms, float(launches)], dtype=torch.float64, device=dev)
+    if world > 1:
+        import torch.distributed as dist
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        dev_ms, launches = float(tmax[0]), int(tsum[1])
+    out = {"workload": desc, "value": K / (dev_ms * 1e-3), "unit": UNIT, "steps": K, "ms_per_step": dev_ms / K,
+           "scaling": "strong", "shard": "generators", "images": n_img,
+           "gpu_launches": launches,
+           "verdicts": {"robust": verdicts.count(L.VERDICT_EMPTY), "unknown": verdicts.count(L.VERDICT_NONEMPTY),
+                        "undecided_on_device": verdicts.count(L.UNDECIDED)},
+           "columns_after_relu_this_rank": [s_["cols_after"] for s_ in stats],
+           "crossing_per_relu": [s_["n_cross"] for s_ in stats],
+           "family_ms_per_step": {k: v["ms"] / K for k, v in prof.items()},
+           "allreduce": {"calls_per_step": sh["calls"] / K, "bytes_per_step": sh["bytes"] / K,
+                         "ms_per_step": sh["ms"] / K, "share_of_step": sh["ms"] / dev_ms if dev_ms else None,
+                         "how": sh["how"]}}
+    for b, _ in batches:
+        b.close()
+    net.close()
+    return out
 
 
 def run_ours(args):
     import torch
     import torch.distributed as dist
 
-    from nnv_b200 import nn
-    from nnv_b200.configs import make_config
-    from nnv_b200.engine import Batch, Context, Network
+    from nnv_b200.engine import Context
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
     if world > 1:
-        torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    else:
-        torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    B, K, W = args.batch, args.steps, args.warmup
-
-    # workload: distinct images per step and per rank, cycling through the 128 of the configuration
-    n_distinct = min(K + W, max(1, 128 // (B * world)) if world * B <= 128 else 1)
-    cfg = make_config("cnn32", n_queries=128)
-    layers, shape = cfg["layers"], cfg["in_shape"]
-    offs = rank * n_distinct * B
-    step_queries = [[cfg["queries"][(offs + s * B + i) % 128] for i in range(B)] for s in range(n_distinct)]
+    K, W = args.steps, args.warmup
 
     ctx = Context(local, args.arena_gb << 30)
-    net = Network(ctx, layers, shape)
     stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
-    batches = []
-    for qs in step_queries:
-        b = Batch(net, qs)
-        b.upload()
-        batches.append((b, np.array([q["target"] for q in qs], dtype=np.int32)))
 
     def barrier():
         torch.cuda.synchronize(dev)
@@ -206,184 +558,79 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    def step(s):
-        b, tg = batches[s % n_distinct]
-        b.reach(keep_layer_bounds=True)
-        return b.verify_robust(tg, "max")
+    env = {"ctx": ctx, "dev": dev, "stream": stream, "barrier": barrier, "world": world, "rank": rank, "args": args}
+    main = args.workload or "cnn32"
 
-    verdict_counts = {1: 0, 2: 0, -1: 0}
-    # sizing pass: the context's working buffers grow to what the largest batch needs, so that no timed step
-    # pays for a reallocation (the engine allocates nothing once its buffers have their size)
-    for s in range(n_distinct):
-        step(s)
-    for s in range(W):
-        step(s)
-    barrier()
+    if args.shard == "generators":
+        sampler = ClockSampler(local) if rank == 0 else None
+        out = run_sharded(env, main, K, W)
+        clocks = sampler.stop() if sampler else None
+        if rank == 0:
+            line = {"metric": METRIC, "value": out["value"], "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+                    "ms_per_step": out["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+                    "vs_baseline": None, "dtype": "f64", "data": "synthetic",
+                    "config": {"workload": out["workload"], "shard": "generators", "images": out["images"],
+                               "l2": "inputs larger than L2 (generator tensors of hundreds of MB per layer)"},
+                    "gpu_launches": out["gpu_launches"], "clocks": clocks, "sharded": out}
+            emit(line)
+        ctx.close()
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
     sampler = ClockSampler(local) if rank == 0 else None
-    ctx.profile_enable(True)
-    l0 = ctx.launch_count
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record(stream)
-    for s in range(K):
-        v, _, _ = step(W + s)
-        for x in v:
-            verdict_counts[int(x)] += 1
-    ev1.record(stream)
-    barrier()
-    dev_ms = ev0.elapsed_time(ev1)
-    prof = ctx.profile_read()
-    ctx.profile_enable(False)
-    launches = ctx.launch_count - l0
-    stats = batches[(W + K - 1) % n_distinct][0].relu_stats()
-
-    # end to end through the public API on host arrays
-    sets = [[nn.ImageStar(q["lb"], q["ub"]) for q in qs] for qs in step_queries]
-    targets = [[q["target"] + 1 for q in qs] for qs in step_queries]
-    model = nn.NN(layers, ctx=ctx)
-    for s in range(min(W, 2)):
-        model.verify_robustness_batch(sets[s % n_distinct], {"reachMethod": "approx-star"}, targets[s % n_distinct])
-    barrier()
-    t0 = time.perf_counter()
-    for s in range(K):
-        model.verify_robustness_batch(sets[(W + s) % n_distinct], {"reachMethod": "approx-star"},
-                                      targets[(W + s) % n_distinct])
-    torch.cuda.synchronize(dev)
-    e2e_s = time.perf_counter() - t0
+    res = run_workload(env, main, K, W, profile=True, keep_first=(world == 1 and not args.no_cpu_baseline))
     clocks = sampler.stop() if sampler else None
-
-    t = torch.tensor([dev_ms, e2e_s * 1e3, float(launches)], dtype=torch.float64, device=dev)
-    if world > 1:
-        tmax = t.clone()
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        tsum = t.clone()
-        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
-        dev_ms, e2e_ms, launches = float(tmax[0]), float(tmax[1]), int(tsum[2])
-    else:
-        e2e_ms = e2e_s * 1e3
-
+    line = None
     if rank == 0:
-        value = world * K * B / (dev_ms * 1e-3)
-        e2e = world * K * B / (e2e_ms * 1e-3)
-        # FP64 contraction roofline: cuBLAS DGEMM measured in this run (no FP64 figure is pre-measured)
-        n = 6144
-        a = torch.randn(n, n, dtype=torch.float64, device=dev)
-        bb = torch.randn(n, n, dtype=torch.float64, device=dev)
-        best = 1e9
-        for _ in range(6):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            torch.matmul(a, bb)
-            e1.record()
-            torch.cuda.synchronize(dev)
-            best = min(best, e0.elapsed_time(e1))
-        dgemm_tflops = 2.0 * n ** 3 / (best * 1e-3) / 1e12
-        del a, bb
+        dgemm_tflops = measure_dgemm(torch, dev)
         peaks = {}
         try:
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
         except Exception:
             pass
         hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
-        hbm_src = "MEASURED_PEAKS.json hbm_gbs" if peaks else "fallback 6650 GB/s"
-        dgemm_src = "cuBLAS DGEMM 6144^3 measured in this run (burst, best of 6)"
-        kernels = {"conv": "conv_win_kernel (windowed generator columns) + conv_f64_kernel (centres): FP64 DMMA "
-                           "implicit GEMM, useful products only; the time includes the window-only copies written for "
-                           "the bound reduction",
-                   "fc": "fc_gather_kernel (windowed columns) + fc_f64_kernel / fc_skinny_kernel: FP64 DMMA GEMM",
-                   "avgpool": "avgpool_windowed_kernel / avgpool_f64_kernel (bytes of the windows)",
-                   "ranges": "range_windows_kernel + range_partial_* + range_finalize_kernel (Star.estimateRanges, "
-                             "bytes of the windows)"}
-        # DRAM bytes (read + write) of one image's convolution launches, from the ncu capture of the batch-1
-        # run summarised in profiles/conv_win_kernel_cnn32_batch1.md; the launches of a batch of B images move
-        # B times as much (every column is touched once per layer).  The capture's launch on the 1x1 windows of
-        # the ReLU-2 columns (51 MB) is no longer made: those columns reach the convolution as unit vectors
-        # the window-only copies written since for the bound reduction add their size, 257 MB (whole sectors)
-        conv_dram_bytes_per_image = 530e6 + 257e6
-
-        def roof(fam):
-            f = prof[fam]
-            tensor = fam in ("conv", "fc")
-            ach = f["work"] / (f["ms"] * 1e-3) / (1e12 if tensor else 1e9) if f["ms"] > 0 else 0.0
-            peak = dgemm_tflops if tensor else hbm_peak
-            return {"bound": "tensor" if tensor else "hbm", "kernel": kernels[fam], "achieved": ach, "peak": peak,
-                    "unit": "TFLOP/s" if tensor else "GB/s", "frac": ach / peak if peak else None,
-                    "peak_source": dgemm_src if tensor else hbm_src, "launches": f["launches"],
-                    "avg_launch_ms": f["ms"] / max(f["launches"], 1), "share_of_step": f["ms"] / dev_ms,
-                    "traffic": (conv_dram_bytes_per_image * B * K / max(f["launches"], 1)) if fam == "conv" else None,
-                    ("algorithmic_flops_per_launch" if tensor else "algorithmic_bytes_per_launch"):
-                        f["work"] / max(f["launches"], 1)}
-
-        # The same families against the dense algorithmic figures (every column a full image:
-        # 2*Ho*Wo*Cout*kh*kw*Cin flop per column and convolution, 2*Out*In per column and FC layer).  The
-        # engine skips the products with the structural zeros outside the columns' windows, so these
-        # exceed the pipe's peak: they say how much dense work a step stands for, not how busy the pipe is.
-        cols_seg = [B * (1 + 3072)] + [s_["cols_after"] for s_ in stats]
-        per_layer = dense_flops_per_layer(layers, cfg["in_shape"], cols_seg)
-        dense = {"conv": sum(f for i, f in per_layer if layers[i]["type"] == "conv2d"),
-                 "fc": sum(f for i, f in per_layer if layers[i]["type"] == "fc")}
-
-        def dense_equiv(fam):
-            ms_step = prof[fam]["ms"] / K
-            ach = dense[fam] / (ms_step * 1e-3) / 1e12 if ms_step > 0 else 0.0
-            return {"achieved": ach, "unit": "TFLOP/s", "frac": ach / dgemm_tflops,
-                    "note": "dense algorithmic flops of the step (columns counted as full images) over the family's "
-                            "time; above 1 because products with structural zeros are skipped, not executed"}
-
-        # ReLU step (Star.estimateRanges + classification + relaxation): bytes of the windows actually moved
-        # over the time of the two families, and the dense-layout figure (V read once, cleared rows and new
-        # one-hot columns written) that the windows and the work left to the next layer avoid
-        relu_ms = (prof["ranges"]["ms"] + prof["relax"]["ms"]) / K
-        # executed: the windows read by the bound reduction, lb/ub written and read back by the relaxation,
-        # the predicate bounds of the new columns (rows are not cleared and one-hot columns not written here)
-        relu_bytes = prof["ranges"]["work"] / K + sum(16.0 * s_["N"] * B + 16.0 * s_["n_cross"] for s_ in stats)
-        dense_relu = 0.0
-        for i, s_ in enumerate(stats):
-            cin, n = cols_seg[i], s_["N"]
-            dense_relu += 8.0 * n * cin + 16.0 * (cin - B) + 16.0 * n * B                      # estimateRanges
-            dense_relu += 16.0 * n * B + 8.0 * (s_["n_dead"] + s_["n_cross"]) * cin / B + 8.0 * n * s_["n_cross"] \
-                + 16.0 * s_["n_cross"]                                                          # relaxation
-        relu_step = {"bound": "hbm", "achieved": relu_bytes / (relu_ms * 1e-3) / 1e9 if relu_ms > 0 else 0.0,
-                     "peak": hbm_peak, "unit": "GB/s", "peak_source": hbm_src, "ms_per_step": relu_ms,
-                     "dense_equivalent": {"achieved": dense_relu / (relu_ms * 1e-3) / 1e9 if relu_ms > 0 else 0.0,
-                                          "unit": "GB/s",
-                                          "note": "dense-layout bytes of the step over the same time; above the "
-                                                  "copy rate because zero windows are skipped, cleared rows are "
-                                                  "masked by the next layer and one-hot columns stay implicit"}}
-        relu_step["frac"] = relu_step["achieved"] / hbm_peak
-        relu_step["dense_equivalent"]["frac"] = relu_step["dense_equivalent"]["achieved"] / hbm_peak
-
-        # the roofline entry is the kernel family with the largest share of the timed region
-        dominant = max(kernels, key=lambda k: prof[k]["ms"])
-        line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f64", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "batch_per_step": B, "distinct_batches": n_distinct,
-                       "l2": "inputs larger than L2 (the column windows one layer reads: up to 0.16 GB per image)",
-                       "verdicts": {"robust": verdict_counts[1], "unknown": verdict_counts[2],
-                                    "undecided_on_device": verdict_counts[-1]},
-                       "columns_after_relu": [s_["cols_after"] for s_ in stats]},
-            "e2e": {"value": e2e, "unit": UNIT, "h2d_bytes_per_step": B * 2 * 3072 * 8,
-                    "d2h_bytes_per_step": B * (4 + 9 * 4 + 9 * 8) + 5 * (B + 1) * 16},
-            "gpu_launches": launches,
-            "clocks": clocks,
-            "roofline": dict(roof(dominant), **({"dense_equivalent": dense_equiv(dominant)} if dominant in dense else {})),
-            "roofline_other": {k: dict(roof(k), **({"dense_equivalent": dense_equiv(k)} if k in dense else {}))
-                               for k in kernels if k != dominant},
-            "relu_step": relu_step,
-            "family_ms_per_step": {k: v["ms"] / K for k, v in prof.items()},
-        }
+        hbm_src = "MEASURED_PEAKS.json hbm_gbs (measured copy bandwidth)" if peaks else "fallback 6650 GB/s"
+        o = res["line"]
+        line = {"metric": METRIC, "value": o["value"], "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+                "ms_per_step": o["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "f64", "data": "synthetic",
+                "config": {"workload": o["workload"], "queries_per_step": o["queries_per_step"],
+                           "batch_per_launch": o["batch_per_launch"],
+                           "l2": "inputs larger than L2 (the column windows one layer reads: up to 0.16 GB per image)",
+                           "verdicts": o["verdicts"], "columns_after_relu": o["columns_after_relu"]},
+                "e2e": o["e2e"], "gpu_launches": o["gpu_launches"], "clocks": clocks}
+        line.update(rooflines(res, K, dgemm_tflops, hbm_peak, hbm_src))
+    # the other workloads of the configuration list ride along (their steps are short)
+    extras = {}
+    if not args.workload and not args.no_extras:
+        for name in EXTRAS:
+            k2 = max(2, min(K, 10))
+            r2 = run_workload(env, name, k2, min(W, 3))
+            extras[name] = r2["line"]
+    if rank == 0:
+        if extras:
+            line["extra"] = extras
         if world == 1 and not args.no_cpu_baseline:
-            one = make_config("cnn32", n_queries=1)
-            v, tcpu, frac = cpu_queries_per_s(one)
-            line["cpu_baseline"] = {
-                "value": v, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
-                "sample": "1 image, layers 1-%d (%.1f%% of the image's dense contraction flops) in %.1f s, scaled to "
-                          "whole queries; reach only, NumPy/OpenBLAS FP64" % (CPU_PREFIX_LAYERS, 100 * frac, tcpu)}
+            v, sample, S = cpu_reference(main)
+            th = _host_threads()
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": th["cores"], "kind": "port", "sample": sample,
+                                    "threads": th}
+            if S is not None and res["first"]:
+                line["parity_check"] = parity_check(res["first"], S)
+            for name in extras:
+                v2, sample2, _ = cpu_reference(name, budget_s=20.0)
+                extras[name]["cpu_baseline"] = {"value": v2, "unit": UNIT, "cores": th["cores"], "kind": "port",
+                                                "sample": sample2}
         emit(line)
-    for b, _ in batches:
-        b.close()
-    net.close()
+    if "cleanup" in res:
+        batches, net, model = res["cleanup"]
+        for b in batches:
+            b.close()
+        model._nets = {}
+        net.close()
+    ctx.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -410,12 +657,17 @@ def main():
     os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=16, help="input sets per step and per GPU")
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+                    help="headline workload (default cnn32, with cnn28 / bright28 / fc5 carried under 'extra')")
+    ap.add_argument("--shard", default="queries", choices=["queries", "generators"])
+    ap.add_argument("--images", type=int, default=1, help="--shard generators: distinct images cycled through")
+    ap.add_argument("--batch", type=int, default=0, help="input sets per engine batch (0: the workload's default)")
     ap.add_argument("--arena-gb", type=int, default=112)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

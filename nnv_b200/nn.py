@@ -677,17 +677,23 @@ class NN:
             return np.concatenate(parts)
         t0 = np.asarray(targets, dtype=np.int64) - 1
         verdict, status, _ = b.verify_robust(t0, class_type)
+        b.close()
+        return self.finish_verdicts(inputSets, reachOptions, targets, verdict, class_type, stats)
+
+    def finish_verdicts(self, inputSets, reachOptions, targets, verdict, class_type="max", stats=None):
+        """Turn the device's first-pass answers (``Batch.verify_robust``: 1 robust, 2 unknown, -1 undecided) into
+        the verdicts of verify_robustness for every set: the undecided ones are re-reached with the crossing rows
+        of every ReLU layer kept, so that the device can also bound each open halfspace row by back-substitution
+        through the recorded relaxations (decides most rows the LP would find empty), and what is still open
+        goes to the feasibility LP of Star.isEmptySet on that pass's constraint system."""
+        verdict = np.asarray(verdict)
+        t0 = np.asarray(targets, dtype=np.int64) - 1
         result = np.where(verdict == L.VERDICT_EMPTY, 1, np.where(verdict == L.VERDICT_NONEMPTY, 2, 0)).astype(np.int64)
         undecided = np.nonzero(verdict == L.UNDECIDED)[0]
         if stats is not None:
             stats["n_prefilter"] = int((verdict == L.VERDICT_EMPTY).sum())
             stats["n_witness"] = int((verdict == L.VERDICT_NONEMPTY).sum())
             stats["n_lp_queries"] = int(len(undecided))
-        b.close()
-        # Second pass, undecided queries only, with the crossing rows of every ReLU layer kept: the device
-        # then also bounds each open row by back-substitution through the recorded relaxations (decides most
-        # rows the LP would find empty), and what is still open goes to the LP on that pass's constraint system.
-        if stats is not None:
             stats["n_backsub"] = 0
         group = 32                      # bounds the size of the constraint records
         for g0 in range(0, len(undecided), group):
