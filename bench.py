@@ -475,7 +475,7 @@ def run_sharded(env, name, K, W):
     cfg = make_config(name, n_queries=n_img)
     net = Network(ctx, cfg["layers"], cfg["in_shape"])
     if world > 1:
-        ctx.set_shard_nccl(rank, world)
+        ctx.set_shard_nccl(rank, world, peer_memory=not env["args"].no_peer_memory)
     batches = []
     for qu in cfg["queries"]:
         b = Batch(net, [qu])
@@ -495,7 +495,6 @@ def run_sharded(env, name, K, W):
         step(s, False)
     barrier()
     ctx.profile_enable(True)
-    ctx.shard_stats(reset=True)
     l0 = ctx.launch_count
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record(stream)
@@ -506,7 +505,7 @@ def run_sharded(env, name, K, W):
     dev_ms = ev0.elapsed_time(ev1)
     prof = ctx.profile_read()
     ctx.profile_enable(False)
-    sh = ctx.shard_stats()
+    sh = prof["allreduce"]
     launches = ctx.launch_count - l0
     stats = batches[(W + K - 1) % n_img][0].relu_stats()
     t = torch.tensor([dev_ms, float(launches)], dtype=torch.float64, device=dev)
@@ -525,9 +524,14 @@ def run_sharded(env, name, K, W):
            "columns_after_relu_this_rank": [s_["cols_after"] for s_ in stats],
            "crossing_per_relu": [s_["n_cross"] for s_ in stats],
            "family_ms_per_step": {k: v["ms"] / K for k, v in prof.items()},
-           "allreduce": {"calls_per_step": sh["calls"] / K, "bytes_per_step": sh["bytes"] / K,
-                         "ms_per_step": sh["ms"] / K, "share_of_step": sh["ms"] / dev_ms if dev_ms else None,
-                         "how": sh["how"]}}
+           "allreduce": {"bytes_per_rank_per_step": sh["work"] / K, "ms_per_step": sh["ms"] / K,
+                         "share_of_step": sh["ms"] / dev_ms if dev_ms else None,
+                         "how": ("none: one rank" if world == 1 else
+                                 "NCCL all-reduce inside the library (ncclDouble, ncclSum) per ReLU layer"
+                                 if env["args"].no_peer_memory else
+                                 "peer memory: per ReLU layer the partial sums are written to a peer-mapped buffer and "
+                                 "added inside the classification kernel (time = reduce + flag + classify kernels); "
+                                 "NCCL for the small verdict reductions")}}
     for b, _ in batches:
         b.close()
     net.close()
@@ -668,6 +672,8 @@ def main():
     ap.add_argument("--arena-gb", type=int, default=112)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--no-peer-memory", action="store_true",
+                    help="--shard generators: NCCL all-reduce instead of the fused peer-memory classification")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

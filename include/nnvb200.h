@@ -144,7 +144,8 @@ int64_t nnvb_launch_count(nnvb_ctx* ctx);
 #define NNVB_PROF_RELAX 5     /* row clearing, column append, list rebuild */
 #define NNVB_PROF_VERIFY 6    /* halfspace rows, box minimum, witness pass */
 #define NNVB_PROF_ONEHOT 7    /* images of the unit-vector columns a ReLU step appended (bytes written) */
-#define NNVB_PROF_FAMILIES 8
+#define NNVB_PROF_ALLREDUCE 8  /* generator sharding: sum of the partial bound sums over the ranks (bytes per rank) */
+#define NNVB_PROF_FAMILIES 9
 int nnvb_profile_enable(nnvb_ctx* ctx, int on);
 int nnvb_profile_read(nnvb_ctx* ctx, int family, double* ms, int64_t* launches, double* work);
 
@@ -171,6 +172,26 @@ int nnvb_profile_read(nnvb_ctx* ctx, int family, double* ms, int64_t* launches, 
  * constraint records (keep_constraints, get_constraints) are not available. */
 typedef int (*nnvb_allreduce_fn)(void* user, double* dev_buf, int64_t count, void* stream);
 int nnvb_set_shard(nnvb_ctx* ctx, int rank, int world, nnvb_allreduce_fn fn, void* user);
+
+/* The same sharding with the collective inside the library, for hosts without
+ * a collective of their own (a MATLAB session per GPU): NCCL is bound at run
+ * time (libnccl.so.2) and ncclAllReduce(ncclDouble, ncclSum) runs on the
+ * context's stream.  Rank 0 obtains a communicator id with
+ * nnvb_nccl_unique_id (NNVB_NCCL_ID_BYTES bytes) and hands it to the other
+ * ranks by any host-side means (a file, a socket); then every rank calls
+ * nnvb_set_shard_nccl with its own context current on its own GPU — the call
+ * is collective and returns when the communicator is up.
+ * peer_memory != 0 additionally maps every rank's sum buffer into every other
+ * rank (CUDA IPC, GPUs of one node linked by NVLink): the ReLU step then
+ * writes its partial sums there, raises a flag at the peers, and the
+ * classification kernel adds the ranks' sums in rank order straight from peer
+ * memory — one pass instead of reduce + all-reduce + classify.  A rank waits
+ * for a peer's flag at most about two seconds; after that the reach returns
+ * NNVB_E_STATE and the context stays usable.  If the mapping cannot be set
+ * up on some rank, all ranks use the NCCL all-reduce. */
+#define NNVB_NCCL_ID_BYTES 128
+int nnvb_nccl_unique_id(void* id_out);
+int nnvb_set_shard_nccl(nnvb_ctx* ctx, int rank, int world, const void* nccl_id, int peer_memory);
 
 /* ---- network ------------------------------------------------------------ */
 

@@ -23,8 +23,9 @@ NNVB_E_UNSUPPORTED = 5
 LAYER_CONV2D, LAYER_FC, LAYER_BN, LAYER_AVGPOOL2D, LAYER_RELU = 1, 2, 3, 4, 5
 
 POOL_DIV_WINDOW, POOL_DIV_INSIDE = 0, 1
+NCCL_ID_BYTES = 128
 
-PROF_FAMILIES = ("conv", "fc", "bn", "avgpool", "ranges", "relax", "verify", "onehot")
+PROF_FAMILIES = ("conv", "fc", "bn", "avgpool", "ranges", "relax", "verify", "onehot", "allreduce")
 
 VERDICT_EMPTY = 1
 VERDICT_NONEMPTY = 2
@@ -84,6 +85,8 @@ SIGNATURES = {
     "nnvb_profile_enable": (C.c_int, [C.c_void_p, C.c_int]),
     "nnvb_profile_read": (C.c_int, [C.c_void_p, C.c_int, c_double_p, c_int64_p, c_double_p]),
     "nnvb_set_shard": (C.c_int, [C.c_void_p, C.c_int, C.c_int, ALLREDUCE_FN, C.c_void_p]),
+    "nnvb_nccl_unique_id": (C.c_int, [C.c_void_p]),
+    "nnvb_set_shard_nccl": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int]),
     "nnvb_net_create": (C.c_int, [C.c_void_p, C.POINTER(LayerDesc), C.c_int, C.c_int64, C.c_int64, C.c_int64,
                                   C.POINTER(C.c_void_p)]),
     "nnvb_net_destroy": (C.c_int, [C.c_void_p]),

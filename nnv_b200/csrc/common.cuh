@@ -254,8 +254,20 @@ int relu_blocks_per_query(int64_t N);
 int launch_estimate_ranges(cudaStream_t st, const ReluWork& w, int64_t* launches);
 // Sharded generators: per-query sums of the chunk partials (no centre), [nq][2][N].
 int launch_reduce_chunks(cudaStream_t st, const ReluWork& w, double* sums, int64_t* launches);
-// sums = nullptr: combine the chunk partials directly; else classify from the (all-reduced) sums.
-int launch_classify_scan(cudaStream_t st, const ReluWork& w, const double* sums, int64_t* launches);
+// Partial sums of all ranks in peer-mapped buffers, for the classification that adds them itself.
+struct PeerSums {
+    double* const* tab;        // device array [world]: every rank's buffer as mapped on this device
+    int64_t slot_off;          // offset (doubles) of this call's [nq][2][N] sums in each buffer
+    int rank, world;
+    unsigned long long epoch;  // a rank's flag (64-bit word `rank` at the start of a buffer) reaches this value
+                               // once its sums of this call are written
+    int* status;               // [0] set to 1 when a wait ran out; [1] the rank waited for, [2] the epoch
+    long long max_polls;
+};
+// sums = nullptr: combine the chunk partials directly; else classify from the (all-reduced) sums;
+// peers != nullptr: wait for every rank's flag and add the ranks' sums from peer memory while classifying.
+int launch_classify_scan(cudaStream_t st, const ReluWork& w, const double* sums, int64_t* launches,
+                         const PeerSums* peers = nullptr);
 int launch_rank_cross(cudaStream_t st, const ReluWork& w, const ReluRecord& rec, int64_t* launches);
 // Zero dead and crossing rows in all existing columns; save crossing rows.
 int launch_relu_zero_rows(cudaStream_t st, const ReluWork& w, int64_t ncols, const int32_t* col_q,

@@ -4,6 +4,7 @@
 // owns device memory, the per-query column bookkeeping and the order of
 // launches on the context's stream.
 #include "common.cuh"
+#include "shard_plane.cuh"
 
 #include <algorithm>
 #include <cmath>
@@ -149,6 +150,8 @@ struct nnvb_ctx {
     int rank = 0, world = 1;
     nnvb_allreduce_fn ar_fn = nullptr;
     void* ar_user = nullptr;
+    ShardPlane plane;       // NCCL communicator and peer-mapped sum buffers owned by the library (nnvb_set_shard_nccl)
+    DevBuf shard_flag;      // one double: "some rank cannot go on", summed over the ranks
     const void* result_owner = nullptr;   // the batch whose results the work buffers and the arena hold
     // per-kernel-family device timing (off by default)
     bool prof_on = false;
@@ -442,6 +445,8 @@ int nnvb_destroy(nnvb_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     ctx->scratch.release();
     ctx->work.release();
+    ctx->plane.release();
+    ctx->shard_flag.release();
     prof_drain(ctx);
     for (cudaEvent_t e : ctx->prof_pool) cudaEventDestroy(e);
     for (auto& x : ctx->spare_pinned) x.release();
@@ -475,11 +480,37 @@ int nnvb_set_shard(nnvb_ctx* ctx, int rank, int world, nnvb_allreduce_fn fn, voi
     NNVB_REQUIRE(ctx, "nnvb_set_shard: NULL context");
     NNVB_REQUIRE(world >= 1 && rank >= 0 && rank < world, "nnvb_set_shard: rank %d of %d", rank, world);
     NNVB_REQUIRE(world == 1 || fn != nullptr, "nnvb_set_shard: an all-reduce hook is required when world > 1");
+    ctx->plane.release();
     ctx->rank = rank;
     ctx->world = world;
     ctx->ar_fn = fn;
     ctx->ar_user = user;
     ctx->result_owner = nullptr;
+    return NNVB_OK;
+}
+
+int nnvb_nccl_unique_id(void* id_out) {
+    NNVB_REQUIRE(id_out, "nnvb_nccl_unique_id: NULL output");
+    return nccl_unique_id(id_out);
+}
+
+int nnvb_set_shard_nccl(nnvb_ctx* ctx, int rank, int world, const void* nccl_id, int peer_memory) {
+    NNVB_REQUIRE(ctx, "nnvb_set_shard_nccl: NULL context");
+    NNVB_REQUIRE(world >= 1 && world <= MAX_SHARD_RANKS && rank >= 0 && rank < world,
+                 "nnvb_set_shard_nccl: rank %d of %d (at most %d ranks)", rank, world, MAX_SHARD_RANKS);
+    NNVB_REQUIRE(world == 1 || nccl_id != nullptr, "nnvb_set_shard_nccl: the communicator id is required when world > 1");
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    NNVB_TRY(sync(ctx));
+    ctx->plane.release();
+    ctx->rank = rank;
+    ctx->world = world;
+    ctx->ar_fn = nullptr;
+    ctx->ar_user = nullptr;
+    ctx->result_owner = nullptr;
+    if (world > 1) {
+        NNVB_TRY(ctx->plane.init(rank, world, nccl_id));
+        ctx->plane.want_p2p = peer_memory != 0;
+    }
     return NNVB_OK;
 }
 
@@ -853,6 +884,9 @@ namespace {
 // Sum a device buffer over the ranks of a generator-sharded run (identity when unsharded).
 int allreduce(nnvb_ctx* ctx, double* buf, int64_t count) {
     if (ctx->world <= 1 || count <= 0) return NNVB_OK;
+    ProfScope ps(ctx, NNVB_PROF_ALLREDUCE, 8.0 * double(count));
+    ctx->launches += 1;              // the collective's kernel
+    if (ctx->plane.comm) return ctx->plane.allreduce(buf, count, ctx->stream);
     if (!ctx->ar_fn) {
         set_error("generator sharding is on but no all-reduce hook is installed");
         return NNVB_E_STATE;
@@ -863,6 +897,34 @@ int allreduce(nnvb_ctx* ctx, double* buf, int64_t count) {
         return NNVB_E_CUDA;
     }
     return NNVB_OK;
+}
+
+// Sharded runs: a decision to stop must be the same on every rank, or the ranks that go on would wait in the
+// next collective for the one that left.  Each rank contributes "I cannot go on" (0/1); the sum comes back.
+int shard_agree(nnvb_ctx* ctx, bool local_fail, bool* any_fail) {
+    *any_fail = local_fail;
+    if (ctx->world <= 1) return NNVB_OK;
+    NNVB_TRY(ctx->shard_flag.ensure(sizeof(double), ctx->stream));
+    const double mine = local_fail ? 1.0 : 0.0;
+    double all = 0.0;
+    NNVB_TRY(h2d_small(ctx, ctx->shard_flag.p, &mine, sizeof(double)));
+    NNVB_TRY(allreduce(ctx, ctx->shard_flag.as<double>(), 1));
+    NNVB_CUDA(cudaMemcpyAsync(&all, ctx->shard_flag.p, sizeof(double), cudaMemcpyDeviceToHost, ctx->stream));
+    NNVB_TRY(sync(ctx));
+    *any_fail = all > 0.0;
+    return NNVB_OK;
+}
+
+// Largest generator buffer (bytes) the layers [from, next ReLU layer] need for `ncols` columns of this rank.
+size_t segment_need(const nnvb_batch* b, size_t from, int64_t ncols, int64_t ld_now) {
+    size_t need = size_t(ld_now) * ncols * sizeof(double);
+    const auto& layers = b->net->layers;
+    for (size_t li = from; li < layers.size(); ++li) {
+        const Layer& L = layers[li];
+        if (L.type == NNVB_LAYER_RELU) break;
+        need = std::max(need, size_t(lead_dim(L.Ho * L.Wo * L.Co)) * ncols * sizeof(double));
+    }
+    return need;
 }
 
 int ensure_col_meta(nnvb_batch* b, int64_t cols) {
@@ -908,7 +970,16 @@ int init_sets(nnvb_batch* b) {
     bool implicit = false;               // the generator columns are not stored: the first layer writes their images
     if (b->kind == 1) {
         const size_t need = size_t(ld) * ncols * sizeof(double);
-        if (need > ctx->vbuf_bytes()) return capacity_error("input set", need, ctx->vbuf_bytes());
+        {
+            bool stop = need > ctx->vbuf_bytes();      // agreed on by all ranks of a sharded run
+            const bool mine = stop;
+            NNVB_TRY(shard_agree(ctx, stop, &stop));
+            if (stop) {
+                if (mine) return capacity_error("input set", need, ctx->vbuf_bytes());
+                set_error("another rank's share of the set outgrew its arena");
+                return NNVB_E_CAPACITY;
+            }
+        }
         NNVB_TRY(b->wk->gen_off.ensure(sizeof(int64_t) * (nq + 1), st));
         NNVB_TRY(h2d_small(ctx, b->wk->gen_off.p, gen_off.data(), sizeof(int64_t) * (nq + 1)));
         double* V = ctx->vbuf(0);
@@ -1002,7 +1073,7 @@ int ensure_clean(nnvb_batch* b, nnvb_batch::Cohort& co) {
     return NNVB_OK;
 }
 
-int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_onehot) {
+int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_onehot, size_t next_layer) {
     nnvb_ctx* ctx = b->net->ctx;
     cudaStream_t st = ctx->stream;
     const int nq = b->nq;
@@ -1137,6 +1208,7 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
     w.q_cross = b->wk->q_cross.as<int64_t>(); w.q_dead = b->wk->q_dead.as<int64_t>();
     w.q_new_off = b->wk->q_new_off.as<int64_t>();
 
+    bool used_peers = false;
     {
         // Star.estimateRanges: V read once, predicate bounds, lb/ub written
         // bytes: the columns' windows (all of a dense column) read once, predicate bounds, lb/ub written
@@ -1151,10 +1223,22 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
         if (ctx->world > 1) {
             // sharded generators: every rank holds part of each sum; add them over the ranks, then
             // all ranks classify the same numbers
-            NNVB_TRY(b->wk->sums.ensure(sizeof(double) * 2 * N * nq, st));
-            NNVB_TRY(launch_reduce_chunks(st, w, b->wk->sums.as<double>(), &ctx->launches));
-            NNVB_TRY(allreduce(ctx, b->wk->sums.as<double>(), int64_t(2) * N * nq));
-            NNVB_TRY(launch_classify_scan(st, w, b->wk->sums.as<double>(), &ctx->launches));
+            ShardPlane& pl = ctx->plane;
+            if (pl.p2p_ok && int64_t(2) * N * nq <= pl.cap_doubles) {
+                // peer memory: the sums go to this rank's mapped buffer, the flag tells the peers, and the
+                // classification adds all ranks' sums itself (no reduction kernel in between)
+                ProfScope pa(ctx, NNVB_PROF_ALLREDUCE, 8.0 * 2.0 * double(N) * nq);
+                NNVB_TRY(launch_reduce_chunks(st, w, pl.next_slot(), &ctx->launches));
+                NNVB_TRY(pl.publish(st, &ctx->launches));
+                PeerSums psums{pl.d_peer_tab, pl.slot_offset(), pl.rank, pl.world, pl.epoch, pl.d_status, PEER_WAIT_POLLS};
+                NNVB_TRY(launch_classify_scan(st, w, nullptr, &ctx->launches, &psums));
+                used_peers = true;
+            } else {
+                NNVB_TRY(b->wk->sums.ensure(sizeof(double) * 2 * N * nq, st));
+                NNVB_TRY(launch_reduce_chunks(st, w, b->wk->sums.as<double>(), &ctx->launches));
+                NNVB_TRY(allreduce(ctx, b->wk->sums.as<double>(), int64_t(2) * N * nq));
+                NNVB_TRY(launch_classify_scan(st, w, b->wk->sums.as<double>(), &ctx->launches));
+            }
         } else {
             NNVB_TRY(launch_classify_scan(st, w, nullptr, &ctx->launches));
         }
@@ -1165,8 +1249,29 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
     std::vector<int64_t> dead(nq);
     NNVB_CUDA(cudaMemcpyAsync(rec->new_off.data(), w.q_new_off, sizeof(int64_t) * (nq + 1), cudaMemcpyDeviceToHost, st));
     NNVB_CUDA(cudaMemcpyAsync(dead.data(), w.q_dead, sizeof(int64_t) * nq, cudaMemcpyDeviceToHost, st));
+    int peer_status[4] = {0, 0, 0, 0};
+    if (used_peers)
+        NNVB_CUDA(cudaMemcpyAsync(peer_status, ctx->plane.d_status, sizeof(peer_status), cudaMemcpyDeviceToHost, st));
     NNVB_TRY(sync(ctx));
+    if (peer_status[0] != 0) {
+        // a peer never raised its flag (it failed or left): this reach is void, the context stays usable
+        cudaMemsetAsync(ctx->plane.d_status, 0, sizeof(peer_status), st);
+        set_error("generator sharding: rank %d did not deliver its bound sums for call %d within the wait limit",
+                  peer_status[1], peer_status[2]);
+        return NNVB_E_STATE;
+    }
     const int64_t K = rec->new_off[nq];
+    {
+        // NNVB_TRACE: one line per ReLU layer on stderr (sizes as they are found, also when a later layer fails)
+        static const bool trace = getenv("NNVB_TRACE") != nullptr;
+        if (trace) {
+            int64_t nd = 0;
+            for (int q = 0; q < nq; ++q) nd += dead[q];
+            fprintf(stderr, "[nnvb rank %d] relu: N=%lld columns(local)=%lld crossing=%lld dead=%lld buffer=%.2f GB\n",
+                    ctx->rank, (long long)N, (long long)b->ncols, (long long)K, (long long)nd,
+                    double(ld) * double(b->ncols) * 8e-9);
+        }
+    }
     rec->N = N;
     rec->K = K;
     rec->n_dead = 0;
@@ -1187,8 +1292,18 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
     const int64_t ncols_old = b->ncols;
     NNVB_REQUIRE(ncols_old + K_loc < (int64_t(1) << 31), "batch has too many generator columns");
     {
-        const size_t need = size_t(ld) * (ncols_old + K_loc) * sizeof(double);
-        if (need > ctx->vbuf_bytes()) return capacity_error("ReLU layer output", need, ctx->vbuf_bytes());
+        // this layer's output and, with sharded generators, every layer up to the next ReLU step: the ranks hold
+        // different column counts, so the go / no-go is agreed on before anybody enters the next collective
+        size_t need = size_t(ld) * (ncols_old + K_loc) * sizeof(double);
+        if (world > 1) need = std::max(need, segment_need(b, next_layer, ncols_old + K_loc, ld));
+        bool stop = need > ctx->vbuf_bytes();
+        const bool mine = stop;
+        NNVB_TRY(shard_agree(ctx, stop, &stop));
+        if (stop) {
+            if (mine) return capacity_error("ReLU layer output", need, ctx->vbuf_bytes());
+            set_error("another rank's share of the set outgrew its arena");
+            return NNVB_E_CAPACITY;
+        }
     }
     NNVB_TRY(ensure_col_meta(b, ncols_old + K_loc));
     // pointers may have moved
@@ -1266,6 +1381,25 @@ int run_layers(nnvb_batch* b) {
     nnvb_ctx* ctx = net->ctx;
     cudaStream_t st = ctx->stream;
     int relu_i = 0;
+    if (ctx->world > 1) {
+        // the first segment's capacity, agreed on by all ranks (later ones are agreed on in relu_step)
+        const size_t need = segment_need(b, 0, b->ncols, b->ld);
+        bool stop = need > ctx->vbuf_bytes();
+        const bool mine = stop;
+        NNVB_TRY(shard_agree(ctx, stop, &stop));
+        if (stop) {
+            if (mine) return capacity_error("layer output", need, ctx->vbuf_bytes());
+            set_error("another rank's share of the set outgrew its arena");
+            return NNVB_E_CAPACITY;
+        }
+        // peer-mapped sum buffers sized for the largest ReLU layer of this network (same on every rank)
+        int64_t slot = 0, Ncur = b->N;
+        for (const Layer& L : net->layers) {
+            if (L.type == NNVB_LAYER_RELU) slot = std::max(slot, int64_t(2) * Ncur * b->nq);
+            Ncur = L.Ho * L.Wo * L.Co;
+        }
+        if (ctx->plane.comm && slot > 0) NNVB_TRY(ctx->plane.ensure_peer(slot, st));
+    }
     for (size_t li = 0; li < net->layers.size(); ++li) {
         const Layer& L = net->layers[li];
         const int64_t Nout = L.Ho * L.Wo * L.Co;
@@ -1513,7 +1647,7 @@ int run_layers(nnvb_batch* b) {
             const bool lazy_mask = !eager && !eager_mask && (nt == NNVB_LAYER_CONV2D || nt == NNVB_LAYER_AVGPOOL2D) &&
                                    int64_t(b->nq) * b->N < (int64_t(1) << 31);     // the mask offsets are 32-bit
             const bool lazy_onehot = !eager && (nt == NNVB_LAYER_CONV2D || nt == NNVB_LAYER_AVGPOOL2D || nt == NNVB_LAYER_FC);
-            NNVB_TRY(relu_step(b, b->wk->relu[relu_i].get(), lazy_mask, lazy_onehot));
+            NNVB_TRY(relu_step(b, b->wk->relu[relu_i].get(), lazy_mask, lazy_onehot, li + 1));
             ++relu_i;
         }
         b->shape[0] = L.Ho; b->shape[1] = L.Wo; b->shape[2] = L.Co;

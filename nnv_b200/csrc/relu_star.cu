@@ -659,6 +659,77 @@ classify_sums_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const 
     }
 }
 
+// The same classification with the sum over the ranks fused in: every rank's [nq][2][N] partial sums sit at
+// slot_off in a buffer that all ranks have mapped (peer memory over NVLink).  A block first waits, with a
+// bounded number of polls, until every rank has raised its flag for this call in THIS rank's buffer, then adds
+// the ranks' sums in rank order with plain loads (L2-only, no multicast).  The order is the same on every rank,
+// so all ranks classify identical numbers.  When a wait runs out the block records which rank it waited for in
+// ps.status, writes "no crossing, no dead" for its rows and returns; the host reads the status word.
+__global__ void __launch_bounds__(FIN_THREADS)
+classify_peers_kernel(int64_t N, int64_t ld, const double* __restrict__ V, PeerSums ps,
+                      double* __restrict__ lb, double* __restrict__ ub, uint8_t* __restrict__ state,
+                      int32_t* __restrict__ blk_cross, unsigned long long* __restrict__ q_dead, int nblk) {
+    const int q = blockIdx.x;
+    __shared__ int s_bad;
+    if (threadIdx.x == 0) s_bad = 0;
+    __syncthreads();
+    if (threadIdx.x < ps.world && threadIdx.x != ps.rank) {
+        const volatile unsigned long long* flags = reinterpret_cast<const volatile unsigned long long*>(ps.tab[ps.rank]);
+        long long polls = 0;
+        while (flags[threadIdx.x] < ps.epoch) {
+            if (++polls > ps.max_polls) {
+                s_bad = 1;
+                if (atomicCAS(ps.status, 0, 1) == 0) {
+                    ps.status[1] = threadIdx.x;
+                    ps.status[2] = int(ps.epoch);
+                }
+                break;
+            }
+            __nanosleep(polls < 64 ? 100 : 500);
+        }
+        __threadfence_system();          // the peer's sums were written before its flag
+    }
+    __syncthreads();
+    const bool bad = s_bad != 0;
+    int n_cross = 0, n_dead = 0;
+    for (int r = 0; r < FIN_ROWS / FIN_THREADS; ++r) {
+        const int64_t i = int64_t(blockIdx.y) * FIN_ROWS + r * FIN_THREADS + threadIdx.x;
+        if (i >= N) break;
+        const double c = V[int64_t(q) * ld + i];
+        double lo = 0.0, hi = 0.0;
+        if (!bad) {
+            const int64_t o = ps.slot_off + (int64_t(q) * 2) * N + i;
+            for (int rk = 0; rk < ps.world; ++rk) {
+                const double* src = ps.tab[rk];
+                lo += __ldcg(src + o);
+                hi += __ldcg(src + o + N);
+            }
+        }
+        const double l = c + lo, u = c + hi;
+        lb[int64_t(q) * N + i] = l;
+        ub[int64_t(q) * N + i] = u;
+        uint8_t s = 0;
+        if (!bad) {
+            if (u <= 0.0) { s = 1; ++n_dead; }
+            else if (l < 0.0 && u > 0.0) { s = 2; ++n_cross; }
+        }
+        state[int64_t(q) * N + i] = s;
+    }
+    __shared__ int sc[FIN_THREADS / 32], sd[FIN_THREADS / 32];
+    for (int o = 16; o; o >>= 1) {
+        n_cross += __shfl_down_sync(0xffffffffu, n_cross, o);
+        n_dead += __shfl_down_sync(0xffffffffu, n_dead, o);
+    }
+    if ((threadIdx.x & 31) == 0) { sc[threadIdx.x >> 5] = n_cross; sd[threadIdx.x >> 5] = n_dead; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tc = 0, td = 0;
+        for (int w = 0; w < FIN_THREADS / 32; ++w) { tc += sc[w]; td += sd[w]; }
+        blk_cross[int64_t(q) * nblk + blockIdx.y] = tc;
+        if (td) atomicAdd(q_dead + q, (unsigned long long)td);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Halfspace rows and their minimum over the predicate box.  A "pair" is one
 // halfspace row G_p x <= g_p tested against the output set of query pair_q[p].
@@ -1048,11 +1119,15 @@ int launch_reduce_chunks(cudaStream_t st, const ReluWork& w, double* sums, int64
     return NNVB_OK;
 }
 
-int launch_classify_scan(cudaStream_t st, const ReluWork& w, const double* sums, int64_t* launches) {
+int launch_classify_scan(cudaStream_t st, const ReluWork& w, const double* sums, int64_t* launches,
+                         const PeerSums* peers) {
     const int nblk = relu_blocks_per_query(w.N);
     NNVB_CUDA(cudaMemsetAsync(w.q_dead, 0, sizeof(int64_t) * w.nq, st));
     dim3 grid((unsigned)w.nq, (unsigned)nblk);
-    if (sums)
+    if (peers)
+        classify_peers_kernel<<<grid, FIN_THREADS, 0, st>>>(w.N, w.ld, w.V, *peers, w.lb, w.ub, w.state, w.blk_cross,
+                                                            reinterpret_cast<unsigned long long*>(w.q_dead), nblk);
+    else if (sums)
         classify_sums_kernel<<<grid, FIN_THREADS, 0, st>>>(w.N, w.ld, w.V, sums, w.lb, w.ub, w.state, w.blk_cross,
                                                            reinterpret_cast<unsigned long long*>(w.q_dead), nblk);
     else

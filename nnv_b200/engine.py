@@ -58,6 +58,25 @@ class Context:
         L.check(self.lib.nnvb_set_shard(self.handle, int(rank), int(world), self._hook, None), "nnvb_set_shard")
         self.rank, self.world = int(rank), int(world)
 
+    def set_shard_nccl(self, rank, world, peer_memory=True, group=None):
+        """The same sharding with the collective inside the library (``nnvb_set_shard_nccl``): NCCL bound by
+        the library itself and, with ``peer_memory``, the fused sum-and-classify kernel over peer-mapped
+        buffers.  torch.distributed only carries the 128-byte communicator id from rank 0 to the others."""
+        buf = C.create_string_buffer(L.NCCL_ID_BYTES)
+        if world > 1:
+            import torch
+            import torch.distributed as dist
+            if rank == 0:
+                L.check(self.lib.nnvb_nccl_unique_id(buf), "nnvb_nccl_unique_id")
+            t = torch.frombuffer(bytearray(buf.raw), dtype=torch.uint8).clone()
+            if dist.get_backend(group) == "nccl":
+                t = t.cuda()
+            dist.broadcast(t, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+            buf = C.create_string_buffer(bytes(t.cpu().numpy().tobytes()), L.NCCL_ID_BYTES)
+        L.check(self.lib.nnvb_set_shard_nccl(self.handle, int(rank), int(world), buf, int(bool(peer_memory))),
+                "nnvb_set_shard_nccl")
+        self.rank, self.world = int(rank), int(world)
+
     def profile_enable(self, on=True):
         """Start (and zero) or stop the per-kernel-family device timers."""
         L.check(self.lib.nnvb_profile_enable(self.handle, int(bool(on))), "nnvb_profile_enable")

@@ -1,6 +1,11 @@
 """One rank of the generator-sharded GPU parity check (launched by tests/test_gpu_sharded.py through
 torch.distributed.run, one process per GPU, NCCL).  Every rank reaches its share of each query's
-generators; the sum over ranks of the per-rank outputs must match the CPU oracle's unsharded set."""
+generators; the sum over ranks of the per-rank outputs must match the CPU oracle's unsharded set.
+
+argv[1] picks the transport of the bound sums: "hook" (the caller's all-reduce callback), "nccl" (the
+library's own NCCL all-reduce), "peer" (peer-mapped buffers added inside the classification kernel), or
+"capacity": rank 1 gets an arena too small for its share, and every rank must come back with the capacity
+status instead of one of them waiting in a collective for the rank that stopped."""
 import os
 import sys
 
@@ -22,8 +27,33 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    mode = sys.argv[1] if len(sys.argv) > 1 else "hook"
+    if mode == "capacity":
+        ctx = Context(local, (4 << 30) if rank != 1 else (1 << 20))
+        ctx.set_shard_nccl(rank, world, peer_memory=True)
+        cfg = make_config("cnn32", n_queries=2, small=True)
+        net = Network(ctx, cfg["layers"], cfg["in_shape"])
+        b = Batch(net, cfg["queries"])
+        b.upload()
+        try:
+            b.reach(keep_layer_bounds=True)
+            status = 0
+        except _lib.NNVError as e:
+            status = e.status
+        flag = torch.tensor([1 if status == _lib.NNVB_E_CAPACITY else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if rank == 0:
+            print("SHARDED CAPACITY OK" if int(flag) == 1 else "SHARDED CAPACITY FAIL (status %d)" % status, flush=True)
+        b.close()
+        net.close()
+        ctx.close()
+        dist.destroy_process_group()
+        sys.exit(0 if int(flag) == 1 else 1)
     ctx = Context(local, 4 << 30)
-    ctx.set_shard(rank, world)
+    if mode == "hook":
+        ctx.set_shard(rank, world)
+    else:
+        ctx.set_shard_nccl(rank, world, peer_memory=(mode == "peer"))
     ok = True
     for name, nq in (("cnn32", 2), ("vgg224", 1), ("bright28", 3), ("fc5", 4)):
         cfg = make_config(name, n_queries=nq, small=(name != "fc5"))

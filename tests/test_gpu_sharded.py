@@ -12,17 +12,29 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def test_two_rank_generator_sharding_matches_oracle():
+def _run_ranks(mode, port):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-                        "--master-addr", "127.0.0.1", "--master-port", "29533",
-                        os.path.join(ROOT, "tests", "sharded_worker.py")],
+                        "--master-addr", "127.0.0.1", "--master-port", str(port),
+                        os.path.join(ROOT, "tests", "sharded_worker.py"), mode],
                        capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
-    assert "SHARDED PARITY OK" in r.stdout
+    return r.stdout
+
+
+@pytest.mark.parametrize("mode,port", [("hook", 29533), ("nccl", 29534), ("peer", 29535)])
+def test_two_rank_generator_sharding_matches_oracle(mode, port):
+    """hook: the caller's all-reduce callback; nccl: the library's own NCCL all-reduce; peer: partial sums in
+    peer-mapped buffers, added inside the classification kernel."""
+    assert "SHARDED PARITY OK" in _run_ranks(mode, port)
+
+
+def test_capacity_stop_is_the_same_on_every_rank():
+    """One rank's arena is too small for its share: all ranks return the capacity status together."""
+    assert "SHARDED CAPACITY OK" in _run_ranks("capacity", 29536)
 
 
 def test_world_size_one_shard_is_the_plain_path(ctx):

@@ -131,3 +131,44 @@ def test_sharded_scheme_two_ranks_gloo(name):
         p.join(120)
     assert all(p.exitcode == 0 for p in procs)
     assert q.get(timeout=5) == "ok"
+
+
+def _agree_worker(rank, world, port, q):
+    """The go / no-go protocol of a sharded reach: every rank contributes "I cannot go on" (its share does
+    not fit its arena), the sum comes back, and all ranks stop at the same point or none does."""
+    import torch
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        arena = [1 << 30, 1 << 20][rank]                 # rank 1 has the small arena
+        cols = [sharding.shard_count(3000, rank, world) + 1, sharding.shard_count(7000, rank, world) + 1]
+        stopped_at = None
+        for layer, (n_rows, c) in enumerate(zip([4096, 4096], cols)):
+            flag = torch.tensor([1.0 if n_rows * c * 8 > arena // 2 else 0.0], dtype=torch.float64)
+            dist.all_reduce(flag)                        # the one-double sum every rank takes part in
+            if flag.item() > 0:
+                stopped_at = layer
+                break
+        q.put((rank, stopped_at))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_capacity_stop_is_agreed_on_by_all_ranks_gloo():
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_agree_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+    assert all(p.exitcode == 0 for p in procs)
+    got = dict(q.get(timeout=5) for _ in range(2))
+    assert got[0] == got[1] == 0                         # rank 0 fits, yet it stops where rank 1 does
