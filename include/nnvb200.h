@@ -202,6 +202,12 @@ int nnvb_set_shard_nccl(nnvb_ctx* ctx, int rank, int world, const void* nccl_id,
 int nnvb_net_create(nnvb_ctx* ctx, const nnvb_layer_desc* layers, int n_layers,
                     int64_t in_h, int64_t in_w, int64_t in_c, nnvb_net** out);
 int nnvb_net_destroy(nnvb_net* net);
+/* NN.evaluate (NN.m:130-145) on n_points concrete inputs at once: X is
+ * [H*W*C x n_points] column-major on the host, Y receives [N_out x n_points].
+ * ReLU layers apply max(x, 0).  This is what falsification (NN.falsify,
+ * NN.m:930-988) and the harness pre-check of the bound images
+ * (examples/Tutorial/SPIE/Classification2D/verifySample.m:5-20) evaluate. */
+int nnvb_net_evaluate(nnvb_net* net, int64_t n_points, const double* X, double* Y);
 /* Output size (H,W,C) of the network. */
 int nnvb_net_out_shape(const nnvb_net* net, int64_t shape[3]);
 

@@ -90,6 +90,7 @@ SIGNATURES = {
     "nnvb_net_create": (C.c_int, [C.c_void_p, C.POINTER(LayerDesc), C.c_int, C.c_int64, C.c_int64, C.c_int64,
                                   C.POINTER(C.c_void_p)]),
     "nnvb_net_destroy": (C.c_int, [C.c_void_p]),
+    "nnvb_net_evaluate": (C.c_int, [C.c_void_p, C.c_int64, c_double_p, c_double_p]),
     "nnvb_net_out_shape": (C.c_int, [C.c_void_p, c_int64_p]),
     "nnvb_batch_create": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_void_p)]),
     "nnvb_batch_destroy": (C.c_int, [C.c_void_p]),

@@ -325,6 +325,8 @@ int launch_witness_x0_star(cudaStream_t st, int n_pairs, const int32_t* pair_q, 
 int launch_witness_relu(cudaStream_t st, int n_pairs, const int32_t* pair_q, int64_t N, int64_t ld, double* X,
                         const double* lb, const double* ub, const int32_t* rank, const int64_t* P_in,
                         const double* r, const int64_t* r_off, double* alpha, int64_t* launches);
+// max(x, 0) in place on n concrete points X [ld x n] (NN.evaluate's ReLU).
+int launch_relu_points(cudaStream_t st, int64_t n, int64_t N, int64_t ld, double* X, int64_t* launches);
 int launch_witness_value(cudaStream_t st, int n_pairs, int64_t Nout, int64_t ld, const double* X, const double* G,
                          const double* g, double* value, double* scale, int64_t* launches);
 

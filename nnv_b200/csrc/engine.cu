@@ -345,6 +345,9 @@ int h2d_small(nnvb_ctx* ctx, void* dst, const void* src, size_t bytes) {
     return NNVB_OK;
 }
 
+int forward_points(nnvb_net* net, WorkBufs* wk, nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, int64_t* ldx,
+                   const double* d_r, const int64_t* d_roff, double* d_alpha);
+
 // Copy the centre (center_col >= 0) and the P_loc listed columns into out[N x (P+1)], each generator
 // at its position in the query's predicate order (out is zero filled beforehand).
 __global__ void gather_cols_kernel(int64_t N, int64_t ld, const double* __restrict__ V, int center_col,
@@ -690,6 +693,35 @@ int nnvb_net_destroy(nnvb_net* net) {
     cudaStreamSynchronize(net->ctx->stream);
     for (void* p : net->owned) cudaFree(p);
     delete net;
+    return NNVB_OK;
+}
+
+int nnvb_net_evaluate(nnvb_net* net, int64_t n_points, const double* X, double* Y) {
+    NNVB_REQUIRE(net && X && Y, "nnvb_net_evaluate: NULL argument");
+    NNVB_REQUIRE(n_points >= 1, "nnvb_net_evaluate: need at least one input");
+    nnvb_ctx* ctx = net->ctx;
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    cudaStream_t st = ctx->stream;
+    const int64_t N0 = net->in_shape[0] * net->in_shape[1] * net->in_shape[2], ld0 = lead_dim(N0);
+    const int64_t Nout = net->out_shape[0] * net->out_shape[1] * net->out_shape[2];
+    int64_t max_ld = ld0;
+    for (const Layer& L : net->layers) max_ld = std::max(max_ld, lead_dim(L.Ho * L.Wo * L.Co));
+    // slices of the inputs that bound the two working buffers to about 2 GiB each
+    const int64_t cap = std::max<int64_t>(1, std::min<int64_t>((int64_t(1) << 31) / (max_ld * 8), 1 << 20));
+    WorkBufs* wk = &ctx->work;
+    for (int64_t p0 = 0; p0 < n_points; p0 += cap) {
+        const int n = int(std::min(cap, n_points - p0));
+        NNVB_TRY(wk->wit[0].ensure(sizeof(double) * max_ld * n, st));
+        NNVB_TRY(wk->wit[1].ensure(sizeof(double) * max_ld * n, st));
+        NNVB_CUDA(cudaMemcpy2DAsync(wk->wit[0].p, sizeof(double) * ld0, X + p0 * N0, sizeof(double) * N0,
+                                    sizeof(double) * N0, size_t(n), cudaMemcpyHostToDevice, st));
+        double* out = nullptr;
+        int64_t ldx = 0;
+        NNVB_TRY(forward_points(net, wk, nullptr, n, nullptr, &out, &ldx, nullptr, nullptr, nullptr));
+        NNVB_CUDA(cudaMemcpy2DAsync(Y + p0 * Nout, sizeof(double) * Nout, out, sizeof(double) * ldx,
+                                    sizeof(double) * Nout, size_t(n), cudaMemcpyDeviceToHost, st));
+        NNVB_TRY(sync(ctx));
+    }
     return NNVB_OK;
 }
 
@@ -1721,15 +1753,16 @@ int output_ranges(nnvb_batch* b) {
     return NNVB_OK;
 }
 
-// Run the affine layers and the relaxed ReLU over witness points X [ld x n] (one per pair).
-int witness_forward(nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, int64_t* ldx, const double* d_r,
-                    const int64_t* d_roff, double* d_alpha = nullptr) {
-    nnvb_net* net = b->net;
+// Run the layers over n points X [ld x n] held in wk.wit[0] (wk.wit[1] is the other buffer).  With a batch
+// (witness pass, one point per halfspace pair) the ReLU layers apply the relaxed ReLU of the pair's query;
+// without one (b == nullptr) they apply max(x, 0): NN.evaluate on n inputs at once.
+int forward_points(nnvb_net* net, WorkBufs* wk, nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, int64_t* ldx,
+                   const double* d_r, const int64_t* d_roff, double* d_alpha) {
     nnvb_ctx* ctx = net->ctx;
     cudaStream_t st = ctx->stream;
-    double* cur = b->wk->wit[0].as<double>();
-    double* oth = b->wk->wit[1].as<double>();
-    int64_t N = b->N0, ld = b->ld0;
+    double* cur = wk->wit[0].as<double>();
+    double* oth = wk->wit[1].as<double>();
+    int64_t N = net->in_shape[0] * net->in_shape[1] * net->in_shape[2], ld = lead_dim(N);
     int relu_i = 0;
     for (size_t li = 0; li < net->layers.size(); ++li) {
         const Layer& L = net->layers[li];
@@ -1746,9 +1779,9 @@ int witness_forward(nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, i
         } else if (L.type == NNVB_LAYER_FC) {
             if (n <= 512) {      // too few columns to fill the GPU with 128-column tiles: slice the contraction instead
                 const int In = int(L.H * L.W * L.C);
-                NNVB_TRY(b->wk->tmp.ensure(sizeof(double) * fc_skinny_scratch_doubles(In, int(L.Co), n), st));
+                NNVB_TRY(wk->tmp.ensure(sizeof(double) * fc_skinny_scratch_doubles(In, int(L.Co), n), st));
                 NNVB_TRY(launch_fc_skinny(st, In, int(L.Co), L.fc_wt, L.fc_ldw, L.bias, cur, ld, oth, ld_out, n,
-                                          b->wk->tmp.as<double>(), &ctx->launches));
+                                          wk->tmp.as<double>(), &ctx->launches));
             } else
                 NNVB_TRY(launch_fc_f64(st, int(L.H * L.W * L.C), int(L.Co), L.fc_wt, L.fc_ldw, L.bias, cur, ld, oth, ld_out,
                                        n, n, &ctx->launches));
@@ -1762,15 +1795,24 @@ int witness_forward(nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, i
                 NNVB_TRY(launch_bn_f64(st, bn, L.H * L.W, N, cur, ld, n, n, &ctx->launches));
             }
         } else if (L.type == NNVB_LAYER_RELU) {
-            ReluLayerRecord& r = *b->wk->relu[relu_i++];
-            NNVB_TRY(launch_witness_relu(st, n, d_pair_q, N, ld, cur, r.lb.as<double>(), r.ub.as<double>(),
-                                         r.rank.as<int32_t>(), r.P_in_dev.as<int64_t>(), d_r, d_roff, d_alpha,
-                                         &ctx->launches));
+            if (b != nullptr) {
+                ReluLayerRecord& r = *wk->relu[relu_i++];
+                NNVB_TRY(launch_witness_relu(st, n, d_pair_q, N, ld, cur, r.lb.as<double>(), r.ub.as<double>(),
+                                             r.rank.as<int32_t>(), r.P_in_dev.as<int64_t>(), d_r, d_roff, d_alpha,
+                                             &ctx->launches));
+            } else {
+                NNVB_TRY(launch_relu_points(st, n, N, ld, cur, &ctx->launches));
+            }
         }
     }
     *X = cur;
     *ldx = ld;
     return NNVB_OK;
+}
+
+int witness_forward(nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, int64_t* ldx, const double* d_r,
+                    const int64_t* d_roff, double* d_alpha = nullptr) {
+    return forward_points(b->net, b->wk, b, n, d_pair_q, X, ldx, d_r, d_roff, d_alpha);
 }
 
 // Relative guard on "this lower bound is positive": a bound b with term magnitudes M proves emptiness only

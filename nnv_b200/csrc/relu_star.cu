@@ -1012,6 +1012,17 @@ witness_relu_kernel(const int32_t* __restrict__ pair_q, int64_t N, int64_t ld, d
     *px = y;
 }
 
+// ReLU of concrete points, in place: PosLin.evaluate (PosLin.m: max(x, 0)) on X [ld x n].
+__global__ void __launch_bounds__(256)
+relu_points_kernel(int64_t n, int64_t N, int64_t ld, double* __restrict__ X) {
+    const int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= N) return;
+    for (int64_t p = blockIdx.y; p < n; p += gridDim.y) {
+        double* px = X + p * ld + i;
+        *px = fmax(*px, 0.0);
+    }
+}
+
 // value[p] = G_p . x_p - g_p and a magnitude for the acceptance tolerance.
 __global__ void witness_value_kernel(int n_pairs, int64_t Nout, int64_t ld, const double* __restrict__ X,
                                      const double* __restrict__ G, const double* __restrict__ g,
@@ -1245,6 +1256,14 @@ int launch_witness_relu(cudaStream_t st, int n_pairs, const int32_t* pair_q, int
                         const double* r, const int64_t* r_off, double* alpha, int64_t* launches) {
     dim3 grid((unsigned)n_pairs, (unsigned)ceil_div(N, 256));
     witness_relu_kernel<<<grid, 256, 0, st>>>(pair_q, N, ld, X, lb, ub, rank, P_in, r, r_off, alpha);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_relu_points(cudaStream_t st, int64_t n, int64_t N, int64_t ld, double* X, int64_t* launches) {
+    dim3 grid((unsigned)ceil_div(N, 256), (unsigned)std::min<int64_t>(n, 65535));
+    relu_points_kernel<<<grid, 256, 0, st>>>(n, N, ld, X);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;

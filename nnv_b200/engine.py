@@ -190,6 +190,15 @@ class Network:
         self.out_shape = tuple(shp)
         self.n_relu = sum(1 for l in layers if l["type"] == "relu")
 
+    def evaluate(self, X):
+        """Concrete forward pass of the columns of X [N_in x n] (or one vector); returns [N_out x n]."""
+        X = _f64(X)
+        one = X.ndim == 1
+        X = X.reshape(int(np.prod(self.in_shape)), -1, order="F")
+        Y = np.empty((int(np.prod(self.out_shape)), X.shape[1]), dtype=np.float64, order="F")
+        L.check(self.lib.nnvb_net_evaluate(self.handle, X.shape[1], _dp(X), _dp(Y)), "nnvb_net_evaluate")
+        return Y[:, 0] if one else Y
+
     def close(self):
         if getattr(self, "handle", None):
             self.lib.nnvb_net_destroy(self.handle)

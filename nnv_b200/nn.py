@@ -29,7 +29,7 @@ from scipy.optimize import linprog
 from . import _lib as L
 from .engine import Batch, Context, Network
 
-__all__ = ["NN", "ImageStar", "Star", "HalfSpace", "Conv2DLayer", "FullyConnectedLayer",
+__all__ = ["NN", "ImageStar", "Star", "HalfSpace", "ImageInputLayer", "FlattenLayer", "Conv2DLayer", "FullyConnectedLayer",
            "BatchNormalizationLayer", "AveragePooling2DLayer", "ReluLayer", "verify_specification",
            "default_context"]
 
@@ -123,6 +123,34 @@ class ImageStar:
             self._C, self.d = self._lazy[0].get_constraints(self._lazy[1])
         return self._C
 
+    def affineMap(self, scale=None, offset=None, ctx=None):
+        """ImageStar.affineMap (ImageStar.m:431-460): every slice of V times ``scale`` (a scalar or one factor
+        per channel), ``offset`` (scalar, per channel or a whole image) added to the centre.  The scaling runs on
+        the GPU as a per-channel affine layer; an offset image, which has no per-channel form, is added to the
+        centre slice on the host."""
+        C = self.numChannel
+        sc = np.ones(C)
+        if scale is not None and np.size(scale):
+            a = np.asarray(scale, dtype=np.float64)
+            if a.size != 1 and (a.ndim < 3 or a.shape[2] != C or a.size != C):
+                raise ValueError("Inconsistent number of channels between scale array and the ImageStar")
+            sc = np.full(C, float(a.reshape(-1)[0])) if a.size == 1 else a.reshape(-1)
+        off = np.zeros(C)
+        off_image = None
+        if offset is not None and np.size(offset):
+            o = np.asarray(offset, dtype=np.float64)
+            if o.size == 1:
+                off = np.full(C, float(o.reshape(-1)[0]))
+            elif o.size == C and (o.ndim < 3 or o.shape[:2] == (1, 1)):
+                off = o.reshape(-1)
+            else:
+                off_image = o.reshape(self.height, self.width, C)
+        layer = {"type": "bn", "mean": np.zeros(C), "var": np.ones(C), "scale": sc, "offset": off, "eps": 0.0}
+        newV = (ctx or default_context()).layer_apply(layer, self.V)
+        if off_image is not None:
+            newV[..., 0] = newV[..., 0] + off_image
+        return ImageStar(newV, self.C, self.d, self.pred_lb, self.pred_ub)
+
     def toStar(self):
         """ImageStar.m:569-592."""
         n = self.height * self.width * self.numChannel
@@ -134,6 +162,37 @@ class ImageStar:
         lb, ub = self.toStar().estimateRanges(ctx)
         shp = (self.height, self.width, self.numChannel)
         return lb.reshape(shp, order="F"), ub.reshape(shp, order="F")
+
+    def evaluate(self, pred_val):
+        """ImageStar.evaluate (ImageStar.m:396-425): the image at a value of the predicate vector."""
+        pred_val = np.asarray(pred_val, dtype=np.float64).reshape(-1)
+        if pred_val.size != self.numPred:
+            raise ValueError("Inconsistency between the size of the predicate vector and the number of predicates in the imagestar")
+        if self._V is None and self.im_lb is not None:
+            n = self.height * self.width * self.numChannel
+            lbv, ubv = self.im_lb.reshape(n, order="F"), self.im_ub.reshape(n, order="F")
+            x = 0.5 * (lbv + ubv)
+            vec = 0.5 * (ubv - lbv)
+            nz = np.nonzero(vec != 0)[0] if n > 1 else np.arange(1)
+            x[nz] += vec[nz] * pred_val
+            return x.reshape(self.height, self.width, self.numChannel, order="F")
+        return self.V[..., 0] + self.V[..., 1:] @ pred_val
+
+    def sample(self, N, rng=None):
+        """ImageStar.sample (ImageStar.m:369-394): predicate vectors sampled from the star
+        (0 | I, C, d, pred_lb, pred_ub) by Star.sample, each evaluated to an image.  Returns a list."""
+        if N < 1:
+            raise ValueError("Invalid number of samples")
+        rng = rng or np.random.default_rng()
+        P = self.numPred
+        C = self.C
+        if not np.size(C) or not np.any(C):                  # predicate box only: no rejection needed
+            A = (self.pred_ub - self.pred_lb)[:, None] * rng.random((P, 2 * N)) + self.pred_lb[:, None]
+            A = A[:, :N]
+        else:
+            S = Star(np.hstack([np.zeros((P, 1)), np.eye(P)]), C, self.d, self.pred_lb, self.pred_ub)
+            A = S.sample(N, rng)
+        return [self.evaluate(A[:, i]) for i in range(A.shape[1])]
 
     def _query(self):
         if self._V is None and self.im_lb is not None and self._lazy is None:
@@ -227,6 +286,34 @@ class Star:
         """Star.isEmptySet, Star.m:1216-1232."""
         return _lp_is_empty(sp.csr_matrix(self.C), self.d, self.predicate_lb, self.predicate_ub)
 
+    def contains(self, x):
+        """Star.contains (Star.m:1189-1213): is there a predicate vector with x = c + V alpha, C alpha <= d,
+        pred_lb <= alpha <= pred_ub (a feasibility LP with equality rows)."""
+        x = np.asarray(x, dtype=np.float64).reshape(-1)
+        if x.size != self.dim:
+            raise ValueError("Dimension mismatch")
+        pl, pu = self._pred_bounds()
+        A = self.C if np.size(self.C) else None
+        res = linprog(np.zeros(self.nVar), A_ub=A, b_ub=self.d if A is not None else None, A_eq=self.V[:, 1:],
+                      b_eq=x - self.V[:, 0], bounds=list(zip(pl, pu)), method="highs")
+        return res.status == 0
+
+    def sample(self, N, rng=None):
+        """Star.sample (Star.m:278-308): 2N points uniform in the set's bounding box, those inside the set
+        kept, at most N returned (columns).  ``rng``: a numpy Generator standing in for MATLAB's rand."""
+        if N < 1:
+            raise ValueError("Invalid number of samples")
+        rng = rng or np.random.default_rng()
+        lb, ub = self.estimateRanges()
+        X = (ub - lb)[:, None] * rng.random((self.dim, 2 * N)) + lb[:, None]
+        pl, pu = self._pred_bounds()
+        box_only = not np.size(self.C) or not np.any(self.C)
+        diag = self.nVar == self.dim and np.count_nonzero(self.V[:, 1:] - np.diag(np.diag(self.V[:, 1:]))) == 0
+        if box_only and diag and np.all(np.asarray(self.d) >= 0):
+            return X[:, :N]                 # a box: every point of its bounding box is a point of the set
+        keep = [i for i in range(2 * N) if self.contains(X[:, i])]
+        return X[:, keep[:N]]
+
     def _query(self):
         pl, pu = self._pred_bounds()
         return {"V": self.V.reshape(self.dim, 1, 1, -1, order="F"), "C": self.C, "d": self.d, "pl": pl, "pu": pu}
@@ -241,6 +328,13 @@ class HalfSpace:
         if G.shape[0] != g.size:
             raise ValueError("Inconsistent dimension between half-space matrix and half-space vector")
         self.G, self.g, self.dim = G, g, G.shape[1]
+
+    def contains(self, x):
+        """HalfSpace.contains (HalfSpace.m:35-55): no row of g - G x is negative."""
+        x = np.asarray(x, dtype=np.float64).reshape(-1)
+        if x.size != self.dim:
+            raise ValueError("Inconsistent dimension between the vector x and the half-space object")
+        return not np.any(self.g - self.G @ x < 0)
 
 
 def _lp_is_empty(Cs, d, pl, pu):
@@ -402,6 +496,13 @@ class ImageInputLayer(_Layer):
         if have:
             return [("add", -self._arr(self.Min)), ("mul", 2.0 / (float(self.Max) - float(self.Min))), ("add", -1.0)]
         return [("mul", 2 / 255), ("add", -1.0)]
+
+    def apply_image(self, x):
+        """ImageInputLayer.evaluate (ImageInputLayer.m:84-114): the normalised copy of a concrete image."""
+        x = np.asarray(x, dtype=np.float64)
+        for kind, v in self._steps():
+            x = x + v if kind == "add" else (x * v if kind == "mul" else x / v)
+        return x
 
     def apply(self, s):
         """The normalised copy of an input ImageStar."""
@@ -610,6 +711,81 @@ class NN:
         self.reachMethod, self.relaxFactor = opts["reachMethod"], opts["relaxFactor"]
         b = self.reach_batch([inputSet], opts, keep_constraints=True)
         return _result_set(b, 0, isinstance(inputSet, Star))
+
+    # -- concrete evaluation and falsification -----------------------------------
+    def evaluate(self, x):
+        """NN.evaluate (NN.m:130-145) on the device; ``x`` is one input (image or vector) or a list of them.
+        Returns the output vector(s), column-major flattened."""
+        many = isinstance(x, (list, tuple))
+        xs = [np.asarray(v, dtype=np.float64) for v in (x if many else [x])]
+        first = self.Layers[0] if self.Layers else None
+        if isinstance(first, ImageInputLayer):
+            xs = [first.apply_image(v) for v in xs]
+        shape = xs[0].shape if xs[0].ndim == 3 else ((xs[0].shape + (1,)) if xs[0].ndim == 2 else (xs[0].size, 1, 1))
+        net = self._network(shape)
+        X = np.stack([v.reshape(-1, order="F") for v in xs], axis=1)
+        Y = net.evaluate(np.asfortranarray(X))
+        return [Y[:, i] for i in range(Y.shape[1])] if many else Y[:, 0]
+
+    def falsify(self, I, U, n_samples, rng=None):
+        """NN.falsify (NN.m:930-988): sample ``n_samples`` inputs from the set, evaluate them (one batched
+        forward pass on the device) and return those whose output lies in one of the halfspaces U."""
+        Us = list(U) if isinstance(U, (list, tuple)) else [U]
+        if not all(isinstance(h, HalfSpace) for h in Us):
+            raise TypeError("Unsafe region (U) is not a HalfSpace.")
+        if not isinstance(I, (ImageStar, Star)):
+            raise TypeError("Input set (I) must be a ImageZono, ImageStar, Star, Zono or Box.")
+        if n_samples < 1:
+            raise ValueError("Invalid number of samples. n_samples > 0")
+        pts = I.sample(n_samples, rng)
+        if isinstance(I, Star):
+            pts = [pts[:, i] for i in range(pts.shape[1])]
+        if not pts:
+            return []
+        ys = self.evaluate(list(pts))
+        return [p for p, y in zip(pts, ys) if any(h.contains(y) for h in Us)]
+
+    def verify_safety(self, I, U, reachOptions=None, n_samples=0, rng=None):
+        """NN.verify_safety (NN.m:827-927) for the over-approximating methods of this engine: 1 safe (every
+        intersection of the reach set with U is empty), else falsification with ``n_samples`` inputs: 0 unsafe
+        when one of them reaches U, 2 unknown otherwise (and when n_samples = 0).  Returns (result, counter_inputs)."""
+        R = self.reach(I, reachOptions)
+        Us = list(U) if isinstance(U, (list, tuple)) else [U]
+        if verify_specification([R], Us) == 1:
+            return 1, []
+        if n_samples == 0:
+            return 2, []
+        counter = self.falsify(I, Us, n_samples, rng)
+        return (0, counter) if counter else (2, [])
+
+    def verify_sample_batch(self, inputSets, images, targets, reachOptions=None, n_samples=0, rng=None):
+        """The harness the reference's examples wrap around verify_robustness
+        (examples/Tutorial/SPIE/Classification2D/verifySample.m:1-32), for a list of sets: -1 the image itself is
+        misclassified, 0 not robust — the upper- or lower-bound image of the set (and, with n_samples > 0, one
+        of that many random points of an "unknown" set) is classified differently — else the verdict of
+        verify_robustness (1 robust, 2 unknown).  All concrete evaluations run as one batched forward pass."""
+        n = len(inputSets)
+        res = np.full(n, 2, dtype=np.int64)
+        pts = []
+        for s, img in zip(inputSets, images):
+            if s.im_lb is None:
+                lb, ub = s.estimateRanges()
+            else:
+                lb, ub = s.im_lb, s.im_ub
+            pts += [np.asarray(img, dtype=np.float64).reshape(lb.shape), ub, lb]
+        ys = self.evaluate(pts)
+        lab = np.array([int(np.argmax(y)) + 1 for y in ys]).reshape(n, 3)
+        t = np.asarray(targets, dtype=np.int64)
+        res[lab[:, 0] != t] = -1
+        res[(lab[:, 0] == t) & ((lab[:, 1] != t) | (lab[:, 2] != t))] = 0
+        todo = np.nonzero(res == 2)[0]
+        if len(todo):
+            res[todo] = self.verify_robustness_batch([inputSets[i] for i in todo], reachOptions, list(t[todo]))
+        if n_samples > 0:
+            for i in np.nonzero(res == 2)[0]:
+                if self.falsify(inputSets[i], self.robustness_set(int(t[i]), "max"), n_samples, rng):
+                    res[i] = 0
+        return res
 
     # -- robustness ------------------------------------------------------------
     def robustness_set(self, target, class_type="max"):

@@ -474,6 +474,66 @@ def verify_robustness(layers, q, keep_trace=False):
     return (v, S) if keep_trace else v
 
 
+def evaluate(layers, x):
+    """NN.evaluate (NN.m:130-145 -> evaluate_noConns :1416-1425): each layer's evaluate on one concrete input
+    x[H,W,C] (or a vector): the affine layer maps above applied to a set without generators, and
+    PosLin.evaluate = max(x, 0) for ReLU.  Returns the output, column-major flattened."""
+    x = np.asarray(x, dtype=np.float64)
+    if x.ndim == 1:
+        x = x.reshape(-1, 1, 1)
+    if x.ndim == 2:
+        x = x[:, :, None]
+    S = ImageStar(np.asfortranarray(x[..., None]), sp.csr_matrix((0, 0)), np.zeros(0), np.zeros(0), np.zeros(0))
+    for L in layers:
+        t = L["type"]
+        if t == "relu":
+            S = ImageStar(np.maximum(S.V, 0.0), S.C, S.d, S.pl, S.pu)
+        elif t == "imageinput":
+            S = image_input_reach(S, L)
+        elif t == "flatten":
+            S = flatten_reach(S, L)
+        elif t == "conv2d":
+            S = conv2d_reach(S, L)
+        elif t == "fc":
+            S = fc_reach(S, L)
+        elif t == "bn":
+            S = bn_reach(S, L)
+        elif t == "avgpool":
+            S = avgpool_reach(S, L)
+        else:
+            raise ValueError(t)
+    return S.V[..., 0].reshape(-1, order="F")
+
+
+def halfspace_contains(G, g, y):
+    """HalfSpace.contains (HalfSpace.m:35-55): no entry of g - G*y is negative."""
+    return not np.any(np.asarray(g, float).ravel() - np.atleast_2d(G) @ y < 0)
+
+
+def falsify(layers, points, G, g):
+    """NN.falsify (NN.m:930-988) on given sample points (the reference draws them with Star.sample /
+    MATLAB's rand; a caller hands the same points to both implementations): the points whose output lies in
+    one of the halfspaces G[j] x <= g[j]."""
+    out = []
+    for x in points:
+        y = evaluate(layers, x)
+        if any(halfspace_contains(G[j:j + 1], g[j:j + 1], y) for j in range(G.shape[0])):
+            out.append(x)
+    return out
+
+
+def verify_sample(layers, q, image, verdict_fn=None):
+    """examples/Tutorial/SPIE/Classification2D/verifySample.m:1-32 for a bounds-form workload query: -1
+    misclassified image, 0 when the upper- or lower-bound image is classified differently, else
+    verify_robustness."""
+    t = q["target"]
+    if int(np.argmax(evaluate(layers, image))) != t:
+        return -1
+    if int(np.argmax(evaluate(layers, q["ub"]))) != t or int(np.argmax(evaluate(layers, q["lb"]))) != t:
+        return 0
+    return (verdict_fn or verify_robustness)(layers, q)
+
+
 def output_ranges(S):
     """Star.estimateRanges of the final set."""
     return estimate_ranges(S.mat(), S.pl, S.pu)
