@@ -241,6 +241,39 @@ int nnvb_batch_upload(nnvb_batch* b);
  * on the same uploaded inputs. */
 int nnvb_batch_reach(nnvb_batch* b, const nnvb_opts* opts);
 
+/* ---- LP-tightened bounds (the reference's default 'approx-star') ---------- */
+
+/* PosLin.reach_star_approx2 (PosLin.m:747-857) uses the estimated ranges only
+ * to pre-select: every neuron they call crossing gets its exact upper bound by
+ * an LP over the set's constraints (Star.getMaxs, Star.m:898-970), those still
+ * above zero their exact lower bound (Star.getMins, :784-856), and the
+ * relaxation is built from the LP bounds.  The LP solver stays on the host, as
+ * in the reference (lpsolver.m); the engine calls `fn` once per ReLU layer that
+ * has such neurons, from inside nnvb_batch_reach, after the classification by
+ * estimated ranges.  Inside the hook the caller may use, for that layer:
+ *   nnvb_batch_get_crossing        the listed neurons of a query and their estimated bounds
+ *   nnvb_batch_get_crossing_rows   their rows of the generator matrix and centre values (the LP objectives)
+ *   nnvb_batch_get_constraints_before / nnvb_batch_out_dims / nnvb_batch_get_pred_bounds
+ *                                  the constraint system and predicate box entering the layer
+ *   nnvb_batch_tighten_crossing    hand back xmin / xmax for the listed neurons of a query
+ * and the engine then classifies again: xmax <= 0 clears the row, xmin >= 0
+ * leaves it untouched, otherwise the neuron is relaxed with [xmin, xmax].
+ * The reach must keep constraint records (opts.keep_constraints).  fn returns
+ * 0 on success.  NULL removes the hook. */
+typedef int (*nnvb_bounds_fn)(void* user, nnvb_batch* b, int relu_layer);
+int nnvb_batch_set_bounds_hook(nnvb_batch* b, nnvb_bounds_fn fn, void* user);
+/* Rows of query q's generator matrix at the listed neurons of the running
+ * layer: G is [k x P_in] column-major in the reference's predicate order, c[k]
+ * the centre values.  Only valid inside the hook, for its relu_layer. */
+int nnvb_batch_get_crossing_rows(nnvb_batch* b, int q, int relu_layer, double* G, double* c);
+/* Constraint system of query q entering ReLU layer relu_layer: *m rows, P_in
+ * columns (what nnvb_batch_get_constraints would give after the layers before
+ * it).  Cmat / d may be NULL to ask for *m only. */
+int nnvb_batch_get_constraints_before(nnvb_batch* b, int q, int relu_layer, int64_t* m, double* Cmat, double* d);
+/* LP bounds of the k listed neurons of query q, in the order of
+ * nnvb_batch_get_crossing.  Only valid inside the hook. */
+int nnvb_batch_tighten_crossing(nnvb_batch* b, int q, int relu_layer, const double* xmin, const double* xmax);
+
 /* ---- results of a reach -------------------------------------------------- */
 
 /* Number of predicates P and of constraint rows m of query q's output set. */

@@ -64,6 +64,10 @@ class ReluStats(C.Structure):
 ALLREDUCE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p)
 
 
+# int (*nnvb_bounds_fn)(void* user, nnvb_batch* b, int relu_layer)
+BOUNDS_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_int)
+
+
 class NNVError(RuntimeError):
     """A non-zero status from the C ABI; ``status`` holds the nnvb_status code."""
 
@@ -99,6 +103,10 @@ SIGNATURES = {
                                       C.c_int64, c_double_p, c_double_p]),
     "nnvb_batch_upload": (C.c_int, [C.c_void_p]),
     "nnvb_batch_reach": (C.c_int, [C.c_void_p, C.POINTER(Opts)]),
+    "nnvb_batch_set_bounds_hook": (C.c_int, [C.c_void_p, BOUNDS_FN, C.c_void_p]),
+    "nnvb_batch_get_crossing_rows": (C.c_int, [C.c_void_p, C.c_int, C.c_int, c_double_p, c_double_p]),
+    "nnvb_batch_get_constraints_before": (C.c_int, [C.c_void_p, C.c_int, C.c_int, c_int64_p, c_double_p, c_double_p]),
+    "nnvb_batch_tighten_crossing": (C.c_int, [C.c_void_p, C.c_int, C.c_int, c_double_p, c_double_p]),
     "nnvb_batch_out_dims": (C.c_int, [C.c_void_p, C.c_int, c_int64_p, c_int64_p]),
     "nnvb_batch_get_V": (C.c_int, [C.c_void_p, C.c_int, c_double_p]),
     "nnvb_batch_get_pred_bounds": (C.c_int, [C.c_void_p, C.c_int, c_double_p, c_double_p]),

@@ -269,6 +269,14 @@ struct PeerSums {
 int launch_classify_scan(cudaStream_t st, const ReluWork& w, const double* sums, int64_t* launches,
                          const PeerSums* peers = nullptr);
 int launch_rank_cross(cudaStream_t st, const ReluWork& w, const ReluRecord& rec, int64_t* launches);
+// LP-tightened bounds: overwrite the bounds of the k listed neurons of one query (lb_q / ub_q point at the
+// query's [N] arrays), then classify every query again from w.lb / w.ub (outputs as launch_classify_scan).
+int launch_tighten_bounds(cudaStream_t st, int64_t k, int64_t N, const int32_t* idx, const double* xmin,
+                          const double* xmax, double* lb_q, double* ub_q, int64_t* launches);
+int launch_reclassify_scan(cudaStream_t st, const ReluWork& w, int64_t* launches);
+// out[pos*k + t] = V[col][idx[t]] for the P listed columns (pos = col_pos[col]): rows of a query's matrix.
+int launch_gather_rows(cudaStream_t st, int64_t k, int64_t P, const int32_t* idx, const int32_t* qcol,
+                       const int64_t* col_pos, const double* V, int64_t ld, double* out, int64_t* launches);
 // Zero dead and crossing rows in all existing columns; save crossing rows.
 int launch_relu_zero_rows(cudaStream_t st, const ReluWork& w, int64_t ncols, const int32_t* col_q,
                           const ReluRecord& rec, const int64_t* col_pos, int64_t* launches);

@@ -250,6 +250,13 @@ struct nnvb_batch {
     nnvb_opts opts{};
     // final output ranges cache
     bool have_out_ranges = false;
+    // LP-tightened bounds (nnvb_batch_set_bounds_hook): the hook runs inside relu_step, between the
+    // classification by estimated ranges and the relaxation
+    nnvb_bounds_fn bounds_fn = nullptr;
+    void* bounds_user = nullptr;
+    int hook_layer = -1;                 // >= 0: the hook of this ReLU layer is running
+    bool hook_tightened = false;
+    ReluWork hook_w{};                   // the layer's working set while the hook runs
 };
 
 namespace {
@@ -345,6 +352,7 @@ int h2d_small(nnvb_ctx* ctx, void* dst, const void* src, size_t bytes) {
     return NNVB_OK;
 }
 
+int assemble_constraints(nnvb_batch* b, int q, int n_layers, int64_t* m_out, double* Cmat, double* d);
 int forward_points(nnvb_net* net, WorkBufs* wk, nnvb_batch* b, int n, const int32_t* d_pair_q, double** X, int64_t* ldx,
                    const double* d_r, const int64_t* d_roff, double* d_alpha);
 
@@ -1105,7 +1113,10 @@ int ensure_clean(nnvb_batch* b, nnvb_batch::Cohort& co) {
     return NNVB_OK;
 }
 
-int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_onehot, size_t next_layer) {
+int relu_step_finish(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_onehot, size_t next_layer, ReluWork& w,
+                     const std::vector<int64_t>& dead);
+
+int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_onehot, size_t next_layer, int relu_index) {
     nnvb_ctx* ctx = b->net->ctx;
     cudaStream_t st = ctx->stream;
     const int nq = b->nq;
@@ -1304,6 +1315,55 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
                     double(ld) * double(b->ncols) * 8e-9);
         }
     }
+    if (b->bounds_fn != nullptr && K > 0) {
+        // The neurons the estimates call crossing are listed (index, centre, estimated bounds) so that the hook
+        // can read them and their rows, solve its LPs and hand the tightened bounds back; then the layer is
+        // classified again from the bound arrays.
+        if (ctx->world > 1) {
+            set_error("LP-tightened bounds are not available with sharded generators");
+            return NNVB_E_UNSUPPORTED;
+        }
+        const size_t k0 = size_t(K);
+        NNVB_TRY(rec->idx.ensure(sizeof(int32_t) * k0, st));
+        NNVB_TRY(rec->q.ensure(sizeof(int32_t) * k0, st));
+        NNVB_TRY(rec->c.ensure(sizeof(double) * k0, st));
+        NNVB_TRY(rec->l.ensure(sizeof(double) * k0, st));
+        NNVB_TRY(rec->u.ensure(sizeof(double) * k0, st));
+        ReluRecord r0{};
+        r0.idx = rec->idx.as<int32_t>(); r0.q = rec->q.as<int32_t>();
+        r0.c = rec->c.as<double>(); r0.l = rec->l.as<double>(); r0.u = rec->u.as<double>();
+        NNVB_TRY(launch_rank_cross(st, w, r0, &ctx->launches));
+        rec->N = N;
+        rec->K = K;
+        rec->P_in.resize(nq);
+        for (int q = 0; q < nq; ++q) rec->P_in[q] = b->h_Pglob[q];
+        b->hook_layer = relu_index;
+        b->hook_tightened = false;
+        b->hook_w = w;
+        const int rc = b->bounds_fn(b->bounds_user, b, relu_index);
+        b->hook_layer = -1;
+        if (rc != 0) {
+            set_error("the bounds hook failed with code %d at ReLU layer %d", rc, relu_index);
+            return NNVB_E_STATE;
+        }
+        if (b->hook_tightened) {
+            NNVB_TRY(launch_reclassify_scan(st, w, &ctx->launches));
+            NNVB_CUDA(cudaMemcpyAsync(rec->new_off.data(), w.q_new_off, sizeof(int64_t) * (nq + 1), cudaMemcpyDeviceToHost, st));
+            NNVB_CUDA(cudaMemcpyAsync(dead.data(), w.q_dead, sizeof(int64_t) * nq, cudaMemcpyDeviceToHost, st));
+            NNVB_TRY(sync(ctx));
+        }
+    }
+    return relu_step_finish(b, rec, lazy_mask, lazy_onehot, next_layer, w, dead);
+}
+
+// Second half of the ReLU step: the relaxation from the (possibly tightened) classification.
+int relu_step_finish(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_onehot, size_t next_layer, ReluWork& w,
+                     const std::vector<int64_t>& dead) {
+    nnvb_ctx* ctx = b->net->ctx;
+    cudaStream_t st = ctx->stream;
+    const int nq = b->nq;
+    const int64_t N = b->N, ld = b->ld;
+    const int64_t K = rec->new_off[nq];
     rec->N = N;
     rec->K = K;
     rec->n_dead = 0;
@@ -1679,7 +1739,7 @@ int run_layers(nnvb_batch* b) {
             const bool lazy_mask = !eager && !eager_mask && (nt == NNVB_LAYER_CONV2D || nt == NNVB_LAYER_AVGPOOL2D) &&
                                    int64_t(b->nq) * b->N < (int64_t(1) << 31);     // the mask offsets are 32-bit
             const bool lazy_onehot = !eager && (nt == NNVB_LAYER_CONV2D || nt == NNVB_LAYER_AVGPOOL2D || nt == NNVB_LAYER_FC);
-            NNVB_TRY(relu_step(b, b->wk->relu[relu_i].get(), lazy_mask, lazy_onehot, li + 1));
+            NNVB_TRY(relu_step(b, b->wk->relu[relu_i].get(), lazy_mask, lazy_onehot, li + 1, relu_i));
             ++relu_i;
         }
         b->shape[0] = L.Ho; b->shape[1] = L.Wo; b->shape[2] = L.Co;
@@ -1691,6 +1751,10 @@ int run_layers(nnvb_batch* b) {
 
 int check_reached(const nnvb_batch* b, int q) {
     if (!b) { set_error("NULL batch"); return NNVB_E_ARG; }
+    if (b->hook_layer >= 0) {            // inside the bounds hook: the layers run so far can be read
+        if (q < 0 || q >= b->nq) { set_error("query %d out of range", q); return NNVB_E_ARG; }
+        return NNVB_OK;
+    }
     if (!b->reached) { set_error("results requested before nnvb_batch_reach succeeded"); return NNVB_E_STATE; }
     if (b->net->ctx->result_owner != b) {
         set_error("the results of this batch were overwritten by a later reach on the same context");
@@ -2114,14 +2178,85 @@ int nnvb_batch_get_layer_ranges(nnvb_batch* b, int q, int relu_layer, double* lb
 int nnvb_batch_get_constraints(nnvb_batch* b, int q, double* Cmat, double* d) {
     NNVB_TRY(check_reached(b, q));
     NNVB_REQUIRE(Cmat && d, "nnvb_batch_get_constraints: NULL output");
+    return assemble_constraints(b, q, b->net->n_relu, nullptr, Cmat, d);
+}
+
+int nnvb_batch_get_constraints_before(nnvb_batch* b, int q, int relu_layer, int64_t* m, double* Cmat, double* d) {
+    NNVB_TRY(check_reached(b, q));
+    NNVB_REQUIRE(relu_layer >= 0 && relu_layer <= b->net->n_relu && m, "nnvb_batch_get_constraints_before: bad argument");
+    NNVB_REQUIRE(b->hook_layer < 0 || relu_layer <= b->hook_layer, "nnvb_batch_get_constraints_before: layer %d has not run yet", relu_layer);
+    return assemble_constraints(b, q, relu_layer, m, Cmat, d);
+}
+
+int nnvb_batch_set_bounds_hook(nnvb_batch* b, nnvb_bounds_fn fn, void* user) {
+    NNVB_REQUIRE(b, "nnvb_batch_set_bounds_hook: NULL batch");
+    b->bounds_fn = fn;
+    b->bounds_user = user;
+    return NNVB_OK;
+}
+
+int nnvb_batch_get_crossing_rows(nnvb_batch* b, int q, int relu_layer, double* G, double* c) {
+    NNVB_REQUIRE(b && b->hook_layer >= 0 && relu_layer == b->hook_layer,
+                 "nnvb_batch_get_crossing_rows: only valid inside the bounds hook, for its layer");
+    NNVB_REQUIRE(q >= 0 && q < b->nq && G && c, "nnvb_batch_get_crossing_rows: bad argument");
+    nnvb_ctx* ctx = b->net->ctx;
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    ReluLayerRecord& r = *b->wk->relu[relu_layer];
+    const int64_t c0 = r.new_off[q], k = r.new_off[q + 1] - c0, P = b->h_qcol_off[q + 1] - b->h_qcol_off[q];
+    if (k == 0) return NNVB_OK;
+    NNVB_TRY(b->wk->tmp.ensure(sizeof(double) * std::max<int64_t>(k * P, 1), ctx->stream));
+    NNVB_TRY(launch_gather_rows(ctx->stream, k, P, r.idx.as<int32_t>() + c0,
+                                b->wk->qcol_idx[b->list_cur].as<int32_t>() + b->h_qcol_off[q],
+                                b->wk->col_pos.as<int64_t>(), b->V, b->ld, b->wk->tmp.as<double>(), &ctx->launches));
+    if (P > 0) NNVB_CUDA(cudaMemcpyAsync(G, b->wk->tmp.p, sizeof(double) * k * P, cudaMemcpyDeviceToHost, ctx->stream));
+    NNVB_CUDA(cudaMemcpyAsync(c, r.c.as<double>() + c0, sizeof(double) * k, cudaMemcpyDeviceToHost, ctx->stream));
+    return sync(ctx);
+}
+
+int nnvb_batch_tighten_crossing(nnvb_batch* b, int q, int relu_layer, const double* xmin, const double* xmax) {
+    NNVB_REQUIRE(b && b->hook_layer >= 0 && relu_layer == b->hook_layer,
+                 "nnvb_batch_tighten_crossing: only valid inside the bounds hook, for its layer");
+    NNVB_REQUIRE(q >= 0 && q < b->nq && xmin && xmax, "nnvb_batch_tighten_crossing: bad argument");
+    nnvb_ctx* ctx = b->net->ctx;
+    NNVB_CUDA(cudaSetDevice(ctx->device));
+    ReluLayerRecord& r = *b->wk->relu[relu_layer];
+    const int64_t c0 = r.new_off[q], k = r.new_off[q + 1] - c0;
+    if (k == 0) return NNVB_OK;
+    for (int64_t t = 0; t < k; ++t)
+        NNVB_REQUIRE(xmin[t] <= xmax[t], "nnvb_batch_tighten_crossing: xmin > xmax (or NaN) at neuron %lld", (long long)t);
+    NNVB_TRY(b->wk->tmp.ensure(sizeof(double) * 2 * k, ctx->stream));
+    NNVB_TRY(h2d_small(ctx, b->wk->tmp.p, xmin, sizeof(double) * k));
+    NNVB_TRY(h2d_small(ctx, b->wk->tmp.as<double>() + k, xmax, sizeof(double) * k));
+    const ReluWork& w = b->hook_w;
+    NNVB_TRY(launch_tighten_bounds(ctx->stream, k, w.N, r.idx.as<int32_t>() + c0, b->wk->tmp.as<double>(),
+                                   b->wk->tmp.as<double>() + k, w.lb + int64_t(q) * w.N, w.ub + int64_t(q) * w.N,
+                                   &ctx->launches));
+    b->hook_tightened = true;
+    return sync(ctx);        // tmp is reused by the next call
+}
+
+}  // extern "C"
+
+namespace {
+
+// Dense constraint system of query q after its first n_layers ReLU layers: rows of the input set, then per
+// layer the three row blocks of PosLin.m:711-735.  *m_out (nullable) receives the row count; Cmat / d nullable.
+int assemble_constraints(nnvb_batch* b, int q, int n_layers, int64_t* m_out, double* Cmat, double* d) {
     nnvb_ctx* ctx = b->net->ctx;
     if (ctx->world > 1) {
         set_error("constraint records are not available with sharded generators");
         return NNVB_E_UNSUPPORTED;
     }
     NNVB_CUDA(cudaSetDevice(ctx->device));
-    int64_t P = 0, m = 0;
-    NNVB_TRY(nnvb_batch_out_dims(b, q, &P, &m));
+    int64_t m = b->m0[q], P = b->P0[q];
+    for (int ri = 0; ri < n_layers; ++ri) {
+        const ReluLayerRecord& r = *b->wk->relu[ri];
+        const int64_t k = r.new_off[q + 1] - r.new_off[q];
+        m += 3 * k;
+        P += k;
+    }
+    if (m_out) *m_out = m;
+    if (!Cmat || !d) return NNVB_OK;
     std::fill(Cmat, Cmat + size_t(m) * P, 0.0);
     // rows of the input set: [C0 0]
     const int64_t m0 = b->m0[q], P0 = b->P0[q];
@@ -2129,7 +2264,7 @@ int nnvb_batch_get_constraints(nnvb_batch* b, int q, double* Cmat, double* d) {
         for (int64_t r = 0; r < m0; ++r) Cmat[size_t(j) * m + r] = b->h_C[q][size_t(j) * m0 + r];
     for (int64_t r = 0; r < m0; ++r) d[r] = b->h_d[q][r];
     int64_t row = m0;
-    for (int ri = 0; ri < b->net->n_relu; ++ri) {
+    for (int ri = 0; ri < n_layers; ++ri) {
         ReluLayerRecord& r = *b->wk->relu[ri];
         const int64_t c0 = r.new_off[q], k = r.new_off[q + 1] - c0, Pin = r.P_in[q];
         if (k == 0) continue;
@@ -2166,6 +2301,10 @@ int nnvb_batch_get_constraints(nnvb_batch* b, int q, double* Cmat, double* d) {
     }
     return NNVB_OK;
 }
+
+}  // namespace
+
+extern "C" {
 
 int nnvb_batch_halfspace_margins(nnvb_batch* b, int q, const double* G, const double* g, int nh, double* margin_lo,
                                  int* status) {

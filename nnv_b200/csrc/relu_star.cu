@@ -730,6 +730,58 @@ classify_peers_kernel(int64_t N, int64_t ld, const double* __restrict__ V, PeerS
     }
 }
 
+// LP-tightened bounds (PosLin.reach_star_approx2, PosLin.m:817-846): the caller solved the LPs of the neurons the
+// estimates call crossing; their bounds replace the estimates ...
+__global__ void tighten_bounds_kernel(int64_t k, int64_t N, const int32_t* __restrict__ idx, const double* __restrict__ xmin,
+                                      const double* __restrict__ xmax, double* __restrict__ lb, double* __restrict__ ub) {
+    const int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= k) return;
+    lb[idx[t]] = xmin[t];
+    ub[idx[t]] = xmax[t];
+}
+
+// ... and the layer is classified again from the bound arrays (same rule, same outputs as range_finalize_kernel).
+__global__ void __launch_bounds__(FIN_THREADS)
+reclassify_kernel(int64_t N, const double* __restrict__ lb, const double* __restrict__ ub, uint8_t* __restrict__ state,
+                  int32_t* __restrict__ blk_cross, unsigned long long* __restrict__ q_dead, int nblk) {
+    const int q = blockIdx.x;
+    int n_cross = 0, n_dead = 0;
+    for (int r = 0; r < FIN_ROWS / FIN_THREADS; ++r) {
+        const int64_t i = int64_t(blockIdx.y) * FIN_ROWS + r * FIN_THREADS + threadIdx.x;
+        if (i >= N) break;
+        const double l = lb[int64_t(q) * N + i], u = ub[int64_t(q) * N + i];
+        uint8_t s = 0;
+        if (u <= 0.0) { s = 1; ++n_dead; }
+        else if (l < 0.0 && u > 0.0) { s = 2; ++n_cross; }
+        state[int64_t(q) * N + i] = s;
+    }
+    __shared__ int sc[FIN_THREADS / 32], sd[FIN_THREADS / 32];
+    for (int o = 16; o; o >>= 1) {
+        n_cross += __shfl_down_sync(0xffffffffu, n_cross, o);
+        n_dead += __shfl_down_sync(0xffffffffu, n_dead, o);
+    }
+    if ((threadIdx.x & 31) == 0) { sc[threadIdx.x >> 5] = n_cross; sd[threadIdx.x >> 5] = n_dead; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tc = 0, td = 0;
+        for (int w = 0; w < FIN_THREADS / 32; ++w) { tc += sc[w]; td += sd[w]; }
+        blk_cross[int64_t(q) * nblk + blockIdx.y] = tc;
+        if (td) atomicAdd(q_dead + q, (unsigned long long)td);
+    }
+}
+
+// Rows idx[0..k) of the query's columns, in predicate order: out[pos*k + t] = V[col(pos)][idx[t]].
+__global__ void gather_rows_kernel(int64_t k, int64_t P, const int32_t* __restrict__ idx, const int32_t* __restrict__ qcol,
+                                   const int64_t* __restrict__ col_pos, const double* __restrict__ V, int64_t ld,
+                                   double* __restrict__ out) {
+    const int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= k) return;
+    for (int64_t j = blockIdx.y; j < P; j += gridDim.y) {
+        const int64_t col = qcol[j];
+        out[col_pos[col] * k + t] = V[col * ld + idx[t]];
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Halfspace rows and their minimum over the predicate box.  A "pair" is one
 // halfspace row G_p x <= g_p tested against the output set of query pair_q[p].
@@ -1151,6 +1203,40 @@ int launch_classify_scan(cudaStream_t st, const ReluWork& w, const double* sums,
     scan_queries_kernel<<<1, 1024, 0, st>>>(w.nq, w.q_cross, w.q_new_off);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 3;
+    return NNVB_OK;
+}
+
+int launch_tighten_bounds(cudaStream_t st, int64_t k, int64_t N, const int32_t* idx, const double* xmin,
+                          const double* xmax, double* lb_q, double* ub_q, int64_t* launches) {
+    if (k <= 0) return NNVB_OK;
+    tighten_bounds_kernel<<<(unsigned)ceil_div(k, 256), 256, 0, st>>>(k, N, idx, xmin, xmax, lb_q, ub_q);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_reclassify_scan(cudaStream_t st, const ReluWork& w, int64_t* launches) {
+    const int nblk = relu_blocks_per_query(w.N);
+    NNVB_CUDA(cudaMemsetAsync(w.q_dead, 0, sizeof(int64_t) * w.nq, st));
+    dim3 grid((unsigned)w.nq, (unsigned)nblk);
+    reclassify_kernel<<<grid, FIN_THREADS, 0, st>>>(w.N, w.lb, w.ub, w.state, w.blk_cross,
+                                                    reinterpret_cast<unsigned long long*>(w.q_dead), nblk);
+    NNVB_CUDA(cudaGetLastError());
+    scan_blocks_kernel<<<w.nq, 256, 0, st>>>(nblk, w.blk_cross, w.q_cross);
+    NNVB_CUDA(cudaGetLastError());
+    scan_queries_kernel<<<1, 1024, 0, st>>>(w.nq, w.q_cross, w.q_new_off);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 3;
+    return NNVB_OK;
+}
+
+int launch_gather_rows(cudaStream_t st, int64_t k, int64_t P, const int32_t* idx, const int32_t* qcol,
+                       const int64_t* col_pos, const double* V, int64_t ld, double* out, int64_t* launches) {
+    if (k <= 0 || P <= 0) return NNVB_OK;
+    dim3 grid((unsigned)ceil_div(k, 128), (unsigned)std::min<int64_t>(P, 32768));
+    gather_rows_kernel<<<grid, 128, 0, st>>>(k, P, idx, qcol, col_pos, V, ld, out);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
     return NNVB_OK;
 }
 

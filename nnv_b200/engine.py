@@ -281,6 +281,47 @@ class Batch:
         o.keep_layer_bounds = int(bool(keep_layer_bounds))
         L.check(self.lib.nnvb_batch_reach(self.handle, C.byref(o)), "nnvb_batch_reach")
 
+    # LP-tightened bounds --------------------------------------------------------
+    def set_bounds_hook(self, fn):
+        """``fn(batch, relu_layer)`` is called inside reach for every ReLU layer with neurons the estimated
+        ranges call crossing (``None`` removes it); see ``lp_bounds_hook``."""
+        if fn is None:
+            self._hook = L.BOUNDS_FN(0)
+        else:
+            def tramp(user, handle, layer):
+                try:
+                    fn(self, int(layer))
+                    return 0
+                except Exception as exc:          # never let an exception cross the C boundary
+                    import sys
+                    print("nnv_b200 bounds hook failed: %r" % (exc,), file=sys.stderr)
+                    self._hook_error = exc
+                    return 1
+            self._hook = L.BOUNDS_FN(tramp)
+        L.check(self.lib.nnvb_batch_set_bounds_hook(self.handle, self._hook, None), "nnvb_batch_set_bounds_hook")
+
+    def get_crossing_rows(self, q, relu_layer, k, P):
+        G = np.empty((k, P), dtype=np.float64, order="F")
+        c = np.empty(k)
+        L.check(self.lib.nnvb_batch_get_crossing_rows(self.handle, q, relu_layer, _dp(G), _dp(c)),
+                "nnvb_batch_get_crossing_rows")
+        return G, c
+
+    def get_constraints_before(self, q, relu_layer, P):
+        m = C.c_int64()
+        L.check(self.lib.nnvb_batch_get_constraints_before(self.handle, q, relu_layer, C.byref(m), None, None),
+                "nnvb_batch_get_constraints_before")
+        Cm = np.empty((m.value, P), dtype=np.float64, order="F")
+        d = np.empty(m.value)
+        L.check(self.lib.nnvb_batch_get_constraints_before(self.handle, q, relu_layer, C.byref(m), _dp(Cm), _dp(d)),
+                "nnvb_batch_get_constraints_before")
+        return Cm, d
+
+    def tighten_crossing(self, q, relu_layer, xmin, xmax):
+        xmin, xmax = _f64(xmin).ravel(), _f64(xmax).ravel()
+        L.check(self.lib.nnvb_batch_tighten_crossing(self.handle, q, relu_layer, _dp(xmin), _dp(xmax)),
+                "nnvb_batch_tighten_crossing")
+
     # results ------------------------------------------------------------------
     def out_dims(self, q):
         P = C.c_int64()

@@ -354,6 +354,47 @@ def _lp_is_empty(Cs, d, pl, pu):
     raise RuntimeError("Error, exitflag = %d (%s)" % (res.status, res.message))
 
 
+def _lp_extreme(f, c0, Cs, d, bounds, box_only, pl, pu, maximize):
+    """Star.getMax / Star.getMin (Star.m:859-895, :745-781) through lpsolver.m: all-zero objective -> the
+    centre value; all-zero constraint matrix -> the closed-form box optimum (lpsolver.m:34-49); else an LP."""
+    if not np.any(f):
+        return c0
+    sgn = -1.0 if maximize else 1.0
+    if box_only:
+        ff = sgn * f
+        return sgn * float(np.sum(np.minimum(ff * pl, ff * pu))) + c0
+    res = linprog(sgn * f, A_ub=Cs, b_ub=d, bounds=bounds, method="highs")
+    if res.status != 0:
+        raise RuntimeError("Cannot find an optimal solution, exitflag = %d (%s)" % (res.status, res.message))
+    return sgn * res.fun + c0
+
+
+def lp_bounds_hook(batch, relu_layer):
+    """The LP half of PosLin.reach_star_approx2 (PosLin.m:813-846) for one ReLU layer of a running reach: for
+    every query, getMaxs over the neurons the estimated ranges call crossing (in ascending index order), then
+    getMins over those whose maximum is positive; the bounds go back to the engine, which re-classifies.  The
+    LPs run on the host (HiGHS standing in for linprog / glpk), as they do in the reference."""
+    for q in range(batch.nq):
+        idx, l_est, u_est = batch.get_crossing(q, relu_layer)
+        k = len(idx)
+        if k == 0:
+            continue
+        P, _ = batch.out_dims(q)
+        G, c = batch.get_crossing_rows(q, relu_layer, k, P)
+        Cm, d = batch.get_constraints_before(q, relu_layer, P)
+        pl, pu = batch.get_pred_bounds(q)
+        Cs = sp.csr_matrix(Cm)
+        box_only = (Cs.shape[0] == 0 or Cs.nnz == 0) and np.all(np.isfinite(pl)) and np.all(np.isfinite(pu)) \
+            and np.all(d >= 0)
+        bounds = list(zip(pl, pu))
+        xmax = np.array([_lp_extreme(G[t], c[t], Cs, d, bounds, box_only, pl, pu, True) for t in range(k)])
+        xmin = np.array(l_est, dtype=np.float64, copy=True)       # only read where xmax > 0
+        for t in np.nonzero(xmax > 0)[0]:
+            xmin[t] = _lp_extreme(G[t], c[t], Cs, d, bounds, box_only, pl, pu, False)
+        xmin = np.minimum(xmin, xmax)
+        batch.tighten_crossing(q, relu_layer, xmin, xmax)
+
+
 # ------------------------------------------------------------------------- layers
 
 
@@ -575,15 +616,16 @@ _LP_FREE_RELAX = ("relax-star-range", "relax-star-area", "relax-star-bound", "re
 
 
 def _validate_reach_options(opts):
-    """The part of NN.validate_reach_options (NN.m:1203-1233) this engine honours.
-    Only the LP-free bound mode exists: 'approx-star' (estimated ranges) or a
-    'relax-star-*' method with relaxFactor = 1."""
+    """The part of NN.validate_reach_options (NN.m:1203-1233) this engine honours:
+    'approx-star' with bounds='estimate' (default: the LP-free ranges of Star.estimateRanges, which is also any
+    'relax-star-*' method at relaxFactor = 1) or bounds='lp' (PosLin.reach_star_approx2 as the reference runs
+    it for 'approx-star': estimated ranges pre-select, host LPs give the bounds of the relaxation)."""
     opts = dict(opts or {})
     method = opts.get("reachMethod", "approx-star")
     rf = opts.get("relaxFactor", 1 if method in _LP_FREE_RELAX else 0)
     if method == "approx-star":
-        if opts.get("bounds", "estimate") != "estimate":
-            raise NotImplementedError("only bounds='estimate' (LP-free ranges) is implemented for approx-star")
+        if opts.get("bounds", "estimate") not in ("estimate", "lp"):
+            raise ValueError("bounds must be 'estimate' (LP-free ranges) or 'lp' (the reference's LP-tightened ranges)")
     elif method in _LP_FREE_RELAX:
         if rf != 1:
             raise NotImplementedError("relax-star methods are implemented for relaxFactor = 1 only (no LP)")
@@ -690,9 +732,13 @@ class NN:
                 raise ValueError("all input sets of a batch must have the same shape")
         net = self._network(shape)
         b = Batch(net, [s._query() for s in inputSets])
+        lp = bool(reachOptions) and dict(reachOptions).get("bounds", "estimate") == "lp"
         t0 = time.perf_counter()
         try:
             b.upload()
+            if lp:                      # the LPs read the constraint system: records are kept
+                b.set_bounds_hook(lp_bounds_hook)
+                keep_constraints = True
             b.reach(keep_constraints=keep_constraints, keep_layer_bounds=keep_layer_bounds)
         except Exception:
             b.close()

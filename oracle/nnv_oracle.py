@@ -319,6 +319,72 @@ def relu_reach(S, keep_constraints=True):
     return ImageStar(newM.reshape(h, w, c, P + 1 + k, order="F"), newC, newd, new_pl, new_pu, trace)
 
 
+def lp_extreme(f, c0, C, d, pl, pu, maximize):
+    """Star.getMax / Star.getMin (Star.m:859-895, :745-781): optimum of c0 + f alpha over C alpha <= d,
+    pl <= alpha <= pu through lpsolver (lpsolver.m): all-zero f returns c0, an all-zero C with d >= 0 the
+    closed-form box optimum (:34-49), else an LP (HiGHS standing in for linprog)."""
+    f = np.asarray(f, dtype=np.float64).ravel()
+    if not np.any(f):
+        return c0
+    sgn = -1.0 if maximize else 1.0
+    if (C.shape[0] == 0 or C.nnz == 0) and np.all(np.isfinite(pl)) and np.all(np.isfinite(pu)) and np.all(d >= 0):
+        ff = sgn * f
+        return sgn * float(np.sum(np.minimum(ff * pl, ff * pu))) + c0
+    res = linprog(sgn * f, A_ub=C, b_ub=d, bounds=list(zip(pl, pu)), method="highs")
+    if res.status != 0:
+        raise RuntimeError("Cannot find an optimal solution, status %d (%s)" % (res.status, res.message))
+    return sgn * res.fun + c0
+
+
+def relu_reach_lp(S):
+    """PosLin.reach_star_approx2, PosLin.m:747-857 — the reference's default 'approx-star': the estimated
+    ranges only pre-select; every neuron they call crossing gets its true upper bound by an LP (getMaxs,
+    :817), those still above zero their true lower bound (getMins, :842); neurons whose LP bounds no longer
+    cross are cleared (xmax <= 0) or left untouched (xmin >= 0); the rest is relaxed with the LP bounds by
+    multipleStepReachStarApprox_at_one (:685-742), ascending index order."""
+    h, w, c, p1 = S.V.shape
+    N = h * w * c
+    P = p1 - 1
+    M = S.mat()
+    lb, ub = estimate_ranges(M, S.pl, S.pu)
+    map1 = np.nonzero(ub <= 0)[0]
+    map2 = np.nonzero((lb < 0) & (ub > 0))[0]
+    C = sp.csr_matrix(S.C)
+    xmax = np.array([lp_extreme(M[i, 1:], M[i, 0], C, S.d, S.pl, S.pu, True) for i in map2])
+    map4 = map2[xmax <= 0] if len(map2) else map2
+    dead = np.concatenate([map1, map4]).astype(np.int64)
+    keep5 = xmax > 0 if len(map2) else np.zeros(0, bool)
+    map6 = map2[keep5]
+    xmax1 = xmax[keep5]
+    xmin = np.array([lp_extreme(M[i, 1:], M[i, 0], C, S.d, S.pl, S.pu, False) for i in map6])
+    keep7 = xmin < 0 if len(map6) else np.zeros(0, bool)
+    cross = map6[keep7]
+    lbc = xmin[keep7]
+    ubc = xmax1[keep7]
+    k = len(cross)
+    In = M.copy(order="F")
+    In[dead, :] = 0.0
+    c_idx = In[cross, 0].copy()
+    G_idx = In[cross, 1:].copy()
+    In[cross, :] = 0.0
+    newM = np.zeros((N, P + 1 + k), order="F")
+    newM[:, :P + 1] = In
+    newM[cross, P + 1 + np.arange(k)] = 1.0
+    a = ubc / (ubc - lbc)
+    b = a * lbc
+    Ik = sp.identity(k, format="csr")
+    m0 = S.C.shape[0]
+    newC = sp.vstack([sp.hstack([S.C, sp.csr_matrix((m0, k))], format="csr"),
+                      sp.hstack([sp.csr_matrix((k, P)), -Ik], format="csr"),
+                      sp.hstack([sp.csr_matrix(G_idx), -Ik], format="csr"),
+                      sp.hstack([sp.csr_matrix(G_idx * (-a)[:, None]), Ik], format="csr")], format="csr")
+    newd = np.concatenate([S.d, np.zeros(k), -c_idx, a * c_idx - b])
+    trace = S.trace + [{"N": N, "lb": lb, "ub": ub, "dead": np.sort(dead), "cross": cross, "cross_est": map2,
+                        "lb_lp": lbc, "ub_lp": ubc, "P_in": P, "P_out": P + k}]
+    return ImageStar(newM.reshape(h, w, c, P + 1 + k, order="F"), newC, newd,
+                     np.concatenate([S.pl, np.zeros(k)]), np.concatenate([S.pu, ubc]), trace)
+
+
 # --------------------------------------------------------------------------
 # network driver and verdict
 
@@ -386,8 +452,9 @@ def flatten_reach(S, L):
     return ImageStar(M.reshape((1, 1, M.shape[0], M.shape[1]), order="F"), S.C, S.d, S.pl, S.pu, S.trace)
 
 
-def reach(layers, S, keep_constraints=True):
-    """NN.reach_noConns layer loop, NN.m:1529-1551."""
+def reach(layers, S, keep_constraints=True, lp_bounds=False):
+    """NN.reach_noConns layer loop, NN.m:1529-1551.  lp_bounds: the ReLU layers use the LP-tightened
+    step (reference default 'approx-star', relaxFactor = 0) instead of the estimated bounds."""
     for L in layers:
         t = L["type"]
         if t == "imageinput":
@@ -403,7 +470,7 @@ def reach(layers, S, keep_constraints=True):
         elif t == "avgpool":
             S = avgpool_reach(S, L)
         elif t == "relu":
-            S = relu_reach(S, keep_constraints)
+            S = relu_reach_lp(S) if lp_bounds else relu_reach(S, keep_constraints)
         else:
             raise ValueError(t)
     return S
