@@ -106,10 +106,13 @@ void conv_arrange_weights(const ConvGeom& g, const double* W, double* dst, int b
 // skipped; see conv_win_f64.cu.  *done stays false, and nothing is launched, for geometries it does not
 // cover (the caller then uses launch_conv_f64).  pack (nullable): the launch also writes a window-only copy of
 // its columns there, column j (from col_base) at j*wh*ww*Cout, entry (h, w, c) of the output window at
-// ((w - w0)*wh + (h - h0))*Cout + c.
+// ((w - w0)*wh + (h - h0))*Cout + c.  cin (nullable): the launch's input columns in the same compact form
+// (column j at cin + j*cin_stride, window wh_in x ww_in), read instead of Vin.  Vout may be null when pack is
+// given: the output then exists in compact form only.
 int launch_conv_win(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn, const RowMask& mask,
                     const ColWindows& win, int wh_in, int ww_in, int64_t col_base, const double* Vin, int64_t ld_in,
-                    double* Vout, int64_t ld_out, int64_t ncols, double* pack, bool* done, int64_t* launches);
+                    double* Vout, int64_t ld_out, int64_t ncols, double* pack, bool* done, int64_t* launches,
+                    const double* cin = nullptr, int64_t cin_stride = 0);
 // Processes columns [col_base, col_base + ncols) of Vin / Vout (pointers to column 0).
 int launch_conv_f64(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn,
                     const RowMask& mask, const ColWindows& win, int64_t col_base, const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
@@ -134,11 +137,13 @@ int launch_zero_outside_windows(cudaStream_t st, int H, int W, int C, const int4
                                 double* V, int64_t ld, int64_t* launches);
 // FC on windowed columns [col0, col0+n) (all with an wh x ww window in the H x W x C input; origins in box):
 // only the weight rows of each column's window are contracted.  scratch: fc_gather_scratch_ints() int32.
+// comp (nullable): the columns in compact form (column col0 + j at comp + j*comp_stride), read instead of Vin.
 size_t fc_gather_scratch_ints(int64_t n, int H, int W, int wh, int ww);
 bool fc_gather_fits(int C, int wh, int ww);
 int launch_fc_gather(cudaStream_t st, int H, int W, int C, int wh, int ww, int Out, const double* Wt, int ldw,
                      const int4* box, int64_t col0, int64_t n, const double* Vin, int64_t ld_in, double* Vout,
-                     int64_t ld_out, int32_t* scratch, int64_t* launches);
+                     int64_t ld_out, int32_t* scratch, int64_t* launches, const double* comp = nullptr,
+                     int64_t comp_stride = 0);
 // FC for a few columns that are all points (bias on every column); used for witness points.
 size_t fc_skinny_scratch_doubles(int In, int Out, int ncols);
 int launch_fc_skinny(cudaStream_t st, int In, int Out, const double* Wt, int ldw, const double* bias,
@@ -355,6 +360,15 @@ int launch_fill_dense_windows(cudaStream_t st, int64_t n, int4* box, int64_t* la
 int launch_avgpool_windowed(cudaStream_t st, const PoolGeom& g, const RowMask& mask, const ColWindows& win,
                             int64_t col_base, const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
                             int64_t ncols, int64_t* launches);
+// Compact (window-only, channel-fastest) storage of windowed columns; see elementwise.cu.  Column jj of the
+// launch (absolute column col_base + jj) starts at comp + jj*stride.
+int launch_avgpool_compact(cudaStream_t st, const PoolGeom& g, const RowMask& mask, const int4* box, int64_t col_base,
+                           int64_t ncols, int wh_in, int ww_in, int wh_out, int ww_out, const double* comp_in,
+                           int64_t stride_in, double* comp_out, int64_t stride_out, int64_t* launches);
+// Writes the in-image entries of the compact windows into the full-length columns [col0, col0+n) of V
+// (clear: the columns are zeroed first, else the memory outside the windows is left as it is).
+int launch_expand_compact(cudaStream_t st, int H, int W, int C, const int4* box, int64_t col0, int64_t n, int wh, int ww,
+                          const double* comp, int64_t stride, double* V, int64_t ld, bool clear, int64_t* launches);
 int launch_count_bounds(cudaStream_t st, int nq, int64_t N, const double* lbub, int64_t* q_count,
                         int64_t* launches);
 

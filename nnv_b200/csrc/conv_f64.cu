@@ -323,7 +323,7 @@ conv_onehot_kernel(ConvGeom g, const double* __restrict__ Wg, int bn_tile, int c
     const int ah = h + g.pad_t - eh, aw = w + g.pad_l - ew;
     const int org_h = ah >= 0 ? (ah + g.sh - 1) / g.sh : -((-ah) / g.sh);
     const int org_w = aw >= 0 ? (aw + g.sw - 1) / g.sw : -((-aw) / g.sw);
-    double* dst = Vout + t * ld_out;
+    double* dst = Vout != nullptr ? Vout + t * ld_out : nullptr;
     // the tap value at output (oh, ow, co), zero where no tap maps it to input (h, w)
     auto entry = [&](int oh, int ow, int co) -> double {
         const int dh_ = h + g.pad_t - oh * g.sh, dw_ = w + g.pad_l - ow * g.sw;
@@ -349,6 +349,7 @@ conv_onehot_kernel(ConvGeom g, const double* __restrict__ Wg, int bn_tile, int c
         }
         if (staged) __syncthreads();
     }
+    if (Vout == nullptr) return;          // the images exist in compact form only
     auto value = [&](int oh, int ow, int co) -> double {
         return staged ? sv[((ow - org_w) * wh + (oh - org_h)) * g.Cout + co] : entry(oh, ow, co);
     };
@@ -547,7 +548,11 @@ int launch_conv_onehot(cudaStream_t st, const ConvGeom& g, const ConvWeights& w,
                        const HotCols& hot, int64_t K_loc, double* Vout, int64_t ld_out, bool zero_fill,
                        double* pack, int64_t* launches) {
     if (K_loc <= 0) return NNVB_OK;
-    if (zero_fill) NNVB_CUDA(cudaMemsetAsync(Vout, 0, sizeof(double) * ld_out * K_loc, st));
+    if (Vout == nullptr && pack == nullptr) {
+        set_error("conv_onehot: no output buffer");
+        return NNVB_E_ARG;
+    }
+    if (zero_fill && Vout != nullptr) NNVB_CUDA(cudaMemsetAsync(Vout, 0, sizeof(double) * ld_out * K_loc, st));
     // the window of a column: (kh-1)*dh/sh + 1 rows, likewise columns, all output channels
     const size_t win_bytes = sizeof(double) * size_t((g.kh - 1) * g.dh / g.sh + 1) * ((g.kw - 1) * g.dw / g.sw + 1) * g.Cout;
     const bool staged = pack != nullptr && win_bytes <= 32768;

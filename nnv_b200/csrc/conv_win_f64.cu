@@ -46,6 +46,10 @@ struct ConvWinParams {
     int64_t pack_stride;            // column j at j*pack_stride + (owl*wh_out + ohl)*Cout + co
     int tab_cap;                    // table entries
     int tail;                       // doubles before the constants and tables
+    // compact input (null: Vin holds full-length columns): the launch's columns window-only and channel fastest,
+    // entry (h, w, c) of column j at cin + j*cin_stride + ((w - w0)*wh_in + (h - h0))*Cin + c
+    const double* cin;
+    int64_t cin_stride;
 };
 
 template <int KH, int WARPS_M, int WARPS_N>
@@ -147,7 +151,8 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
         const int wi = bx.y + owl + kwi - ext_w;
         int off = -1, mo = -1;
         if (hi >= 0 && hi < H && wi >= 0 && wi < W && j0 + col < ncols) {
-            off = int(col * ld_in) + hi + H * wi;
+            off = p.cin != nullptr ? int(col * p.cin_stride) + ((wi - bx.y) * p.wh_in + (hi - bx.x)) * p.g.Cin
+                                   : int(col * ld_in) + hi + H * wi;
             if (mask.state != nullptr && col_base + j0 + col < mask.ncols)
                 mo = int(mask.col_q[col_base + j0 + col] * mask.N) + hi + H * wi;
         }
@@ -157,7 +162,9 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
     }
     __syncthreads();
 
-    const double* in_base = Vin + (col_base + j0) * ld_in;
+    const bool compact_in = p.cin != nullptr;
+    const double* in_base = compact_in ? p.cin + j0 * p.cin_stride : Vin + (col_base + j0) * ld_in;
+    const double* zero_src = compact_in ? p.cin : Vin;      // a valid address for the zero-size copies
     const double* w_base = Wg + (int64_t(n_tile) * p.n_chunks) * p.w_stage;
 
     auto load_stage = [&](int stage, int chunk) {
@@ -166,7 +173,7 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
         const int cil = warp & 7;
         const int ci = chunk * KC + cil;
         const bool ci_ok = ci < p.g.Cin;
-        const double* src_c = in_base + int64_t(ci_ok ? ci : 0) * hw_in;
+        const double* src_c = in_base + (compact_in ? int64_t(ci_ok ? ci : 0) : int64_t(ci_ok ? ci : 0) * hw_in);
         const uint8_t* st_c = mask.state != nullptr ? mask.state + int64_t(ci_ok ? ci : 0) * hw_in : nullptr;
         double* dst_c = is + cil * p.CSI;
         for (int e0 = (warp >> 3) * 32 + lane; e0 < n_e; e0 += 256) {
@@ -184,7 +191,7 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
             for (int u = 0; u < 4; ++u) {
                 if (so[u] < 0) continue;
                 const bool ok = off[u] >= 0 && sv[u] == 0;
-                cp_async8(dst_c + so[u], ok ? (src_c + off[u]) : Vin, ok ? 8 : 0);
+                cp_async8(dst_c + so[u], ok ? (src_c + off[u]) : zero_src, ok ? 8 : 0);
             }
         }
         double* ws = wts + stage * p.w_stage;
@@ -264,7 +271,8 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
     }
     __syncthreads();
     // epilogue 2: staging -> memory; 8 lanes write the 8 patch rows of one (column, channel): 64 contiguous bytes
-    {
+    // (skipped when the launch keeps its output in compact form only)
+    if (Vout != nullptr) {
         const int o = lane & 7;
         const int sub = lane >> 3;
         const int64_t hw_out = int64_t(p.g.Ho) * p.g.Wo;
@@ -303,10 +311,15 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
 template <int KH, int WARPS_M, int WARPS_N>
 int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn, const RowMask& mask,
                const ColWindows& win, int wh_in, int ww_in, int64_t col_base, const double* Vin, int64_t ld_in,
-               double* Vout, int64_t ld_out, int64_t ncols, double* pack, bool* done) {
+               double* Vout, int64_t ld_out, int64_t ncols, double* pack, const double* cin, int64_t cin_stride,
+               bool* done) {
     constexpr int BN = WARPS_N * 8;
     ConvWinParams p;
     p.g = g;
+    p.cin = cin;
+    p.cin_stride = cin_stride;
+    if (Vout == nullptr && (pack == nullptr || g.Cout % 2 != 0)) return NNVB_OK;     // nowhere to write
+    if (cin != nullptr && int64_t(16 * WARPS_M) * cin_stride >= (int64_t(1) << 31)) return NNVB_OK;
     p.pack = g.Cout % 2 == 0 ? pack : nullptr;
     p.pack_stride = int64_t(win.wh) * win.ww * g.Cout;
     p.wh_in = wh_in; p.ww_in = ww_in;
@@ -349,16 +362,17 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
 // nothing is launched) for geometries this kernel does not cover: the caller then uses launch_conv_f64.
 int launch_conv_win(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn, const RowMask& mask,
                     const ColWindows& win, int wh_in, int ww_in, int64_t col_base, const double* Vin, int64_t ld_in,
-                    double* Vout, int64_t ld_out, int64_t ncols, double* pack, bool* done, int64_t* launches) {
+                    double* Vout, int64_t ld_out, int64_t ncols, double* pack, bool* done, int64_t* launches,
+                    const double* cin, int64_t cin_stride) {
     *done = false;
     if (ncols <= 0) { *done = true; return NNVB_OK; }
     if (g.sh != 1 || g.sw != 1 || g.dh != 1 || g.dw != 1 || g.kh != 3 || g.kw > 7 || win.box == nullptr) return NNVB_OK;
     if (win.wh != wh_in + g.kh - 1 || win.ww != ww_in + g.kw - 1) return NNVB_OK;
     int rc = NNVB_OK;
     if (w.bn_tile == 64)
-        rc = launch_cfg<3, 2, 8>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, pack, done);
+        rc = launch_cfg<3, 2, 8>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, pack, cin, cin_stride, done);
     else if (w.bn_tile == 32)
-        rc = launch_cfg<3, 4, 4>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, pack, done);
+        rc = launch_cfg<3, 4, 4>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, pack, cin, cin_stride, done);
     if (rc == NNVB_OK && *done && launches) *launches += 1;
     return rc;
 }

@@ -394,6 +394,100 @@ __global__ void avgpool_windowed_2x2_kernel(PoolGeom g, RowMask mask, ColWindows
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Compact storage of windowed columns.  Column j of a cohort [col0, col0+n) whose columns are zero outside a
+// wh x ww window is kept as its window only, channel fastest: entry (h, w, c) at
+//     base + (j - col0)*stride + ((w - w0_j)*wh + (h - h0_j))*C + c,     (h0_j, w0_j) = box[j].xy.
+// A pixel's channels are contiguous (256-512 bytes for 32-64 channels), so readers and writers move whole
+// sectors.  Entries of a window that hang over the image border are never read (every reader tests the
+// image bounds), so writers may leave anything there.
+
+// Average pooling, compact -> compact.  One thread per (column, output window position, channel), channel
+// fastest.  Same window sum, in the same order, and the same divisor as avgpool_f64_kernel.
+__global__ void __launch_bounds__(256)
+avgpool_compact_kernel(PoolGeom g, RowMask mask, const int4* __restrict__ box, int64_t col_base, int64_t ncols,
+                       int wh_in, int ww_in, int wh_out, int ww_out, const double* __restrict__ Cin_, int64_t stride_in,
+                       double* __restrict__ Cout_, int64_t stride_out) {
+    const int per_col = wh_out * ww_out * g.C;
+    const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= ncols * per_col) return;
+    const int64_t jj = e / per_col;
+    int r = int(e % per_col);
+    const int c = r % g.C;
+    r /= g.C;
+    const int ohl = r % wh_out, owl = r / wh_out;
+    const int64_t j = col_base + jj;
+    const int4 bx = box[j];
+    const int a0 = bx.x + g.pad_t - (g.ph - 1), b0 = bx.y + g.pad_l - (g.pw - 1);
+    const int oh = (a0 >= 0 ? (a0 + g.sh - 1) / g.sh : -((-a0) / g.sh)) + ohl;
+    const int ow = (b0 >= 0 ? (b0 + g.sw - 1) / g.sw : -((-b0) / g.sw)) + owl;
+    double out = 0.0;
+    if (oh >= 0 && ow >= 0 && oh < g.Ho && ow < g.Wo) {
+        const int h0 = oh * g.sh - g.pad_t, w0 = ow * g.sw - g.pad_l;
+        const double* src = Cin_ + jj * stride_in + c;
+        const uint8_t* st = (mask.state != nullptr && j < mask.ncols)
+                                ? mask.state + mask.col_q[j] * mask.N + int64_t(c) * g.H * g.W : nullptr;
+        double acc = 0.0;
+        for (int a = 0; a < g.ph; ++a) {
+            const int h = h0 + a;
+            for (int b = 0; b < g.pw; ++b) {
+                const int w = w0 + b;
+                double v = 0.0;
+                if (h >= 0 && h < g.H && w >= 0 && w < g.W && unsigned(h - bx.x) < unsigned(wh_in) &&
+                    unsigned(w - bx.y) < unsigned(ww_in)) {
+                    if (st == nullptr || st[h + int64_t(g.H) * w] == 0)
+                        v = src[int64_t((w - bx.y) * wh_in + (h - bx.x)) * g.C];
+                }
+                acc = acc + v;
+            }
+        }
+        out = acc / pool_divisor(g, h0, w0);
+    }
+    Cout_[jj * stride_out + int64_t(owl * wh_out + ohl) * g.C + c] = out;
+}
+
+// Compact -> full-length columns: scatter of the in-image window entries.
+__global__ void __launch_bounds__(256)
+expand_compact_kernel(int H, int W, int C, const int4* __restrict__ box, int64_t col0, int64_t n, int wh, int ww,
+                      const double* __restrict__ comp, int64_t stride, double* __restrict__ V, int64_t ld) {
+    const int per_col = wh * ww * C;
+    const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= n * per_col) return;
+    const int64_t jj = e / per_col;
+    int r = int(e % per_col);
+    const int c = r % C;
+    r /= C;
+    const int hl = r % wh, wl = r / wh;
+    const int4 bx = box[col0 + jj];
+    const int h = bx.x + hl, w = bx.y + wl;
+    if (h < 0 || h >= H || w < 0 || w >= W) return;
+    V[(col0 + jj) * ld + h + int64_t(H) * (w + int64_t(W) * c)] = comp[jj * stride + e % per_col];
+}
+
+int launch_avgpool_compact(cudaStream_t st, const PoolGeom& g, const RowMask& mask, const int4* box, int64_t col_base,
+                           int64_t ncols, int wh_in, int ww_in, int wh_out, int ww_out, const double* comp_in,
+                           int64_t stride_in, double* comp_out, int64_t stride_out, int64_t* launches) {
+    if (ncols <= 0) return NNVB_OK;
+    const int64_t total = ncols * wh_out * ww_out * g.C;
+    avgpool_compact_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(g, mask, box, col_base, ncols, wh_in, ww_in,
+                                                                            wh_out, ww_out, comp_in, stride_in, comp_out,
+                                                                            stride_out);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_expand_compact(cudaStream_t st, int H, int W, int C, const int4* box, int64_t col0, int64_t n, int wh, int ww,
+                          const double* comp, int64_t stride, double* V, int64_t ld, bool clear, int64_t* launches) {
+    if (n <= 0) return NNVB_OK;
+    if (clear) NNVB_CUDA(cudaMemsetAsync(V + col0 * ld, 0, sizeof(double) * ld * n, st));
+    const int64_t total = n * wh * ww * C;
+    expand_compact_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(H, W, C, box, col0, n, wh, ww, comp, stride, V, ld);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
 int launch_avgpool_windowed(cudaStream_t st, const PoolGeom& g, const RowMask& mask, const ColWindows& win,
                             int64_t col_base, const double* Vin, int64_t ld_in, double* Vout, int64_t ld_out,
                             int64_t ncols, int64_t* launches) {

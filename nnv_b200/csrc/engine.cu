@@ -118,13 +118,14 @@ struct WorkBufs {
     DevBuf fcg;                          // column grouping of the window-gathered FC
     DevBuf winsort;                      // origin bins and sorted columns of the windowed bound reduction
     DevBuf hot_idx, hot_scale;           // neuron and scale of one-hot columns carried through a pooling layer
-    DevBuf pack;                         // window-only copies of the windowed cohorts for the bound reduction
+    DevBuf pack2[2];                     // compact (window-only, channel-fastest) storage of the windowed cohorts: a layer
+                                         // reads one buffer and writes the other
     DevBuf hs_G, hs_g, hs_q, hs_margin, hs_r, hs_roff, hs_val, hs_scale, hs_bound, wit[2];   // halfspace tests
     std::vector<std::unique_ptr<ReluLayerRecord>> relu;
     void release() {
         DevBuf* bufs[] = {&col_q, &pl, &pu, &col_pos, &box, &qcol_off[0], &qcol_off[1], &qcol_idx[0], &qcol_idx[1],
                           &chunk_beg, &chunk_end, &q_chunk_off, &partial, &sums, &lb, &ub, &state, &rank, &blk_cross,
-                          &q_cross, &q_dead, &q_new_off, &gen_off, &tmp, &fcg, &winsort, &hot_idx, &hot_scale, &pack, &hs_G, &hs_g, &hs_q, &hs_margin, &hs_r,
+                          &q_cross, &q_dead, &q_new_off, &gen_off, &tmp, &fcg, &winsort, &hot_idx, &hot_scale, &pack2[0], &pack2[1], &hs_G, &hs_g, &hs_q, &hs_margin, &hs_r,
                           &hs_roff, &hs_val, &hs_scale, &hs_bound, &wit[0], &wit[1]};
         for (DevBuf* d : bufs) d->release();
         for (auto& r : relu) r->release();
@@ -233,6 +234,10 @@ struct nnvb_batch {
         // window-only copy of the columns in wk->pack, written by the convolution in front of a ReLU layer
         // (offset in doubles, -1: none) for the bound reduction; stale once any layer has run
         int64_t pack_off = -1, pack_stride = 0;
+        int pack_buf = 0;                // which of wk->pack2 holds it
+        // the full-length columns hold the data too (false: the cohort exists in compact form only; a reader
+        // that wants columns has them written first, see ensure_full)
+        bool full_valid = true;
     };
     std::vector<Cohort> cohorts;
     // work a ReLU step left to the layer that follows it (see relu_step)
@@ -1104,7 +1109,29 @@ int make_writable(nnvb_batch* b, int64_t extra_cols) {
 // lazy_onehot: do not materialise the appended unit-vector columns; the next layer writes their images.
 // Windowed launches write the columns' windows only.  A reader that does not go by the windows first has
 // the rest of those columns cleared.
+// A cohort kept in compact form only gets its full-length columns written (windows only when the run fills
+// lazily: the memory outside the windows then stays stale, as after any windowed launch).
+int ensure_full(nnvb_batch* b, nnvb_batch::Cohort& co) {
+    if (co.full_valid) return NNVB_OK;
+    nnvb_ctx* ctx = b->net->ctx;
+    if (co.pack_off < 0) {
+        set_error("internal: a cohort has neither compact nor full-length storage");
+        return NNVB_E_STATE;
+    }
+    NNVB_TRY(make_writable(b, 0));
+    const bool clear = !lazy_fill(b);
+    ProfScope ps(ctx, NNVB_PROF_RELAX, 16.0 * double(co.pack_stride) * double(co.col1 - co.col0));
+    NNVB_TRY(launch_expand_compact(ctx->stream, int(b->shape[0]), int(b->shape[1]), int(b->shape[2]), b->wk->box.as<int4>(),
+                                   co.col0, co.col1 - co.col0, co.wh, co.ww,
+                                   b->wk->pack2[co.pack_buf].as<double>() + co.pack_off, co.pack_stride, b->V, b->ld, clear,
+                                   &ctx->launches));
+    co.full_valid = true;
+    co.clean = clear;
+    return NNVB_OK;
+}
+
 int ensure_clean(nnvb_batch* b, nnvb_batch::Cohort& co) {
+    NNVB_TRY(ensure_full(b, co));
     if (co.clean) return NNVB_OK;
     nnvb_ctx* ctx = b->net->ctx;
     NNVB_TRY(launch_zero_outside_windows(ctx->stream, int(b->shape[0]), int(b->shape[1]), int(b->shape[2]),
@@ -1234,13 +1261,21 @@ int relu_step(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool lazy_one
         int32_t* seg_dev = w.win_scratch + ints;
         NNVB_TRY(h2d_small(ctx, seg_dev, win_seg.data(), sizeof(int32_t) * win_seg.size()));
         w.win_seg = seg_dev;
-        // the window-only copies are read when every windowed cohort has one
+        // the compact copies are read when every windowed cohort has one (they then sit in one buffer: the
+        // layer in front wrote them all); else the cohorts are read from their full-length columns
         bool all_packed = true;
-        for (int k = 0; k < wc.n; ++k) all_packed = all_packed && wc.c[k].pack_off >= 0;
-        w.win_pack = all_packed ? b->wk->pack.as<double>() : nullptr;
+        int buf = -1;
+        for (size_t k = 0; k < b->cohorts.size(); ++k) {
+            if (!is_win[k]) continue;
+            const auto& co = b->cohorts[k];
+            all_packed = all_packed && co.pack_off >= 0 && (buf < 0 || buf == co.pack_buf);
+            if (co.pack_off >= 0) buf = co.pack_buf;
+        }
+        w.win_pack = all_packed && buf >= 0 ? b->wk->pack2[buf].as<double>() : nullptr;
+        if (w.win_pack == nullptr)
+            for (size_t k = 0; k < b->cohorts.size(); ++k)
+                if (is_win[k]) NNVB_TRY(ensure_full(b, b->cohorts[k]));
     }
-    // whatever follows rewrites the tensor: the copies are stale from here on
-    for (auto& co : b->cohorts) co.pack_off = -1;
     w.n_chunks = n_chunks;
     w.chunk_beg = b->wk->chunk_beg.as<int64_t>(); w.chunk_end = b->wk->chunk_end.as<int64_t>();
     w.q_chunk_off = b->wk->q_chunk_off.as<int32_t>();
@@ -1438,6 +1473,15 @@ int relu_step_finish(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool l
         ProfScope ps(ctx, NNVB_PROF_RELAX, relax_bytes);
         if (K > 0) NNVB_TRY(launch_rank_cross(st, w, r, &ctx->launches));
         if (b->opts.keep_constraints) lazy_mask = false;     // the row-clearing kernel also saves the crossing rows
+        if ((K > 0 || rec->n_dead > 0) && !lazy_mask) {
+            // rows are cleared in the full-length columns: cohorts kept in compact form are written out first,
+            // and their compact copies no longer describe the tensor
+            for (auto& co : b->cohorts) {
+                if (co.col0 >= ncols_old) continue;
+                NNVB_TRY(ensure_full(b, co));
+                co.pack_off = -1;
+            }
+        }
         if ((K > 0 || rec->n_dead > 0) && !lazy_mask)
             NNVB_TRY(launch_relu_zero_rows(st, w, ncols_old, b->wk->col_q.as<int32_t>(), r, b->wk->col_pos.as<int64_t>(),
                                            &ctx->launches));
@@ -1466,6 +1510,26 @@ int relu_step_finish(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool l
         b->cohorts.push_back({ncols_old, ncols_old + K_loc, no_windows, 1, 1, true, std::move(qn)});
     }
     return NNVB_OK;
+}
+
+// Whether the consumers of layer li's output can all read compact storage: past the layer's fused BN and an
+// optional ReLU layer (which reads compact copies and leaves its row clearing to a mask when a convolution or
+// pooling layer follows), the next layer must be a convolution the windowed kernel covers, a pooling layer, or
+// a fully connected layer right behind (no ReLU in between: its rows would have to be cleared in memory).
+bool next_reads_compact(const nnvb_net* net, size_t li) {
+    const auto& Ls = net->layers;
+    size_t nx = li + 1;
+    if (Ls[li].type == NNVB_LAYER_CONV2D && Ls[li].fused_bn >= 0) nx = size_t(Ls[li].fused_bn) + 1;
+    bool relu = false;
+    if (nx < Ls.size() && Ls[nx].type == NNVB_LAYER_RELU) { relu = true; ++nx; }
+    if (nx >= Ls.size()) return false;
+    const Layer& N = Ls[nx];
+    if (N.type == NNVB_LAYER_CONV2D)
+        return N.cg.sh == 1 && N.cg.sw == 1 && N.cg.dh == 1 && N.cg.dw == 1 && N.cg.kh == 3 && N.cg.kw <= 7 &&
+               (N.cw.bn_tile == 32 || N.cw.bn_tile == 64);
+    if (N.type == NNVB_LAYER_AVGPOOL2D) return true;
+    if (N.type == NNVB_LAYER_FC) return !relu;
+    return false;
 }
 
 int run_layers(nnvb_batch* b) {
@@ -1501,7 +1565,22 @@ int run_layers(nnvb_batch* b) {
             if (need > ctx->vbuf_bytes()) return capacity_error("layer output", need, ctx->vbuf_bytes());
             double* out = other_vbuf(b);
             const bool lazy = lazy_fill(b);
-            for (auto& co : b->cohorts) co.pack_off = -1;
+            // Compact storage: a layer reads the cohorts' compact copies from one of the two buffers and writes
+            // the other.  The cohorts keep their input state until the layer is through; the output state is
+            // collected here and committed at the end.
+            static const bool pack_on = getenv("NNVB_NO_PACK") == nullptr;
+            static const bool compact_env = getenv("NNVB_NO_COMPACT") == nullptr;
+            const bool compact_on = pack_on && compact_env && lazy;
+            int in_buf = -1;
+            for (auto& co : b->cohorts)
+                if (co.pack_off >= 0) in_buf = co.pack_buf;
+            const int out_buf = in_buf >= 0 ? 1 - in_buf : 0;
+            const size_t n_co = b->cohorts.size();
+            std::vector<int64_t> out_off(n_co, -1), out_stride(n_co, 0);
+            std::vector<char> out_full(n_co, 1);
+            auto comp_in = [&](const nnvb_batch::Cohort& co) -> const double* {
+                return co.pack_off >= 0 ? b->wk->pack2[co.pack_buf].as<double>() + co.pack_off : nullptr;
+            };
             // test aid: fill the output buffer with NaN patterns first, so that a reader that strays outside
             // the windows it was given shows up in the results instead of depending on what the memory held
             static const bool poison = getenv("NNVB_POISON") != nullptr;
@@ -1527,31 +1606,31 @@ int run_layers(nnvb_batch* b) {
                 // one launch per cohort: dense cohorts are tiled over the whole image, windowed cohorts
                 // compute one small output patch per column (the rest of their output stays zero)
                 const double per_pos = 2.0 * L.cg.Cout * L.cg.kh * L.cg.kw * L.cg.Cin;
-                // A ReLU layer next (behind the fused BN): the windowed launches also write a window-only,
-                // channel-fastest copy of their columns, which the bound reduction reads instead of the short
-                // runs of rows in the full-length columns
-                static const bool pack_on = getenv("NNVB_NO_PACK") == nullptr;
+                // The windowed launches write their columns in compact form (window only, channel fastest) when a
+                // ReLU layer follows (its bound reduction reads that form) or when every consumer reads it; in the
+                // second case they write nothing else: the full-length columns of those cohorts stay untouched.
                 double* pack_base = nullptr;
                 int64_t pack_next = 0;
-                {
-                    const size_t nx = L.fused_bn >= 0 ? size_t(L.fused_bn) + 1 : li + 1;
-                    const bool relu_next = nx < net->layers.size() && net->layers[nx].type == NNVB_LAYER_RELU;
-                    if (pack_on && relu_next && !b->opts.keep_constraints && L.cg.Cout % 2 == 0) {
-                        int64_t tot = 0;
-                        for (auto& co : b->cohorts) {
-                            if (co.dense || co.col1 <= co.col0) continue;
-                            const int64_t wh = (co.wh - 1 + (L.cg.kh - 1) * L.cg.dh) / L.cg.sh + 1;
-                            const int64_t ww = (co.ww - 1 + (L.cg.kw - 1) * L.cg.dw) / L.cg.sw + 1;
-                            if (wh * ww <= 128) tot += (co.col1 - co.col0) * wh * ww * L.cg.Cout;
-                        }
-                        // an optimisation only: a copy that would take more than an eighth of the arena, or that
-                        // cannot be allocated, is left out and the bound reduction reads the columns
-                        if (tot > 0 && sizeof(double) * size_t(tot) <= ctx->arena_bytes / 8 &&
-                            b->wk->pack.ensure(sizeof(double) * tot, st) == NNVB_OK)
-                            pack_base = b->wk->pack.as<double>();
+                const size_t nx = L.fused_bn >= 0 ? size_t(L.fused_bn) + 1 : li + 1;
+                const bool relu_next = nx < net->layers.size() && net->layers[nx].type == NNVB_LAYER_RELU;
+                const bool only = compact_on && L.cg.Cout % 2 == 0 && next_reads_compact(net, li);
+                if (pack_on && (relu_next || only) && !b->opts.keep_constraints && L.cg.Cout % 2 == 0) {
+                    int64_t tot = 0;
+                    for (auto& co : b->cohorts) {
+                        if (co.dense || co.col1 <= co.col0) continue;
+                        const int64_t wh = (co.wh - 1 + (L.cg.kh - 1) * L.cg.dh) / L.cg.sh + 1;
+                        const int64_t ww = (co.ww - 1 + (L.cg.kw - 1) * L.cg.dw) / L.cg.sw + 1;
+                        if (wh * ww <= 128) tot += (co.col1 - co.col0) * wh * ww * L.cg.Cout;
                     }
+                    // an optimisation only: a copy that would take more than an eighth of the arena, or that
+                    // cannot be allocated, is left out and everything goes through the full-length columns
+                    if (tot > 0 && sizeof(double) * size_t(tot) <= ctx->arena_bytes / 8 &&
+                        b->wk->pack2[out_buf].ensure(sizeof(double) * tot, st) == NNVB_OK)
+                        pack_base = b->wk->pack2[out_buf].as<double>();
                 }
-                for (auto& co : b->cohorts) {
+                const bool write_full = !(only && pack_base != nullptr);
+                for (size_t k = 0; k < n_co; ++k) {
+                    auto& co = b->cohorts[k];
                     const int64_t c1 = std::min(co.col1, n_dense);
                     if (c1 <= co.col0) continue;
                     const int wh = (co.wh - 1 + (L.cg.kh - 1) * L.cg.dh) / L.cg.sh + 1;
@@ -1566,23 +1645,27 @@ int run_layers(nnvb_batch* b) {
                         bool done = false;
                         if (!no_conv_win && co.col0 >= b->nq) {
                             ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * co.wh * co.ww * double(c1 - co.col0));
-                            NNVB_TRY(launch_conv_win(st, L.cg, L.cw, bn, mask, win, co.wh, co.ww, co.col0, b->V, b->ld, out,
-                                                     ld_out, c1 - co.col0, pack_base ? pack_base + pack_next : nullptr,
-                                                     &done, &ctx->launches));
+                            double* pk = (pack_base && c1 == co.col1) ? pack_base + pack_next : nullptr;
+                            NNVB_TRY(launch_conv_win(st, L.cg, L.cw, bn, mask, win, co.wh, co.ww, co.col0, b->V, b->ld,
+                                                     (pk != nullptr && !write_full) ? nullptr : out, ld_out, c1 - co.col0, pk,
+                                                     &done, &ctx->launches, comp_in(co), co.pack_stride));
                             if (!done) ps.cancel();
-                            if (done && pack_base && c1 == co.col1) {
-                                co.pack_off = pack_next;
-                                co.pack_stride = int64_t(wh) * ww * L.cg.Cout;
-                                pack_next += (c1 - co.col0) * co.pack_stride;
+                            if (done && pk != nullptr) {
+                                out_off[k] = pack_next;
+                                out_stride[k] = int64_t(wh) * ww * L.cg.Cout;
+                                out_full[k] = write_full ? 1 : 0;
+                                pack_next += (c1 - co.col0) * out_stride[k];
                             }
                         }
                         if (!done) {
+                            NNVB_TRY(ensure_full(b, co));
                             ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * wh * ww * double(c1 - co.col0));
                             NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, mask, win, co.col0, b->V, b->ld, out, ld_out,
                                                      c1 - co.col0, b->nq, &ctx->launches));
                         }
                         co.clean = !lazy;
                     } else {
+                        NNVB_TRY(ensure_full(b, co));
                         ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * L.cg.Ho * L.cg.Wo * double(c1 - co.col0));
                         ColWindows win{b->wk->box.as<int4>(), 0, 0};     // whole images; the windows mask the reads
                         NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, mask, win, co.col0, b->V, b->ld, out, ld_out,
@@ -1591,17 +1674,19 @@ int run_layers(nnvb_batch* b) {
                     }
                 }
                 ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(lazy ? L.cg.kh * L.cg.kw * L.cg.Cout : Nout) * double(n_hot));
-                // the unit-vector columns are one cohort (the last): its copy follows the others
+                // the unit-vector columns are one cohort (the last): its compact images follow the others
                 const int64_t hot_stride = int64_t((L.cg.kh - 1) * L.cg.dh / L.cg.sh + 1) *
                                            ((L.cg.kw - 1) * L.cg.dw / L.cg.sw + 1) * L.cg.Cout;
                 const bool pack_hot = pack_base != nullptr && n_hot > 0 && !b->cohorts.empty() &&
                                       b->cohorts.back().col0 == n_dense && b->cohorts.back().col1 == b->ncols &&
                                       !b->cohorts.back().dense;
-                NNVB_TRY(launch_conv_onehot(st, L.cg, L.cw, bn, hot, n_hot, out + n_dense * ld_out, ld_out, !lazy,
+                NNVB_TRY(launch_conv_onehot(st, L.cg, L.cw, bn, hot, n_hot,
+                                            (pack_hot && !write_full) ? nullptr : out + n_dense * ld_out, ld_out, !lazy,
                                             pack_hot ? pack_base + pack_next : nullptr, &ctx->launches));
                 if (pack_hot) {
-                    b->cohorts.back().pack_off = pack_next;
-                    b->cohorts.back().pack_stride = hot_stride;
+                    out_off[n_co - 1] = pack_next;
+                    out_stride[n_co - 1] = hot_stride;
+                    out_full[n_co - 1] = write_full ? 1 : 0;
                     pack_next += n_hot * hot_stride;
                 }
                 for (auto& co : b->cohorts)
@@ -1610,6 +1695,19 @@ int run_layers(nnvb_batch* b) {
                 // one launch per cohort: windowed cohorts contract only the weight rows of their windows
                 static const bool no_fcg = getenv("NNVB_NO_FC_GATHER") != nullptr;
                 const int In = int(L.H * L.W * L.C);
+                // Cohorts that take the dense kernel and lie next to each other go in one launch: every launch
+                // streams the whole weight matrix, so a launch per small cohort would re-read it per cohort.
+                int64_t run0 = -1, run1 = -1;
+                auto flush_dense = [&]() -> int {
+                    if (run0 < 0) return NNVB_OK;
+                    const int64_t n = run1 - run0;
+                    ProfScope ps(ctx, NNVB_PROF_FC, 2.0 * double(L.Co) * double(In) * double(n));
+                    NNVB_TRY(launch_fc_f64(st, In, int(L.Co), L.fc_wt, L.fc_ldw, L.bias, b->V + run0 * b->ld, b->ld,
+                                           out + run0 * ld_out, ld_out, n, std::max<int64_t>(0, b->nq - run0),
+                                           &ctx->launches));
+                    run0 = run1 = -1;
+                    return NNVB_OK;
+                };
                 for (auto& co : b->cohorts) {
                     const int64_t c1 = std::min(co.col1, n_dense);
                     if (c1 <= co.col0) continue;
@@ -1617,12 +1715,18 @@ int run_layers(nnvb_batch* b) {
                     const bool gather = !no_fcg && !co.dense && 2 * co.wh * co.ww <= L.H * L.W &&
                                         fc_gather_fits(int(L.C), co.wh, co.ww);
                     if (gather) {
+                        NNVB_TRY(flush_dense());
                         NNVB_TRY(b->wk->fcg.ensure(sizeof(int32_t) * fc_gather_scratch_ints(n, int(L.H), int(L.W), co.wh, co.ww), st));
                         ProfScope ps(ctx, NNVB_PROF_FC, 2.0 * double(L.Co) * double(L.C) * co.wh * co.ww * double(n));
+                        // a cohort in compact form is contracted from there (when the launch covers all of it)
+                        const double* cin = c1 == co.col1 ? comp_in(co) : nullptr;
+                        if (cin == nullptr) NNVB_TRY(ensure_full(b, co));
                         NNVB_TRY(launch_fc_gather(st, int(L.H), int(L.W), int(L.C), co.wh, co.ww, int(L.Co), L.fc_wt, L.fc_ldw,
                                                   b->wk->box.as<int4>(), co.col0, n, b->V, b->ld, out, ld_out,
-                                                  b->wk->fcg.as<int32_t>(), &ctx->launches));
+                                                  b->wk->fcg.as<int32_t>(), &ctx->launches, cin, co.pack_stride));
                     } else if (co.col1 <= b->nq && n <= 32 && In >= 1024) {
+                        NNVB_TRY(flush_dense());
+                        NNVB_TRY(ensure_full(b, co));
                         // a few centre columns: slice the contraction over the grid instead of two fat tiles
                         ProfScope ps(ctx, NNVB_PROF_FC, 2.0 * double(L.Co) * double(In) * double(n));
                         NNVB_TRY(b->wk->tmp.ensure(sizeof(double) * fc_skinny_scratch_doubles(In, int(L.Co), int(n)), st));
@@ -1631,23 +1735,51 @@ int run_layers(nnvb_batch* b) {
                                                   &ctx->launches));
                     } else {
                         NNVB_TRY(ensure_clean(b, co));
-                        ProfScope ps(ctx, NNVB_PROF_FC, 2.0 * double(L.Co) * double(In) * double(n));
-                        NNVB_TRY(launch_fc_f64(st, In, int(L.Co), L.fc_wt, L.fc_ldw, L.bias, b->V + co.col0 * b->ld, b->ld,
-                                               out + co.col0 * ld_out, ld_out, n, std::max<int64_t>(0, b->nq - co.col0),
-                                               &ctx->launches));
+                        if (run0 >= 0 && run1 != co.col0) NNVB_TRY(flush_dense());
+                        if (run0 < 0) run0 = co.col0;
+                        run1 = c1;
                     }
                 }
+                NNVB_TRY(flush_dense());
                 ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(Nout) * double(n_hot));
                 NNVB_TRY(launch_fc_onehot(st, int(L.Co), L.fc_wt, L.fc_ldw, hot, n_hot, out + n_dense * ld_out, ld_out,
                                           &ctx->launches));
             } else {
-                for (auto& co : b->cohorts) {
+                // cohorts in compact form stay in compact form when every consumer of this layer's output reads it
+                const bool only = compact_on && !b->opts.keep_constraints && next_reads_compact(net, li);
+                double* pack_base = nullptr;
+                int64_t pack_next = 0;
+                if (only) {
+                    int64_t tot = 0;
+                    for (auto& co : b->cohorts) {
+                        if (co.dense || co.pack_off < 0 || co.col1 > n_dense) continue;
+                        const int64_t wh = (co.wh - 1 + L.pg.ph - 1) / L.pg.sh + 1, ww = (co.ww - 1 + L.pg.pw - 1) / L.pg.sw + 1;
+                        if (wh * ww <= 128) tot += (co.col1 - co.col0) * wh * ww * L.pg.C;
+                    }
+                    if (tot > 0 && sizeof(double) * size_t(tot) <= ctx->arena_bytes / 8 &&
+                        b->wk->pack2[out_buf].ensure(sizeof(double) * tot, st) == NNVB_OK)
+                        pack_base = b->wk->pack2[out_buf].as<double>();
+                }
+                for (size_t k = 0; k < n_co; ++k) {
+                    auto& co = b->cohorts[k];
                     const int64_t c1 = std::min(co.col1, n_dense);
                     if (c1 <= co.col0) continue;
                     const int wh = (co.wh - 1 + L.pg.ph - 1) / L.pg.sh + 1;
                     const int ww = (co.ww - 1 + L.pg.pw - 1) / L.pg.sw + 1;
                     const bool windowed = !co.dense && wh * ww <= 128 && 2 * wh * ww <= L.pg.Ho * L.pg.Wo;
-                    if (windowed) {
+                    if (windowed && pack_base != nullptr && co.pack_off >= 0 && c1 == co.col1) {
+                        ProfScope ps(ctx, NNVB_PROF_AVGPOOL,
+                                     8.0 * (double(co.wh) * co.ww * L.pg.C + double(wh) * ww * L.pg.C) * double(c1 - co.col0));
+                        out_off[k] = pack_next;
+                        out_stride[k] = int64_t(wh) * ww * L.pg.C;
+                        out_full[k] = 0;
+                        NNVB_TRY(launch_avgpool_compact(st, L.pg, mask, b->wk->box.as<int4>(), co.col0, c1 - co.col0, co.wh, co.ww,
+                                                        wh, ww, comp_in(co), co.pack_stride, pack_base + pack_next, out_stride[k],
+                                                        &ctx->launches));
+                        pack_next += (c1 - co.col0) * out_stride[k];
+                        co.clean = false;
+                    } else if (windowed) {
+                        NNVB_TRY(ensure_full(b, co));
                         if (!lazy) NNVB_CUDA(cudaMemsetAsync(out + co.col0 * ld_out, 0, sizeof(double) * ld_out * (c1 - co.col0), st));
                         // bytes: the input windows read, the output windows (with a zero fill: columns) written
                         ProfScope ps(ctx, NNVB_PROF_AVGPOOL,
@@ -1658,6 +1790,7 @@ int run_layers(nnvb_batch* b) {
                                                          c1 - co.col0, &ctx->launches));
                         co.clean = !lazy;
                     } else {
+                        NNVB_TRY(ensure_full(b, co));
                         ProfScope ps(ctx, NNVB_PROF_AVGPOOL, 8.0 * double(b->N + Nout) * double(c1 - co.col0));
                         // the kernel numbers columns from 0: shift the mask to the cohort's first column
                         RowMask m2 = mask;
@@ -1718,13 +1851,24 @@ int run_layers(nnvb_batch* b) {
                 b->pend_onehot = 0;
                 b->pend_scaled = false;
             }
+            // the cohorts' storage after the layer
+            for (size_t k = 0; k < n_co; ++k) {
+                auto& co = b->cohorts[k];
+                co.pack_off = out_off[k];
+                co.pack_stride = out_stride[k];
+                co.pack_buf = out_buf;
+                co.full_valid = out_full[k] != 0 || out_off[k] < 0;
+            }
             b->V = out;
             b->N = Nout;
             b->ld = ld_out;
         } else if (L.type == NNVB_LAYER_BN) {
             if (!L.fused_into_prev) {
-                for (auto& co : b->cohorts) co.pack_off = -1;
                 NNVB_TRY(make_writable(b, 0));
+                for (auto& co : b->cohorts) {
+                    NNVB_TRY(ensure_full(b, co));
+                    co.pack_off = -1;
+                }
                 ChanAffine bn{L.bn_mean, L.bn_den, L.bn_rden, L.bn_scale, L.bn_offset};
                 ProfScope ps(ctx, NNVB_PROF_BN, 16.0 * double(b->N) * double(b->ncols));
                 NNVB_TRY(launch_bn_f64(st, bn, L.H * L.W, b->N, b->V, b->ld, b->ncols, b->nq, &ctx->launches));
@@ -2060,9 +2204,11 @@ int nnvb_batch_out_dims(const nnvb_batch* b, int q, int64_t* P, int64_t* m) {
     if (P) *P = Pq;
     if (m) {
         int64_t mm = b->m0[q];
-        for (int i = 0; i < b->net->n_relu; ++i) {
+        // inside the bounds hook: the layers that have run so far
+        const int n_done = b->hook_layer >= 0 ? b->hook_layer : b->net->n_relu;
+        for (int i = 0; i < n_done; ++i) {
             const ReluLayerRecord& r = *b->wk->relu[i];
-            mm += 3 * (r.new_off[q + 1] - r.new_off[q]);
+            if (r.new_off.size() > size_t(q) + 1) mm += 3 * (r.new_off[q + 1] - r.new_off[q]);
         }
         *m = mm;
     }

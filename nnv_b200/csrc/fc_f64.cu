@@ -363,7 +363,11 @@ fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad
                  const double* __restrict__ Wt, int ldw, const double* __restrict__ Vin, int64_t ld_in,
                  double* __restrict__ Vout, int64_t ld_out, const int32_t* __restrict__ tile_key,
                  const int32_t* __restrict__ tile_start, const int32_t* __restrict__ tile_count,
-                 const int32_t* __restrict__ n_tiles, const int32_t* __restrict__ perm) {
+                 const int32_t* __restrict__ n_tiles, const int32_t* __restrict__ perm,
+                 const double* __restrict__ comp, int64_t comp_stride, int64_t comp_col0) {
+    // comp (nullable): the columns in compact form (window only, channel fastest; column j at
+    // comp + (j - comp_col0)*comp_stride).  The contraction index then runs in that storage order,
+    // k = (wl*wh + hl)*C + c, so that a column's operand row is one contiguous run.
     using Cfg = FcCfg<FCG_WM, FCG_WN, FCG_WARPS_M, FCG_WARPS_N>;
     if (int(blockIdx.x) >= *n_tiles) return;
     extern __shared__ __align__(16) double smem[];
@@ -385,8 +389,18 @@ fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad
     for (int k = tid; k < Kt_pad; k += Cfg::THREADS) {
         int row = -1;
         if (k < Kt && !null_bin) {
-            const int hl = k % wh, r2 = k / wh;
-            const int wl = r2 % ww, c = r2 / ww;
+            int hl, wl, c;
+            if (comp != nullptr) {
+                c = k % C;
+                const int pos = k / C;
+                hl = pos % wh;
+                wl = pos / wh;
+            } else {
+                hl = k % wh;
+                const int r2 = k / wh;
+                wl = r2 % ww;
+                c = r2 / ww;
+            }
             const int h = h0 + hl, w = w0 + wl;
             if (h >= 0 && h < H && w >= 0 && w < W) row = h + H * (w + W * c);
         }
@@ -402,7 +416,10 @@ fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad
             const int m = c / FC_BK, kk = c % FC_BK;
             const int row = rows_s[k0 + kk], col = cols_s[m];
             const bool ok = row >= 0 && col >= 0;
-            cp_async8(a + m * FC_AST + kk, ok ? Vin + int64_t(col) * ld_in + row : Vin, ok ? 8 : 0);
+            const double* src = comp != nullptr ? comp : Vin;
+            if (ok) src = comp != nullptr ? comp + (int64_t(col) - comp_col0) * comp_stride + (k0 + kk)
+                                          : Vin + int64_t(col) * ld_in + row;
+            cp_async8(a + m * FC_AST + kk, src, ok ? 8 : 0);
         }
         for (int c = tid; c < FC_BK * (Cfg::BN / 2); c += Cfg::THREADS) {
             const int kr = c / (Cfg::BN / 2), nc = c % (Cfg::BN / 2);
@@ -495,7 +512,7 @@ bool fc_gather_fits(int C, int wh, int ww) { return round_up(int64_t(C) * wh * w
 
 int launch_fc_gather(cudaStream_t st, int H, int W, int C, int wh, int ww, int Out, const double* Wt, int ldw,
                      const int4* box, int64_t col0, int64_t n, const double* Vin, int64_t ld_in, double* Vout,
-                     int64_t ld_out, int32_t* scratch, int64_t* launches) {
+                     int64_t ld_out, int32_t* scratch, int64_t* launches, const double* comp, int64_t comp_stride) {
     if (n <= 0) return NNVB_OK;
     using Cfg = FcCfg<FCG_WM, FCG_WN, FCG_WARPS_M, FCG_WARPS_N>;
     const int KH = H + wh - 1;
@@ -526,7 +543,8 @@ int launch_fc_gather(cudaStream_t st, int H, int W, int C, int wh, int ww, int O
     }
     dim3 grid((unsigned)max_tiles, (unsigned)ceil_div(Out, Cfg::BN));
     fc_gather_kernel<<<grid, Cfg::THREADS, smem, st>>>(H, W, C, wh, ww, KH, Kt, Kt_pad, Out, Wt, ldw, Vin, ld_in, Vout,
-                                                      ld_out, tile_key, tile_start, tile_count, n_tiles, perm);
+                                                      ld_out, tile_key, tile_start, tile_count, n_tiles, perm, comp,
+                                                      comp_stride, col0);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 4;
     return NNVB_OK;

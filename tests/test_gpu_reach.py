@@ -463,3 +463,53 @@ def test_capacity_error_is_reported_not_fatal():
     b.close()
     net.close()
     small_ctx.close()
+
+
+@pytest.mark.parametrize("pool_pad", [False, True])
+def test_compact_storage_chain(ctx, pool_pad):
+    """Channel counts the tap-skipping convolution covers (more than 16 output channels), so that the windowed
+    cohorts travel in compact form (window only, channel fastest) from the first convolution through ReLU
+    layers, two pooling layers and into the gathered FC layer, with windows that hang over every image border.
+    With a padded pooling layer the second half of the chain falls back to full-length columns."""
+    from nnv_b200.configs import _conv, _bn, _fc, RELU, out_shape
+    rng = np.random.default_rng(41)
+    shape = (16, 12, 3)
+    layers = [_conv(rng, 3, 3, 3, 32, (1, 1, 1, 1)), _bn(rng, 32), RELU,
+              _conv(rng, 3, 3, 32, 36, (1, 1, 1, 1)), RELU, _pool(2, 2, 2, 2),
+              _conv(rng, 3, 5, 36, 66, (1, 1, 2, 2)), _bn(rng, 66), RELU,
+              _pool(2, 2, 2, 2, (1, 1, 0, 0) if pool_pad else (0, 0, 0, 0))]
+    h, w, c = out_shape(layers, shape)
+    layers += [_fc(rng, h * w * c, 24), RELU, _fc(rng, 24, 5)]
+    queries = []
+    for k in range(3):
+        x = rng.uniform(0, 1, shape)
+        e = np.zeros(shape)
+        e[k::4, 1::3, :] = 0.02
+        e[0, 0, :] = e[-1, -1, :] = e[0, -1, :] = e[-1, 0, :] = 0.02
+        queries.append({"lb": np.maximum(x - e, 0), "ub": np.minimum(x + e, 1)})
+    net = Network(ctx, layers, shape)
+    b = Batch(net, queries)
+    b.upload()
+    b.reach(keep_layer_bounds=True)
+    for q, qu in enumerate(queries):
+        S = O.reach(layers, O.star_from_query(qu))
+        V = b.get_V(q)
+        assert V.shape == S.V.shape and _rel(V, S.V) < TOL
+        assert sum(len(t["cross"]) for t in S.trace) > 20
+        for li, t in enumerate(S.trace):
+            idx, _, _ = b.get_crossing(q, li)
+            assert np.array_equal(idx, t["cross"]), li
+            ll, lu = b.get_layer_ranges(q, li, t["N"])
+            bscale = max(np.abs(t["lb"]).max(), np.abs(t["ub"]).max())
+            assert np.abs(ll - t["lb"]).max() / bscale < TOL and np.abs(lu - t["ub"]).max() / bscale < TOL
+    b.close()
+    net.close()
+    # a network that ends while its cohorts are in compact form: the set handed out is the dense tensor
+    net = Network(ctx, layers[:6], shape)
+    b = Batch(net, queries[:1])
+    b.upload()
+    b.reach()
+    S = O.reach(layers[:6], O.star_from_query(queries[0]))
+    assert _rel(b.get_V(0), S.V) < TOL
+    b.close()
+    net.close()
