@@ -83,6 +83,8 @@ struct RowMask {
     const int32_t* col_q;
     int64_t ncols;
     int64_t N;
+    // the same states in channel-fastest order, [q][(w*H + h)*C + c] (null: not made), for readers of compact storage
+    const uint8_t* state_cf = nullptr;
 };
 
 // Column windows: column j (absolute index) is exactly zero outside its input window box[j] = {h0, w0, h
@@ -365,6 +367,8 @@ int launch_avgpool_windowed(cudaStream_t st, const PoolGeom& g, const RowMask& m
 int launch_avgpool_compact(cudaStream_t st, const PoolGeom& g, const RowMask& mask, const int4* box, int64_t col_base,
                            int64_t ncols, int wh_in, int ww_in, int wh_out, int ww_out, const double* comp_in,
                            int64_t stride_in, double* comp_out, int64_t stride_out, int64_t* launches);
+int launch_state_channel_fastest(cudaStream_t st, int nq, int H, int W, int C, const uint8_t* state, uint8_t* cf,
+                                 int64_t* launches);
 // Writes the in-image entries of the compact windows into the full-length columns [col0, col0+n) of V
 // (clear: the columns are zeroed first, else the memory outside the windows is left as it is).
 int launch_expand_compact(cudaStream_t st, int H, int W, int C, const int4* box, int64_t col0, int64_t n, int wh, int ww,

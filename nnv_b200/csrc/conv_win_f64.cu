@@ -52,7 +52,11 @@ struct ConvWinParams {
     int64_t cin_stride;
 };
 
-template <int KH, int WARPS_M, int WARPS_N>
+// CIN: the input is read from compact storage (p.cin).  A (column, input position) then holds its 8-channel chunk
+// in 64 contiguous bytes: one thread fetches it with four 16-byte copies into a staging row [column][8 channels]
+// (channel index XOR 4 for every other column pair, which keeps the fragment loads free of bank conflicts without
+// padding), and reads the eight row states of the chunk as one 8-byte word when they come in channel-fastest order.
+template <int KH, int WARPS_M, int WARPS_N, bool CIN>
 __global__ void __launch_bounds__(CW_THREADS, 1)
 conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const ChanAffine bn, const RowMask mask,
                 const int4* __restrict__ box, int64_t col_base, const double* __restrict__ Vin, int64_t ld_in,
@@ -151,47 +155,90 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
         const int wi = bx.y + owl + kwi - ext_w;
         int off = -1, mo = -1;
         if (hi >= 0 && hi < H && wi >= 0 && wi < W && j0 + col < ncols) {
-            off = p.cin != nullptr ? int(col * p.cin_stride) + ((wi - bx.y) * p.wh_in + (hi - bx.x)) * p.g.Cin
-                                   : int(col * ld_in) + hi + H * wi;
-            if (mask.state != nullptr && col_base + j0 + col < mask.ncols)
-                mo = int(mask.col_q[col_base + j0 + col] * mask.N) + hi + H * wi;
+            off = CIN ? int(col * p.cin_stride) + ((wi - bx.y) * p.wh_in + (hi - bx.x)) * p.g.Cin
+                      : int(col * ld_in) + hi + H * wi;
+            if (mask.state != nullptr && col_base + j0 + col < mask.ncols) {
+                const int q_off = int(mask.col_q[col_base + j0 + col] * mask.N);
+                mo = (CIN && mask.state_cf != nullptr) ? q_off + (hi + H * wi) * p.g.Cin : q_off + hi + H * wi;
+            }
         }
         goff[e] = off;
         moff[e] = mo;
-        soff[e] = (kwi * p.ni_s + i_idx) * p.RS + col;
+        // CIN: [origin column][input row][column][8 channels], the swizzle bit of the column in bit 30
+        soff[e] = CIN ? (((kwi * p.ni_s + i_idx) * p.ncol + col) * KC) | (((col >> 1) & 1) << 30)
+                      : (kwi * p.ni_s + i_idx) * p.RS + col;
     }
     __syncthreads();
 
-    const bool compact_in = p.cin != nullptr;
-    const double* in_base = compact_in ? p.cin + j0 * p.cin_stride : Vin + (col_base + j0) * ld_in;
-    const double* zero_src = compact_in ? p.cin : Vin;      // a valid address for the zero-size copies
+    const double* in_base = CIN ? p.cin + j0 * p.cin_stride : Vin + (col_base + j0) * ld_in;
+    const double* zero_src = CIN ? p.cin : Vin;      // a valid address for the zero-size copies
     const double* w_base = Wg + (int64_t(n_tile) * p.n_chunks) * p.w_stage;
 
     auto load_stage = [&](int stage, int chunk) {
         double* is = in_s + stage * p.in_stage;
-        // warp w fetches channel w % 8 of the chunk; the two warps of a channel split the table
-        const int cil = warp & 7;
-        const int ci = chunk * KC + cil;
-        const bool ci_ok = ci < p.g.Cin;
-        const double* src_c = in_base + (compact_in ? int64_t(ci_ok ? ci : 0) : int64_t(ci_ok ? ci : 0) * hw_in);
-        const uint8_t* st_c = mask.state != nullptr ? mask.state + int64_t(ci_ok ? ci : 0) * hw_in : nullptr;
-        double* dst_c = is + cil * p.CSI;
-        for (int e0 = (warp >> 3) * 32 + lane; e0 < n_e; e0 += 256) {
-            int off[4], so[4];
-            uint8_t sv[4];
+        if (CIN) {
+            // one entry per thread and round: the chunk's eight channels of one (column, input position)
+            const int c0 = chunk * KC;
+            const double* src_b = in_base + c0;
+            const bool cf = mask.state_cf != nullptr;
+            const bool word_ok = cf && (p.g.Cin % 8 == 0) && (mask.N % 8 == 0);
+            for (int e = tid; e < n_e; e += CW_THREADS) {
+                const int off = goff[e], so_raw = soff[e], mo = moff[e];
+                const int so = so_raw & 0x3fffffff;
+                const int sw = (so_raw >> 30) & 1 ? 4 : 0;
+                unsigned long long sv = 0ull;          // byte u != 0: channel c0 + u reads as zero
+                if (off >= 0 && mo >= 0) {
+                    if (word_ok) {
+                        sv = *reinterpret_cast<const unsigned long long*>(mask.state_cf + mo + c0);
+                    } else {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int e = e0 + 64 * u;
-                off[u] = (e < n_e && ci_ok) ? goff[e] : -1;
-                so[u] = e < n_e ? soff[e] : -1;
-                const int mo = (e < n_e && ci_ok && st_c != nullptr) ? moff[e] : -1;
-                sv[u] = mo >= 0 ? st_c[mo] : uint8_t(0);
+                        for (int u = 0; u < KC; ++u) {
+                            if (c0 + u >= p.g.Cin) break;
+                            const uint8_t sb = cf ? mask.state_cf[mo + c0 + u] : mask.state[mo + int64_t(c0 + u) * hw_in];
+                            sv |= (unsigned long long)(sb != 0 ? 1 : 0) << (8 * u);
+                        }
+                    }
+                }
+                double* dst = is + so;
+#pragma unroll
+                for (int pr = 0; pr < KC / 2; ++pr) {
+                    const int u0 = 2 * pr;
+                    const bool ok0 = off >= 0 && c0 + u0 < p.g.Cin && ((sv >> (8 * u0)) & 0xffull) == 0;
+                    const bool ok1 = off >= 0 && c0 + u0 + 1 < p.g.Cin && ((sv >> (8 * u0 + 8)) & 0xffull) == 0;
+                    double* d2 = dst + (u0 ^ sw);
+                    if (ok0 && ok1) {
+                        cp_async16(d2, src_b + off + u0, 16);
+                    } else {
+                        cp_async8(d2, ok0 ? src_b + off + u0 : zero_src, ok0 ? 8 : 0);
+                        cp_async8(d2 + 1, ok1 ? src_b + off + u0 + 1 : zero_src, ok1 ? 8 : 0);
+                    }
+                }
             }
+        } else {
+            // warp w fetches channel w % 8 of the chunk; the two warps of a channel split the table
+            const int cil = warp & 7;
+            const int ci = chunk * KC + cil;
+            const bool ci_ok = ci < p.g.Cin;
+            const double* src_c = in_base + int64_t(ci_ok ? ci : 0) * hw_in;
+            const uint8_t* st_c = mask.state != nullptr ? mask.state + int64_t(ci_ok ? ci : 0) * hw_in : nullptr;
+            double* dst_c = is + cil * p.CSI;
+            for (int e0 = (warp >> 3) * 32 + lane; e0 < n_e; e0 += 256) {
+                int off[4], so[4];
+                uint8_t sv[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                if (so[u] < 0) continue;
-                const bool ok = off[u] >= 0 && sv[u] == 0;
-                cp_async8(dst_c + so[u], ok ? (src_c + off[u]) : zero_src, ok ? 8 : 0);
+                for (int u = 0; u < 4; ++u) {
+                    const int e = e0 + 64 * u;
+                    off[u] = (e < n_e && ci_ok) ? goff[e] : -1;
+                    so[u] = e < n_e ? soff[e] : -1;
+                    const int mo = (e < n_e && ci_ok && st_c != nullptr) ? moff[e] : -1;
+                    sv[u] = mo >= 0 ? st_c[mo] : uint8_t(0);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (so[u] < 0) continue;
+                    const bool ok = off[u] >= 0 && sv[u] == 0;
+                    cp_async8(dst_c + so[u], ok ? (src_c + off[u]) : zero_src, ok ? 8 : 0);
+                }
             }
         }
         double* ws = wts + stage * p.w_stage;
@@ -206,7 +253,13 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
         for (int r = 0; r < 4; ++r) acc[o][r] = 0.0;
 
     auto compute = [&](int ch) {
-        const double* is = in_s + (ch & 1) * p.in_stage + t * p.CSI + wm * 16 + g;   // row = column g, k = channel t
+        // row = column g (and g + 8), k = channel t (and t + 4)
+        const int sw = CIN ? ((g >> 1) & 1) * 4 : 0;
+        const double* is = CIN ? in_s + (ch & 1) * p.in_stage + (wm * 16 + g) * KC
+                               : in_s + (ch & 1) * p.in_stage + t * p.CSI + wm * 16 + g;
+        const int RSr = CIN ? p.ncol * KC : p.RS;                                    // stride between staged input rows
+        const int o1 = CIN ? 8 * KC : 8, o2 = CIN ? ((t ^ sw) ^ 4) - (t ^ sw) : 4 * p.CSI;
+        const int o0 = CIN ? (t ^ sw) : 0;
         const double* ws = wts + (ch & 1) * p.w_stage + t * p.CS + wn * 8 + g;      // k = channel t, n = g
         for (int kwi = kw_lo; kwi < kw_hi; ++kwi) {
             double bf[KH][2];
@@ -216,16 +269,16 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
                 bf[khi][0] = wt[0];
                 bf[khi][1] = wt[4 * p.CS];
             }
-            const double* a_col = is + (kwi * p.ni_s - i_lo) * p.RS;
+            const double* a_col = is + (kwi * p.ni_s - i_lo) * RSr + o0;
 #pragma unroll
             for (int i = 0; i < NI; ++i) {
                 if (i < i_lo || i >= i_hi) continue;
-                const double* a = a_col + i * p.RS;
+                const double* a = a_col + i * RSr;
                 double af[4];
                 af[0] = a[0];
-                af[1] = a[8];
-                af[2] = a[4 * p.CSI];
-                af[3] = a[4 * p.CSI + 8];
+                af[1] = a[o1];
+                af[2] = a[o2];
+                af[3] = a[o2 + o1];
                 // input row i meets output row i - khi through tap khi
 #pragma unroll
                 for (int khi = 0; khi < KH; ++khi) {
@@ -308,7 +361,7 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
     }
 }
 
-template <int KH, int WARPS_M, int WARPS_N>
+template <int KH, int WARPS_M, int WARPS_N, bool CIN>
 int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn, const RowMask& mask,
                const ColWindows& win, int wh_in, int ww_in, int64_t col_base, const double* Vin, int64_t ld_in,
                double* Vout, int64_t ld_out, int64_t ncols, double* pack, const double* cin, int64_t cin_stride,
@@ -319,7 +372,9 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
     p.cin = cin;
     p.cin_stride = cin_stride;
     if (Vout == nullptr && (pack == nullptr || g.Cout % 2 != 0)) return NNVB_OK;     // nowhere to write
-    if (cin != nullptr && int64_t(16 * WARPS_M) * cin_stride >= (int64_t(1) << 31)) return NNVB_OK;
+    if (CIN && (int64_t(16 * WARPS_M) * cin_stride >= (int64_t(1) << 31) || g.Cin % 2 != 0 || cin_stride % 2 != 0 ||
+                (reinterpret_cast<uintptr_t>(cin) & 15) != 0))
+        return NNVB_OK;
     p.pack = g.Cout % 2 == 0 ? pack : nullptr;
     p.pack_stride = int64_t(win.wh) * win.ww * g.Cout;
     p.wh_in = wh_in; p.ww_in = ww_in;
@@ -330,7 +385,8 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
     p.CSI = p.ncol + 4;             // = 4 (mod 16): the four channel rows of a fragment fall on distinct banks
     p.CS = w.cs;
     p.RS = KC * p.CSI + 1;
-    p.in_stage = (g.kw * p.ni_s * p.RS + 1) / 2 * 2;        // even: the weights behind it are fetched 16 bytes at a time
+    p.in_stage = CIN ? g.kw * p.ni_s * p.ncol * KC
+                     : (g.kw * p.ni_s * p.RS + 1) / 2 * 2;  // even: the weights behind it are fetched 16 bytes at a time
     p.w_stage = g.kh * g.kw * KC * p.CS;
     p.n_chunks = w.n_chunks;
     p.OSTR = BN + 2;
@@ -347,7 +403,7 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
     if (int64_t(p.ncol) * std::max(ld_in, ld_out) >= (int64_t(1) << 31)) return NNVB_OK;
     const int64_t blocks = ceil_div(ncols, p.ncol) * p.ww_out * p.n_ohb;
     if (blocks >= (int64_t(1) << 31)) return NNVB_OK;
-    auto kern = conv_win_kernel<KH, WARPS_M, WARPS_N>;
+    auto kern = conv_win_kernel<KH, WARPS_M, WARPS_N, CIN>;
     NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((unsigned)blocks, (unsigned)w.n_tiles);
     kern<<<grid, CW_THREADS, smem, st>>>(p, w.w, bn, mask, win.box, col_base, Vin, ld_in, Vout, ld_out, ncols);
@@ -369,10 +425,14 @@ int launch_conv_win(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, co
     if (g.sh != 1 || g.sw != 1 || g.dh != 1 || g.dw != 1 || g.kh != 3 || g.kw > 7 || win.box == nullptr) return NNVB_OK;
     if (win.wh != wh_in + g.kh - 1 || win.ww != ww_in + g.kw - 1) return NNVB_OK;
     int rc = NNVB_OK;
-    if (w.bn_tile == 64)
-        rc = launch_cfg<3, 2, 8>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, pack, cin, cin_stride, done);
+    if (w.bn_tile == 64 && cin != nullptr)
+        rc = launch_cfg<3, 2, 8, true>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, pack, cin, cin_stride, done);
+    else if (w.bn_tile == 64)
+        rc = launch_cfg<3, 2, 8, false>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, pack, cin, cin_stride, done);
+    else if (w.bn_tile == 32 && cin != nullptr)
+        rc = launch_cfg<3, 4, 4, true>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, pack, cin, cin_stride, done);
     else if (w.bn_tile == 32)
-        rc = launch_cfg<3, 4, 4>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, pack, cin, cin_stride, done);
+        rc = launch_cfg<3, 4, 4, false>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, pack, cin, cin_stride, done);
     if (rc == NNVB_OK && *done && launches) *launches += 1;
     return rc;
 }

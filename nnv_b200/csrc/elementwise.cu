@@ -402,48 +402,67 @@ __global__ void avgpool_windowed_2x2_kernel(PoolGeom g, RowMask mask, ColWindows
 // sectors.  Entries of a window that hang over the image border are never read (every reader tests the
 // image bounds), so writers may leave anything there.
 
-// Average pooling, compact -> compact.  One thread per (column, output window position, channel), channel
-// fastest.  Same window sum, in the same order, and the same divisor as avgpool_f64_kernel.
+// Average pooling, compact -> compact.  A thread owns one (output window position, channel), channel fastest, and
+// walks over the columns (blockIdx.y strided), so the index arithmetic is done once.  Same window sum, in the same
+// order, and the same divisor as avgpool_f64_kernel.  mask.state_cf: the row states in channel-fastest order, so that
+// the lanes of a warp (neighbouring channels of one pixel) read neighbouring bytes.
 __global__ void __launch_bounds__(256)
 avgpool_compact_kernel(PoolGeom g, RowMask mask, const int4* __restrict__ box, int64_t col_base, int64_t ncols,
                        int wh_in, int ww_in, int wh_out, int ww_out, const double* __restrict__ Cin_, int64_t stride_in,
                        double* __restrict__ Cout_, int64_t stride_out) {
     const int per_col = wh_out * ww_out * g.C;
-    const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (e >= ncols * per_col) return;
-    const int64_t jj = e / per_col;
-    int r = int(e % per_col);
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= per_col) return;
     const int c = r % g.C;
-    r /= g.C;
-    const int ohl = r % wh_out, owl = r / wh_out;
-    const int64_t j = col_base + jj;
-    const int4 bx = box[j];
-    const int a0 = bx.x + g.pad_t - (g.ph - 1), b0 = bx.y + g.pad_l - (g.pw - 1);
-    const int oh = (a0 >= 0 ? (a0 + g.sh - 1) / g.sh : -((-a0) / g.sh)) + ohl;
-    const int ow = (b0 >= 0 ? (b0 + g.sw - 1) / g.sw : -((-b0) / g.sw)) + owl;
-    double out = 0.0;
-    if (oh >= 0 && ow >= 0 && oh < g.Ho && ow < g.Wo) {
-        const int h0 = oh * g.sh - g.pad_t, w0 = ow * g.sw - g.pad_l;
-        const double* src = Cin_ + jj * stride_in + c;
-        const uint8_t* st = (mask.state != nullptr && j < mask.ncols)
-                                ? mask.state + mask.col_q[j] * mask.N + int64_t(c) * g.H * g.W : nullptr;
-        double acc = 0.0;
-        for (int a = 0; a < g.ph; ++a) {
-            const int h = h0 + a;
-            for (int b = 0; b < g.pw; ++b) {
-                const int w = w0 + b;
-                double v = 0.0;
-                if (h >= 0 && h < g.H && w >= 0 && w < g.W && unsigned(h - bx.x) < unsigned(wh_in) &&
-                    unsigned(w - bx.y) < unsigned(ww_in)) {
-                    if (st == nullptr || st[h + int64_t(g.H) * w] == 0)
-                        v = src[int64_t((w - bx.y) * wh_in + (h - bx.x)) * g.C];
+    const int pos = r / g.C;
+    const int ohl = pos % wh_out, owl = pos / wh_out;
+    const int64_t plane = int64_t(g.H) * g.W;
+    for (int64_t jj = blockIdx.y; jj < ncols; jj += gridDim.y) {
+        const int64_t j = col_base + jj;
+        const int4 bx = box[j];
+        const int a0 = bx.x + g.pad_t - (g.ph - 1), b0 = bx.y + g.pad_l - (g.pw - 1);
+        const int oh = (a0 >= 0 ? (a0 + g.sh - 1) / g.sh : -((-a0) / g.sh)) + ohl;
+        const int ow = (b0 >= 0 ? (b0 + g.sw - 1) / g.sw : -((-b0) / g.sw)) + owl;
+        double out = 0.0;
+        if (oh >= 0 && ow >= 0 && oh < g.Ho && ow < g.Wo) {
+            const int h0 = oh * g.sh - g.pad_t, w0 = ow * g.sw - g.pad_l;
+            const double* src = Cin_ + jj * stride_in + c;
+            const bool masked = mask.state != nullptr && j < mask.ncols;
+            const uint8_t* st = masked ? (mask.state_cf != nullptr ? mask.state_cf + mask.col_q[j] * mask.N + c
+                                                                  : mask.state + mask.col_q[j] * mask.N + c * plane)
+                                       : nullptr;
+            const bool cf = mask.state_cf != nullptr;
+            double acc = 0.0;
+            for (int a = 0; a < g.ph; ++a) {
+                const int h = h0 + a;
+                for (int b = 0; b < g.pw; ++b) {
+                    const int w = w0 + b;
+                    double v = 0.0;
+                    if (h >= 0 && h < g.H && w >= 0 && w < g.W && unsigned(h - bx.x) < unsigned(wh_in) &&
+                        unsigned(w - bx.y) < unsigned(ww_in)) {
+                        const int64_t pix = h + int64_t(g.H) * w;
+                        if (st == nullptr || st[cf ? pix * g.C : pix] == 0)
+                            v = src[int64_t((w - bx.y) * wh_in + (h - bx.x)) * g.C];
+                    }
+                    acc = acc + v;
                 }
-                acc = acc + v;
             }
+            out = acc / pool_divisor(g, h0, w0);
         }
-        out = acc / pool_divisor(g, h0, w0);
+        Cout_[jj * stride_out + r] = out;
     }
-    Cout_[jj * stride_out + int64_t(owl * wh_out + ohl) * g.C + c] = out;
+}
+
+// Row states in channel-fastest order: cf[q][(w*H + h)*C + c] = state[q][h + H*(w + W*c)].
+__global__ void __launch_bounds__(256)
+state_channel_fastest_kernel(int nq, int H, int W, int C, const uint8_t* __restrict__ state, uint8_t* __restrict__ cf) {
+    const int64_t N = int64_t(H) * W * C;
+    const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (e >= N * nq) return;
+    const int64_t q = e / N, i = e % N;
+    const int c = int(i % C);
+    const int64_t pix = i / C;
+    cf[e] = state[q * N + pix + int64_t(H) * W * c];
 }
 
 // Compact -> full-length columns: scatter of the in-image window entries.
@@ -468,10 +487,21 @@ int launch_avgpool_compact(cudaStream_t st, const PoolGeom& g, const RowMask& ma
                            int64_t ncols, int wh_in, int ww_in, int wh_out, int ww_out, const double* comp_in,
                            int64_t stride_in, double* comp_out, int64_t stride_out, int64_t* launches) {
     if (ncols <= 0) return NNVB_OK;
-    const int64_t total = ncols * wh_out * ww_out * g.C;
-    avgpool_compact_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(g, mask, box, col_base, ncols, wh_in, ww_in,
-                                                                            wh_out, ww_out, comp_in, stride_in, comp_out,
-                                                                            stride_out);
+    const int per_col = wh_out * ww_out * g.C;
+    const int threads = per_col >= 256 ? 256 : 128;
+    dim3 grid((unsigned)ceil_div(per_col, threads), (unsigned)std::min<int64_t>(ncols, 16384));
+    avgpool_compact_kernel<<<grid, threads, 0, st>>>(g, mask, box, col_base, ncols, wh_in, ww_in, wh_out, ww_out, comp_in,
+                                                     stride_in, comp_out, stride_out);
+    NNVB_CUDA(cudaGetLastError());
+    if (launches) *launches += 1;
+    return NNVB_OK;
+}
+
+int launch_state_channel_fastest(cudaStream_t st, int nq, int H, int W, int C, const uint8_t* state, uint8_t* cf,
+                                 int64_t* launches) {
+    const int64_t total = int64_t(nq) * H * W * C;
+    if (total <= 0) return NNVB_OK;
+    state_channel_fastest_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, st>>>(nq, H, W, C, state, cf);
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 1;
     return NNVB_OK;

@@ -113,6 +113,7 @@ struct WorkBufs {
     DevBuf col_q, pl, pu, col_pos, box;      // box: int4 {h0, w0, wh, ww} window of each column
     DevBuf qcol_off[2], qcol_idx[2];
     DevBuf chunk_beg, chunk_end, q_chunk_off, partial, sums;
+    DevBuf state_cf;                     // the row states in channel-fastest order (readers of compact storage)
     DevBuf lb, ub, state, rank, blk_cross, q_cross, q_dead, q_new_off, gen_off;
     DevBuf tmp;                          // gathers for downloads
     DevBuf fcg;                          // column grouping of the window-gathered FC
@@ -124,7 +125,7 @@ struct WorkBufs {
     std::vector<std::unique_ptr<ReluLayerRecord>> relu;
     void release() {
         DevBuf* bufs[] = {&col_q, &pl, &pu, &col_pos, &box, &qcol_off[0], &qcol_off[1], &qcol_idx[0], &qcol_idx[1],
-                          &chunk_beg, &chunk_end, &q_chunk_off, &partial, &sums, &lb, &ub, &state, &rank, &blk_cross,
+                          &chunk_beg, &chunk_end, &q_chunk_off, &partial, &sums, &lb, &ub, &state, &state_cf, &rank, &blk_cross,
                           &q_cross, &q_dead, &q_new_off, &gen_off, &tmp, &fcg, &winsort, &hot_idx, &hot_scale, &pack2[0], &pack2[1], &hs_G, &hs_g, &hs_q, &hs_margin, &hs_r,
                           &hs_roff, &hs_val, &hs_scale, &hs_bound, &wit[0], &wit[1]};
         for (DevBuf* d : bufs) d->release();
@@ -243,6 +244,7 @@ struct nnvb_batch {
     // work a ReLU step left to the layer that follows it (see relu_step)
     int64_t pend_mask_ncols = 0;         // > 0: rows with state != 0 of columns [0, n) read as zero
     int64_t pend_mask_N = 0;
+    bool pend_mask_cf = false;           // wk->state_cf holds the same states in channel-fastest order
     int64_t pend_onehot = 0;             // > 0: the last n columns are implicit unit vectors
     ReluLayerRecord* pend_rec = nullptr; // ... of the neurons listed in this record,
     bool pend_scaled = false;            // ... or (after a pooling layer) of wk->hot_idx, times wk->hot_scale
@@ -1500,6 +1502,18 @@ int relu_step_finish(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool l
     rec->cols_after = b->ncols;
     b->pend_mask_ncols = (lazy_mask && (K > 0 || rec->n_dead > 0)) ? ncols_old : 0;
     b->pend_mask_N = N;
+    b->pend_mask_cf = false;
+    if (b->pend_mask_ncols > 0 && b->shape[2] > 1 && b->shape[0] * b->shape[1] * b->shape[2] == N) {
+        // readers of compact storage have neighbouring channels on neighbouring lanes: give them the states in that order
+        bool any_compact = false;
+        for (auto& co : b->cohorts) any_compact = any_compact || co.pack_off >= 0;
+        if (any_compact && b->wk->state_cf.ensure(size_t(nq) * N, st) == NNVB_OK) {
+            ProfScope ps(ctx, NNVB_PROF_RELAX, 2.0 * double(N) * nq);
+            NNVB_TRY(launch_state_channel_fastest(st, nq, int(b->shape[0]), int(b->shape[1]), int(b->shape[2]),
+                                                  b->wk->state.as<uint8_t>(), b->wk->state_cf.as<uint8_t>(), &ctx->launches));
+            b->pend_mask_cf = true;
+        }
+    }
     b->pend_onehot = lazy_onehot ? K_loc : 0;
     b->pend_rec = rec;
     static const bool no_windows = getenv("NNVB_NO_WINDOWS") != nullptr;
@@ -1596,7 +1610,8 @@ int run_layers(nnvb_batch* b) {
             bool keep_hot = false;          // the one-hot columns stay unwritten past this layer
             RowMask mask{nullptr, nullptr, 0, 0};
             if (b->pend_mask_ncols > 0)
-                mask = RowMask{b->wk->state.as<uint8_t>(), b->wk->col_q.as<int32_t>(), b->pend_mask_ncols, b->pend_mask_N};
+                mask = RowMask{b->wk->state.as<uint8_t>(), b->wk->col_q.as<int32_t>(), b->pend_mask_ncols, b->pend_mask_N,
+                               b->pend_mask_cf ? b->wk->state_cf.as<uint8_t>() : nullptr};
             if (L.type == NNVB_LAYER_CONV2D) {
                 ChanAffine bn{nullptr, nullptr, nullptr, nullptr, nullptr};
                 if (L.fused_bn >= 0) {
@@ -1649,6 +1664,13 @@ int run_layers(nnvb_batch* b) {
                             NNVB_TRY(launch_conv_win(st, L.cg, L.cw, bn, mask, win, co.wh, co.ww, co.col0, b->V, b->ld,
                                                      (pk != nullptr && !write_full) ? nullptr : out, ld_out, c1 - co.col0, pk,
                                                      &done, &ctx->launches, comp_in(co), co.pack_stride));
+                            if (!done && comp_in(co) != nullptr) {
+                                // the compact-input form does not cover this geometry: from full-length columns
+                                NNVB_TRY(ensure_full(b, co));
+                                NNVB_TRY(launch_conv_win(st, L.cg, L.cw, bn, mask, win, co.wh, co.ww, co.col0, b->V, b->ld,
+                                                         (pk != nullptr && !write_full) ? nullptr : out, ld_out, c1 - co.col0,
+                                                         pk, &done, &ctx->launches));
+                            }
                             if (!done) ps.cancel();
                             if (done && pk != nullptr) {
                                 out_off[k] = pack_next;

@@ -130,6 +130,10 @@ void create_net(int nlhs, mxArray* plhs[], int nrhs, const mxArray* prhs[], Err&
             const double* p = field_doubles(prhs[1], i, "PoolSize", &n, e); fill_ints(p, n, d.pool, 2, 2);
             p = field_doubles(prhs[1], i, "Stride", &n, e); fill_ints(p, n, d.stride, 2, 1);
             p = field_doubles(prhs[1], i, "PaddingSize", &n, e); fill_ints(p, n, d.pad, 4, 0);
+            // how a padded window is averaged: a MATLAB host reaches this engine where its CPU path would call
+            // vl_nnpool (entries inside the image); DivisorWindow = 1 selects ph*pw (the gpuArray path's avgpool)
+            const double* dv = field_doubles(prhs[1], i, "DivisorWindow", &n, e);
+            d.avgpool_divisor = (dv && dv[0] != 0.0) ? NNVB_POOL_DIV_WINDOW : NNVB_POOL_DIV_INSIDE;
         } else if (type == "relu") {
             d.type = NNVB_LAYER_RELU;
         } else {
