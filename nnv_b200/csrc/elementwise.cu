@@ -453,6 +453,65 @@ avgpool_compact_kernel(PoolGeom g, RowMask mask, const int4* __restrict__ box, i
     }
 }
 
+// The same for 2x2 windows at stride 2 without padding and an even channel count: a thread owns two neighbouring
+// channels of one output position (16-byte loads and stores, the two row states as one 2-byte load), the window
+// origin comes from shifts, and the four loads of a window are issued together.  Per output the same four values
+// in the same order as the general kernel; the quotient by 4 is exact.
+__global__ void __launch_bounds__(256)
+avgpool_compact_2x2_kernel(PoolGeom g, RowMask mask, const int4* __restrict__ box, int64_t col_base, int64_t ncols,
+                           int wh_in, int ww_in, int wh_out, int ww_out, const double* __restrict__ Cin_,
+                           int64_t stride_in, double* __restrict__ Cout_, int64_t stride_out) {
+    const int C2 = g.C / 2;
+    const int per_col = wh_out * ww_out * C2;
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= per_col) return;
+    const int c = 2 * (r % C2);
+    const int pos = r / C2;
+    const int ohl = pos % wh_out, owl = pos / wh_out;
+    const bool cf = mask.state_cf != nullptr;
+    const int64_t plane = int64_t(g.H) * g.W;
+    for (int64_t jj = blockIdx.y; jj < ncols; jj += gridDim.y) {
+        const int64_t j = col_base + jj;
+        const int4 bx = box[j];
+        const int a = bx.x - 1, b2 = bx.y - 1;
+        const int oh = (a >= 0 ? (a + 1) >> 1 : -((-a) >> 1)) + ohl;
+        const int ow = (b2 >= 0 ? (b2 + 1) >> 1 : -((-b2) >> 1)) + owl;
+        double2 out = make_double2(0.0, 0.0);
+        if (oh >= 0 && ow >= 0 && oh < g.Ho && ow < g.Wo) {
+            const int h0 = 2 * oh, w0 = 2 * ow;
+            const double* src = Cin_ + jj * stride_in + c;
+            const bool masked = mask.state != nullptr && j < mask.ncols;
+            const uint8_t* st = masked ? (cf ? mask.state_cf + mask.col_q[j] * mask.N + c
+                                             : mask.state + mask.col_q[j] * mask.N + c * plane) : nullptr;
+            double2 v[4];
+            unsigned sbits[4];
+            bool in[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int h = h0 + (k >> 1), w = w0 + (k & 1);
+                in[k] = h < g.H && w < g.W && unsigned(h - bx.x) < unsigned(wh_in) && unsigned(w - bx.y) < unsigned(ww_in);
+                v[k] = make_double2(0.0, 0.0);
+                sbits[k] = 0u;
+                if (in[k]) {
+                    const int64_t pix = h + int64_t(g.H) * w;
+                    if (st != nullptr)
+                        sbits[k] = cf ? unsigned(*reinterpret_cast<const unsigned short*>(st + pix * g.C))
+                                      : (unsigned(st[pix]) | (unsigned(st[pix + plane]) << 8));
+                    v[k] = *reinterpret_cast<const double2*>(src + int64_t((w - bx.y) * wh_in + (h - bx.x)) * g.C);
+                }
+            }
+            double a0 = 0.0, a1 = 0.0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                a0 = a0 + ((sbits[k] & 0xffu) == 0 ? v[k].x : 0.0);
+                a1 = a1 + ((sbits[k] >> 8) == 0 ? v[k].y : 0.0);
+            }
+            out = make_double2(a0 * 0.25, a1 * 0.25);
+        }
+        *reinterpret_cast<double2*>(Cout_ + jj * stride_out + int64_t(pos) * g.C + c) = out;
+    }
+}
+
 // Row states in channel-fastest order: cf[q][(w*H + h)*C + c] = state[q][h + H*(w + W*c)].
 __global__ void __launch_bounds__(256)
 state_channel_fastest_kernel(int nq, int H, int W, int C, const uint8_t* __restrict__ state, uint8_t* __restrict__ cf) {
@@ -487,9 +546,24 @@ int launch_avgpool_compact(cudaStream_t st, const PoolGeom& g, const RowMask& ma
                            int64_t ncols, int wh_in, int ww_in, int wh_out, int ww_out, const double* comp_in,
                            int64_t stride_in, double* comp_out, int64_t stride_out, int64_t* launches) {
     if (ncols <= 0) return NNVB_OK;
+    const bool pairs = g.ph == 2 && g.pw == 2 && g.sh == 2 && g.sw == 2 && g.pad_t == 0 && g.pad_l == 0 && g.C % 2 == 0 &&
+                       stride_in % 2 == 0 && stride_out % 2 == 0 && (reinterpret_cast<uintptr_t>(comp_in) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(comp_out) & 15) == 0 &&
+                       (mask.state_cf == nullptr || mask.N % 2 == 0);
+    static const bool one_row = getenv("NNVB_POOL_ONE_ROW") != nullptr;
+    if (pairs && !one_row) {
+        const int per2 = wh_out * ww_out * (g.C / 2);
+        const int th2 = per2 >= 256 ? 256 : 128;
+        dim3 grid2((unsigned)ceil_div(per2, th2), (unsigned)std::min<int64_t>(ncols, 65535));
+        avgpool_compact_2x2_kernel<<<grid2, th2, 0, st>>>(g, mask, box, col_base, ncols, wh_in, ww_in, wh_out, ww_out,
+                                                          comp_in, stride_in, comp_out, stride_out);
+        NNVB_CUDA(cudaGetLastError());
+        if (launches) *launches += 1;
+        return NNVB_OK;
+    }
     const int per_col = wh_out * ww_out * g.C;
     const int threads = per_col >= 256 ? 256 : 128;
-    dim3 grid((unsigned)ceil_div(per_col, threads), (unsigned)std::min<int64_t>(ncols, 16384));
+    dim3 grid((unsigned)ceil_div(per_col, threads), (unsigned)std::min<int64_t>(ncols, 65535));
     avgpool_compact_kernel<<<grid, threads, 0, st>>>(g, mask, box, col_base, ncols, wh_in, ww_in, wh_out, ww_out, comp_in,
                                                      stride_in, comp_out, stride_out);
     NNVB_CUDA(cudaGetLastError());

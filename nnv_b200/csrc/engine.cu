@@ -1016,7 +1016,13 @@ int init_sets(nnvb_batch* b) {
     NNVB_TRY(h2d_small(ctx, b->wk->qcol_off[0].p, b->h_qcol_off.data(), sizeof(int64_t) * (nq + 1)));
     bool implicit = false;               // the generator columns are not stored: the first layer writes their images
     if (b->kind == 1) {
-        const size_t need = size_t(ld) * ncols * sizeof(double);
+        // a generator of ImageStar(lb,ub) is a half width times a unit vector: when the first layer writes the
+        // images of such columns itself, they start out as (entry, half width) pairs and are never stored
+        static const bool eager = getenv("NNVB_EAGER_RELU") != nullptr;
+        const int t0 = b->net->layers.empty() ? 0 : b->net->layers[0].type;
+        implicit = !eager && lazy_fill(b) && ncols > nq && N < (int64_t(1) << 31) &&
+                   (t0 == NNVB_LAYER_CONV2D || t0 == NNVB_LAYER_FC || t0 == NNVB_LAYER_AVGPOOL2D);
+        const size_t need = size_t(ld) * ((implicit && ctx->world == 1) ? nq : ncols) * sizeof(double);
         {
             bool stop = need > ctx->vbuf_bytes();      // agreed on by all ranks of a sharded run
             const bool mine = stop;
@@ -1030,17 +1036,11 @@ int init_sets(nnvb_batch* b) {
         NNVB_TRY(b->wk->gen_off.ensure(sizeof(int64_t) * (nq + 1), st));
         NNVB_TRY(h2d_small(ctx, b->wk->gen_off.p, gen_off.data(), sizeof(int64_t) * (nq + 1)));
         double* V = ctx->vbuf(0);
-        // a generator of ImageStar(lb,ub) is a half width times a unit vector: when the first layer writes the
-        // images of such columns itself, they start out as (entry, half width) pairs and are never stored
-        static const bool eager = getenv("NNVB_EAGER_RELU") != nullptr;
-        const int t0 = b->net->layers.empty() ? 0 : b->net->layers[0].type;
-        implicit = !eager && lazy_fill(b) && ncols > nq && N < (int64_t(1) << 31) &&
-                   (t0 == NNVB_LAYER_CONV2D || t0 == NNVB_LAYER_FC || t0 == NNVB_LAYER_AVGPOOL2D);
         if (implicit) {
             NNVB_TRY(b->wk->hot_idx.ensure(sizeof(int32_t) * (ncols - nq), st));
             NNVB_TRY(b->wk->hot_scale.ensure(sizeof(double) * (ncols - nq), st));
         }
-        NNVB_CUDA(cudaMemsetAsync(V, 0, implicit ? size_t(ld) * nq * sizeof(double) : need, st));
+        NNVB_CUDA(cudaMemsetAsync(V, 0, size_t(ld) * (implicit ? nq : ncols) * sizeof(double), st));
         NNVB_TRY(launch_build_from_bounds(st, nq, N, ld, b->d_in.as<double>(), b->wk->gen_off.as<int64_t>(), ctx->rank,
                                           ctx->world, V,
                                           b->wk->col_q.as<int32_t>(), b->wk->pl.as<double>(), b->wk->pu.as<double>(),
@@ -1094,9 +1094,20 @@ double* other_vbuf(nnvb_batch* b) {
     return b->V == ctx->vbuf(0) ? ctx->vbuf(1) : ctx->vbuf(0);
 }
 
+// Leading columns whose full-length storage is in use: cohorts kept in compact form only, and unit-vector columns
+// no layer has written yet, occupy none (a sharded run counts every column: its ranks agree on one figure).
+int64_t full_extent(const nnvb_batch* b) {
+    if (b->net->ctx->world > 1) return b->ncols;
+    int64_t ext = b->nq;
+    const int64_t first_hot = b->ncols - b->pend_onehot;
+    for (const auto& co : b->cohorts)
+        if (co.full_valid && co.col0 < first_hot) ext = std::max(ext, std::min(co.col1, first_hot));
+    return ext;
+}
+
 int make_writable(nnvb_batch* b, int64_t extra_cols) {
     nnvb_ctx* ctx = b->net->ctx;
-    const size_t need = size_t(b->ld) * (b->ncols + extra_cols) * sizeof(double);
+    const size_t need = size_t(b->ld) * (full_extent(b) + extra_cols) * sizeof(double);
     if (need > ctx->vbuf_bytes()) return capacity_error("generator matrix", need, ctx->vbuf_bytes());
     if (b->V != ctx->vbuf(0) && b->V != ctx->vbuf(1)) {
         double* dst = ctx->vbuf(0);
@@ -1121,6 +1132,10 @@ int ensure_full(nnvb_batch* b, nnvb_batch::Cohort& co) {
         return NNVB_E_STATE;
     }
     NNVB_TRY(make_writable(b, 0));
+    {
+        const size_t need = size_t(b->ld) * co.col1 * sizeof(double);
+        if (need > ctx->vbuf_bytes()) return capacity_error("columns of a cohort kept in compact form", need, ctx->vbuf_bytes());
+    }
     const bool clear = !lazy_fill(b);
     ProfScope ps(ctx, NNVB_PROF_RELAX, 16.0 * double(co.pack_stride) * double(co.col1 - co.col0));
     NNVB_TRY(launch_expand_compact(ctx->stream, int(b->shape[0]), int(b->shape[1]), int(b->shape[2]), b->wk->box.as<int4>(),
@@ -1423,7 +1438,8 @@ int relu_step_finish(nnvb_batch* b, ReluLayerRecord* rec, bool lazy_mask, bool l
     {
         // this layer's output and, with sharded generators, every layer up to the next ReLU step: the ranks hold
         // different column counts, so the go / no-go is agreed on before anybody enters the next collective
-        size_t need = size_t(ld) * (ncols_old + K_loc) * sizeof(double);
+        // (new columns that stay implicit until the next layer, and cohorts kept in compact form, take no columns)
+        size_t need = size_t(ld) * ((lazy_onehot && world == 1) ? full_extent(b) : ncols_old + K_loc) * sizeof(double);
         if (world > 1) need = std::max(need, segment_need(b, next_layer, ncols_old + K_loc, ld));
         bool stop = need > ctx->vbuf_bytes();
         const bool mine = stop;
@@ -1576,7 +1592,13 @@ int run_layers(nnvb_batch* b) {
         const int64_t ld_out = lead_dim(Nout);
         if (L.type == NNVB_LAYER_CONV2D || L.type == NNVB_LAYER_FC || L.type == NNVB_LAYER_AVGPOOL2D) {
             const size_t need = size_t(ld_out) * b->ncols * sizeof(double);
-            if (need > ctx->vbuf_bytes()) return capacity_error("layer output", need, ctx->vbuf_bytes());
+            if (ctx->world > 1 && need > ctx->vbuf_bytes()) return capacity_error("layer output", need, ctx->vbuf_bytes());
+            // full-length output columns [.., col1) must fit the buffer; cohorts that leave the layer in compact
+            // form do not touch theirs, so the test is made per launch
+            auto fits = [&](int64_t col1) -> int {
+                const size_t nd = size_t(ld_out) * col1 * sizeof(double);
+                return nd > ctx->vbuf_bytes() ? capacity_error("layer output", nd, ctx->vbuf_bytes()) : NNVB_OK;
+            };
             double* out = other_vbuf(b);
             const bool lazy = lazy_fill(b);
             // Compact storage: a layer reads the cohorts' compact copies from one of the two buffers and writes
@@ -1598,7 +1620,7 @@ int run_layers(nnvb_batch* b) {
             // test aid: fill the output buffer with NaN patterns first, so that a reader that strays outside
             // the windows it was given shows up in the results instead of depending on what the memory held
             static const bool poison = getenv("NNVB_POISON") != nullptr;
-            if (poison) NNVB_CUDA(cudaMemsetAsync(out, 0xFF, need, st));
+            if (poison) NNVB_CUDA(cudaMemsetAsync(out, 0xFF, std::min(need, ctx->vbuf_bytes()), st));
             // columns the layer contracts densely, and the unit-vector columns whose images it writes directly
             const int64_t n_dense = b->ncols - b->pend_onehot;
             const int64_t n_hot = b->pend_onehot;
@@ -1652,7 +1674,10 @@ int run_layers(nnvb_batch* b) {
                     const int ww = (co.ww - 1 + (L.cg.kw - 1) * L.cg.dw) / L.cg.sw + 1;
                     const bool windowed = !co.dense && wh * ww <= 128 && 2 * wh * ww <= L.cg.Ho * L.cg.Wo;
                     if (windowed) {
-                        if (!lazy) NNVB_CUDA(cudaMemsetAsync(out + co.col0 * ld_out, 0, sizeof(double) * ld_out * (c1 - co.col0), st));
+                        if (!lazy) {
+                            NNVB_TRY(fits(c1));
+                            NNVB_CUDA(cudaMemsetAsync(out + co.col0 * ld_out, 0, sizeof(double) * ld_out * (c1 - co.col0), st));
+                        }
                         ColWindows win{b->wk->box.as<int4>(), wh, ww};
                         // generator columns: the kernel that skips the taps falling outside the input window
                         // (its products: kh*kw per input position), else the patch-tiled kernel (per output position)
@@ -1661,6 +1686,7 @@ int run_layers(nnvb_batch* b) {
                         if (!no_conv_win && co.col0 >= b->nq) {
                             ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * co.wh * co.ww * double(c1 - co.col0));
                             double* pk = (pack_base && c1 == co.col1) ? pack_base + pack_next : nullptr;
+                            if (pk == nullptr || write_full) NNVB_TRY(fits(c1));
                             NNVB_TRY(launch_conv_win(st, L.cg, L.cw, bn, mask, win, co.wh, co.ww, co.col0, b->V, b->ld,
                                                      (pk != nullptr && !write_full) ? nullptr : out, ld_out, c1 - co.col0, pk,
                                                      &done, &ctx->launches, comp_in(co), co.pack_stride));
@@ -1681,6 +1707,7 @@ int run_layers(nnvb_batch* b) {
                         }
                         if (!done) {
                             NNVB_TRY(ensure_full(b, co));
+                            NNVB_TRY(fits(c1));
                             ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * wh * ww * double(c1 - co.col0));
                             NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, mask, win, co.col0, b->V, b->ld, out, ld_out,
                                                      c1 - co.col0, b->nq, &ctx->launches));
@@ -1688,6 +1715,7 @@ int run_layers(nnvb_batch* b) {
                         co.clean = !lazy;
                     } else {
                         NNVB_TRY(ensure_full(b, co));
+                        NNVB_TRY(fits(c1));
                         ProfScope ps(ctx, NNVB_PROF_CONV, per_pos * L.cg.Ho * L.cg.Wo * double(c1 - co.col0));
                         ColWindows win{b->wk->box.as<int4>(), 0, 0};     // whole images; the windows mask the reads
                         NNVB_TRY(launch_conv_f64(st, L.cg, L.cw, bn, mask, win, co.col0, b->V, b->ld, out, ld_out,
@@ -1702,6 +1730,7 @@ int run_layers(nnvb_batch* b) {
                 const bool pack_hot = pack_base != nullptr && n_hot > 0 && !b->cohorts.empty() &&
                                       b->cohorts.back().col0 == n_dense && b->cohorts.back().col1 == b->ncols &&
                                       !b->cohorts.back().dense;
+                if (n_hot > 0 && !(pack_hot && !write_full)) NNVB_TRY(fits(b->ncols));
                 NNVB_TRY(launch_conv_onehot(st, L.cg, L.cw, bn, hot, n_hot,
                                             (pack_hot && !write_full) ? nullptr : out + n_dense * ld_out, ld_out, !lazy,
                                             pack_hot ? pack_base + pack_next : nullptr, &ctx->launches));
@@ -1717,6 +1746,7 @@ int run_layers(nnvb_batch* b) {
                 // one launch per cohort: windowed cohorts contract only the weight rows of their windows
                 static const bool no_fcg = getenv("NNVB_NO_FC_GATHER") != nullptr;
                 const int In = int(L.H * L.W * L.C);
+                NNVB_TRY(fits(b->ncols));
                 // Cohorts that take the dense kernel and lie next to each other go in one launch: every launch
                 // streams the whole weight matrix, so a launch per small cohort would re-read it per cohort.
                 int64_t run0 = -1, run1 = -1;
@@ -1802,6 +1832,7 @@ int run_layers(nnvb_batch* b) {
                         co.clean = false;
                     } else if (windowed) {
                         NNVB_TRY(ensure_full(b, co));
+                        NNVB_TRY(fits(c1));
                         if (!lazy) NNVB_CUDA(cudaMemsetAsync(out + co.col0 * ld_out, 0, sizeof(double) * ld_out * (c1 - co.col0), st));
                         // bytes: the input windows read, the output windows (with a zero fill: columns) written
                         ProfScope ps(ctx, NNVB_PROF_AVGPOOL,
@@ -1813,6 +1844,7 @@ int run_layers(nnvb_batch* b) {
                         co.clean = !lazy;
                     } else {
                         NNVB_TRY(ensure_full(b, co));
+                        NNVB_TRY(fits(c1));
                         ProfScope ps(ctx, NNVB_PROF_AVGPOOL, 8.0 * double(b->N + Nout) * double(c1 - co.col0));
                         // the kernel numbers columns from 0: shift the mask to the cohort's first column
                         RowMask m2 = mask;
@@ -1840,6 +1872,7 @@ int run_layers(nnvb_batch* b) {
                     b->pend_scaled = true;
                 } else {
                     ProfScope ps(ctx, NNVB_PROF_ONEHOT, 8.0 * double(lazy ? L.pg.C : Nout) * double(n_hot));
+                    if (n_hot > 0) NNVB_TRY(fits(b->ncols));
                     NNVB_TRY(launch_avgpool_onehot(st, L.pg, hot, n_hot, out + n_dense * ld_out, ld_out, !lazy,
                                                    &ctx->launches));
                     for (auto& co : b->cohorts)
