@@ -47,7 +47,7 @@ UNIT = "queries/s"
 
 # name -> (queries of the configuration, queries per engine batch, description)
 WORKLOADS = {
-    "cnn32": (128, 16, "cnn32: 32x32x3 CNN, eps=2/255 on 3072 pixels, 128 images, approx-star (estimated bounds) "
+    "cnn32": (128, 64, "cnn32: 32x32x3 CNN, eps=2/255 on 3072 pixels, 128 images, approx-star (estimated bounds) "
                        "reach + halfspace verdict"),
     "cnn28": (256, 256, "cnn28: 28x28x1 CNN, eps=1/255 on 784 pixels, 256 images, reach + verdict"),
     "bright28": (16384, 4096, "bright28: 28x28x1 CNN, one brightening predicate per image, 16384 images, reach + verdict"),

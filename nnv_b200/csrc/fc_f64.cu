@@ -384,6 +384,7 @@ fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad
     const int key = tile_key[blockIdx.x];
     const int h0 = key % KH - (wh - 1), w0 = key / KH - (ww - 1);
     const bool null_bin = key == KH * (W + ww - 1);     // columns whose window lies off the image
+    const bool comp_pairs = comp != nullptr && comp_stride % 2 == 0 && (reinterpret_cast<uintptr_t>(comp) & 15) == 0;
     const int start = tile_start[blockIdx.x], count = tile_count[blockIdx.x];
     for (int m = tid; m < Cfg::BM; m += Cfg::THREADS) cols_s[m] = m < count ? perm[start + m] : -1;
     for (int k = tid; k < Kt_pad; k += Cfg::THREADS) {
@@ -412,14 +413,31 @@ fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad
         const int k0 = kt * FC_BK;
         double* a = As + stage * Cfg::A_STAGE;
         double* b = Bs + stage * Cfg::B_STAGE;
-        for (int c = tid; c < Cfg::BM * FC_BK; c += Cfg::THREADS) {
-            const int m = c / FC_BK, kk = c % FC_BK;
-            const int row = rows_s[k0 + kk], col = cols_s[m];
-            const bool ok = row >= 0 && col >= 0;
-            const double* src = comp != nullptr ? comp : Vin;
-            if (ok) src = comp != nullptr ? comp + (int64_t(col) - comp_col0) * comp_stride + (k0 + kk)
-                                          : Vin + int64_t(col) * ld_in + row;
-            cp_async8(a + m * FC_AST + kk, src, ok ? 8 : 0);
+        if (comp != nullptr && comp_pairs) {
+            // compact columns: a column's operand row is contiguous in the contraction order, 16 bytes a copy
+            for (int c = tid; c < Cfg::BM * (FC_BK / 2); c += Cfg::THREADS) {
+                const int m = c / (FC_BK / 2), kk = 2 * (c % (FC_BK / 2));
+                const int r0 = rows_s[k0 + kk], r1 = rows_s[k0 + kk + 1], col = cols_s[m];
+                double* d = a + m * FC_AST + kk;
+                const double* src = col >= 0 ? comp + (int64_t(col) - comp_col0) * comp_stride + (k0 + kk) : comp;
+                if (col >= 0 && r0 >= 0 && r1 >= 0) {
+                    cp_async16(d, src, 16);
+                } else {
+                    const bool ok0 = col >= 0 && r0 >= 0, ok1 = col >= 0 && r1 >= 0;
+                    cp_async8(d, ok0 ? src : comp, ok0 ? 8 : 0);
+                    cp_async8(d + 1, ok1 ? src + 1 : comp, ok1 ? 8 : 0);
+                }
+            }
+        } else {
+            for (int c = tid; c < Cfg::BM * FC_BK; c += Cfg::THREADS) {
+                const int m = c / FC_BK, kk = c % FC_BK;
+                const int row = rows_s[k0 + kk], col = cols_s[m];
+                const bool ok = row >= 0 && col >= 0;
+                const double* src = comp != nullptr ? comp : Vin;
+                if (ok) src = comp != nullptr ? comp + (int64_t(col) - comp_col0) * comp_stride + (k0 + kk)
+                                              : Vin + int64_t(col) * ld_in + row;
+                cp_async8(a + m * FC_AST + kk, src, ok ? 8 : 0);
+            }
         }
         for (int c = tid; c < FC_BK * (Cfg::BN / 2); c += Cfg::THREADS) {
             const int kr = c / (Cfg::BN / 2), nc = c % (Cfg::BN / 2);
