@@ -55,7 +55,7 @@ WORKLOADS = {
     "vgg224": (8, 1, "vgg224: VGG16-shaped 224x224x3 network, 64 perturbed entries (eps=2/255), reach + verdict"),
 }
 # what the default line carries beside cnn32, with the steps they get (their steps are short)
-EXTRAS = ("cnn28", "bright28", "fc5")
+EXTRAS = ("cnn28", "bright28", "fc5")          # plus vgg224, generator-sharded over the ranks
 
 
 def dense_flops_per_layer(layers, in_shape, cols):
@@ -252,6 +252,9 @@ def run_workload(env, name, K, W, profile=False, keep_first=False):
     nq, sub, desc = WORKLOADS[name]
     if env["args"].batch and name == (env["args"].workload or "cnn32"):
         sub = env["args"].batch
+    if env["args"].queries and name == (env["args"].workload or "cnn32"):
+        nq = min(nq, env["args"].queries)          # a shorter list (profiling runs): not the benchmark's workload
+        desc += " [first %d queries only]" % nq
     cfg = make_config(name, n_queries=nq)
     layers, shape = cfg["layers"], cfg["in_shape"]
     kind = cfg["queries"][0].get("spec", "max")
@@ -537,6 +540,8 @@ def run_sharded(env, name, K, W):
     for b, _ in batches:
         b.close()
     net.close()
+    if world > 1:
+        ctx.set_shard_nccl(0, 1)              # back to unsharded sets
     return out
 
 
@@ -615,6 +620,8 @@ def run_ours(args):
             k2 = max(2, min(K, 10))
             r2 = run_workload(env, name, k2, min(W, 3))
             extras[name] = r2["line"]
+        # the fifth configuration: one 224x224 set per step, its generators split over the N ranks
+        extras["vgg224"] = run_sharded(env, "vgg224", 3, 1)
     if rank == 0:
         if extras:
             line["extra"] = extras
@@ -626,6 +633,10 @@ def run_ours(args):
             if S is not None and "cross" in res["first"]:
                 line["parity_check"] = parity_check(res["first"], S)
             for name in extras:
+                if name == "vgg224":
+                    extras[name]["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": th["cores"], "kind": "port",
+                                                    "sample": cpu_reference(name)[1]}
+                    continue
                 v2, sample2, _ = cpu_reference(name, budget_s=20.0)
                 extras[name]["cpu_baseline"] = {"value": v2, "unit": UNIT, "cores": th["cores"], "kind": "port",
                                                 "sample": sample2}
@@ -671,6 +682,8 @@ def main():
     ap.add_argument("--shard", default="queries", choices=["queries", "generators"])
     ap.add_argument("--images", type=int, default=1, help="--shard generators: distinct images cycled through")
     ap.add_argument("--batch", type=int, default=0, help="input sets per engine batch (0: the workload's default)")
+    ap.add_argument("--queries", type=int, default=0,
+                    help="use only the first N queries of the headline workload (profiling captures)")
     ap.add_argument("--arena-gb", type=int, default=112)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")

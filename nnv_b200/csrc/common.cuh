@@ -63,6 +63,10 @@ struct ConvWeights {
     int cs;                 // padded channel stride in shared memory (doubles)
     int n_tiles;            // ceil(Cout / bn_tile)
     int n_chunks;           // ceil(Cin / KC)
+    // Filter footprints for unit-vector columns (unit stride and dilation only, else null): the image of the unit
+    // vector of input channel ci, window only and channel fastest, [Cin][kw][kh][Cout]:
+    // foot[((ci*kw + owl)*kh + ohl)*Cout + co] = W(kh-1-ohl, kw-1-owl, ci, co)
+    double* foot = nullptr;
 };
 
 // Optional per-channel affine fused behind a contraction (BatchNormalization

@@ -387,6 +387,30 @@ conv_onehot_kernel(ConvGeom g, const double* __restrict__ Wg, int bn_tile, int c
     }
 }
 
+// The same images for unit stride and dilation, compact form only: a column's window is the filter flipped in
+// both directions, read as one contiguous run from the footprint table (ConvWeights::foot) and scaled in the
+// order of conv_onehot_kernel.  Four columns per block, lanes along (position, channel).
+__global__ void __launch_bounds__(256)
+conv_onehot_foot_kernel(ConvGeom g, const double* __restrict__ foot, ChanAffine bn, HotCols hot, int64_t K_loc,
+                        double* __restrict__ pack) {
+    const int per_col = g.kh * g.kw * g.Cout;
+    const int64_t t = int64_t(blockIdx.x) * 4 + (threadIdx.x >> 6);
+    if (t >= K_loc) return;
+    const int i = hot.idx[hot.first + t * hot.step];
+    const bool scaled = hot.scale != nullptr;
+    const double sc = scaled ? hot.scale[t] : 1.0;
+    const int ci = i / (g.H * g.W);
+    const double* src = foot + int64_t(ci) * per_col;
+    double* pk = pack + t * int64_t(per_col);
+    for (int e = threadIdx.x & 63; e < per_col; e += 64) {
+        const int co = e % g.Cout;
+        double v = src[e];
+        if (scaled) v = v * sc;
+        if (bn.rden != nullptr) v = (v * bn.rden[co]) * bn.scale[co];
+        pk[e] = v;
+    }
+}
+
 int pad_stride(int n) {            // smallest s >= n with s = 4 (mod 8)
     int s = (n + 7) / 8 * 8 + 4;
     if (s - 8 >= n) s -= 8;
@@ -553,6 +577,12 @@ int launch_conv_onehot(cudaStream_t st, const ConvGeom& g, const ConvWeights& w,
         return NNVB_E_ARG;
     }
     if (zero_fill && Vout != nullptr) NNVB_CUDA(cudaMemsetAsync(Vout, 0, sizeof(double) * ld_out * K_loc, st));
+    if (Vout == nullptr && w.foot != nullptr && g.sh == 1 && g.sw == 1 && g.dh == 1 && g.dw == 1) {
+        conv_onehot_foot_kernel<<<(unsigned)ceil_div(K_loc, 4), 256, 0, st>>>(g, w.foot, bn, hot, K_loc, pack);
+        NNVB_CUDA(cudaGetLastError());
+        if (launches) *launches += 1;
+        return NNVB_OK;
+    }
     // the window of a column: (kh-1)*dh/sh + 1 rows, likewise columns, all output channels
     const size_t win_bytes = sizeof(double) * size_t((g.kh - 1) * g.dh / g.sh + 1) * ((g.kw - 1) * g.dw / g.sw + 1) * g.Cout;
     const bool staged = pack != nullptr && win_bytes <= 32768;

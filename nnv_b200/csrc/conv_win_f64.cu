@@ -146,10 +146,20 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
     // table: entry e = (column, origin column, input row), input row fastest (contiguous in memory)
     const int n_e = p.ncol * n_kw * n_i;
     for (int e = tid; e < n_e; e += CW_THREADS) {
-        const int i_idx = e % n_i;
-        const int e2 = e / n_i;
-        const int kwi = kw_lo + e2 % n_kw;
-        const int col = e2 / n_kw;
+        // full-length input: input row fastest (contiguous in memory); compact input: column fastest, so that
+        // neighbouring lanes of the fetch write neighbouring 64-byte slots of the staging row
+        int i_idx, kwi, col;
+        if (CIN) {
+            col = e % p.ncol;
+            const int e2 = e / p.ncol;
+            i_idx = e2 % n_i;
+            kwi = kw_lo + e2 / n_i;
+        } else {
+            i_idx = e % n_i;
+            const int e2 = e / n_i;
+            kwi = kw_lo + e2 % n_kw;
+            col = e2 / n_kw;
+        }
         const int4 bx = s_box[col];
         const int hi = bx.x + ih_base + i_lo + i_idx;
         const int wi = bx.y + owl + kwi - ext_w;
@@ -177,41 +187,35 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
     auto load_stage = [&](int stage, int chunk) {
         double* is = in_s + stage * p.in_stage;
         if (CIN) {
-            // one entry per thread and round: the chunk's eight channels of one (column, input position)
+            // one 16-byte channel pair of one (column, input position) per thread and round: four neighbouring
+            // lanes fetch the 64 bytes of an entry, eight neighbouring entries are eight neighbouring columns, so a
+            // warp's copies fill 512 contiguous bytes of the staging row (no bank conflicts)
             const int c0 = chunk * KC;
             const double* src_b = in_base + c0;
             const bool cf = mask.state_cf != nullptr;
-            const bool word_ok = cf && (p.g.Cin % 8 == 0) && (mask.N % 8 == 0);
-            for (int e = tid; e < n_e; e += CW_THREADS) {
+            const bool pair_ok = cf && (p.g.Cin % 2 == 0) && (mask.N % 2 == 0);
+            for (int it = tid; it < 4 * n_e; it += CW_THREADS) {
+                const int e = it >> 2, u0 = 2 * (it & 3);
                 const int off = goff[e], so_raw = soff[e], mo = moff[e];
                 const int so = so_raw & 0x3fffffff;
                 const int sw = (so_raw >> 30) & 1 ? 4 : 0;
-                unsigned long long sv = 0ull;          // byte u != 0: channel c0 + u reads as zero
-                if (off >= 0 && mo >= 0) {
-                    if (word_ok) {
-                        sv = *reinterpret_cast<const unsigned long long*>(mask.state_cf + mo + c0);
+                bool ok0 = off >= 0 && c0 + u0 < p.g.Cin, ok1 = off >= 0 && c0 + u0 + 1 < p.g.Cin;
+                if (mo >= 0 && (ok0 || ok1)) {                   // rows the ReLU step cleared read as zero
+                    if (pair_ok) {
+                        const unsigned sv = *reinterpret_cast<const unsigned short*>(mask.state_cf + mo + c0 + u0);
+                        ok0 = ok0 && (sv & 0xffu) == 0;
+                        ok1 = ok1 && (sv >> 8) == 0;
                     } else {
-#pragma unroll
-                        for (int u = 0; u < KC; ++u) {
-                            if (c0 + u >= p.g.Cin) break;
-                            const uint8_t sb = cf ? mask.state_cf[mo + c0 + u] : mask.state[mo + int64_t(c0 + u) * hw_in];
-                            sv |= (unsigned long long)(sb != 0 ? 1 : 0) << (8 * u);
-                        }
+                        if (ok0) ok0 = (cf ? mask.state_cf[mo + c0 + u0] : mask.state[mo + int64_t(c0 + u0) * hw_in]) == 0;
+                        if (ok1) ok1 = (cf ? mask.state_cf[mo + c0 + u0 + 1] : mask.state[mo + int64_t(c0 + u0 + 1) * hw_in]) == 0;
                     }
                 }
-                double* dst = is + so;
-#pragma unroll
-                for (int pr = 0; pr < KC / 2; ++pr) {
-                    const int u0 = 2 * pr;
-                    const bool ok0 = off >= 0 && c0 + u0 < p.g.Cin && ((sv >> (8 * u0)) & 0xffull) == 0;
-                    const bool ok1 = off >= 0 && c0 + u0 + 1 < p.g.Cin && ((sv >> (8 * u0 + 8)) & 0xffull) == 0;
-                    double* d2 = dst + (u0 ^ sw);
-                    if (ok0 && ok1) {
-                        cp_async16(d2, src_b + off + u0, 16);
-                    } else {
-                        cp_async8(d2, ok0 ? src_b + off + u0 : zero_src, ok0 ? 8 : 0);
-                        cp_async8(d2 + 1, ok1 ? src_b + off + u0 + 1 : zero_src, ok1 ? 8 : 0);
-                    }
+                double* d2 = is + so + (u0 ^ sw);
+                if (ok0 && ok1) {
+                    cp_async16(d2, src_b + off + u0, 16);
+                } else {
+                    cp_async8(d2, ok0 ? src_b + off + u0 : zero_src, ok0 ? 8 : 0);
+                    cp_async8(d2 + 1, ok1 ? src_b + off + u0 + 1 : zero_src, ok1 ? 8 : 0);
                 }
             }
         } else {

@@ -596,6 +596,18 @@ int nnvb_net_create(nnvb_ctx* ctx, const nnvb_layer_desc* layers, int n_layers, 
                 s = upload_vec(net.get(), bias, &L.cw.bias);
                 if (s) return fail(s);
                 L.cw.bn_tile = bn_tile; L.cw.cs = cs; L.cw.n_tiles = n_tiles; L.cw.n_chunks = n_chunks;
+                if (g.sh == 1 && g.sw == 1 && g.dh == 1 && g.dw == 1) {
+                    // footprints of unit vectors: the filter flipped in both directions, per input channel
+                    std::vector<double> foot(size_t(d.cin) * d.kw * d.kh * d.cout);
+                    for (int ci = 0; ci < d.cin; ++ci)
+                        for (int owl = 0; owl < d.kw; ++owl)
+                            for (int ohl = 0; ohl < d.kh; ++ohl)
+                                for (int co = 0; co < d.cout; ++co)
+                                    foot[((size_t(ci) * d.kw + owl) * d.kh + ohl) * d.cout + co] =
+                                        d.W[size_t(d.kh - 1 - ohl) + size_t(d.kh) * ((d.kw - 1 - owl) + size_t(d.kw) * (ci + size_t(d.cin) * co))];
+                    s = upload_vec(net.get(), foot, &L.cw.foot);
+                    if (s) return fail(s);
+                }
                 break;
             }
             case NNVB_LAYER_FC: {
