@@ -3,7 +3,7 @@
  * (nnv_b200/csrc/nnvb200_mex.cpp) on machines without MATLAB.  It declares only
  * the documented MEX/MX API functions the gateway calls, with the documented
  * signatures.  It is never linked: a real build uses MATLAB's own header via
- * `mex` (see INTEGRATION.md).
+ * `mex`.
  */
 #ifndef NNVB_MEX_STUB_H
 #define NNVB_MEX_STUB_H

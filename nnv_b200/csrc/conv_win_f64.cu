@@ -14,7 +14,7 @@
 // An input row fragment is loaded once and used by the (up to kh) taps that pair it with different
 // output rows.
 //
-// Conv2DLayer.reach_star_single_input (Conv2DLayer.m:1110-1137) applies the layer to the centre
+// Conv2DLayer.reach_star_single_input (Conv2DLayer.m:559-601) applies the layer to the centre
 // with bias and to every generator without; this kernel is used for generator columns only.
 #include <algorithm>
 

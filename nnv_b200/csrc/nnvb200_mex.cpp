@@ -241,6 +241,34 @@ void stats(int nlhs, mxArray* plhs[], int nrhs, const mxArray* prhs[], Err& e) {
     if (nlhs > 0) plhs[0] = out;
 }
 
+// Y = nnvb200_mex('evaluate', h, X): NN.evaluate (NN.m:130-145) on the columns of X [H*W*C x n] in one pass
+void evaluate(int nlhs, mxArray* plhs[], int nrhs, const mxArray* prhs[], Err& e) {
+    if (nrhs < 3 || !mxIsDouble(prhs[2]) || mxIsComplex(prhs[2])) { e.fail("NNVB200:args", "usage: evaluate(h, X) with a real double X"); return; }
+    NetHandle* h = get_handle(prhs[1], e);
+    if (!h) return;
+    const size_t n = mxGetN(prhs[2]);
+    const size_t n_out = (size_t)(h->shape[0] * h->shape[1] * h->shape[2]);
+    mxArray* Y = mxCreateDoubleMatrix((mwSize)n_out, (mwSize)n, mxREAL);
+    e.check(nnvb_net_evaluate(h->net, (int64_t)n, mxGetDoubles(prhs[2]), mxGetDoubles(Y)), "nnvb_net_evaluate");
+    if (!e.set && nlhs > 0) plhs[0] = Y;
+}
+
+// id = nnvb200_mex('nccl_id') on worker 1; nnvb200_mex('set_shard', rank, world, id [, peer_memory]) on every worker
+// (rank 1-based like spmdIndex): one set split along its generators over the workers' GPUs
+void nccl_id(int nlhs, mxArray* plhs[], Err& e) {
+    mxArray* id = mxCreateNumericMatrix(1, NNVB_NCCL_ID_BYTES / 8, mxUINT64_CLASS, mxREAL);
+    e.check(nnvb_nccl_unique_id(mxGetData(id)), "nnvb_nccl_unique_id");
+    if (!e.set && nlhs > 0) plhs[0] = id;
+}
+
+void set_shard(int nrhs, const mxArray* prhs[], Err& e) {
+    if (nrhs < 4 || mxGetNumberOfElements(prhs[3]) * 8 != NNVB_NCCL_ID_BYTES) { e.fail("NNVB200:args", "usage: set_shard(rank, world, id)"); return; }
+    if (!g_ctx) { e.fail("NNVB200:state", "create a network first: the context is made with it"); return; }
+    const int rank = (int)mxGetScalar(prhs[1]) - 1, world = (int)mxGetScalar(prhs[2]);
+    const int peer = nrhs > 4 ? (mxGetScalar(prhs[4]) != 0.0) : 1;
+    e.check(nnvb_set_shard_nccl(g_ctx, rank, world, mxGetData(prhs[3]), peer), "nnvb_set_shard_nccl");
+}
+
 }  // namespace
 
 extern "C" void mexFunction(int nlhs, mxArray* plhs[], int nrhs, const mxArray* prhs[]) {
@@ -255,6 +283,9 @@ extern "C" void mexFunction(int nlhs, mxArray* plhs[], int nrhs, const mxArray* 
         else if (cmd == "reach") reach_or_verify(false, nlhs, plhs, nrhs, prhs, e);
         else if (cmd == "verify") reach_or_verify(true, nlhs, plhs, nrhs, prhs, e);
         else if (cmd == "stats") stats(nlhs, plhs, nrhs, prhs, e);
+        else if (cmd == "evaluate") evaluate(nlhs, plhs, nrhs, prhs, e);
+        else if (cmd == "nccl_id") nccl_id(nlhs, plhs, e);
+        else if (cmd == "set_shard") set_shard(nrhs, prhs, e);
         else if (cmd == "destroy") {
             NetHandle* h = nrhs > 1 ? get_handle(prhs[1], e) : nullptr;
             if (h) {
