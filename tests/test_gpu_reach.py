@@ -513,3 +513,30 @@ def test_compact_storage_chain(ctx, pool_pad):
     assert _rel(b.get_V(0), S.V) < TOL
     b.close()
     net.close()
+
+
+def test_halfspace_row_with_zero_margin_is_left_to_the_lp(ctx):
+    """A row whose minimum over the set is exactly zero touches the halfspace: the intersection is not empty
+    (Star.isEmptySet finds the point), so the device must not call it empty because of a rounding error of either
+    sign — it leaves the row undecided; rows that are clearly apart are decided."""
+    from nnv_b200 import _lib as L
+    W = np.array([[1.0, 0.0], [0.0, 1.0], [1.0, 1.0]])
+    layers = [{"type": "fc", "W": W, "b": np.zeros(3)}]
+    net = Network(ctx, layers, (2, 1, 1))
+    b = Batch(net, [{"lb": np.array([-1.0, -1.0]).reshape(2, 1, 1), "ub": np.array([1.0, 1.0]).reshape(2, 1, 1)}])
+    b.upload()
+    b.reach(keep_constraints=True, keep_layer_bounds=True)
+    G = np.array([[-1.0, 0.0, 0.0],        # -x1 <= -1: touches the set at x1 = 1, minimum of G x - g is exactly 0
+                  [-1.0, 0.0, 0.0],        # -x1 <= -1.5: empty, minimum 0.5
+                  [0.0, 0.0, 1.0]])        # x1 + x2 <= 0: half of the set
+    g = np.array([-1.0, -1.5, 0.0])
+    margin, status = b.halfspace_margins(0, G, g)
+    assert margin[0] == 0.0 and status[0] == L.UNDECIDED
+    assert margin[1] == 0.5 and status[1] == L.VERDICT_EMPTY
+    assert status[2] == L.VERDICT_NONEMPTY
+    S = O.reach(layers, O.star_from_bounds(np.array([-1.0, -1.0]), np.array([1.0, 1.0])))
+    for i, want in enumerate([False, True, False]):
+        C, d = O.intersect_halfspace_system(S, G[i:i + 1], g[i:i + 1])
+        assert O.is_empty_set(C, d, S.pl, S.pu) == want
+    b.close()
+    net.close()
