@@ -310,6 +310,29 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
         cp_async_commit();
     }
     cp_async_wait<0>();
+    if (Vout == nullptr && p.pack != nullptr) {
+        // Compact output only: straight from the accumulators.  A lane holds two neighbouring channels of a
+        // (column, patch row), so its store is 16 bytes; the four lanes of a quad fill the 64 bytes of an
+        // 8-channel group, whole sectors of the channel-fastest output without a pass through shared memory.
+        const int nn = wn * 8 + 2 * t;
+        if (n0 + nn < p.g.Cout) {
+            const double r0 = chan[nn], s0 = chan[BN + nn], r1 = chan[nn + 1], s1 = chan[BN + nn + 1];
+            const int64_t ca = j0 + wm * 16 + g, cb = ca + 8;
+            double* da = p.pack + ca * p.pack_stride + int64_t(owl * p.wh_out + ohb * CW_TH) * p.g.Cout + n0 + nn;
+            double* db = da + 8 * p.pack_stride;
+#pragma unroll
+            for (int o = 0; o < CW_TH; ++o) {
+                if (o >= th_cnt) break;
+                if (ca < ncols)
+                    *reinterpret_cast<double2*>(da + int64_t(o) * p.g.Cout) =
+                        make_double2((acc[o][0] * r0) * s0, (acc[o][1] * r1) * s1);
+                if (cb < ncols)
+                    *reinterpret_cast<double2*>(db + int64_t(o) * p.g.Cout) =
+                        make_double2((acc[o][2] * r0) * s0, (acc[o][3] * r1) * s1);
+            }
+        }
+        return;
+    }
     __syncthreads();        // every warp is done with the stages: they become the output staging area
 
     // epilogue 1: accumulators -> staging [column][patch row][channel]; 16-byte stores
