@@ -119,7 +119,12 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
         chan[BN + c] = ok ? bn.scale[co] : 1.0;
     }
     __shared__ unsigned row_used[WARPS_M];
+    __shared__ __align__(8) uint64_t w_bar[CW_STAGES];      // one barrier per weight stage (bulk copies land on it)
     if (tid < WARPS_M) row_used[tid] = 0u;
+    if (tid == 0) {
+        for (int s = 0; s < CW_STAGES; ++s) mbar_init(&w_bar[s], 1);
+        mbar_init_fence();
+    }
     __syncthreads();
 
     // Patches near the image border hang over it.  Columns that lie next to each other in memory come from
@@ -245,9 +250,14 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
                 }
             }
         }
-        double* ws = wts + stage * p.w_stage;
-        const double* wsrc = w_base + int64_t(chunk) * p.w_stage;
-        for (int c = tid; c < p.w_stage / 2; c += CW_THREADS) cp_async16(ws + 2 * c, wsrc + 2 * c, 16);
+        // the chunk's weights are one contiguous block in memory and in the stage: a single bulk copy issued by
+        // one thread moves it, and its bytes are counted on the stage's barrier
+        if (tid == 0) {
+            async_proxy_fence();
+            mbar_expect_bytes(&w_bar[stage], uint32_t(p.w_stage) * 8u);
+            bulk_copy_g2s(wts + stage * p.w_stage, w_base + int64_t(chunk) * p.w_stage, uint32_t(p.w_stage) * 8u,
+                          &w_bar[stage]);
+        }
     };
 
     double acc[CW_TH][4];
@@ -303,6 +313,7 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
     const bool load_first = (warp >> 3) == 0;
     for (int ch = 0; ch < NCH; ++ch) {
         cp_async_wait<0>();
+        mbar_wait(&w_bar[ch & 1], (ch >> 1) & 1);       // stage ch % 2 is on its (ch / 2)-th use
         __syncthreads();
         if (load_first && ch + 1 < NCH) load_stage((ch + 1) & 1, ch + 1);
         compute(ch);

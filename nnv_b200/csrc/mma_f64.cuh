@@ -48,4 +48,41 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
 }
 
+
+// Bulk asynchronous copy (the copy engine behind TMA) of one contiguous block global -> shared, completion counted
+// in bytes on an mbarrier.  Both addresses 16-byte aligned, bytes a multiple of 16 and below 2^20.
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+// makes freshly initialised barriers visible to the copy engine
+__device__ __forceinline__ void mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+}
+// orders this thread's earlier shared-memory accesses before copies the copy engine makes afterwards
+__device__ __forceinline__ void async_proxy_fence() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_bytes(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy_g2s(void* smem, const void* gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                     smem_u32(smem)),
+                 "l"(gmem), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+// Waits for the phase of the given parity to complete.  The wait is bounded: after max_polls unsuccessful polls it
+// gives up and returns false, so a copy that never lands cannot hang the kernel.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int max_polls = 1 << 22) {
+    const uint32_t addr = smem_u32(bar);
+    for (int i = 0; i < max_polls; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
 }  // namespace nnvb
