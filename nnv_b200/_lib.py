@@ -31,7 +31,7 @@ VERDICT_EMPTY = 1
 VERDICT_NONEMPTY = 2
 UNDECIDED = -1
 
-c_double_p = C.POINTER(C.c_double)
+c_double_p = C.c_void_p          # double*: callers pass array addresses
 c_int_p = C.POINTER(C.c_int)
 c_int32_p = C.POINTER(C.c_int32)
 c_int64_p = C.POINTER(C.c_int64)

@@ -20,6 +20,7 @@
 
 #include "common.cuh"
 #include "mma_f64.cuh"
+#include <type_traits>
 
 namespace nnvb {
 namespace {
@@ -56,7 +57,9 @@ struct ConvWinParams {
 // in 64 contiguous bytes: one thread fetches it with four 16-byte copies into a staging row [column][8 channels]
 // (channel index XOR 4 for every other column pair, which keeps the fragment loads free of bank conflicts without
 // padding), and reads the eight row states of the chunk as one 8-byte word when they come in channel-fastest order.
-template <int KH, int WARPS_M, int WARPS_N, bool CIN>
+// NROWS > 0: the input windows are NROWS rows high and one block covers all patch rows, so the rows a block meets
+// are known at compile time and the unrolled product loop carries no range tests (0: any height, tested at run time).
+template <int KH, int WARPS_M, int WARPS_N, bool CIN, int NROWS>
 __global__ void __launch_bounds__(CW_THREADS, 1)
 conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const ChanAffine bn, const RowMask mask,
                 const int4* __restrict__ box, int64_t col_base, const double* __restrict__ Vin, int64_t ld_in,
@@ -97,8 +100,8 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
 
     // input rows i (relative to ih_base) that lie in the window, and the output rows of this block
     const int ih_base = ohb * CW_TH - ext_h;
-    const int i_lo = max(0, -ih_base);
-    const int i_hi = min(NI, p.wh_in - ih_base);
+    const int i_lo = NROWS > 0 ? KH - 1 : max(0, -ih_base);
+    const int i_hi = NROWS > 0 ? KH - 1 + NROWS : min(NI, p.wh_in - ih_base);
     const int n_i = i_hi - i_lo;
     const int th_cnt = min(CW_TH, p.wh_out - ohb * CW_TH);
     // origin columns kwi whose input column owl + kwi - ext_w lies in the window
@@ -266,7 +269,10 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
 #pragma unroll
         for (int r = 0; r < 4; ++r) acc[o][r] = 0.0;
 
-    auto compute = [&](int ch) {
+    // FULL: every patch row of the block is on the image for this warp's columns (the common case): the products
+    // carry no per-row test, which would otherwise put a branch around every DMMA
+    auto compute = [&](int ch, auto full_rows) {
+        constexpr bool FULL = decltype(full_rows)::value;
         // row = column g (and g + 8), k = channel t (and t + 4)
         const int sw = CIN ? ((g >> 1) & 1) * 4 : 0;
         const double* is = CIN ? in_s + (ch & 1) * p.in_stage + (wm * 16 + g) * KC
@@ -298,7 +304,7 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
                 for (int khi = 0; khi < KH; ++khi) {
                     const int o = i - khi;
                     if (o >= 0 && o < CW_TH) {
-                        if ((rows_on >> o) & 1u) dmma_16x8x8(acc[o], af, bf[khi]);
+                        if (FULL || ((rows_on >> o) & 1u)) dmma_16x8x8(acc[o], af, bf[khi]);
                     }
                 }
             }
@@ -306,6 +312,8 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
     };
 
     const int NCH = p.n_chunks;
+    const unsigned row_bits = (1u << th_cnt) - 1u;
+    const bool all_rows = (rows_on & row_bits) == row_bits;
     load_stage(0, 0);
     cp_async_commit();
     // Half of the warps fetch the next stage before their products, the other half after: while one half
@@ -316,7 +324,8 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
         mbar_wait(&w_bar[ch & 1], (ch >> 1) & 1);       // stage ch % 2 is on its (ch / 2)-th use
         __syncthreads();
         if (load_first && ch + 1 < NCH) load_stage((ch + 1) & 1, ch + 1);
-        compute(ch);
+        if (all_rows) compute(ch, std::true_type{});
+        else compute(ch, std::false_type{});
         if (!load_first && ch + 1 < NCH) load_stage((ch + 1) & 1, ch + 1);
         cp_async_commit();
     }
@@ -399,7 +408,7 @@ conv_win_kernel(const ConvWinParams p, const double* __restrict__ Wg, const Chan
     }
 }
 
-template <int KH, int WARPS_M, int WARPS_N, bool CIN>
+template <int KH, int WARPS_M, int WARPS_N, bool CIN, int NROWS = 0>
 int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn, const RowMask& mask,
                const ColWindows& win, int wh_in, int ww_in, int64_t col_base, const double* Vin, int64_t ld_in,
                double* Vout, int64_t ld_out, int64_t ncols, double* pack, const double* cin, int64_t cin_stride,
@@ -441,7 +450,8 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
     if (int64_t(p.ncol) * std::max(ld_in, ld_out) >= (int64_t(1) << 31)) return NNVB_OK;
     const int64_t blocks = ceil_div(ncols, p.ncol) * p.ww_out * p.n_ohb;
     if (blocks >= (int64_t(1) << 31)) return NNVB_OK;
-    auto kern = conv_win_kernel<KH, WARPS_M, WARPS_N, CIN>;
+    if (NROWS > 0 && (p.n_ohb != 1 || wh_in != NROWS)) return NNVB_OK;
+    auto kern = conv_win_kernel<KH, WARPS_M, WARPS_N, CIN, NROWS>;
     NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((unsigned)blocks, (unsigned)w.n_tiles);
     kern<<<grid, CW_THREADS, smem, st>>>(p, w.w, bn, mask, win.box, col_base, Vin, ld_in, Vout, ld_out, ncols);
@@ -463,14 +473,32 @@ int launch_conv_win(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, co
     if (g.sh != 1 || g.sw != 1 || g.dh != 1 || g.dw != 1 || g.kh != 3 || g.kw > 7 || win.box == nullptr) return NNVB_OK;
     if (win.wh != wh_in + g.kh - 1 || win.ww != ww_in + g.kw - 1) return NNVB_OK;
     int rc = NNVB_OK;
-    if (w.bn_tile == 64 && cin != nullptr)
-        rc = launch_cfg<3, 2, 8, true>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, pack, cin, cin_stride, done);
-    else if (w.bn_tile == 64)
-        rc = launch_cfg<3, 2, 8, false>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, pack, cin, cin_stride, done);
-    else if (w.bn_tile == 32 && cin != nullptr)
-        rc = launch_cfg<3, 4, 4, true>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, pack, cin, cin_stride, done);
-    else if (w.bn_tile == 32)
-        rc = launch_cfg<3, 4, 4, false>(st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, pack, cin, cin_stride, done);
+#define NNVB_CW_ARGS st, g, w, bn, mask, win, wh_in, ww_in, col_base, Vin, ld_in, Vout, ld_out, ncols, pack, cin, cin_stride, done
+    // window heights 3 to 6 with one row block (the windows of the first layers behind an input or a ReLU layer)
+    // have their own instances of the compact-input kernel
+    const int rows = (cin != nullptr && wh_in >= 3 && wh_in <= 6 && win.wh <= CW_TH) ? wh_in : 0;
+    if (w.bn_tile == 64 && cin != nullptr) {
+        switch (rows) {
+            case 3: rc = launch_cfg<3, 2, 8, true, 3>(NNVB_CW_ARGS); break;
+            case 4: rc = launch_cfg<3, 2, 8, true, 4>(NNVB_CW_ARGS); break;
+            case 5: rc = launch_cfg<3, 2, 8, true, 5>(NNVB_CW_ARGS); break;
+            case 6: rc = launch_cfg<3, 2, 8, true, 6>(NNVB_CW_ARGS); break;
+            default: rc = launch_cfg<3, 2, 8, true>(NNVB_CW_ARGS);
+        }
+    } else if (w.bn_tile == 64) {
+        rc = launch_cfg<3, 2, 8, false>(NNVB_CW_ARGS);
+    } else if (w.bn_tile == 32 && cin != nullptr) {
+        switch (rows) {
+            case 3: rc = launch_cfg<3, 4, 4, true, 3>(NNVB_CW_ARGS); break;
+            case 4: rc = launch_cfg<3, 4, 4, true, 4>(NNVB_CW_ARGS); break;
+            case 5: rc = launch_cfg<3, 4, 4, true, 5>(NNVB_CW_ARGS); break;
+            case 6: rc = launch_cfg<3, 4, 4, true, 6>(NNVB_CW_ARGS); break;
+            default: rc = launch_cfg<3, 4, 4, true>(NNVB_CW_ARGS);
+        }
+    } else if (w.bn_tile == 32) {
+        rc = launch_cfg<3, 4, 4, false>(NNVB_CW_ARGS);
+    }
+#undef NNVB_CW_ARGS
     if (rc == NNVB_OK && *done && launches) *launches += 1;
     return rc;
 }

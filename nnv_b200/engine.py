@@ -14,10 +14,16 @@ from . import _lib as L
 
 
 def _dp(a):
-    return a.ctypes.data_as(L.c_double_p) if a is not None else None
+    # the address as an integer: the double* parameters are declared void* on the Python side, which accepts it
+    # without building a typed pointer object per call (this sits on the per-set path of large batches)
+    return a.__array_interface__["data"][0] if a is not None else None
 
 
 def _f64(a, order="F"):
+    if type(a) is np.ndarray and a.dtype == np.float64:
+        f = a.flags
+        if f.aligned and (f.f_contiguous if order == "F" else f.c_contiguous):
+            return a
     return np.require(np.asarray(a, dtype=np.float64), requirements=["F" if order == "F" else "C", "A"])
 
 
@@ -177,6 +183,7 @@ class Network:
         self.lib = ctx.lib
         self.layers = list(layers)
         self.in_shape = tuple(int(x) for x in in_shape)
+        self.n_in = int(np.prod(self.in_shape))
         keep = []
         descs = (L.LayerDesc * max(len(layers), 1))()
         for i, layer in enumerate(layers):
@@ -241,14 +248,14 @@ class Batch:
     def set_bounds(self, q, lb, ub):
         lb = _f64(lb).ravel(order="F")
         ub = _f64(ub).ravel(order="F")
-        n = int(np.prod(self.net.in_shape))
+        n = self.net.n_in
         if lb.size != n or ub.size != n:
             raise ValueError("Inconsistency between lower bound image and upper bound image")
         L.check(self.lib.nnvb_batch_set_bounds(self.handle, q, _dp(lb), _dp(ub)), "nnvb_batch_set_bounds")
 
     def set_star(self, q, V, pl, pu, Cm=None, d=None):
         V = _f64(V)
-        n = int(np.prod(self.net.in_shape))
+        n = self.net.n_in
         M = V.reshape(n, -1, order="F")
         P = M.shape[1] - 1
         pl = _f64(pl).ravel()
