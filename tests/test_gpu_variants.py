@@ -3,7 +3,8 @@ output sets of a reach must not depend on them beyond the rounding of a differen
 windows vs dense columns, window-only writes vs zero-filled columns, the tap-skipping convolution vs the
 patch-tiled one, the window-sorted bound reduction vs the chunked dense one, masked rows and implicit
 unit-vector columns vs their eager forms, the gathered FC vs the dense one, unit-vector columns carried
-through a pooling layer vs written by it, the bound reduction on window-only copies vs on the columns.  NNVB_POISON fills every layer's
+through a pooling layer vs written by it, the bound reduction on window-only copies vs on the columns, the persistent
+form of the windowed convolution vs one block per tile.  NNVB_POISON fills every layer's
 output buffer with NaN patterns before the layer writes its windows: any read outside a window would
 surface as NaN in the sets."""
 import os
@@ -16,7 +17,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SWITCHES = ["NNVB_NO_WINDOWS", "NNVB_ZERO_FILL", "NNVB_NO_CONV_WIN", "NNVB_NO_RANGE_SKIP", "NNVB_EAGER_RELU",
-            "NNVB_EAGER_MASK", "NNVB_NO_FC_GATHER", "NNVB_NO_HOT_POOL", "NNVB_NO_PACK", "NNVB_NO_COMPACT", "NNVB_POOL_ONE_ROW", "NNVB_POISON"]
+            "NNVB_EAGER_MASK", "NNVB_NO_FC_GATHER", "NNVB_NO_HOT_POOL", "NNVB_NO_PACK", "NNVB_NO_COMPACT", "NNVB_NO_PERSIST", "NNVB_POOL_ONE_ROW", "NNVB_POISON"]
 
 
 def _run(tmp_path, switch):
