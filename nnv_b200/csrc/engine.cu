@@ -625,7 +625,9 @@ int nnvb_net_create(nnvb_ctx* ctx, const nnvb_layer_desc* layers, int n_layers, 
                 const int Out = d.cout;
                 const int ldw = (int)round_up(Out, 8);
                 const int64_t In_pad = round_up(In, 16);
-                std::vector<double> wt(size_t(In_pad) * ldw, 0.0);
+                // one more row than the padded input size: a row of zeros for the gathered FC, whose bulk copies
+                // cannot zero-fill the weight rows of positions off the image
+                std::vector<double> wt(size_t(In_pad + 1) * ldw, 0.0);
                 for (int64_t k = 0; k < In; ++k)
                     for (int o = 0; o < Out; ++o) wt[size_t(k) * ldw + o] = d.W[size_t(o) + size_t(Out) * k];
                 int s = upload_vec(net.get(), wt, &L.fc_wt);

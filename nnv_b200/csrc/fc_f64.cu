@@ -364,7 +364,8 @@ fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad
                  double* __restrict__ Vout, int64_t ld_out, const int32_t* __restrict__ tile_key,
                  const int32_t* __restrict__ tile_start, const int32_t* __restrict__ tile_count,
                  const int32_t* __restrict__ n_tiles, const int32_t* __restrict__ perm,
-                 const double* __restrict__ comp, int64_t comp_stride, int64_t comp_col0) {
+                 const double* __restrict__ comp, int64_t comp_stride, int64_t comp_col0, int zero_row) {
+    // zero_row: a row of Wt that holds zeros (stands in for the weight rows of positions off the image).
     // comp (nullable): the columns in compact form (window only, channel fastest; column j at
     // comp + (j - comp_col0)*comp_stride).  The contraction index then runs in that storage order,
     // k = (wl*wh + hl)*C + c, so that a column's operand row is one contiguous run.
@@ -375,6 +376,7 @@ fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad
     double* Bs = smem + FCG_STAGES * Cfg::A_STAGE;
     int* rows_s = reinterpret_cast<int*>(Bs + FCG_STAGES * Cfg::B_STAGE);   // [Kt_pad] input row of k, -1 = none
     int* cols_s = rows_s + Kt_pad;                                          // [BM] column of tile row m, -1 = none
+    __shared__ __align__(8) uint64_t b_bar[FCG_STAGES];                     // the weight rows of a stage land on these
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int wm = warp % FCG_WARPS_M, wn = warp / FCG_WARPS_M;
@@ -386,6 +388,12 @@ fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad
     const bool null_bin = key == KH * (W + ww - 1);     // columns whose window lies off the image
     const bool comp_pairs = comp != nullptr && comp_stride % 2 == 0 && (reinterpret_cast<uintptr_t>(comp) & 15) == 0;
     const int start = tile_start[blockIdx.x], count = tile_count[blockIdx.x];
+    if (tid == 0) {
+        for (int s = 0; s < FCG_STAGES; ++s) mbar_init(&b_bar[s], 1);
+        mbar_init_fence();
+    }
+    // a weight row of the tile is one contiguous run of Wt: one bulk copy each (16-byte multiples: ldw is even)
+    const uint32_t row_bytes = uint32_t(min(Cfg::BN, ldw - n0)) * 8u;
     for (int m = tid; m < Cfg::BM; m += Cfg::THREADS) cols_s[m] = m < count ? perm[start + m] : -1;
     for (int k = tid; k < Kt_pad; k += Cfg::THREADS) {
         int row = -1;
@@ -439,12 +447,20 @@ fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad
                 cp_async8(a + m * FC_AST + kk, src, ok ? 8 : 0);
             }
         }
-        for (int c = tid; c < FC_BK * (Cfg::BN / 2); c += Cfg::THREADS) {
-            const int kr = c / (Cfg::BN / 2), nc = c % (Cfg::BN / 2);
-            const int n = n0 + 2 * nc;
-            const int row = rows_s[k0 + kr];
-            const bool ok = row >= 0 && n < ldw;
-            cp_async16(b + kr * Cfg::BST + 2 * nc, ok ? Wt + int64_t(row) * ldw + n : Wt, ok ? 16 : 0);
+        // B: the FC_BK weight rows of the chunk, one bulk copy per row issued by the lanes of warp 0; their bytes are
+        // counted on the stage's barrier.  Positions off the image take the zero row.  Outputs past ldw are not
+        // copied: they feed accumulator columns that are never stored.
+        if (warp == 0) {
+            if (lane == 0) {
+                async_proxy_fence();
+                mbar_expect_bytes(&b_bar[stage], row_bytes * FC_BK);
+            }
+            __syncwarp();
+            if (lane < FC_BK) {
+                const int row = rows_s[k0 + lane];
+                bulk_copy_g2s(b + lane * Cfg::BST, Wt + int64_t(row >= 0 ? row : zero_row) * ldw + n0, row_bytes,
+                              &b_bar[stage]);
+            }
         }
     };
 
@@ -464,6 +480,7 @@ fc_gather_kernel(int H, int W, int C, int wh, int ww, int KH, int Kt, int Kt_pad
     }
     for (int kt = 0; kt < KT; ++kt) {
         cp_async_wait<FCG_STAGES - 2>();
+        mbar_wait(&b_bar[kt % FCG_STAGES], (kt / FCG_STAGES) & 1);      // stage kt % S is on its (kt / S)-th use
         __syncthreads();
         {
             const int nk = kt + FCG_STAGES - 1;
@@ -562,7 +579,7 @@ int launch_fc_gather(cudaStream_t st, int H, int W, int C, int wh, int ww, int O
     dim3 grid((unsigned)max_tiles, (unsigned)ceil_div(Out, Cfg::BN));
     fc_gather_kernel<<<grid, Cfg::THREADS, smem, st>>>(H, W, C, wh, ww, KH, Kt, Kt_pad, Out, Wt, ldw, Vin, ld_in, Vout,
                                                       ld_out, tile_key, tile_start, tile_count, n_tiles, perm, comp,
-                                                      comp_stride, col0);
+                                                      comp_stride, col0, (int)round_up(int64_t(H) * W * C, 16));
     NNVB_CUDA(cudaGetLastError());
     if (launches) *launches += 4;
     return NNVB_OK;
