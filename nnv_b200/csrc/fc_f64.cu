@@ -353,7 +353,7 @@ __global__ void fcg_scatter_kernel(int64_t col0, int64_t n, const int4* __restri
 
 // Tiles of 32 columns x 256 outputs: columns sharing a window origin come in small groups (tens), so a
 // short M tile keeps the tiles full; the weight rows of a tile are then re-read from L2 once per 32 columns.
-constexpr int FCG_WM = 1, FCG_WN = 8, FCG_WARPS_M = 2, FCG_WARPS_N = 4;
+constexpr int FCG_WM = 2, FCG_WN = 4, FCG_WARPS_M = 1, FCG_WARPS_N = 8;
 constexpr int FCG_BM = FCG_WARPS_M * FCG_WM * 16;
 constexpr size_t FCG_SMEM = size_t(FCG_STAGES) * (FcCfg<FCG_WM, FCG_WN, FCG_WARPS_M, FCG_WARPS_N>::A_STAGE +
                                                   FcCfg<FCG_WM, FCG_WN, FCG_WARPS_M, FCG_WARPS_N>::B_STAGE) * sizeof(double);
