@@ -115,6 +115,7 @@ void conv_arrange_weights(const ConvGeom& g, const double* W, double* dst, int b
 // ((w - w0)*wh + (h - h0))*Cout + c.  cin (nullable): the launch's input columns in the same compact form
 // (column j at cin + j*cin_stride, window wh_in x ww_in), read instead of Vin.  Vout may be null when pack is
 // given: the output then exists in compact form only.
+int conv_win_wait_timeouts(cudaStream_t st, int* out);
 int launch_conv_win(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn, const RowMask& mask,
                     const ColWindows& win, int wh_in, int ww_in, int64_t col_base, const double* Vin, int64_t ld_in,
                     double* Vout, int64_t ld_out, int64_t ncols, double* pack, bool* done, int64_t* launches,

@@ -792,6 +792,360 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
 }
 
 
+// Warp-specialised form of the persistent kernel.  Sixteen consumer warps (four warpgroups) only multiply: they wait
+// for a stage to be full, run its products, and hand the stage back.  One producer warpgroup (four warps) does
+// everything else: window boxes, flags and fetch table of the next tile, the input copies and the weight copy of
+// every stage.  Stages are handed over through mbarriers (full: the producer's copies have landed; empty: all
+// consumer warps are done with the stage), so there is no block-wide barrier in the main loop and a consumer warp
+// never waits for another consumer warp.  The producers give most of their registers to the consumers.
+// Every wait is bounded; a wait that runs out sets *err and lets the kernel finish.
+constexpr int WS_CONSUMER_WARPS = 16;
+constexpr int WS_PRODUCERS = 128;                                   // threads of the producer warpgroup
+constexpr int WS_THREADS = WS_CONSUMER_WARPS * 32 + WS_PRODUCERS;   // 640
+constexpr int WS_BAR_PRODUCERS = 1;                                 // named barrier of the producer warps
+
+template <int KH, int WARPS_M, int WARPS_N, int NROWS>
+__global__ void __launch_bounds__(WS_THREADS, 1)
+conv_win_ws_kernel(const ConvWinParams p, const double* __restrict__ Wg, const ChanAffine bn, const RowMask mask,
+                   const int4* __restrict__ box, int64_t col_base, int64_t ncols, int* __restrict__ err) {
+    static_assert(WARPS_M * WARPS_N == WS_CONSUMER_WARPS, "16 consumer warps");
+    constexpr int BN = WARPS_N * 8;
+    constexpr int NI = CW_TH + KH - 1;
+
+    extern __shared__ __align__(16) double smem[];
+    double* in_s = smem;                                        // [2][in_stage]
+    double* wts = smem + 2 * p.in_stage;                        // [2][w_stage]
+    int* tab = reinterpret_cast<int*>(smem + p.tail);           // [2 buffers][goff, soff, moff][tab_cap]
+    int4* s_box = reinterpret_cast<int4*>(tab + 6 * p.tab_cap); // [2][ncol]
+    int* s_q = reinterpret_cast<int*>(s_box + 2 * p.ncol);      // [2][ncol] query of the column
+    unsigned* s_rows = reinterpret_cast<unsigned*>(s_q + 2 * p.ncol);   // [2][WARPS_M] patch rows on the image
+    int* s_on = reinterpret_cast<int*>(s_rows + 2 * WARPS_M);   // [2] some column of the tile has its patch column on the image
+    __shared__ __align__(8) uint64_t full_bar[2], empty_bar[2];
+    __shared__ int s_abort;             // raised by the first wait that runs out: every role then leaves its loop
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int H = p.g.H, W = p.g.W;
+    const int KW = p.g.kw;
+    const int ext_h = KH - 1, ext_w = KW - 1;
+    const int per = p.ww_out * p.n_ohb;
+    const int NCH = p.n_chunks;
+
+    if (tid == 0) {
+        s_abort = 0;
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&full_bar[s], WS_PRODUCERS + 1);      // every producer thread's copies, and the weight copy
+            mbar_init(&empty_bar[s], WS_CONSUMER_WARPS);    // one arrival per consumer warp
+        }
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    struct Tile { int n_tile, owl, ohb; int64_t j0; };
+    auto decode = [&](int tile) {        // the tile count fits 31 bits (checked at launch)
+        Tile x;
+        x.n_tile = tile % p.n_ytiles;
+        const int r = tile / p.n_ytiles;
+        x.j0 = int64_t(r / per) * p.ncol;
+        const int rem = r % per;
+        x.owl = rem / p.n_ohb;
+        x.ohb = rem % p.n_ohb;
+        return x;
+    };
+    auto i_lo_of = [&](int ohb) { return NROWS > 0 ? KH - 1 : max(0, ext_h - ohb * CW_TH); };
+    auto i_hi_of = [&](int ohb) { return NROWS > 0 ? KH - 1 + NROWS : min(NI, p.wh_in - (ohb * CW_TH - ext_h)); };
+    auto kw_lo_of = [&](int owl) { return max(0, ext_w - owl); };
+    auto kw_hi_of = [&](int owl) { return min(KW, p.ww_in + ext_w - owl); };
+
+    if (warp >= WS_CONSUMER_WARPS) {
+        // ------------------------------------------------------------------ producer warpgroup
+        // the block owns 640 x 96 registers: 128 x 32 for the producers leave 512 x 112 for the consumers
+        setmaxnreg_dec<32>();
+        const int ptid = tid - WS_CONSUMER_WARPS * 32;
+        const bool cf = mask.state_cf != nullptr;
+        const bool pair_ok = cf && (p.g.Cin % 2 == 0) && (mask.N % 2 == 0);
+        const int hw_in = H * W;
+
+        // boxes and query numbers of a tile's columns into buffer b (async copies)
+        auto prep_boxes = [&](const Tile& x, int b) {
+            if (ptid < p.ncol) {
+                const bool ok = x.j0 + ptid < ncols;
+                cp_async16(&s_box[b * p.ncol + ptid], ok ? box + col_base + x.j0 + ptid : box, ok ? 16 : 0);
+            } else if (ptid < 2 * p.ncol) {
+                const int c = ptid - p.ncol;
+                const int64_t gj = col_base + x.j0 + c;
+                const bool ok = mask.state != nullptr && x.j0 + c < ncols && gj < mask.ncols;
+                cp_async4(&s_q[b * p.ncol + c], ok ? static_cast<const void*>(mask.col_q + gj) : static_cast<const void*>(box),
+                          ok ? 4 : 0);
+            }
+        };
+        // flags and fetch table of the tile whose boxes are in buffer b
+        auto prep_table = [&](const Tile& x, int b) {
+            const int th_cnt = min(CW_TH, p.wh_out - x.ohb * CW_TH);
+            // Patches near the image border hang over it: a tile none of whose columns has its patch column on the
+            // image has nothing to do, and a consumer warp skips the patch rows that are off the image for its 16
+            // columns.  Producer warp w works out the flags of column group w (of WARPS_M <= 4).
+            const int pw = ptid >> 5;
+            if (pw < WARPS_M) {
+                unsigned m = 0u;
+                if (lane < 16) {
+                    const int c = pw * 16 + lane;
+                    if (x.j0 + c < ncols) {
+                        const int4 bx = s_box[b * p.ncol + c];
+                        const int ow = bx.y + p.g.pad_l - ext_w + x.owl;
+                        if (ow >= 0 && ow < p.g.Wo) {
+                            m = 1u << 31;                       // the patch column is on the image
+                            for (int o = 0; o < th_cnt; ++o) {
+                                const int oh = bx.x + p.g.pad_t - ext_h + x.ohb * CW_TH + o;
+                                if (oh >= 0 && oh < p.g.Ho) m |= 1u << o;
+                            }
+                        }
+                    }
+                }
+                m = __reduce_or_sync(0xffffffffu, m);
+                if (lane == 0) s_rows[b * WARPS_M + pw] = m;
+            }
+            named_bar_sync(WS_BAR_PRODUCERS, WS_PRODUCERS);
+            unsigned any = 0u;
+            for (int i = 0; i < WARPS_M; ++i) any |= s_rows[b * WARPS_M + i];
+            const bool on = (any >> 31) != 0u;
+            if (ptid == 0) s_on[b] = on ? 1 : 0;
+            if (!on) return;
+            const int ih_base = x.ohb * CW_TH - ext_h;
+            const int i_lo = i_lo_of(x.ohb), n_i = i_hi_of(x.ohb) - i_lo;
+            const int kw_lo = kw_lo_of(x.owl), n_kw = kw_hi_of(x.owl) - kw_lo;
+            const int n_e = p.ncol * n_kw * n_i;
+            int* goff = tab + b * 3 * p.tab_cap;
+            int* soff = goff + p.tab_cap;
+            int* moff = soff + p.tab_cap;
+            // entry e = (origin column, input row, column), column fastest: neighbouring lanes of the fetch write
+            // neighbouring 64-byte slots of the staging row
+            for (int e = ptid; e < n_e; e += WS_PRODUCERS) {
+                const int col = e % p.ncol;
+                const int e2 = e / p.ncol;
+                const int i_idx = e2 % n_i;
+                const int kwi = kw_lo + e2 / n_i;
+                const int4 bx = s_box[b * p.ncol + col];
+                const int hi = bx.x + ih_base + i_lo + i_idx;
+                const int wi = bx.y + x.owl + kwi - ext_w;
+                int off = -1, mo = -1;
+                if (hi >= 0 && hi < H && wi >= 0 && wi < W && x.j0 + col < ncols) {
+                    off = int(col * p.cin_stride) + ((wi - bx.y) * p.wh_in + (hi - bx.x)) * p.g.Cin;
+                    if (mask.state != nullptr && col_base + x.j0 + col < mask.ncols) {
+                        const int q_off = int(s_q[b * p.ncol + col] * mask.N);
+                        mo = cf ? q_off + (hi + H * wi) * p.g.Cin : q_off + hi + H * wi;
+                    }
+                }
+                goff[e] = off;
+                moff[e] = mo;
+                soff[e] = (((kwi * p.ni_s + i_idx) * p.ncol + col) * KC) | (((col >> 1) & 1) << 30);
+            }
+        };
+        // one stage of a tile: the chunk's weights by one bulk copy (a contiguous block; its bytes are counted on the
+        // stage's full barrier), the inputs by 16-byte copies, one channel pair of one (column, input position) each
+        auto fill_stage = [&](int stage, const Tile& x, int b, int chunk) {
+            if (ptid == 0) {
+                mbar_expect_bytes(&full_bar[stage], uint32_t(p.w_stage) * 8u);
+                bulk_copy_g2s(wts + stage * p.w_stage, Wg + (int64_t(x.n_tile) * p.n_chunks + chunk) * p.w_stage,
+                              uint32_t(p.w_stage) * 8u, &full_bar[stage]);
+            }
+            if (s_on[b]) {
+                const int n_e = p.ncol * (kw_hi_of(x.owl) - kw_lo_of(x.owl)) * (i_hi_of(x.ohb) - i_lo_of(x.ohb));
+                const int* goff = tab + b * 3 * p.tab_cap;
+                const int* soff = goff + p.tab_cap;
+                const int* moff = soff + p.tab_cap;
+                double* is = in_s + stage * p.in_stage;
+                const int c0 = chunk * KC;
+                const double* src_b = p.cin + x.j0 * p.cin_stride + c0;
+                for (int it = ptid; it < 4 * n_e; it += WS_PRODUCERS) {
+                    const int e = it >> 2, u0 = 2 * (it & 3);
+                    const int off = goff[e], so_raw = soff[e], mo = moff[e];
+                    const int so = so_raw & 0x3fffffff;
+                    const int sw = (so_raw >> 30) & 1 ? 4 : 0;
+                    bool ok0 = off >= 0 && c0 + u0 < p.g.Cin, ok1 = off >= 0 && c0 + u0 + 1 < p.g.Cin;
+                    if (mo >= 0 && (ok0 || ok1)) {                   // rows the ReLU step cleared read as zero
+                        if (pair_ok) {
+                            const unsigned sv = *reinterpret_cast<const unsigned short*>(mask.state_cf + mo + c0 + u0);
+                            ok0 = ok0 && (sv & 0xffu) == 0;
+                            ok1 = ok1 && (sv >> 8) == 0;
+                        } else {
+                            if (ok0) ok0 = (cf ? mask.state_cf[mo + c0 + u0] : mask.state[mo + int64_t(c0 + u0) * hw_in]) == 0;
+                            if (ok1) ok1 = (cf ? mask.state_cf[mo + c0 + u0 + 1] : mask.state[mo + int64_t(c0 + u0 + 1) * hw_in]) == 0;
+                        }
+                    }
+                    double* d2 = is + so + (u0 ^ sw);
+                    if (ok0 && ok1) {
+                        cp_async16(d2, src_b + off + u0, 16);
+                    } else {
+                        cp_async8(d2, ok0 ? src_b + off + u0 : p.cin, ok0 ? 8 : 0);
+                        cp_async8(d2 + 1, ok1 ? src_b + off + u0 + 1 : p.cin, ok1 ? 8 : 0);
+                    }
+                }
+            }
+            cp_async_arrive_on(&full_bar[stage]);       // this thread's part of the stage has landed
+        };
+
+        int tile = blockIdx.x;
+        Tile cx = decode(tile), nx = cx;
+        int buf = 0;
+        prep_boxes(cx, 0);
+        cp_async_wait_all();
+        named_bar_sync(WS_BAR_PRODUCERS, WS_PRODUCERS);
+        prep_table(cx, 0);
+        named_bar_sync(WS_BAR_PRODUCERS, WS_PRODUCERS);
+        unsigned k = 0;                 // position in the (tile, chunk) sequence: stage k % 2, on its (k / 2)-th use
+        for (;;) {
+            const int64_t next = int64_t(tile) + gridDim.x;
+            const bool has_next = next < p.n_flat;
+            if (has_next) nx = decode(int(next));
+            for (int ch = 0; ch < NCH; ++ch, ++k) {
+                const int stage = k & 1;
+                // the consumers have left the stage (its previous use); passes at once on a stage's first use
+                // (a wait that ran out raises the abort flag; the producers then run through the remaining items
+                // without waiting, so that all four warps still meet at their named barriers, and the consumers leave)
+                if (!mbar_wait_or_abort(&empty_bar[stage], ((k >> 1) & 1) ^ 1, &s_abort)) atomicExch(err, 1);
+                fill_stage(stage, cx, buf, ch);
+                // the next tile's start-up, spread over this tile's first chunks
+                if (has_next && ch == 0) prep_boxes(nx, buf ^ 1);
+                if (has_next && ch == 1) {
+                    cp_async_wait_all();
+                    named_bar_sync(WS_BAR_PRODUCERS, WS_PRODUCERS);
+                    prep_table(nx, buf ^ 1);
+                    named_bar_sync(WS_BAR_PRODUCERS, WS_PRODUCERS);
+                }
+            }
+            if (!has_next) break;
+            tile = int(next);
+            cx = nx;
+            buf ^= 1;
+        }
+        cp_async_wait_all();
+        return;
+    }
+    // ---------------------------------------------------------------------- consumer warps
+    setmaxnreg_inc<112>();
+    const int wm = warp % WARPS_M;
+    const int wn = warp / WARPS_M;
+    const int g = lane >> 2;
+    const int t = lane & 3;
+
+    double acc[CW_TH][4];
+#pragma unroll
+    for (int o = 0; o < CW_TH; ++o)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) acc[o][r] = 0.0;
+
+    int tile = blockIdx.x;
+    Tile cx = decode(tile);
+    int buf = 0;
+    int kw_lo = 0, kw_hi = 0, i_lo = 0, i_hi = 0;
+    unsigned rows_on = 0u;
+    bool all_rows = false, tile_on = false;
+    auto enter_tile = [&]() {           // reads the flags the producers left in buffer buf (behind the full barrier)
+        kw_lo = kw_lo_of(cx.owl); kw_hi = kw_hi_of(cx.owl);
+        i_lo = i_lo_of(cx.ohb); i_hi = i_hi_of(cx.ohb);
+        tile_on = s_on[buf] != 0;
+        rows_on = tile_on ? (s_rows[buf * WARPS_M + wm] & 0xffu) : 0u;
+        if (rows_on == 0u) kw_hi = kw_lo;         // nothing of this warp's columns is on the image
+        const unsigned row_bits = (1u << min(CW_TH, p.wh_out - cx.ohb * CW_TH)) - 1u;
+        all_rows = (rows_on & row_bits) == row_bits;
+    };
+
+    // FULL: every patch row of the tile is on the image for this warp's columns (the common case): the products
+    // carry no per-row test, which would otherwise put a branch around every DMMA
+    auto compute = [&](int stage, auto full_rows) {
+        constexpr bool FULL = decltype(full_rows)::value;
+        // row = column g (and g + 8), k = channel t (and t + 4); the channel index is XORed with 4 for every other
+        // column pair (the staging swizzle)
+        const int sw = ((g >> 1) & 1) * 4;
+        const double* is = in_s + stage * p.in_stage + (wm * 16 + g) * KC;
+        const int RSr = p.ncol * KC;                                                // stride between staged input rows
+        constexpr int o1 = 8 * KC;
+        const int o0 = t ^ sw, o2 = (o0 ^ 4) - o0;
+        const double* ws = wts + stage * p.w_stage + t * p.CS + wn * 8 + g;         // k = channel t, n = g
+        for (int kwi = kw_lo; kwi < kw_hi; ++kwi) {
+            double bf[KH][2];
+#pragma unroll
+            for (int khi = 0; khi < KH; ++khi) {
+                const double* wt = ws + (khi + KH * kwi) * (KC * p.CS);     // tap index: kh fastest
+                bf[khi][0] = wt[0];
+                bf[khi][1] = wt[4 * p.CS];
+            }
+            const double* a_col = is + (kwi * p.ni_s - i_lo) * RSr + o0;
+#pragma unroll
+            for (int i = 0; i < NI; ++i) {
+                if (i < i_lo || i >= i_hi) continue;
+                const double* a = a_col + i * RSr;
+                double af[4];
+                af[0] = a[0];
+                af[1] = a[o1];
+                af[2] = a[o2];
+                af[3] = a[o2 + o1];
+                // input row i meets output row i - khi through tap khi
+#pragma unroll
+                for (int khi = 0; khi < KH; ++khi) {
+                    const int o = i - khi;
+                    if (o >= 0 && o < CW_TH) {
+                        if (FULL || ((rows_on >> o) & 1u)) dmma_16x8x8(acc[o], af, bf[khi]);
+                    }
+                }
+            }
+        }
+    };
+
+    // results of the finished tile: a lane holds two neighbouring channels of a (column, patch row), so its store is
+    // 16 bytes; the four lanes of a quad fill the 64 bytes of an 8-channel group of the channel-fastest output
+    auto store_tile = [&]() {
+        const int th_cnt = min(CW_TH, p.wh_out - cx.ohb * CW_TH);
+        const int co = cx.n_tile * BN + wn * 8 + 2 * t;
+        if (tile_on && co < p.g.Cout) {
+            const bool has_bn = bn.rden != nullptr;
+            const double r0 = has_bn ? bn.rden[co] : 1.0, s0 = has_bn ? bn.scale[co] : 1.0;
+            const double r1 = has_bn ? bn.rden[co + 1] : 1.0, s1 = has_bn ? bn.scale[co + 1] : 1.0;
+            const int64_t ca = cx.j0 + wm * 16 + g, cb = ca + 8;
+            double* da = p.pack + ca * p.pack_stride + int64_t(cx.owl * p.wh_out + cx.ohb * CW_TH) * p.g.Cout + co;
+            double* db = da + 8 * p.pack_stride;
+#pragma unroll
+            for (int o = 0; o < CW_TH; ++o) {
+                if (o >= th_cnt) break;
+                if (ca < ncols)
+                    *reinterpret_cast<double2*>(da + int64_t(o) * p.g.Cout) =
+                        make_double2((acc[o][0] * r0) * s0, (acc[o][1] * r1) * s1);
+                if (cb < ncols)
+                    *reinterpret_cast<double2*>(db + int64_t(o) * p.g.Cout) =
+                        make_double2((acc[o][2] * r0) * s0, (acc[o][3] * r1) * s1);
+            }
+        }
+#pragma unroll
+        for (int o = 0; o < CW_TH; ++o)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) acc[o][r] = 0.0;
+    };
+
+    unsigned k = 0;
+    for (;;) {
+        for (int ch = 0; ch < NCH; ++ch, ++k) {
+            const int stage = k & 1;
+            if (!mbar_wait_or_abort(&full_bar[stage], (k >> 1) & 1, &s_abort)) {
+                atomicExch(err, 1);
+                return;
+            }
+            if (ch == 0) enter_tile();
+            if (all_rows) compute(stage, std::true_type{});
+            else compute(stage, std::false_type{});
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[stage]);      // this warp is done with the stage
+        }
+        store_tile();
+        const int64_t next = int64_t(tile) + gridDim.x;
+        if (next >= p.n_flat) break;
+        tile = int(next);
+        cx = decode(tile);
+        buf ^= 1;
+    }
+}
+
 int sm_count_of_current_device() {
     static int cached_dev = -1, cached = 0;
     int dev = 0;
@@ -805,7 +1159,10 @@ int sm_count_of_current_device() {
     return cached;
 }
 
-template <int KH, int WARPS_M, int WARPS_N, int NROWS>
+// set by the warp-specialised kernel when one of its bounded waits ran out (read by conv_win_wait_timeouts)
+__device__ int g_ws_wait_timeout = 0;
+
+template <int KH, int WARPS_M, int WARPS_N, int NROWS, bool WS = true>
 int launch_persist(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn, const RowMask& mask,
                    const ColWindows& win, int wh_in, int ww_in, int64_t col_base, int64_t ncols, double* pack,
                    const double* cin, int64_t cin_stride, bool* done) {
@@ -838,16 +1195,37 @@ int launch_persist(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, con
     const size_t smem = size_t(p.tail) * sizeof(double) + size_t(6 * p.tab_cap) * sizeof(int) +
                         size_t(2 * p.ncol) * (sizeof(int4) + sizeof(int)) + size_t(2 * (CW_THREADS / 32) + 4) * sizeof(int);
     if (smem > 227 * 1024) return NNVB_OK;
-    auto kern = conv_win_persist_kernel<KH, WARPS_M, WARPS_N, NROWS>;
-    NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const unsigned grid = (unsigned)std::min<int64_t>(p.n_flat, sm_count_of_current_device());
-    kern<<<grid, CW_THREADS, smem, st>>>(p, w.w, bn, mask, win.box, col_base, ncols);
+    static const bool no_ws = getenv("NNVB_NO_WARP_SPEC") != nullptr;
+    if (WS && !no_ws) {
+        static int* err = nullptr;
+        if (err == nullptr) NNVB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_ws_wait_timeout));
+        auto kern = conv_win_ws_kernel<KH, WARPS_M, WARPS_N, NROWS>;
+        NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<grid, WS_THREADS, smem, st>>>(p, w.w, bn, mask, win.box, col_base, ncols, err);
+    } else {
+        auto kern = conv_win_persist_kernel<KH, WARPS_M, WARPS_N, NROWS>;
+        NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<grid, CW_THREADS, smem, st>>>(p, w.w, bn, mask, win.box, col_base, ncols);
+    }
     NNVB_CUDA(cudaGetLastError());
     *done = true;
     return NNVB_OK;
 }
 
 }  // namespace
+
+// Number of launches of the warp-specialised kernel since the last call in which a bounded wait ran out (0 in a
+// healthy run); synchronises the stream.
+int conv_win_wait_timeouts(cudaStream_t st, int* out) {
+    int v = 0;
+    static const int zero = 0;
+    NNVB_CUDA(cudaMemcpyFromSymbolAsync(&v, g_ws_wait_timeout, sizeof(int), 0, cudaMemcpyDeviceToHost, st));
+    NNVB_CUDA(cudaStreamSynchronize(st));
+    if (v != 0) NNVB_CUDA(cudaMemcpyToSymbolAsync(g_ws_wait_timeout, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, st));
+    *out = v;
+    return NNVB_OK;
+}
 
 // Windowed convolution with tap skipping.  *done is set when the launch was made; it stays false (and
 // nothing is launched) for geometries this kernel does not cover: the caller then uses launch_conv_f64.

@@ -2263,6 +2263,16 @@ int nnvb_batch_reach(nnvb_batch* b, const nnvb_opts* opts) {
     b->pend_scaled = false;
     NNVB_TRY(init_sets(b));
     NNVB_TRY(run_layers(b));
+    {
+        // the warp-specialised convolution bounds its waits on shared-memory barriers; one that ran out left wrong
+        // numbers behind and must not pass for a result
+        int timeouts = 0;
+        NNVB_TRY(conv_win_wait_timeouts(ctx->stream, &timeouts));
+        if (timeouts != 0) {
+            set_error("nnvb_batch_reach: a bounded wait inside conv_win_ws_kernel ran out; the results are not valid");
+            return NNVB_E_CUDA;
+        }
+    }
     b->reached = true;
     return NNVB_OK;
 }

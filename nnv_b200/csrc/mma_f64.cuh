@@ -85,4 +85,45 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int ma
     return false;
 }
 
+// Wait bounded by time (about 0.2 s of SM clock) and by a block-wide abort flag: the first wait that runs out raises
+// the flag, and every later wait of the block returns false at once, so a block whose hand-over protocol broke
+// ends within a fraction of a second instead of hanging.
+__device__ __forceinline__ bool mbar_wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    const uint32_t addr = smem_u32(bar);
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t ok;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (*abort_flag != 0 || clock64() - t0 > 400000000LL) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
+// plain arrival (release) on an mbarrier
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+// The barrier receives one arrival from this thread once all cp.async copies the thread has issued so far have
+// landed; the arrival is not added to the expected count (the count given at initialisation covers it).
+__device__ __forceinline__ void cp_async_arrive_on(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+// barrier among a subset of the block's warps (id 1..15; count = participating threads, a multiple of 32)
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+    asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(count) : "memory");
+}
+// register reallocation between the warpgroups of a block (every warp of a warpgroup executes it)
+template <int REGS>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;\n" ::"n"(REGS)); }
+template <int REGS>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;\n" ::"n"(REGS)); }
+
 }  // namespace nnvb
