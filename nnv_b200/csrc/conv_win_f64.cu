@@ -54,6 +54,8 @@ struct ConvWinParams {
     // persistent form: tiles = column groups x patch columns x row blocks x output-channel tiles, channel tiles fastest
     int n_ytiles;
     int64_t n_flat;
+    int use_bits;                   // warp-specialised form, at most 64 input channels: the row states of a table entry
+                                    // are gathered once into a 64-bit word
 };
 
 // CIN: the input is read from compact storage (p.cin).  A (column, input position) then holds its 8-channel chunk
@@ -815,8 +817,9 @@ conv_win_ws_kernel(const ConvWinParams p, const double* __restrict__ Wg, const C
     extern __shared__ __align__(16) double smem[];
     double* in_s = smem;                                        // [2][in_stage]
     double* wts = smem + 2 * p.in_stage;                        // [2][w_stage]
-    int* tab = reinterpret_cast<int*>(smem + p.tail);           // [2 buffers][goff, soff, moff][tab_cap]
-    int4* s_box = reinterpret_cast<int4*>(tab + 6 * p.tab_cap); // [2][ncol]
+    // fetch tables, [2 buffers][goff | soff | moff, or the row-state bits (two ints per entry)][tab_cap]
+    int* tab = reinterpret_cast<int*>(smem + p.tail);
+    int4* s_box = reinterpret_cast<int4*>(tab + 8 * p.tab_cap); // [2][ncol]
     int* s_q = reinterpret_cast<int*>(s_box + 2 * p.ncol);      // [2][ncol] query of the column
     unsigned* s_rows = reinterpret_cast<unsigned*>(s_q + 2 * p.ncol);   // [2][WARPS_M] patch rows on the image
     int* s_on = reinterpret_cast<int*>(s_rows + 2 * WARPS_M);   // [2] some column of the tile has its patch column on the image
@@ -916,9 +919,10 @@ conv_win_ws_kernel(const ConvWinParams p, const double* __restrict__ Wg, const C
             const int i_lo = i_lo_of(x.ohb), n_i = i_hi_of(x.ohb) - i_lo;
             const int kw_lo = kw_lo_of(x.owl), n_kw = kw_hi_of(x.owl) - kw_lo;
             const int n_e = p.ncol * n_kw * n_i;
-            int* goff = tab + b * 3 * p.tab_cap;
+            int* goff = tab + b * 4 * p.tab_cap;
             int* soff = goff + p.tab_cap;
             int* moff = soff + p.tab_cap;
+            unsigned long long* mbits = reinterpret_cast<unsigned long long*>(moff);
             // entry e = (origin column, input row, column), column fastest: neighbouring lanes of the fetch write
             // neighbouring 64-byte slots of the staging row
             for (int e = ptid; e < n_e; e += WS_PRODUCERS) {
@@ -938,8 +942,30 @@ conv_win_ws_kernel(const ConvWinParams p, const double* __restrict__ Wg, const C
                     }
                 }
                 goff[e] = off;
-                moff[e] = mo;
                 soff[e] = (((kwi * p.ni_s + i_idx) * p.ncol + col) * KC) | (((col >> 1) & 1) << 30);
+                if (!p.use_bits) {
+                    moff[e] = mo;
+                    continue;
+                }
+                // the entry's row states, one bit per channel (bit c: channel c was cleared by the ReLU step): read
+                // here once per tile instead of once per channel chunk, so that filling a stage depends on no
+                // global load
+                unsigned long long mb = 0ull;
+                if (mo >= 0) {
+                    const uint8_t* sp = mask.state_cf + mo;
+                    if ((p.g.Cin & 7) == 0 && (reinterpret_cast<uintptr_t>(sp) & 7) == 0) {
+                        for (int w8 = 0; w8 < p.g.Cin / 8; ++w8) {
+                            const unsigned long long v = *reinterpret_cast<const unsigned long long*>(sp + 8 * w8);
+                            // high bit of every non-zero byte, then the eight bits gathered into one byte
+                            const unsigned long long y =
+                                (((v & 0x7f7f7f7f7f7f7f7full) + 0x7f7f7f7f7f7f7f7full) | v) & 0x8080808080808080ull;
+                            mb |= (((y >> 7) * 0x0102040810204080ull) >> 56) << (8 * w8);
+                        }
+                    } else {
+                        for (int c = 0; c < p.g.Cin; ++c) mb |= (unsigned long long)(sp[c] != 0) << c;
+                    }
+                }
+                mbits[e] = mb;
             }
         };
         // one stage of a tile: the chunk's weights by one bulk copy (a contiguous block; its bytes are counted on the
@@ -952,19 +978,25 @@ conv_win_ws_kernel(const ConvWinParams p, const double* __restrict__ Wg, const C
             }
             if (s_on[b]) {
                 const int n_e = p.ncol * (kw_hi_of(x.owl) - kw_lo_of(x.owl)) * (i_hi_of(x.ohb) - i_lo_of(x.ohb));
-                const int* goff = tab + b * 3 * p.tab_cap;
+                const int* goff = tab + b * 4 * p.tab_cap;
                 const int* soff = goff + p.tab_cap;
                 const int* moff = soff + p.tab_cap;
+                const unsigned long long* mbits = reinterpret_cast<const unsigned long long*>(moff);
                 double* is = in_s + stage * p.in_stage;
                 const int c0 = chunk * KC;
                 const double* src_b = p.cin + x.j0 * p.cin_stride + c0;
                 for (int it = ptid; it < 4 * n_e; it += WS_PRODUCERS) {
                     const int e = it >> 2, u0 = 2 * (it & 3);
-                    const int off = goff[e], so_raw = soff[e], mo = moff[e];
+                    const int off = goff[e], so_raw = soff[e];
                     const int so = so_raw & 0x3fffffff;
                     const int sw = (so_raw >> 30) & 1 ? 4 : 0;
                     bool ok0 = off >= 0 && c0 + u0 < p.g.Cin, ok1 = off >= 0 && c0 + u0 + 1 < p.g.Cin;
-                    if (mo >= 0 && (ok0 || ok1)) {                   // rows the ReLU step cleared read as zero
+                    const int mo = p.use_bits ? -1 : moff[e];
+                    if (p.use_bits) {                                // rows the ReLU step cleared read as zero
+                        const unsigned two = unsigned(mbits[e] >> (c0 + u0)) & 3u;
+                        ok0 = ok0 && (two & 1u) == 0;
+                        ok1 = ok1 && (two & 2u) == 0;
+                    } else if (mo >= 0 && (ok0 || ok1)) {
                         if (pair_ok) {
                             const unsigned sv = *reinterpret_cast<const unsigned short*>(mask.state_cf + mo + c0 + u0);
                             ok0 = ok0 && (sv & 0xffu) == 0;
@@ -1192,7 +1224,9 @@ int launch_persist(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, con
     p.n_ytiles = w.n_tiles;
     p.n_flat = ceil_div(ncols, p.ncol) * p.ww_out * p.n_ohb * w.n_tiles;
     if (p.n_flat >= (int64_t(1) << 31)) return NNVB_OK;
-    const size_t smem = size_t(p.tail) * sizeof(double) + size_t(6 * p.tab_cap) * sizeof(int) +
+    p.use_bits = g.Cin <= 64 && (mask.state == nullptr || mask.state_cf != nullptr);
+    // (both forms get room for four ints per table entry and buffer; the one-block-per-role form uses three)
+    const size_t smem = size_t(p.tail) * sizeof(double) + size_t(8 * p.tab_cap) * sizeof(int) +
                         size_t(2 * p.ncol) * (sizeof(int4) + sizeof(int)) + size_t(2 * (CW_THREADS / 32) + 4) * sizeof(int);
     if (smem > 227 * 1024) return NNVB_OK;
     const unsigned grid = (unsigned)std::min<int64_t>(p.n_flat, sm_count_of_current_device());
