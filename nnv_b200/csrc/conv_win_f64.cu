@@ -29,6 +29,7 @@ constexpr int KC = 8;               // input channels per pipeline stage, as con
 constexpr int CW_TH = 8;            // patch rows per block
 constexpr int CW_THREADS = 512;
 constexpr int CW_STAGES = 2;
+constexpr int CW_MAX_STAGES = 4;   // warp-specialised form: 2 to 4 stages, as many as shared memory holds
 
 struct ConvWinParams {
     ConvGeom g;
@@ -54,6 +55,7 @@ struct ConvWinParams {
     // persistent form: tiles = column groups x patch columns x row blocks x output-channel tiles, channel tiles fastest
     int n_ytiles;
     int64_t n_flat;
+    int stages;                     // warp-specialised form: pipeline depth
     int use_bits;                   // warp-specialised form, at most 64 input channels: the row states of a table entry
                                     // are gathered once into a 64-bit word
 };
@@ -815,15 +817,16 @@ conv_win_ws_kernel(const ConvWinParams p, const double* __restrict__ Wg, const C
     constexpr int NI = CW_TH + KH - 1;
 
     extern __shared__ __align__(16) double smem[];
-    double* in_s = smem;                                        // [2][in_stage]
-    double* wts = smem + 2 * p.in_stage;                        // [2][w_stage]
+    const int S = p.stages;                                     // 2 to 4 pipeline stages, as many as fit
+    double* in_s = smem;                                        // [S][in_stage]
+    double* wts = smem + S * p.in_stage;                        // [S][w_stage]
     // fetch tables, [2 buffers][goff | soff | moff, or the row-state bits (two ints per entry)][tab_cap]
     int* tab = reinterpret_cast<int*>(smem + p.tail);
     int4* s_box = reinterpret_cast<int4*>(tab + 8 * p.tab_cap); // [2][ncol]
     int* s_q = reinterpret_cast<int*>(s_box + 2 * p.ncol);      // [2][ncol] query of the column
     unsigned* s_rows = reinterpret_cast<unsigned*>(s_q + 2 * p.ncol);   // [2][WARPS_M] patch rows on the image
     int* s_on = reinterpret_cast<int*>(s_rows + 2 * WARPS_M);   // [2] some column of the tile has its patch column on the image
-    __shared__ __align__(8) uint64_t full_bar[2], empty_bar[2];
+    __shared__ __align__(8) uint64_t full_bar[CW_MAX_STAGES], empty_bar[CW_MAX_STAGES];
     __shared__ int s_abort;             // raised by the first wait that runs out: every role then leaves its loop
 
     const int tid = threadIdx.x;
@@ -837,7 +840,7 @@ conv_win_ws_kernel(const ConvWinParams p, const double* __restrict__ Wg, const C
 
     if (tid == 0) {
         s_abort = 0;
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < CW_MAX_STAGES; ++s) {
             mbar_init(&full_bar[s], WS_PRODUCERS + 1);      // every producer thread's copies, and the weight copy
             mbar_init(&empty_bar[s], WS_CONSUMER_WARPS);    // one arrival per consumer warp
         }
@@ -1026,18 +1029,19 @@ conv_win_ws_kernel(const ConvWinParams p, const double* __restrict__ Wg, const C
         named_bar_sync(WS_BAR_PRODUCERS, WS_PRODUCERS);
         prep_table(cx, 0);
         named_bar_sync(WS_BAR_PRODUCERS, WS_PRODUCERS);
-        unsigned k = 0;                 // position in the (tile, chunk) sequence: stage k % 2, on its (k / 2)-th use
+        int stage = 0;                  // the (tile, chunk) sequence walks the stages round robin;
+        unsigned use = 0;               // use = how often the current stage has been filled before
         for (;;) {
             const int64_t next = int64_t(tile) + gridDim.x;
             const bool has_next = next < p.n_flat;
             if (has_next) nx = decode(int(next));
-            for (int ch = 0; ch < NCH; ++ch, ++k) {
-                const int stage = k & 1;
+            for (int ch = 0; ch < NCH; ++ch) {
                 // the consumers have left the stage (its previous use); passes at once on a stage's first use
                 // (a wait that ran out raises the abort flag; the producers then run through the remaining items
                 // without waiting, so that all four warps still meet at their named barriers, and the consumers leave)
-                if (!mbar_wait_or_abort(&empty_bar[stage], ((k >> 1) & 1) ^ 1, &s_abort)) atomicExch(err, 1);
+                if (!mbar_wait_or_abort(&empty_bar[stage], (use & 1) ^ 1, &s_abort)) atomicExch(err, 1);
                 fill_stage(stage, cx, buf, ch);
+                if (++stage == S) { stage = 0; ++use; }
                 // the next tile's start-up, spread over this tile's first chunks
                 if (has_next && ch == 0) prep_boxes(nx, buf ^ 1);
                 if (has_next && ch == 1) {
@@ -1155,11 +1159,11 @@ conv_win_ws_kernel(const ConvWinParams p, const double* __restrict__ Wg, const C
             for (int r = 0; r < 4; ++r) acc[o][r] = 0.0;
     };
 
-    unsigned k = 0;
+    int stage = 0;
+    unsigned use = 0;
     for (;;) {
-        for (int ch = 0; ch < NCH; ++ch, ++k) {
-            const int stage = k & 1;
-            if (!mbar_wait_or_abort(&full_bar[stage], (k >> 1) & 1, &s_abort)) {
+        for (int ch = 0; ch < NCH; ++ch) {
+            if (!mbar_wait_or_abort(&full_bar[stage], use & 1, &s_abort)) {
                 atomicExch(err, 1);
                 return;
             }
@@ -1168,6 +1172,7 @@ conv_win_ws_kernel(const ConvWinParams p, const double* __restrict__ Wg, const C
             else compute(stage, std::false_type{});
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[stage]);      // this warp is done with the stage
+            if (++stage == S) { stage = 0; ++use; }
         }
         store_tile();
         const int64_t next = int64_t(tile) + gridDim.x;
@@ -1220,6 +1225,7 @@ int launch_persist(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, con
     p.w_stage = g.kh * g.kw * KC * p.CS;
     p.n_chunks = w.n_chunks;
     p.tab_cap = p.ncol * g.kw * p.ni_s;
+    p.stages = 2;
     p.tail = 2 * (p.in_stage + p.w_stage);
     p.n_ytiles = w.n_tiles;
     p.n_flat = ceil_div(ncols, p.ncol) * p.ww_out * p.n_ohb * w.n_tiles;
@@ -1232,11 +1238,17 @@ int launch_persist(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, con
     const unsigned grid = (unsigned)std::min<int64_t>(p.n_flat, sm_count_of_current_device());
     static const bool no_ws = getenv("NNVB_NO_WARP_SPEC") != nullptr;
     if (WS && !no_ws) {
+        // deeper pipeline where the stages are small: the producers then run further ahead of the consumers
+        const size_t stage_bytes = size_t(p.in_stage + p.w_stage) * sizeof(double);
+        const size_t fixed = smem - 2 * stage_bytes;
+        p.stages = int(std::min<size_t>(CW_MAX_STAGES, (size_t(227) * 1024 - fixed) / stage_bytes));
+        p.tail = p.stages * (p.in_stage + p.w_stage);
+        const size_t smem_ws = fixed + p.stages * stage_bytes;
         static int* err = nullptr;
         if (err == nullptr) NNVB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_ws_wait_timeout));
         auto kern = conv_win_ws_kernel<KH, WARPS_M, WARPS_N, NROWS>;
-        NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<grid, WS_THREADS, smem, st>>>(p, w.w, bn, mask, win.box, col_base, ncols, err);
+        NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_ws));
+        kern<<<grid, WS_THREADS, smem_ws, st>>>(p, w.w, bn, mask, win.box, col_base, ncols, err);
     } else {
         auto kern = conv_win_persist_kernel<KH, WARPS_M, WARPS_N, NROWS>;
         NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
