@@ -480,7 +480,7 @@ def run_sharded(env, name, K, W):
     cfg = make_config(name, n_queries=n_img)
     net = Network(ctx, cfg["layers"], cfg["in_shape"])
     if world > 1:
-        ctx.set_shard_nccl(rank, world, peer_memory=not env["args"].no_peer_memory)
+        ctx.set_shard_nccl(rank, world, peer_memory=bool(env["args"].peer_memory))
     batches = []
     for qu in cfg["queries"]:
         b = Batch(net, [qu])
@@ -533,7 +533,7 @@ def run_sharded(env, name, K, W):
                          "share_of_step": sh["ms"] / dev_ms if dev_ms else None,
                          "how": ("none: one rank" if world == 1 else
                                  "NCCL all-reduce inside the library (ncclDouble, ncclSum) per ReLU layer"
-                                 if env["args"].no_peer_memory else
+                                 if not env["args"].peer_memory else
                                  "peer memory: per ReLU layer the partial sums are written to a peer-mapped buffer and "
                                  "added inside the classification kernel (time = reduce + flag + classify kernels); "
                                  "NCCL for the small verdict reductions")}}
@@ -543,6 +543,112 @@ def run_sharded(env, name, K, W):
     if world > 1:
         ctx.set_shard_nccl(0, 1)              # back to unsharded sets
     return out
+
+
+def run_contexts(args, n_ctx):
+    """``--contexts C``: the workload's query list split over C engine contexts of ONE GPU, each with its own stream
+    and host thread (ctypes releases the GIL inside the library).  Small batches leave the GPU mostly idle between a
+    reach's host round trips (one per ReLU layer, two in the verdict); a second context fills those gaps with the
+    other batch's kernels.  Timing: wall clock between two device synchronisations around the K steps of all
+    threads (the contexts' streams are independent, so no single stream's events cover the region)."""
+    import threading
+
+    import torch
+
+    from nnv_b200 import _lib as L
+    from nnv_b200 import nn
+    from nnv_b200.configs import make_config
+    from nnv_b200.engine import Batch, Context, Network
+
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    K, W = args.steps, args.warmup
+    name = args.workload or "cnn32"
+    nq, sub, desc = WORKLOADS[name]
+    if args.batch:
+        sub = args.batch
+    if args.queries:
+        nq = min(nq, args.queries)
+        desc += " [first %d queries only]" % nq
+    cfg = make_config(name, n_queries=nq)
+    layers, shape = cfg["layers"], cfg["in_shape"]
+    kind = cfg["queries"][0].get("spec", "max")
+    groups = [np.arange(i, min(nq, i + sub)) for i in range(0, nq, sub)]
+    opts = {"reachMethod": "approx-star"}
+    sets_all = _sets_of(nn, cfg["queries"])
+    gate = threading.Barrier(n_ctx + 1)
+    counts = [dict(robust=0, unknown=0, second_pass=0, launches=0) for _ in range(n_ctx)]
+    errors = []
+
+    def worker(c):
+        try:
+            torch.cuda.set_device(local)
+            ctx = Context(local, (args.arena_gb << 30) // n_ctx)
+            net = Network(ctx, layers, shape)
+            model = nn.NN(layers, ctx=ctx)
+            model._nets[tuple(int(x) for x in shape)] = net
+            mine = groups[c::n_ctx]
+            batches = []
+            for g in mine:
+                b = Batch(net, [cfg["queries"][i] for i in g])
+                b.upload()
+                batches.append(b)
+            targets0 = [np.array([cfg["queries"][i]["target"] for i in g], dtype=np.int32) for g in mine]
+
+            def step(count):
+                for b, g, t0 in zip(batches, mine, targets0):
+                    b.reach(keep_layer_bounds=True)
+                    v, _, _ = b.verify_robust(t0, kind)
+                    und = int((v == L.UNDECIDED).sum())
+                    res = (model.finish_verdicts([sets_all[i] for i in g], opts, t0 + 1, v, kind) if und
+                           else np.where(v == L.VERDICT_EMPTY, 1, 2))
+                    if count:
+                        counts[c]["robust"] += int((res == 1).sum())
+                        counts[c]["unknown"] += int((res == 2).sum())
+                        counts[c]["second_pass"] += und
+
+            for _ in range(W + 1):
+                step(False)
+            torch.cuda.synchronize(dev)
+            gate.wait()                 # all contexts warm: the main thread starts the clock
+            l0 = ctx.launch_count
+            for _ in range(K):
+                step(True)
+            torch.cuda.synchronize(dev)
+            counts[c]["launches"] = ctx.launch_count - l0
+            gate.wait()
+            ctx.close()
+        except BaseException as exc:     # a failed worker must not leave the others at the gate
+            errors.append(exc)
+            gate.abort()
+
+    threads = [threading.Thread(target=worker, args=(c,)) for c in range(n_ctx)]
+    sampler = ClockSampler(local)
+    for t in threads:
+        t.start()
+    try:
+        gate.wait()
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        gate.wait()
+        torch.cuda.synchronize(dev)
+        wall = time.perf_counter() - t0
+    except threading.BrokenBarrierError:
+        wall = None
+    for t in threads:
+        t.join()
+    clocks = sampler.stop()
+    if errors or wall is None:
+        raise errors[0] if errors else RuntimeError("a context thread failed")
+    emit({"metric": METRIC, "value": K * nq / wall, "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": W,
+          "ms_per_step": wall * 1e3 / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+          "dtype": "f64", "data": "synthetic",
+          "config": {"workload": desc, "queries_per_step": nq, "batch_per_launch": sub, "contexts": n_ctx,
+                     "timing": "wall clock between device synchronisations around the K steps of all context threads",
+                     "verdicts": {"robust": sum(x["robust"] for x in counts), "unknown": sum(x["unknown"] for x in counts),
+                                  "finished_by_second_pass": sum(x["second_pass"] for x in counts)}},
+          "gpu_launches": sum(x["launches"] for x in counts), "clocks": clocks})
 
 
 def run_ours(args):
@@ -687,11 +793,17 @@ def main():
     ap.add_argument("--arena-gb", type=int, default=112)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
-    ap.add_argument("--no-peer-memory", action="store_true",
-                    help="--shard generators: NCCL all-reduce instead of the fused peer-memory classification")
+    ap.add_argument("--peer-memory", action="store_true",
+                    help="--shard generators: the fused peer-memory classification instead of the NCCL all-reduce "
+                         "(measured slower than NCCL at 2 and at 8 GPUs, so not the default)")
+    ap.add_argument("--no-peer-memory", action="store_true", help="accepted for older command lines; the default now")
+    ap.add_argument("--contexts", type=int, default=1,
+                    help="one GPU: split the query list over this many engine contexts (own stream and host thread each)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.contexts > 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        run_contexts(args, args.contexts)
     else:
         run_ours(args)
 

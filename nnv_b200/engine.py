@@ -64,7 +64,7 @@ class Context:
         L.check(self.lib.nnvb_set_shard(self.handle, int(rank), int(world), self._hook, None), "nnvb_set_shard")
         self.rank, self.world = int(rank), int(world)
 
-    def set_shard_nccl(self, rank, world, peer_memory=True, group=None):
+    def set_shard_nccl(self, rank, world, peer_memory=False, group=None):
         """The same sharding with the collective inside the library (``nnvb_set_shard_nccl``): NCCL bound by
         the library itself and, with ``peer_memory``, the fused sum-and-classify kernel over peer-mapped
         buffers.  torch.distributed only carries the 128-byte communicator id from rank 0 to the others."""
