@@ -618,6 +618,9 @@ def run_contexts(args, n_ctx):
             torch.cuda.synchronize(dev)
             counts[c]["launches"] = ctx.launch_count - l0
             gate.wait()
+            for b in batches:           # handles go in the order batch, network, context
+                b.close()
+            net.close()
             ctx.close()
         except BaseException as exc:     # a failed worker must not leave the others at the gate
             errors.append(exc)
