@@ -29,7 +29,9 @@ constexpr int KC = 8;               // input channels per pipeline stage, as con
 constexpr int CW_TH = 8;            // patch rows per block
 constexpr int CW_THREADS = 512;
 constexpr int CW_STAGES = 2;
-constexpr int CW_MAX_STAGES = 4;   // warp-specialised form: 2 to 4 stages, as many as shared memory holds
+constexpr int CW_MAX_STAGES = 4;    // warp-specialised form: 2 to 4 stages, as many as shared memory holds
+// dynamic shared memory a block may ask for: the 227 KB of an SM less the kernels' static variables (barriers, flags)
+constexpr size_t CW_SMEM_LIMIT = size_t(227) * 1024 - 256;
 
 struct ConvWinParams {
     ConvGeom g;
@@ -781,7 +783,7 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
     p.tail = int(std::max(pipe, stage_out) / sizeof(double));
     const size_t smem = std::max(pipe, stage_out) + size_t(2 * BN) * sizeof(double) +
                         size_t(3 * p.tab_cap) * sizeof(int) + size_t(p.ncol) * sizeof(int4);
-    if (smem > 227 * 1024) return NNVB_OK;
+    if (smem > CW_SMEM_LIMIT) return NNVB_OK;
     if (int64_t(p.ncol) * std::max(ld_in, ld_out) >= (int64_t(1) << 31)) return NNVB_OK;
     const int64_t blocks = ceil_div(ncols, p.ncol) * p.ww_out * p.n_ohb;
     if (blocks >= (int64_t(1) << 31)) return NNVB_OK;
@@ -1234,14 +1236,14 @@ int launch_persist(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, con
     // (both forms get room for four ints per table entry and buffer; the one-block-per-role form uses three)
     const size_t smem = size_t(p.tail) * sizeof(double) + size_t(8 * p.tab_cap) * sizeof(int) +
                         size_t(2 * p.ncol) * (sizeof(int4) + sizeof(int)) + size_t(2 * (CW_THREADS / 32) + 4) * sizeof(int);
-    if (smem > 227 * 1024) return NNVB_OK;
+    if (smem > CW_SMEM_LIMIT) return NNVB_OK;
     const unsigned grid = (unsigned)std::min<int64_t>(p.n_flat, sm_count_of_current_device());
     static const bool no_ws = getenv("NNVB_NO_WARP_SPEC") != nullptr;
     if (WS && !no_ws) {
         // deeper pipeline where the stages are small: the producers then run further ahead of the consumers
         const size_t stage_bytes = size_t(p.in_stage + p.w_stage) * sizeof(double);
         const size_t fixed = smem - 2 * stage_bytes;
-        p.stages = int(std::min<size_t>(CW_MAX_STAGES, (size_t(227) * 1024 - fixed) / stage_bytes));
+        p.stages = int(std::min<size_t>(CW_MAX_STAGES, (CW_SMEM_LIMIT - fixed) / stage_bytes));
         p.tail = p.stages * (p.in_stage + p.w_stage);
         const size_t smem_ws = fixed + p.stages * stage_bytes;
         static int* err = nullptr;
