@@ -460,7 +460,18 @@ def rooflines(res, K, dgemm_tflops, hbm_peak, hbm_src):
     relu_step["frac"] = relu_step["achieved"] / hbm_peak
     relu_step["dense_equivalent"]["frac"] = relu_step["dense_equivalent"]["achieved"] / hbm_peak
     dominant = max(kernels, key=lambda k: prof[k]["ms"])
-    return {"roofline": dict(roof(dominant), **({"dense_equivalent": dense_equiv(dominant)} if dominant in dense else {})),
+    out_main = roof(dominant)
+    if dominant == "conv" and cfg.get("name") == "cnn32" and not cfg.get("small"):
+        # DRAM read + write of the convolution launches of one reach, from the committed ncu capture at 8 images per
+        # batch (profiles/conv_win_ws_and_fc_gather_cnn32_batch8.md: 154.6 + 289.5 + 64.2 + 773.1 + 275.1 + 380.7 MB
+        # for the six windowed launches of 8 images), scaled by the images a step processes: the columns, and with
+        # them the bytes, grow in proportion to the images
+        traffic_per_image = 1937.2e6 / 8.0
+        out_main["traffic"] = traffic_per_image * res["line"]["queries_per_step"] * K / max(prof["conv"]["launches"], 1)
+        out_main["traffic_source"] = ("dram__bytes (read + write) of conv_win_ws_kernel from an ncu capture at 8 images "
+                                      "per batch, scaled to this step's images; per launch of the family "
+                                      "(the family's launches include the small centre-column launches)")
+    return {"roofline": dict(out_main, **({"dense_equivalent": dense_equiv(dominant)} if dominant in dense else {})),
             "roofline_other": {k: dict(roof(k), **({"dense_equivalent": dense_equiv(k)} if k in dense else {}))
                                for k in kernels if k != dominant},
             "relu_step": relu_step,
