@@ -395,6 +395,59 @@ def lp_bounds_hook(batch, relu_layer):
         batch.tighten_crossing(q, relu_layer, xmin, xmax)
 
 
+def _matlab_round(x):
+    return int(np.floor(x + 0.5))
+
+
+def relax_bounds_hook(method, relax_factor, rng=None):
+    """Bounds hook of the 'relax-star-*' methods with relaxFactor < 1 (PosLin.reach_relaxed_star_area / _range /
+    _static / _random, PosLin.m:986-1105, 863-984, 1541-1646, 1425-1539): of the neurons the estimated ranges call
+    crossing, n1 = round((1 - relaxFactor) * count) get LP-optimised ranges (largest triangle area / largest range /
+    first in index order / random choice), the others keep the estimated bounds.  Returns the hook function.
+    The engine appends the new predicates in ascending neuron order; the reference appends the neurons without
+    optimised ranges first (map9 = [map22; map8]): the same set with its new predicate variables permuted."""
+    rng = rng or np.random.default_rng(0)
+
+    def hook(batch, relu_layer):
+        for q in range(batch.nq):
+            idx, l_est, u_est = batch.get_crossing(q, relu_layer)
+            k = len(idx)
+            if k == 0:
+                continue
+            n1 = _matlab_round((1.0 - relax_factor) * k)
+            if method == "relax-star-area":
+                sel = np.argsort(-(0.5 * np.abs(u_est) * np.abs(l_est)), kind="stable")[:n1]
+            elif method == "relax-star-range":
+                sel = np.argsort(-(u_est - l_est), kind="stable")[:n1]
+            elif method == "relax-star-static":
+                sel = np.arange(n1)
+            else:                                   # relax-star-random
+                sel = rng.permutation(k)[:n1]
+            xmin = np.array(l_est, dtype=np.float64, copy=True)
+            xmax = np.array(u_est, dtype=np.float64, copy=True)
+            if n1 > 0:
+                P, _ = batch.out_dims(q)
+                G, c = batch.get_crossing_rows(q, relu_layer, k, P)
+                Cm, d = batch.get_constraints_before(q, relu_layer, P)
+                pl, pu = batch.get_pred_bounds(q)
+                Cs = sp.csr_matrix(Cm)
+                box_only = (Cs.shape[0] == 0 or Cs.nnz == 0) and np.all(np.isfinite(pl)) and np.all(np.isfinite(pu)) \
+                    and np.all(d >= 0)
+                bounds = list(zip(pl, pu))
+                for t in sel:
+                    xmax[t] = _lp_extreme(G[t], c[t], Cs, d, bounds, box_only, pl, pu, True)
+                    if xmax[t] > 0:
+                        xmin[t] = min(_lp_extreme(G[t], c[t], Cs, d, bounds, box_only, pl, pu, False), xmax[t])
+                    else:
+                        xmin[t] = min(xmin[t], xmax[t])
+            batch.tighten_crossing(q, relu_layer, xmin, xmax)
+
+    return hook
+
+
+_RELAX_WITH_LP = ("relax-star-area", "relax-star-range", "relax-star-static", "relax-star-random")
+
+
 # ------------------------------------------------------------------------- layers
 
 
@@ -627,8 +680,9 @@ def _validate_reach_options(opts):
         if opts.get("bounds", "estimate") not in ("estimate", "lp"):
             raise ValueError("bounds must be 'estimate' (LP-free ranges) or 'lp' (the reference's LP-tightened ranges)")
     elif method in _LP_FREE_RELAX:
-        if rf != 1:
-            raise NotImplementedError("relax-star methods are implemented for relaxFactor = 1 only (no LP)")
+        if rf != 1 and method not in _RELAX_WITH_LP:
+            raise NotImplementedError("%s is implemented for relaxFactor = 1 only (no LP); relaxFactor < 1 is "
+                                      "available for %s" % (method, ", ".join(_RELAX_WITH_LP)))
     else:
         raise NotImplementedError("reachMethod %r is outside this engine (approx-star / relax-star-* only)" % (method,))
     if not (0 <= rf <= 1):
@@ -732,11 +786,17 @@ class NN:
                 raise ValueError("all input sets of a batch must have the same shape")
         net = self._network(shape)
         b = Batch(net, [s._query() for s in inputSets])
-        lp = bool(reachOptions) and dict(reachOptions).get("bounds", "estimate") == "lp"
+        ro = dict(reachOptions or {})
+        lp = ro.get("bounds", "estimate") == "lp"
+        method, rf = ro.get("reachMethod", "approx-star"), ro.get("relaxFactor", None)
+        relax_lp = method in _RELAX_WITH_LP and rf is not None and rf < 1
         t0 = time.perf_counter()
         try:
             b.upload()
-            if lp:                      # the LPs read the constraint system: records are kept
+            if relax_lp:                # a share of the crossing neurons gets LP bounds
+                b.set_bounds_hook(relax_bounds_hook(method, rf))
+                keep_constraints = True
+            elif lp:                    # the LPs read the constraint system: records are kept
                 b.set_bounds_hook(lp_bounds_hook)
                 keep_constraints = True
             b.reach(keep_constraints=keep_constraints, keep_layer_bounds=keep_layer_bounds)

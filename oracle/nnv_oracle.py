@@ -385,6 +385,90 @@ def relu_reach_lp(S):
                      np.concatenate([S.pl, np.zeros(k)]), np.concatenate([S.pu, ubc]), trace)
 
 
+def _matlab_round(x):
+    """MATLAB round: halves away from zero (Python's round goes to even)."""
+    return int(np.floor(x + 0.5)) if x >= 0 else -int(np.floor(-x + 0.5))
+
+
+def relax_selection(method, relax_factor, lb2, ub2, rng=None):
+    """Which of the neurons the estimated ranges call crossing get LP-optimised ranges, and the order of the rest:
+    n1 = round((1 - relaxFactor) * numel(map2)) neurons, picked by
+      'relax-star-area'   largest triangle area 0.5*|ub|*|lb| first   (PosLin.m:1044-1052)
+      'relax-star-range'  largest ub - lb first                        (PosLin.m:929-936)
+      'relax-star-static' the first n1 in index order                  (PosLin.m:1599-1607)
+      'relax-star-random' randperm (not reproducible across RNGs)      (PosLin.m:1483-1491)
+    (MATLAB's sort is stable: ties keep index order).  Returns (positions of map21, positions of map22) within
+    map2, each in the reference's order."""
+    k = len(lb2)
+    n1 = _matlab_round((1.0 - relax_factor) * k)
+    if method == "relax-star-area":
+        order = np.argsort(-(0.5 * np.abs(ub2) * np.abs(lb2)), kind="stable")
+    elif method == "relax-star-range":
+        order = np.argsort(-(ub2 - lb2), kind="stable")
+    elif method == "relax-star-static":
+        order = np.arange(k)
+    elif method == "relax-star-random":
+        rng = rng or np.random.default_rng(0)
+        pick = rng.permutation(k)[:n1]
+        rest = np.setdiff1d(np.arange(k), pick)              # setdiff(map2, map21, 'stable'): index order
+        return pick, rest
+    else:
+        raise ValueError(method)
+    return order[:n1], order[n1:]
+
+
+def relu_reach_relaxed(S, method, relax_factor, rng=None):
+    """PosLin.reach_relaxed_star_area / _range / _static / _random (PosLin.m:986-1105, 863-984, 1541-1646,
+    1425-1539): estimated ranges classify; of the crossing neurons only the selected share gets LP bounds
+    (getMaxs, then getMins where the maximum is positive); the others keep the estimated bounds.  New predicates
+    are appended in the reference's order map9 = [map22; map8]: first the neurons without optimised ranges (in
+    selection order), then the optimised ones that still cross."""
+    h, w, c, p1 = S.V.shape
+    N = h * w * c
+    P = p1 - 1
+    M = S.mat()
+    lb, ub = estimate_ranges(M, S.pl, S.pu)
+    map1 = np.nonzero(ub <= 0)[0]
+    map2 = np.nonzero((lb < 0) & (ub > 0))[0]
+    p21, p22 = relax_selection(method, relax_factor, lb[map2], ub[map2], rng)
+    map21, map22 = map2[p21], map2[p22]
+    C = sp.csr_matrix(S.C)
+    xmax = np.array([lp_extreme(M[i, 1:], M[i, 0], C, S.d, S.pl, S.pu, True) for i in map21])
+    map4 = map21[xmax <= 0] if len(map21) else map21
+    dead = np.concatenate([map1, map4]).astype(np.int64)
+    keep5 = xmax > 0 if len(map21) else np.zeros(0, bool)
+    map6 = map21[keep5]
+    xmax1 = xmax[keep5]
+    xmin = np.array([lp_extreme(M[i, 1:], M[i, 0], C, S.d, S.pl, S.pu, False) for i in map6])
+    keep7 = xmin < 0 if len(map6) else np.zeros(0, bool)
+    map8 = map6[keep7]
+    cross = np.concatenate([map22, map8]).astype(np.int64)                      # map9
+    lbc = np.concatenate([lb[map22], xmin[keep7] if len(map6) else np.zeros(0)])
+    ubc = np.concatenate([ub[map22], xmax1[keep7] if len(map6) else np.zeros(0)])
+    k = len(cross)
+    In = M.copy(order="F")
+    In[dead, :] = 0.0
+    c_idx = In[cross, 0].copy()
+    G_idx = In[cross, 1:].copy()
+    In[cross, :] = 0.0
+    newM = np.zeros((N, P + 1 + k), order="F")
+    newM[:, :P + 1] = In
+    newM[cross, P + 1 + np.arange(k)] = 1.0
+    a = ubc / (ubc - lbc)
+    b = a * lbc
+    Ik = sp.identity(k, format="csr")
+    m0 = S.C.shape[0]
+    newC = sp.vstack([sp.hstack([S.C, sp.csr_matrix((m0, k))], format="csr"),
+                      sp.hstack([sp.csr_matrix((k, P)), -Ik], format="csr"),
+                      sp.hstack([sp.csr_matrix(G_idx), -Ik], format="csr"),
+                      sp.hstack([sp.csr_matrix(G_idx * (-a)[:, None]), Ik], format="csr")], format="csr")
+    newd = np.concatenate([S.d, np.zeros(k), -c_idx, a * c_idx - b])
+    trace = S.trace + [{"N": N, "lb": lb, "ub": ub, "dead": np.sort(dead), "cross": cross, "cross_est": map2,
+                        "optimised": map21, "lb_lp": lbc, "ub_lp": ubc, "P_in": P, "P_out": P + k}]
+    return ImageStar(newM.reshape(h, w, c, P + 1 + k, order="F"), newC, newd,
+                     np.concatenate([S.pl, np.zeros(k)]), np.concatenate([S.pu, ubc]), trace)
+
+
 # --------------------------------------------------------------------------
 # network driver and verdict
 
@@ -452,9 +536,10 @@ def flatten_reach(S, L):
     return ImageStar(M.reshape((1, 1, M.shape[0], M.shape[1]), order="F"), S.C, S.d, S.pl, S.pu, S.trace)
 
 
-def reach(layers, S, keep_constraints=True, lp_bounds=False):
+def reach(layers, S, keep_constraints=True, lp_bounds=False, relax=None):
     """NN.reach_noConns layer loop, NN.m:1529-1551.  lp_bounds: the ReLU layers use the LP-tightened
-    step (reference default 'approx-star', relaxFactor = 0) instead of the estimated bounds."""
+    step (reference default 'approx-star', relaxFactor = 0) instead of the estimated bounds.  relax =
+    (method, relaxFactor): the 'relax-star-*' step with LPs for a share of the crossing neurons."""
     for L in layers:
         t = L["type"]
         if t == "imageinput":
@@ -470,7 +555,10 @@ def reach(layers, S, keep_constraints=True, lp_bounds=False):
         elif t == "avgpool":
             S = avgpool_reach(S, L)
         elif t == "relu":
-            S = relu_reach_lp(S) if lp_bounds else relu_reach(S, keep_constraints)
+            if relax is not None:
+                S = relu_reach_relaxed(S, relax[0], relax[1])
+            else:
+                S = relu_reach_lp(S) if lp_bounds else relu_reach(S, keep_constraints)
         else:
             raise ValueError(t)
     return S

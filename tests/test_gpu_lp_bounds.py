@@ -87,3 +87,67 @@ def test_hook_errors_surface_as_status(ctx):
     b.reach(keep_constraints=True)                     # the context and the batch stay usable
     b.close()
     model.close()
+
+
+def _oracle_in_engine_order(S):
+    """The oracle appends a layer's new predicates in the reference's order (neurons without optimised ranges
+    first), the engine in ascending neuron order: the column permutation that turns the first into the second,
+    layer by layer, and the per-layer crossing lists in ascending order."""
+    perm = list(range(1 + S.trace[0]["P_in"]))
+    crossings = []
+    for t in S.trace:
+        order = np.argsort(t["cross"], kind="stable")
+        base = 1 + t["P_in"]
+        perm.extend(int(base + o) for o in order)
+        crossings.append((t["cross"][order], t["lb_lp"][order], t["ub_lp"][order]))
+    return np.array(perm, dtype=np.int64), crossings
+
+
+@pytest.mark.parametrize("method,rf", [("relax-star-area", 0.5), ("relax-star-range", 0.25), ("relax-star-static", 0.5),
+                                       ("relax-star-area", 0.0)])
+@pytest.mark.parametrize("name,small,nq", [("fc5", False, 5), ("cnn28", True, 2)])
+def test_relax_star_with_lp_share_matches_oracle(ctx, name, small, nq, method, rf):
+    """'relax-star-*' with relaxFactor < 1 (PosLin.m:863-1105, 1541-1646): a share of the crossing neurons,
+    chosen by the method's heuristic on the estimated ranges, gets LP bounds.  Same neurons optimised, same
+    crossing sets, same set up to the order of the new predicate variables."""
+    cfg = make_config(name, n_queries=nq, small=small)
+    model = nn.NN(cfg["layers"], ctx=ctx)
+    opts = {"reachMethod": method, "relaxFactor": rf}
+    b = model.reach_batch(_sets(cfg), opts, keep_layer_bounds=True)
+    n_opt = n_est = 0
+    for q, qu in enumerate(cfg["queries"]):
+        S = O.reach(cfg["layers"], O.star_from_query(qu), relax=(method, rf))
+        perm, crossings = _oracle_in_engine_order(S)
+        for li, (t, (cr, cl_o, cu_o)) in enumerate(zip(S.trace, crossings)):
+            idx, cl, cu = b.get_crossing(q, li)
+            assert np.array_equal(idx, cr), (q, li)
+            sc = max(np.abs(t["lb"]).max(), np.abs(t["ub"]).max())
+            assert np.abs(cl - cl_o).max(initial=0) <= 1e-7 * sc and np.abs(cu - cu_o).max(initial=0) <= 1e-7 * sc
+            n_opt += len(t["optimised"])
+            n_est += len(t["cross_est"])
+        V = b.get_V(q)
+        Vo = S.V[..., perm]
+        assert V.shape == Vo.shape and _rel(V, Vo) < TOL
+        pl, pu = b.get_pred_bounds(q)
+        assert np.array_equal(pl, S.pl[perm[1:] - 1])
+        assert np.abs(pu - S.pu[perm[1:] - 1]).max(initial=0) <= 1e-7 * max(1.0, np.abs(S.pu).max())
+    b.close()
+    model.close()
+    assert n_opt > 0
+    if rf >= 0.5:       # (layers with one or two crossing neurons round a share of 0.75 up to all of them)
+        assert n_opt < n_est, "the share must be a proper part of the crossing neurons for the case to count"
+
+
+def test_relax_star_verdicts_match_oracle(ctx):
+    cfg = make_config("fc5", n_queries=10)
+    model = nn.NN(cfg["layers"], ctx=ctx)
+    opts = {"reachMethod": "relax-star-area", "relaxFactor": 0.5}
+    kind = cfg["queries"][0]["spec"]
+    got = model.verify_robustness_batch(_sets(cfg), opts, [q["target"] + 1 for q in cfg["queries"]], kind)
+    ref = []
+    for qu in cfg["queries"]:
+        S = O.reach(cfg["layers"], O.star_from_query(qu), relax=("relax-star-area", 0.5))
+        G, g = O.robustness_set(S.mat().shape[0], qu["target"], kind)
+        ref.append(O.verify_specification(S, G, g))
+    assert np.array_equal(got, np.array(ref))
+    model.close()

@@ -197,3 +197,36 @@ def test_conv_backends_agree():
     finally:
         O.set_conv_backend("numpy")
     assert a.shape == b.shape and np.abs(a - b).max() <= 1e-13 * np.abs(a).max()
+
+
+def test_relax_star_selection_and_limits():
+    """The 'relax-star-*' step with an LP share (PosLin.m:863-1105, 1541-1646) pinned at its two ends and on a
+    hand-worked selection: relaxFactor = 0 with the static order is reach_star_approx2 (every crossing neuron
+    optimised, ascending order); relaxFactor = 1 optimises nothing and is the LP-free step up to the order of
+    the new predicates; n1 = round((1 - relaxFactor) * count) rounds halves up as MATLAB does."""
+    from nnv_b200.configs import make_config
+    lb2 = np.array([-1.0, -4.0, -2.0, -1.0, -3.0])
+    ub2 = np.array([2.0, 1.0, 2.0, 2.0, 1.0])
+    # areas 1, 2, 2, 1, 1.5 -> descending, ties in index order: 1, 2, 4, 0, 3; n1 = round(0.5 * 5) = 3
+    p21, p22 = O.relax_selection("relax-star-area", 0.5, lb2, ub2)
+    assert list(p21) == [1, 2, 4] and list(p22) == [0, 3]
+    # ranges 3, 5, 4, 3, 4 -> 1, 2, 4, 0, 3; n1 = round(0.75 * 5) = 4
+    p21, p22 = O.relax_selection("relax-star-range", 0.25, lb2, ub2)
+    assert list(p21) == [1, 2, 4, 0] and list(p22) == [3]
+    p21, p22 = O.relax_selection("relax-star-static", 0.5, lb2, ub2)
+    assert list(p21) == [0, 1, 2] and list(p22) == [3, 4]
+    cfg = make_config("fc5", n_queries=3)
+    for qu in cfg["queries"]:
+        S0 = O.star_from_query(qu)
+        A = O.reach(cfg["layers"], S0, lp_bounds=True)
+        B = O.reach(cfg["layers"], S0, relax=("relax-star-static", 0.0))
+        assert A.V.shape == B.V.shape and np.array_equal(A.V, B.V) and np.array_equal(A.pu, B.pu)
+        E = O.reach(cfg["layers"], S0)
+        F = O.reach(cfg["layers"], S0, relax=("relax-star-area", 1.0))
+        assert E.V.shape == F.V.shape
+        for te, tf in zip(E.trace, F.trace):
+            assert np.array_equal(np.sort(tf["cross"]), te["cross"]) and len(tf["optimised"]) == 0
+        # same set, new predicates permuted: the output ranges agree
+        le, ue = O.estimate_ranges(E.mat(), E.pl, E.pu)
+        lf, uf = O.estimate_ranges(F.mat(), F.pl, F.pu)
+        assert np.allclose(le, lf, rtol=1e-12, atol=1e-12) and np.allclose(ue, uf, rtol=1e-12, atol=1e-12)
