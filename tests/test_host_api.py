@@ -77,8 +77,11 @@ def test_reach_option_validation():
     assert v({"reachMethod": "relax-star-area", "relaxFactor": 1})["relaxFactor"] == 1
     with pytest.raises(NotImplementedError):
         v({"reachMethod": "exact-star"})
-    with pytest.raises(NotImplementedError):
-        v({"reachMethod": "relax-star-range", "relaxFactor": 0.5})
+    assert v({"reachMethod": "relax-star-range", "relaxFactor": 0.5})["relaxFactor"] == 0.5
+    with pytest.raises(NotImplementedError):      # upper and lower bounds of different neurons: not built
+        v({"reachMethod": "relax-star-ub", "relaxFactor": 0.5})
+    with pytest.raises(ValueError, match="relax factor"):
+        v({"reachMethod": "relax-star-area", "relaxFactor": 1.5})
     with pytest.raises(TypeError, match="Wrong input set type"):
         nn.NN([nn.ReluLayer()]).reach(np.zeros(3))
 
