@@ -235,6 +235,14 @@ int nnvb_batch_set_star(nnvb_batch* b, int q, int64_t P, const double* V,
                         const double* pl, const double* pu,
                         int64_t m, const double* Cmat, const double* d);
 
+/* The same for n queries q0 .. q0+n-1 in one call (arrays of sets, e.g. the 16 384
+ * attack sets of a brightening study built by ImageStar.m:172-227 in a loop):
+ * set k reads lb + k*stride / ub + k*stride (stride >= H*W*C doubles), or, for
+ * stars that share P and m, V + k*N*(P+1), pl/pu + k*P, Cmat + k*m*P, d + k*m. */
+int nnvb_batch_set_bounds_many(nnvb_batch* b, int q0, int n, const double* lb, const double* ub, int64_t stride);
+int nnvb_batch_set_stars(nnvb_batch* b, int q0, int n, int64_t P, int64_t m, const double* V, const double* pl,
+                         const double* pu, const double* Cmat, const double* d);
+
 /* Copy all staged queries to the device (asynchronous on the context stream). */
 int nnvb_batch_upload(nnvb_batch* b);
 

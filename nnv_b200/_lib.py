@@ -101,6 +101,9 @@ SIGNATURES = {
     "nnvb_batch_set_bounds": (C.c_int, [C.c_void_p, C.c_int, c_double_p, c_double_p]),
     "nnvb_batch_set_star": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, c_double_p, c_double_p, c_double_p,
                                       C.c_int64, c_double_p, c_double_p]),
+    "nnvb_batch_set_bounds_many": (C.c_int, [C.c_void_p, C.c_int, C.c_int, c_double_p, c_double_p, C.c_int64]),
+    "nnvb_batch_set_stars": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_int64, c_double_p, c_double_p,
+                                       c_double_p, c_double_p, c_double_p]),
     "nnvb_batch_upload": (C.c_int, [C.c_void_p]),
     "nnvb_batch_reach": (C.c_int, [C.c_void_p, C.POINTER(Opts)]),
     "nnvb_batch_set_bounds_hook": (C.c_int, [C.c_void_p, BOUNDS_FN, C.c_void_p]),

@@ -879,6 +879,31 @@ int nnvb_batch_set_star(nnvb_batch* b, int q, int64_t P, const double* V, const 
     return NNVB_OK;
 }
 
+// Queries q0 .. q0+n-1 in one call (the per-set entry points cost a foreign-function call each, which bounds the
+// end-to-end rate of batches of thousands of tiny sets).
+int nnvb_batch_set_bounds_many(nnvb_batch* b, int q0, int n, const double* lb, const double* ub, int64_t stride) {
+    NNVB_REQUIRE(b && lb && ub, "nnvb_batch_set_bounds_many: NULL argument");
+    NNVB_REQUIRE(n >= 0 && q0 >= 0 && q0 + n <= b->nq, "nnvb_batch_set_bounds_many: queries %d..%d out of range", q0,
+                 q0 + n - 1);
+    NNVB_REQUIRE(stride >= b->N0, "nnvb_batch_set_bounds_many: stride %lld below the image size", (long long)stride);
+    for (int k = 0; k < n; ++k) NNVB_TRY(nnvb_batch_set_bounds(b, q0 + k, lb + size_t(k) * stride, ub + size_t(k) * stride));
+    return NNVB_OK;
+}
+
+int nnvb_batch_set_stars(nnvb_batch* b, int q0, int n, int64_t P, int64_t m, const double* V, const double* pl,
+                         const double* pu, const double* Cmat, const double* d) {
+    NNVB_REQUIRE(b && V, "nnvb_batch_set_stars: NULL argument");
+    NNVB_REQUIRE(n >= 0 && q0 >= 0 && q0 + n <= b->nq, "nnvb_batch_set_stars: queries %d..%d out of range", q0,
+                 q0 + n - 1);
+    NNVB_REQUIRE(P >= 0 && m >= 0, "nnvb_batch_set_stars: negative size");
+    const size_t vs = size_t(b->N0) * size_t(P + 1);
+    for (int k = 0; k < n; ++k)
+        NNVB_TRY(nnvb_batch_set_star(b, q0 + k, P, V + size_t(k) * vs, pl ? pl + size_t(k) * P : nullptr,
+                                     pu ? pu + size_t(k) * P : nullptr, m, Cmat ? Cmat + size_t(k) * m * P : nullptr,
+                                     d ? d + size_t(k) * m : nullptr));
+    return NNVB_OK;
+}
+
 int nnvb_batch_upload(nnvb_batch* b) {
     NNVB_REQUIRE(b, "nnvb_batch_upload: NULL argument");
     nnvb_ctx* ctx = b->net->ctx;

@@ -230,8 +230,55 @@ class Batch:
         L.check(self.lib.nnvb_batch_create(net.handle, n, C.byref(h)), "nnvb_batch_create")
         self.handle = h
         if queries is not None:
-            for q, qu in enumerate(queries):
-                self.set_query(q, qu)
+            if n < 8 or not self._set_many(queries):
+                for q, qu in enumerate(queries):
+                    self.set_query(q, qu)
+
+    def _set_many(self, queries):
+        """All sets of a uniform list in one call across the ABI (``nnvb_batch_set_bounds_many`` /
+        ``nnvb_batch_set_stars``); False when the list is not uniform (mixed forms, different predicate or
+        constraint counts, shapes that do not fit): the per-set path then reports what is wrong."""
+        n, N = len(queries), self.net.n_in
+        try:
+            if all("lb" in q for q in queries):
+                LB, UB = np.empty((n, N)), np.empty((n, N))
+                for k, q in enumerate(queries):
+                    LB[k] = np.asarray(q["lb"], dtype=np.float64).ravel(order="F")
+                    UB[k] = np.asarray(q["ub"], dtype=np.float64).ravel(order="F")
+                L.check(self.lib.nnvb_batch_set_bounds_many(self.handle, 0, n, _dp(LB), _dp(UB), N),
+                        "nnvb_batch_set_bounds_many")
+                return True
+            if any("lb" in q for q in queries):
+                return False
+            V0 = np.asarray(queries[0]["V"])
+            if V0.size % N:
+                return False
+            P = V0.size // N - 1
+            C0 = queries[0].get("C")
+            m = 0 if C0 is None or np.size(C0) == 0 else int(np.atleast_2d(C0).shape[0])
+            Vs, PL, PU = np.empty((n, N * (P + 1))), np.empty((n, P)), np.empty((n, P))
+            Cs, Ds = np.empty((n, m * P)), np.empty((n, m))
+            for k, q in enumerate(queries):
+                Vk = np.asarray(q["V"], dtype=np.float64)
+                Ck = q.get("C")
+                mk = 0 if Ck is None or np.size(Ck) == 0 else int(np.atleast_2d(Ck).shape[0])
+                if Vk.size != N * (P + 1) or mk != m or np.size(q["pl"]) != P or np.size(q["pu"]) != P:
+                    return False
+                Vs[k] = Vk.ravel(order="F")
+                PL[k] = np.asarray(q["pl"], dtype=np.float64).ravel()
+                PU[k] = np.asarray(q["pu"], dtype=np.float64).ravel()
+                if m:
+                    Ck = np.atleast_2d(np.asarray(Ck, dtype=np.float64))
+                    if Ck.shape[1] != P or np.size(q["d"]) != m:
+                        return False
+                    Cs[k] = Ck.ravel(order="F")
+                    Ds[k] = np.asarray(q["d"], dtype=np.float64).ravel()
+            L.check(self.lib.nnvb_batch_set_stars(self.handle, 0, n, P, m, _dp(Vs), _dp(PL) if P else None,
+                                                  _dp(PU) if P else None, _dp(Cs) if m else None, _dp(Ds) if m else None),
+                    "nnvb_batch_set_stars")
+            return True
+        except (ValueError, TypeError, KeyError):
+            return False
 
     def close(self):
         if getattr(self, "handle", None):

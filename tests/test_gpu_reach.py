@@ -540,3 +540,29 @@ def test_halfspace_row_with_zero_margin_is_left_to_the_lp(ctx):
         assert O.is_empty_set(C, d, S.pl, S.pu) == want
     b.close()
     net.close()
+
+
+@pytest.mark.parametrize("name", ["cnn28", "bright28"])
+def test_bulk_set_entry_points_equal_the_per_set_ones(ctx, name):
+    """A uniform list of eight or more sets crosses the ABI in one call (nnvb_batch_set_bounds_many for
+    ImageStar(lb, ub) lists, nnvb_batch_set_stars for stars that share their predicate and constraint counts);
+    the batch must be the one the per-set calls build."""
+    cfg = make_config(name, n_queries=9, small=True)
+    net = Network(ctx, cfg["layers"], cfg["in_shape"])
+    bulk = Batch(net, cfg["queries"])                  # nine sets: the bulk path
+    one = Batch(net, n_queries=9)
+    for q, qu in enumerate(cfg["queries"]):
+        one.set_query(q, qu)
+    for b in (bulk, one):
+        b.upload()
+        b.reach()
+    res = {}
+    for key, b in (("bulk", bulk), ("one", one)):
+        b.reach()                                       # results belong to the batch reached last
+        res[key] = [(b.get_V(q), b.get_pred_bounds(q), b.get_ranges(q)) for q in range(9)]
+    for (V, (pl, pu), (lb, ub)), (V1, (pl1, pu1), (lb1, ub1)) in zip(res["bulk"], res["one"]):
+        assert np.array_equal(V, V1) and np.array_equal(pl, pl1) and np.array_equal(pu, pu1)
+        assert np.array_equal(lb, lb1) and np.array_equal(ub, ub1)
+    bulk.close()
+    one.close()
+    net.close()
