@@ -1147,10 +1147,12 @@ int launch_estimate_ranges(cudaStream_t st, const ReluWork& w, int64_t* launches
         win_rank_kernel<<<gcol, 256, 0, st>>>(w.win, w.nq, w.box, w.col_q, bins, w.win_seg, tmp, perm);
         // strip height: a thread per (pixel, channel) where the channels allow it
         // the window-only copies hold a pixel's channels contiguously: short strips read them as well as long
-        // ones and stage fewer candidates per block (4 pixels measured best: 1.49 ms against 1.61 with 8 and
-        // 2.27 with 16 for the bound reduction of the 32x32x3 CNN at 16 images per step)
+        // ones and stage fewer candidates per block; a strip taller than the windows spends most of its
+        // (row, candidate) pairs outside the candidate's window.  Measured on the 32x32x3 CNN (bound reduction of a
+        // 128-image step): strips of 256 / C pixels (one row per thread) 8.8 ms, 128 / C (half the threads idle on
+        // 32-channel layers) 9.3 ms, 512 / C 10.5 ms
         const int TH = w.win_pack != nullptr
-                           ? std::min(rw_strip_height(w.img_h, w.img_c), std::max(4, 128 / std::max(1, w.img_c)))
+                           ? std::min(rw_strip_height(w.img_h, w.img_c), std::max(4, 256 / std::max(1, w.img_c)))
                            : rw_strip_height(w.img_h, w.img_c);
         if (int64_t(TH) * w.img_c > int64_t(RW_THREADS) * RW_RPT) {
             set_error("range_windows: %d channels exceed the rows a block owns", w.img_c);
