@@ -172,8 +172,11 @@ constexpr int RW_THREADS = 256;
 constexpr int RW_RPT = 4;
 constexpr int RW_MLP = 8;            // window loads a thread keeps in flight
 constexpr int RW_MAX_RUNS = MAX_WIN_COHORTS * MAX_WIN_EXTENT;
+// Four blocks per SM: at 64 registers the compiler keeps a few values of the prologue on the stack (56 bytes, none
+// inside the candidate loop); 80 registers without any spill (three blocks per SM) measured 7 % slower: the kernel
+// lives on loads in flight.
 template <bool PACKED>
-__global__ void __launch_bounds__(RW_THREADS)
+__global__ void __launch_bounds__(RW_THREADS, 4)
 range_windows_kernel(int64_t N, int64_t ld, const double* __restrict__ V, const double* __restrict__ pl,
                      const double* __restrict__ pu, const int4* __restrict__ box, int H, int W, int C, int TH, int nq,
                      WinCohorts wc, const int32_t* __restrict__ bins, const int32_t* __restrict__ perm,
