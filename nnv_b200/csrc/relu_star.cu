@@ -172,7 +172,7 @@ constexpr int RW_THREADS = 256;
 constexpr int RW_RPT = 4;
 constexpr int RW_MLP = 8;            // window loads a thread keeps in flight
 constexpr int RW_MAX_RUNS = MAX_WIN_COHORTS * MAX_WIN_EXTENT;
-// Four blocks per SM: at 64 registers the compiler keeps a few values of the prologue on the stack (56 bytes, none
+// Four blocks per SM: at 64 registers the compiler keeps a few values of the prologue on the stack (about 60 bytes, none
 // inside the candidate loop); 80 registers without any spill (three blocks per SM) measured 7 % slower: the kernel
 // lives on loads in flight.
 template <bool PACKED>
