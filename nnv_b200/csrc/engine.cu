@@ -2124,8 +2124,13 @@ constexpr double EMPTY_GUARD = 1e-6;
 // Test halfspace rows against the reached sets: pair p = (query pair_q[p], row G[p], offset g[p]).
 // status: EMPTY when the box minimum of the row is positive; NONEMPTY when the greedy witness
 // point lies inside the halfspace (needs the layer bounds kept during reach); else UNDECIDED.
+// one_witness_per_query: the caller only needs to know whether SOME row of a query is non-empty (the robustness
+// verdict: one reachable halfspace makes the query "unknown"), so the witness / back-substitution pass first runs
+// on each query's most promising row (smallest box minimum) and only the queries it leaves open get their other
+// rows tested.  Verdicts are the same; rows of a query that is already decided stay UNDECIDED.
 int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vector<double>& G,
-               const std::vector<double>& g, std::vector<double>& margin, std::vector<int>& status) {
+               const std::vector<double>& g, std::vector<double>& margin, std::vector<int>& status,
+               bool one_witness_per_query = false) {
     nnvb_ctx* ctx = b->net->ctx;
     cudaStream_t st = ctx->stream;
     const int n = (int)pair_q.size();
@@ -2183,6 +2188,7 @@ int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vec
     int64_t max_ld = b->ld0;
     for (const Layer& L : b->net->layers) max_ld = std::max(max_ld, lead_dim(L.Ho * L.Wo * L.Co));
     const int64_t chunk_cap = std::max<int64_t>(1, (int64_t(1) << 31) / (max_ld * 8));
+    auto run = [&](const std::vector<int>& open) -> int {
     for (size_t c0 = 0; c0 < open.size(); c0 += chunk_cap) {
         const int m = (int)std::min<size_t>(chunk_cap, open.size() - c0);
         std::vector<int32_t> pq(m);
@@ -2264,6 +2270,19 @@ int test_pairs(nnvb_batch* b, const std::vector<int32_t>& pair_q, const std::vec
         }
     }
     return NNVB_OK;
+    };
+    if (!one_witness_per_query) return run(open);
+    std::vector<int> best(b->nq, -1), first, rest;
+    for (int p : open) {
+        int& bp = best[pair_q[p]];
+        if (bp < 0 || margin[p] < margin[bp]) bp = p;
+    }
+    for (int q = 0; q < b->nq; ++q)
+        if (best[q] >= 0) first.push_back(best[q]);
+    NNVB_TRY(run(first));
+    for (int p : open)
+        if (p != best[pair_q[p]] && status[best[pair_q[p]]] != NNVB_VERDICT_NONEMPTY) rest.push_back(p);
+    return run(rest);
 }
 
 }  // namespace
@@ -2682,7 +2701,7 @@ int nnvb_batch_verify_robust(nnvb_batch* b, const int32_t* target, int kind, int
         }
     }
     std::vector<int> st;
-    NNVB_TRY(test_pairs(b, pq, G, g, margin, st));
+    NNVB_TRY(test_pairs(b, pq, G, g, margin, st, true));
     for (int q = 0; q < nq; ++q) {
         bool all_empty = true, any_nonempty = false;
         for (int h = 0; h < nh; ++h) {
