@@ -470,9 +470,22 @@ avgpool_compact_2x2_kernel(PoolGeom g, RowMask mask, const int4* __restrict__ bo
     const int ohl = pos % wh_out, owl = pos / wh_out;
     const bool cf = mask.state_cf != nullptr;
     const int64_t plane = int64_t(g.H) * g.W;
+    // the window box and the query of the NEXT column are requested while this column is summed: they head the
+    // dependent chain box -> addresses -> values, which otherwise costs a memory round trip per column
+    int4 bx_n = make_int4(0, 0, 0, 0);
+    int q_n = 0;
+    if (int64_t(blockIdx.y) < ncols) {
+        bx_n = box[col_base + blockIdx.y];
+        if (mask.state != nullptr && col_base + blockIdx.y < mask.ncols) q_n = mask.col_q[col_base + blockIdx.y];
+    }
     for (int64_t jj = blockIdx.y; jj < ncols; jj += gridDim.y) {
         const int64_t j = col_base + jj;
-        const int4 bx = box[j];
+        const int4 bx = bx_n;
+        const int q_j = q_n;
+        if (jj + gridDim.y < ncols) {
+            bx_n = box[j + gridDim.y];
+            if (mask.state != nullptr && j + gridDim.y < mask.ncols) q_n = mask.col_q[j + gridDim.y];
+        }
         const int a = bx.x - 1, b2 = bx.y - 1;
         const int oh = (a >= 0 ? (a + 1) >> 1 : -((-a) >> 1)) + ohl;
         const int ow = (b2 >= 0 ? (b2 + 1) >> 1 : -((-b2) >> 1)) + owl;
@@ -481,8 +494,8 @@ avgpool_compact_2x2_kernel(PoolGeom g, RowMask mask, const int4* __restrict__ bo
             const int h0 = 2 * oh, w0 = 2 * ow;
             const double* src = Cin_ + jj * stride_in + c;
             const bool masked = mask.state != nullptr && j < mask.ncols;
-            const uint8_t* st = masked ? (cf ? mask.state_cf + mask.col_q[j] * mask.N + c
-                                             : mask.state + mask.col_q[j] * mask.N + c * plane) : nullptr;
+            const uint8_t* st = masked ? (cf ? mask.state_cf + q_j * mask.N + c
+                                             : mask.state + q_j * mask.N + c * plane) : nullptr;
             double2 v[4];
             unsigned sbits[4];
             bool in[4];
