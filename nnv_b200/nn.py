@@ -438,6 +438,24 @@ def _matlab_round(x):
     return int(np.floor(x + 0.5))
 
 
+def relax_select(method, relax_factor, l_est, u_est, rng=None):
+    """Positions (within the crossing list) of the n1 = round((1 - relaxFactor) * count) neurons whose ranges are
+    optimised (PosLin.m:929-936, 1044-1052, 1483-1491, 1599-1607; MATLAB's sort is stable and its round takes
+    halves away from zero)."""
+    l_est, u_est = np.asarray(l_est, dtype=np.float64), np.asarray(u_est, dtype=np.float64)
+    k = len(l_est)
+    n1 = _matlab_round((1.0 - relax_factor) * k)
+    if method == "relax-star-area":
+        return np.argsort(-(0.5 * np.abs(u_est) * np.abs(l_est)), kind="stable")[:n1]
+    if method == "relax-star-range":
+        return np.argsort(-(u_est - l_est), kind="stable")[:n1]
+    if method == "relax-star-static":
+        return np.arange(n1)
+    if method == "relax-star-random":
+        return (rng or np.random.default_rng(0)).permutation(k)[:n1]
+    raise ValueError(method)
+
+
 def relax_bounds_hook(method, relax_factor, rng=None):
     """Bounds hook of the 'relax-star-*' methods with relaxFactor < 1 (PosLin.reach_relaxed_star_area / _range /
     _static / _random, PosLin.m:986-1105, 863-984, 1541-1646, 1425-1539): of the neurons the estimated ranges call
@@ -453,15 +471,8 @@ def relax_bounds_hook(method, relax_factor, rng=None):
             k = len(idx)
             if k == 0:
                 continue
-            n1 = _matlab_round((1.0 - relax_factor) * k)
-            if method == "relax-star-area":
-                sel = np.argsort(-(0.5 * np.abs(u_est) * np.abs(l_est)), kind="stable")[:n1]
-            elif method == "relax-star-range":
-                sel = np.argsort(-(u_est - l_est), kind="stable")[:n1]
-            elif method == "relax-star-static":
-                sel = np.arange(n1)
-            else:                                   # relax-star-random
-                sel = rng.permutation(k)[:n1]
+            sel = relax_select(method, relax_factor, l_est, u_est, rng)
+            n1 = len(sel)
             xmin = np.array(l_est, dtype=np.float64, copy=True)
             xmax = np.array(u_est, dtype=np.float64, copy=True)
             if n1 > 0:

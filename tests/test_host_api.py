@@ -158,3 +158,18 @@ def test_image_input_layer_normalisations_match_the_oracle():
         assert np.abs(by_V.V - ref.V).max() <= 1e-12 * np.abs(ref.V).max()
     with pytest.raises(ValueError):
         nn.ImageInputLayer(shape, "zerophase")
+
+
+def test_relax_star_selection_matches_the_oracle():
+    """The host hook and the oracle pick the same neurons for LP-optimised ranges (ties, rounding of halves)."""
+    from oracle import nnv_oracle as O
+    rng = np.random.default_rng(5)
+    for k in (1, 2, 5, 8, 33):
+        lb = -np.round(rng.uniform(0.1, 3.0, k), 1)         # rounded: ties occur
+        ub = np.round(rng.uniform(0.1, 3.0, k), 1)
+        for method in ("relax-star-area", "relax-star-range", "relax-star-static"):
+            for rf in (0.0, 0.25, 0.5, 0.75, 1.0):
+                sel = nn.relax_select(method, rf, lb, ub)
+                p21, p22 = O.relax_selection(method, rf, lb, ub)
+                assert list(sel) == list(p21), (k, method, rf)
+                assert sorted(list(p21) + list(p22)) == list(range(k))
