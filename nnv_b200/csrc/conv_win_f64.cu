@@ -57,8 +57,8 @@ struct ConvWinParams {
     // persistent form: tiles = column groups x patch columns x row blocks x output-channel tiles, channel tiles fastest
     int n_ytiles;
     int64_t n_flat;
-    int stages;                     // warp-specialised form: pipeline depth
-    int use_bits;                   // warp-specialised form, at most 64 input channels: the row states of a table entry
+    int stages;                     // persistent form: pipeline depth
+    int use_bits;                   // persistent form, at most 64 input channels: the row states of a table entry
                                     // are gathered once into a 64-bit word
 };
 
@@ -423,328 +423,6 @@ __device__ __forceinline__ void cp_async4(void* smem, const void* gmem, int src_
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(src_bytes));
 }
 
-// Persistent form of the compact-input, compact-output case (the hot one): one block per SM walks the tiles with
-// stride gridDim.x and treats (tile, channel chunk) pairs as ONE pipelined sequence, so the start-up of a tile
-// (window boxes, flags, fetch table, first stage) runs underneath the products of the tile before it instead of in
-// front of an idle DMMA pipe.  While tile t is multiplied:
-//   chunk 0: the boxes and query numbers of tile t+1's columns are requested (async copies, second buffer)
-//   chunk 1: every warp derives tile t+1's flags from them and the block builds its fetch table (second buffer)
-//   last chunk: the first stage of tile t+1 is requested
-// Each step is separated from its reader by the block barrier of a later chunk, which is why the form needs three
-// chunks per tile at least.  Results leave straight from the accumulators (16-byte stores), so shared memory is
-// never reused as an output staging area.
-template <int KH, int WARPS_M, int WARPS_N, int NROWS>
-__global__ void __launch_bounds__(CW_THREADS, 1)
-conv_win_persist_kernel(const ConvWinParams p, const double* __restrict__ Wg, const ChanAffine bn, const RowMask mask,
-                        const int4* __restrict__ box, int64_t col_base, int64_t ncols) {
-    static_assert(WARPS_M * WARPS_N * 32 == CW_THREADS, "16 warps");
-    constexpr int BN = WARPS_N * 8;
-    constexpr int NI = CW_TH + KH - 1;
-    constexpr int NW = CW_THREADS / 32;
-
-    extern __shared__ __align__(16) double smem[];
-    double* in_s = smem;                                        // [2][in_stage]
-    double* wts = smem + 2 * p.in_stage;                        // [2][w_stage]
-    int* tab = reinterpret_cast<int*>(smem + p.tail);           // [2 buffers][goff, soff, moff][tab_cap]
-    int4* s_box = reinterpret_cast<int4*>(tab + 6 * p.tab_cap); // [2][ncol]
-    int* s_q = reinterpret_cast<int*>(s_box + 2 * p.ncol);      // [2][ncol] query of the column
-    unsigned* s_rows = reinterpret_cast<unsigned*>(s_q + 2 * p.ncol);   // [2][NW] patch rows on the image, per warp
-    int* s_on = reinterpret_cast<int*>(s_rows + 2 * NW);        // [2] some column of the tile has its patch column on the image
-    __shared__ __align__(8) uint64_t w_bar[2];
-
-    const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const int warp = tid >> 5;
-    const int wm = warp % WARPS_M;
-    const int wn = warp / WARPS_M;
-    const int g = lane >> 2;
-    const int t = lane & 3;
-    const int H = p.g.H, W = p.g.W;
-    const int KW = p.g.kw;
-    const int ext_h = KH - 1, ext_w = KW - 1;
-    const int per = p.ww_out * p.n_ohb;
-
-    if (tid == 0) {
-        mbar_init(&w_bar[0], 1);
-        mbar_init(&w_bar[1], 1);
-        mbar_init_fence();
-    }
-
-    // tile -> (output-channel tile, column group, patch column, row block)
-    struct Tile { int n_tile, owl, ohb; int64_t j0; };
-    auto decode = [&](int tile) {        // the tile count fits 31 bits (checked at launch)
-        Tile x;
-        x.n_tile = tile % p.n_ytiles;
-        const int r = tile / p.n_ytiles;
-        x.j0 = int64_t(r / per) * p.ncol;
-        const int rem = r % per;
-        x.owl = rem / p.n_ohb;
-        x.ohb = rem % p.n_ohb;
-        return x;
-    };
-    auto i_lo_of = [&](int ohb) { return NROWS > 0 ? KH - 1 : max(0, ext_h - ohb * CW_TH); };
-    auto i_hi_of = [&](int ohb) { return NROWS > 0 ? KH - 1 + NROWS : min(NI, p.wh_in - (ohb * CW_TH - ext_h)); };
-    auto kw_lo_of = [&](int owl) { return max(0, ext_w - owl); };
-    auto kw_hi_of = [&](int owl) { return min(KW, p.ww_in + ext_w - owl); };
-
-    // step A: boxes and query numbers of a tile's columns into buffer b (joins the caller's copy group)
-    auto prep_boxes = [&](const Tile& x, int b) {
-        if (tid < p.ncol) {
-            const bool ok = x.j0 + tid < ncols;
-            cp_async16(&s_box[b * p.ncol + tid], ok ? box + col_base + x.j0 + tid : box, ok ? 16 : 0);
-        } else if (tid < 2 * p.ncol) {
-            const int c = tid - p.ncol;
-            const int64_t gj = col_base + x.j0 + c;
-            const bool ok = mask.state != nullptr && x.j0 + c < ncols && gj < mask.ncols;
-            cp_async4(&s_q[b * p.ncol + c], ok ? static_cast<const void*>(mask.col_q + gj) : static_cast<const void*>(box),
-                      ok ? 4 : 0);
-        }
-    };
-    // step B: flags and fetch table of the tile whose boxes are in buffer b
-    auto prep_table = [&](const Tile& x, int b) {
-        const int th_cnt = min(CW_TH, p.wh_out - x.ohb * CW_TH);
-        // Patches near the image border hang over it: a tile none of whose columns has its patch column on the
-        // image has nothing to do, and a warp skips the patch rows that are off the image for its 16 columns.
-        unsigned m = 0u;
-        bool any_on = false;
-        for (int c = lane; c < p.ncol; c += 32) {
-            if (x.j0 + c >= ncols) continue;
-            const int4 bx = s_box[b * p.ncol + c];
-            const int ow = bx.y + p.g.pad_l - ext_w + x.owl;
-            if (ow < 0 || ow >= p.g.Wo) continue;
-            any_on = true;
-            if ((c >> 4) != wm) continue;
-            for (int o = 0; o < th_cnt; ++o) {
-                const int oh = bx.x + p.g.pad_t - ext_h + x.ohb * CW_TH + o;
-                if (oh >= 0 && oh < p.g.Ho) m |= 1u << o;
-            }
-        }
-        m = __reduce_or_sync(0xffffffffu, m);
-        const bool on = __any_sync(0xffffffffu, any_on);
-        if (lane == 0) s_rows[b * NW + warp] = m;
-        if (tid == 0) s_on[b] = on ? 1 : 0;
-        if (!on) return;
-        const int ih_base = x.ohb * CW_TH - ext_h;
-        const int i_lo = i_lo_of(x.ohb), n_i = i_hi_of(x.ohb) - i_lo;
-        const int kw_lo = kw_lo_of(x.owl), n_kw = kw_hi_of(x.owl) - kw_lo;
-        const int n_e = p.ncol * n_kw * n_i;
-        int* goff = tab + b * 3 * p.tab_cap;
-        int* soff = goff + p.tab_cap;
-        int* moff = soff + p.tab_cap;
-        // entry e = (origin column, input row, column), column fastest: neighbouring lanes of the fetch write
-        // neighbouring 64-byte slots of the staging row
-        for (int e = tid; e < n_e; e += CW_THREADS) {
-            const int col = e % p.ncol;
-            const int e2 = e / p.ncol;
-            const int i_idx = e2 % n_i;
-            const int kwi = kw_lo + e2 / n_i;
-            const int4 bx = s_box[b * p.ncol + col];
-            const int hi = bx.x + ih_base + i_lo + i_idx;
-            const int wi = bx.y + x.owl + kwi - ext_w;
-            int off = -1, mo = -1;
-            if (hi >= 0 && hi < H && wi >= 0 && wi < W && x.j0 + col < ncols) {
-                off = int(col * p.cin_stride) + ((wi - bx.y) * p.wh_in + (hi - bx.x)) * p.g.Cin;
-                if (mask.state != nullptr && col_base + x.j0 + col < mask.ncols) {
-                    const int q_off = int(s_q[b * p.ncol + col] * mask.N);
-                    mo = mask.state_cf != nullptr ? q_off + (hi + H * wi) * p.g.Cin : q_off + hi + H * wi;
-                }
-            }
-            goff[e] = off;
-            moff[e] = mo;
-            soff[e] = (((kwi * p.ni_s + i_idx) * p.ncol + col) * KC) | (((col >> 1) & 1) << 30);
-        }
-    };
-
-    const bool cf = mask.state_cf != nullptr;
-    const bool pair_ok = cf && (p.g.Cin % 2 == 0) && (mask.N % 2 == 0);
-    const int hw_in = H * W;
-    // one stage of a tile: the chunk's weights by one bulk copy (a contiguous block, counted on the stage's
-    // barrier), the inputs by 16-byte copies, one channel pair of one (column, input position) per thread and round
-    auto load_stage = [&](int stage, const Tile& x, int b, int chunk) {
-        if (tid == 0) {
-            async_proxy_fence();
-            mbar_expect_bytes(&w_bar[stage], uint32_t(p.w_stage) * 8u);
-            bulk_copy_g2s(wts + stage * p.w_stage, Wg + (int64_t(x.n_tile) * p.n_chunks + chunk) * p.w_stage,
-                          uint32_t(p.w_stage) * 8u, &w_bar[stage]);
-        }
-        if (!s_on[b]) return;
-        const int n_e = p.ncol * (kw_hi_of(x.owl) - kw_lo_of(x.owl)) * (i_hi_of(x.ohb) - i_lo_of(x.ohb));
-        const int* goff = tab + b * 3 * p.tab_cap;
-        const int* soff = goff + p.tab_cap;
-        const int* moff = soff + p.tab_cap;
-        double* is = in_s + stage * p.in_stage;
-        const int c0 = chunk * KC;
-        const double* src_b = p.cin + x.j0 * p.cin_stride + c0;
-        for (int it = tid; it < 4 * n_e; it += CW_THREADS) {
-            const int e = it >> 2, u0 = 2 * (it & 3);
-            const int off = goff[e], so_raw = soff[e], mo = moff[e];
-            const int so = so_raw & 0x3fffffff;
-            const int sw = (so_raw >> 30) & 1 ? 4 : 0;
-            bool ok0 = off >= 0 && c0 + u0 < p.g.Cin, ok1 = off >= 0 && c0 + u0 + 1 < p.g.Cin;
-            if (mo >= 0 && (ok0 || ok1)) {                   // rows the ReLU step cleared read as zero
-                if (pair_ok) {
-                    const unsigned sv = *reinterpret_cast<const unsigned short*>(mask.state_cf + mo + c0 + u0);
-                    ok0 = ok0 && (sv & 0xffu) == 0;
-                    ok1 = ok1 && (sv >> 8) == 0;
-                } else {
-                    if (ok0) ok0 = (cf ? mask.state_cf[mo + c0 + u0] : mask.state[mo + int64_t(c0 + u0) * hw_in]) == 0;
-                    if (ok1) ok1 = (cf ? mask.state_cf[mo + c0 + u0 + 1] : mask.state[mo + int64_t(c0 + u0 + 1) * hw_in]) == 0;
-                }
-            }
-            double* d2 = is + so + (u0 ^ sw);
-            if (ok0 && ok1) {
-                cp_async16(d2, src_b + off + u0, 16);
-            } else {
-                cp_async8(d2, ok0 ? src_b + off + u0 : p.cin, ok0 ? 8 : 0);
-                cp_async8(d2 + 1, ok1 ? src_b + off + u0 + 1 : p.cin, ok1 ? 8 : 0);
-            }
-        }
-    };
-
-    double acc[CW_TH][4];
-#pragma unroll
-    for (int o = 0; o < CW_TH; ++o)
-#pragma unroll
-        for (int r = 0; r < 4; ++r) acc[o][r] = 0.0;
-
-    // the tile being multiplied
-    int tile = blockIdx.x;
-    Tile cx = decode(tile), nx = cx;
-    int buf = 0;
-    int owl = 0, ohb = 0, kw_lo = 0, kw_hi = 0, i_lo = 0, i_hi = 0;
-    unsigned rows_on = 0u;
-    bool all_rows = false;
-    auto enter_tile = [&]() {           // reads what prep_table left in buffer buf (a block barrier lies between)
-        owl = cx.owl; ohb = cx.ohb;
-        kw_lo = kw_lo_of(owl); kw_hi = kw_hi_of(owl);
-        i_lo = i_lo_of(ohb); i_hi = i_hi_of(ohb);
-        rows_on = s_on[buf] ? s_rows[buf * NW + warp] : 0u;
-        if (rows_on == 0u) kw_hi = kw_lo;         // nothing of this warp's columns is on the image
-        const unsigned row_bits = (1u << min(CW_TH, p.wh_out - ohb * CW_TH)) - 1u;
-        all_rows = (rows_on & row_bits) == row_bits;
-    };
-
-    // FULL: every patch row of the tile is on the image for this warp's columns (the common case): the products
-    // carry no per-row test, which would otherwise put a branch around every DMMA
-    auto compute = [&](int stage, auto full_rows) {
-        constexpr bool FULL = decltype(full_rows)::value;
-        // row = column g (and g + 8), k = channel t (and t + 4); the channel index is XORed with 4 for every other
-        // column pair (the staging swizzle)
-        const int sw = ((g >> 1) & 1) * 4;
-        const double* is = in_s + stage * p.in_stage + (wm * 16 + g) * KC;
-        const int RSr = p.ncol * KC;                                                // stride between staged input rows
-        constexpr int o1 = 8 * KC;
-        const int o0 = t ^ sw, o2 = (o0 ^ 4) - o0;
-        const double* ws = wts + stage * p.w_stage + t * p.CS + wn * 8 + g;         // k = channel t, n = g
-        for (int kwi = kw_lo; kwi < kw_hi; ++kwi) {
-            double bf[KH][2];
-#pragma unroll
-            for (int khi = 0; khi < KH; ++khi) {
-                const double* wt = ws + (khi + KH * kwi) * (KC * p.CS);     // tap index: kh fastest
-                bf[khi][0] = wt[0];
-                bf[khi][1] = wt[4 * p.CS];
-            }
-            const double* a_col = is + (kwi * p.ni_s - i_lo) * RSr + o0;
-#pragma unroll
-            for (int i = 0; i < NI; ++i) {
-                if (i < i_lo || i >= i_hi) continue;
-                const double* a = a_col + i * RSr;
-                double af[4];
-                af[0] = a[0];
-                af[1] = a[o1];
-                af[2] = a[o2];
-                af[3] = a[o2 + o1];
-                // input row i meets output row i - khi through tap khi
-#pragma unroll
-                for (int khi = 0; khi < KH; ++khi) {
-                    const int o = i - khi;
-                    if (o >= 0 && o < CW_TH) {
-                        if (FULL || ((rows_on >> o) & 1u)) dmma_16x8x8(acc[o], af, bf[khi]);
-                    }
-                }
-            }
-        }
-    };
-
-    // results of the finished tile: a lane holds two neighbouring channels of a (column, patch row), so its store is
-    // 16 bytes; the four lanes of a quad fill the 64 bytes of an 8-channel group of the channel-fastest output
-    auto store_tile = [&]() {
-        const Tile& x = cx;
-        const int th_cnt = min(CW_TH, p.wh_out - x.ohb * CW_TH);
-        const int co = x.n_tile * BN + wn * 8 + 2 * t;
-        if (s_on[buf] && co < p.g.Cout) {
-            const bool has_bn = bn.rden != nullptr;
-            const double r0 = has_bn ? bn.rden[co] : 1.0, s0 = has_bn ? bn.scale[co] : 1.0;
-            const double r1 = has_bn ? bn.rden[co + 1] : 1.0, s1 = has_bn ? bn.scale[co + 1] : 1.0;
-            const int64_t ca = x.j0 + wm * 16 + g, cb = ca + 8;
-            double* da = p.pack + ca * p.pack_stride + int64_t(x.owl * p.wh_out + x.ohb * CW_TH) * p.g.Cout + co;
-            double* db = da + 8 * p.pack_stride;
-#pragma unroll
-            for (int o = 0; o < CW_TH; ++o) {
-                if (o >= th_cnt) break;
-                if (ca < ncols)
-                    *reinterpret_cast<double2*>(da + int64_t(o) * p.g.Cout) =
-                        make_double2((acc[o][0] * r0) * s0, (acc[o][1] * r1) * s1);
-                if (cb < ncols)
-                    *reinterpret_cast<double2*>(db + int64_t(o) * p.g.Cout) =
-                        make_double2((acc[o][2] * r0) * s0, (acc[o][3] * r1) * s1);
-            }
-        }
-#pragma unroll
-        for (int o = 0; o < CW_TH; ++o)
-#pragma unroll
-            for (int r = 0; r < 4; ++r) acc[o][r] = 0.0;
-    };
-
-    // start-up of the block's first tile: the only one that is not hidden
-    prep_boxes(cx, 0);
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();                    // also publishes the barriers' initialisation
-    prep_table(cx, 0);
-    __syncthreads();
-    enter_tile();
-    load_stage(0, cx, 0, 0);
-    cp_async_commit();
-
-    const int NCH = p.n_chunks;
-    // Half of the warps fetch the next stage before their products, the other half after: while one half
-    // waits on its table and row-state loads the other keeps the DMMA pipe busy.
-    const bool load_first = (warp >> 3) == 0;
-    unsigned k = 0;                     // position in the (tile, chunk) sequence: stage k % 2, on its (k / 2)-th use
-    for (;;) {
-        const int64_t next = int64_t(tile) + gridDim.x;
-        const bool has_next = next < p.n_flat;
-        if (has_next) nx = decode(int(next));
-        for (int ch = 0; ch < NCH; ++ch, ++k) {
-            const int stage = k & 1;
-            cp_async_wait<0>();
-            mbar_wait(&w_bar[stage], (k >> 1) & 1);
-            __syncthreads();
-            if (has_next && ch == 0) prep_boxes(nx, buf ^ 1);
-            if (has_next && ch == 1) prep_table(nx, buf ^ 1);
-            const bool last = ch + 1 == NCH;
-            if (load_first) {
-                if (!last) load_stage(stage ^ 1, cx, buf, ch + 1);
-                else if (has_next) load_stage(stage ^ 1, nx, buf ^ 1, 0);
-            }
-            if (all_rows) compute(stage, std::true_type{});
-            else compute(stage, std::false_type{});
-            if (!load_first) {
-                if (!last) load_stage(stage ^ 1, cx, buf, ch + 1);
-                else if (has_next) load_stage(stage ^ 1, nx, buf ^ 1, 0);
-            }
-            cp_async_commit();
-        }
-        store_tile();
-        if (!has_next) break;
-        tile = int(next);
-        cx = nx;
-        buf ^= 1;
-        enter_tile();
-    }
-    cp_async_wait<0>();
-}
 template <int KH, int WARPS_M, int WARPS_N, bool CIN, int NROWS = 0>
 int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn, const RowMask& mask,
                const ColWindows& win, int wh_in, int ww_in, int64_t col_base, const double* Vin, int64_t ld_in,
@@ -798,13 +476,20 @@ int launch_cfg(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const C
 }
 
 
-// Warp-specialised form of the persistent kernel.  Sixteen consumer warps (four warpgroups) only multiply: they wait
-// for a stage to be full, run its products, and hand the stage back.  One producer warpgroup (four warps) does
-// everything else: window boxes, flags and fetch table of the next tile, the input copies and the weight copy of
-// every stage.  Stages are handed over through mbarriers (full: the producer's copies have landed; empty: all
-// consumer warps are done with the stage), so there is no block-wide barrier in the main loop and a consumer warp
-// never waits for another consumer warp.  The producers give most of their registers to the consumers.
-// Every wait is bounded; a wait that runs out sets *err and lets the kernel finish.
+// Persistent, warp-specialised form of the compact-input, compact-output case (the hot one).  One block per SM walks
+// the tiles with stride gridDim.x and treats (tile, channel chunk) pairs as ONE pipelined sequence, so the start-up
+// of a tile (window boxes, flags, fetch table, first stage) runs underneath the products of the tile before it
+// instead of in front of an idle DMMA pipe.  Sixteen consumer warps (four warpgroups) only multiply: they wait for a
+// stage to be full, run its products, and hand the stage back; results leave straight from the accumulators
+// (16-byte stores), so shared memory is never reused as an output staging area.  One producer warpgroup (four
+// warps) does everything else: while tile t is multiplied it requests the boxes and query numbers of tile t+1's
+// columns (chunk 0), derives tile t+1's flags and fetch table from them (chunk 1), and fills every stage — the input
+// copies and the weight copy.  Stages are handed over through mbarriers (full: the producer's copies have landed;
+// empty: all consumer warps are done with the stage), so there is no block-wide barrier in the main loop and a
+// consumer warp never waits for another consumer warp.  The producers give most of their registers to the
+// consumers.  The form needs three chunks per tile at least (the table of tile t+1 is built during chunk 1 of tile
+// t and first used for its last chunk).  Every wait is bounded; a wait that runs out sets *err and lets the kernel
+// finish.
 constexpr int WS_CONSUMER_WARPS = 16;
 constexpr int WS_PRODUCERS = 128;                                   // threads of the producer warpgroup
 constexpr int WS_THREADS = WS_CONSUMER_WARPS * 32 + WS_PRODUCERS;   // 640
@@ -1201,7 +886,7 @@ int sm_count_of_current_device() {
 // set by the warp-specialised kernel when one of its bounded waits ran out (read by conv_win_wait_timeouts)
 __device__ int g_ws_wait_timeout = 0;
 
-template <int KH, int WARPS_M, int WARPS_N, int NROWS, bool WS = true>
+template <int KH, int WARPS_M, int WARPS_N, int NROWS>
 int launch_persist(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, const ChanAffine& bn, const RowMask& mask,
                    const ColWindows& win, int wh_in, int ww_in, int64_t col_base, int64_t ncols, double* pack,
                    const double* cin, int64_t cin_stride, bool* done) {
@@ -1227,35 +912,25 @@ int launch_persist(cudaStream_t st, const ConvGeom& g, const ConvWeights& w, con
     p.w_stage = g.kh * g.kw * KC * p.CS;
     p.n_chunks = w.n_chunks;
     p.tab_cap = p.ncol * g.kw * p.ni_s;
-    p.stages = 2;
-    p.tail = 2 * (p.in_stage + p.w_stage);
     p.n_ytiles = w.n_tiles;
     p.n_flat = ceil_div(ncols, p.ncol) * p.ww_out * p.n_ohb * w.n_tiles;
     if (p.n_flat >= (int64_t(1) << 31)) return NNVB_OK;
     p.use_bits = g.Cin <= 64 && (mask.state == nullptr || mask.state_cf != nullptr);
-    // (both forms get room for four ints per table entry and buffer; the one-block-per-role form uses three)
-    const size_t smem = size_t(p.tail) * sizeof(double) + size_t(8 * p.tab_cap) * sizeof(int) +
-                        size_t(2 * p.ncol) * (sizeof(int4) + sizeof(int)) + size_t(2 * (CW_THREADS / 32) + 4) * sizeof(int);
-    if (smem > CW_SMEM_LIMIT) return NNVB_OK;
+    // two to four stages, as many as fit beside the tables (four ints per table entry and buffer, the tiles' boxes,
+    // query numbers and flags): where the stages are small the producers run further ahead of the consumers
+    const size_t stage_bytes = size_t(p.in_stage + p.w_stage) * sizeof(double);
+    const size_t fixed = size_t(8 * p.tab_cap) * sizeof(int) + size_t(2 * p.ncol) * (sizeof(int4) + sizeof(int)) +
+                         size_t(2 * (CW_THREADS / 32) + 4) * sizeof(int);
+    if (fixed + 2 * stage_bytes > CW_SMEM_LIMIT) return NNVB_OK;
+    p.stages = int(std::min<size_t>(CW_MAX_STAGES, (CW_SMEM_LIMIT - fixed) / stage_bytes));
+    p.tail = p.stages * (p.in_stage + p.w_stage);
+    const size_t smem = fixed + p.stages * stage_bytes;
     const unsigned grid = (unsigned)std::min<int64_t>(p.n_flat, sm_count_of_current_device());
-    static const bool no_ws = getenv("NNVB_NO_WARP_SPEC") != nullptr;
-    if (WS && !no_ws) {
-        // deeper pipeline where the stages are small: the producers then run further ahead of the consumers
-        const size_t stage_bytes = size_t(p.in_stage + p.w_stage) * sizeof(double);
-        const size_t fixed = smem - 2 * stage_bytes;
-        p.stages = int(std::min<size_t>(CW_MAX_STAGES, (CW_SMEM_LIMIT - fixed) / stage_bytes));
-        p.tail = p.stages * (p.in_stage + p.w_stage);
-        const size_t smem_ws = fixed + p.stages * stage_bytes;
-        static int* err = nullptr;
-        if (err == nullptr) NNVB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_ws_wait_timeout));
-        auto kern = conv_win_ws_kernel<KH, WARPS_M, WARPS_N, NROWS>;
-        NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_ws));
-        kern<<<grid, WS_THREADS, smem_ws, st>>>(p, w.w, bn, mask, win.box, col_base, ncols, err);
-    } else {
-        auto kern = conv_win_persist_kernel<KH, WARPS_M, WARPS_N, NROWS>;
-        NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        kern<<<grid, CW_THREADS, smem, st>>>(p, w.w, bn, mask, win.box, col_base, ncols);
-    }
+    static int* err = nullptr;
+    if (err == nullptr) NNVB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&err), g_ws_wait_timeout));
+    auto kern = conv_win_ws_kernel<KH, WARPS_M, WARPS_N, NROWS>;
+    NNVB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, WS_THREADS, smem, st>>>(p, w.w, bn, mask, win.box, col_base, ncols, err);
     NNVB_CUDA(cudaGetLastError());
     *done = true;
     return NNVB_OK;

@@ -17,7 +17,7 @@ import pytest
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 SWITCHES = ["NNVB_NO_WINDOWS", "NNVB_ZERO_FILL", "NNVB_NO_CONV_WIN", "NNVB_NO_RANGE_SKIP", "NNVB_EAGER_RELU",
-            "NNVB_EAGER_MASK", "NNVB_NO_FC_GATHER", "NNVB_NO_HOT_POOL", "NNVB_NO_PACK", "NNVB_NO_COMPACT", "NNVB_NO_PERSIST", "NNVB_NO_WARP_SPEC", "NNVB_POOL_ONE_ROW", "NNVB_POISON"]
+            "NNVB_EAGER_MASK", "NNVB_NO_FC_GATHER", "NNVB_NO_HOT_POOL", "NNVB_NO_PACK", "NNVB_NO_COMPACT", "NNVB_NO_PERSIST", "NNVB_POOL_ONE_ROW", "NNVB_POISON"]
 
 
 def _run(tmp_path, switch):
